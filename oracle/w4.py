@@ -1,0 +1,54 @@
+"""INT4 affine weights: packing, dequantisation and the small-M product.
+
+Layout (volundr-mlx/convert.py:7-14, :82-96; tests/reference.py:26-36 `w4_pack_row`): codes u in [0, 15] packed
+eight to a uint32, nibble j of word w = element 8 w + j, lowest nibble first; bf16 scales and biases [N, K/G].
+The reference converter always has bias = -8 scale (convert.py:11-14) and its test pins dequant == bf16(q * scale)
+exactly for that case (tests/test_volundr.py:127-156). For a free bias the rounding of s*u + b inside
+mx.dequantize is not pinned by any reference test ("parity unpinned"); it is defined here as the exact sum rounded
+once to bf16, which agrees with the pinned case because s*(u-8) is exact in fp32."""
+import numpy as np
+
+from .numerics import bf, bf_from_f64_exact
+
+
+def pack_codes(u):
+    """u [N, K] ints in [0, 15] -> uint32 [N, K/8] (tests/reference.py:26-36 with nibble = q + 8 already applied)."""
+    u = np.asarray(u, dtype=np.uint32)
+    N, K = u.shape
+    assert K % 8 == 0 and u.max() <= 15
+    w = np.zeros((N, K // 8), dtype=np.uint32)
+    for j in range(8):
+        w |= u[:, j::8] << np.uint32(4 * j)
+    return w
+
+
+def unpack_codes(w, K):
+    w = np.asarray(w, dtype=np.uint32)
+    N = w.shape[0]
+    u = np.zeros((N, K), dtype=np.uint32)
+    for j in range(8):
+        u[:, j::8] = (w >> np.uint32(4 * j)) & np.uint32(0xF)
+    return u
+
+
+def dequant(w, scales, biases, group):
+    """bf16(s * u + b), the exact sum rounded once -> float32 [N, K] (bf16-valued).
+    s * u is exact in float64 (8-bit by 4-bit significands); the float64 sum's remainder is recovered with TwoSum."""
+    s = np.asarray(scales, dtype=np.float64)
+    b = np.asarray(biases, dtype=np.float64)
+    N, Gq = s.shape
+    K = Gq * group
+    u = unpack_codes(w, K).astype(np.float64)
+    p = u * np.repeat(s, group, axis=1)
+    bb = np.repeat(b, group, axis=1)
+    r = p + bb
+    bv = r - p
+    err = (p - (r - bv)) + (bb - bv)  # TwoSum remainder: p + bb == r + err exactly
+    return bf_from_f64_exact(r, err)
+
+
+def matmul(x, w, scales, biases, group, acc=np.float64):
+    """y = bf16(x . dequant(w)^T): what nn.QuantizedLinear computes (volundr.py:185-190), fp32 accumulation in the
+    reference; float64 here so the oracle carries no accumulation-order noise of its own (tolerance rtol 2e-2)."""
+    W = dequant(w, scales, biases, group).astype(acc)
+    return bf((np.asarray(x, dtype=acc) @ W.T).astype(np.float32))

@@ -1,0 +1,48 @@
+"""ctypes binding of libvolundr_b200.so (the C ABI declared in include/volundr_b200.h).
+
+There is no CPU or PyTorch fallback behind these calls: a missing library or a non-zero return raises."""
+import ctypes
+from ctypes import c_int, c_size_t, c_void_p, c_char_p, c_float, c_longlong
+from pathlib import Path
+
+_LIB = None
+_PATH = Path(__file__).resolve().parent / "libvolundr_b200.so"
+
+# name -> (restype, argtypes). Every exported symbol of include/volundr_b200.h appears here.
+SIGNATURES = {
+    "vk_version": (c_int, []),
+    "vk_set_pdl": (None, [c_int]),
+    "vk_status_fetch": (c_int, [c_void_p, c_void_p]),
+    "vk_status_string": (c_char_p, [c_int]),
+    "vk_w4_packed_bytes": (c_size_t, [c_int, c_int]),
+    "vk_w4_repack": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p]),
+    "vk_w4_dequant": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p]),
+    "vk_w4_force_plan": (None, [c_int, c_int]),
+    "vk_w4_workspace_bytes": (c_size_t, [c_int, c_int, c_int]),
+    "vk_w4_gemm": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_size_t, c_void_p]),
+}
+
+
+def path() -> Path:
+    return _PATH
+
+
+def lib():
+    """The loaded library; raises if it has not been built (python -m volundr_mlx_b200.build)."""
+    global _LIB
+    if _LIB is None:
+        if not _PATH.exists():
+            raise RuntimeError(f"{_PATH} is missing: build it with `python -m volundr_mlx_b200.build` "
+                               "(there is no fallback path)")
+        L = ctypes.CDLL(str(_PATH))
+        for name, (res, args) in SIGNATURES.items():
+            f = getattr(L, name)
+            f.restype, f.argtypes = res, args
+        _LIB = L
+    return _LIB
+
+
+def check(rc: int, what: str):
+    if rc != 0:
+        kind = "invalid argument" if rc == -1 else "workspace too small" if rc == -2 else f"CUDA error {rc}"
+        raise RuntimeError(f"{what}: {kind}")

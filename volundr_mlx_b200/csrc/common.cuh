@@ -1,0 +1,128 @@
+// Shared device helpers for the sm_100a kernels: bf16 bit handling, bounded mbarrier waits, 1-D TMA bulk copies,
+// programmatic dependent launch (PDL) and the launch wrapper every kernel in this library goes through.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define VK_OK 0
+#define VK_EINVAL (-1)
+#define VK_ENOSPC (-2)
+
+// Device-side status word: 0 = fine; otherwise the code of the first kernel that gave up on a bounded wait or met
+// an out-of-range index. Read (and cleared) by vk_status_read at the caller's sync point.
+__device__ int g_vk_status = 0;  // (the library is one translation unit: volundr_b200.cu)
+enum : int {
+    VK_ST_MBAR_TIMEOUT = 1,   // a TMA bulk copy did not complete within the spin limit
+    VK_ST_BAD_INDEX = 2,      // page / block index outside its pool
+    VK_ST_POOL_EMPTY = 3,     // the page allocator ran out of free pages
+    VK_ST_FLAG_TIMEOUT = 4,   // a split-K / peer flag wait ran out
+};
+
+__device__ __forceinline__ void vk_set_status(int code) { atomicCAS(&g_vk_status, 0, code); }
+
+// ---------------------------------------------------------------- bf16 <-> fp32 on raw bits
+__device__ __forceinline__ float bf_lo(uint32_t u) { return __uint_as_float(u << 16); }
+__device__ __forceinline__ float bf_hi(uint32_t u) { return __uint_as_float(u & 0xFFFF0000u); }
+__device__ __forceinline__ float bf2f(__nv_bfloat16 x) { return __bfloat162float(x); }
+__device__ __forceinline__ __nv_bfloat16 f2bf(float x) { return __float2bfloat16_rn(x); }
+// fp32 -> the fp32 value of its bf16 rounding (round to nearest even)
+__device__ __forceinline__ float bfr(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
+__device__ __forceinline__ uint32_t pack_bf2(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// ---------------------------------------------------------------- warp / block reductions (fixed order)
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+// Sum over a block of NW warps; `red` holds NW floats of shared memory. Every thread gets the total. The order of
+// the additions is fixed (xor tree inside a warp, then warps 0..NW-1), so results do not depend on scheduling.
+template <int NW>
+__device__ __forceinline__ float block_sum(float v, float* red) {
+    v = warp_sum(v);
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+    __syncthreads();
+    float t = 0.f;
+#pragma unroll
+    for (int i = 0; i < NW; i++) t += red[i];
+    return t;
+}
+
+// ---------------------------------------------------------------- mbarrier + TMA bulk (1-D) copies
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_fence_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t phase) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(phase)
+        : "memory");
+    return ok != 0;
+}
+// Wait for phase `phase` of `bar` with an iteration limit. Returns false (and records VK_ST_MBAR_TIMEOUT) when the
+// limit runs out, so a copy that never lands ends the kernel instead of hanging the GPU.
+#define VK_MBAR_SPIN_LIMIT (1u << 22)
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t phase) {
+    for (uint32_t i = 0; i < VK_MBAR_SPIN_LIMIT; i++) {
+        if (mbar_try_wait(bar, phase)) return true;
+    }
+    vk_set_status(VK_ST_MBAR_TIMEOUT);
+    return false;
+}
+// global -> shared bulk copy through the TMA engine; both addresses 16-byte aligned, bytes a multiple of 16.
+__device__ __forceinline__ void tma_bulk_g2s(void* dst_smem, const void* src_gmem, uint32_t bytes, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_u32(dst_smem)),
+        "l"(src_gmem), "r"(bytes), "r"(smem_u32(bar))
+        : "memory");
+}
+
+// ---------------------------------------------------------------- programmatic dependent launch
+// pdl_wait: block until the kernels this one depends on have completed and their writes are visible. Everything a
+// kernel does before it may only touch memory no earlier kernel of the stream writes (weights, its own smem).
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+// Host: launch with the PDL attribute (the kernel must call pdl_wait before reading its inputs).
+bool vk_pdl_enabled();
+template <typename... KArgs, typename... Args>
+static inline cudaError_t vk_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                    Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = vk_pdl_enabled() ? 1 : 0;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
+#define VK_CUDA(call)                              \
+    do {                                           \
+        cudaError_t e_ = (call);                   \
+        if (e_ != cudaSuccess) return (int)e_;     \
+    } while (0)

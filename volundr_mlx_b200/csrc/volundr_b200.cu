@@ -1,0 +1,3 @@
+// Single translation unit of libvolundr_b200.so (one device link unit: the status word is shared by every kernel).
+#include "runtime.cu"
+#include "w4_gemm.cu"

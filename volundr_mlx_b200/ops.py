@@ -1,0 +1,91 @@
+"""torch-facing wrappers of the C ABI: tensors in, tensors out, raw pointers and the current stream underneath."""
+import torch
+
+from . import _lib
+
+BF16 = torch.bfloat16
+
+
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _p(t):
+    return None if t is None else t.data_ptr()
+
+
+class W4Weight:
+    """An INT4 affine weight in the GEMM's streaming layout (1152-byte chunks of 32 rows x 64 columns)."""
+
+    def __init__(self, packed, N, K, group):
+        self.packed, self.N, self.K, self.group = packed, N, K, group
+
+    @property
+    def nbytes(self):
+        return self.packed.numel()
+
+
+def w4_repack(w, scales, biases, group=64) -> W4Weight:
+    """Reference layout (uint32 [N, K/8] codes as int32 tensor, bf16 scales/biases [N, K/group]) -> W4Weight."""
+    L = _lib.lib()
+    N, K = w.shape[0], w.shape[1] * 8
+    assert w.dtype == torch.int32 and scales.dtype == BF16 and biases.dtype == BF16
+    assert scales.shape == (N, K // group) == biases.shape
+    packed = torch.empty(L.vk_w4_packed_bytes(N, K), dtype=torch.uint8, device=w.device)
+    _lib.check(L.vk_w4_repack(_p(w.contiguous()), _p(scales.contiguous()), _p(biases.contiguous()), N, K, group,
+                              _p(packed), _stream()), "vk_w4_repack")
+    return W4Weight(packed, N, K, group)
+
+
+def w4_dequant(w, scales, biases, group=64):
+    L = _lib.lib()
+    N, K = w.shape[0], w.shape[1] * 8
+    out = torch.empty((N, K), dtype=BF16, device=w.device)
+    _lib.check(L.vk_w4_dequant(_p(w.contiguous()), _p(scales.contiguous()), _p(biases.contiguous()), N, K, group,
+                               _p(out), _stream()), "vk_w4_dequant")
+    return out
+
+
+_ws = {}
+
+
+def workspace(nbytes, device):
+    """One grow-only scratch buffer per device: split-K arrival counters (zero between launches) then the partial
+    sums. Allocated outside the step's hot loop."""
+    key = str(device)
+    buf = _ws.get(key)
+    if buf is None or buf.numel() < nbytes:
+        buf = torch.zeros(max(nbytes, 1 << 25), dtype=torch.uint8, device=device)
+        _ws[key] = buf
+    return buf
+
+
+def w4_gemm(x, wt: W4Weight, out=None):
+    """y[M, N] = x[M, K] . dequant(W)^T, bf16 in / out, fp32 accumulation."""
+    L = _lib.lib()
+    assert x.dtype == BF16 and x.dim() == 2 and x.shape[1] == wt.K and x.stride(1) == 1
+    M = x.shape[0]
+    if out is None:
+        out = torch.empty((M, wt.N), dtype=BF16, device=x.device)
+    need = L.vk_w4_workspace_bytes(min(M, 16), wt.N, wt.K)
+    ws = workspace(need, x.device)
+    _lib.check(L.vk_w4_gemm(_p(wt.packed), _p(x), x.stride(0), _p(out), out.stride(0), M, wt.N, wt.K, _p(ws),
+                            ws.numel(), _stream()), "vk_w4_gemm")
+    return out
+
+
+_status_buf = {}
+
+
+def check_status(device=None):
+    """Read and clear the device status word (synchronises); raises if a kernel recorded an error."""
+    L = _lib.lib()
+    device = device or torch.device("cuda", torch.cuda.current_device())
+    key = str(device)
+    if key not in _status_buf:
+        _status_buf[key] = torch.zeros(1, dtype=torch.int32, device=device)
+    buf = _status_buf[key]
+    _lib.check(L.vk_status_fetch(_p(buf), _stream()), "vk_status_fetch")
+    code = int(buf.item())
+    if code:
+        raise RuntimeError("volundr_b200 device status: " + L.vk_status_string(code).decode())
