@@ -49,6 +49,83 @@ int vk_w4_gemm(const void* packed, const void* x, int ldx, void* y, int ldy, int
 /* Testing aid: force warps per CTA (4 or 8) and the number of K slabs; 0 = choose automatically. */
 void vk_w4_force_plan(int warps, int split);
 
+/* ---- row-wise fused kernels (one CTA per token row). bf16 activations [B, D] unless noted. */
+/* x = embed[tok]; H[b][0..3] = x; hn = RMSNorm(x) * w_mhc0 (volundr-mlx/volundr.py:921-930, :944; batch.py:525-538).
+ * With engram_prev != NULL also advances the id window [B, max(order) - 1] and hashes the n-gram rows
+ * engram_rows_out [B, n_orders] (volundr.py:572-582; host ints `orders`). */
+int vk_embed(const int* tok, const void* embed, const void* w_mhc0, void* H, void* hn, int* engram_prev,
+             int* engram_rows_out, const int* orders, int n_orders, int engram_rows, int B, int D, float eps,
+             vk_stream_t stream);
+/* MHC.mix_norm (volundr.py:336-340; decode_fused.py:230-248; ops: volundr.py:264-278, :237-243): dyn linear, pre /
+ * post, Sinkhorn, x_in, h = OffsetRMSNorm(x_in) * (1 + w_in). post [B,4], res [B,16] are fp32 holding bf16 values. */
+int vk_mhc_mix_norm(const void* H, const void* hn, const void* w_dyn, const void* pre_s, const void* post_s,
+                    const void* res_s, const void* w_in, void* x_in, void* h, float* post, float* res, int B, int D,
+                    int iters, float eps, vk_stream_t stream);
+/* kernels.rms_norm(x, w, eps, offset, r) (kernels.py:285-306; volundr.py:893-899): h2 = bf16(x + r) (r, h2 may be
+ * NULL), hn = RMSNorm(h2) * (offset + w). */
+int vk_add_rmsnorm(const void* x, const void* r, const void* w, void* h2, void* hn, int B, int D, float eps, int offset,
+                   vk_stream_t stream);
+/* _silu_mul (volundr.py:166-168) on gu = [gate (I) | up (I)] rows of stride ld_gu. */
+int vk_silu_mul(const void* gu, void* act, int B, int I, int ld_gu, vk_stream_t stream);
+/* Engram row gather + RMSNorm (volundr.py:594-595). tables / ld_table / col0 are host arrays of n_orders entries. */
+int vk_engram_gather(const void* const* tables, const int* ld_table, const int* col0, const int* rows, const void* w,
+                     void* e, int B, int n_orders, int dim, float eps, vk_stream_t stream);
+/* Residual add + (Engram gate) + MHC.combine_norm (volundr.py:342-347, :281-290, :594-597; decode_fused.py:341-355):
+ * H updated in place; hn = next layer's mHC norm of the stream mean, or with final_norm the model's final norm of
+ * stream 0 (volundr.py:949). */
+int vk_mhc_combine_norm(void* H, const void* h2, const void* m, const void* x_in, const float* post, const float* res,
+                        const void* w_next, void* hn, const void* eng_val, const void* eng_gate_w, const void* eng_gate_b,
+                        void* y_out, int B, int D, int final_norm, float eps, vk_stream_t stream);
+/* The linears kept in bf16 (convert.py:16-17): y = bf16(x . W^T + bias), W [N, K] row-major. */
+int vk_bf16_gemm(const void* x, int ldx, const void* W, const void* bias, void* y, int ldy, int M, int N, int K,
+                 vk_stream_t stream);
+/* Greedy token: first maximum over logits[:, :valid] (scheduler.py:391). */
+int vk_argmax(const void* logits, int ld, int valid, int* out, int B, vk_stream_t stream);
+
+/* ---- Kimi Delta Attention decode step (KDA.__call__, volundr.py:388-410: DF.kda_conv_gates decode_fused.py:469-493,
+ * kernels.gated_delta_vec kernels.py:446-458, kernels.gated_norm kernels.py:918-928, plus in_proj_b and f_up).
+ * proj [B, ldp] = [q | k | v | z (at off_z) | f_down (at off_fd)]; conv [2, slots, 3, C] with *parity naming the
+ * current buffer; S fp32 [slots, HV, 128, 128] updated in place; out [B, HV*128]. */
+int vk_kda_step(const void* proj, int ldp, int off_z, int off_fd, const void* h, const void* w_b, const void* w_fup,
+                const float* conv_w, const float* A_log, const float* dt_bias, const void* norm_w, void* conv,
+                const int* parity, size_t conv_stride, float* S, void* out, const float* g_override, int B, int D, int Hk,
+                int HV, int Dk, int Dv, int rank, float eps, vk_stream_t stream);
+
+/* ---- paged ragged attention (64-token pages). */
+typedef struct vk_attn_geom {
+    int Hq, KVH, D;        /* heads of this shard, head dim (128) */
+    int W, C, topk;        /* BCSA window, block size, far blocks kept; W = 0: dense causal attention */
+    int IH, Di;            /* indexer heads / dim (indexer mode) */
+    int NS;                /* selection groups: 1 = shared indexer (reference), KVH = per kv head from pooled keys */
+    int far_tokens;        /* 1: far keys are the tokens of the chosen blocks, 0: their mean-pooled K/V (reference) */
+    int max_pages, n_pages;
+} vk_attn_geom;
+/* BatchRows / BCSAStep (batch.py:52-122) on the GPU: allocates a page from free_list[--*free_top] for every row whose
+ * next position opens one (rows in order) and writes desc [B, 8] = {pos, page, row in page, closes a block, nv, nf,
+ * keys attended, window start}. */
+int vk_batch_step_begin(const int* pos, int* table, int max_pages, int* free_list, int* free_top, int* desc, int B, int W,
+                        int C, int topk, vk_stream_t stream);
+/* BatchRows.advance (batch.py:74-77): pos += 1; flips *parity. */
+int vk_batch_step_end(int* pos, int* parity, int B, vk_stream_t stream);
+/* Attention._batched up to the cache write (volundr.py:737-747; batch.py:224-259): q/k offset norms, RoPE at pos[b],
+ * K/V into the row's page, indexer query/key norms, and the pooled means of a block the step closes. */
+int vk_attn_prep(const vk_attn_geom* g, const void* proj, int ldp, int off_k, int off_v, const void* idxq, const void* idxk,
+                 const void* q_norm, const void* k_norm, const void* idx_norm, const int* pos, const int* table, void* q,
+                 void* qi, void* K, void* V, void* PK, void* PV, void* BK, void* IK, int B, int rope_dims, double rope_theta,
+                 float eps, vk_stream_t stream);
+/* _block_scores + _topk_blocks (volundr.py:601-618; kernels.bcsa_scores kernels.py:1227-1240, bcsa_topk :86-98):
+ * sel [B, NS, topk] ascending block indices (-1 padded), nsel [B, NS]. scratch: max_blocks uint32 per (row, group). */
+size_t vk_bcsa_select_scratch_bytes(const vk_attn_geom* g, int B, int max_blocks);
+int vk_bcsa_select(const vk_attn_geom* g, const void* q, const void* keys, const int* pos, const int* table, void* scratch,
+                   int max_blocks, int* sel, int* nsel, int B, vk_stream_t stream);
+/* The SDPA of _bcsa_batched / BatchKVCache.attend (volundr.py:790-791; batch.py:315-316) over window pages and far
+ * keys, split over `nsplit` CTAs per (row, kv head), merged, times sigmoid(gate) (volundr.py:177-179).
+ * part: fp32 scratch of vk_attend_scratch_bytes. out [B, Hq*D]. */
+size_t vk_attend_scratch_bytes(const vk_attn_geom* g, int B, int nsplit);
+int vk_attend_decode(const vk_attn_geom* g, const void* q, const void* K, const void* V, const void* PK, const void* PV,
+                     const int* pos, const int* table, const int* sel, const int* nsel, const void* proj, int ldp,
+                     void* part, int nsplit, void* out, int B, vk_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,431 @@
+"""Batched decode with per-row positions: B live sequences of different lengths, one token each per step.
+
+Mirrors the reference's batch.py: `BatchCache(model)` (batch.py:323-515: `.B .pos .keys .row(key) .apply(leave, join)
+.capture_row`) and `forward(model, bc, toks, capture) -> (logits [B, V], features)` (batch.py:518-554). Differences
+that come with the hardware:
+  * Rows live in fixed slots 0..B-1 of preallocated device buffers; positions, the page table and the page free
+    list live on the GPU and advance there, so a step launches the same kernels with the same arguments every time
+    and is replayed as one CUDA graph (the reference rebuilds a lazy graph per step and pipelines the host work,
+    batch.py:368-414; here there is no per-step host work to hide).
+  * Attention K/V live in 64-token pages of a shared pool instead of per-row rings padded to the longest row
+    (batch.py:8-15); BCSAStep's host-side index lists (batch.py:94-122) are computed inside the kernels.
+  * Snapshots are clones (`capture_row`): PyTorch has no copy-on-write arrays (session.py:13-28 relies on MLX's).
+"""
+import ctypes
+import math
+
+import numpy as np
+import torch
+
+from . import _lib, ops
+from .volundr import BF16, Model
+
+PAGE = 64
+
+
+def _p(t):
+    return None if t is None else t.data_ptr()
+
+
+class _Geom(ctypes.Structure):
+    _fields_ = [(n, ctypes.c_int) for n in ("Hq", "KVH", "D", "W", "C", "topk", "IH", "Di", "NS", "far_tokens",
+                                            "max_pages", "n_pages")]
+
+
+class BatchCache:
+    def __init__(self, model: Model, max_rows: int = 16, n_pages: int = 1024, max_pages_per_row: int = None, seed: int = 0):
+        a, d = model.args, model.device
+        self.model, self.args, self.S = model, a, max_rows
+        self.keys, self._pos = [], []
+        self.n_pages = n_pages
+        self.max_pages = max_pages_per_row or n_pages
+        S, D = max_rows, a.hidden_size
+        i32 = dict(dtype=torch.int32, device=d)
+        self.pos = torch.zeros(S, **i32)
+        self.tok = torch.zeros(S, **i32)
+        self.table = torch.full((S, self.max_pages), -1, **i32)
+        # the page pool is handed out in a shuffled order (a seeded permutation): pages of a row are not contiguous
+        perm = np.random.Generator(np.random.PCG64(seed)).permutation(n_pages).astype(np.int32)
+        self.free_list = torch.from_numpy(perm).to(d)
+        self.free_top = torch.tensor([n_pages], **i32)
+        self.desc = torch.zeros((S, 8), **i32)
+        self.parity = torch.zeros(1, **i32)
+        self.greedy = torch.zeros(S, **i32)
+        bf = dict(dtype=BF16, device=d)
+        f32 = dict(dtype=torch.float32, device=d)
+        m = model
+        self.has_bcsa = "bcsa" in a.mixer_types
+        self.indexer = self.has_bcsa and a.bcsa_score == "indexer"
+        C = a.bcsa_compress
+        self.layers = []
+        for mix in a.mixer_types:
+            if mix == "kda":
+                Cc = 2 * m.Hk * 128 + m.HV * 128
+                self.layers.append({"conv": torch.zeros((2, S, 3, Cc), **bf), "S": torch.zeros((S, m.HV, 128, 128), **f32)})
+            else:
+                st = {"K": torch.zeros((n_pages, m.KVH, PAGE, 128), **bf), "V": torch.zeros((n_pages, m.KVH, PAGE, 128), **bf)}
+                if mix == "bcsa":
+                    st["PK"] = torch.zeros((n_pages, m.KVH, PAGE // C, 128), **bf)
+                    st["PV"] = torch.zeros((n_pages, m.KVH, PAGE // C, 128), **bf)
+                    if self.indexer:
+                        st["BK"] = torch.zeros((n_pages, PAGE // C, a.bcsa_index_dim), **bf)
+                        st["IK"] = torch.zeros((S, C, a.bcsa_index_dim), **bf)
+                self.layers.append(st)
+        self.keep = max(a.engram_orders) - 1 if a.engram_layers else 0
+        self.engram_prev = torch.full((S, max(self.keep, 1)), -1, **i32)
+        self.engram_rows = torch.zeros((S, max(len(a.engram_orders), 1)), **i32)
+        # ---- activations of one step (fixed addresses: the step is captured as a CUDA graph)
+        wid = 0
+        for w in m.layers:
+            wid = max(wid, w["proj"].N)
+        self.H = torch.zeros((S, 4, D), **bf)
+        self.hn, self.x_in, self.h = (torch.zeros((S, D), **bf) for _ in range(3))
+        self.post, self.res = torch.zeros((S, 4), **f32), torch.zeros((S, 16), **f32)
+        self.proj = torch.zeros((S, wid), **bf)
+        self.mix = torch.zeros((S, max(m.HV * 128, m.Hq * 128)), **bf)
+        self.r, self.h2, self.hn2, self.mlp = (torch.zeros((S, D), **bf) for _ in range(4))
+        self.gu = torch.zeros((S, 2 * m.I), **bf)
+        self.act = torch.zeros((S, m.I), **bf)
+        self.logits = torch.zeros((S, m.lm_head.shape[0]), **bf)
+        self.y_dbg = None
+        self.q = torch.zeros((S, m.Hq, 128), **bf)
+        if self.indexer:
+            self.qi = torch.zeros((S, a.bcsa_index_heads, a.bcsa_index_dim), **bf)
+            self.idxq = torch.zeros((S, a.bcsa_index_heads * a.bcsa_index_dim), **bf)
+            self.idxk = torch.zeros((S, a.bcsa_index_dim), **bf)
+        self.NS = (1 if self.indexer else m.KVH) if self.has_bcsa else 0
+        self.sel = torch.full((S, max(self.NS, 1), max(a.bcsa_topk, 1)), -1, **i32)
+        self.nsel = torch.zeros((S, max(self.NS, 1)), **i32)
+        self.max_blocks = self.max_pages * (PAGE // C) if self.has_bcsa else 1
+        self.sel_scratch = torch.zeros((S, max(self.NS, 1), self.max_blocks), **i32)
+        self.nsplit_bcsa, self.nsplit_dense = 8, 32
+        self.part = torch.zeros((S, m.Hq, max(self.nsplit_bcsa, self.nsplit_dense), 130), **f32)
+        if a.engram_layers:
+            cat = a.engram_dim * len(a.engram_orders)
+            self.eng_e = torch.zeros((S, cat), **bf)
+            self.eng_val = torch.zeros((S, D), **bf)
+        self.orders = (ctypes.c_int * 4)(*(list(a.engram_orders) + [0] * 4)[:4])
+        self.geom = {}
+        for mix in ("bcsa", "attn"):
+            g = _Geom()
+            g.Hq, g.KVH, g.D = m.Hq, m.KVH, 128
+            bc = mix == "bcsa"
+            g.W, g.C, g.topk = (a.bcsa_window, C, a.bcsa_topk) if bc else (0, 1, 1)
+            g.IH, g.Di = a.bcsa_index_heads, a.bcsa_index_dim
+            g.NS = self.NS if bc else 0
+            g.far_tokens = 1 if a.bcsa_far == "tokens" else 0
+            g.max_pages, g.n_pages = self.max_pages, n_pages
+            self.geom[mix] = g
+        self.graphs = {}
+        self.use_graph = True
+        self.steps = 0
+
+    # ------------------------------------------------------------------ membership
+    @property
+    def B(self):
+        return len(self.keys)
+
+    def host_pos(self):
+        return list(self._pos)
+
+    def row(self, key) -> int:
+        return self.keys.index(key)
+
+    def _sync_rows(self):
+        self.pos[: self.B] = torch.tensor(self._pos, dtype=torch.int32, device=self.pos.device) if self.B else self.pos[:0]
+
+    def apply(self, leave=(), join=()):
+        """Remove the rows of the keys in `leave` (swap-remove: the last row moves into the hole, batch.py:416-431)
+        and append one fresh row (position 0, zero state) per key in `join`."""
+        torch.cuda.synchronize(self.pos.device)
+        for b in sorted((self.keys.index(k) for k in leave), reverse=True):
+            last = self.B - 1
+            self._release_pages(b)
+            if b != last:
+                self._move_row(last, b)
+            self._clear_row(last)
+            self.keys[b], self._pos[b] = self.keys[last], self._pos[last]
+            self.keys.pop()
+            self._pos.pop()
+        for key in join:
+            assert self.B < self.S, "batch is full"
+            b = self.B
+            self._clear_row(b)
+            self.keys.append(key)
+            self._pos.append(0)
+        self._sync_rows()
+
+    def _release_pages(self, b):
+        n = (self._pos[b] + PAGE - 1) // PAGE
+        if n:
+            top = int(self.free_top.item())
+            self.free_list[top: top + n] = self.table[b, :n].flip(0)
+            self.free_top += n
+            self.table[b, :n] = -1
+
+    def _par(self):
+        return self.steps & 1
+
+    def _move_row(self, src, dst):
+        par = self._par()
+        for st in self.layers:
+            if "S" in st:
+                st["S"][dst] = st["S"][src]
+                st["conv"][par, dst] = st["conv"][par, src]
+            elif "IK" in st:
+                st["IK"][dst] = st["IK"][src]
+        self.table[dst] = self.table[src]
+        self.engram_prev[dst] = self.engram_prev[src]
+
+    def _clear_row(self, b):
+        for st in self.layers:
+            if "S" in st:
+                st["S"][b].zero_()
+                st["conv"][:, b].zero_()
+            elif "IK" in st:
+                st["IK"][b].zero_()
+        self.table[b] = -1
+        self.engram_prev[b] = -1
+
+    def capture_row(self, key):
+        """The row's decode state as own copies (batch.py:488-510): position, per-layer ("arrays", conv, state) /
+        ("kv", P, keys, values) / ("bcsa", ...) tuples gathered from the pages, ("engram", keep, prev)."""
+        torch.cuda.synchronize(self.pos.device)
+        b, P = self.keys.index(key), self._pos[self.keys.index(key)]
+        npg = (P + PAGE - 1) // PAGE
+        pages = self.table[b, :npg].long()
+        a = self.args
+        out = []
+        for mix, st in zip(a.mixer_types, self.layers):
+            if mix == "kda":
+                out.append(("arrays", st["conv"][self._par(), b].clone(), st["S"][b].clone()))
+            else:
+                k = st["K"][pages].permute(1, 0, 2, 3).reshape(self.model.KVH, npg * PAGE, 128)[:, :P].clone()
+                v = st["V"][pages].permute(1, 0, 2, 3).reshape(self.model.KVH, npg * PAGE, 128)[:, :P].clone()
+                if mix == "attn":
+                    out.append(("kv", P, k, v))
+                else:
+                    C = a.bcsa_compress
+                    nb = P // C
+                    pk = st["PK"][pages].permute(1, 0, 2, 3).reshape(self.model.KVH, -1, 128)[:, :nb].clone()
+                    pv = st["PV"][pages].permute(1, 0, 2, 3).reshape(self.model.KVH, -1, 128)[:, :nb].clone()
+                    bk = st["BK"][pages].reshape(-1, a.bcsa_index_dim)[:nb].clone() if "BK" in st else None
+                    ik = st["IK"][b].clone() if "IK" in st else None
+                    out.append(("bcsa", a.bcsa_window, C, a.bcsa_topk, P, nb, k, v, pk, pv, bk, ik))
+        out.append(("engram", self.keep, self.engram_prev[b, : self.keep].clone()))
+        return {"pos": P, "layers": out}
+
+    # ------------------------------------------------------------------ synthetic contexts (benchmarks, kernel tests)
+    def fill_synthetic(self, keys, ctx_lens, seed=0):
+        """Rows that already hold `ctx_lens[i]` tokens: pages allocated from the shuffled pool, K/V ~ N(0,1) (bf16),
+        pooled block means computed from them, KDA state ~ N(0, 0.1) fp32, conv state ~ N(0, 1)."""
+        assert self.B == 0 and len(keys) <= self.S
+        dev = self.pos.device
+        gen = torch.Generator(device=dev)
+        gen.manual_seed(seed)
+        self.keys, self._pos = list(keys), [int(c) for c in ctx_lens]
+        top = self.n_pages
+        fl = self.free_list.cpu().numpy()
+        tab = np.full((self.S, self.max_pages), -1, np.int32)
+        for b, P in enumerate(self._pos):
+            n = (P + PAGE - 1) // PAGE
+            assert n <= self.max_pages and n <= top
+            for i in range(n):
+                top -= 1
+                tab[b, i] = fl[top]
+        self.table.copy_(torch.from_numpy(tab))
+        self.free_top.fill_(top)
+        C = self.args.bcsa_compress
+        for st in self.layers:
+            if "S" in st:
+                st["S"].normal_(0, 0.1, generator=gen)
+                st["conv"].normal_(0, 1, generator=gen)
+            else:
+                for nm in ("K", "V"):
+                    buf = st[nm]
+                    for i in range(0, self.n_pages, 256):  # chunked: the pool can be many GB
+                        buf[i:i + 256].normal_(0, 1, generator=gen)
+                if "PK" in st:
+                    for i in range(0, self.n_pages, 256):
+                        for nm, pn in (("K", "PK"), ("V", "PV")):
+                            x = st[nm][i:i + 256].float().reshape(-1, st[nm].shape[1], PAGE // C, C, 128)
+                            st[pn][i:i + 256] = (x.sum(3) * (1.0 / C)).to(BF16)
+                    if "BK" in st:
+                        st["BK"].normal_(0, 1, generator=gen)
+                        st["IK"].normal_(0, 1, generator=gen)
+        self._sync_rows()
+        torch.cuda.synchronize(dev)
+
+    def state_bytes_per_step(self):
+        """Bytes of per-row state one decode step must move: KDA state read + written, conv state, K/V rows read."""
+        a, m = self.args, self.model
+        n = 0
+        for mix, st in zip(a.mixer_types, self.layers):
+            if mix == "kda":
+                n += self.B * (2 * st["S"][0].numel() * 4 + 2 * st["conv"][0, 0].numel() * 2)
+            else:
+                for P in self._pos:
+                    if mix == "attn":
+                        keys = P + 1
+                    else:
+                        W, C = a.bcsa_window, a.bcsa_compress
+                        nv = max(0, (P - W + 1) // C)
+                        nf = min(nv, a.bcsa_topk)
+                        keys = min(P + 1, W) + (nf * C if a.bcsa_far == "tokens" else nf)
+                        if nv > a.bcsa_topk:  # scoring reads one pooled key per valid block (per kv head)
+                            n += nv * (m.KVH * 128 * 2 if a.bcsa_score == "pooled_key" else a.bcsa_index_dim * 2)
+                    n += keys * m.KVH * 128 * 2 * 2
+        return n
+
+
+def _launch_step(model: Model, bc: BatchCache, capture=()):
+    """Enqueue one decode step for rows 0..B-1 on the current stream (VolundrModel._fused_layers, volundr.py:939-949;
+    DecoderLayer.__call__ :887-906 with split=True; batch.forward, batch.py:518-554)."""
+    L = _lib.lib()
+    a, B, D = model.args, bc.B, model.args.hidden_size
+    st = torch.cuda.current_stream().cuda_stream
+    eps = a.rms_norm_eps
+    ck = _lib.check
+    tp = model.tp_size > 1
+    ws = ops.workspace(1 << 26, model.device)
+    caps = []
+
+    def gemm(x, wt, y):
+        ck(L.vk_w4_gemm(_p(wt.packed), _p(x), x.stride(0), _p(y), y.stride(0), B, wt.N, wt.K, _p(ws), ws.numel(), st),
+           "vk_w4_gemm")
+
+    def allreduce(t):
+        if tp:
+            torch.distributed.all_reduce(t[:B], group=model.group)
+
+    w0 = model.layers[0]
+    ck(L.vk_embed(_p(bc.tok), _p(model.embed), _p(w0["mhc_norm"]), _p(bc.H), _p(bc.hn),
+                  _p(bc.engram_prev) if a.engram_layers else None, _p(bc.engram_rows), bc.orders,
+                  len(a.engram_orders) if a.engram_layers else 0, a.engram_rows, B, D, eps, st), "vk_embed")
+    if bc.has_bcsa or "attn" in a.mixer_types:
+        ck(L.vk_batch_step_begin(_p(bc.pos), _p(bc.table), bc.max_pages, _p(bc.free_list), _p(bc.free_top), _p(bc.desc), B,
+                                 a.bcsa_window if bc.has_bcsa else 0, a.bcsa_compress, a.bcsa_topk, st), "vk_batch_step_begin")
+    nl = len(model.layers)
+    for i, (w, lst) in enumerate(zip(model.layers, bc.layers)):
+        if i in capture:
+            caps.append(bc.H[:B, 0].clone())
+        ck(L.vk_mhc_mix_norm(_p(bc.H), _p(bc.hn), _p(w["dyn"]), _p(w["pre_s"]), _p(w["post_s"]), _p(w["res_s"]),
+                             _p(w["ln_in"]), _p(bc.x_in), _p(bc.h), _p(bc.post), _p(bc.res), B, D, a.mhc_sinkhorn_iters,
+                             eps, st), "vk_mhc_mix_norm")
+        gemm(bc.h, w["proj"], bc.proj)
+        if w["mixer"] == "kda":
+            nmix = model.HV * 128
+            ck(L.vk_kda_step(_p(bc.proj), bc.proj.stride(0), w["off_z"], w["off_fd"], _p(bc.h), _p(w["in_proj_b"]),
+                             _p(w["f_up"]), _p(w["conv_w"]), _p(w["A_log"]), _p(w["dt_bias"]), _p(w["gnorm"]),
+                             _p(lst["conv"]), _p(bc.parity), lst["conv"][0].numel(), _p(lst["S"]), _p(bc.mix), None, B, D,
+                             model.Hk, model.HV, 128, 128, a.kda_gate_rank, eps, st), "vk_kda_step")
+        else:
+            bcsa = w["mixer"] == "bcsa"
+            g = bc.geom[w["mixer"]]
+            nmix = model.Hq * 128
+            idx = bcsa and bc.indexer
+            if idx:
+                ck(L.vk_bf16_gemm(_p(bc.h), D, _p(w["idx_q"]), None, _p(bc.idxq), bc.idxq.stride(0), B,
+                                  w["idx_q"].shape[0], D, st), "vk_bf16_gemm")
+                ck(L.vk_bf16_gemm(_p(bc.h), D, _p(w["idx_k"]), None, _p(bc.idxk), bc.idxk.stride(0), B,
+                                  w["idx_k"].shape[0], D, st), "vk_bf16_gemm")
+            ck(L.vk_attn_prep(ctypes.byref(g), _p(bc.proj), bc.proj.stride(0), w["off_k"], w["off_v"],
+                              _p(bc.idxq) if idx else None, _p(bc.idxk) if idx else None, _p(w["q_norm"]), _p(w["k_norm"]),
+                              _p(w["idx_norm"]) if idx else None, _p(bc.pos), _p(bc.table), _p(bc.q),
+                              _p(bc.qi) if idx else None, _p(lst["K"]), _p(lst["V"]), _p(lst.get("PK")), _p(lst.get("PV")),
+                              _p(lst.get("BK")), _p(lst.get("IK")), B, model.rope_dims, float(a.rope_theta), eps, st),
+               "vk_attn_prep")
+            if bcsa:
+                ck(L.vk_bcsa_select(ctypes.byref(g), _p(bc.qi) if idx else _p(bc.q), _p(lst["BK"]) if idx else _p(lst["PK"]),
+                                    _p(bc.pos), _p(bc.table), _p(bc.sel_scratch), bc.max_blocks, _p(bc.sel), _p(bc.nsel), B,
+                                    st), "vk_bcsa_select")
+            ck(L.vk_attend_decode(ctypes.byref(g), _p(bc.q), _p(lst["K"]), _p(lst["V"]), _p(lst.get("PK")),
+                                  _p(lst.get("PV")), _p(bc.pos), _p(bc.table), _p(bc.sel), _p(bc.nsel), _p(bc.proj),
+                                  bc.proj.stride(0), _p(bc.part), bc.nsplit_bcsa if bcsa else bc.nsplit_dense, _p(bc.mix), B,
+                                  st), "vk_attend_decode")
+        mixv = bc.mix[:, :nmix]
+        gemm(mixv, w["out"], bc.r)
+        allreduce(bc.r)
+        ck(L.vk_add_rmsnorm(_p(bc.x_in), _p(bc.r), _p(w["ln_post"]), _p(bc.h2), _p(bc.hn2), B, D, eps, 1, st),
+           "vk_add_rmsnorm")
+        gemm(bc.hn2, w["gate_up"], bc.gu)
+        ck(L.vk_silu_mul(_p(bc.gu), _p(bc.act), B, model.I, bc.gu.stride(0), st), "vk_silu_mul")
+        gemm(bc.act, w["down"], bc.mlp)
+        allreduce(bc.mlp)
+        eng = "eng_norm" in w
+        if eng:
+            ptrs, lds, c0 = w["eng_ptrs"]
+            ck(L.vk_engram_gather(ptrs.ctypes.data_as(ctypes.c_void_p), lds.ctypes.data_as(ctypes.c_void_p),
+                                  c0.ctypes.data_as(ctypes.c_void_p), _p(bc.engram_rows), _p(w["eng_norm"]), _p(bc.eng_e),
+                                  B, len(a.engram_orders), a.engram_dim, eps, st), "vk_engram_gather")
+            val = bc.eng_e
+            if a.engram_value:
+                ck(L.vk_bf16_gemm(_p(bc.eng_e), bc.eng_e.stride(0), _p(w["eng_value"]), None, _p(bc.eng_val), D, B, D,
+                                  bc.eng_e.shape[1], st), "vk_bf16_gemm")
+                val = bc.eng_val
+        last = i + 1 == nl
+        w_next = model.norm_w if last else model.layers[i + 1]["mhc_norm"]
+        ck(L.vk_mhc_combine_norm(_p(bc.H), _p(bc.h2), _p(bc.mlp), _p(bc.x_in), _p(bc.post), _p(bc.res), _p(w_next),
+                                 _p(bc.hn), _p(val) if eng else None, _p(w["eng_gate_w"]) if eng else None,
+                                 _p(w["eng_gate_b"]) if eng else None, _p(bc.y_dbg) if bc.y_dbg is not None else None, B, D,
+                                 1 if last else 0, eps, st), "vk_mhc_combine_norm")
+    V = model.lm_head.shape[0]
+    ck(L.vk_bf16_gemm(_p(bc.hn), D, _p(model.lm_head), None, _p(bc.logits), bc.logits.stride(0), B, V, D, st), "vk_bf16_gemm")
+    if not tp:
+        ck(L.vk_argmax(_p(bc.logits), bc.logits.stride(0), min(a.vocab_valid, V), _p(bc.greedy), B, st), "vk_argmax")
+    ck(L.vk_batch_step_end(_p(bc.pos), _p(bc.parity), B, st), "vk_batch_step_end")
+    return caps
+
+
+def forward(model: Model, bc: BatchCache, toks, capture=()):
+    """One decode step of every row: toks [B] int32 (tensor on the device, or a host sequence). Returns
+    (logits [B, V] bf16, features [B, len(capture) * hidden] or None); the rows' positions advance by one. The
+    greedy token of each row (first maximum over the valid vocabulary, scheduler.py:391) is left in bc.greedy[:B].
+    The returned tensors are views of step buffers: they are overwritten by the next step."""
+    B = bc.B
+    assert B > 0
+    if not torch.is_tensor(toks):
+        toks = torch.tensor(list(toks), dtype=torch.int32)
+    bc.tok[:B].copy_(toks.to(torch.int32), non_blocking=True)
+    key = (B, tuple(capture))
+    if bc.use_graph and not capture and model.tp_size == 1:
+        g = bc.graphs.get(key)
+        if g is None:
+            # warm-up launch outside capture is not possible without advancing the rows, so capture directly; the
+            # library's kernels need no lazy initialisation beyond the first GEMM's attribute calls
+            model_warm(model)
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                _launch_step(model, bc, capture)
+            bc.graphs[key] = g
+        g.replay()
+        caps = []
+    else:
+        caps = _launch_step(model, bc, capture)
+    bc.steps += 1
+    bc._pos = [p + 1 for p in bc._pos]
+    feats = torch.cat(caps, dim=-1) if caps else None
+    return bc.logits[:B], feats
+
+
+_warm = set()
+
+
+def model_warm(model: Model):
+    """Run each GEMM shape once on scratch activations so that one-time function-attribute calls happen outside
+    graph capture."""
+    key = id(model)
+    if key in _warm:
+        return
+    _warm.add(key)
+    d = model.device
+    seen = set()
+    for w in model.layers:
+        for nm in ("proj", "out", "gate_up", "down"):
+            wt = w[nm]
+            for M in (1, 16):
+                if (wt.N, wt.K, M) in seen:
+                    continue
+                seen.add((wt.N, wt.K, M))
+                ops.w4_gemm(torch.zeros((M, wt.K), dtype=BF16, device=d), wt)
+    torch.cuda.synchronize(d)

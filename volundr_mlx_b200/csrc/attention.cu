@@ -1,0 +1,609 @@
+// Gated attention of the decode step over a paged, ragged KV cache: dense GQA and BCSA (local window + top-k far
+// blocks, one joint softmax). Replaces Attention._batched / _bcsa_batched (volundr.py:737-791), the per-row index
+// arithmetic of BCSAStep (batch.py:94-122), BatchBCSACache.write_ring / close_blocks (batch.py:224-259),
+// BatchKVCache.attend (batch.py:306-316), _block_scores / _topk_blocks (volundr.py:601-618; kernels.py:8-98,
+// 1168-1240) and the SDPA call (volundr.py:790).
+//
+// Layout. One page table [slot, max_pages] serves every attention layer: page i of a row holds its positions
+// [64 i, 64 i + 64). Per layer: K, V pools bf16 [n_pages, KVH, 64, D] (post-norm, post-RoPE keys); pooled means of
+// closed blocks of C positions PK, PV bf16 [n_pages, KVH, 64/C, D] (block j of a row sits in its page j C / 64, slot
+// j mod 64/C); in indexer mode pooled indexer keys BK bf16 [n_pages, 64/C, Di] and the open block's keys
+// IK [slot, C, Di]. The reference keeps a ring of the last W positions per row (slot p mod W); a page table holds the
+// same positions without wrap-around and without padding rows to the longest one. Everything a step needs (slot,
+// closing block, valid far blocks nv = max(0, (p - W + 1) / C), key counts) is derived on the GPU from pos[b].
+//
+// Modes (far, score): (pooled, indexer) is the reference: far keys are PK/PV rows picked by the shared indexer heads.
+// (tokens, pooled_key) is the 64-token-block form: far keys are the tokens of the picked blocks, a block's score per
+// kv head comes from that head's query heads against PK. Scores follow the reference's rounding chain
+// bf16(bf16(mean_h fp32(bf16(q_h . k_j))) * scale) with the dot summed in a fixed order (4 consecutive elements per
+// lane, then an xor tree), so the selected indices are reproducible bit for bit.
+#include "common.cuh"
+
+namespace {
+
+constexpr int kPage = 64;
+constexpr int kD = 128;  // head dim handled by these kernels
+
+struct AttnGeom {
+    int Hq, KVH, W, C, topk, IH, Di, NS;   // NS: selection groups (KVH in pooled_key mode, 1 in indexer mode, 0 dense)
+    int far_tokens;                        // 1: far keys are tokens of the selected blocks; 0: pooled rows
+    int max_pages;
+};
+
+// ------------------------------------------------------------------------------------------------ step bookkeeping
+// For every row: allocate a page when the new token opens one (rows in order, so the assignment is deterministic),
+// and write the step descriptor {pos, page id, row in page, closes block?, nv, nf, key count, window start}.
+__global__ void batch_step_begin_kernel(const int* __restrict__ pos, int* __restrict__ table, int max_pages,
+                                        int* __restrict__ free_list, int* __restrict__ free_top, int* __restrict__ desc,
+                                        int B, int W, int C, int topk) {
+    pdl_launch_dependents();
+    pdl_wait();
+    if (threadIdx.x != 0) return;
+    int top = *free_top;
+    for (int b = 0; b < B; b++) {
+        const int p = pos[b];
+        const int pi = p / kPage;
+        if (pi >= max_pages) { vk_set_status(VK_ST_BAD_INDEX); continue; }
+        if (p % kPage == 0) {
+            if (top <= 0) { vk_set_status(VK_ST_POOL_EMPTY); continue; }
+            table[b * max_pages + pi] = free_list[--top];
+        }
+        const int nv = W > 0 ? max(0, (p - W + 1) / C) : 0;
+        const int nf = min(nv, topk);
+        const int lo = W > 0 ? max(0, p - W + 1) : 0;
+        int* d = desc + b * 8;
+        d[0] = p; d[1] = table[b * max_pages + pi]; d[2] = p % kPage; d[3] = (W > 0 && (p + 1) % C == 0) ? 1 : 0;
+        d[4] = nv; d[5] = nf; d[6] = (p - lo + 1) + nf; d[7] = lo;
+    }
+    *free_top = top;
+}
+
+// every row holds one more token; the KDA conv-state buffers swap roles
+__global__ void batch_step_end_kernel(int* pos, int* parity, int B) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int b = blockIdx.x * blockDim.x + threadIdx.x;
+    if (b < B) pos[b] += 1;
+    if (b == 0 && parity != nullptr) *parity ^= 1;
+}
+
+// ------------------------------------------------------------------------------------------------ projections -> cache
+struct PrepParams {
+    const __nv_bfloat16* proj;    // [B, ldp]: per q head [q (D) | gate (D)], then k [KVH, D] at off_k, v at off_v
+    const __nv_bfloat16* idxq;    // [B, IH*Di] or null
+    const __nv_bfloat16* idxk;    // [B, Di] or null
+    const __nv_bfloat16* q_norm;  // [D] offset-norm weights
+    const __nv_bfloat16* k_norm;
+    const __nv_bfloat16* idx_norm;  // [Di]
+    const int* pos;               // [B]
+    const int* table;             // [slots, max_pages]
+    __nv_bfloat16* q;             // [B, Hq, D]
+    __nv_bfloat16* qi;            // [B, IH, Di]
+    __nv_bfloat16 *K, *V, *PK, *PV, *BK, *IK;
+    int ldp, off_k, off_v, n_pages, rope_dims;
+    double log2_theta;
+    float eps;
+    AttnGeom g;
+};
+
+// offset RMSNorm of one 128-vector held 4 elements per lane; returns bf16-rounded values
+__device__ __forceinline__ void head_norm128(float (&x)[4], const __nv_bfloat16* w, int lane, float eps) {
+    float ss = x[0] * x[0] + x[1] * x[1] + x[2] * x[2] + x[3] * x[3];
+    ss = warp_sum(ss);
+    const float inv = rsqrtf(ss * (1.f / 128.f) + eps);
+#pragma unroll
+    for (int e = 0; e < 4; e++) x[e] = bfr((x[e] * inv) * (1.f + bf2f(w[4 * lane + e])));
+}
+
+__device__ __forceinline__ void load4(const __nv_bfloat16* p, int lane, float (&x)[4]) {
+    const uint2 u = *reinterpret_cast<const uint2*>(p + 4 * lane);
+    x[0] = bf_lo(u.x); x[1] = bf_hi(u.x); x[2] = bf_lo(u.y); x[3] = bf_hi(u.y);
+}
+__device__ __forceinline__ void store4(__nv_bfloat16* p, int lane, const float (&x)[4]) {
+    uint2 u;
+    u.x = pack_bf2(x[0], x[1]);
+    u.y = pack_bf2(x[2], x[3]);
+    *reinterpret_cast<uint2*>(p + 4 * lane) = u;
+}
+
+// NeoX rotate-half on the first rd dims of a 128-vector spread 4 per lane, angle = pos * theta^(-2i/rd) in double.
+__device__ __forceinline__ void rope128(float (&x)[4], int lane, int pos, int rd, double log2_theta) {
+    const int half = rd / 2;
+    float other[4];
+    // partner lane holds the element half a rotation away
+    const int shift = half / 4;  // lanes per half (rd a multiple of 8)
+#pragma unroll
+    for (int e = 0; e < 4; e++) {
+        const float up = __shfl_down_sync(0xffffffffu, x[e], shift);
+        const float dn = __shfl_up_sync(0xffffffffu, x[e], shift);
+        other[e] = (4 * lane < half) ? up : dn;
+    }
+#pragma unroll
+    for (int e = 0; e < 4; e++) {
+        const int d = 4 * lane + e;
+        if (d < rd) {
+            const int i = d < half ? d : d - half;
+            const double ang = (double)pos * exp2(-(2.0 * i / rd) * log2_theta);
+            double sn, cs;
+            sincos(ang, &sn, &cs);
+            const double v = d < half ? (double)x[e] * cs - (double)other[e] * sn : (double)x[e] * cs + (double)other[e] * sn;
+            x[e] = bfr((float)v);
+        }
+    }
+}
+
+__global__ void __launch_bounds__(256) attn_prep_kernel(const PrepParams p) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int b = blockIdx.x;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const AttnGeom& g = p.g;
+    const int pos = p.pos[b];
+    const int page = p.table[b * g.max_pages + pos / kPage];
+    const int row = pos % kPage;
+    if (page < 0 || page >= p.n_pages) {
+        if (threadIdx.x == 0) vk_set_status(VK_ST_BAD_INDEX);
+        return;
+    }
+    const __nv_bfloat16* pr = p.proj + (size_t)b * p.ldp;
+    const int nheads = g.Hq + 2 * g.KVH + (p.idxq ? g.IH + 1 : 0);
+    for (int hd = warp; hd < nheads; hd += 8) {
+        float x[4];
+        if (hd < g.Hq) {                                   // query head: norm, rope
+            load4(pr + (size_t)hd * 2 * kD, lane, x);
+            head_norm128(x, p.q_norm, lane, p.eps);
+            rope128(x, lane, pos, p.rope_dims, p.log2_theta);
+            store4(p.q + ((size_t)b * g.Hq + hd) * kD, lane, x);
+        } else if (hd < g.Hq + g.KVH) {                    // key head: norm, rope, into the page
+            const int kv = hd - g.Hq;
+            load4(pr + p.off_k + (size_t)kv * kD, lane, x);
+            head_norm128(x, p.k_norm, lane, p.eps);
+            rope128(x, lane, pos, p.rope_dims, p.log2_theta);
+            store4(p.K + (((size_t)page * g.KVH + kv) * kPage + row) * kD, lane, x);
+        } else if (hd < g.Hq + 2 * g.KVH) {                // value head: as projected
+            const int kv = hd - g.Hq - g.KVH;
+            load4(pr + p.off_v + (size_t)kv * kD, lane, x);
+            store4(p.V + (((size_t)page * g.KVH + kv) * kPage + row) * kD, lane, x);
+        } else if (hd < g.Hq + 2 * g.KVH + g.IH) {         // indexer query heads
+            const int ih = hd - g.Hq - 2 * g.KVH;
+            load4(p.idxq + ((size_t)b * g.IH + ih) * kD, lane, x);
+            head_norm128(x, p.idx_norm, lane, p.eps);
+            store4(p.qi + ((size_t)b * g.IH + ih) * kD, lane, x);
+        } else {                                           // indexer key of this position -> open block slot
+            load4(p.idxk + (size_t)b * kD, lane, x);
+            head_norm128(x, p.idx_norm, lane, p.eps);
+            store4(p.IK + ((size_t)b * g.C + pos % g.C) * kD, lane, x);
+        }
+    }
+    if (g.W <= 0 || (pos + 1) % g.C != 0) return;
+    // ---- the step closes block pos / C: means of its C rows (added in order in fp32, times 1/C, rounded once)
+    __syncthreads();  // this CTA's K / V / IK writes above are visible to its own reads below
+    const int slot = (pos / g.C) % (kPage / g.C);
+    const int r0 = row - (g.C - 1);
+    const float invc = 1.f / (float)g.C;
+    const int njobs = 2 * g.KVH + (p.idxq ? 1 : 0);
+    for (int j = warp; j < njobs; j += 8) {
+        float acc[4] = {0.f, 0.f, 0.f, 0.f};
+        if (j < 2 * g.KVH) {
+            const int kv = j >> 1;
+            const __nv_bfloat16* src = (j & 1 ? p.V : p.K) + (((size_t)page * g.KVH + kv) * kPage + r0) * kD;
+            for (int i = 0; i < g.C; i++) {
+                float x[4];
+                load4(src + (size_t)i * kD, lane, x);
+#pragma unroll
+                for (int e = 0; e < 4; e++) acc[e] += x[e];
+            }
+#pragma unroll
+            for (int e = 0; e < 4; e++) acc[e] = bfr(acc[e] * invc);
+            __nv_bfloat16* dst = (j & 1 ? p.PV : p.PK) + (((size_t)page * g.KVH + kv) * (kPage / g.C) + slot) * kD;
+            store4(dst, lane, acc);
+        } else {
+            for (int i = 0; i < g.C; i++) {
+                float x[4];
+                load4(p.IK + ((size_t)b * g.C + i) * kD, lane, x);
+#pragma unroll
+                for (int e = 0; e < 4; e++) acc[e] += x[e];
+            }
+#pragma unroll
+            for (int e = 0; e < 4; e++) acc[e] = bfr(acc[e] * invc);
+            store4(p.BK + ((size_t)page * (kPage / g.C) + slot) * kD, lane, acc);
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------------ far-block selection
+struct SelectParams {
+    const __nv_bfloat16* q;       // score queries: qi [B, IH, Di] (indexer) or q [B, Hq, D] (pooled_key)
+    const __nv_bfloat16* keys;    // BK [n_pages, 64/C, Di] (indexer) or PK [n_pages, KVH, 64/C, D] (pooled_key)
+    const int* pos;
+    const int* table;
+    uint32_t* scratch;            // [B, NS, cap] sort keys
+    int* sel;                     // [B, NS, topk] ascending block indices, -1 padded
+    int* nsel;                    // [B, NS]
+    int cap, n_pages;
+    float scale;                  // Di^-1/2
+    AttnGeom g;
+};
+
+__device__ __forceinline__ uint32_t score_key(float s, int j) {
+    const uint32_t u = __float_as_uint(s) >> 16;  // s is bf16-valued
+    const uint32_t mono = (u & 0x8000u) ? (0xFFFFu - u) : (u | 0x8000u);
+    return (mono << 16) | (0xFFFFu - (uint32_t)j);
+}
+
+__global__ void __launch_bounds__(256) bcsa_select_kernel(const SelectParams p) {
+    __shared__ int hist[256];
+    __shared__ uint32_t s_prefix;
+    __shared__ int s_k;
+    __shared__ int wcount[8];
+    __shared__ int s_base;
+    pdl_launch_dependents();
+    pdl_wait();
+    const AttnGeom& g = p.g;
+    const int ns = blockIdx.x, b = blockIdx.y;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int pos = p.pos[b];
+    const int nv = max(0, (pos - g.W + 1) / g.C);
+    int* sel = p.sel + ((size_t)b * g.NS + ns) * g.topk;
+    if (nv <= g.topk) {
+        for (int i = threadIdx.x; i < g.topk; i += 256) sel[i] = i < nv ? i : -1;
+        if (threadIdx.x == 0) p.nsel[b * g.NS + ns] = nv;
+        return;
+    }
+    if (nv > p.cap || nv > 65536) {
+        if (threadIdx.x == 0) { vk_set_status(VK_ST_BAD_INDEX); p.nsel[b * g.NS + ns] = 0; }
+        return;
+    }
+    const bool per_kv = g.NS > 1;
+    const int nh = per_kv ? g.Hq / g.KVH : g.IH;
+    const __nv_bfloat16* qb = per_kv ? p.q + ((size_t)b * g.Hq + (size_t)ns * nh) * kD : p.q + (size_t)b * g.IH * kD;
+    const int spp = kPage / g.C;  // pooled slots per page
+    uint32_t* keys = p.scratch + ((size_t)b * g.NS + ns) * p.cap;
+    float qv[8][4];
+    for (int h = 0; h < nh; h++) load4(qb + (size_t)h * kD, lane, qv[h]);
+    const float inv_nh = 1.f / (float)nh;
+    for (int j = warp; j < nv; j += 8) {
+        const int page = p.table[b * g.max_pages + (j / spp)];
+        const __nv_bfloat16* kr = per_kv ? p.keys + (((size_t)page * g.KVH + ns) * spp + j % spp) * kD
+                                         : p.keys + ((size_t)page * spp + j % spp) * kD;
+        float kx[4];
+        load4(kr, lane, kx);
+        float s = 0.f;
+        for (int h = 0; h < nh; h++) {
+            float a = qv[h][0] * kx[0];
+            a = fmaf(qv[h][1], kx[1], a);
+            a = fmaf(qv[h][2], kx[2], a);
+            a = fmaf(qv[h][3], kx[3], a);
+            a = warp_sum(a);
+            s += bfr(a);
+        }
+        s = bfr(s * inv_nh);
+        s = bfr(s * p.scale);
+        if (lane == 0) keys[j] = score_key(s, j);
+    }
+    __syncthreads();
+    // ---- radix select: the topk-th largest key (keys are unique), 8 bits per pass from the top
+    if (threadIdx.x == 0) { s_prefix = 0; s_k = g.topk; }
+    uint32_t mask = 0;
+    for (int pass = 3; pass >= 0; pass--) {
+        const int shift = 8 * pass;
+        hist[threadIdx.x] = 0;
+        __syncthreads();
+        const uint32_t prefix = s_prefix;
+        for (int j = threadIdx.x; j < nv; j += 256) {
+            const uint32_t k = __ldcg(keys + j);
+            if ((k & mask) == prefix) atomicAdd(&hist[(k >> shift) & 0xFF], 1);
+        }
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            int need = s_k, d = 255;
+            for (; d > 0; d--) {
+                if (hist[d] >= need) break;
+                need -= hist[d];
+            }
+            s_k = need;
+            s_prefix = prefix | ((uint32_t)d << shift);
+        }
+        mask |= 0xFFu << shift;
+        __syncthreads();
+    }
+    const uint32_t thr = s_prefix;
+    // ---- ordered compaction: indices of keys >= thr, ascending
+    if (threadIdx.x == 0) s_base = 0;
+    __syncthreads();
+    for (int j0 = 0; j0 < nv; j0 += 256) {
+        const int j = j0 + threadIdx.x;
+        const bool take = j < nv && __ldcg(keys + j) >= thr;
+        const uint32_t bal = __ballot_sync(0xffffffffu, take);
+        if (lane == 0) wcount[warp] = __popc(bal);
+        __syncthreads();
+        int off = s_base;
+        for (int w = 0; w < warp; w++) off += wcount[w];
+        if (take) {
+            const int r = off + __popc(bal & ((1u << lane) - 1u));
+            if (r < g.topk) sel[r] = j;
+        }
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            int t = 0;
+            for (int w = 0; w < 8; w++) t += wcount[w];
+            s_base += t;
+        }
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) p.nsel[b * g.NS + ns] = g.topk;
+}
+
+// ------------------------------------------------------------------------------------------------ attention
+struct AttendParams {
+    const __nv_bfloat16* q;     // [B, Hq, D]
+    const __nv_bfloat16 *K, *V, *PK, *PV;
+    const int* pos;
+    const int* table;
+    const int* sel;             // [B, NS, topk] or null
+    const int* nsel;
+    float* part;                // [B, KVH, nsplit, G, D + 2]: O (D), m, l
+    int nsplit, n_pages;
+    float scale;
+    AttnGeom g;
+};
+
+constexpr int kRowStride = kD + 8;  // bf16 elements; keeps 16-byte row reads conflict-free
+
+template <int G>
+__global__ void __launch_bounds__(128) attend_decode_kernel(const AttendParams p) {
+    __shared__ __align__(16) __nv_bfloat16 Ks[kPage * kRowStride];
+    __shared__ __align__(16) __nv_bfloat16 Vs[kPage * kRowStride];
+    __shared__ __align__(16) float qs[G * kD];
+    __shared__ float sc[G * kPage];
+    __shared__ float umax[G], usum[G];
+    __shared__ const __nv_bfloat16* rowK[kPage];
+    __shared__ const __nv_bfloat16* rowV[kPage];
+    pdl_launch_dependents();
+    pdl_wait();
+    const AttnGeom& g = p.g;
+    const int split = blockIdx.x, kv = blockIdx.y, b = blockIdx.z;
+    const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
+    const int pos = p.pos[b];
+    const int lo = g.W > 0 ? max(0, pos - g.W + 1) : 0;
+    const int wp0 = lo / kPage, nwp = pos / kPage - wp0 + 1;
+    const int ns = g.NS > 1 ? kv : 0;
+    const int nf = (p.sel != nullptr && g.NS > 0) ? p.nsel[b * g.NS + ns] : 0;
+    const int* sel = p.sel ? p.sel + ((size_t)b * g.NS + ns) * g.topk : nullptr;
+    const int spp = g.W > 0 ? kPage / g.C : 1;
+    const int nfu = g.far_tokens ? nf : (nf + kPage - 1) / kPage;  // far units
+    const int U = nwp + nfu;
+
+    for (int i = t; i < G * kD; i += 128) qs[i] = bf2f(p.q[((size_t)b * g.Hq + (size_t)kv * G) * kD + i]) * p.scale;
+    float m_run[G], l_run[G], O[G];
+#pragma unroll
+    for (int h = 0; h < G; h++) { m_run[h] = -INFINITY; l_run[h] = 0.f; O[h] = 0.f; }
+
+    for (int u = split; u < U; u += p.nsplit) {
+        __syncthreads();
+        // ---- which rows make up this unit
+        int nrows;
+        if (u < nwp) {
+            const int page = p.table[b * g.max_pages + wp0 + u];
+            const int ra = u == 0 ? lo % kPage : 0;
+            const int rb = u == nwp - 1 ? pos % kPage : kPage - 1;
+            nrows = rb - ra + 1;
+            if (t < nrows) {
+                const size_t off = (((size_t)page * g.KVH + kv) * kPage + ra + t) * kD;
+                rowK[t] = p.K + off;
+                rowV[t] = p.V + off;
+            }
+        } else if (g.far_tokens) {
+            const int j = sel[u - nwp];
+            const int tok0 = j * g.C;
+            const int page = p.table[b * g.max_pages + tok0 / kPage];
+            nrows = g.C;
+            if (t < nrows) {
+                const size_t off = (((size_t)page * g.KVH + kv) * kPage + tok0 % kPage + t) * kD;
+                rowK[t] = p.K + off;
+                rowV[t] = p.V + off;
+            }
+        } else {
+            const int f0 = (u - nwp) * kPage;
+            nrows = min(kPage, nf - f0);
+            if (t < nrows) {
+                const int j = sel[f0 + t];
+                const int page = p.table[b * g.max_pages + (j / spp)];
+                const size_t off = (((size_t)page * g.KVH + kv) * spp + j % spp) * kD;
+                rowK[t] = p.PK + off;
+                rowV[t] = p.PV + off;
+            }
+        }
+        __syncthreads();
+        // ---- stage the rows (16 bytes per thread per go: 16 threads per 256-byte row)
+        for (int i = t; i < nrows * 16; i += 128) {
+            const int r = i >> 4, cch = i & 15;
+            *reinterpret_cast<uint4*>(Ks + r * kRowStride + cch * 8) = *reinterpret_cast<const uint4*>(rowK[r] + cch * 8);
+            *reinterpret_cast<uint4*>(Vs + r * kRowStride + cch * 8) = *reinterpret_cast<const uint4*>(rowV[r] + cch * 8);
+        }
+        __syncthreads();
+        // ---- scores: thread (key i = t % 64, heads h = t / 64, t / 64 + 2, ...)
+        {
+            const int i = t & 63;
+            for (int h = t >> 6; h < G; h += 2) {
+                float a = -INFINITY;
+                if (i < nrows) {
+                    a = 0.f;
+                    const __nv_bfloat16* kr = Ks + i * kRowStride;
+                    const float* qh = qs + h * kD;
+#pragma unroll 4
+                    for (int d = 0; d < kD; d += 8) {
+                        const uint4 kk = *reinterpret_cast<const uint4*>(kr + d);
+                        a = fmaf(bf_lo(kk.x), qh[d], a); a = fmaf(bf_hi(kk.x), qh[d + 1], a);
+                        a = fmaf(bf_lo(kk.y), qh[d + 2], a); a = fmaf(bf_hi(kk.y), qh[d + 3], a);
+                        a = fmaf(bf_lo(kk.z), qh[d + 4], a); a = fmaf(bf_hi(kk.z), qh[d + 5], a);
+                        a = fmaf(bf_lo(kk.w), qh[d + 6], a); a = fmaf(bf_hi(kk.w), qh[d + 7], a);
+                    }
+                }
+                sc[h * kPage + i] = a;
+            }
+        }
+        __syncthreads();
+        // ---- softmax pieces of this unit per head (warp w takes heads w, w + 4, ...): max, exp, sum
+        for (int h = warp; h < G; h += 4) {
+            const float s0 = sc[h * kPage + lane], s1 = sc[h * kPage + 32 + lane];
+            const float mx = warp_max(fmaxf(s0, s1));  // finite: a unit has at least one row
+            const float p0 = __expf(s0 - mx), p1 = __expf(s1 - mx);
+            sc[h * kPage + lane] = p0;
+            sc[h * kPage + 32 + lane] = p1;
+            const float sum = warp_sum(p0 + p1);
+            if (lane == 0) { umax[h] = mx; usum[h] = sum; }
+        }
+        __syncthreads();
+        // every thread keeps the running max / sum of every head (identical values in all threads)
+        float w_unit[G];
+#pragma unroll
+        for (int h = 0; h < G; h++) {
+            const float mx = umax[h];
+            const float m_new = fmaxf(m_run[h], mx);
+            const float a_old = m_run[h] == -INFINITY ? 0.f : __expf(m_run[h] - m_new);
+            const float a_new = __expf(mx - m_new);
+            l_run[h] = l_run[h] * a_old + usum[h] * a_new;
+            O[h] *= a_old;
+            w_unit[h] = a_new;
+            m_run[h] = m_new;
+        }
+        // ---- O[h][d = t] += sum_i p[h][i] V[i][t]
+        for (int i = 0; i < nrows; i++) {
+            const float v = bf2f(Vs[i * kRowStride + t]);
+#pragma unroll
+            for (int h = 0; h < G; h++) O[h] = fmaf(sc[h * kPage + i] * w_unit[h], v, O[h]);
+        }
+    }
+    float* out = p.part + (((size_t)b * g.KVH + kv) * p.nsplit + split) * G * (kD + 2);
+#pragma unroll
+    for (int h = 0; h < G; h++) {
+        out[h * (kD + 2) + t] = O[h];
+        if (t == 0) { out[h * (kD + 2) + kD] = m_run[h]; out[h * (kD + 2) + kD + 1] = l_run[h]; }
+    }
+}
+
+// merge the splits of one query head, divide, round, apply sigmoid(gate) (volundr.py:177-179, :752-753)
+__global__ void __launch_bounds__(128) attend_merge_kernel(const float* __restrict__ part, const __nv_bfloat16* __restrict__ proj,
+                                                           int ldp, __nv_bfloat16* __restrict__ out, int Hq, int KVH,
+                                                           int nsplit) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int hq = blockIdx.x, b = blockIdx.y, t = threadIdx.x;
+    const int G = Hq / KVH, kv = hq / G, h = hq % G;
+    const float* base = part + (((size_t)b * KVH + kv) * nsplit) * G * (kD + 2) + (size_t)h * (kD + 2);
+    float m = -INFINITY;
+    for (int s = 0; s < nsplit; s++) m = fmaxf(m, base[(size_t)s * G * (kD + 2) + kD]);
+    float l = 0.f, o = 0.f;
+    for (int s = 0; s < nsplit; s++) {
+        const float* ps = base + (size_t)s * G * (kD + 2);
+        const float ms = ps[kD];
+        if (ms == -INFINITY) continue;
+        const float w = __expf(ms - m);
+        l = fmaf(ps[kD + 1], w, l);
+        o = fmaf(ps[t], w, o);
+    }
+    const float ob = bfr(o / l);
+    const float gate = bf2f(proj[(size_t)b * ldp + (size_t)hq * 2 * kD + kD + t]);
+    out[((size_t)b * Hq + hq) * kD + t] = f2bf(ob * (1.f / (1.f + expf(-gate))));
+}
+
+template <int G>
+cudaError_t launch_attend(const AttendParams& p, int B, cudaStream_t stream) {
+    return vk_launch(attend_decode_kernel<G>, dim3(p.nsplit, p.g.KVH, B), dim3(128), 0, stream, p);
+}
+
+}  // namespace
+
+extern "C" {
+
+struct vk_attn_geom {
+    int Hq, KVH, D, W, C, topk, IH, Di, NS, far_tokens, max_pages, n_pages;
+};
+
+static int geom_ok(const vk_attn_geom* gm) {
+    if (gm->D != kD || gm->Hq <= 0 || gm->KVH <= 0 || gm->Hq % gm->KVH != 0 || gm->Hq / gm->KVH > 8) return 0;
+    if (gm->W > 0) {
+        if (gm->C <= 0 || kPage % gm->C != 0 || gm->W % gm->C != 0 || gm->topk <= 0) return 0;
+        if (gm->NS != 1 && gm->NS != gm->KVH) return 0;
+        if (gm->NS == 1 && (gm->Di != kD || gm->IH <= 0 || gm->IH > 8)) return 0;
+    }
+    return 1;
+}
+static AttnGeom to_geom(const vk_attn_geom* gm) {
+    AttnGeom g = {gm->Hq, gm->KVH, gm->W, gm->C, gm->topk, gm->IH, gm->Di, gm->W > 0 ? gm->NS : 0, gm->far_tokens, gm->max_pages};
+    return g;
+}
+
+int vk_batch_step_begin(const int* pos, int* table, int max_pages, int* free_list, int* free_top, int* desc, int B, int W,
+                        int C, int topk, cudaStream_t stream) {
+    if (B <= 0 || max_pages <= 0 || (W > 0 && C <= 0)) return VK_EINVAL;
+    return (int)vk_launch(batch_step_begin_kernel, dim3(1), dim3(32), 0, stream, pos, table, max_pages, free_list, free_top,
+                          desc, B, W, C, topk);
+}
+
+int vk_batch_step_end(int* pos, int* parity, int B, cudaStream_t stream) {
+    if (B <= 0) return VK_EINVAL;
+    return (int)vk_launch(batch_step_end_kernel, dim3((B + 63) / 64), dim3(64), 0, stream, pos, parity, B);
+}
+
+int vk_attn_prep(const vk_attn_geom* gm, const void* proj, int ldp, int off_k, int off_v, const void* idxq, const void* idxk,
+                 const void* q_norm, const void* k_norm, const void* idx_norm, const int* pos, const int* table, void* q,
+                 void* qi, void* K, void* V, void* PK, void* PV, void* BK, void* IK, int B, int rope_dims, double rope_theta,
+                 float eps, cudaStream_t stream) {
+    if (!geom_ok(gm) || B <= 0 || rope_dims % 8 != 0 || rope_dims > kD) return VK_EINVAL;
+    PrepParams p = {};
+    p.proj = (const __nv_bfloat16*)proj; p.idxq = (const __nv_bfloat16*)idxq; p.idxk = (const __nv_bfloat16*)idxk;
+    p.q_norm = (const __nv_bfloat16*)q_norm; p.k_norm = (const __nv_bfloat16*)k_norm; p.idx_norm = (const __nv_bfloat16*)idx_norm;
+    p.pos = pos; p.table = table; p.q = (__nv_bfloat16*)q; p.qi = (__nv_bfloat16*)qi;
+    p.K = (__nv_bfloat16*)K; p.V = (__nv_bfloat16*)V; p.PK = (__nv_bfloat16*)PK; p.PV = (__nv_bfloat16*)PV;
+    p.BK = (__nv_bfloat16*)BK; p.IK = (__nv_bfloat16*)IK;
+    p.ldp = ldp; p.off_k = off_k; p.off_v = off_v; p.n_pages = gm->n_pages; p.rope_dims = rope_dims;
+    p.log2_theta = log2(rope_theta); p.eps = eps; p.g = to_geom(gm);
+    return (int)vk_launch(attn_prep_kernel, dim3(B), dim3(256), 0, stream, p);
+}
+
+size_t vk_bcsa_select_scratch_bytes(const vk_attn_geom* gm, int B, int max_blocks) {
+    return (size_t)B * (gm->NS > 0 ? gm->NS : 1) * max_blocks * 4;
+}
+
+int vk_bcsa_select(const vk_attn_geom* gm, const void* q, const void* keys, const int* pos, const int* table, void* scratch,
+                   int max_blocks, int* sel, int* nsel, int B, cudaStream_t stream) {
+    if (!geom_ok(gm) || gm->W <= 0 || B <= 0 || max_blocks <= 0) return VK_EINVAL;
+    SelectParams p = {};
+    p.q = (const __nv_bfloat16*)q; p.keys = (const __nv_bfloat16*)keys; p.pos = pos; p.table = table;
+    p.scratch = (uint32_t*)scratch; p.sel = sel; p.nsel = nsel; p.cap = max_blocks; p.n_pages = gm->n_pages;
+    p.scale = (float)(1.0 / sqrt((double)kD)); p.g = to_geom(gm);
+    return (int)vk_launch(bcsa_select_kernel, dim3(p.g.NS, B), dim3(256), 0, stream, p);
+}
+
+size_t vk_attend_scratch_bytes(const vk_attn_geom* gm, int B, int nsplit) {
+    return (size_t)B * gm->Hq * nsplit * (kD + 2) * 4;
+}
+
+int vk_attend_decode(const vk_attn_geom* gm, const void* q, const void* K, const void* V, const void* PK, const void* PV,
+                     const int* pos, const int* table, const int* sel, const int* nsel, const void* proj, int ldp,
+                     void* part, int nsplit, void* out, int B, cudaStream_t stream) {
+    if (!geom_ok(gm) || B <= 0 || nsplit <= 0) return VK_EINVAL;
+    AttendParams p = {};
+    p.q = (const __nv_bfloat16*)q; p.K = (const __nv_bfloat16*)K; p.V = (const __nv_bfloat16*)V;
+    p.PK = (const __nv_bfloat16*)PK; p.PV = (const __nv_bfloat16*)PV; p.pos = pos; p.table = table;
+    p.sel = gm->W > 0 ? sel : nullptr; p.nsel = nsel; p.part = (float*)part; p.nsplit = nsplit; p.n_pages = gm->n_pages;
+    p.scale = (float)(1.0 / sqrt((double)kD)); p.g = to_geom(gm);
+    cudaError_t e;
+    switch (gm->Hq / gm->KVH) {
+        case 1: e = launch_attend<1>(p, B, stream); break;
+        case 2: e = launch_attend<2>(p, B, stream); break;
+        case 3: e = launch_attend<3>(p, B, stream); break;
+        case 4: e = launch_attend<4>(p, B, stream); break;
+        case 5: e = launch_attend<5>(p, B, stream); break;
+        case 6: e = launch_attend<6>(p, B, stream); break;
+        case 8: e = launch_attend<8>(p, B, stream); break;
+        default: return VK_EINVAL;
+    }
+    if (e != cudaSuccess) return (int)e;
+    return (int)vk_launch(attend_merge_kernel, dim3(gm->Hq, B), dim3(128), 0, stream, (const float*)part,
+                          (const __nv_bfloat16*)proj, ldp, (__nv_bfloat16*)out, gm->Hq, gm->KVH, nsplit);
+}
+
+}  // extern "C"

@@ -1,0 +1,483 @@
+// Fused row-wise kernels of the decode step: token embedding + first mHC norm, mHC mix (+ Sinkhorn) + input norm,
+// residual add + post-attention norm, SiLU-gated product, mHC combine (+ Engram gate) + next norm, Engram row hashing
+// and gather. One CTA per token row; every rounding to bf16 sits where the reference's ops path materialises a bf16
+// array (volundr.py:264-290, 145-150, 166-168, 594-597; the fused reference kernels decode_fused.py:43-355 compute
+// the same values).
+#include "common.cuh"
+
+namespace {
+
+constexpr int kEwThreads = 256;
+constexpr int kEwWarps = kEwThreads / 32;
+
+__device__ __forceinline__ float ldbf(const __nv_bfloat16* p, size_t i) { return bf2f(p[i]); }
+
+// sum over the block in a fixed order (see block_sum)
+__device__ __forceinline__ float ew_block_sum(float v, float* red) { return block_sum<kEwWarps>(v, red); }
+
+// ------------------------------------------------------------------------------------------------ embedding
+// x = embed[tok]; the four residual streams start as copies of x (volundr.py:929-930); hn = RMSNorm(x) * w0 is the
+// first layer's mHC norm input (volundr.py:944). Also advances the Engram id window and hashes the n-gram rows
+// (volundr.py:572-582, batch.py:526-529): row = (sum-product code over the last n ids, uint32 wrapping) & (rows - 1).
+struct EmbedParams {
+    const int* tok;                 // [B]
+    const __nv_bfloat16* embed;     // [V, D]
+    const __nv_bfloat16* w_mhc0;    // [D] plain RMSNorm weight of mhc[0]
+    __nv_bfloat16* H;               // [B, 4, D]
+    __nv_bfloat16* hn;              // [B, D]
+    int* engram_prev;               // [B, keep] or null
+    int* engram_rows_out;           // [B, n_orders]
+    int D, keep, n_orders, engram_rows;
+    int orders[4];
+    float eps;
+};
+
+__global__ void __launch_bounds__(kEwThreads) embed_kernel(const EmbedParams p) {
+    __shared__ float red[kEwWarps];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int b = blockIdx.x;
+    const int tok = p.tok[b];
+    const __nv_bfloat16* e = p.embed + (size_t)tok * p.D;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < p.D; i += kEwThreads) {
+        const __nv_bfloat16 v = e[i];
+        const float f = bf2f(v);
+        ss += f * f;
+#pragma unroll
+        for (int s = 0; s < 4; s++) p.H[((size_t)b * 4 + s) * p.D + i] = v;
+    }
+    ss = ew_block_sum(ss, red);
+    const float inv = rsqrtf(ss / (float)p.D + p.eps);
+    for (int i = threadIdx.x; i < p.D; i += kEwThreads)
+        p.hn[(size_t)b * p.D + i] = f2bf((bf2f(e[i]) * inv) * bf2f(p.w_mhc0[i]));
+    if (p.engram_prev != nullptr && threadIdx.x == 0) {
+        const uint32_t primes[5] = {1000003u, 1000033u, 1000037u, 1000039u, 1000081u};
+        int full[8];
+        for (int j = 0; j < p.keep; j++) full[j] = p.engram_prev[b * p.keep + j];
+        full[p.keep] = tok;
+        for (int o = 0; o < p.n_orders; o++) {
+            const int n = p.orders[o];
+            uint32_t code = 0;
+            for (int j = 0; j < n; j++) code = code * primes[j % 5] + (uint32_t)(full[p.keep + 1 - n + j] + 1);
+            p.engram_rows_out[b * p.n_orders + o] = (int)(code & (uint32_t)(p.engram_rows - 1));
+        }
+        for (int j = 0; j < p.keep; j++) p.engram_prev[b * p.keep + j] = full[j + 1];
+    }
+}
+
+// ------------------------------------------------------------------------------------------------ mHC mix + norm
+// d = dyn(hn) (bf16 linear D -> 24); pre = bf(pre_s + d[0:4]); post = bf(post_s + d[4:8]);
+// res = bf(Sinkhorn_iters(exp(l - max))), l = res_s + d[8:24]; x_in = bf(((p0 + p1) + p2) + p3), p_s = bf(pre_s H_s);
+// h = bf(x_in * rsqrt(mean x_in^2 + eps) * (1 + w_in)).   (volundr.py:319-322 with :264-278, :237-243, :132-150)
+struct MixParams {
+    const __nv_bfloat16* H;        // [B, 4, D]
+    const __nv_bfloat16* hn;       // [B, D]
+    const __nv_bfloat16* w_dyn;    // [24, D]
+    const __nv_bfloat16* pre_s;    // [4]
+    const __nv_bfloat16* post_s;   // [4]
+    const __nv_bfloat16* res_s;    // [16]
+    const __nv_bfloat16* w_in;     // [D] input_layernorm (offset norm)
+    __nv_bfloat16* x_in;           // [B, D]
+    __nv_bfloat16* h;              // [B, D]
+    float* post;                   // [B, 4]  (bf16-valued)
+    float* res;                    // [B, 16] (bf16-valued)
+    int D, iters;
+    float eps;
+};
+
+__global__ void __launch_bounds__(kEwThreads) mhc_mix_norm_kernel(const MixParams p) {
+    __shared__ float red[kEwWarps];
+    __shared__ float dsm[24];
+    __shared__ float pre_sm[4];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int b = blockIdx.x;
+    const int D = p.D;
+    const __nv_bfloat16* hn = p.hn + (size_t)b * D;
+    // the 24 dot products, 4 at a time to bound registers
+    for (int j0 = 0; j0 < 24; j0 += 4) {
+        float a[4] = {0.f, 0.f, 0.f, 0.f};
+        for (int i = threadIdx.x; i < D; i += kEwThreads) {
+            const float x = bf2f(hn[i]);
+#pragma unroll
+            for (int j = 0; j < 4; j++) a[j] = fmaf(x, bf2f(p.w_dyn[(size_t)(j0 + j) * D + i]), a[j]);
+        }
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const float t = ew_block_sum(a[j], red);
+            if (threadIdx.x == 0) dsm[j0 + j] = bfr(t);
+        }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float m[16];
+        float mx = -INFINITY;
+        for (int k = 0; k < 16; k++) {
+            m[k] = bf2f(p.res_s[k]) + dsm[8 + k];
+            mx = fmaxf(mx, m[k]);
+        }
+        for (int k = 0; k < 16; k++) m[k] = expf(m[k] - mx);
+        for (int it = 0; it < p.iters; it++) {
+            for (int r = 0; r < 4; r++) {
+                const float s = fmaxf(((m[4 * r] + m[4 * r + 1]) + m[4 * r + 2]) + m[4 * r + 3], 1e-9f);
+                for (int c = 0; c < 4; c++) m[4 * r + c] = m[4 * r + c] / s;
+            }
+            for (int c = 0; c < 4; c++) {
+                const float s = fmaxf(((m[c] + m[4 + c]) + m[8 + c]) + m[12 + c], 1e-9f);
+                for (int r = 0; r < 4; r++) m[4 * r + c] = m[4 * r + c] / s;
+            }
+        }
+        for (int k = 0; k < 16; k++) p.res[b * 16 + k] = bfr(m[k]);
+        for (int s = 0; s < 4; s++) {
+            pre_sm[s] = bfr(bf2f(p.pre_s[s]) + dsm[s]);
+            p.post[b * 4 + s] = bfr(bf2f(p.post_s[s]) + dsm[4 + s]);
+        }
+    }
+    __syncthreads();
+    const float pr0 = pre_sm[0], pr1 = pre_sm[1], pr2 = pre_sm[2], pr3 = pre_sm[3];
+    const __nv_bfloat16* Hb = p.H + (size_t)b * 4 * D;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < D; i += kEwThreads) {
+        const float p0 = bfr(pr0 * bf2f(Hb[i])), p1 = bfr(pr1 * bf2f(Hb[D + i]));
+        const float p2 = bfr(pr2 * bf2f(Hb[2 * D + i])), p3 = bfr(pr3 * bf2f(Hb[3 * D + i]));
+        const float x = bfr(((p0 + p1) + p2) + p3);
+        p.x_in[(size_t)b * D + i] = f2bf(x);
+        ss += x * x;
+    }
+    ss = ew_block_sum(ss, red);
+    const float inv = rsqrtf(ss / (float)D + p.eps);
+    for (int i = threadIdx.x; i < D; i += kEwThreads) {
+        const float x = bf2f(p.x_in[(size_t)b * D + i]);
+        p.h[(size_t)b * D + i] = f2bf((x * inv) * (1.f + bf2f(p.w_in[i])));
+    }
+}
+
+// ------------------------------------------------------------------------------------------------ add + norm
+// h2 = bf(x + r); hn = bf(h2 * rsqrt(mean h2^2 + eps) * (off + w))      (volundr.py:893-899)
+__global__ void __launch_bounds__(kEwThreads) add_rmsnorm_kernel(const __nv_bfloat16* __restrict__ x,
+                                                                 const __nv_bfloat16* __restrict__ r,
+                                                                 const __nv_bfloat16* __restrict__ w,
+                                                                 __nv_bfloat16* __restrict__ h2,
+                                                                 __nv_bfloat16* __restrict__ hn, int D, float eps,
+                                                                 float offset) {
+    __shared__ float red[kEwWarps];
+    pdl_launch_dependents();
+    pdl_wait();
+    const size_t base = (size_t)blockIdx.x * D;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < D; i += kEwThreads) {
+        float v = bf2f(x[base + i]);
+        if (r != nullptr) v = bfr(v + bf2f(r[base + i]));
+        if (h2 != nullptr) h2[base + i] = f2bf(v);
+        ss += v * v;
+    }
+    ss = ew_block_sum(ss, red);
+    const float inv = rsqrtf(ss / (float)D + eps);
+    for (int i = threadIdx.x; i < D; i += kEwThreads) {
+        float v = bf2f(x[base + i]);
+        if (r != nullptr) v = bfr(v + bf2f(r[base + i]));
+        hn[base + i] = f2bf((v * inv) * (offset + bf2f(w[i])));
+    }
+}
+
+// ------------------------------------------------------------------------------------------------ silu(g) * u
+// act = bf(silu(gate) * up) in fp32 (volundr.py:166-168); gu holds [gate (I) | up (I)] per row.
+__global__ void silu_mul_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ act, int I, int ld_gu) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int b = blockIdx.y;
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= I) return;
+    const float g = bf2f(gu[(size_t)b * ld_gu + i]), u = bf2f(gu[(size_t)b * ld_gu + I + i]);
+    act[(size_t)b * I + i] = f2bf((g / (1.f + expf(-g))) * u);
+}
+
+// ------------------------------------------------------------------------------------------------ Engram gather
+// e = RMSNorm(concat_i table_i[row_i]) * w (volundr.py:594-595); table_i = columns [i dim, (i+1) dim) of one shared
+// table when `shared`, else separate tables laid out one after another.
+struct EngramGatherParams {
+    const __nv_bfloat16* tables[4];
+    const int* rows;               // [B, n_orders]
+    const __nv_bfloat16* w;        // [n_orders * dim]
+    __nv_bfloat16* e;              // [B, n_orders * dim]
+    int n_orders, dim, ld_table[4], col0[4];
+    float eps;
+};
+
+__global__ void __launch_bounds__(kEwThreads) engram_gather_kernel(const EngramGatherParams p) {
+    __shared__ float red[kEwWarps];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int b = blockIdx.x;
+    const int cat = p.n_orders * p.dim;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < cat; i += kEwThreads) {
+        const int o = i / p.dim, c = i - o * p.dim;
+        const int row = p.rows[b * p.n_orders + o];
+        const float v = bf2f(p.tables[o][(size_t)row * p.ld_table[o] + p.col0[o] + c]);
+        ss += v * v;
+    }
+    ss = ew_block_sum(ss, red);
+    const float inv = rsqrtf(ss / (float)cat + p.eps);
+    for (int i = threadIdx.x; i < cat; i += kEwThreads) {
+        const int o = i / p.dim, c = i - o * p.dim;
+        const int row = p.rows[b * p.n_orders + o];
+        const float v = bf2f(p.tables[o][(size_t)row * p.ld_table[o] + p.col0[o] + c]);
+        p.e[(size_t)b * cat + i] = f2bf((v * inv) * bf2f(p.w[i]));
+    }
+}
+
+// ------------------------------------------------------------------------------------------------ mHC combine + norm
+// y = bf(h2 + m); Engram layers: y = bf(y + bf(g * val)), g = bf(sigmoid(bf(gate_w . y + gate_b))) (volundr.py:594-597);
+// delta = bf(y - x_in); mixed_s = bf(sum_j res_sj H_j) (fp32, j in order); H'_s = bf(mixed_s + bf(post_s delta));
+// mean = bf((((o0+o1)+o2)+o3) / 4)  (volundr.py:330-331, :281-290). Then either the next layer's mHC norm of the mean
+// (plain RMSNorm, volundr.py:944-948) or, after the last layer, the model's final offset norm of stream 0 (:949).
+struct CombineParams {
+    __nv_bfloat16* H;              // [B, 4, D] in / out
+    const __nv_bfloat16* h2;       // [B, D]
+    const __nv_bfloat16* m;        // [B, D]
+    const __nv_bfloat16* x_in;     // [B, D]
+    const float* post;             // [B, 4]
+    const float* res;              // [B, 16]
+    const __nv_bfloat16* w_next;   // [D]
+    __nv_bfloat16* hn;             // [B, D]
+    const __nv_bfloat16* eng_val;  // [B, D] or null
+    const __nv_bfloat16* eng_gate_w;  // [D]
+    const __nv_bfloat16* eng_gate_b;  // [1]
+    __nv_bfloat16* y_out;          // [B, D] or null (debug / tests)
+    int D, final_norm;
+    float eps;
+};
+
+__global__ void __launch_bounds__(kEwThreads) mhc_combine_norm_kernel(const CombineParams p) {
+    __shared__ float red[kEwWarps];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int b = blockIdx.x, D = p.D;
+    const size_t base = (size_t)b * D;
+    float gate = 0.f;
+    if (p.eng_val != nullptr) {
+        float a = 0.f;
+        for (int i = threadIdx.x; i < D; i += kEwThreads) {
+            const float y = bfr(bf2f(p.h2[base + i]) + bf2f(p.m[base + i]));
+            a = fmaf(y, bf2f(p.eng_gate_w[i]), a);
+        }
+        a = ew_block_sum(a, red);
+        const float lin = bfr(a + bf2f(p.eng_gate_b[0]));
+        gate = bfr(1.f / (1.f + expf(-lin)));
+    }
+    float r[16], po[4];
+#pragma unroll
+    for (int k = 0; k < 16; k++) r[k] = p.res[b * 16 + k];
+#pragma unroll
+    for (int s = 0; s < 4; s++) po[s] = p.post[b * 4 + s];
+    __nv_bfloat16* Hb = p.H + (size_t)b * 4 * D;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < D; i += kEwThreads) {
+        float y = bfr(bf2f(p.h2[base + i]) + bf2f(p.m[base + i]));
+        if (p.eng_val != nullptr) y = bfr(y + bfr(gate * bf2f(p.eng_val[base + i])));
+        if (p.y_out != nullptr) p.y_out[base + i] = f2bf(y);
+        const float delta = bfr(y - bf2f(p.x_in[base + i]));
+        float hj[4], o[4];
+#pragma unroll
+        for (int j = 0; j < 4; j++) hj[j] = bf2f(Hb[(size_t)j * D + i]);
+#pragma unroll
+        for (int s = 0; s < 4; s++) {
+            float mixed = r[4 * s] * hj[0];
+            mixed = fmaf(r[4 * s + 1], hj[1], mixed);
+            mixed = fmaf(r[4 * s + 2], hj[2], mixed);
+            mixed = fmaf(r[4 * s + 3], hj[3], mixed);
+            o[s] = bfr(bfr(mixed) + bfr(po[s] * delta));
+        }
+#pragma unroll
+        for (int s = 0; s < 4; s++) Hb[(size_t)s * D + i] = f2bf(o[s]);
+        const float v = p.final_norm ? o[0] : bfr((((o[0] + o[1]) + o[2]) + o[3]) * 0.25f);
+        ss += v * v;
+    }
+    if (p.w_next == nullptr) return;
+    ss = ew_block_sum(ss, red);
+    const float inv = rsqrtf(ss / (float)D + p.eps);
+    const float off = p.final_norm ? 1.f : 0.f;
+    for (int i = threadIdx.x; i < D; i += kEwThreads) {
+        float v;
+        if (p.final_norm) {
+            v = bf2f(Hb[i]);
+        } else {
+            const float o0 = bf2f(Hb[i]), o1 = bf2f(Hb[(size_t)D + i]), o2 = bf2f(Hb[(size_t)2 * D + i]),
+                        o3 = bf2f(Hb[(size_t)3 * D + i]);
+            v = bfr((((o0 + o1) + o2) + o3) * 0.25f);
+        }
+        p.hn[base + i] = f2bf((v * inv) * (off + bf2f(p.w_next[i])));
+    }
+}
+
+// ------------------------------------------------------------------------------------------------ bf16 linear, few rows
+// y[M, N] = bf16(x[M, K] . W[N, K]^T (+ bias)), fp32 accumulation: the linears the reference keeps unquantised
+// (convert.py:16-17: lm_head, in_proj_b, mhc.dyn, BCSA indexer, Engram gate / value, f_up). One warp per output row.
+template <int MMAX>
+__global__ void __launch_bounds__(256) bf16_gemm_rows_kernel(const __nv_bfloat16* __restrict__ x, int ldx,
+                                                            const __nv_bfloat16* __restrict__ W,
+                                                            const __nv_bfloat16* __restrict__ bias,
+                                                            __nv_bfloat16* __restrict__ y, int ldy, int M, int N, int K) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n = blockIdx.x * 8 + warp;
+    if (n >= N) return;
+    float acc[MMAX];
+#pragma unroll
+    for (int m = 0; m < MMAX; m++) acc[m] = 0.f;
+    const __nv_bfloat16* wr = W + (size_t)n * K;
+    for (int k = lane * 8; k < K; k += 256) {
+        const uint4 wv = *reinterpret_cast<const uint4*>(wr + k);
+        const float w0 = bf_lo(wv.x), w1 = bf_hi(wv.x), w2 = bf_lo(wv.y), w3 = bf_hi(wv.y);
+        const float w4 = bf_lo(wv.z), w5 = bf_hi(wv.z), w6 = bf_lo(wv.w), w7 = bf_hi(wv.w);
+#pragma unroll
+        for (int m = 0; m < MMAX; m++) {
+            if (m < M) {
+                const uint4 xv = *reinterpret_cast<const uint4*>(x + (size_t)m * ldx + k);
+                float a = acc[m];
+                a = fmaf(bf_lo(xv.x), w0, a); a = fmaf(bf_hi(xv.x), w1, a);
+                a = fmaf(bf_lo(xv.y), w2, a); a = fmaf(bf_hi(xv.y), w3, a);
+                a = fmaf(bf_lo(xv.z), w4, a); a = fmaf(bf_hi(xv.z), w5, a);
+                a = fmaf(bf_lo(xv.w), w6, a); a = fmaf(bf_hi(xv.w), w7, a);
+                acc[m] = a;
+            }
+        }
+    }
+#pragma unroll
+    for (int m = 0; m < MMAX; m++) {
+        if (m < M) {
+            float t = warp_sum(acc[m]);
+            if (lane == 0) {
+                if (bias != nullptr) t += bf2f(bias[n]);
+                y[(size_t)m * ldy + n] = f2bf(t);
+            }
+        }
+    }
+}
+
+// first maximum over logits[:, :vocab_valid] (scheduler.py:391)
+__global__ void __launch_bounds__(1024) argmax_kernel(const __nv_bfloat16* __restrict__ logits, int ld, int valid,
+                                                      int* __restrict__ out) {
+    __shared__ float bv[32];
+    __shared__ int bi[32];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int b = blockIdx.x;
+    float best = -INFINITY;
+    int idx = 0x7fffffff;
+    for (int i = threadIdx.x; i < valid; i += blockDim.x) {
+        const float v = bf2f(logits[(size_t)b * ld + i]);
+        if (v > best || (v == best && i < idx)) { best = v; idx = i; }
+    }
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+        if (ov > best || (ov == best && oi < idx)) { best = ov; idx = oi; }
+    }
+    if ((threadIdx.x & 31) == 0) { bv[threadIdx.x >> 5] = best; bi[threadIdx.x >> 5] = idx; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < (int)(blockDim.x >> 5); w++)
+            if (bv[w] > best || (bv[w] == best && bi[w] < idx)) { best = bv[w]; idx = bi[w]; }
+        out[b] = idx;
+    }
+}
+
+}  // namespace
+
+extern "C" {
+
+int vk_embed(const int* tok, const void* embed, const void* w_mhc0, void* H, void* hn, int* engram_prev,
+             int* engram_rows_out, const int* orders, int n_orders, int engram_rows, int B, int D, float eps,
+             cudaStream_t stream) {
+    if (B <= 0 || D <= 0 || n_orders < 0 || n_orders > 4) return VK_EINVAL;
+    EmbedParams p = {};
+    p.tok = tok; p.embed = (const __nv_bfloat16*)embed; p.w_mhc0 = (const __nv_bfloat16*)w_mhc0;
+    p.H = (__nv_bfloat16*)H; p.hn = (__nv_bfloat16*)hn; p.engram_prev = engram_prev; p.engram_rows_out = engram_rows_out;
+    p.D = D; p.n_orders = n_orders; p.engram_rows = engram_rows; p.eps = eps;
+    int keep = 0;
+    for (int i = 0; i < n_orders; i++) {
+        if (orders[i] < 1 || orders[i] > 8) return VK_EINVAL;
+        p.orders[i] = orders[i];
+        keep = orders[i] - 1 > keep ? orders[i] - 1 : keep;
+    }
+    p.keep = keep;
+    return (int)vk_launch(embed_kernel, dim3(B), dim3(kEwThreads), 0, stream, p);
+}
+
+int vk_mhc_mix_norm(const void* H, const void* hn, const void* w_dyn, const void* pre_s, const void* post_s,
+                    const void* res_s, const void* w_in, void* x_in, void* h, float* post, float* res, int B, int D,
+                    int iters, float eps, cudaStream_t stream) {
+    if (B <= 0 || D <= 0) return VK_EINVAL;
+    MixParams p = {(const __nv_bfloat16*)H, (const __nv_bfloat16*)hn, (const __nv_bfloat16*)w_dyn,
+                   (const __nv_bfloat16*)pre_s, (const __nv_bfloat16*)post_s, (const __nv_bfloat16*)res_s,
+                   (const __nv_bfloat16*)w_in, (__nv_bfloat16*)x_in, (__nv_bfloat16*)h, post, res, D, iters, eps};
+    return (int)vk_launch(mhc_mix_norm_kernel, dim3(B), dim3(kEwThreads), 0, stream, p);
+}
+
+int vk_add_rmsnorm(const void* x, const void* r, const void* w, void* h2, void* hn, int B, int D, float eps, int offset,
+                   cudaStream_t stream) {
+    if (B <= 0 || D <= 0) return VK_EINVAL;
+    return (int)vk_launch(add_rmsnorm_kernel, dim3(B), dim3(kEwThreads), 0, stream, (const __nv_bfloat16*)x,
+                          (const __nv_bfloat16*)r, (const __nv_bfloat16*)w, (__nv_bfloat16*)h2, (__nv_bfloat16*)hn, D, eps,
+                          offset ? 1.f : 0.f);
+}
+
+int vk_silu_mul(const void* gu, void* act, int B, int I, int ld_gu, cudaStream_t stream) {
+    if (B <= 0 || I <= 0) return VK_EINVAL;
+    return (int)vk_launch(silu_mul_kernel, dim3((I + 255) / 256, B), dim3(256), 0, stream, (const __nv_bfloat16*)gu,
+                          (__nv_bfloat16*)act, I, ld_gu);
+}
+
+int vk_engram_gather(const void* const* tables, const int* ld_table, const int* col0, const int* rows, const void* w,
+                     void* e, int B, int n_orders, int dim, float eps, cudaStream_t stream) {
+    if (B <= 0 || n_orders <= 0 || n_orders > 4) return VK_EINVAL;
+    EngramGatherParams p = {};
+    for (int i = 0; i < n_orders; i++) {
+        p.tables[i] = (const __nv_bfloat16*)tables[i];
+        p.ld_table[i] = ld_table[i];
+        p.col0[i] = col0[i];
+    }
+    p.rows = rows; p.w = (const __nv_bfloat16*)w; p.e = (__nv_bfloat16*)e; p.n_orders = n_orders; p.dim = dim; p.eps = eps;
+    return (int)vk_launch(engram_gather_kernel, dim3(B), dim3(kEwThreads), 0, stream, p);
+}
+
+int vk_mhc_combine_norm(void* H, const void* h2, const void* m, const void* x_in, const float* post, const float* res,
+                        const void* w_next, void* hn, const void* eng_val, const void* eng_gate_w, const void* eng_gate_b,
+                        void* y_out, int B, int D, int final_norm, float eps, cudaStream_t stream) {
+    if (B <= 0 || D <= 0) return VK_EINVAL;
+    CombineParams p = {(__nv_bfloat16*)H, (const __nv_bfloat16*)h2, (const __nv_bfloat16*)m, (const __nv_bfloat16*)x_in,
+                       post, res, (const __nv_bfloat16*)w_next, (__nv_bfloat16*)hn, (const __nv_bfloat16*)eng_val,
+                       (const __nv_bfloat16*)eng_gate_w, (const __nv_bfloat16*)eng_gate_b, (__nv_bfloat16*)y_out, D,
+                       final_norm, eps};
+    return (int)vk_launch(mhc_combine_norm_kernel, dim3(B), dim3(kEwThreads), 0, stream, p);
+}
+
+int vk_bf16_gemm(const void* x, int ldx, const void* W, const void* bias, void* y, int ldy, int M, int N, int K,
+                 cudaStream_t stream) {
+    if (M <= 0 || N <= 0 || K <= 0 || K % 8 != 0 || ldx % 8 != 0) return VK_EINVAL;
+    for (int m0 = 0; m0 < M; m0 += 16) {
+        const int m = M - m0 < 16 ? M - m0 : 16;
+        const __nv_bfloat16* xp = (const __nv_bfloat16*)x + (size_t)m0 * ldx;
+        __nv_bfloat16* yp = (__nv_bfloat16*)y + (size_t)m0 * ldy;
+        cudaError_t e;
+        if (m <= 4)
+            e = vk_launch(bf16_gemm_rows_kernel<4>, dim3((N + 7) / 8), dim3(256), 0, stream, xp, ldx,
+                          (const __nv_bfloat16*)W, (const __nv_bfloat16*)bias, yp, ldy, m, N, K);
+        else
+            e = vk_launch(bf16_gemm_rows_kernel<16>, dim3((N + 7) / 8), dim3(256), 0, stream, xp, ldx,
+                          (const __nv_bfloat16*)W, (const __nv_bfloat16*)bias, yp, ldy, m, N, K);
+        if (e != cudaSuccess) return (int)e;
+    }
+    return VK_OK;
+}
+
+int vk_argmax(const void* logits, int ld, int valid, int* out, int B, cudaStream_t stream) {
+    if (B <= 0 || valid <= 0) return VK_EINVAL;
+    return (int)vk_launch(argmax_kernel, dim3(B), dim3(1024), 0, stream, (const __nv_bfloat16*)logits, ld, valid, out);
+}
+
+}  // extern "C"

@@ -1,0 +1,186 @@
+// Kimi Delta Attention decode step, one CTA per (value head, row): depthwise causal conv (k = 4) + SiLU of this
+// head's q / k / v channels, q/k l2 normalisation, the per-channel decay g and beta, the gated-delta-rule update of
+// the fp32 state S[Dv, Dk] (read once, written once), y = S q, and the z-gated RMSNorm of y.
+//
+// Replaces, for L = 1, KDA.__call__ (volundr.py:388-439): DF.kda_conv_gates (decode_fused.py:362-493) ->
+// kernels.gated_delta_vec (kernels.py:374-458) -> kernels.gated_norm (kernels.py:890-928), and the two small bf16
+// linears in front of them (in_proj_b, f_up; volundr.py:392-393). Arithmetic per (b, hv), key head hk = hv / (HV/Hk):
+//   c = sum_j x[t-3+j] * w[j] (fp32, products and sums rounded separately, j = 0..3); s = bf16(c * sigmoid(c))
+//   q^ = s_q / sqrt(sum s_q^2 + 1e-6) * Dk^-1/2 ; k^ = s_k / sqrt(sum s_k^2 + 1e-6) ; v = s_v
+//   g = exp(-exp(A_log) * softplus(a + dt_bias)), a = bf16(f_up . f_down(h)) ; beta = sigmoid(bf16(in_proj_b . h))
+//   S <- S * g (per column) ; delta = (v - S k^) beta ; S <- S + delta (x) k^ ; y = S q^
+//   out = bf16(w * (bf16(y) * rsqrt(mean bf16(y)^2 + eps)) * silu(z))
+// State layout: fp32 [slot, HV, Dv, Dk], row = value dim, Dk contiguous (volundr.py:406). Dk = Dv = 128.
+#include "common.cuh"
+
+namespace {
+
+struct KdaParams {
+    const __nv_bfloat16* proj;     // [B, ldp]: q (Hk*128) | k (Hk*128) | v (HV*128) at 0, z at off_z, f_down at off_fd
+    const __nv_bfloat16* h;        // [B, D] layer input (for in_proj_b)
+    const __nv_bfloat16* w_b;      // [HV, D]
+    const __nv_bfloat16* w_fup;    // [HV*128, rank]
+    const float* conv_w;           // [C, 4]
+    const float* A_log;            // [HV]
+    const float* dt_bias;          // [HV*128]
+    const __nv_bfloat16* norm_w;   // [128]
+    __nv_bfloat16* conv;           // [2, slots, 3, C]: buffer *parity holds the state before the step, the other one
+                                   // receives the state after it (two buffers: value heads that share a key head
+                                   // read its q / k channels while one of them writes the new rows)
+    const int* parity;             // device word, flipped at the end of every step
+    size_t conv_stride;            // elements between the two buffers
+    float* S;                      // [slots, HV, 128, 128]
+    __nv_bfloat16* out;            // [B, HV*128]
+    const float* g_override;       // null, or [B] multipliers: 1 keeps the step, 0 turns it into a no-op (verify replay)
+    int ldp, off_z, off_fd, D, Hk, HV, rank;
+    float eps;
+};
+
+__device__ __forceinline__ float softplus_f(float x) { return fmaxf(x, 0.f) + log1pf(expf(-fabsf(x))); }
+
+__global__ void __launch_bounds__(128) kda_step_kernel(const KdaParams p) {
+    __shared__ float red[4];
+    __shared__ __align__(16) float qs[128], ks[128], gs[128], ys[128];
+    __shared__ float vs[128];
+    __shared__ float fd[256];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int hv = blockIdx.x, b = blockIdx.y;
+    const int c = threadIdx.x, lane = c & 31, warp = c >> 5;
+    const int rep = p.HV / p.Hk, hk = hv / rep;
+    const int KD = p.Hk * 128, C = 2 * KD + p.HV * 128;
+    const __nv_bfloat16* pr = p.proj + (size_t)b * p.ldp;
+    const int par = *p.parity & 1;
+    const __nv_bfloat16* conv_in = p.conv + (size_t)par * p.conv_stride;
+    __nv_bfloat16* conv_out = p.conv + (size_t)(1 - par) * p.conv_stride;
+
+    for (int i = c; i < p.rank; i += 128) fd[i] = bf2f(pr[p.off_fd + i]);
+
+    // ---- conv + SiLU of this head's q, k, v channel c; new conv state
+    const int ch[3] = {hk * 128 + c, KD + hk * 128 + c, 2 * KD + hv * 128 + c};
+    float s3[3];
+#pragma unroll
+    for (int i = 0; i < 3; i++) {
+        const size_t cb = (size_t)b * 3 * C + ch[i];
+        const __nv_bfloat16 x0 = conv_in[cb], x1 = conv_in[cb + C], x2 = conv_in[cb + 2 * (size_t)C];
+        const __nv_bfloat16 x3 = pr[ch[i]];
+        const float* w = p.conv_w + (size_t)ch[i] * 4;
+        float acc = __fmul_rn(bf2f(x0), w[0]);
+        acc = __fadd_rn(acc, __fmul_rn(bf2f(x1), w[1]));
+        acc = __fadd_rn(acc, __fmul_rn(bf2f(x2), w[2]));
+        acc = __fadd_rn(acc, __fmul_rn(bf2f(x3), w[3]));
+        s3[i] = bfr(acc / (1.f + expf(-acc)));
+        if (i == 2 || hv % rep == 0) {
+            conv_out[cb] = x1;
+            conv_out[cb + C] = x2;
+            conv_out[cb + 2 * (size_t)C] = x3;
+        }
+    }
+    const float ssq = block_sum<4>(s3[0] * s3[0], red);
+    const float ssk = block_sum<4>(s3[1] * s3[1], red);
+    qs[c] = (s3[0] / sqrtf(ssq + 1e-6f)) * 0.08838834764831845f;  // 128^-1/2
+    ks[c] = s3[1] / sqrtf(ssk + 1e-6f);
+    vs[c] = s3[2];
+
+    // ---- decay g[c] and beta
+    __syncthreads();  // fd
+    {
+        const __nv_bfloat16* wr = p.w_fup + (size_t)(hv * 128 + c) * p.rank;
+        float a = 0.f;
+        for (int r = 0; r < p.rank; r += 8) {
+            const uint4 wv = *reinterpret_cast<const uint4*>(wr + r);
+            a = fmaf(bf_lo(wv.x), fd[r], a); a = fmaf(bf_hi(wv.x), fd[r + 1], a);
+            a = fmaf(bf_lo(wv.y), fd[r + 2], a); a = fmaf(bf_hi(wv.y), fd[r + 3], a);
+            a = fmaf(bf_lo(wv.z), fd[r + 4], a); a = fmaf(bf_hi(wv.z), fd[r + 5], a);
+            a = fmaf(bf_lo(wv.w), fd[r + 6], a); a = fmaf(bf_hi(wv.w), fd[r + 7], a);
+        }
+        a = bfr(a);
+        gs[c] = expf(-expf(p.A_log[hv]) * softplus_f(a + p.dt_bias[hv * 128 + c]));
+    }
+    float bdot = 0.f;
+    {
+        const __nv_bfloat16* wb = p.w_b + (size_t)hv * p.D;
+        const __nv_bfloat16* hb = p.h + (size_t)b * p.D;
+        for (int k = c * 8; k < p.D; k += 1024) {
+            const uint4 wv = *reinterpret_cast<const uint4*>(wb + k);
+            const uint4 xv = *reinterpret_cast<const uint4*>(hb + k);
+            bdot = fmaf(bf_lo(wv.x), bf_lo(xv.x), bdot); bdot = fmaf(bf_hi(wv.x), bf_hi(xv.x), bdot);
+            bdot = fmaf(bf_lo(wv.y), bf_lo(xv.y), bdot); bdot = fmaf(bf_hi(wv.y), bf_hi(xv.y), bdot);
+            bdot = fmaf(bf_lo(wv.z), bf_lo(xv.z), bdot); bdot = fmaf(bf_hi(wv.z), bf_hi(xv.z), bdot);
+            bdot = fmaf(bf_lo(wv.w), bf_lo(xv.w), bdot); bdot = fmaf(bf_hi(wv.w), bf_hi(xv.w), bdot);
+        }
+    }
+    bdot = bfr(block_sum<4>(bdot, red));   // (also orders the qs/ks/gs/vs writes before the reads below)
+    float beta = 1.f / (1.f + expf(-bdot));
+    float4 g4 = *reinterpret_cast<const float4*>(gs + 4 * lane);
+    if (p.g_override != nullptr && p.g_override[b] == 0.f) {  // replay past the accepted prefix: g = 1, beta = 0
+        beta = 0.f;
+        g4 = make_float4(1.f, 1.f, 1.f, 1.f);
+    }
+
+    // ---- recurrence: warp w owns rows 32 w .. 32 w + 31 of S; lane l columns 4 l .. 4 l + 3
+    const float4 k4 = *reinterpret_cast<const float4*>(ks + 4 * lane);
+    const float4 q4 = *reinterpret_cast<const float4*>(qs + 4 * lane);
+    float* Sb = p.S + (((size_t)b * p.HV + hv) * 128) * 128;
+#pragma unroll 1
+    for (int r0 = warp * 32; r0 < warp * 32 + 32; r0 += 8) {
+        float4 s[8];
+#pragma unroll
+        for (int i = 0; i < 8; i++) s[i] = *reinterpret_cast<const float4*>(Sb + (size_t)(r0 + i) * 128 + 4 * lane);
+        float kv[8];
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            s[i].x *= g4.x; s[i].y *= g4.y; s[i].z *= g4.z; s[i].w *= g4.w;
+            kv[i] = fmaf(s[i].w, k4.w, fmaf(s[i].z, k4.z, fmaf(s[i].y, k4.y, s[i].x * k4.x)));
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+            for (int i = 0; i < 8; i++) kv[i] += __shfl_xor_sync(0xffffffffu, kv[i], o);
+        float y[8];
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            const float d = (vs[r0 + i] - kv[i]) * beta;
+            s[i].x = fmaf(d, k4.x, s[i].x); s[i].y = fmaf(d, k4.y, s[i].y);
+            s[i].z = fmaf(d, k4.z, s[i].z); s[i].w = fmaf(d, k4.w, s[i].w);
+            y[i] = fmaf(s[i].w, q4.w, fmaf(s[i].z, q4.z, fmaf(s[i].y, q4.y, s[i].x * q4.x)));
+            *reinterpret_cast<float4*>(Sb + (size_t)(r0 + i) * 128 + 4 * lane) = s[i];
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+            for (int i = 0; i < 8; i++) y[i] += __shfl_xor_sync(0xffffffffu, y[i], o);
+        if (lane == 0) {
+#pragma unroll
+            for (int i = 0; i < 8; i++) ys[r0 + i] = y[i];
+        }
+    }
+    __syncthreads();
+
+    // ---- gated norm over the value head
+    const float yb = bfr(ys[c]);
+    const float ss = block_sum<4>(yb * yb, red);
+    const float inv = rsqrtf(ss * (1.f / 128.f) + p.eps);
+    const float z = bf2f(pr[p.off_z + hv * 128 + c]);
+    p.out[(size_t)b * p.HV * 128 + hv * 128 + c] = f2bf(((yb * inv) * bf2f(p.norm_w[c])) * (z / (1.f + expf(-z))));
+}
+
+}  // namespace
+
+extern "C" {
+
+int vk_kda_step(const void* proj, int ldp, int off_z, int off_fd, const void* h, const void* w_b, const void* w_fup,
+                const float* conv_w, const float* A_log, const float* dt_bias, const void* norm_w, void* conv,
+                const int* parity, size_t conv_stride, float* S, void* out, const float* g_override, int B, int D, int Hk,
+                int HV, int Dk, int Dv, int rank, float eps, cudaStream_t stream) {
+    if (B <= 0 || Dk != 128 || Dv != 128 || Hk <= 0 || HV % Hk != 0 || rank <= 0 || rank > 256 || rank % 8 != 0 ||
+        D % 8 != 0 || parity == nullptr)
+        return VK_EINVAL;
+    KdaParams p = {(const __nv_bfloat16*)proj, (const __nv_bfloat16*)h, (const __nv_bfloat16*)w_b,
+                   (const __nv_bfloat16*)w_fup, conv_w, A_log, dt_bias, (const __nv_bfloat16*)norm_w,
+                   (__nv_bfloat16*)conv, parity, conv_stride, S, (__nv_bfloat16*)out, g_override,
+                   ldp, off_z, off_fd, D, Hk, HV, rank, eps};
+    return (int)vk_launch(kda_step_kernel, dim3(HV, B), dim3(128), 0, stream, p);
+}
+
+}  // extern "C"

@@ -1,3 +1,6 @@
 // Single translation unit of libvolundr_b200.so (one device link unit: the status word is shared by every kernel).
 #include "runtime.cu"
 #include "w4_gemm.cu"
+#include "elementwise.cu"
+#include "kda.cu"
+#include "attention.cu"
