@@ -25,6 +25,9 @@ void vk_set_pdl(int on);
 /* Copies the device status word to *device_out (4 bytes of device memory) and clears it. Stream-ordered. */
 int vk_status_fetch(int* device_out, vk_stream_t stream);
 const char* vk_status_string(int code);
+/* Kernels launched by the library since the last call with reset != 0 (host-side counter; a stream capture counts
+ * the captured kernels once). */
+long long vk_launch_count(int reset);
 
 /* ---- INT4 affine weight GEMM, 1..16 activation rows per pass (more rows re-stream the weights per 16).
  * Replaces nn.QuantizedLinear.__call__ -> mx.quantized_matmul(x, w, scales, biases, transpose=True, group_size, bits=4)

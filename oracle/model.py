@@ -68,11 +68,13 @@ class Args:
 
 
 def silu(x):
-    return x / (1 + np.exp(-x))
+    with np.errstate(over="ignore"):
+        return x / (1 + np.exp(-x))
 
 
 def sigmoid(x):
-    return 1 / (1 + np.exp(-x))
+    with np.errstate(over="ignore"):
+        return 1 / (1 + np.exp(-x))
 
 
 def tree_dot32(a, b):
@@ -130,8 +132,9 @@ class Row:
 
 
 class Oracle:
-    def __init__(self, args: Args, params: dict, exact: bool = False):
-        self.a, self.p, self.exact = args, params, exact
+    def __init__(self, args: Args, params: dict, exact: bool = False, fast: bool = False):
+        """fast=True (CPU-baseline timing only): weights dequantised and multiplied in float32 instead of float64."""
+        self.a, self.p, self.exact, self.fast = args, params, exact, fast
         self.dt = np.float64 if exact else np.float32
         self._wcache = {}
 
@@ -143,16 +146,17 @@ class Oracle:
         """Dense [N, K] matrix of linear `name` (dequantised when stored as W4)."""
         if name not in self._wcache:
             if name + ".scales" in self.p:
-                w = W4.dequant(self.p[name + ".weight"], self.p[name + ".scales"], self.p[name + ".biases"],
-                               self.a.quant_group)
+                dq = W4.dequant_fast if self.fast else W4.dequant
+                w = dq(self.p[name + ".weight"], self.p[name + ".scales"], self.p[name + ".biases"], self.a.quant_group)
             else:
                 w = self.p[name + ".weight"]
-            self._wcache[name] = np.asarray(w, dtype=np.float64)
+            self._wcache[name] = np.asarray(w, dtype=np.float32 if self.fast else np.float64)
         return self._wcache[name]
 
     def lin(self, x, name):
         """nn.Linear / nn.QuantizedLinear: fp32-accumulated product rounded once (volundr.py:185-190)."""
-        y = np.asarray(x, dtype=np.float64) @ self.weight(name).T
+        W = self.weight(name)
+        y = np.asarray(x, dtype=W.dtype) @ W.T
         if name + ".bias" in self.p:
             y = y + np.asarray(self.p[name + ".bias"], dtype=np.float64)
         return self.rnd(y)

@@ -47,6 +47,20 @@ def dequant(w, scales, biases, group):
     return bf_from_f64_exact(r, err)
 
 
+def dequant_fast(w, scales, biases, group):
+    """float32 s * u + b rounded to bf16, row block by row block: for timing the CPU baseline only (it can differ from
+    `dequant` in the last bit where the float32 sum lands on a bf16 tie)."""
+    s = np.asarray(scales, dtype=np.float32)
+    b = np.asarray(biases, dtype=np.float32)
+    N, Gq = s.shape
+    K = Gq * group
+    out = np.empty((N, K), dtype=np.float32)
+    for r0 in range(0, N, 2048):
+        u = unpack_codes(w[r0:r0 + 2048], K).astype(np.float32)
+        out[r0:r0 + 2048] = bf(u * np.repeat(s[r0:r0 + 2048], group, axis=1) + np.repeat(b[r0:r0 + 2048], group, axis=1))
+    return out
+
+
 def matmul(x, w, scales, biases, group, acc=np.float64):
     """y = bf16(x . dequant(w)^T): what nn.QuantizedLinear computes (volundr.py:185-190), fp32 accumulation in the
     reference; float64 here so the oracle carries no accumulation-order noise of its own (tolerance rtol 2e-2)."""

@@ -14,6 +14,7 @@ SIGNATURES = {
     "vk_set_pdl": (None, [c_int]),
     "vk_status_fetch": (c_int, [c_void_p, c_void_p]),
     "vk_status_string": (c_char_p, [c_int]),
+    "vk_launch_count": (ctypes.c_longlong, [c_int]),
     "vk_w4_packed_bytes": (c_size_t, [c_int, c_int]),
     "vk_w4_repack": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p]),
     "vk_w4_dequant": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p]),

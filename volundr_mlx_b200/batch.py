@@ -117,6 +117,7 @@ class BatchCache:
             g.max_pages, g.n_pages = self.max_pages, n_pages
             self.geom[mix] = g
         self.graphs = {}
+        self.kernels_per_step = None
         self.use_graph = True
         self.steps = 0
 
@@ -395,8 +396,10 @@ def forward(model: Model, bc: BatchCache, toks, capture=()):
             # library's kernels need no lazy initialisation beyond the first GEMM's attribute calls
             model_warm(model)
             g = torch.cuda.CUDAGraph()
+            n0 = _lib.lib().vk_launch_count(0)
             with torch.cuda.graph(g):
                 _launch_step(model, bc, capture)
+            bc.kernels_per_step = _lib.lib().vk_launch_count(0) - n0
             bc.graphs[key] = g
         g.replay()
         caps = []

@@ -105,6 +105,7 @@ __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepc
 
 // Host: launch with the PDL attribute (the kernel must call pdl_wait before reading its inputs).
 bool vk_pdl_enabled();
+extern long long g_vk_launches;  // kernels launched through vk_launch since the last reset (host counter)
 template <typename... KArgs, typename... Args>
 static inline cudaError_t vk_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
                                     Args... args) {
@@ -118,6 +119,7 @@ static inline cudaError_t vk_launch(void (*kernel)(KArgs...), dim3 grid, dim3 bl
     attr[0].val.programmaticStreamSerializationAllowed = vk_pdl_enabled() ? 1 : 0;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
+    g_vk_launches++;
     return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
 }
 

@@ -1,6 +1,8 @@
 // Library-wide state: the device status word and the programmatic-dependent-launch switch.
 #include "common.cuh"
 
+long long g_vk_launches = 0;
+
 namespace {
 bool g_pdl = true;
 __global__ void vk_status_fetch_kernel(int* out) {
@@ -34,5 +36,12 @@ const char* vk_status_string(int code) {
 }
 
 int vk_version() { return 1; }
+
+// Kernels launched by this library since the last call with reset != 0 (a graph capture counts its kernels once).
+long long vk_launch_count(int reset) {
+    const long long n = g_vk_launches;
+    if (reset) g_vk_launches = 0;
+    return n;
+}
 
 }  // extern "C"

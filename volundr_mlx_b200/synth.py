@@ -180,10 +180,10 @@ def make_params(a: ModelArgs, seed: int = 0, quant: bool = True, bias_mode: str 
     for name, (n, k) in linear_shapes(a).items():
         quantize = quant and not any(t in name for t in _BF16_LINEARS) and k % g == 0
         if quantize:
-            u = rng.integers(0, 16, size=(n, k), dtype=np.uint8)
+            words = rng.integers(0, 1 << 32, size=(n, k // 8), dtype=np.uint32)  # eight uniform codes per word
             s = bf(np.abs(rng.normal(0, 0.02, size=(n, k // g))) / 8 + 1e-5)
             b = bf(rng.normal(0, 0.01, size=(n, k // g))) if bias_mode == "free" else bf(-8.0 * s)
-            p[name + ".weight"], p[name + ".scales"], p[name + ".biases"] = pack_codes(u), s, b
+            p[name + ".weight"], p[name + ".scales"], p[name + ".biases"] = words, s, b
         else:
             p[name + ".weight"] = r(rng.normal(0, weight_std, size=(n, k)))
         if name.endswith("engram.gate"):

@@ -22,19 +22,26 @@ BF16 = torch.bfloat16
 
 
 def _t(a, device, dtype=None):
-    t = torch.from_numpy(np.ascontiguousarray(a)).to(device)
-    return t if dtype is None else t.to(dtype)
+    """numpy array or tensor -> contiguous device tensor (bf16-valued float arrays become bf16 when dtype says so)."""
+    t = a if torch.is_tensor(a) else torch.from_numpy(np.ascontiguousarray(a))
+    if not torch.is_tensor(a) and t.dtype == torch.uint32:
+        t = t.view(torch.int32)
+    t = t.to(device)
+    return t.contiguous() if dtype is None else t.to(dtype).contiguous()
 
 
 class _W4:
-    """Reference-layout pieces of a 4-bit linear (numpy), sliceable and stackable along the output dimension."""
+    """Reference-layout pieces of a 4-bit linear (device tensors), sliceable and stackable along the output rows."""
 
     def __init__(self, w, s, b):
         self.w, self.s, self.b = w, s, b
 
     @staticmethod
-    def get(p, name):
-        return _W4(p[name + ".weight"], p[name + ".scales"], p[name + ".biases"])
+    def get(p, name, device):
+        w = p[name + ".weight"]
+        if not torch.is_tensor(w):
+            w = torch.from_numpy(np.ascontiguousarray(w).view(np.int32))
+        return _W4(w.to(device), _t(p[name + ".scales"], device, BF16), _t(p[name + ".biases"], device, BF16))
 
     def rows(self, idx):
         return _W4(self.w[idx], self.s[idx], self.b[idx])
@@ -44,12 +51,116 @@ class _W4:
 
     @staticmethod
     def cat(parts):
-        return _W4(np.concatenate([x.w for x in parts]), np.concatenate([x.s for x in parts]),
-                   np.concatenate([x.b for x in parts]))
+        return _W4(torch.cat([x.w for x in parts]), torch.cat([x.s for x in parts]), torch.cat([x.b for x in parts]))
 
     def to_device(self, device, group):
-        w = torch.from_numpy(np.ascontiguousarray(self.w).view(np.int32)).to(device)
-        return ops.w4_repack(w, _t(self.s, device, BF16), _t(self.b, device, BF16), group)
+        return ops.w4_repack(self.w.contiguous(), self.s.contiguous(), self.b.contiguous(), group)
+
+
+class SynthParams:
+    """Random-init parameters generated on the GPU, one tensor per lookup, never all resident at once: the same
+    names, shapes and distributions as synth.make_params (codes uniform in [0, 15], scales |N(0, 0.02)| / 8 + 1e-5,
+    biases N(0, 0.01) or -8 scale), seeded per name. For models too large to draw on the host."""
+
+    def __init__(self, args: ModelArgs, device, seed: int = 0, bias_mode: str = "free"):
+        from . import synth
+
+        self.a, self.device, self.seed, self.bias_mode = args, device, seed, bias_mode
+        self.shapes = synth.linear_shapes(args)
+        self.bf16_linears = synth._BF16_LINEARS
+        self._shared = {}
+
+    def _gen(self, name):
+        g = torch.Generator(device=self.device)
+        g.manual_seed((hash_name(name) + 1000003 * self.seed) & 0x7FFFFFFFFFFF)
+        return g
+
+    def _normal(self, name, shape, std=1.0, mean=0.0, dtype=BF16):
+        x = torch.empty(shape, dtype=torch.float32, device=self.device).normal_(mean, std, generator=self._gen(name))
+        return x.to(dtype)
+
+    def __contains__(self, name):
+        try:
+            self[name]
+            return True
+        except KeyError:
+            return False
+
+    def __getitem__(self, name):
+        a = self.a
+        base, _, leaf = name.rpartition(".")
+        if base in self.shapes:
+            n, k = self.shapes[base]
+            quant = not any(t in base for t in self.bf16_linears) and k % a.quant_group == 0
+            if quant:
+                if leaf == "weight":
+                    lo = torch.randint(0, 1 << 16, (n, k // 8), device=self.device, generator=self._gen(name), dtype=torch.int32)
+                    hi = torch.randint(0, 1 << 16, (n, k // 8), device=self.device, generator=self._gen(name + "#hi"), dtype=torch.int32)
+                    return lo | (hi << 16)
+                s = (self._normal(base + ".scales", (n, k // a.quant_group), 0.02, dtype=torch.float32).abs() / 8 + 1e-5).to(BF16)
+                if leaf == "scales":
+                    return s
+                if leaf == "biases":
+                    if self.bias_mode == "free":
+                        return self._normal(name, (n, k // a.quant_group), 0.01)
+                    return (-8.0 * s.float()).to(BF16)
+            elif leaf == "weight":
+                return self._normal(name, (n, k), 0.02)
+            elif leaf == "bias" and base.endswith("engram.gate"):
+                return self._normal(name, (1,), 0.02)
+            raise KeyError(name)
+        H = a.hidden_size
+        Hk, HV = a.linear_num_key_heads, a.linear_num_value_heads
+        K, V = a.linear_key_head_dim, a.linear_value_head_dim
+        if name == "model.embed_tokens.weight":
+            return self._normal(name, (a.vocab_size, H), 1.0)
+        if name == "model.norm.weight" or leaf == "weight" and base.endswith(("input_layernorm", "post_attention_layernorm")):
+            return self._normal(name, (H,), 0.1)
+        if base.endswith(("q_norm", "k_norm")):
+            return self._normal(name, (a.head_dim,), 0.1)
+        if base.endswith("idx_norm"):
+            return self._normal(name, (a.bcsa_index_dim,), 0.1)
+        if ".mhc." in name:
+            n = a.mhc_streams
+            if base.endswith("norm"):
+                return self._normal(name, (H,), 0.1, 1.0)
+            if leaf in ("pre_static", "post_static"):
+                return self._normal(name, (n,), 0.2, 1.0)
+            if leaf == "res_static":
+                return (4.0 * torch.eye(n, device=self.device) + self._normal(name, (n, n), 1.0, dtype=torch.float32)).to(BF16)
+        if "linear_attn" in name:
+            C = 2 * Hk * K + HV * V
+            if leaf == "weight" and base.endswith("conv1d"):
+                return self._normal(name, (C, a.linear_conv_kernel_dim), 0.5, dtype=torch.float32)
+            if leaf == "A_log":
+                return self._normal(name, (HV,), 0.3, dtype=torch.float32)
+            if leaf == "dt_bias":
+                return self._normal(name, (HV * K,), 0.3, dtype=torch.float32)
+            if base.endswith("linear_attn.norm"):
+                return self._normal(name, (V,), 0.1, 1.0)
+        if "engram" in name:
+            cat = a.engram_dim * len(a.engram_orders)
+            if base.endswith("engram.table"):
+                if "table" not in self._shared:
+                    t = torch.empty((a.engram_rows, cat), dtype=BF16, device=self.device)
+                    g = self._gen("model.engram_table.weight")
+                    for i in range(0, a.engram_rows, 1 << 16):  # chunked: the fp32 staging copy stays small
+                        t[i:i + (1 << 16)] = torch.empty((min(1 << 16, a.engram_rows - i), cat), dtype=torch.float32,
+                                                        device=self.device).normal_(0, 1, generator=g).to(BF16)
+                    self._shared["table"] = t
+                return self._shared["table"]
+            if ".tables." in name:
+                return self._normal(name, (a.engram_rows, a.engram_dim), 1.0)
+            if base.endswith("engram.norm"):
+                return self._normal(name, (cat,), 0.1, 1.0)
+        raise KeyError(name)
+
+
+def hash_name(name: str) -> int:
+    h = 1469598103934665603
+    for ch in name.encode():
+        h = ((h ^ ch) * 1099511628211) & 0xFFFFFFFFFFFFFFFF
+    return h
 
 
 class Model:
@@ -75,7 +186,7 @@ class Model:
         self.norm_w = _t(params["model.norm.weight"], d, BF16)
         V = a.vocab_size
         assert V % n == 0
-        self.lm_head = _t(params["lm_head.weight"][r * (V // n):(r + 1) * (V // n)], d, BF16)
+        self.lm_head = _t(params["lm_head.weight"], d, BF16)[r * (V // n):(r + 1) * (V // n)].contiguous()
         self.layers = []
         self.engram_table = None
         for i, m in enumerate(a.mixer_types):
@@ -85,35 +196,35 @@ class Model:
             w["dyn"] = _t(params[M + "dyn.weight"], d, BF16)
             w["pre_s"] = _t(params[M + "pre_static"], d, BF16)
             w["post_s"] = _t(params[M + "post_static"], d, BF16)
-            w["res_s"] = _t(params[M + "res_static"].reshape(16), d, BF16)
+            w["res_s"] = _t(params[M + "res_static"], d, BF16).reshape(16).contiguous()
             w["ln_in"] = _t(params[L + "input_layernorm.weight"], d, BF16)
             w["ln_post"] = _t(params[L + "post_attention_layernorm.weight"], d, BF16)
             if m == "kda":
                 P = L + "linear_attn."
                 KD_full = a.linear_num_key_heads * 128
-                qkv = _W4.get(params, P + "in_proj_qkv")
+                qkv = _W4.get(params, P + "in_proj_qkv", d)
                 parts = [qkv.rows(sl(128, Hk)),                                    # q heads of this rank
                          qkv.rows(slice(KD_full + r * Hk * 128, KD_full + (r + 1) * Hk * 128)),
                          qkv.rows(slice(2 * KD_full + r * HV * 128, 2 * KD_full + (r + 1) * HV * 128)),
-                         _W4.get(params, P + "in_proj_z").rows(sl(128, HV)),
-                         _W4.get(params, P + "f_down")]
+                         _W4.get(params, P + "in_proj_z", d).rows(sl(128, HV)),
+                         _W4.get(params, P + "f_down", d)]
                 w["proj"] = _W4.cat(parts).to_device(d, g)
                 w["off_z"] = 2 * Hk * 128 + HV * 128
                 w["off_fd"] = w["off_z"] + HV * 128
-                w["in_proj_b"] = _t(params[P + "in_proj_b.weight"][r * HV:(r + 1) * HV], d, BF16)
-                w["f_up"] = _t(params[P + "f_up.weight"][sl(128, HV)], d, BF16)
-                cw = params[P + "conv1d.weight"]
+                w["in_proj_b"] = _t(params[P + "in_proj_b.weight"], d, BF16)[r * HV:(r + 1) * HV].contiguous()
+                w["f_up"] = _t(params[P + "f_up.weight"], d, BF16)[sl(128, HV)].contiguous()
+                cw = _t(params[P + "conv1d.weight"], d, torch.float32)
                 cidx = np.r_[np.arange(KD_full)[sl(128, Hk)], KD_full + np.arange(KD_full)[sl(128, Hk)],
                              2 * KD_full + np.arange(a.linear_num_value_heads * 128)[sl(128, HV)]]
-                w["conv_w"] = _t(cw[cidx].astype(np.float32), d)
-                w["A_log"] = _t(params[P + "A_log"][r * HV:(r + 1) * HV].astype(np.float32), d)
-                w["dt_bias"] = _t(params[P + "dt_bias"][sl(128, HV)].astype(np.float32), d)
+                w["conv_w"] = cw[torch.from_numpy(cidx).to(d)].contiguous()
+                w["A_log"] = _t(params[P + "A_log"], d, torch.float32)[r * HV:(r + 1) * HV].contiguous()
+                w["dt_bias"] = _t(params[P + "dt_bias"], d, torch.float32)[sl(128, HV)].contiguous()
                 w["gnorm"] = _t(params[P + "norm.weight"], d, BF16)
-                w["out"] = _W4.get(params, P + "out_proj").cols(r * HV * 128, (r + 1) * HV * 128, g).to_device(d, g)
+                w["out"] = _W4.get(params, P + "out_proj", d).cols(r * HV * 128, (r + 1) * HV * 128, g).to_device(d, g)
             else:
                 P = L + "self_attn."
-                parts = [_W4.get(params, P + "q_proj").rows(sl(2 * D, Hq)),
-                         _W4.get(params, P + "k_proj").rows(sl(D, KVH)), _W4.get(params, P + "v_proj").rows(sl(D, KVH))]
+                parts = [_W4.get(params, P + "q_proj", d).rows(sl(2 * D, Hq)),
+                         _W4.get(params, P + "k_proj", d).rows(sl(D, KVH)), _W4.get(params, P + "v_proj", d).rows(sl(D, KVH))]
                 w["proj"] = _W4.cat(parts).to_device(d, g)
                 w["off_k"] = Hq * 2 * D
                 w["off_v"] = w["off_k"] + KVH * D
@@ -123,11 +234,11 @@ class Model:
                     w["idx_q"] = _t(params[P + "idx_q.weight"], d, BF16)
                     w["idx_k"] = _t(params[P + "idx_k.weight"], d, BF16)
                     w["idx_norm"] = _t(params[P + "idx_norm.weight"], d, BF16)
-                w["out"] = _W4.get(params, P + "o_proj").cols(r * Hq * D, (r + 1) * Hq * D, g).to_device(d, g)
+                w["out"] = _W4.get(params, P + "o_proj", d).cols(r * Hq * D, (r + 1) * Hq * D, g).to_device(d, g)
             I = a.intermediate_size
-            gate, up = _W4.get(params, L + "mlp.gate_proj"), _W4.get(params, L + "mlp.up_proj")
+            gate, up = _W4.get(params, L + "mlp.gate_proj", d), _W4.get(params, L + "mlp.up_proj", d)
             w["gate_up"] = _W4.cat([gate.rows(sl(1, self.I)), up.rows(sl(1, self.I))]).to_device(d, g)
-            w["down"] = _W4.get(params, L + "mlp.down_proj").cols(r * self.I, (r + 1) * self.I, g).to_device(d, g)
+            w["down"] = _W4.get(params, L + "mlp.down_proj", d).cols(r * self.I, (r + 1) * self.I, g).to_device(d, g)
             if i in a.engram_layers:
                 E = L + "engram."
                 cat = a.engram_dim * len(a.engram_orders)
@@ -142,8 +253,8 @@ class Model:
                     w["eng_ld"] = [a.engram_dim] * len(a.engram_orders)
                     w["eng_col0"] = [0] * len(a.engram_orders)
                 w["eng_norm"] = _t(params[E + "norm.weight"], d, BF16)
-                w["eng_gate_w"] = _t(params[E + "gate.weight"].reshape(-1), d, BF16)
-                w["eng_gate_b"] = _t(params[E + "gate.bias"].reshape(-1), d, BF16)
+                w["eng_gate_w"] = _t(params[E + "gate.weight"], d, BF16).reshape(-1).contiguous()
+                w["eng_gate_b"] = _t(params[E + "gate.bias"], d, BF16).reshape(-1).contiguous()
                 if a.engram_value:
                     w["eng_value"] = _t(params[E + "value.weight"], d, BF16)
                 w["eng_ptrs"] = (np.array([t.data_ptr() for t in w["eng_tables"]], dtype=np.uint64),
