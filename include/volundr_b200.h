@@ -43,14 +43,15 @@ int vk_w4_repack(const void* w, const void* scales, const void* biases, int N, i
  * weights (volundr-mlx/tests/test_volundr.py:127-156). */
 int vk_w4_dequant(const void* w, const void* scales, const void* biases, int N, int K, int group, void* out,
                   vk_stream_t stream);
-/* Workspace bytes vk_w4_gemm needs for this shape (arrival counters + split-K partial sums). The first 16 KiB of the
- * workspace must be zero before the first call and are left zero by every call. */
+/* Workspace bytes vk_w4_gemm needs for this shape (arrival counters, the activation records, partial sums of ranges
+ * that split a block of rows over K). The first 16 KiB of the workspace must be zero before the first call and are
+ * left zero by every call. */
 size_t vk_w4_workspace_bytes(int M, int N, int K);
 /* y[M, ldy] (bf16) = x[M, ldx] (bf16) . dequant(W)^T, fp32 accumulation. ldx a multiple of 8, x 16-byte aligned. */
 int vk_w4_gemm(const void* packed, const void* x, int ldx, void* y, int ldy, int M, int N, int K, void* workspace,
                size_t workspace_bytes, vk_stream_t stream);
-/* Testing aid: force warps per CTA (4 or 8) and the number of K slabs; 0 = choose automatically. */
-void vk_w4_force_plan(int warps, int split);
+/* Testing aid: force the number of persistent CTAs the work is dealt to (0 = two per SM); second argument unused. */
+void vk_w4_force_plan(int ctas, int unused);
 
 /* ---- row-wise fused kernels (one CTA per token row). bf16 activations [B, D] unless noted. */
 /* x = embed[tok]; H[b][0..3] = x; hn = RMSNorm(x) * w_mhc0 (volundr-mlx/volundr.py:921-930, :944; batch.py:525-538).
@@ -60,10 +61,11 @@ int vk_embed(const int* tok, const void* embed, const void* w_mhc0, void* H, voi
              int* engram_rows_out, const int* orders, int n_orders, int engram_rows, int B, int D, float eps,
              vk_stream_t stream);
 /* MHC.mix_norm (volundr.py:336-340; decode_fused.py:230-248; ops: volundr.py:264-278, :237-243): dyn linear, pre /
- * post, Sinkhorn, x_in, h = OffsetRMSNorm(x_in) * (1 + w_in). post [B,4], res [B,16] are fp32 holding bf16 values. */
+ * post, Sinkhorn, x_in, h = OffsetRMSNorm(x_in) * (1 + w_in). post [B,4], res [B,16] are fp32 holding bf16 values;
+ * d_scratch [B, 24] fp32 receives the dyn linear's output. */
 int vk_mhc_mix_norm(const void* H, const void* hn, const void* w_dyn, const void* pre_s, const void* post_s,
-                    const void* res_s, const void* w_in, void* x_in, void* h, float* post, float* res, int B, int D,
-                    int iters, float eps, vk_stream_t stream);
+                    const void* res_s, const void* w_in, void* x_in, void* h, float* post, float* res, float* d_scratch,
+                    int B, int D, int iters, float eps, vk_stream_t stream);
 /* kernels.rms_norm(x, w, eps, offset, r) (kernels.py:285-306; volundr.py:893-899): h2 = bf16(x + r) (r, h2 may be
  * NULL), hn = RMSNorm(h2) * (offset + w). */
 int vk_add_rmsnorm(const void* x, const void* r, const void* w, void* h2, void* hn, int B, int D, float eps, int offset,

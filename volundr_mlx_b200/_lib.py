@@ -22,7 +22,7 @@ SIGNATURES = {
     "vk_w4_workspace_bytes": (c_size_t, [c_int, c_int, c_int]),
     "vk_w4_gemm": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_size_t, c_void_p]),
     "vk_embed": (c_int, [c_void_p] * 7 + [c_void_p, c_int, c_int, c_int, c_int, c_float, c_void_p]),
-    "vk_mhc_mix_norm": (c_int, [c_void_p] * 11 + [c_int, c_int, c_int, c_float, c_void_p]),
+    "vk_mhc_mix_norm": (c_int, [c_void_p] * 12 + [c_int, c_int, c_int, c_float, c_void_p]),
     "vk_add_rmsnorm": (c_int, [c_void_p] * 5 + [c_int, c_int, c_float, c_int, c_void_p]),
     "vk_silu_mul": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
     "vk_engram_gather": (c_int, [c_void_p] * 6 + [c_int, c_int, c_int, c_float, c_void_p]),
@@ -64,5 +64,6 @@ def lib():
 
 def check(rc: int, what: str):
     if rc != 0:
-        kind = "invalid argument" if rc == -1 else "workspace too small" if rc == -2 else f"CUDA error {rc}"
+        kind = {-1: "invalid argument", -2: "workspace too small",
+                -3: "problem larger than the entry point's fixed capacity"}.get(rc, f"CUDA error {rc}")
         raise RuntimeError(f"{what}: {kind}")

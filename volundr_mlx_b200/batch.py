@@ -80,7 +80,7 @@ class BatchCache:
             wid = max(wid, w["proj"].N)
         self.H = torch.zeros((S, 4, D), **bf)
         self.hn, self.x_in, self.h = (torch.zeros((S, D), **bf) for _ in range(3))
-        self.post, self.res = torch.zeros((S, 4), **f32), torch.zeros((S, 16), **f32)
+        self.post, self.res, self.dyn = torch.zeros((S, 4), **f32), torch.zeros((S, 16), **f32), torch.zeros((S, 24), **f32)
         self.proj = torch.zeros((S, wid), **bf)
         self.mix = torch.zeros((S, max(m.HV * 128, m.Hq * 128)), **bf)
         self.r, self.h2, self.hn2, self.mlp = (torch.zeros((S, D), **bf) for _ in range(4))
@@ -311,7 +311,7 @@ def _launch_step(model: Model, bc: BatchCache, capture=()):
         if i in capture:
             caps.append(bc.H[:B, 0].clone())
         ck(L.vk_mhc_mix_norm(_p(bc.H), _p(bc.hn), _p(w["dyn"]), _p(w["pre_s"]), _p(w["post_s"]), _p(w["res_s"]),
-                             _p(w["ln_in"]), _p(bc.x_in), _p(bc.h), _p(bc.post), _p(bc.res), B, D, a.mhc_sinkhorn_iters,
+                             _p(w["ln_in"]), _p(bc.x_in), _p(bc.h), _p(bc.post), _p(bc.res), _p(bc.dyn), B, D, a.mhc_sinkhorn_iters,
                              eps, st), "vk_mhc_mix_norm")
         gemm(bc.h, w["proj"], bc.proj)
         if w["mixer"] == "kda":

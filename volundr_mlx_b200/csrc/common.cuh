@@ -8,6 +8,7 @@
 #define VK_OK 0
 #define VK_EINVAL (-1)
 #define VK_ENOSPC (-2)
+#define VK_ETOOBIG (-3)  // the problem exceeds a fixed capacity of the entry point
 
 // Device-side status word: 0 = fine; otherwise the code of the first kernel that gave up on a bounded wait or met
 // an out-of-range index. Read (and cleared) by vk_status_read at the caller's sync point.

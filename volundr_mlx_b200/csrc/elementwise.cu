@@ -15,6 +15,34 @@ __device__ __forceinline__ float ldbf(const __nv_bfloat16* p, size_t i) { return
 // sum over the block in a fixed order (see block_sum)
 __device__ __forceinline__ float ew_block_sum(float v, float* red) { return block_sum<kEwWarps>(v, red); }
 
+// row kernels that move whole rows: one 16-byte piece (8 bf16) per thread and pass, blockDim = min(1024, D / 8 up to
+// a warp multiple); sums over a block of any width in a fixed order
+constexpr int kRowMaxWarps = 32;
+__device__ __forceinline__ float row_block_sum(float v, float* red) {
+    const int nw = (blockDim.x + 31) >> 5;
+    v = warp_sum(v);
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+    __syncthreads();
+    float t = 0.f;
+    for (int i = 0; i < nw; i++) t += red[i];
+    return t;
+}
+__device__ __forceinline__ void ld8(const __nv_bfloat16* p, float (&x)[8]) {
+    const uint4 u = *reinterpret_cast<const uint4*>(p);
+    x[0] = bf_lo(u.x); x[1] = bf_hi(u.x); x[2] = bf_lo(u.y); x[3] = bf_hi(u.y);
+    x[4] = bf_lo(u.z); x[5] = bf_hi(u.z); x[6] = bf_lo(u.w); x[7] = bf_hi(u.w);
+}
+__device__ __forceinline__ void st8(__nv_bfloat16* p, const float (&x)[8]) {
+    uint4 u;
+    u.x = pack_bf2(x[0], x[1]); u.y = pack_bf2(x[2], x[3]); u.z = pack_bf2(x[4], x[5]); u.w = pack_bf2(x[6], x[7]);
+    *reinterpret_cast<uint4*>(p) = u;
+}
+static inline int row_threads(int D) {
+    int t = ((D / 8 + 31) / 32) * 32;
+    return t > 1024 ? 1024 : (t < 32 ? 32 : t);
+}
+
 // ------------------------------------------------------------------------------------------------ embedding
 // x = embed[tok]; the four residual streams start as copies of x (volundr.py:929-930); hn = RMSNorm(x) * w0 is the
 // first layer's mHC norm input (volundr.py:944). Also advances the Engram id window and hashes the n-gram rows
@@ -73,7 +101,7 @@ __global__ void __launch_bounds__(kEwThreads) embed_kernel(const EmbedParams p) 
 struct MixParams {
     const __nv_bfloat16* H;        // [B, 4, D]
     const __nv_bfloat16* hn;       // [B, D]
-    const __nv_bfloat16* w_dyn;    // [24, D]
+    const float* d;                // [B, 24] dyn(hn), bf16-valued
     const __nv_bfloat16* pre_s;    // [4]
     const __nv_bfloat16* post_s;   // [4]
     const __nv_bfloat16* res_s;    // [16]
@@ -86,31 +114,37 @@ struct MixParams {
     float eps;
 };
 
-__global__ void __launch_bounds__(kEwThreads) mhc_mix_norm_kernel(const MixParams p) {
-    __shared__ float red[kEwWarps];
-    __shared__ float dsm[24];
+// d[b][j] = bf16(hn[b] . w_dyn[j]), one warp per (row, output)
+__global__ void __launch_bounds__(256) mhc_dyn_kernel(const __nv_bfloat16* __restrict__ hn, const __nv_bfloat16* __restrict__ w_dyn,
+                                                      float* __restrict__ d, int B, int D) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int wid = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (wid >= B * 24) return;
+    const int b = wid / 24, j = wid - b * 24;
+    const __nv_bfloat16* x = hn + (size_t)b * D;
+    const __nv_bfloat16* w = w_dyn + (size_t)j * D;
+    float a = 0.f;
+    for (int k = lane * 8; k < D; k += 256) {
+        float xv[8], wv[8];
+        ld8(x + k, xv);
+        ld8(w + k, wv);
+#pragma unroll
+        for (int e = 0; e < 8; e++) a = fmaf(xv[e], wv[e], a);
+    }
+    a = warp_sum(a);
+    if (lane == 0) d[wid] = bfr(a);
+}
+
+__global__ void __launch_bounds__(1024) mhc_mix_norm_kernel(const MixParams p) {
+    __shared__ float red[kRowMaxWarps];
     __shared__ float pre_sm[4];
     pdl_launch_dependents();
     pdl_wait();
     const int b = blockIdx.x;
     const int D = p.D;
-    const __nv_bfloat16* hn = p.hn + (size_t)b * D;
-    // the 24 dot products, 4 at a time to bound registers
-    for (int j0 = 0; j0 < 24; j0 += 4) {
-        float a[4] = {0.f, 0.f, 0.f, 0.f};
-        for (int i = threadIdx.x; i < D; i += kEwThreads) {
-            const float x = bf2f(hn[i]);
-#pragma unroll
-            for (int j = 0; j < 4; j++) a[j] = fmaf(x, bf2f(p.w_dyn[(size_t)(j0 + j) * D + i]), a[j]);
-        }
-#pragma unroll
-        for (int j = 0; j < 4; j++) {
-            const float t = ew_block_sum(a[j], red);
-            if (threadIdx.x == 0) dsm[j0 + j] = bfr(t);
-        }
-    }
-    __syncthreads();
     if (threadIdx.x == 0) {
+        const float* dsm = p.d + b * 24;
         float m[16];
         float mx = -INFINITY;
         for (int k = 0; k < 16; k++) {
@@ -134,50 +168,98 @@ __global__ void __launch_bounds__(kEwThreads) mhc_mix_norm_kernel(const MixParam
             p.post[b * 4 + s] = bfr(bf2f(p.post_s[s]) + dsm[4 + s]);
         }
     }
+    // (threads other than 0 load their pieces of H meanwhile)
+    const __nv_bfloat16* Hb = p.H + (size_t)b * 4 * D;
+    const int k0 = threadIdx.x * 8;
+    float h0[8], h1[8], h2[8], h3[8];
+    if (k0 < D) { ld8(Hb + k0, h0); ld8(Hb + D + k0, h1); ld8(Hb + 2 * (size_t)D + k0, h2); ld8(Hb + 3 * (size_t)D + k0, h3); }
     __syncthreads();
     const float pr0 = pre_sm[0], pr1 = pre_sm[1], pr2 = pre_sm[2], pr3 = pre_sm[3];
-    const __nv_bfloat16* Hb = p.H + (size_t)b * 4 * D;
     float ss = 0.f;
-    for (int i = threadIdx.x; i < D; i += kEwThreads) {
-        const float p0 = bfr(pr0 * bf2f(Hb[i])), p1 = bfr(pr1 * bf2f(Hb[D + i]));
-        const float p2 = bfr(pr2 * bf2f(Hb[2 * D + i])), p3 = bfr(pr3 * bf2f(Hb[3 * D + i]));
-        const float x = bfr(((p0 + p1) + p2) + p3);
-        p.x_in[(size_t)b * D + i] = f2bf(x);
-        ss += x * x;
+    float x0[8];
+    for (int k = k0; k < D; k += blockDim.x * 8) {
+        if (k != k0) { ld8(Hb + k, h0); ld8(Hb + D + k, h1); ld8(Hb + 2 * (size_t)D + k, h2); ld8(Hb + 3 * (size_t)D + k, h3); }
+        float x[8];
+#pragma unroll
+        for (int e = 0; e < 8; e++) {
+            x[e] = bfr(((bfr(pr0 * h0[e]) + bfr(pr1 * h1[e])) + bfr(pr2 * h2[e])) + bfr(pr3 * h3[e]));
+            ss += x[e] * x[e];
+        }
+        st8(p.x_in + (size_t)b * D + k, x);
+        if (k == k0) {
+#pragma unroll
+            for (int e = 0; e < 8; e++) x0[e] = x[e];
+        }
     }
-    ss = ew_block_sum(ss, red);
+    ss = row_block_sum(ss, red);
     const float inv = rsqrtf(ss / (float)D + p.eps);
-    for (int i = threadIdx.x; i < D; i += kEwThreads) {
-        const float x = bf2f(p.x_in[(size_t)b * D + i]);
-        p.h[(size_t)b * D + i] = f2bf((x * inv) * (1.f + bf2f(p.w_in[i])));
+    for (int k = k0; k < D; k += blockDim.x * 8) {
+        float x[8], w[8], o[8];
+        if (k == k0) {
+#pragma unroll
+            for (int e = 0; e < 8; e++) x[e] = x0[e];
+        } else {
+            ld8(p.x_in + (size_t)b * D + k, x);
+        }
+        ld8(p.w_in + k, w);
+#pragma unroll
+        for (int e = 0; e < 8; e++) o[e] = (x[e] * inv) * (1.f + w[e]);
+        st8(p.h + (size_t)b * D + k, o);
     }
 }
 
 // ------------------------------------------------------------------------------------------------ add + norm
 // h2 = bf(x + r); hn = bf(h2 * rsqrt(mean h2^2 + eps) * (off + w))      (volundr.py:893-899)
-__global__ void __launch_bounds__(kEwThreads) add_rmsnorm_kernel(const __nv_bfloat16* __restrict__ x,
-                                                                 const __nv_bfloat16* __restrict__ r,
-                                                                 const __nv_bfloat16* __restrict__ w,
-                                                                 __nv_bfloat16* __restrict__ h2,
-                                                                 __nv_bfloat16* __restrict__ hn, int D, float eps,
-                                                                 float offset) {
-    __shared__ float red[kEwWarps];
+__global__ void __launch_bounds__(1024) add_rmsnorm_kernel(const __nv_bfloat16* __restrict__ x,
+                                                           const __nv_bfloat16* __restrict__ r,
+                                                           const __nv_bfloat16* __restrict__ w,
+                                                           __nv_bfloat16* __restrict__ h2,
+                                                           __nv_bfloat16* __restrict__ hn, int D, float eps,
+                                                           float offset) {
+    __shared__ float red[kRowMaxWarps];
     pdl_launch_dependents();
     pdl_wait();
     const size_t base = (size_t)blockIdx.x * D;
+    const int k0 = threadIdx.x * 8;
     float ss = 0.f;
-    for (int i = threadIdx.x; i < D; i += kEwThreads) {
-        float v = bf2f(x[base + i]);
-        if (r != nullptr) v = bfr(v + bf2f(r[base + i]));
-        if (h2 != nullptr) h2[base + i] = f2bf(v);
-        ss += v * v;
+    float v0[8];
+    for (int k = k0; k < D; k += blockDim.x * 8) {
+        float v[8];
+        ld8(x + base + k, v);
+        if (r != nullptr) {
+            float rv[8];
+            ld8(r + base + k, rv);
+#pragma unroll
+            for (int e = 0; e < 8; e++) v[e] = bfr(v[e] + rv[e]);
+        }
+        if (h2 != nullptr) st8(h2 + base + k, v);
+#pragma unroll
+        for (int e = 0; e < 8; e++) ss += v[e] * v[e];
+        if (k == k0) {
+#pragma unroll
+            for (int e = 0; e < 8; e++) v0[e] = v[e];
+        }
     }
-    ss = ew_block_sum(ss, red);
+    ss = row_block_sum(ss, red);
     const float inv = rsqrtf(ss / (float)D + eps);
-    for (int i = threadIdx.x; i < D; i += kEwThreads) {
-        float v = bf2f(x[base + i]);
-        if (r != nullptr) v = bfr(v + bf2f(r[base + i]));
-        hn[base + i] = f2bf((v * inv) * (offset + bf2f(w[i])));
+    for (int k = k0; k < D; k += blockDim.x * 8) {
+        float v[8], wv[8], o[8];
+        if (k == k0) {
+#pragma unroll
+            for (int e = 0; e < 8; e++) v[e] = v0[e];
+        } else {
+            ld8(x + base + k, v);
+            if (r != nullptr) {
+                float rv[8];
+                ld8(r + base + k, rv);
+#pragma unroll
+                for (int e = 0; e < 8; e++) v[e] = bfr(v[e] + rv[e]);
+            }
+        }
+        ld8(w + k, wv);
+#pragma unroll
+        for (int e = 0; e < 8; e++) o[e] = (v[e] * inv) * (offset + wv[e]);
+        st8(hn + base + k, o);
     }
 }
 
@@ -250,20 +332,24 @@ struct CombineParams {
     float eps;
 };
 
-__global__ void __launch_bounds__(kEwThreads) mhc_combine_norm_kernel(const CombineParams p) {
-    __shared__ float red[kEwWarps];
+__global__ void __launch_bounds__(1024) mhc_combine_norm_kernel(const CombineParams p) {
+    __shared__ float red[kRowMaxWarps];
     pdl_launch_dependents();
     pdl_wait();
     const int b = blockIdx.x, D = p.D;
     const size_t base = (size_t)b * D;
+    const int k0 = threadIdx.x * 8;
+    const int stride = blockDim.x * 8;
     float gate = 0.f;
     if (p.eng_val != nullptr) {
         float a = 0.f;
-        for (int i = threadIdx.x; i < D; i += kEwThreads) {
-            const float y = bfr(bf2f(p.h2[base + i]) + bf2f(p.m[base + i]));
-            a = fmaf(y, bf2f(p.eng_gate_w[i]), a);
+        for (int k = k0; k < D; k += stride) {
+            float hv[8], mv[8], gw[8];
+            ld8(p.h2 + base + k, hv); ld8(p.m + base + k, mv); ld8(p.eng_gate_w + k, gw);
+#pragma unroll
+            for (int e = 0; e < 8; e++) a = fmaf(bfr(hv[e] + mv[e]), gw[e], a);
         }
-        a = ew_block_sum(a, red);
+        a = row_block_sum(a, red);
         const float lin = bfr(a + bf2f(p.eng_gate_b[0]));
         gate = bfr(1.f / (1.f + expf(-lin)));
     }
@@ -274,41 +360,55 @@ __global__ void __launch_bounds__(kEwThreads) mhc_combine_norm_kernel(const Comb
     for (int s = 0; s < 4; s++) po[s] = p.post[b * 4 + s];
     __nv_bfloat16* Hb = p.H + (size_t)b * 4 * D;
     float ss = 0.f;
-    for (int i = threadIdx.x; i < D; i += kEwThreads) {
-        float y = bfr(bf2f(p.h2[base + i]) + bf2f(p.m[base + i]));
-        if (p.eng_val != nullptr) y = bfr(y + bfr(gate * bf2f(p.eng_val[base + i])));
-        if (p.y_out != nullptr) p.y_out[base + i] = f2bf(y);
-        const float delta = bfr(y - bf2f(p.x_in[base + i]));
-        float hj[4], o[4];
+    float keep[8];
+    for (int k = k0; k < D; k += stride) {
+        float hv[8], mv[8], xv[8], hj[4][8], o[4][8], y[8], val[8];
+        ld8(p.h2 + base + k, hv); ld8(p.m + base + k, mv); ld8(p.x_in + base + k, xv);
 #pragma unroll
-        for (int j = 0; j < 4; j++) hj[j] = bf2f(Hb[(size_t)j * D + i]);
+        for (int j = 0; j < 4; j++) ld8(Hb + (size_t)j * D + k, hj[j]);
+        if (p.eng_val != nullptr) ld8(p.eng_val + base + k, val);
 #pragma unroll
-        for (int s = 0; s < 4; s++) {
-            float mixed = r[4 * s] * hj[0];
-            mixed = fmaf(r[4 * s + 1], hj[1], mixed);
-            mixed = fmaf(r[4 * s + 2], hj[2], mixed);
-            mixed = fmaf(r[4 * s + 3], hj[3], mixed);
-            o[s] = bfr(bfr(mixed) + bfr(po[s] * delta));
+        for (int e = 0; e < 8; e++) {
+            y[e] = bfr(hv[e] + mv[e]);
+            if (p.eng_val != nullptr) y[e] = bfr(y[e] + bfr(gate * val[e]));
+            const float delta = bfr(y[e] - xv[e]);
+#pragma unroll
+            for (int s = 0; s < 4; s++) {
+                float mixed = r[4 * s] * hj[0][e];
+                mixed = fmaf(r[4 * s + 1], hj[1][e], mixed);
+                mixed = fmaf(r[4 * s + 2], hj[2][e], mixed);
+                mixed = fmaf(r[4 * s + 3], hj[3][e], mixed);
+                o[s][e] = bfr(bfr(mixed) + bfr(po[s] * delta));
+            }
+            const float v = p.final_norm ? o[0][e] : bfr((((o[0][e] + o[1][e]) + o[2][e]) + o[3][e]) * 0.25f);
+            ss += v * v;
+            if (k == k0) keep[e] = v;
         }
+        if (p.y_out != nullptr) st8(p.y_out + base + k, y);
 #pragma unroll
-        for (int s = 0; s < 4; s++) Hb[(size_t)s * D + i] = f2bf(o[s]);
-        const float v = p.final_norm ? o[0] : bfr((((o[0] + o[1]) + o[2]) + o[3]) * 0.25f);
-        ss += v * v;
+        for (int s = 0; s < 4; s++) st8(Hb + (size_t)s * D + k, o[s]);
     }
     if (p.w_next == nullptr) return;
-    ss = ew_block_sum(ss, red);
+    ss = row_block_sum(ss, red);
     const float inv = rsqrtf(ss / (float)D + p.eps);
     const float off = p.final_norm ? 1.f : 0.f;
-    for (int i = threadIdx.x; i < D; i += kEwThreads) {
-        float v;
-        if (p.final_norm) {
-            v = bf2f(Hb[i]);
+    for (int k = k0; k < D; k += stride) {
+        float v[8], w[8], o[8];
+        if (k == k0) {
+#pragma unroll
+            for (int e = 0; e < 8; e++) v[e] = keep[e];
+        } else if (p.final_norm) {
+            ld8(Hb + k, v);
         } else {
-            const float o0 = bf2f(Hb[i]), o1 = bf2f(Hb[(size_t)D + i]), o2 = bf2f(Hb[(size_t)2 * D + i]),
-                        o3 = bf2f(Hb[(size_t)3 * D + i]);
-            v = bfr((((o0 + o1) + o2) + o3) * 0.25f);
+            float o0[8], o1[8], o2[8], o3[8];
+            ld8(Hb + k, o0); ld8(Hb + (size_t)D + k, o1); ld8(Hb + 2 * (size_t)D + k, o2); ld8(Hb + 3 * (size_t)D + k, o3);
+#pragma unroll
+            for (int e = 0; e < 8; e++) v[e] = bfr((((o0[e] + o1[e]) + o2[e]) + o3[e]) * 0.25f);
         }
-        p.hn[base + i] = f2bf((v * inv) * (off + bf2f(p.w_next[i])));
+        ld8(p.w_next + k, w);
+#pragma unroll
+        for (int e = 0; e < 8; e++) o[e] = (v[e] * inv) * (off + w[e]);
+        st8(p.hn + base + k, o);
     }
 }
 
@@ -409,19 +509,21 @@ int vk_embed(const int* tok, const void* embed, const void* w_mhc0, void* H, voi
 }
 
 int vk_mhc_mix_norm(const void* H, const void* hn, const void* w_dyn, const void* pre_s, const void* post_s,
-                    const void* res_s, const void* w_in, void* x_in, void* h, float* post, float* res, int B, int D,
-                    int iters, float eps, cudaStream_t stream) {
-    if (B <= 0 || D <= 0) return VK_EINVAL;
-    MixParams p = {(const __nv_bfloat16*)H, (const __nv_bfloat16*)hn, (const __nv_bfloat16*)w_dyn,
+                    const void* res_s, const void* w_in, void* x_in, void* h, float* post, float* res, float* d_scratch,
+                    int B, int D, int iters, float eps, cudaStream_t stream) {
+    if (B <= 0 || D <= 0 || D % 8 != 0 || d_scratch == nullptr) return VK_EINVAL;
+    VK_CUDA(vk_launch(mhc_dyn_kernel, dim3((B * 24 + 7) / 8), dim3(256), 0, stream, (const __nv_bfloat16*)hn,
+                      (const __nv_bfloat16*)w_dyn, d_scratch, B, D));
+    MixParams p = {(const __nv_bfloat16*)H, (const __nv_bfloat16*)hn, d_scratch,
                    (const __nv_bfloat16*)pre_s, (const __nv_bfloat16*)post_s, (const __nv_bfloat16*)res_s,
                    (const __nv_bfloat16*)w_in, (__nv_bfloat16*)x_in, (__nv_bfloat16*)h, post, res, D, iters, eps};
-    return (int)vk_launch(mhc_mix_norm_kernel, dim3(B), dim3(kEwThreads), 0, stream, p);
+    return (int)vk_launch(mhc_mix_norm_kernel, dim3(B), dim3(row_threads(D)), 0, stream, p);
 }
 
 int vk_add_rmsnorm(const void* x, const void* r, const void* w, void* h2, void* hn, int B, int D, float eps, int offset,
                    cudaStream_t stream) {
-    if (B <= 0 || D <= 0) return VK_EINVAL;
-    return (int)vk_launch(add_rmsnorm_kernel, dim3(B), dim3(kEwThreads), 0, stream, (const __nv_bfloat16*)x,
+    if (B <= 0 || D <= 0 || D % 8 != 0) return VK_EINVAL;
+    return (int)vk_launch(add_rmsnorm_kernel, dim3(B), dim3(row_threads(D)), 0, stream, (const __nv_bfloat16*)x,
                           (const __nv_bfloat16*)r, (const __nv_bfloat16*)w, (__nv_bfloat16*)h2, (__nv_bfloat16*)hn, D, eps,
                           offset ? 1.f : 0.f);
 }
@@ -453,7 +555,8 @@ int vk_mhc_combine_norm(void* H, const void* h2, const void* m, const void* x_in
                        post, res, (const __nv_bfloat16*)w_next, (__nv_bfloat16*)hn, (const __nv_bfloat16*)eng_val,
                        (const __nv_bfloat16*)eng_gate_w, (const __nv_bfloat16*)eng_gate_b, (__nv_bfloat16*)y_out, D,
                        final_norm, eps};
-    return (int)vk_launch(mhc_combine_norm_kernel, dim3(B), dim3(kEwThreads), 0, stream, p);
+    if (D % 8 != 0) return VK_EINVAL;
+    return (int)vk_launch(mhc_combine_norm_kernel, dim3(B), dim3(row_threads(D)), 0, stream, p);
 }
 
 int vk_bf16_gemm(const void* x, int ldx, const void* W, const void* bias, void* y, int ldy, int M, int N, int K,

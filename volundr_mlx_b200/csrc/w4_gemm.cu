@@ -3,48 +3,56 @@
 // Replaces mx.quantized_matmul as called by every nn.QuantizedLinear of the reference (volundr.py:185-190, 377-386,
 // 645-648) and the reference's small-M kernel qmm_nax_prepped (agens-mlx-bench/smallm/qmm_nax.py:28-139). Like that
 // kernel it multiplies the raw 4-bit codes on the tensor cores and applies scale and bias per (row, group) to the
-// fp32 group product: acc += s * (x_g . u_g) + b * sum(x_g).
+// fp32 group product, acc += s * (x_g . u_g) + b * sum(x_g), with the per-group activation sums prepared ahead of
+// the product (the reference's prep_nax.prep, smallm/prep_nax.py:123-148).
 //
-// Memory layout. The reference layout (convert.py:7-14: u32 [N, K/8], nibble j of a word = element 8w + j, lowest
-// first; bf16 scales / biases [N, K/G]) is repacked once at load time (vk_w4_repack) into a stream of 1152-byte
-// chunks, one per (32 output rows, 64 input columns):
+// Weight layout. The reference layout (convert.py:7-14: u32 [N, K/8], nibble j of a word = element 8w + j, lowest
+// first; bf16 scales / biases [N, K/G]) is repacked once at load time (vk_w4_repack) into 1152-byte chunks, one per
+// (32 output rows, 64 input columns), stored [superblock of 256 rows][64-column group][8 chunks]:
 //   bytes    0..1023  codes  [stripe 2][lane 32][kstep 4] u32 : for lane (g = lane / 4, t = lane % 4), stripe s,
 //                     kstep q the word holds the mma.m16n8k16 A fragment of rows r0 = 16 s + g, r1 = r0 + 8 and
 //                     columns c = 16 q + 2 t: nibbles {0: (r0,c) 4: (r0,c+1) 1: (r1,c) 5: (r1,c+1) 2: (r0,c+8)
 //                     6: (r0,c+9) 3: (r1,c+8) 7: (r1,c+9)}, so (w >> 4 i) & 0x000F000F | 0x43004300 is fragment
 //                     register i as two bf16 values 128 + u.
 //   bytes 1024..1151  [g 8][4] u32 = (scale | bias << 16) of rows g, g + 8, 16 + g, 24 + g.
-// Chunks of one 32-row block are consecutive over K, so a warp streams its rows with 1-D TMA bulk copies into a
-// private shared-memory ring; no byte of the weights is read twice and the packed size equals the algorithmic
-// N*K/2 + N*(K/64)*4 bytes.
+// One step of the kernel = one (superblock, group) = 9216 contiguous bytes, fetched by one TMA bulk copy; the packed
+// size equals the algorithmic N*K/2 + N*(K/64)*4 bytes and no byte of it is read twice.
 //
-// Work split. grid = (ceil(N/32 / WARPS), S): each warp owns one 32-row block, each CTA one of S slabs of K. With
-// S > 1 the fp32 partial sums go to a workspace [S][N32][16]; the CTA that arrives last at a grid column (an arrival
-// counter per column, left at zero again) adds them in slab order, so the result does not depend on scheduling
-// (the reference lists batch-variant matmuls as an open problem, NOTES_BATCHED_SERVE.md:256-258; here a row's
-// result is the same for every M).
+// Activation layout ("x records"). Per 64-column group one 2112-byte record: x[16 rows][64] bf16 with the eight
+// 16-byte pieces of a row xor-swizzled by (row & 7) (conflict-free ldmatrix), then the 16 row sums of the group in
+// fp32, ordered so that mma thread t finds its columns {2t, 2t+1, 8+2t, 9+2t} in one 16-byte read. vk_w4_gemm builds
+// the records from a row-major x with a small kernel.
+//
+// Work split. total = superblocks * groups steps, in superblock-major order, dealt in equal contiguous ranges to
+// P persistent CTAs (two per SM). A CTA is one producer warp (TMA into an 8-stage ring: weights as soon as the CTA
+// starts, the x record once the kernel's predecessor has finished) and eight consumer warps, one 32-row block each.
+// A range that does not cover a superblock's whole K writes fp32 partial sums; the CTA that arrives last at the
+// superblock (arrival counter, left at zero) adds the partials in range order, so the result does not depend on
+// scheduling and a row's result is the same for every M (the reference lists batch-variant matmuls as an open
+// problem, NOTES_BATCHED_SERVE.md:256-258).
 #include "common.cuh"
 
 namespace {
 
 constexpr int kChunkBytes = 1152;
-#ifndef VK_STAGES
-#define VK_STAGES 4
-#endif
-#ifndef VK_CH
-#define VK_CH 1
-#endif
-constexpr int kStages = VK_STAGES;   // ring depth per warp
-constexpr int kCH = VK_CH;       // chunks per stage
-constexpr size_t kCounterBytes = 16384;  // split-K arrival counters at the head of the workspace (4096 grid columns)
+constexpr int kBlocksPerSB = 8;                                 // 32-row blocks per superblock = consumer warps
+constexpr int kSBRows = 32 * kBlocksPerSB;                      // 256
+constexpr int kWStageBytes = kBlocksPerSB * kChunkBytes;        // 9216
+constexpr int kXRecBytes = 2112;                                // 16 x 64 bf16 + 16 fp32
+constexpr int kStageBytes = kWStageBytes + kXRecBytes;          // 11328
+constexpr int kStages = 8;
+constexpr int kThreads = 32 * (1 + kBlocksPerSB);               // 288
+constexpr size_t kCounterBytes = 16384;                         // arrival counters at the head of the workspace
+constexpr size_t kSmemBytes = (size_t)kStages * kStageBytes + 2 * kStages * 8;
 
 struct W4Params {
     const uint8_t* wp;      // packed weights
-    const __nv_bfloat16* x; // [M, ldx]
+    const uint8_t* xrec;    // [G] x records
     __nv_bfloat16* y;       // [M, ldy]
-    float* part;            // [S][NB*32][16] when S > 1
-    int* counters;          // one per grid column; zero between launches
-    int M, N, NB, G, S, ldx, ldy, ksmax;
+    float* part;            // [NSB][maxc][256][16] partial sums
+    int* counters;          // [NSB] zero between launches
+    long long T;            // NSB * G steps
+    int M, N, NSB, G, P, ldy, maxc;
 };
 
 __device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
@@ -52,6 +60,13 @@ __device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], 
         "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
         : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+// mma with a zero accumulator input (first k-step of a group)
+__device__ __forceinline__ void mma_bf16_z(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+        : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "f"(0.f));
 }
 
 __device__ __forceinline__ uint32_t lop3_and_or(uint32_t w, uint32_t mask, uint32_t orv) {
@@ -68,229 +83,260 @@ __device__ __forceinline__ void unpack_codes(uint32_t w, uint32_t (&a)[4]) {
     a[3] = lop3_and_or(w >> 12, 0x000F000Fu, 0x43004300u);
 }
 
-// mma with a zero accumulator input (first k-step of a group)
-__device__ __forceinline__ void mma_bf16_z(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-    asm volatile(
-        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
-        : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
-        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "f"(0.f));
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
+__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
 
-template <int MT, int WARPS>
-__global__ void __launch_bounds__(WARPS * 32, (MT == 2 ? 3 : 4)) w4_gemm_kernel(const W4Params p) {
+// the CTA whose range [c T / P, (c + 1) T / P) holds step t
+__device__ __forceinline__ int step_owner(long long t, long long T, int P) { return (int)(((t + 1) * P - 1) / T); }
+
+template <int MT>
+__global__ void __launch_bounds__(kThreads, 2) w4_gemm_kernel(const W4Params p) {
     extern __shared__ __align__(128) uint8_t smem[];
-    constexpr int MR = MT * 8;                              // activation rows held (M padded)
-    constexpr int kStageBytes = kCH * kChunkBytes;
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int g = lane >> 2, t = lane & 3;
-    const int nb = blockIdx.x * WARPS + warp;
-    const bool active = nb < p.NB;
-    const int split = blockIdx.y;
-    const int kg0 = (int)((long long)split * p.G / p.S), kg1 = (int)((long long)(split + 1) * p.G / p.S);
-    const int ks = kg1 - kg0;
-    const int nit = (ks + kCH - 1) / kCH;
-    const int XS = p.ksmax * 64 + 8;                        // x slab row stride (bf16 elements); +8 keeps ldmatrix conflict-free
-
-    uint8_t* ring = smem + (size_t)warp * kStages * kStageBytes;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (size_t)WARPS * kStages * kStageBytes) + warp * kStages;
-    __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(smem + (size_t)WARPS * kStages * kStageBytes + WARPS * kStages * 8);
-    float* sxs = reinterpret_cast<float*>(xs + (size_t)MR * XS);
+    constexpr int MR = MT * 8;
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + (size_t)kStages * kStageBytes);
+    uint64_t* empty = full + kStages;
     __shared__ int s_last;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const long long t0 = (long long)blockIdx.x * p.T / p.P, t1 = (long long)(blockIdx.x + 1) * p.T / p.P;
+    const int n = (int)(t1 - t0);
 
-    const uint8_t* src = p.wp + ((size_t)nb * p.G + kg0) * kChunkBytes;
-    if (active && lane == 0) {
-        for (int s = 0; s < kStages; s++) mbar_init(&bars[s], 1);
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; s++) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], kBlocksPerSB);
+        }
         mbar_fence_init();
-        // the weights depend on no earlier kernel: start streaming before waiting for the producer of x
-        for (int it = 0; it < kStages && it < nit; it++) {
-            const int cnt = min(kCH, ks - it * kCH);
-            mbar_expect_tx(&bars[it], cnt * kChunkBytes);
-            tma_bulk_g2s(ring + it * kStageBytes, src + (size_t)it * kStageBytes, cnt * kChunkBytes, &bars[it]);
-        }
     }
-    pdl_launch_dependents();
-    pdl_wait();
+    __syncthreads();
 
-    // ---- stage the activation slab x[:, kg0*64 : kg1*64] (rows >= M are zero) and its per-group sums
-    {
-        const int vec_per_row = ks * 8;                     // 16-byte vectors per row
-        for (int i = threadIdx.x; i < MR * vec_per_row; i += WARPS * 32) {
-            const int r = i / vec_per_row, v = i - r * vec_per_row;
-            uint4 val = make_uint4(0, 0, 0, 0);
-            if (r < p.M) val = *reinterpret_cast<const uint4*>(p.x + (size_t)r * p.ldx + (size_t)kg0 * 64 + v * 8);
-            *reinterpret_cast<uint4*>(xs + (size_t)r * XS + v * 8) = val;
-        }
-        __syncthreads();
-        // one (group, row) sum per 4 lanes: 16 elements each, added in order, then a 2-step xor tree
-        const int nsum = ks * MR;
-        for (int i0 = 0; i0 < nsum; i0 += WARPS * 8) {
-            const int i = i0 + (threadIdx.x >> 2);
-            float s = 0.f;
-            int kgl = 0, m = 0;
-            if (i < nsum) {
-                kgl = i / MR; m = i - kgl * MR;
-                const uint4* row = reinterpret_cast<const uint4*>(xs + (size_t)m * XS + kgl * 64 + (threadIdx.x & 3) * 16);
-                const uint4 a = row[0], b = row[1];
-                s = bf_lo(a.x); s += bf_hi(a.x); s += bf_lo(a.y); s += bf_hi(a.y);
-                s += bf_lo(a.z); s += bf_hi(a.z); s += bf_lo(a.w); s += bf_hi(a.w);
-                s += bf_lo(b.x); s += bf_hi(b.x); s += bf_lo(b.y); s += bf_hi(b.y);
-                s += bf_lo(b.z); s += bf_hi(b.z); s += bf_lo(b.w); s += bf_hi(b.w);
+    if (warp == 0) {
+        // ---------------------------------------------------------------- producer
+        if (lane == 0) {
+            const uint8_t* wsrc = p.wp + (size_t)t0 * kWStageBytes;
+            const int pre = n < kStages ? n : kStages;
+            // the weights depend on no earlier kernel: start streaming before waiting for the producer of x
+            for (int i = 0; i < pre; i++) {
+                mbar_expect_tx(&full[i], kStageBytes);
+                tma_bulk_g2s(smem + (size_t)i * kStageBytes, wsrc + (size_t)i * kWStageBytes, kWStageBytes, &full[i]);
             }
-            s += __shfl_xor_sync(0xffffffffu, s, 1);
-            s += __shfl_xor_sync(0xffffffffu, s, 2);
-            // position so that thread t reads {m = 2t, 2t+1, 8+2t, 9+2t} as one vector
-            if (i < nsum && (threadIdx.x & 3) == 0)
-                sxs[kgl * MR + ((m & 7) >> 1) * (2 * MT) + (m >> 3) * 2 + (m & 1)] = s;
+            pdl_launch_dependents();
+            pdl_wait();
+            for (int i = 0; i < pre; i++) {
+                const int kg = (int)((t0 + i) % p.G);
+                tma_bulk_g2s(smem + (size_t)i * kStageBytes + kWStageBytes, p.xrec + (size_t)kg * kXRecBytes, kXRecBytes, &full[i]);
+            }
+            for (int i = pre; i < n; i++) {
+                const int st = i % kStages;
+                if (!mbar_wait(&empty[st], ((i / kStages) - 1) & 1)) break;
+                const int kg = (int)((t0 + i) % p.G);
+                mbar_expect_tx(&full[st], kStageBytes);
+                tma_bulk_g2s(smem + (size_t)st * kStageBytes, wsrc + (size_t)i * kWStageBytes, kWStageBytes, &full[st]);
+                tma_bulk_g2s(smem + (size_t)st * kStageBytes + kWStageBytes, p.xrec + (size_t)kg * kXRecBytes, kXRecBytes, &full[st]);
+            }
         }
-        __syncthreads();
+        return;
     }
 
+    // -------------------------------------------------------------------- consumers
+    const int j = warp - 1;                    // 32-row block inside the superblock
+    const int g = lane >> 2, t = lane & 3;
+    const int ctid = threadIdx.x - 32;         // 0..255
     float acc[2][MT][4];
 #pragma unroll
     for (int s = 0; s < 2; s++)
 #pragma unroll
-        for (int j = 0; j < MT; j++)
+        for (int jj = 0; jj < MT; jj++)
 #pragma unroll
-            for (int e = 0; e < 4; e++) acc[s][j][e] = 0.f;
+            for (int e = 0; e < 4; e++) acc[s][jj][e] = 0.f;
 
+    // ldmatrix source of this lane inside an x record: row, and which 16-byte piece of each 32-byte k-step
+    const int lm_mat = lane >> 3, lm_r = lane & 7;
+    const int lm_row = (MT == 2 ? (lm_mat >> 1) * 8 : 0) + lm_r;
+    const int lm_half = lm_mat & 1;
+
+    int sb = (int)(t0 / p.G), kg = (int)(t0 % p.G);
+    int seg_kg0 = kg;
     bool ok = true;
-    if (active) {
-        // ldmatrix row address of this lane inside the x slab (without the k offset)
-        const int lm_mat = lane >> 3, lm_r = lane & 7;
-        const int lm_row = (MT == 2 ? (lm_mat >> 1) * 8 : 0) + lm_r;
-        const uint32_t xs_lane = smem_u32(xs + (size_t)lm_row * XS + (lm_mat & 1) * 8);
-        for (int it = 0; it < nit && ok; it++) {
-            const int st = it % kStages;
-            ok = mbar_wait(&bars[st], (it / kStages) & 1);
-            if (!ok) break;
-            const int cnt = min(kCH, ks - it * kCH);
-            for (int c = 0; c < cnt; c++) {
-                const uint8_t* ch = ring + st * kStageBytes + c * kChunkBytes;
-                const uint4 w0 = *reinterpret_cast<const uint4*>(ch + lane * 16);
-                const uint4 w1 = *reinterpret_cast<const uint4*>(ch + 512 + lane * 16);
-                const uint4 sb = *reinterpret_cast<const uint4*>(ch + 1024 + g * 16);
-                const int kgl = it * kCH + c;
-                float d[2][MT][4];
-                const uint32_t wq0[4] = {w0.x, w0.y, w0.z, w0.w};
-                const uint32_t wq1[4] = {w1.x, w1.y, w1.z, w1.w};
-#pragma unroll
-                for (int q = 0; q < 4; q++) {
-                    uint32_t b[2 * MT];
-                    const uint32_t addr = xs_lane + (uint32_t)(kgl * 64 + q * 16) * 2;
-                    if constexpr (MT == 2) {
-                        asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
-                                     : "=r"(b[0]), "=r"(b[1]), "=r"(b[2]), "=r"(b[3])
-                                     : "r"(addr));
-                    } else {
-                        asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];" : "=r"(b[0]), "=r"(b[1]) : "r"(addr));
-                    }
-                    uint32_t a[4];
-                    unpack_codes(wq0[q], a);
-#pragma unroll
-                    for (int j = 0; j < MT; j++) {
-                        if (q == 0) mma_bf16_z(d[0][j], a, b[2 * j], b[2 * j + 1]);
-                        else mma_bf16(d[0][j], a, b[2 * j], b[2 * j + 1]);
-                    }
-                    unpack_codes(wq1[q], a);
-#pragma unroll
-                    for (int j = 0; j < MT; j++) {
-                        if (q == 0) mma_bf16_z(d[1][j], a, b[2 * j], b[2 * j + 1]);
-                        else mma_bf16(d[1][j], a, b[2 * j], b[2 * j + 1]);
-                    }
-                }
-                // group epilogue: acc += s * (D - 128 sum x) + b * sum x = s * D + (b - 128 s) * sum x
-                float sx[MT][2];
-                if constexpr (MT == 2) {
-                    const float4 v = *reinterpret_cast<const float4*>(sxs + kgl * MR + t * 4);
-                    sx[0][0] = v.x; sx[0][1] = v.y; sx[1][0] = v.z; sx[1][1] = v.w;
-                } else {
-                    const float2 v = *reinterpret_cast<const float2*>(sxs + kgl * MR + t * 2);
-                    sx[0][0] = v.x; sx[0][1] = v.y;
-                }
-                const uint32_t sbw[4] = {sb.x, sb.y, sb.z, sb.w};
-#pragma unroll
-                for (int s = 0; s < 2; s++) {
-                    const float s0 = bf_lo(sbw[2 * s]), c0 = fmaf(-128.f, s0, bf_hi(sbw[2 * s]));
-                    const float s1 = bf_lo(sbw[2 * s + 1]), c1 = fmaf(-128.f, s1, bf_hi(sbw[2 * s + 1]));
-#pragma unroll
-                    for (int j = 0; j < MT; j++) {
-                        acc[s][j][0] = fmaf(c0, sx[j][0], fmaf(s0, d[s][j][0], acc[s][j][0]));
-                        acc[s][j][1] = fmaf(c0, sx[j][1], fmaf(s0, d[s][j][1], acc[s][j][1]));
-                        acc[s][j][2] = fmaf(c1, sx[j][0], fmaf(s1, d[s][j][2], acc[s][j][2]));
-                        acc[s][j][3] = fmaf(c1, sx[j][1], fmaf(s1, d[s][j][3], acc[s][j][3]));
-                    }
-                }
-            }
-            __syncwarp();
-            if (lane == 0 && it + kStages < nit) {
-                const int nx = it + kStages;
-                const int ncnt = min(kCH, ks - nx * kCH);
-                mbar_expect_tx(&bars[st], ncnt * kChunkBytes);
-                tma_bulk_g2s(ring + st * kStageBytes, src + (size_t)nx * kStageBytes, ncnt * kChunkBytes, &bars[st]);
-            }
-        }
-        if (!ok) {
-            // a copy never landed: give the ones still in flight a (bounded) chance to land before the CTA's shared
-            // memory is released; the output of this block is then left unwritten (status word set)
-            for (int s = 0; s < kStages; s++) mbar_wait(&bars[s], 0);
-        }
-    }
 
-    if (active && ok) {
+    auto flush = [&](int fsb, int kga, int kgb) {
+        const bool whole = (kga == 0 && kgb == p.G);
+        const long long s0 = (long long)fsb * p.G;
+        const int c_first = step_owner(s0, p.T, p.P);
+        if (!whole) {
+            float* dst = p.part + (((size_t)fsb * p.maxc + (blockIdx.x - c_first)) * kSBRows) * 16;
+#pragma unroll
+            for (int s = 0; s < 2; s++)
+#pragma unroll
+                for (int jj = 0; jj < MT; jj++)
+#pragma unroll
+                    for (int h = 0; h < 2; h++) {
+                        const int r = j * 32 + s * 16 + g + h * 8;
+                        __stcg(reinterpret_cast<float2*>(dst + (size_t)r * 16 + jj * 8 + 2 * t),
+                               make_float2(acc[s][jj][2 * h], acc[s][jj][2 * h + 1]));
+                    }
+            __threadfence();
+            consumer_sync();
+            if (ctid == 0) {
+                const int ncontrib = step_owner(s0 + p.G - 1, p.T, p.P) - c_first + 1;
+                const int old = atomicAdd(&p.counters[fsb], 1);
+                s_last = (old == ncontrib - 1) ? ncontrib : 0;
+                if (s_last) p.counters[fsb] = 0;  // ready for the next launch
+            }
+            consumer_sync();
+            const int ncontrib = s_last;
+            if (ncontrib) {
+                __threadfence();
+                const int nrow = fsb * kSBRows + ctid;  // one output row per consumer thread
+                if (nrow < p.N) {
+                    const float* src = p.part + ((size_t)fsb * p.maxc * kSBRows + ctid) * 16;
+                    float sum[MR];
+#pragma unroll
+                    for (int m = 0; m < MR; m++) sum[m] = 0.f;
+                    for (int c = 0; c < ncontrib; c++) {
+                        const float4* q4 = reinterpret_cast<const float4*>(src + (size_t)c * kSBRows * 16);
+#pragma unroll
+                        for (int v = 0; v < MR / 4; v++) {
+                            const float4 x = __ldcg(q4 + v);
+                            sum[4 * v] += x.x; sum[4 * v + 1] += x.y; sum[4 * v + 2] += x.z; sum[4 * v + 3] += x.w;
+                        }
+                    }
+#pragma unroll
+                    for (int m = 0; m < MR; m++)
+                        if (m < p.M) p.y[(size_t)m * p.ldy + nrow] = f2bf(sum[m]);
+                }
+            }
+            consumer_sync();  // s_last is reused by the next flush
+        } else {
+#pragma unroll
+            for (int s = 0; s < 2; s++)
+#pragma unroll
+                for (int jj = 0; jj < MT; jj++)
+#pragma unroll
+                    for (int h = 0; h < 2; h++) {
+                        const int nrow = fsb * kSBRows + j * 32 + s * 16 + g + h * 8;
+                        const int m = jj * 8 + 2 * t;
+                        if (nrow < p.N) {
+                            if (m < p.M) p.y[(size_t)m * p.ldy + nrow] = f2bf(acc[s][jj][2 * h]);
+                            if (m + 1 < p.M) p.y[(size_t)(m + 1) * p.ldy + nrow] = f2bf(acc[s][jj][2 * h + 1]);
+                        }
+                    }
+        }
+#pragma unroll
+        for (int s = 0; s < 2; s++)
+#pragma unroll
+            for (int jj = 0; jj < MT; jj++)
+#pragma unroll
+                for (int e = 0; e < 4; e++) acc[s][jj][e] = 0.f;
+    };
+
+    for (int i = 0; i < n; i++) {
+        const int st = i % kStages;
+        if (!mbar_wait(&full[st], (i / kStages) & 1)) { ok = false; break; }
+        const uint8_t* stage = smem + (size_t)st * kStageBytes;
+        const uint8_t* ch = stage + j * kChunkBytes;
+        const uint8_t* xr = stage + kWStageBytes;
+        const uint4 w0 = *reinterpret_cast<const uint4*>(ch + lane * 16);
+        const uint4 w1 = *reinterpret_cast<const uint4*>(ch + 512 + lane * 16);
+        const uint4 sb4 = *reinterpret_cast<const uint4*>(ch + 1024 + g * 16);
+        const uint32_t xrow = smem_u32(xr) + lm_row * 128;
+        float d[2][MT][4];
+        const uint32_t wq0[4] = {w0.x, w0.y, w0.z, w0.w};
+        const uint32_t wq1[4] = {w1.x, w1.y, w1.z, w1.w};
+#pragma unroll
+        for (int q = 0; q < 4; q++) {
+            uint32_t b[2 * MT];
+            const uint32_t addr = xrow + (uint32_t)(((2 * q + lm_half) ^ lm_r) << 4);
+            if constexpr (MT == 2) {
+                asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                             : "=r"(b[0]), "=r"(b[1]), "=r"(b[2]), "=r"(b[3])
+                             : "r"(addr));
+            } else {
+                asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];" : "=r"(b[0]), "=r"(b[1]) : "r"(addr));
+            }
+            uint32_t a[4];
+            unpack_codes(wq0[q], a);
+#pragma unroll
+            for (int jj = 0; jj < MT; jj++) {
+                if (q == 0) mma_bf16_z(d[0][jj], a, b[2 * jj], b[2 * jj + 1]);
+                else mma_bf16(d[0][jj], a, b[2 * jj], b[2 * jj + 1]);
+            }
+            unpack_codes(wq1[q], a);
+#pragma unroll
+            for (int jj = 0; jj < MT; jj++) {
+                if (q == 0) mma_bf16_z(d[1][jj], a, b[2 * jj], b[2 * jj + 1]);
+                else mma_bf16(d[1][jj], a, b[2 * jj], b[2 * jj + 1]);
+            }
+        }
+        // group epilogue: acc += s * (D - 128 sum x) + b * sum x = s * D + (b - 128 s) * sum x
+        float sx[MT][2];
+        if constexpr (MT == 2) {
+            const float4 v = *reinterpret_cast<const float4*>(xr + 2048 + t * 16);
+            sx[0][0] = v.x; sx[0][1] = v.y; sx[1][0] = v.z; sx[1][1] = v.w;
+        } else {
+            const float2 v = *reinterpret_cast<const float2*>(xr + 2048 + t * 16);
+            sx[0][0] = v.x; sx[0][1] = v.y;
+        }
+        const uint32_t sbw[4] = {sb4.x, sb4.y, sb4.z, sb4.w};
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&empty[st]);   // everything of this stage is in registers now
 #pragma unroll
         for (int s = 0; s < 2; s++) {
+            const float s0 = bf_lo(sbw[2 * s]), c0 = fmaf(-128.f, s0, bf_hi(sbw[2 * s]));
+            const float s1 = bf_lo(sbw[2 * s + 1]), c1 = fmaf(-128.f, s1, bf_hi(sbw[2 * s + 1]));
 #pragma unroll
-            for (int j = 0; j < MT; j++) {
-#pragma unroll
-                for (int h = 0; h < 2; h++) {
-                    const int n = nb * 32 + s * 16 + g + h * 8;
-                    const int m = j * 8 + 2 * t;
-                    const float v0 = acc[s][j][2 * h], v1 = acc[s][j][2 * h + 1];
-                    if (p.S > 1) {
-                        __stcg(reinterpret_cast<float2*>(p.part + ((size_t)split * p.NB * 32 + n) * 16 + m), make_float2(v0, v1));
-                    } else if (n < p.N) {
-                        if (m < p.M) p.y[(size_t)m * p.ldy + n] = f2bf(v0);
-                        if (m + 1 < p.M) p.y[(size_t)(m + 1) * p.ldy + n] = f2bf(v1);
-                    }
-                }
+            for (int jj = 0; jj < MT; jj++) {
+                acc[s][jj][0] = fmaf(c0, sx[jj][0], fmaf(s0, d[s][jj][0], acc[s][jj][0]));
+                acc[s][jj][1] = fmaf(c0, sx[jj][1], fmaf(s0, d[s][jj][1], acc[s][jj][1]));
+                acc[s][jj][2] = fmaf(c1, sx[jj][0], fmaf(s1, d[s][jj][2], acc[s][jj][2]));
+                acc[s][jj][3] = fmaf(c1, sx[jj][1], fmaf(s1, d[s][jj][3], acc[s][jj][3]));
             }
         }
+        if (++kg == p.G) {
+            flush(sb, seg_kg0, p.G);
+            kg = 0; seg_kg0 = 0; sb++;
+        }
     }
-    if (p.S == 1) return;
+    if (ok && kg != seg_kg0) flush(sb, seg_kg0, kg);
+    // (a timed-out wait leaves the output unwritten and the status word set; copies still in flight land in this
+    // CTA's shared memory, which stays allocated until the last warp of the CTA has left, after its own bounded waits)
+}
 
-    // ---- split-K: the CTA that arrives last at this column of the grid adds the S partial sums in slab order
-    __threadfence();
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        const int old = atomicAdd(&p.counters[blockIdx.x], 1);
-        s_last = (old == p.S - 1);
-        if (s_last) p.counters[blockIdx.x] = 0;  // leave the counter ready for the next launch
-    }
-    __syncthreads();
-    if (!s_last) return;
-    __threadfence();
-    const int n_base = blockIdx.x * WARPS * 32;
-    for (int i = threadIdx.x; i < WARPS * 32 * MR; i += WARPS * 32) {
-        const int nl = i / MR, m = i - nl * MR;
-        const int n = n_base + nl;
-        if (n >= p.N || m >= p.M) continue;
-        float s = 0.f;
-        for (int k = 0; k < p.S; k++) s += __ldcg(p.part + ((size_t)k * p.NB * 32 + n) * 16 + m);
-        p.y[(size_t)m * p.ldy + n] = f2bf(s);
-    }
+// ------------------------------------------------------------------------------------------------ x records
+// x [M, ldx] row-major bf16 -> [G] records (see the file comment). One CTA of 128 threads per group: thread (m, c)
+// moves the 16-byte piece c of row m and the eight lanes of a row add up its 64 values (each lane its 8 in order,
+// then an xor tree over the lanes).
+__global__ void __launch_bounds__(128) w4_xrec_kernel(const __nv_bfloat16* __restrict__ x, int ldx, int M, uint8_t* __restrict__ xrec) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int kg = blockIdx.x, m = threadIdx.x >> 3, c = threadIdx.x & 7;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (m < M) v = *reinterpret_cast<const uint4*>(x + (size_t)m * ldx + kg * 64 + c * 8);
+    uint8_t* rec = xrec + (size_t)kg * kXRecBytes;
+    *reinterpret_cast<uint4*>(rec + m * 128 + ((c ^ (m & 7)) << 4)) = v;
+    float s = bf_lo(v.x); s += bf_hi(v.x); s += bf_lo(v.y); s += bf_hi(v.y);
+    s += bf_lo(v.z); s += bf_hi(v.z); s += bf_lo(v.w); s += bf_hi(v.w);
+    s += __shfl_xor_sync(0xffffffffu, s, 1);
+    s += __shfl_xor_sync(0xffffffffu, s, 2);
+    s += __shfl_xor_sync(0xffffffffu, s, 4);
+    if (c == 0) reinterpret_cast<float*>(rec + 2048)[((m & 7) >> 1) * 4 + (m >> 3) * 2 + (m & 1)] = s;
 }
 
 // ------------------------------------------------------------------------------------------------ repack / dequant
 // reference layout -> packed chunks. One thread per packed u32 (codes) or per scale word.
 __global__ void w4_repack_kernel(const uint32_t* __restrict__ w, const __nv_bfloat16* __restrict__ sc,
                                  const __nv_bfloat16* __restrict__ bi, int N, int K, int group, uint8_t* __restrict__ out,
-                                 int NB, int G) {
+                                 int NSB, int G) {
     const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-    const size_t total = (size_t)NB * G * 288;  // u32 words per chunk
+    const size_t total = (size_t)NSB * G * kBlocksPerSB * 288;  // u32 words per chunk
     if (idx >= total) return;
     const size_t chunk = idx / 288;
     const int wi = (int)(idx - chunk * 288);
-    const int nb = (int)(chunk / G), kg = (int)(chunk - (size_t)nb * G);
+    const int jb = (int)(chunk % kBlocksPerSB);
+    const size_t step = chunk / kBlocksPerSB;
+    const int sbk = (int)(step / G), kg = (int)(step - (size_t)sbk * G);
+    const int nb = sbk * kBlocksPerSB + jb;
     uint32_t* dst = reinterpret_cast<uint32_t*>(out + chunk * kChunkBytes) + wi;
     const int KW = K / 8;
     if (wi < 256) {
@@ -306,8 +352,8 @@ __global__ void w4_repack_kernel(const uint32_t* __restrict__ w, const __nv_bflo
                      (code(r0, c + 1) << 16) | (code(r1, c + 1) << 20) | (code(r0, c + 9) << 24) | (code(r1, c + 9) << 28);
         *dst = v;
     } else {
-        const int j = wi - 256;  // [g][4]
-        const int g = j >> 2, e = j & 3;
+        const int jx = wi - 256;  // [g][4]
+        const int g = jx >> 2, e = jx & 3;
         const int r = nb * 32 + (e >> 1) * 16 + g + (e & 1) * 8;
         uint32_t v = 0;
         if (r < N) {
@@ -334,94 +380,61 @@ __global__ void w4_dequant_kernel(const uint32_t* __restrict__ w, const __nv_bfl
     const __nv_bfloat16 s = sc[(size_t)n * (K / group) + gi], b = bi[(size_t)n * (K / group) + gi];
     uint32_t o[4];
 #pragma unroll
-    for (int j = 0; j < 4; j++) {
-        const __nv_bfloat16 u0 = __ushort_as_bfloat16((unsigned short)(0x4300u | ((word >> (8 * j)) & 0xFu)));
-        const __nv_bfloat16 u1 = __ushort_as_bfloat16((unsigned short)(0x4300u | ((word >> (8 * j + 4)) & 0xFu)));
+    for (int jx = 0; jx < 4; jx++) {
+        const __nv_bfloat16 u0 = __ushort_as_bfloat16((unsigned short)(0x4300u | ((word >> (8 * jx)) & 0xFu)));
+        const __nv_bfloat16 u1 = __ushort_as_bfloat16((unsigned short)(0x4300u | ((word >> (8 * jx + 4)) & 0xFu)));
         const __nv_bfloat16 k128 = __ushort_as_bfloat16((unsigned short)0x4300u);
         const __nv_bfloat16 r0 = __hfma(__hsub(u0, k128), s, b);   // 128 + u - 128 is exact
         const __nv_bfloat16 r1 = __hfma(__hsub(u1, k128), s, b);
-        o[j] = (uint32_t)__bfloat16_as_ushort(r0) | ((uint32_t)__bfloat16_as_ushort(r1) << 16);
+        o[jx] = (uint32_t)__bfloat16_as_ushort(r0) | ((uint32_t)__bfloat16_as_ushort(r1) << 16);
     }
     *reinterpret_cast<uint4*>(out + (size_t)n * K + (size_t)wi * 8) = make_uint4(o[0], o[1], o[2], o[3]);
 }
 
+int g_force_ctas = 0;
+
 struct W4Plan {
-    int warps, S, ksmax, mt;
-    size_t smem;
+    int P, maxc, NSB, G;
+    long long T;
 };
 
-size_t w4_smem_bytes(int warps, int mt, int ksmax) {
-    const int MR = mt * 8;
-    return (size_t)warps * kStages * kCH * kChunkBytes + (size_t)warps * kStages * 8 +
-           (size_t)MR * (ksmax * 64 + 8) * 2 + (size_t)ksmax * MR * 4;
+W4Plan w4_plan(int N, int K) {
+    W4Plan pl;
+    pl.NSB = (N + kSBRows - 1) / kSBRows;
+    pl.G = K / 64;
+    pl.T = (long long)pl.NSB * pl.G;
+    int P = 2 * 148;                       // two CTAs per SM, all resident at once
+    if (g_force_ctas > 0) P = g_force_ctas;
+    if ((long long)P > pl.T) P = (int)pl.T;
+    pl.P = P;
+    // the largest number of ranges that meet one superblock
+    int maxc = 1;
+    for (int sb = 0; sb < pl.NSB; sb++) {
+        const long long s0 = (long long)sb * pl.G;
+        const int c0 = (int)(((s0 + 1) * P - 1) / pl.T), c1 = (int)(((s0 + pl.G) * P - 1) / pl.T);
+        maxc = c1 - c0 + 1 > maxc ? c1 - c0 + 1 : maxc;
+    }
+    pl.maxc = maxc;
+    return pl;
 }
 
-int g_force_warps = 0, g_force_split = 0;
-
-// Choose warps per CTA and the number of K slabs: fill 148 SMs in whole waves while keeping slabs long enough that
-// the per-CTA activation slab and the partial sums stay small next to the weights streamed.
-W4Plan w4_plan(int M, int N, int K) {
-    const int NB = (N + 31) / 32, G = K / 64;
-    const int mt = M <= 8 ? 1 : 2;
-    W4Plan best = {};
-    double best_cost = 1e300;
-    for (int warps : {8, 4}) {
-        if (g_force_warps && warps != g_force_warps) continue;
-        const int nctas_n = (NB + warps - 1) / warps;
-        for (int S = 1; S <= G && S <= 64; S++) {
-            if (g_force_split && S != g_force_split) continue;
-            const int ksmax = (G + S - 1) / S;
-            if (ksmax < 2 && S > 1) break;
-            const size_t smem = w4_smem_bytes(warps, mt, ksmax);
-            if (smem > 200 * 1024) continue;
-            int occ = (int)((220 * 1024) / (smem + 1024));
-            occ = occ < 1 ? 1 : occ;
-            const int occ_thr = 2048 / (warps * 32);
-            occ = occ > occ_thr ? occ_thr : occ;
-            const int occ_reg = mt == 2 ? 3 : 4;   // __launch_bounds__ of the kernel
-            occ = occ > occ_reg ? occ_reg : occ;
-            const long long ctas = (long long)nctas_n * S;
-            const long long slots = 148LL * occ;
-            const long long waves = (ctas + slots - 1) / slots;
-            // bytes through one SM, plus a fixed cost per wave (ramp-up / drain) and the partial-sum traffic
-            double cost = (double)waves * ((double)occ * ksmax * warps * kChunkBytes + 24e3);
-            cost += (double)ksmax * mt * 8 * 128 * occ * waves * 0.5;  // activation slab re-read from L2
-            if (S > 1) cost += 2.0 * S * NB * 32 * 16 * 4 / 148.0 + 6e3;
-            if (cost < best_cost) {
-                best_cost = cost;
-                best = {warps, S, ksmax, mt, smem};
-            }
-        }
-    }
-    return best;
-}
-
-template <int MT, int WARPS>
-cudaError_t launch_gemm(const W4Params& p, const W4Plan& plan, cudaStream_t stream) {
-    static size_t configured = 0;
-    auto kern = w4_gemm_kernel<MT, WARPS>;
-    if (plan.smem > configured) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-        if (e != cudaSuccess) return e;
-        configured = 200 * 1024;
-    }
-    dim3 grid((p.NB + WARPS - 1) / WARPS, p.S);
-    return vk_launch(kern, grid, dim3(WARPS * 32), plan.smem, stream, p);
+size_t w4_ws_bytes(const W4Plan& pl) {
+    return kCounterBytes + (size_t)pl.G * kXRecBytes + (size_t)pl.NSB * pl.maxc * kSBRows * 16 * 4;
 }
 
 }  // namespace
 
 extern "C" {
 
-size_t vk_w4_packed_bytes(int N, int K) { return (size_t)((N + 31) / 32) * (K / 64) * kChunkBytes; }
+size_t vk_w4_packed_bytes(int N, int K) { return (size_t)((N + kSBRows - 1) / kSBRows) * (K / 64) * kWStageBytes; }
 
 int vk_w4_repack(const void* w, const void* scales, const void* biases, int N, int K, int group, void* packed,
                  cudaStream_t stream) {
     if (N <= 0 || K <= 0 || K % 64 != 0 || (group != 64 && group != 128) || K % group != 0) return VK_EINVAL;
-    const int NB = (N + 31) / 32, G = K / 64;
-    const size_t total = (size_t)NB * G * 288;
+    const int NSB = (N + kSBRows - 1) / kSBRows, G = K / 64;
+    const size_t total = (size_t)NSB * G * kBlocksPerSB * 288;
     w4_repack_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(
-        (const uint32_t*)w, (const __nv_bfloat16*)scales, (const __nv_bfloat16*)biases, N, K, group, (uint8_t*)packed, NB, G);
+        (const uint32_t*)w, (const __nv_bfloat16*)scales, (const __nv_bfloat16*)biases, N, K, group, (uint8_t*)packed, NSB, G);
     return (int)cudaGetLastError();
 }
 
@@ -434,36 +447,45 @@ int vk_w4_dequant(const void* w, const void* scales, const void* biases, int N, 
     return (int)cudaGetLastError();
 }
 
-void vk_w4_force_plan(int warps, int split) {
-    g_force_warps = warps;
-    g_force_split = split;
+void vk_w4_force_plan(int ctas, int unused) {
+    (void)unused;
+    g_force_ctas = ctas;
 }
 
 size_t vk_w4_workspace_bytes(int M, int N, int K) {
-    if (M > 16) M = 16;
-    const W4Plan pl = w4_plan(M, N, K);
-    return kCounterBytes + (pl.S > 1 ? (size_t)pl.S * ((N + 31) / 32) * 32 * 16 * 4 : 0);
+    (void)M;
+    if (N <= 0 || K <= 0 || K % 64 != 0) return 0;
+    return w4_ws_bytes(w4_plan(N, K));
 }
 
 int vk_w4_gemm(const void* packed, const void* x, int ldx, void* y, int ldy, int M, int N, int K, void* workspace,
                size_t workspace_bytes, cudaStream_t stream) {
     if (M <= 0 || N <= 0 || K <= 0 || K % 64 != 0 || ldx % 8 != 0 || ldx < K || ldy < N) return VK_EINVAL;
-    if (((uintptr_t)x & 15) || ((uintptr_t)packed & 15)) return VK_EINVAL;
+    if (((uintptr_t)x & 15) || ((uintptr_t)packed & 15) || workspace == nullptr || ((uintptr_t)workspace & 15)) return VK_EINVAL;
+    const W4Plan pl = w4_plan(N, K);
+    if (pl.NSB > (int)(kCounterBytes / 4)) return VK_EINVAL;
+    if (workspace_bytes < w4_ws_bytes(pl)) return VK_ENOSPC;
+    static bool configured = false;
+    if (!configured) {
+        VK_CUDA(cudaFuncSetAttribute(w4_gemm_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes));
+        VK_CUDA(cudaFuncSetAttribute(w4_gemm_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes));
+        configured = true;
+    }
+    uint8_t* ws = (uint8_t*)workspace;
     // rows beyond 16 re-stream the weights once per 16 rows
     for (int m0 = 0; m0 < M; m0 += 16) {
         const int m = M - m0 < 16 ? M - m0 : 16;
-        const W4Plan pl = w4_plan(m, N, K);
         W4Params p;
         p.wp = (const uint8_t*)packed;
-        p.x = (const __nv_bfloat16*)x + (size_t)m0 * ldx;
+        p.xrec = ws + kCounterBytes;
         p.y = (__nv_bfloat16*)y + (size_t)m0 * ldy;
-        p.counters = (int*)workspace;
-        p.part = (float*)((uint8_t*)workspace + kCounterBytes);
-        p.M = m; p.N = N; p.NB = (N + 31) / 32; p.G = K / 64; p.S = pl.S; p.ldx = ldx; p.ldy = ldy; p.ksmax = pl.ksmax;
-        if (pl.S > 1 && (workspace == nullptr || workspace_bytes < kCounterBytes + (size_t)pl.S * p.NB * 32 * 16 * 4)) return VK_ENOSPC;
-        cudaError_t e;
-        if (pl.mt == 1) e = pl.warps == 8 ? launch_gemm<1, 8>(p, pl, stream) : launch_gemm<1, 4>(p, pl, stream);
-        else e = pl.warps == 8 ? launch_gemm<2, 8>(p, pl, stream) : launch_gemm<2, 4>(p, pl, stream);
+        p.counters = (int*)ws;
+        p.part = (float*)(ws + kCounterBytes + (size_t)pl.G * kXRecBytes);
+        p.T = pl.T; p.M = m; p.N = N; p.NSB = pl.NSB; p.G = pl.G; p.P = pl.P; p.ldy = ldy; p.maxc = pl.maxc;
+        VK_CUDA(vk_launch(w4_xrec_kernel, dim3(pl.G), dim3(128), 0, stream, (const __nv_bfloat16*)x + (size_t)m0 * ldx, ldx, m,
+                          ws + kCounterBytes));
+        cudaError_t e = m <= 8 ? vk_launch(w4_gemm_kernel<1>, dim3(pl.P), dim3(kThreads), kSmemBytes, stream, p)
+                               : vk_launch(w4_gemm_kernel<2>, dim3(pl.P), dim3(kThreads), kSmemBytes, stream, p);
         if (e != cudaSuccess) return (int)e;
     }
     return VK_OK;
