@@ -123,6 +123,18 @@ int vk_attn_prep(const vk_attn_geom* g, const void* proj, int ldp, int off_k, in
 size_t vk_bcsa_select_scratch_bytes(const vk_attn_geom* g, int B, int max_blocks);
 int vk_bcsa_select(const vk_attn_geom* g, const void* q, const void* keys, const int* pos, const int* table, void* scratch,
                    int max_blocks, int* sel, int* nsel, int B, vk_stream_t stream);
+/* Far-block selection for callers that may not allocate device memory: a CUDA-graph node builder, a plugin running
+ * inside another runtime's memory budget, or a process whose allocator is owned by someone else has no buffer to hand
+ * in as `scratch`. This variant has no counterpart in the reference. It computes exactly what vk_bcsa_select computes
+ * but keeps the sort keys in a 1 MiB array that is part of the library image, so it calls no cudaMalloc / cudaFree
+ * and no allocating library routine. Limits: B <= 16 rows, NS <= 8 groups, max_pages * (64 / C) <= 2048 blocks per
+ * row; anything larger returns -3 (VK_ETOOBIG) and launches nothing. The first call on each device looks up the
+ * array's device address (cudaGetSymbolAddress, with that device current): make that first call outside any stream
+ * capture. All calls on a device share the one array, which keeps whatever the last call left in it (nothing in it
+ * needs clearing: every key is written before it is read): two calls that overlap on the GPU (different streams, or
+ * a graph replayed concurrently) race on it. */
+int vk_bcsa_select_static(const vk_attn_geom* g, const void* q, const void* keys, const int* pos, const int* table, int* sel,
+                          int* nsel, int B, vk_stream_t stream);
 /* The SDPA of _bcsa_batched / BatchKVCache.attend (volundr.py:790-791; batch.py:315-316) over window pages and far
  * keys, split over `nsplit` CTAs per (row, kv head), merged, times sigmoid(gate) (volundr.py:177-179).
  * part: fp32 scratch of vk_attend_scratch_bytes. out [B, Hq*D]. */

@@ -577,6 +577,36 @@ int vk_bcsa_select(const vk_attn_geom* gm, const void* q, const void* keys, cons
     return (int)vk_launch(bcsa_select_kernel, dim3(p.g.NS, B), dim3(256), 0, stream, p);
 }
 
+// ---- far-block selection for callers that cannot allocate
+// Fixed capacity of the built-in scratch: 16 rows x 8 selection groups x 2048 blocks per row (1 MiB, held by every
+// GPU that loads the library until the process exits).
+namespace {
+constexpr int kStaticRows = 16, kStaticGroups = 8, kStaticBlocks = 2048;
+static __device__ __align__(256) uint32_t g_select_scratch[kStaticRows * kStaticGroups * kStaticBlocks];
+uint32_t* g_select_scratch_addr[64] = {};  // device address of the array, per device ordinal (host-side cache)
+}  // namespace
+
+int vk_bcsa_select_static(const vk_attn_geom* gm, const void* q, const void* keys, const int* pos, const int* table, int* sel,
+                          int* nsel, int B, cudaStream_t stream) {
+    if (!geom_ok(gm) || gm->W <= 0 || B <= 0) return VK_EINVAL;
+    const int blocks = gm->max_pages * (kPage / gm->C);
+    if (B > kStaticRows || gm->NS > kStaticGroups || blocks > kStaticBlocks) return VK_ETOOBIG;
+    int dev = -1;
+    VK_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return VK_EINVAL;
+    if (g_select_scratch_addr[dev] == nullptr) {
+        // In host code the array's name is only a handle; the kernel needs the address the current device gave it.
+        void* addr = nullptr;
+        VK_CUDA(cudaGetSymbolAddress(&addr, g_select_scratch));
+        g_select_scratch_addr[dev] = (uint32_t*)addr;
+    }
+    SelectParams p = {};
+    p.q = (const __nv_bfloat16*)q; p.keys = (const __nv_bfloat16*)keys; p.pos = pos; p.table = table;
+    p.scratch = g_select_scratch_addr[dev]; p.sel = sel; p.nsel = nsel; p.cap = kStaticBlocks; p.n_pages = gm->n_pages;
+    p.scale = (float)(1.0 / sqrt((double)kD)); p.g = to_geom(gm);
+    return (int)vk_launch(bcsa_select_kernel, dim3(p.g.NS, B), dim3(256), 0, stream, p);
+}
+
 size_t vk_attend_scratch_bytes(const vk_attn_geom* gm, int B, int nsplit) {
     return (size_t)B * gm->Hq * nsplit * (kD + 2) * 4;
 }
