@@ -126,20 +126,28 @@ def run_reference(a):
 def gemm_roofline(model, bc, torch, ops, reps=3):
     """Every W4 GEMM of one step, launched back to back over all layers' weights (18+ GB: far beyond L2), timed with
     CUDA events on the launching stream. Returns (launches per step, algorithmic bytes per launch, seconds per launch)."""
+    from volundr_mlx_b200 import _lib
+
+    L = _lib.lib()
     B = bc.B
     jobs = []
     for w in model.layers:
-        for nm, x, y in (("proj", bc.h, bc.proj), ("out", bc.mix, bc.r), ("gate_up", bc.hn2, bc.gu), ("down", bc.act, bc.mlp)):
-            wt = w[nm]
-            jobs.append((wt, x[:B, : wt.K], y[:B]))
+        for nm, xr, y in (("proj", bc.xr_h, bc.proj), ("out", bc.xr_mix, bc.r), ("gate_up", bc.xr_hn2, bc.gu), ("down", bc.xr_act, bc.mlp)):
+            jobs.append((w[nm], xr, y[:B]))
     nbytes = sum(wt.nbytes + B * wt.K * 2 + B * wt.N * 2 for wt, _, _ in jobs)
-    st = torch.cuda.current_stream()
-    for wt, x, y in jobs:
-        ops.w4_gemm(x, wt, y)
+    ws = ops.workspace(1 << 26, model.device)
+
+    def run_all():
+        st = torch.cuda.current_stream().cuda_stream
+        for wt, xr, y in jobs:   # the entry point the step itself uses: activations already in the kernel's input layout
+            rc = L.vk_w4_gemm_xrec(wt.packed.data_ptr(), xr.data_ptr(), y.data_ptr(), y.stride(0), B, wt.N, wt.K, ws.data_ptr(),
+                                   ws.numel(), st)
+            assert rc == 0, rc
+
+    run_all()
     g = torch.cuda.CUDAGraph()
     with torch.cuda.graph(g):
-        for wt, x, y in jobs:
-            ops.w4_gemm(x, wt, y)
+        run_all()
     g.replay()
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)

@@ -50,10 +50,26 @@ size_t vk_w4_workspace_bytes(int M, int N, int K);
 /* y[M, ldy] (bf16) = x[M, ldx] (bf16) . dequant(W)^T, fp32 accumulation. ldx a multiple of 8, x 16-byte aligned. */
 int vk_w4_gemm(const void* packed, const void* x, int ldx, void* y, int ldy, int M, int N, int K, void* workspace,
                size_t workspace_bytes, vk_stream_t stream);
+/* The same product for activations that already sit in the kernel's input layout ("x records": per 64 columns 2176
+ * bytes = 16 rows x 64 bf16 with the 16-byte pieces xor-swizzled by row, then per row the group's sum as two bf16 pairs;
+ * rows >= M zero). The row kernels below write this layout directly when given an `xrec_*` pointer (as the reference
+ * fuses its input preparation into the producing op, agens-mlx-bench/smallm/prep_nax.py:24-148). M <= 16. */
+int vk_w4_gemm_xrec(const void* packed, const void* xrec, void* y, int ldy, int M, int N, int K, void* workspace,
+                    size_t workspace_bytes, vk_stream_t stream);
+/* The same streaming kernel over plain bf16 weights: the linears the reference keeps unquantised (convert.py:16-17),
+ * above all lm_head (volundr.py:958, :968; batch.py:552). W [N, K] row-major bf16 is repacked once into the kernel's
+ * fragment order (vk_bf16_repack); y = bf16(x . W^T), fp32 accumulation, 1..16 rows per pass. Workspace rules as for
+ * vk_w4_gemm. */
+size_t vk_bf16_packed_bytes(int N, int K);
+int vk_bf16_repack(const void* W, int N, int K, void* packed, vk_stream_t stream);
+size_t vk_bf16_workspace_bytes(int M, int N, int K);
+int vk_bf16_gemm_packed(const void* packed, const void* x, int ldx, void* y, int ldy, int M, int N, int K, void* workspace,
+                        size_t workspace_bytes, vk_stream_t stream);
 /* Testing aid: force the number of persistent CTAs the work is dealt to (0 = two per SM); second argument unused. */
 void vk_w4_force_plan(int ctas, int unused);
 
-/* ---- row-wise fused kernels (one CTA per token row). bf16 activations [B, D] unless noted. */
+/* ---- row-wise fused kernels (one CTA per token row). bf16 activations [B, D] unless noted. An `xrec_*` argument may
+ * be NULL; otherwise it receives the same output as x records for a following vk_w4_gemm_xrec (B <= 16). */
 /* x = embed[tok]; H[b][0..3] = x; hn = RMSNorm(x) * w_mhc0 (volundr-mlx/volundr.py:921-930, :944; batch.py:525-538).
  * With engram_prev != NULL also advances the id window [B, max(order) - 1] and hashes the n-gram rows
  * engram_rows_out [B, n_orders] (volundr.py:572-582; host ints `orders`). */
@@ -64,14 +80,14 @@ int vk_embed(const int* tok, const void* embed, const void* w_mhc0, void* H, voi
  * post, Sinkhorn, x_in, h = OffsetRMSNorm(x_in) * (1 + w_in). post [B,4], res [B,16] are fp32 holding bf16 values;
  * d_scratch [B, 24] fp32 receives the dyn linear's output. */
 int vk_mhc_mix_norm(const void* H, const void* hn, const void* w_dyn, const void* pre_s, const void* post_s,
-                    const void* res_s, const void* w_in, void* x_in, void* h, float* post, float* res, float* d_scratch,
-                    int B, int D, int iters, float eps, vk_stream_t stream);
+                    const void* res_s, const void* w_in, void* x_in, void* h, void* xrec_h, float* post, float* res,
+                    float* d_scratch, int B, int D, int iters, float eps, vk_stream_t stream);
 /* kernels.rms_norm(x, w, eps, offset, r) (kernels.py:285-306; volundr.py:893-899): h2 = bf16(x + r) (r, h2 may be
  * NULL), hn = RMSNorm(h2) * (offset + w). */
-int vk_add_rmsnorm(const void* x, const void* r, const void* w, void* h2, void* hn, int B, int D, float eps, int offset,
-                   vk_stream_t stream);
+int vk_add_rmsnorm(const void* x, const void* r, const void* w, void* h2, void* hn, void* xrec_hn, int B, int D, float eps,
+                   int offset, vk_stream_t stream);
 /* _silu_mul (volundr.py:166-168) on gu = [gate (I) | up (I)] rows of stride ld_gu. */
-int vk_silu_mul(const void* gu, void* act, int B, int I, int ld_gu, vk_stream_t stream);
+int vk_silu_mul(const void* gu, void* act, void* xrec_act, int B, int I, int ld_gu, vk_stream_t stream);
 /* Engram row gather + RMSNorm (volundr.py:594-595). tables / ld_table / col0 are host arrays of n_orders entries. */
 int vk_engram_gather(const void* const* tables, const int* ld_table, const int* col0, const int* rows, const void* w,
                      void* e, int B, int n_orders, int dim, float eps, vk_stream_t stream);
@@ -86,6 +102,12 @@ int vk_bf16_gemm(const void* x, int ldx, const void* W, const void* bias, void* 
                  vk_stream_t stream);
 /* Greedy token: first maximum over logits[:, :valid] (scheduler.py:391). */
 int vk_argmax(const void* logits, int ld, int valid, int* out, int B, vk_stream_t stream);
+/* The same over a vocabulary split across tensor-parallel ranks (no counterpart in the single-GPU reference): each rank
+ * writes pairs [B, 2] = (float bits of its largest logit among its first `valid` columns, index_offset + its first
+ * position; (-inf, INT_MAX) when valid <= 0); after an all-gather to [ranks, B, 2], vk_argmax_merge picks the largest
+ * value, ties to the lowest index. */
+int vk_argmax_pairs(const void* logits, int ld, int valid, int index_offset, int* pairs, int B, vk_stream_t stream);
+int vk_argmax_merge(const int* pairs, int n_ranks, int* out, int B, vk_stream_t stream);
 
 /* ---- Kimi Delta Attention decode step (KDA.__call__, volundr.py:388-410: DF.kda_conv_gates decode_fused.py:469-493,
  * kernels.gated_delta_vec kernels.py:446-458, kernels.gated_norm kernels.py:918-928, plus in_proj_b and f_up).
@@ -93,8 +115,8 @@ int vk_argmax(const void* logits, int ld, int valid, int* out, int B, vk_stream_
  * current buffer; S fp32 [slots, HV, 128, 128] updated in place; out [B, HV*128]. */
 int vk_kda_step(const void* proj, int ldp, int off_z, int off_fd, const void* h, const void* w_b, const void* w_fup,
                 const float* conv_w, const float* A_log, const float* dt_bias, const void* norm_w, void* conv,
-                const int* parity, size_t conv_stride, float* S, void* out, const float* g_override, int B, int D, int Hk,
-                int HV, int Dk, int Dv, int rank, float eps, vk_stream_t stream);
+                const int* parity, size_t conv_stride, float* S, void* out, void* xrec_out, const float* g_override, int B,
+                int D, int Hk, int HV, int Dk, int Dv, int rank, float eps, vk_stream_t stream);
 
 /* ---- paged ragged attention (64-token pages). */
 typedef struct vk_attn_geom {
@@ -141,7 +163,7 @@ int vk_bcsa_select_static(const vk_attn_geom* g, const void* q, const void* keys
 size_t vk_attend_scratch_bytes(const vk_attn_geom* g, int B, int nsplit);
 int vk_attend_decode(const vk_attn_geom* g, const void* q, const void* K, const void* V, const void* PK, const void* PV,
                      const int* pos, const int* table, const int* sel, const int* nsel, const void* proj, int ldp,
-                     void* part, int nsplit, void* out, int B, vk_stream_t stream);
+                     void* part, int nsplit, void* out, void* xrec_out, int B, vk_stream_t stream);
 
 #ifdef __cplusplus
 }

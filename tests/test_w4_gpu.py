@@ -128,3 +128,27 @@ def test_rejects_bad_arguments(cuda):
     L = _lib.lib()
     assert L.vk_w4_gemm(None, None, 100, None, 64, 1, 64, 100, None, 0, None) == -1  # K not a multiple of 64
     assert L.vk_w4_repack(None, None, None, 32, 512, 32, None, None) == -1           # group 32 unsupported
+
+
+@pytest.mark.parametrize("M", [1, 7, 16, 21])
+@pytest.mark.parametrize("N,K", [(300, 256), (2050, 1024)])
+def test_bf16_streaming_gemm(cuda, M, N, K):
+    """The unquantised linears (lm_head): y = bf16(x . W^T) on the same streaming kernel. Floating point only, so the
+    reference here is the fp32 product of the same bf16 inputs; rtol 2e-2 / atol 2e-2 as for every bf16 output."""
+    from volundr_mlx_b200 import _lib, ops
+
+    gen = torch.Generator(device=cuda)
+    gen.manual_seed(N + M)
+    W = (torch.randn((N, K), device=cuda, generator=gen) * 0.05).to(torch.bfloat16)
+    x = torch.randn((M, K), device=cuda, generator=gen).to(torch.bfloat16)
+    wt = ops.bf16_repack(W)
+    L = _lib.lib()
+    for ctas in (0, 1, 7):
+        L.vk_w4_force_plan(ctas, 0)
+        try:
+            y = ops.bf16_gemm(x, wt)
+        finally:
+            L.vk_w4_force_plan(0, 0)
+        want = x.float() @ W.float().T
+        torch.testing.assert_close(y.float(), want, rtol=2e-2, atol=2e-2)
+    ops.check_status()

@@ -21,15 +21,22 @@ SIGNATURES = {
     "vk_w4_force_plan": (None, [c_int, c_int]),
     "vk_w4_workspace_bytes": (c_size_t, [c_int, c_int, c_int]),
     "vk_w4_gemm": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_size_t, c_void_p]),
+    "vk_bf16_packed_bytes": (c_size_t, [c_int, c_int]),
+    "vk_bf16_repack": (c_int, [c_void_p, c_int, c_int, c_void_p, c_void_p]),
+    "vk_bf16_workspace_bytes": (c_size_t, [c_int, c_int, c_int]),
+    "vk_bf16_gemm_packed": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_size_t, c_void_p]),
+    "vk_w4_gemm_xrec": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_size_t, c_void_p]),
     "vk_embed": (c_int, [c_void_p] * 7 + [c_void_p, c_int, c_int, c_int, c_int, c_float, c_void_p]),
-    "vk_mhc_mix_norm": (c_int, [c_void_p] * 12 + [c_int, c_int, c_int, c_float, c_void_p]),
-    "vk_add_rmsnorm": (c_int, [c_void_p] * 5 + [c_int, c_int, c_float, c_int, c_void_p]),
-    "vk_silu_mul": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
+    "vk_mhc_mix_norm": (c_int, [c_void_p] * 13 + [c_int, c_int, c_int, c_float, c_void_p]),
+    "vk_add_rmsnorm": (c_int, [c_void_p] * 6 + [c_int, c_int, c_float, c_int, c_void_p]),
+    "vk_silu_mul": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
     "vk_engram_gather": (c_int, [c_void_p] * 6 + [c_int, c_int, c_int, c_float, c_void_p]),
     "vk_mhc_combine_norm": (c_int, [c_void_p] * 12 + [c_int, c_int, c_int, c_float, c_void_p]),
     "vk_bf16_gemm": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]),
     "vk_argmax": (c_int, [c_void_p, c_int, c_int, c_void_p, c_int, c_void_p]),
-    "vk_kda_step": (c_int, [c_void_p, c_int, c_int, c_int] + [c_void_p] * 9 + [c_size_t, c_void_p, c_void_p, c_void_p]
+    "vk_argmax_pairs": (c_int, [c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_void_p]),
+    "vk_argmax_merge": (c_int, [c_void_p, c_int, c_void_p, c_int, c_void_p]),
+    "vk_kda_step": (c_int, [c_void_p, c_int, c_int, c_int] + [c_void_p] * 9 + [c_size_t, c_void_p, c_void_p, c_void_p, c_void_p]
                     + [c_int] * 7 + [c_float, c_void_p]),
     "vk_batch_step_begin": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                     c_void_p]),
@@ -40,7 +47,7 @@ SIGNATURES = {
     "vk_bcsa_select": (c_int, [c_void_p] * 6 + [c_int, c_void_p, c_void_p, c_int, c_void_p]),
     "vk_bcsa_select_static": (c_int, [c_void_p] * 7 + [c_int, c_void_p]),
     "vk_attend_scratch_bytes": (c_size_t, [c_void_p, c_int, c_int]),
-    "vk_attend_decode": (c_int, [c_void_p] * 11 + [c_int, c_void_p, c_int, c_void_p, c_int, c_void_p]),
+    "vk_attend_decode": (c_int, [c_void_p] * 11 + [c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p]),
 }
 
 

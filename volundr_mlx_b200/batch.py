@@ -51,6 +51,8 @@ class BatchCache:
         self.desc = torch.zeros((S, 8), **i32)
         self.parity = torch.zeros(1, **i32)
         self.greedy = torch.zeros(S, **i32)
+        self.pairs = torch.zeros((S, 2), **i32)
+        self.pairs_all = torch.zeros((model.tp_size, S, 2), **i32)
         bf = dict(dtype=BF16, device=d)
         f32 = dict(dtype=torch.float32, device=d)
         m = model
@@ -86,7 +88,15 @@ class BatchCache:
         self.r, self.h2, self.hn2, self.mlp = (torch.zeros((S, D), **bf) for _ in range(4))
         self.gu = torch.zeros((S, 2 * m.I), **bf)
         self.act = torch.zeros((S, m.I), **bf)
-        self.logits = torch.zeros((S, m.lm_head.shape[0]), **bf)
+        self.logits = torch.zeros((S, m.vocab_shard), **bf)
+        # activations in the W4 GEMM's input layout (2176 bytes per 64 columns), written by the producing kernels;
+        # rows the batch does not use stay zero (cleared whenever the membership changes)
+        u8 = dict(dtype=torch.uint8, device=d)
+        self.xr_h = torch.zeros(D // 64 * 2176, **u8)
+        self.xr_mix = torch.zeros(self.mix.shape[1] // 64 * 2176, **u8)
+        self.xr_hn2 = torch.zeros(D // 64 * 2176, **u8)
+        self.xr_act = torch.zeros(m.I // 64 * 2176, **u8)
+        self.fused_xrec = S <= 16
         self.y_dbg = None
         self.q = torch.zeros((S, m.Hq, 128), **bf)
         if self.indexer:
@@ -98,7 +108,7 @@ class BatchCache:
         self.nsel = torch.zeros((S, max(self.NS, 1)), **i32)
         self.max_blocks = self.max_pages * (PAGE // C) if self.has_bcsa else 1
         self.sel_scratch = torch.zeros((S, max(self.NS, 1), self.max_blocks), **i32)
-        self.nsplit_bcsa, self.nsplit_dense = 8, 32
+        self.nsplit_bcsa, self.nsplit_dense = 16, 64
         self.part = torch.zeros((S, m.Hq, max(self.nsplit_bcsa, self.nsplit_dense), 130), **f32)
         if a.engram_layers:
             cat = a.engram_dim * len(a.engram_orders)
@@ -132,7 +142,12 @@ class BatchCache:
     def row(self, key) -> int:
         return self.keys.index(key)
 
+    def _clear_xrec(self):
+        for t in (self.xr_h, self.xr_mix, self.xr_hn2, self.xr_act):
+            t.zero_()
+
     def _sync_rows(self):
+        self._clear_xrec()
         self.pos[: self.B] = torch.tensor(self._pos, dtype=torch.int32, device=self.pos.device) if self.B else self.pos[:0]
 
     def apply(self, leave=(), join=()):
@@ -291,9 +306,15 @@ def _launch_step(model: Model, bc: BatchCache, capture=()):
     ws = ops.workspace(1 << 26, model.device)
     caps = []
 
-    def gemm(x, wt, y):
-        ck(L.vk_w4_gemm(_p(wt.packed), _p(x), x.stride(0), _p(y), y.stride(0), B, wt.N, wt.K, _p(ws), ws.numel(), st),
-           "vk_w4_gemm")
+    fx = bc.fused_xrec
+
+    def gemm(x, wt, y, xr=None):
+        if fx and xr is not None:
+            ck(L.vk_w4_gemm_xrec(_p(wt.packed), _p(xr), _p(y), y.stride(0), B, wt.N, wt.K, _p(ws), ws.numel(), st),
+               "vk_w4_gemm_xrec")
+        else:
+            ck(L.vk_w4_gemm(_p(wt.packed), _p(x), x.stride(0), _p(y), y.stride(0), B, wt.N, wt.K, _p(ws), ws.numel(), st),
+               "vk_w4_gemm")
 
     def allreduce(t):
         if tp:
@@ -311,14 +332,16 @@ def _launch_step(model: Model, bc: BatchCache, capture=()):
         if i in capture:
             caps.append(bc.H[:B, 0].clone())
         ck(L.vk_mhc_mix_norm(_p(bc.H), _p(bc.hn), _p(w["dyn"]), _p(w["pre_s"]), _p(w["post_s"]), _p(w["res_s"]),
-                             _p(w["ln_in"]), _p(bc.x_in), _p(bc.h), _p(bc.post), _p(bc.res), _p(bc.dyn), B, D, a.mhc_sinkhorn_iters,
+                             _p(w["ln_in"]), _p(bc.x_in), _p(bc.h), _p(bc.xr_h) if fx else None, _p(bc.post), _p(bc.res), _p(bc.dyn), B, D,
+                             a.mhc_sinkhorn_iters,
                              eps, st), "vk_mhc_mix_norm")
-        gemm(bc.h, w["proj"], bc.proj)
+        gemm(bc.h, w["proj"], bc.proj, bc.xr_h)
         if w["mixer"] == "kda":
             nmix = model.HV * 128
             ck(L.vk_kda_step(_p(bc.proj), bc.proj.stride(0), w["off_z"], w["off_fd"], _p(bc.h), _p(w["in_proj_b"]),
                              _p(w["f_up"]), _p(w["conv_w"]), _p(w["A_log"]), _p(w["dt_bias"]), _p(w["gnorm"]),
-                             _p(lst["conv"]), _p(bc.parity), lst["conv"][0].numel(), _p(lst["S"]), _p(bc.mix), None, B, D,
+                             _p(lst["conv"]), _p(bc.parity), lst["conv"][0].numel(), _p(lst["S"]), _p(bc.mix),
+                             _p(bc.xr_mix) if fx else None, None, B, D,
                              model.Hk, model.HV, 128, 128, a.kda_gate_rank, eps, st), "vk_kda_step")
         else:
             bcsa = w["mixer"] == "bcsa"
@@ -342,16 +365,18 @@ def _launch_step(model: Model, bc: BatchCache, capture=()):
                                     st), "vk_bcsa_select")
             ck(L.vk_attend_decode(ctypes.byref(g), _p(bc.q), _p(lst["K"]), _p(lst["V"]), _p(lst.get("PK")),
                                   _p(lst.get("PV")), _p(bc.pos), _p(bc.table), _p(bc.sel), _p(bc.nsel), _p(bc.proj),
-                                  bc.proj.stride(0), _p(bc.part), bc.nsplit_bcsa if bcsa else bc.nsplit_dense, _p(bc.mix), B,
-                                  st), "vk_attend_decode")
+                                  bc.proj.stride(0), _p(bc.part), bc.nsplit_bcsa if bcsa else bc.nsplit_dense, _p(bc.mix),
+                                  _p(bc.xr_mix) if fx else None, B, st), "vk_attend_decode")
         mixv = bc.mix[:, :nmix]
-        gemm(mixv, w["out"], bc.r)
+        gemm(mixv, w["out"], bc.r, bc.xr_mix)
         allreduce(bc.r)
-        ck(L.vk_add_rmsnorm(_p(bc.x_in), _p(bc.r), _p(w["ln_post"]), _p(bc.h2), _p(bc.hn2), B, D, eps, 1, st),
+        ck(L.vk_add_rmsnorm(_p(bc.x_in), _p(bc.r), _p(w["ln_post"]), _p(bc.h2), _p(bc.hn2), _p(bc.xr_hn2) if fx else None, B, D,
+                            eps, 1, st),
            "vk_add_rmsnorm")
-        gemm(bc.hn2, w["gate_up"], bc.gu)
-        ck(L.vk_silu_mul(_p(bc.gu), _p(bc.act), B, model.I, bc.gu.stride(0), st), "vk_silu_mul")
-        gemm(bc.act, w["down"], bc.mlp)
+        gemm(bc.hn2, w["gate_up"], bc.gu, bc.xr_hn2)
+        ck(L.vk_silu_mul(_p(bc.gu), None if fx else _p(bc.act), _p(bc.xr_act) if fx else None, B, model.I, bc.gu.stride(0), st),
+           "vk_silu_mul")
+        gemm(bc.act, w["down"], bc.mlp, bc.xr_act)
         allreduce(bc.mlp)
         eng = "eng_norm" in w
         if eng:
@@ -370,10 +395,21 @@ def _launch_step(model: Model, bc: BatchCache, capture=()):
                                  _p(bc.hn), _p(val) if eng else None, _p(w["eng_gate_w"]) if eng else None,
                                  _p(w["eng_gate_b"]) if eng else None, _p(bc.y_dbg) if bc.y_dbg is not None else None, B, D,
                                  1 if last else 0, eps, st), "vk_mhc_combine_norm")
-    V = model.lm_head.shape[0]
-    ck(L.vk_bf16_gemm(_p(bc.hn), D, _p(model.lm_head), None, _p(bc.logits), bc.logits.stride(0), B, V, D, st), "vk_bf16_gemm")
+    V = model.vocab_shard
+    if isinstance(model.lm_head, ops.BF16Weight):
+        ck(L.vk_bf16_gemm_packed(_p(model.lm_head.packed), _p(bc.hn), D, _p(bc.logits), bc.logits.stride(0), B, V, D, _p(ws),
+                                 ws.numel(), st), "vk_bf16_gemm_packed")
+    else:
+        ck(L.vk_bf16_gemm(_p(bc.hn), D, _p(model.lm_head), None, _p(bc.logits), bc.logits.stride(0), B, V, D, st), "vk_bf16_gemm")
     if not tp:
         ck(L.vk_argmax(_p(bc.logits), bc.logits.stride(0), min(a.vocab_valid, V), _p(bc.greedy), B, st), "vk_argmax")
+    else:  # vocabulary-sharded: local (max, index) pairs, all-gather, merge
+        n = model.tp_size
+        ck(L.vk_argmax_pairs(_p(bc.logits), bc.logits.stride(0), max(0, min(a.vocab_valid - model.vocab0, V)), model.vocab0,
+                             _p(bc.pairs), B, st), "vk_argmax_pairs")
+        gathered = bc.pairs_all.view(-1)[: n * B * 2].view(n, B, 2)   # contiguous [ranks, B, 2]
+        torch.distributed.all_gather_into_tensor(gathered, bc.pairs[:B], group=model.group)
+        ck(L.vk_argmax_merge(_p(bc.pairs_all), n, _p(bc.greedy), B, st), "vk_argmax_merge")
     ck(L.vk_batch_step_end(_p(bc.pos), _p(bc.parity), B, st), "vk_batch_step_end")
     return caps
 
@@ -431,4 +467,7 @@ def model_warm(model: Model):
                     continue
                 seen.add((wt.N, wt.K, M))
                 ops.w4_gemm(torch.zeros((M, wt.K), dtype=BF16, device=d), wt)
+    if isinstance(model.lm_head, ops.BF16Weight):
+        for M in (1, 16):
+            ops.bf16_gemm(torch.zeros((M, model.lm_head.K), dtype=BF16, device=d), model.lm_head)
     torch.cuda.synchronize(d)

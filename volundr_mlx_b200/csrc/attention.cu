@@ -18,6 +18,7 @@
 // bf16(bf16(mean_h fp32(bf16(q_h . k_j))) * scale) with the dot summed in a fixed order (4 consecutive elements per
 // lane, then an xor tree), so the selected indices are reproducible bit for bit.
 #include "common.cuh"
+#include "xrec.cuh"
 
 namespace {
 
@@ -262,24 +263,36 @@ __global__ void __launch_bounds__(256) bcsa_select_kernel(const SelectParams p) 
     float qv[8][4];
     for (int h = 0; h < nh; h++) load4(qb + (size_t)h * kD, lane, qv[h]);
     const float inv_nh = 1.f / (float)nh;
-    for (int j = warp; j < nv; j += 8) {
-        const int page = p.table[b * g.max_pages + (j / spp)];
-        const __nv_bfloat16* kr = per_kv ? p.keys + (((size_t)page * g.KVH + ns) * spp + j % spp) * kD
-                                         : p.keys + ((size_t)page * spp + j % spp) * kD;
-        float kx[4];
-        load4(kr, lane, kx);
-        float s = 0.f;
-        for (int h = 0; h < nh; h++) {
-            float a = qv[h][0] * kx[0];
-            a = fmaf(qv[h][1], kx[1], a);
-            a = fmaf(qv[h][2], kx[2], a);
-            a = fmaf(qv[h][3], kx[3], a);
-            a = warp_sum(a);
-            s += bfr(a);
+    // four blocks per warp and pass: their table entries and keys are fetched together, then scored one by one
+    for (int j0 = warp * 4; j0 < nv; j0 += 32) {
+        float kx[4][4];
+#pragma unroll
+        for (int u = 0; u < 4; u++) {
+            const int j = j0 + u;
+            if (j < nv) {
+                const int page = p.table[b * g.max_pages + (j / spp)];
+                const __nv_bfloat16* kr = per_kv ? p.keys + (((size_t)page * g.KVH + ns) * spp + j % spp) * kD
+                                                 : p.keys + ((size_t)page * spp + j % spp) * kD;
+                load4(kr, lane, kx[u]);
+            }
         }
-        s = bfr(s * inv_nh);
-        s = bfr(s * p.scale);
-        if (lane == 0) keys[j] = score_key(s, j);
+#pragma unroll
+        for (int u = 0; u < 4; u++) {
+            const int j = j0 + u;
+            if (j >= nv) break;
+            float sc = 0.f;
+            for (int h = 0; h < nh; h++) {
+                float a = qv[h][0] * kx[u][0];
+                a = fmaf(qv[h][1], kx[u][1], a);
+                a = fmaf(qv[h][2], kx[u][2], a);
+                a = fmaf(qv[h][3], kx[u][3], a);
+                a = warp_sum(a);
+                sc += bfr(a);
+            }
+            sc = bfr(sc * inv_nh);
+            sc = bfr(sc * p.scale);
+            if (lane == 0) keys[j] = score_key(sc, j);
+        }
     }
     __syncthreads();
     // ---- radix select: the topk-th largest key (keys are unique), 8 bits per pass from the top
@@ -295,14 +308,29 @@ __global__ void __launch_bounds__(256) bcsa_select_kernel(const SelectParams p) 
             if ((k & mask) == prefix) atomicAdd(&hist[(k >> shift) & 0xFF], 1);
         }
         __syncthreads();
-        if (threadIdx.x == 0) {
-            int need = s_k, d = 255;
-            for (; d > 0; d--) {
-                if (hist[d] >= need) break;
-                need -= hist[d];
+        if (warp == 0) {
+            // the digit d with count(digits > d) < need <= count(digits >= d): lane l holds digits 8l .. 8l+7
+            int c8[8], mine = 0;
+#pragma unroll
+            for (int e = 0; e < 8; e++) { c8[e] = hist[lane * 8 + e]; mine += c8[e]; }
+            int incl = mine;  // keys in the digits of this lane and of every higher lane
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int v = __shfl_down_sync(0xffffffffu, incl, o);
+                if (lane + o < 32) incl += v;
             }
-            s_k = need;
-            s_prefix = prefix | ((uint32_t)d << shift);
+            const int suffix = incl - mine;
+            const int need = s_k;
+            const bool here = suffix < need && suffix + mine >= need;
+            if (here) {
+                int acc = suffix, d = lane * 8 + 7;
+                for (int e = 7; e >= 0; e--) {
+                    if (acc + c8[e] >= need) { d = lane * 8 + e; break; }
+                    acc += c8[e];
+                }
+                s_k = need - acc;
+                s_prefix = prefix | ((uint32_t)d << shift);
+            }
         }
         mask |= 0xFFu << shift;
         __syncthreads();
@@ -349,6 +377,10 @@ struct AttendParams {
 };
 
 constexpr int kRowStride = kD + 8;  // bf16 elements; keeps 16-byte row reads conflict-free
+
+__device__ __forceinline__ void cp_async16(void* dst_smem, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst_smem)), "l"(src) : "memory");
+}
 
 template <int G>
 __global__ void __launch_bounds__(128) attend_decode_kernel(const AttendParams p) {
@@ -415,12 +447,13 @@ __global__ void __launch_bounds__(128) attend_decode_kernel(const AttendParams p
             }
         }
         __syncthreads();
-        // ---- stage the rows (16 bytes per thread per go: 16 threads per 256-byte row)
+        // ---- stage the rows: 16-byte asynchronous copies, all in flight at once (16 per 256-byte row)
         for (int i = t; i < nrows * 16; i += 128) {
             const int r = i >> 4, cch = i & 15;
-            *reinterpret_cast<uint4*>(Ks + r * kRowStride + cch * 8) = *reinterpret_cast<const uint4*>(rowK[r] + cch * 8);
-            *reinterpret_cast<uint4*>(Vs + r * kRowStride + cch * 8) = *reinterpret_cast<const uint4*>(rowV[r] + cch * 8);
+            cp_async16(Ks + r * kRowStride + cch * 8, rowK[r] + cch * 8);
+            cp_async16(Vs + r * kRowStride + cch * 8, rowV[r] + cch * 8);
         }
+        asm volatile("cp.async.wait_all;" ::: "memory");
         __syncthreads();
         // ---- scores: thread (key i = t % 64, heads h = t / 64, t / 64 + 2, ...)
         {
@@ -485,8 +518,9 @@ __global__ void __launch_bounds__(128) attend_decode_kernel(const AttendParams p
 
 // merge the splits of one query head, divide, round, apply sigmoid(gate) (volundr.py:177-179, :752-753)
 __global__ void __launch_bounds__(128) attend_merge_kernel(const float* __restrict__ part, const __nv_bfloat16* __restrict__ proj,
-                                                           int ldp, __nv_bfloat16* __restrict__ out, int Hq, int KVH,
-                                                           int nsplit) {
+                                                           int ldp, __nv_bfloat16* __restrict__ out, uint8_t* __restrict__ xrec_out,
+                                                           int Hq, int KVH, int nsplit) {
+    __shared__ float red[4];
     pdl_launch_dependents();
     pdl_wait();
     const int hq = blockIdx.x, b = blockIdx.y, t = threadIdx.x;
@@ -505,7 +539,16 @@ __global__ void __launch_bounds__(128) attend_merge_kernel(const float* __restri
     }
     const float ob = bfr(o / l);
     const float gate = bf2f(proj[(size_t)b * ldp + (size_t)hq * 2 * kD + kD + t]);
-    out[((size_t)b * Hq + hq) * kD + t] = f2bf(ob * (1.f / (1.f + expf(-gate))));
+    const float ov = bfr(ob * (1.f / (1.f + expf(-gate))));
+    out[((size_t)b * Hq + hq) * kD + t] = f2bf(ov);
+    if (xrec_out != nullptr) {
+        const int kg = hq * 2 + (t >> 6);
+        *xrec_elem(xrec_out, kg, b, t & 63) = f2bf(ov);
+        const float ws = warp_sum(ov);
+        if ((t & 31) == 0) red[t >> 5] = ws;
+        __syncthreads();
+        if ((t & 63) == 0) xrec_store_sum(xrec_out, kg, b, red[t >> 5] + red[(t >> 5) + 1]);
+    }
 }
 
 template <int G>
@@ -613,8 +656,8 @@ size_t vk_attend_scratch_bytes(const vk_attn_geom* gm, int B, int nsplit) {
 
 int vk_attend_decode(const vk_attn_geom* gm, const void* q, const void* K, const void* V, const void* PK, const void* PV,
                      const int* pos, const int* table, const int* sel, const int* nsel, const void* proj, int ldp,
-                     void* part, int nsplit, void* out, int B, cudaStream_t stream) {
-    if (!geom_ok(gm) || B <= 0 || nsplit <= 0) return VK_EINVAL;
+                     void* part, int nsplit, void* out, void* xrec_out, int B, cudaStream_t stream) {
+    if (!geom_ok(gm) || B <= 0 || nsplit <= 0 || (xrec_out != nullptr && B > 16)) return VK_EINVAL;
     AttendParams p = {};
     p.q = (const __nv_bfloat16*)q; p.K = (const __nv_bfloat16*)K; p.V = (const __nv_bfloat16*)V;
     p.PK = (const __nv_bfloat16*)PK; p.PV = (const __nv_bfloat16*)PV; p.pos = pos; p.table = table;
@@ -633,7 +676,7 @@ int vk_attend_decode(const vk_attn_geom* gm, const void* q, const void* K, const
     }
     if (e != cudaSuccess) return (int)e;
     return (int)vk_launch(attend_merge_kernel, dim3(gm->Hq, B), dim3(128), 0, stream, (const float*)part,
-                          (const __nv_bfloat16*)proj, ldp, (__nv_bfloat16*)out, gm->Hq, gm->KVH, nsplit);
+                          (const __nv_bfloat16*)proj, ldp, (__nv_bfloat16*)out, (uint8_t*)xrec_out, gm->Hq, gm->KVH, nsplit);
 }
 
 }  // extern "C"

@@ -4,6 +4,7 @@
 // array (volundr.py:264-290, 145-150, 166-168, 594-597; the fused reference kernels decode_fused.py:43-355 compute
 // the same values).
 #include "common.cuh"
+#include "xrec.cuh"
 
 namespace {
 
@@ -108,6 +109,7 @@ struct MixParams {
     const __nv_bfloat16* w_in;     // [D] input_layernorm (offset norm)
     __nv_bfloat16* x_in;           // [B, D]
     __nv_bfloat16* h;              // [B, D]
+    uint8_t* xrec_h;               // null, or D / 64 x records receiving h
     float* post;                   // [B, 4]  (bf16-valued)
     float* res;                    // [B, 16] (bf16-valued)
     int D, iters;
@@ -205,6 +207,7 @@ __global__ void __launch_bounds__(1024) mhc_mix_norm_kernel(const MixParams p) {
 #pragma unroll
         for (int e = 0; e < 8; e++) o[e] = (x[e] * inv) * (1.f + w[e]);
         st8(p.h + (size_t)b * D + k, o);
+        if (p.xrec_h != nullptr) xrec_store_row_piece(p.xrec_h, b, k >> 3, o);
     }
 }
 
@@ -214,8 +217,8 @@ __global__ void __launch_bounds__(1024) add_rmsnorm_kernel(const __nv_bfloat16* 
                                                            const __nv_bfloat16* __restrict__ r,
                                                            const __nv_bfloat16* __restrict__ w,
                                                            __nv_bfloat16* __restrict__ h2,
-                                                           __nv_bfloat16* __restrict__ hn, int D, float eps,
-                                                           float offset) {
+                                                           __nv_bfloat16* __restrict__ hn, uint8_t* __restrict__ xrec_hn,
+                                                           int D, float eps, float offset) {
     __shared__ float red[kRowMaxWarps];
     pdl_launch_dependents();
     pdl_wait();
@@ -260,19 +263,31 @@ __global__ void __launch_bounds__(1024) add_rmsnorm_kernel(const __nv_bfloat16* 
 #pragma unroll
         for (int e = 0; e < 8; e++) o[e] = (v[e] * inv) * (offset + wv[e]);
         st8(hn + base + k, o);
+        if (xrec_hn != nullptr) xrec_store_row_piece(xrec_hn, blockIdx.x, k >> 3, o);
     }
 }
 
 // ------------------------------------------------------------------------------------------------ silu(g) * u
 // act = bf(silu(gate) * up) in fp32 (volundr.py:166-168); gu holds [gate (I) | up (I)] per row.
-__global__ void silu_mul_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ act, int I, int ld_gu) {
+__global__ void __launch_bounds__(256) silu_mul_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ act,
+                                                       uint8_t* __restrict__ xrec_act, int I, int ld_gu) {
     pdl_launch_dependents();
     pdl_wait();
     const int b = blockIdx.y;
-    const int i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= I) return;
-    const float g = bf2f(gu[(size_t)b * ld_gu + i]), u = bf2f(gu[(size_t)b * ld_gu + I + i]);
-    act[(size_t)b * I + i] = f2bf((g / (1.f + expf(-g))) * u);
+    const int piece = blockIdx.x * blockDim.x + threadIdx.x;   // 8 outputs
+    const bool valid = piece * 8 < I;                           // (I is a multiple of 64: groups never straddle the edge)
+    float g[8] = {}, u[8] = {}, o[8];
+    if (valid) {
+        ld8(gu + (size_t)b * ld_gu + piece * 8, g);
+        ld8(gu + (size_t)b * ld_gu + I + piece * 8, u);
+    }
+#pragma unroll
+    for (int e = 0; e < 8; e++) o[e] = (g[e] / (1.f + expf(-g[e]))) * u[e];
+    if (valid && act != nullptr) st8(act + (size_t)b * I + piece * 8, o);
+    if (xrec_act != nullptr) {   // whole warps take part in the group sums; pieces past the row write nothing
+        if (valid) xrec_store_row_piece(xrec_act, b, piece, o);
+        else { __shfl_xor_sync(0xffffffffu, 0.f, 1); __shfl_xor_sync(0xffffffffu, 0.f, 2); __shfl_xor_sync(0xffffffffu, 0.f, 4); }
+    }
 }
 
 // ------------------------------------------------------------------------------------------------ Engram gather
@@ -486,9 +501,65 @@ __global__ void __launch_bounds__(1024) argmax_kernel(const __nv_bfloat16* __res
     }
 }
 
+// Vocabulary-sharded greedy token. Each rank: (bits of its largest valid logit, global index of its first maximum).
+__global__ void __launch_bounds__(1024) argmax_pairs_kernel(const __nv_bfloat16* __restrict__ logits, int ld, int valid,
+                                                            int index_offset, int* __restrict__ pairs) {
+    __shared__ float bv[32];
+    __shared__ int bi[32];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int b = blockIdx.x;
+    float best = -INFINITY;
+    int idx = 0x7fffffff;
+    for (int i = threadIdx.x; i < valid; i += blockDim.x) {
+        const float v = bf2f(logits[(size_t)b * ld + i]);
+        if (v > best || (v == best && i < idx)) { best = v; idx = i; }
+    }
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+        if (ov > best || (ov == best && oi < idx)) { best = ov; idx = oi; }
+    }
+    if ((threadIdx.x & 31) == 0) { bv[threadIdx.x >> 5] = best; bi[threadIdx.x >> 5] = idx; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < (int)(blockDim.x >> 5); w++)
+            if (bv[w] > best || (bv[w] == best && bi[w] < idx)) { best = bv[w]; idx = bi[w]; }
+        pairs[2 * b] = __float_as_int(best);
+        pairs[2 * b + 1] = idx == 0x7fffffff ? idx : idx + index_offset;
+    }
+}
+
+// pairs [ranks, B, 2] -> the largest value, ties to the lowest global index
+__global__ void argmax_merge_kernel(const int* __restrict__ pairs, int n_ranks, int* __restrict__ out, int B) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int b = blockIdx.x * blockDim.x + threadIdx.x;
+    if (b >= B) return;
+    float best = -INFINITY;
+    int idx = 0x7fffffff;
+    for (int r = 0; r < n_ranks; r++) {
+        const float v = __int_as_float(pairs[((size_t)r * B + b) * 2]);
+        const int i = pairs[((size_t)r * B + b) * 2 + 1];
+        if (v > best || (v == best && i < idx)) { best = v; idx = i; }
+    }
+    out[b] = idx;
+}
+
 }  // namespace
 
 extern "C" {
+
+int vk_argmax_pairs(const void* logits, int ld, int valid, int index_offset, int* pairs, int B, cudaStream_t stream) {
+    if (B <= 0) return VK_EINVAL;
+    return (int)vk_launch(argmax_pairs_kernel, dim3(B), dim3(1024), 0, stream, (const __nv_bfloat16*)logits, ld,
+                          valid < 0 ? 0 : valid, index_offset, pairs);
+}
+
+int vk_argmax_merge(const int* pairs, int n_ranks, int* out, int B, cudaStream_t stream) {
+    if (B <= 0 || n_ranks <= 0) return VK_EINVAL;
+    return (int)vk_launch(argmax_merge_kernel, dim3((B + 63) / 64), dim3(64), 0, stream, pairs, n_ranks, out, B);
+}
 
 int vk_embed(const int* tok, const void* embed, const void* w_mhc0, void* H, void* hn, int* engram_prev,
              int* engram_rows_out, const int* orders, int n_orders, int engram_rows, int B, int D, float eps,
@@ -509,29 +580,29 @@ int vk_embed(const int* tok, const void* embed, const void* w_mhc0, void* H, voi
 }
 
 int vk_mhc_mix_norm(const void* H, const void* hn, const void* w_dyn, const void* pre_s, const void* post_s,
-                    const void* res_s, const void* w_in, void* x_in, void* h, float* post, float* res, float* d_scratch,
-                    int B, int D, int iters, float eps, cudaStream_t stream) {
-    if (B <= 0 || D <= 0 || D % 8 != 0 || d_scratch == nullptr) return VK_EINVAL;
+                    const void* res_s, const void* w_in, void* x_in, void* h, void* xrec_h, float* post, float* res,
+                    float* d_scratch, int B, int D, int iters, float eps, cudaStream_t stream) {
+    if (B <= 0 || D <= 0 || D % 8 != 0 || d_scratch == nullptr || (xrec_h != nullptr && (D % 64 != 0 || B > 16))) return VK_EINVAL;
     VK_CUDA(vk_launch(mhc_dyn_kernel, dim3((B * 24 + 7) / 8), dim3(256), 0, stream, (const __nv_bfloat16*)hn,
                       (const __nv_bfloat16*)w_dyn, d_scratch, B, D));
     MixParams p = {(const __nv_bfloat16*)H, (const __nv_bfloat16*)hn, d_scratch,
                    (const __nv_bfloat16*)pre_s, (const __nv_bfloat16*)post_s, (const __nv_bfloat16*)res_s,
-                   (const __nv_bfloat16*)w_in, (__nv_bfloat16*)x_in, (__nv_bfloat16*)h, post, res, D, iters, eps};
+                   (const __nv_bfloat16*)w_in, (__nv_bfloat16*)x_in, (__nv_bfloat16*)h, (uint8_t*)xrec_h, post, res, D, iters, eps};
     return (int)vk_launch(mhc_mix_norm_kernel, dim3(B), dim3(row_threads(D)), 0, stream, p);
 }
 
-int vk_add_rmsnorm(const void* x, const void* r, const void* w, void* h2, void* hn, int B, int D, float eps, int offset,
-                   cudaStream_t stream) {
-    if (B <= 0 || D <= 0 || D % 8 != 0) return VK_EINVAL;
+int vk_add_rmsnorm(const void* x, const void* r, const void* w, void* h2, void* hn, void* xrec_hn, int B, int D, float eps,
+                   int offset, cudaStream_t stream) {
+    if (B <= 0 || D <= 0 || D % 8 != 0 || (xrec_hn != nullptr && (D % 64 != 0 || B > 16))) return VK_EINVAL;
     return (int)vk_launch(add_rmsnorm_kernel, dim3(B), dim3(row_threads(D)), 0, stream, (const __nv_bfloat16*)x,
-                          (const __nv_bfloat16*)r, (const __nv_bfloat16*)w, (__nv_bfloat16*)h2, (__nv_bfloat16*)hn, D, eps,
-                          offset ? 1.f : 0.f);
+                          (const __nv_bfloat16*)r, (const __nv_bfloat16*)w, (__nv_bfloat16*)h2, (__nv_bfloat16*)hn,
+                          (uint8_t*)xrec_hn, D, eps, offset ? 1.f : 0.f);
 }
 
-int vk_silu_mul(const void* gu, void* act, int B, int I, int ld_gu, cudaStream_t stream) {
-    if (B <= 0 || I <= 0) return VK_EINVAL;
-    return (int)vk_launch(silu_mul_kernel, dim3((I + 255) / 256, B), dim3(256), 0, stream, (const __nv_bfloat16*)gu,
-                          (__nv_bfloat16*)act, I, ld_gu);
+int vk_silu_mul(const void* gu, void* act, void* xrec_act, int B, int I, int ld_gu, cudaStream_t stream) {
+    if (B <= 0 || I <= 0 || I % 64 != 0 || ld_gu % 8 != 0 || (xrec_act != nullptr && B > 16)) return VK_EINVAL;
+    return (int)vk_launch(silu_mul_kernel, dim3((I / 8 + 255) / 256, B), dim3(256), 0, stream, (const __nv_bfloat16*)gu,
+                          (__nv_bfloat16*)act, (uint8_t*)xrec_act, I, ld_gu);
 }
 
 int vk_engram_gather(const void* const* tables, const int* ld_table, const int* col0, const int* rows, const void* w,

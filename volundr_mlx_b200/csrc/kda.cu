@@ -12,6 +12,7 @@
 //   out = bf16(w * (bf16(y) * rsqrt(mean bf16(y)^2 + eps)) * silu(z))
 // State layout: fp32 [slot, HV, Dv, Dk], row = value dim, Dk contiguous (volundr.py:406). Dk = Dv = 128.
 #include "common.cuh"
+#include "xrec.cuh"
 
 namespace {
 
@@ -31,6 +32,7 @@ struct KdaParams {
     size_t conv_stride;            // elements between the two buffers
     float* S;                      // [slots, HV, 128, 128]
     __nv_bfloat16* out;            // [B, HV*128]
+    uint8_t* xrec_out;             // null, or HV * 2 x records receiving out
     const float* g_override;       // null, or [B] multipliers: 1 keeps the step, 0 turns it into a no-op (verify replay)
     int ldp, off_z, off_fd, D, Hk, HV, rank;
     float eps;
@@ -162,7 +164,18 @@ __global__ void __launch_bounds__(128) kda_step_kernel(const KdaParams p) {
     const float ss = block_sum<4>(yb * yb, red);
     const float inv = rsqrtf(ss * (1.f / 128.f) + p.eps);
     const float z = bf2f(pr[p.off_z + hv * 128 + c]);
-    p.out[(size_t)b * p.HV * 128 + hv * 128 + c] = f2bf(((yb * inv) * bf2f(p.norm_w[c])) * (z / (1.f + expf(-z))));
+    const float ov = bfr(((yb * inv) * bf2f(p.norm_w[c])) * (z / (1.f + expf(-z))));
+    p.out[(size_t)b * p.HV * 128 + hv * 128 + c] = f2bf(ov);
+    if (p.xrec_out != nullptr) {
+        // this head fills two 64-column groups: element stores, group sums = warp xor tree, then warp 2g + warp 2g+1
+        const int kg = hv * 2 + (c >> 6);
+        *xrec_elem(p.xrec_out, kg, b, c & 63) = f2bf(ov);
+        const float ws = warp_sum(ov);
+        __syncthreads();
+        if (lane == 0) red[warp] = ws;
+        __syncthreads();
+        if ((c & 63) == 0) xrec_store_sum(p.xrec_out, kg, b, red[warp] + red[warp + 1]);
+    }
 }
 
 }  // namespace
@@ -171,14 +184,14 @@ extern "C" {
 
 int vk_kda_step(const void* proj, int ldp, int off_z, int off_fd, const void* h, const void* w_b, const void* w_fup,
                 const float* conv_w, const float* A_log, const float* dt_bias, const void* norm_w, void* conv,
-                const int* parity, size_t conv_stride, float* S, void* out, const float* g_override, int B, int D, int Hk,
-                int HV, int Dk, int Dv, int rank, float eps, cudaStream_t stream) {
+                const int* parity, size_t conv_stride, float* S, void* out, void* xrec_out, const float* g_override, int B,
+                int D, int Hk, int HV, int Dk, int Dv, int rank, float eps, cudaStream_t stream) {
     if (B <= 0 || Dk != 128 || Dv != 128 || Hk <= 0 || HV % Hk != 0 || rank <= 0 || rank > 256 || rank % 8 != 0 ||
-        D % 8 != 0 || parity == nullptr)
+        D % 8 != 0 || parity == nullptr || (xrec_out != nullptr && B > 16))
         return VK_EINVAL;
     KdaParams p = {(const __nv_bfloat16*)proj, (const __nv_bfloat16*)h, (const __nv_bfloat16*)w_b,
                    (const __nv_bfloat16*)w_fup, conv_w, A_log, dt_bias, (const __nv_bfloat16*)norm_w,
-                   (__nv_bfloat16*)conv, parity, conv_stride, S, (__nv_bfloat16*)out, g_override,
+                   (__nv_bfloat16*)conv, parity, conv_stride, S, (__nv_bfloat16*)out, (uint8_t*)xrec_out, g_override,
                    ldp, off_z, off_fd, D, Hk, HV, rank, eps};
     return (int)vk_launch(kda_step_kernel, dim3(HV, B), dim3(128), 0, stream, p);
 }

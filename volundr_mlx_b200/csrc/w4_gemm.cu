@@ -18,10 +18,12 @@
 // One step of the kernel = one (superblock, group) = 9216 contiguous bytes, fetched by one TMA bulk copy; the packed
 // size equals the algorithmic N*K/2 + N*(K/64)*4 bytes and no byte of it is read twice.
 //
-// Activation layout ("x records"). Per 64-column group one 2112-byte record: x[16 rows][64] bf16 with the eight
-// 16-byte pieces of a row xor-swizzled by (row & 7) (conflict-free ldmatrix), then the 16 row sums of the group in
-// fp32, ordered so that mma thread t finds its columns {2t, 2t+1, 8+2t, 9+2t} in one 16-byte read. vk_w4_gemm builds
-// the records from a row-major x with a small kernel.
+// Activation layout ("x records"). Per 64-column group one 2176-byte record: x[16 rows][64] bf16 with the eight
+// 16-byte pieces of a row xor-swizzled by (row & 7) (conflict-free ldmatrix), then per row two words holding the
+// group's row sum S split into two bf16 parts, S = S_hi + S_lo: word 0 = (-128 S_hi, S_hi), word 1 = (-128 S_lo, S_lo).
+// With the row's (scale, bias) word as A operand they are the B operand of one extra mma per group that adds
+// (bias - 128 scale) * S to the accumulator (every factor is an exact bf16, the products are exact in fp32).
+// vk_w4_gemm builds the records from a row-major x with a small kernel.
 //
 // Work split. total = superblocks * groups steps, in superblock-major order, dealt in equal contiguous ranges to
 // P persistent CTAs (two per SM). A CTA is one producer warp (TMA into an 8-stage ring: weights as soon as the CTA
@@ -31,19 +33,30 @@
 // scheduling and a row's result is the same for every M (the reference lists batch-variant matmuls as an open
 // problem, NOTES_BATCHED_SERVE.md:256-258).
 #include "common.cuh"
+#include "xrec.cuh"
 
 namespace {
 
-constexpr int kChunkBytes = 1152;
 constexpr int kBlocksPerSB = 8;                                 // 32-row blocks per superblock = consumer warps
 constexpr int kSBRows = 32 * kBlocksPerSB;                      // 256
-constexpr int kWStageBytes = kBlocksPerSB * kChunkBytes;        // 9216
-constexpr int kXRecBytes = 2112;                                // 16 x 64 bf16 + 16 fp32
-constexpr int kStageBytes = kWStageBytes + kXRecBytes;          // 11328
-constexpr int kStages = 8;
 constexpr int kThreads = 32 * (1 + kBlocksPerSB);               // 288
 constexpr size_t kCounterBytes = 16384;                         // arrival counters at the head of the workspace
-constexpr size_t kSmemBytes = (size_t)kStages * kStageBytes + 2 * kStages * 8;
+
+// Weight formats the kernel streams. 0: 4-bit codes + (scale, bias), 1152-byte chunks. 1: plain bf16 (the linears the
+// reference keeps unquantised, convert.py:16-17; the lm_head above all), 4096-byte chunks of 32 rows x 64 columns
+// stored [stripe 2][kstep 4][lane 32][4 u32] = the mma A fragments as they are loaded.
+template <int FMT> struct Fmt;
+template <> struct Fmt<0> {
+    static constexpr int kChunk = 1152, kStages = 8, kCtasPerSM = 2;
+    static constexpr int kWStage = kBlocksPerSB * kChunk, kStage = kWStage + kXRecBytes;
+};
+template <> struct Fmt<1> {
+    static constexpr int kChunk = 4096, kStages = 6, kCtasPerSM = 1;
+    static constexpr int kWStage = kBlocksPerSB * kChunk, kStage = kWStage + kXRecBytes;
+};
+template <int FMT> constexpr int wstage_bytes() { return Fmt<FMT>::kWStage; }
+template <int FMT> constexpr size_t smem_bytes() { return (size_t)Fmt<FMT>::kStages * Fmt<FMT>::kStage + 2 * Fmt<FMT>::kStages * 8; }
+constexpr int kChunkBytes = Fmt<0>::kChunk;
 
 struct W4Params {
     const uint8_t* wp;      // packed weights
@@ -91,10 +104,14 @@ __device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, 256;
 // the CTA whose range [c T / P, (c + 1) T / P) holds step t
 __device__ __forceinline__ int step_owner(long long t, long long T, int P) { return (int)(((t + 1) * P - 1) / T); }
 
-template <int MT>
-__global__ void __launch_bounds__(kThreads, 2) w4_gemm_kernel(const W4Params p) {
+template <int MT, int FMT>
+__global__ void __launch_bounds__(kThreads, Fmt<FMT>::kCtasPerSM) w4_gemm_kernel(const W4Params p) {
     extern __shared__ __align__(128) uint8_t smem[];
     constexpr int MR = MT * 8;
+    constexpr int kStages = Fmt<FMT>::kStages;
+    constexpr int kStageBytes = Fmt<FMT>::kStage;
+    constexpr int kWStageBytes = Fmt<FMT>::kWStage;
+    constexpr int kChunkB = Fmt<FMT>::kChunk;
     uint64_t* full = reinterpret_cast<uint64_t*>(smem + (size_t)kStages * kStageBytes);
     uint64_t* empty = full + kStages;
     __shared__ int s_last;
@@ -194,12 +211,26 @@ __global__ void __launch_bounds__(kThreads, 2) w4_gemm_kernel(const W4Params p) 
                     float sum[MR];
 #pragma unroll
                     for (int m = 0; m < MR; m++) sum[m] = 0.f;
-                    for (int c = 0; c < ncontrib; c++) {
-                        const float4* q4 = reinterpret_cast<const float4*>(src + (size_t)c * kSBRows * 16);
+                    // contributions are fetched several at a time (all loads in flight together) and added in range order
+                    constexpr int kBatch = 16 / (MR / 4);
+                    for (int c0 = 0; c0 < ncontrib; c0 += kBatch) {
+                        float4 buf[kBatch][MR / 4];
 #pragma unroll
-                        for (int v = 0; v < MR / 4; v++) {
-                            const float4 x = __ldcg(q4 + v);
-                            sum[4 * v] += x.x; sum[4 * v + 1] += x.y; sum[4 * v + 2] += x.z; sum[4 * v + 3] += x.w;
+                        for (int u = 0; u < kBatch; u++) {
+                            const float4* q4 = reinterpret_cast<const float4*>(src + (size_t)(c0 + u) * kSBRows * 16);
+#pragma unroll
+                            for (int v = 0; v < MR / 4; v++)
+                                buf[u][v] = (c0 + u < ncontrib) ? __ldcg(q4 + v) : make_float4(0.f, 0.f, 0.f, 0.f);
+                        }
+#pragma unroll
+                        for (int u = 0; u < kBatch; u++) {
+                            if (c0 + u < ncontrib) {
+#pragma unroll
+                                for (int v = 0; v < MR / 4; v++) {
+                                    sum[4 * v] += buf[u][v].x; sum[4 * v + 1] += buf[u][v].y;
+                                    sum[4 * v + 2] += buf[u][v].z; sum[4 * v + 3] += buf[u][v].w;
+                                }
+                            }
                         }
                     }
 #pragma unroll
@@ -235,12 +266,36 @@ __global__ void __launch_bounds__(kThreads, 2) w4_gemm_kernel(const W4Params p) 
         const int st = i % kStages;
         if (!mbar_wait(&full[st], (i / kStages) & 1)) { ok = false; break; }
         const uint8_t* stage = smem + (size_t)st * kStageBytes;
-        const uint8_t* ch = stage + j * kChunkBytes;
+        const uint8_t* ch = stage + j * kChunkB;
         const uint8_t* xr = stage + kWStageBytes;
+        const uint32_t xrow = smem_u32(xr) + lm_row * 128;
+        if constexpr (FMT == 1) {
+            // plain bf16 weights: fragments as stored, accumulate straight into acc
+#pragma unroll
+            for (int q = 0; q < 4; q++) {
+                uint32_t b[2 * MT];
+                const uint32_t addr = xrow + (uint32_t)(((2 * q + lm_half) ^ lm_r) << 4);
+                if constexpr (MT == 2) {
+                    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                                 : "=r"(b[0]), "=r"(b[1]), "=r"(b[2]), "=r"(b[3])
+                                 : "r"(addr));
+                } else {
+                    asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];" : "=r"(b[0]), "=r"(b[1]) : "r"(addr));
+                }
+#pragma unroll
+                for (int s = 0; s < 2; s++) {
+                    const uint4 av = *reinterpret_cast<const uint4*>(ch + ((s * 4 + q) * 32 + lane) * 16);
+                    const uint32_t a[4] = {av.x, av.y, av.z, av.w};
+#pragma unroll
+                    for (int jj = 0; jj < MT; jj++) mma_bf16(acc[s][jj], a, b[2 * jj], b[2 * jj + 1]);
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&empty[st]);
+        } else {
         const uint4 w0 = *reinterpret_cast<const uint4*>(ch + lane * 16);
         const uint4 w1 = *reinterpret_cast<const uint4*>(ch + 512 + lane * 16);
         const uint4 sb4 = *reinterpret_cast<const uint4*>(ch + 1024 + g * 16);
-        const uint32_t xrow = smem_u32(xr) + lm_row * 128;
         float d[2][MT][4];
         const uint32_t wq0[4] = {w0.x, w0.y, w0.z, w0.w};
         const uint32_t wq1[4] = {w1.x, w1.y, w1.z, w1.w};
@@ -269,29 +324,29 @@ __global__ void __launch_bounds__(kThreads, 2) w4_gemm_kernel(const W4Params p) 
                 else mma_bf16(d[1][jj], a, b[2 * jj], b[2 * jj + 1]);
             }
         }
-        // group epilogue: acc += s * (D - 128 sum x) + b * sum x = s * D + (b - 128 s) * sum x
-        float sx[MT][2];
-        if constexpr (MT == 2) {
-            const float4 v = *reinterpret_cast<const float4*>(xr + 2048 + t * 16);
-            sx[0][0] = v.x; sx[0][1] = v.y; sx[1][0] = v.z; sx[1][1] = v.w;
-        } else {
-            const float2 v = *reinterpret_cast<const float2*>(xr + 2048 + t * 16);
-            sx[0][0] = v.x; sx[0][1] = v.y;
-        }
+        // group epilogue: acc += s * (D - 128 S) + b * S = s * D + (b - 128 s) * S. The second term goes through one
+        // more mma: A = the rows' (scale, bias) words in columns 0..3, B = (-128 S_hi, S_hi, -128 S_lo, S_lo).
         const uint32_t sbw[4] = {sb4.x, sb4.y, sb4.z, sb4.w};
+        uint32_t bw[MT];
+#pragma unroll
+        for (int jj = 0; jj < MT; jj++)
+            bw[jj] = t < 2 ? *reinterpret_cast<const uint32_t*>(xr + 2048 + (jj * 8 + g) * 8 + t * 4) : 0u;
         __syncwarp();
         if (lane == 0) mbar_arrive(&empty[st]);   // everything of this stage is in registers now
 #pragma unroll
         for (int s = 0; s < 2; s++) {
-            const float s0 = bf_lo(sbw[2 * s]), c0 = fmaf(-128.f, s0, bf_hi(sbw[2 * s]));
-            const float s1 = bf_lo(sbw[2 * s + 1]), c1 = fmaf(-128.f, s1, bf_hi(sbw[2 * s + 1]));
+            const float s0 = bf_lo(sbw[2 * s]), s1 = bf_lo(sbw[2 * s + 1]);
 #pragma unroll
             for (int jj = 0; jj < MT; jj++) {
-                acc[s][jj][0] = fmaf(c0, sx[jj][0], fmaf(s0, d[s][jj][0], acc[s][jj][0]));
-                acc[s][jj][1] = fmaf(c0, sx[jj][1], fmaf(s0, d[s][jj][1], acc[s][jj][1]));
-                acc[s][jj][2] = fmaf(c1, sx[jj][0], fmaf(s1, d[s][jj][2], acc[s][jj][2]));
-                acc[s][jj][3] = fmaf(c1, sx[jj][1], fmaf(s1, d[s][jj][3], acc[s][jj][3]));
+                acc[s][jj][0] = fmaf(s0, d[s][jj][0], acc[s][jj][0]);
+                acc[s][jj][1] = fmaf(s0, d[s][jj][1], acc[s][jj][1]);
+                acc[s][jj][2] = fmaf(s1, d[s][jj][2], acc[s][jj][2]);
+                acc[s][jj][3] = fmaf(s1, d[s][jj][3], acc[s][jj][3]);
             }
+            const uint32_t ab[4] = {t < 2 ? sbw[2 * s] : 0u, t < 2 ? sbw[2 * s + 1] : 0u, 0u, 0u};
+#pragma unroll
+            for (int jj = 0; jj < MT; jj++) mma_bf16(acc[s][jj], ab, bw[jj], 0u);
+        }
         }
         if (++kg == p.G) {
             flush(sb, seg_kg0, p.G);
@@ -313,14 +368,8 @@ __global__ void __launch_bounds__(128) w4_xrec_kernel(const __nv_bfloat16* __res
     const int kg = blockIdx.x, m = threadIdx.x >> 3, c = threadIdx.x & 7;
     uint4 v = make_uint4(0, 0, 0, 0);
     if (m < M) v = *reinterpret_cast<const uint4*>(x + (size_t)m * ldx + kg * 64 + c * 8);
-    uint8_t* rec = xrec + (size_t)kg * kXRecBytes;
-    *reinterpret_cast<uint4*>(rec + m * 128 + ((c ^ (m & 7)) << 4)) = v;
-    float s = bf_lo(v.x); s += bf_hi(v.x); s += bf_lo(v.y); s += bf_hi(v.y);
-    s += bf_lo(v.z); s += bf_hi(v.z); s += bf_lo(v.w); s += bf_hi(v.w);
-    s += __shfl_xor_sync(0xffffffffu, s, 1);
-    s += __shfl_xor_sync(0xffffffffu, s, 2);
-    s += __shfl_xor_sync(0xffffffffu, s, 4);
-    if (c == 0) reinterpret_cast<float*>(rec + 2048)[((m & 7) >> 1) * 4 + (m >> 3) * 2 + (m & 1)] = s;
+    float f[8] = {bf_lo(v.x), bf_hi(v.x), bf_lo(v.y), bf_hi(v.y), bf_lo(v.z), bf_hi(v.z), bf_lo(v.w), bf_hi(v.w)};
+    xrec_store_row_piece(xrec, m, kg * 8 + c, f);
 }
 
 // ------------------------------------------------------------------------------------------------ repack / dequant
@@ -391,6 +440,26 @@ __global__ void w4_dequant_kernel(const uint32_t* __restrict__ w, const __nv_bfl
     *reinterpret_cast<uint4*>(out + (size_t)n * K + (size_t)wi * 8) = make_uint4(o[0], o[1], o[2], o[3]);
 }
 
+// row-major bf16 W [N, K] -> 4096-byte chunks in fragment order. One thread per u32 (two consecutive columns).
+__global__ void bf16_repack_kernel(const __nv_bfloat16* __restrict__ W, int N, int K, uint8_t* __restrict__ out, int NSB, int G) {
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t total = (size_t)NSB * G * kBlocksPerSB * 1024;
+    if (idx >= total) return;
+    const size_t chunk = idx >> 10;
+    const int wi = (int)(idx & 1023);
+    const int jb = (int)(chunk % kBlocksPerSB);
+    const size_t step = chunk / kBlocksPerSB;
+    const int sbk = (int)(step / G), kg = (int)(step - (size_t)sbk * G);
+    const int nb = sbk * kBlocksPerSB + jb;
+    const int i = wi & 3, lane = (wi >> 2) & 31, q = (wi >> 7) & 3, s = wi >> 9;
+    const int g = lane >> 2, t = lane & 3;
+    const int r = nb * 32 + s * 16 + g + (i & 1) * 8;
+    const int c = kg * 64 + q * 16 + 2 * t + (i >> 1) * 8;
+    uint32_t v = 0;
+    if (r < N) v = *reinterpret_cast<const uint32_t*>(W + (size_t)r * K + c);
+    reinterpret_cast<uint32_t*>(out)[idx] = v;
+}
+
 int g_force_ctas = 0;
 
 struct W4Plan {
@@ -398,12 +467,12 @@ struct W4Plan {
     long long T;
 };
 
-W4Plan w4_plan(int N, int K) {
+W4Plan w4_plan(int N, int K, int ctas_per_sm = 2) {
     W4Plan pl;
     pl.NSB = (N + kSBRows - 1) / kSBRows;
     pl.G = K / 64;
     pl.T = (long long)pl.NSB * pl.G;
-    int P = 2 * 148;                       // two CTAs per SM, all resident at once
+    int P = ctas_per_sm * 148;             // every CTA resident at once
     if (g_force_ctas > 0) P = g_force_ctas;
     if ((long long)P > pl.T) P = (int)pl.T;
     pl.P = P;
@@ -426,7 +495,7 @@ size_t w4_ws_bytes(const W4Plan& pl) {
 
 extern "C" {
 
-size_t vk_w4_packed_bytes(int N, int K) { return (size_t)((N + kSBRows - 1) / kSBRows) * (K / 64) * kWStageBytes; }
+size_t vk_w4_packed_bytes(int N, int K) { return (size_t)((N + kSBRows - 1) / kSBRows) * (K / 64) * wstage_bytes<0>(); }
 
 int vk_w4_repack(const void* w, const void* scales, const void* biases, int N, int K, int group, void* packed,
                  cudaStream_t stream) {
@@ -458,6 +527,34 @@ size_t vk_w4_workspace_bytes(int M, int N, int K) {
     return w4_ws_bytes(w4_plan(N, K));
 }
 
+// y = x . dequant(W)^T for activations already laid out as x records (K / 64 records of 2176 bytes, rows >= M zero):
+// what the fused producers of this library write. M <= 16.
+int vk_w4_gemm_xrec(const void* packed, const void* xrec, void* y, int ldy, int M, int N, int K, void* workspace,
+                    size_t workspace_bytes, cudaStream_t stream) {
+    if (M <= 0 || M > 16 || N <= 0 || K <= 0 || K % 64 != 0 || ldy < N) return VK_EINVAL;
+    if (((uintptr_t)xrec & 15) || ((uintptr_t)packed & 15) || workspace == nullptr || ((uintptr_t)workspace & 15)) return VK_EINVAL;
+    const W4Plan pl = w4_plan(N, K);
+    if (pl.NSB > (int)(kCounterBytes / 4)) return VK_EINVAL;
+    if (workspace_bytes < w4_ws_bytes(pl)) return VK_ENOSPC;
+    static bool configured = false;
+    if (!configured) {
+        VK_CUDA(cudaFuncSetAttribute(w4_gemm_kernel<1, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes<0>()));
+        VK_CUDA(cudaFuncSetAttribute(w4_gemm_kernel<2, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes<0>()));
+        configured = true;
+    }
+    uint8_t* ws = (uint8_t*)workspace;
+    W4Params p;
+    p.wp = (const uint8_t*)packed;
+    p.xrec = (const uint8_t*)xrec;
+    p.y = (__nv_bfloat16*)y;
+    p.counters = (int*)ws;
+    p.part = (float*)(ws + kCounterBytes + (size_t)pl.G * kXRecBytes);
+    p.T = pl.T; p.M = M; p.N = N; p.NSB = pl.NSB; p.G = pl.G; p.P = pl.P; p.ldy = ldy; p.maxc = pl.maxc;
+    cudaError_t e = M <= 8 ? vk_launch(w4_gemm_kernel<1, 0>, dim3(pl.P), dim3(kThreads), smem_bytes<0>(), stream, p)
+                           : vk_launch(w4_gemm_kernel<2, 0>, dim3(pl.P), dim3(kThreads), smem_bytes<0>(), stream, p);
+    return (int)e;
+}
+
 int vk_w4_gemm(const void* packed, const void* x, int ldx, void* y, int ldy, int M, int N, int K, void* workspace,
                size_t workspace_bytes, cudaStream_t stream) {
     if (M <= 0 || N <= 0 || K <= 0 || K % 64 != 0 || ldx % 8 != 0 || ldx < K || ldy < N) return VK_EINVAL;
@@ -467,8 +564,8 @@ int vk_w4_gemm(const void* packed, const void* x, int ldx, void* y, int ldy, int
     if (workspace_bytes < w4_ws_bytes(pl)) return VK_ENOSPC;
     static bool configured = false;
     if (!configured) {
-        VK_CUDA(cudaFuncSetAttribute(w4_gemm_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes));
-        VK_CUDA(cudaFuncSetAttribute(w4_gemm_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes));
+        VK_CUDA(cudaFuncSetAttribute(w4_gemm_kernel<1, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes<0>()));
+        VK_CUDA(cudaFuncSetAttribute(w4_gemm_kernel<2, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes<0>()));
         configured = true;
     }
     uint8_t* ws = (uint8_t*)workspace;
@@ -484,8 +581,57 @@ int vk_w4_gemm(const void* packed, const void* x, int ldx, void* y, int ldy, int
         p.T = pl.T; p.M = m; p.N = N; p.NSB = pl.NSB; p.G = pl.G; p.P = pl.P; p.ldy = ldy; p.maxc = pl.maxc;
         VK_CUDA(vk_launch(w4_xrec_kernel, dim3(pl.G), dim3(128), 0, stream, (const __nv_bfloat16*)x + (size_t)m0 * ldx, ldx, m,
                           ws + kCounterBytes));
-        cudaError_t e = m <= 8 ? vk_launch(w4_gemm_kernel<1>, dim3(pl.P), dim3(kThreads), kSmemBytes, stream, p)
-                               : vk_launch(w4_gemm_kernel<2>, dim3(pl.P), dim3(kThreads), kSmemBytes, stream, p);
+        cudaError_t e = m <= 8 ? vk_launch(w4_gemm_kernel<1, 0>, dim3(pl.P), dim3(kThreads), smem_bytes<0>(), stream, p)
+                               : vk_launch(w4_gemm_kernel<2, 0>, dim3(pl.P), dim3(kThreads), smem_bytes<0>(), stream, p);
+        if (e != cudaSuccess) return (int)e;
+    }
+    return VK_OK;
+}
+
+// ---- the same streaming kernel over plain bf16 weights (lm_head and the other unquantised linears)
+size_t vk_bf16_packed_bytes(int N, int K) { return (size_t)((N + kSBRows - 1) / kSBRows) * (K / 64) * wstage_bytes<1>(); }
+
+int vk_bf16_repack(const void* W, int N, int K, void* packed, cudaStream_t stream) {
+    if (N <= 0 || K <= 0 || K % 64 != 0) return VK_EINVAL;
+    const int NSB = (N + kSBRows - 1) / kSBRows, G = K / 64;
+    const size_t total = (size_t)NSB * G * kBlocksPerSB * 1024;
+    bf16_repack_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>((const __nv_bfloat16*)W, N, K, (uint8_t*)packed, NSB, G);
+    return (int)cudaGetLastError();
+}
+
+size_t vk_bf16_workspace_bytes(int M, int N, int K) {
+    (void)M;
+    if (N <= 0 || K <= 0 || K % 64 != 0) return 0;
+    return w4_ws_bytes(w4_plan(N, K, Fmt<1>::kCtasPerSM));
+}
+
+int vk_bf16_gemm_packed(const void* packed, const void* x, int ldx, void* y, int ldy, int M, int N, int K, void* workspace,
+                        size_t workspace_bytes, cudaStream_t stream) {
+    if (M <= 0 || N <= 0 || K <= 0 || K % 64 != 0 || ldx % 8 != 0 || ldx < K || ldy < N) return VK_EINVAL;
+    if (((uintptr_t)x & 15) || ((uintptr_t)packed & 15) || workspace == nullptr || ((uintptr_t)workspace & 15)) return VK_EINVAL;
+    const W4Plan pl = w4_plan(N, K, Fmt<1>::kCtasPerSM);
+    if (pl.NSB > (int)(kCounterBytes / 4)) return VK_EINVAL;
+    if (workspace_bytes < w4_ws_bytes(pl)) return VK_ENOSPC;
+    static bool configured = false;
+    if (!configured) {
+        VK_CUDA(cudaFuncSetAttribute(w4_gemm_kernel<1, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes<1>()));
+        VK_CUDA(cudaFuncSetAttribute(w4_gemm_kernel<2, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes<1>()));
+        configured = true;
+    }
+    uint8_t* ws = (uint8_t*)workspace;
+    for (int m0 = 0; m0 < M; m0 += 16) {
+        const int m = M - m0 < 16 ? M - m0 : 16;
+        W4Params p;
+        p.wp = (const uint8_t*)packed;
+        p.xrec = ws + kCounterBytes;
+        p.y = (__nv_bfloat16*)y + (size_t)m0 * ldy;
+        p.counters = (int*)ws;
+        p.part = (float*)(ws + kCounterBytes + (size_t)pl.G * kXRecBytes);
+        p.T = pl.T; p.M = m; p.N = N; p.NSB = pl.NSB; p.G = pl.G; p.P = pl.P; p.ldy = ldy; p.maxc = pl.maxc;
+        VK_CUDA(vk_launch(w4_xrec_kernel, dim3(pl.G), dim3(128), 0, stream, (const __nv_bfloat16*)x + (size_t)m0 * ldx, ldx, m,
+                          ws + kCounterBytes));
+        cudaError_t e = m <= 8 ? vk_launch(w4_gemm_kernel<1, 1>, dim3(pl.P), dim3(kThreads), smem_bytes<1>(), stream, p)
+                               : vk_launch(w4_gemm_kernel<2, 1>, dim3(pl.P), dim3(kThreads), smem_bytes<1>(), stream, p);
         if (e != cudaSuccess) return (int)e;
     }
     return VK_OK;

@@ -1,0 +1,41 @@
+// The activation layout the streaming GEMM reads ("x records"): per 64-column group one 2176-byte record,
+//   bytes 0..2047    x[16 rows][64] bf16, the eight 16-byte pieces of a row xor-swizzled by (row & 7),
+//   bytes 2048..2175 per row two words from the group's row sum S = S_hi + S_lo (two bf16 parts):
+//                    word 0 = (-128 S_hi, S_hi), word 1 = (-128 S_lo, S_lo).
+// Kernels that produce a GEMM input write their rows straight into records with these helpers (the reference fuses
+// the same preparation into its producers: agens-mlx-bench/smallm/prep_nax.py:24-148). Rows a batch does not use
+// must hold zeros.
+#pragma once
+#include "common.cuh"
+
+constexpr int kXRecBytes = 2176;
+
+// 16-byte piece `c` (0..7) of row m in group kg
+__device__ __forceinline__ uint8_t* xrec_piece(uint8_t* xrec, int kg, int m, int c) {
+    return xrec + (size_t)kg * kXRecBytes + m * 128 + ((c ^ (m & 7)) << 4);
+}
+// element k (0..63) of row m in group kg
+__device__ __forceinline__ __nv_bfloat16* xrec_elem(uint8_t* xrec, int kg, int m, int k) {
+    return reinterpret_cast<__nv_bfloat16*>(xrec_piece(xrec, kg, m, k >> 3)) + (k & 7);
+}
+__device__ __forceinline__ void xrec_store_sum(uint8_t* xrec, int kg, int m, float s) {
+    const float hi = bfr(s), lo = bfr(s - hi);
+    uint2 w;
+    w.x = pack_bf2(-128.f * hi, hi);
+    w.y = pack_bf2(-128.f * lo, lo);
+    *reinterpret_cast<uint2*>(xrec + (size_t)kg * kXRecBytes + 2048 + m * 8) = w;
+}
+// Eight consecutive lanes hold the eight pieces of one (row, group): each lane's 8 values are added in order, then an
+// xor tree over the lanes; the lane of piece 0 stores the sum words.
+__device__ __forceinline__ void xrec_store_row_piece(uint8_t* xrec, int m, int piece_index, const float (&v)[8]) {
+    const int kg = piece_index >> 3, c = piece_index & 7;
+    uint4 u;
+    u.x = pack_bf2(v[0], v[1]); u.y = pack_bf2(v[2], v[3]); u.z = pack_bf2(v[4], v[5]); u.w = pack_bf2(v[6], v[7]);
+    *reinterpret_cast<uint4*>(xrec_piece(xrec, kg, m, c)) = u;
+    float s = bf_lo(u.x); s += bf_hi(u.x); s += bf_lo(u.y); s += bf_hi(u.y);
+    s += bf_lo(u.z); s += bf_hi(u.z); s += bf_lo(u.w); s += bf_hi(u.w);
+    s += __shfl_xor_sync(0xffffffffu, s, 1);
+    s += __shfl_xor_sync(0xffffffffu, s, 2);
+    s += __shfl_xor_sync(0xffffffffu, s, 4);
+    if (c == 0) xrec_store_sum(xrec, kg, m, s);
+}

@@ -74,6 +74,39 @@ def w4_gemm(x, wt: W4Weight, out=None):
     return out
 
 
+class BF16Weight:
+    """A bf16 weight [N, K] in the streaming kernel's fragment order (4096-byte chunks of 32 rows x 64 columns)."""
+
+    def __init__(self, packed, N, K):
+        self.packed, self.N, self.K = packed, N, K
+
+    @property
+    def nbytes(self):
+        return self.packed.numel()
+
+
+def bf16_repack(W) -> BF16Weight:
+    L = _lib.lib()
+    N, K = W.shape
+    assert W.dtype == BF16 and W.is_contiguous()
+    packed = torch.empty(L.vk_bf16_packed_bytes(N, K), dtype=torch.uint8, device=W.device)
+    _lib.check(L.vk_bf16_repack(_p(W), N, K, _p(packed), _stream()), "vk_bf16_repack")
+    return BF16Weight(packed, N, K)
+
+
+def bf16_gemm(x, wt: BF16Weight, out=None):
+    """y[M, N] = x[M, K] . W^T for a repacked bf16 weight."""
+    L = _lib.lib()
+    assert x.dtype == BF16 and x.dim() == 2 and x.shape[1] == wt.K and x.stride(1) == 1
+    M = x.shape[0]
+    if out is None:
+        out = torch.empty((M, wt.N), dtype=BF16, device=x.device)
+    ws = workspace(L.vk_bf16_workspace_bytes(min(M, 16), wt.N, wt.K), x.device)
+    _lib.check(L.vk_bf16_gemm_packed(_p(wt.packed), _p(x), x.stride(0), _p(out), out.stride(0), M, wt.N, wt.K, _p(ws),
+                                     ws.numel(), _stream()), "vk_bf16_gemm_packed")
+    return out
+
+
 _status_buf = {}
 
 

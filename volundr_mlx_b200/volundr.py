@@ -15,7 +15,7 @@ import math
 import numpy as np
 import torch
 
-from . import _lib, ops
+from . import _lib, ops, sharding
 from .synth import ModelArgs
 
 BF16 = torch.bfloat16
@@ -176,17 +176,20 @@ class Model:
         r, n = tp_rank, tp_size
         assert a.head_dim == 128 and a.linear_key_head_dim == 128 and a.linear_value_head_dim == 128, \
             "the CUDA kernels take 128-wide heads"
-        assert a.num_key_value_heads % n == 0 and a.linear_num_key_heads % n == 0 and a.intermediate_size % (64 * n) == 0
+        sharding.check(a, n)
+        ix = lambda v: torch.from_numpy(np.asarray(v)).to(d)  # index array -> device
         Hq, KVH, D = a.num_attention_heads // n, a.num_key_value_heads // n, a.head_dim
         Hk, HV = a.linear_num_key_heads // n, a.linear_num_value_heads // n
         self.Hq, self.KVH, self.Hk, self.HV = Hq, KVH, Hk, HV
         self.I = a.intermediate_size // n
-        sl = lambda per, cnt: slice(r * cnt * per, (r + 1) * cnt * per)  # this rank's rows: cnt units of `per`
         self.embed = _t(params["model.embed_tokens.weight"], d, BF16)
         self.norm_w = _t(params["model.norm.weight"], d, BF16)
-        V = a.vocab_size
-        assert V % n == 0
-        self.lm_head = _t(params["lm_head.weight"], d, BF16)[r * (V // n):(r + 1) * (V // n)].contiguous()
+        v0, v1 = sharding.vocab_rows(a, r, n)
+        self.vocab0 = v0
+        head = _t(params["lm_head.weight"], d, BF16)[v0:v1].contiguous()
+        self.vocab_shard = head.shape[0]
+        self.lm_head = ops.bf16_repack(head) if a.hidden_size % 64 == 0 else head  # streaming layout (tensor cores)
+        del head
         self.layers = []
         self.engram_table = None
         for i, m in enumerate(a.mixer_types):
@@ -201,30 +204,25 @@ class Model:
             w["ln_post"] = _t(params[L + "post_attention_layernorm.weight"], d, BF16)
             if m == "kda":
                 P = L + "linear_attn."
-                KD_full = a.linear_num_key_heads * 128
-                qkv = _W4.get(params, P + "in_proj_qkv", d)
-                parts = [qkv.rows(sl(128, Hk)),                                    # q heads of this rank
-                         qkv.rows(slice(KD_full + r * Hk * 128, KD_full + (r + 1) * Hk * 128)),
-                         qkv.rows(slice(2 * KD_full + r * HV * 128, 2 * KD_full + (r + 1) * HV * 128)),
-                         _W4.get(params, P + "in_proj_z", d).rows(sl(128, HV)),
+                sh = sharding.kda_rows(a, r, n)
+                parts = [_W4.get(params, P + "in_proj_qkv", d).rows(ix(sh["qkv"])),   # q | k | v heads of this rank
+                         _W4.get(params, P + "in_proj_z", d).rows(ix(sh["z"])),
                          _W4.get(params, P + "f_down", d)]
                 w["proj"] = _W4.cat(parts).to_device(d, g)
                 w["off_z"] = 2 * Hk * 128 + HV * 128
                 w["off_fd"] = w["off_z"] + HV * 128
-                w["in_proj_b"] = _t(params[P + "in_proj_b.weight"], d, BF16)[r * HV:(r + 1) * HV].contiguous()
-                w["f_up"] = _t(params[P + "f_up.weight"], d, BF16)[sl(128, HV)].contiguous()
-                cw = _t(params[P + "conv1d.weight"], d, torch.float32)
-                cidx = np.r_[np.arange(KD_full)[sl(128, Hk)], KD_full + np.arange(KD_full)[sl(128, Hk)],
-                             2 * KD_full + np.arange(a.linear_num_value_heads * 128)[sl(128, HV)]]
-                w["conv_w"] = cw[torch.from_numpy(cidx).to(d)].contiguous()
-                w["A_log"] = _t(params[P + "A_log"], d, torch.float32)[r * HV:(r + 1) * HV].contiguous()
-                w["dt_bias"] = _t(params[P + "dt_bias"], d, torch.float32)[sl(128, HV)].contiguous()
+                w["in_proj_b"] = _t(params[P + "in_proj_b.weight"], d, BF16)[ix(sh["b"])].contiguous()
+                w["f_up"] = _t(params[P + "f_up.weight"], d, BF16)[ix(sh["f_up"])].contiguous()
+                w["conv_w"] = _t(params[P + "conv1d.weight"], d, torch.float32)[ix(sh["qkv"])].contiguous()
+                w["A_log"] = _t(params[P + "A_log"], d, torch.float32)[ix(sh["b"])].contiguous()
+                w["dt_bias"] = _t(params[P + "dt_bias"], d, torch.float32)[ix(sh["f_up"])].contiguous()
                 w["gnorm"] = _t(params[P + "norm.weight"], d, BF16)
-                w["out"] = _W4.get(params, P + "out_proj", d).cols(r * HV * 128, (r + 1) * HV * 128, g).to_device(d, g)
+                w["out"] = _W4.get(params, P + "out_proj", d).cols(*sh["out_cols"], g).to_device(d, g)
             else:
                 P = L + "self_attn."
-                parts = [_W4.get(params, P + "q_proj", d).rows(sl(2 * D, Hq)),
-                         _W4.get(params, P + "k_proj", d).rows(sl(D, KVH)), _W4.get(params, P + "v_proj", d).rows(sl(D, KVH))]
+                sh = sharding.attn_rows(a, r, n)
+                parts = [_W4.get(params, P + "q_proj", d).rows(ix(sh["q"])),
+                         _W4.get(params, P + "k_proj", d).rows(ix(sh["k"])), _W4.get(params, P + "v_proj", d).rows(ix(sh["v"]))]
                 w["proj"] = _W4.cat(parts).to_device(d, g)
                 w["off_k"] = Hq * 2 * D
                 w["off_v"] = w["off_k"] + KVH * D
@@ -234,11 +232,11 @@ class Model:
                     w["idx_q"] = _t(params[P + "idx_q.weight"], d, BF16)
                     w["idx_k"] = _t(params[P + "idx_k.weight"], d, BF16)
                     w["idx_norm"] = _t(params[P + "idx_norm.weight"], d, BF16)
-                w["out"] = _W4.get(params, P + "o_proj", d).cols(r * Hq * D, (r + 1) * Hq * D, g).to_device(d, g)
-            I = a.intermediate_size
+                w["out"] = _W4.get(params, P + "o_proj", d).cols(*sh["o_cols"], g).to_device(d, g)
+            sm = sharding.mlp_rows(a, r, n)
             gate, up = _W4.get(params, L + "mlp.gate_proj", d), _W4.get(params, L + "mlp.up_proj", d)
-            w["gate_up"] = _W4.cat([gate.rows(sl(1, self.I)), up.rows(sl(1, self.I))]).to_device(d, g)
-            w["down"] = _W4.get(params, L + "mlp.down_proj", d).cols(r * self.I, (r + 1) * self.I, g).to_device(d, g)
+            w["gate_up"] = _W4.cat([gate.rows(ix(sm["gate"])), up.rows(ix(sm["up"]))]).to_device(d, g)
+            w["down"] = _W4.get(params, L + "mlp.down_proj", d).cols(*sm["down_cols"], g).to_device(d, g)
             if i in a.engram_layers:
                 E = L + "engram."
                 cat = a.engram_dim * len(a.engram_orders)
@@ -265,7 +263,7 @@ class Model:
 
     def weight_bytes(self):
         """Bytes of parameters one decode step streams (4-bit weights in their packed layout, bf16 linears, lm_head)."""
-        n = self.lm_head.numel() * 2
+        n = self.vocab_shard * self.args.hidden_size * 2
         for w in self.layers:
             for k, v in w.items():
                 if isinstance(v, ops.W4Weight):
