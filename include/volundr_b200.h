@@ -97,6 +97,13 @@ int vk_engram_gather(const void* const* tables, const int* ld_table, const int* 
 int vk_mhc_combine_norm(void* H, const void* h2, const void* m, const void* x_in, const float* post, const float* res,
                         const void* w_next, void* hn, const void* eng_val, const void* eng_gate_w, const void* eng_gate_b,
                         void* y_out, int B, int D, int final_norm, float eps, vk_stream_t stream);
+/* vk_mhc_combine_norm of layer i and vk_mhc_mix_norm of layer i + 1 in one launch (VolundrModel._fused_layers runs them
+ * back to back, volundr.py:945-948): H, x_in, post, res are updated in place for the next layer; h / xrec_h receive its
+ * input norm. Same values as the two separate calls. D / 8 <= 768. */
+int vk_mhc_boundary(void* H, const void* h2, const void* m, void* x_in, float* post, float* res, const void* w_next,
+                    const void* eng_val, const void* eng_gate_w, const void* eng_gate_b, const void* w_dyn, const void* pre_s,
+                    const void* post_s, const void* res_s, const void* w_in, void* h, void* xrec_h, int B, int D, int iters,
+                    float eps, vk_stream_t stream);
 /* The linears kept in bf16 (convert.py:16-17): y = bf16(x . W^T + bias), W [N, K] row-major. */
 int vk_bf16_gemm(const void* x, int ldx, const void* W, const void* bias, void* y, int ldy, int M, int N, int K,
                  vk_stream_t stream);

@@ -88,3 +88,25 @@ def test_graph_replay_equals_eager(cuda):
             res.append(lg.clone())
         outs.append(torch.stack(res))
     assert torch.equal(outs[0], outs[1])
+
+
+def test_fused_layer_boundary_equals_separate_kernels(cuda):
+    """combine(i) + mix(i + 1) in one kernel gives the same logits, bit for bit, as the separate kernels."""
+    from volundr_mlx_b200 import batch as BT
+    from volundr_mlx_b200.volundr import Model
+
+    args = synth.small_args()
+    params = synth.make_params(args, seed=6)
+    model = Model(args, params, cuda)
+    outs = []
+    for fuse in (True, False):
+        bc = model.make_cache(max_rows=4, n_pages=32, max_pages_per_row=4)
+        bc.fuse_boundary = fuse
+        bc.apply(join=["a", "b", "c"])
+        rng = np.random.default_rng(1)
+        res = []
+        for t in range(30):
+            lg, _ = BT.forward(model, bc, rng.integers(0, args.vocab_valid, size=3).tolist())
+            res.append(lg.clone())
+        outs.append(torch.stack(res))
+    assert torch.equal(outs[0], outs[1])

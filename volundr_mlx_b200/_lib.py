@@ -32,6 +32,7 @@ SIGNATURES = {
     "vk_silu_mul": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
     "vk_engram_gather": (c_int, [c_void_p] * 6 + [c_int, c_int, c_int, c_float, c_void_p]),
     "vk_mhc_combine_norm": (c_int, [c_void_p] * 12 + [c_int, c_int, c_int, c_float, c_void_p]),
+    "vk_mhc_boundary": (c_int, [c_void_p] * 17 + [c_int, c_int, c_int, c_float, c_void_p]),
     "vk_bf16_gemm": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]),
     "vk_argmax": (c_int, [c_void_p, c_int, c_int, c_void_p, c_int, c_void_p]),
     "vk_argmax_pairs": (c_int, [c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_void_p]),

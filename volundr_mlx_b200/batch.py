@@ -97,6 +97,7 @@ class BatchCache:
         self.xr_hn2 = torch.zeros(D // 64 * 2176, **u8)
         self.xr_act = torch.zeros(m.I // 64 * 2176, **u8)
         self.fused_xrec = S <= 16
+        self.fuse_boundary = True   # one kernel for combine(layer i) + mix(layer i + 1)
         self.y_dbg = None
         self.q = torch.zeros((S, m.Hq, 128), **bf)
         if self.indexer:
@@ -307,6 +308,7 @@ def _launch_step(model: Model, bc: BatchCache, capture=()):
     caps = []
 
     fx = bc.fused_xrec
+    fuse_boundary = bc.fuse_boundary and D % 64 == 0 and D // 8 <= 768 and not capture
 
     def gemm(x, wt, y, xr=None):
         if fx and xr is not None:
@@ -331,10 +333,10 @@ def _launch_step(model: Model, bc: BatchCache, capture=()):
     for i, (w, lst) in enumerate(zip(model.layers, bc.layers)):
         if i in capture:
             caps.append(bc.H[:B, 0].clone())
-        ck(L.vk_mhc_mix_norm(_p(bc.H), _p(bc.hn), _p(w["dyn"]), _p(w["pre_s"]), _p(w["post_s"]), _p(w["res_s"]),
-                             _p(w["ln_in"]), _p(bc.x_in), _p(bc.h), _p(bc.xr_h) if fx else None, _p(bc.post), _p(bc.res), _p(bc.dyn), B, D,
-                             a.mhc_sinkhorn_iters,
-                             eps, st), "vk_mhc_mix_norm")
+        if i == 0 or not fuse_boundary:   # (otherwise the previous layer's boundary kernel already did this layer's mix)
+            ck(L.vk_mhc_mix_norm(_p(bc.H), _p(bc.hn), _p(w["dyn"]), _p(w["pre_s"]), _p(w["post_s"]), _p(w["res_s"]),
+                                 _p(w["ln_in"]), _p(bc.x_in), _p(bc.h), _p(bc.xr_h) if fx else None, _p(bc.post), _p(bc.res),
+                                 _p(bc.dyn), B, D, a.mhc_sinkhorn_iters, eps, st), "vk_mhc_mix_norm")
         gemm(bc.h, w["proj"], bc.proj, bc.xr_h)
         if w["mixer"] == "kda":
             nmix = model.HV * 128
@@ -391,6 +393,14 @@ def _launch_step(model: Model, bc: BatchCache, capture=()):
                 val = bc.eng_val
         last = i + 1 == nl
         w_next = model.norm_w if last else model.layers[i + 1]["mhc_norm"]
+        if fuse_boundary and not last and bc.y_dbg is None:
+            wn = model.layers[i + 1]
+            ck(L.vk_mhc_boundary(_p(bc.H), _p(bc.h2), _p(bc.mlp), _p(bc.x_in), _p(bc.post), _p(bc.res), _p(w_next),
+                                 _p(val) if eng else None, _p(w["eng_gate_w"]) if eng else None,
+                                 _p(w["eng_gate_b"]) if eng else None, _p(wn["dyn"]), _p(wn["pre_s"]), _p(wn["post_s"]),
+                                 _p(wn["res_s"]), _p(wn["ln_in"]), _p(bc.h), _p(bc.xr_h) if fx else None, B, D,
+                                 a.mhc_sinkhorn_iters, eps, st), "vk_mhc_boundary")
+            continue
         ck(L.vk_mhc_combine_norm(_p(bc.H), _p(bc.h2), _p(bc.mlp), _p(bc.x_in), _p(bc.post), _p(bc.res), _p(w_next),
                                  _p(bc.hn), _p(val) if eng else None, _p(w["eng_gate_w"]) if eng else None,
                                  _p(w["eng_gate_b"]) if eng else None, _p(bc.y_dbg) if bc.y_dbg is not None else None, B, D,

@@ -260,8 +260,12 @@ __global__ void __launch_bounds__(256) bcsa_select_kernel(const SelectParams p) 
     const __nv_bfloat16* qb = per_kv ? p.q + ((size_t)b * g.Hq + (size_t)ns * nh) * kD : p.q + (size_t)b * g.IH * kD;
     const int spp = kPage / g.C;  // pooled slots per page
     uint32_t* keys = p.scratch + ((size_t)b * g.NS + ns) * p.cap;
-    float qv[8][4];
-    for (int h = 0; h < nh; h++) load4(qb + (size_t)h * kD, lane, qv[h]);
+    float qv[8][4];  // fully unrolled below, so the heads stay in registers
+#pragma unroll
+    for (int h = 0; h < 8; h++) {
+        if (h < nh) load4(qb + (size_t)h * kD, lane, qv[h]);
+        else { qv[h][0] = qv[h][1] = qv[h][2] = qv[h][3] = 0.f; }
+    }
     const float inv_nh = 1.f / (float)nh;
     // four blocks per warp and pass: their table entries and keys are fetched together, then scored one by one
     for (int j0 = warp * 4; j0 < nv; j0 += 32) {
@@ -281,7 +285,9 @@ __global__ void __launch_bounds__(256) bcsa_select_kernel(const SelectParams p) 
             const int j = j0 + u;
             if (j >= nv) break;
             float sc = 0.f;
-            for (int h = 0; h < nh; h++) {
+#pragma unroll
+            for (int h = 0; h < 8; h++) {
+                if (h >= nh) break;
                 float a = qv[h][0] * kx[u][0];
                 a = fmaf(qv[h][1], kx[u][1], a);
                 a = fmaf(qv[h][2], kx[u][2], a);

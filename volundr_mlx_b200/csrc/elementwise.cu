@@ -427,6 +427,162 @@ __global__ void __launch_bounds__(1024) mhc_combine_norm_kernel(const CombinePar
     }
 }
 
+// ------------------------------------------------------------------------------------------------ layer boundary
+// mhc_combine_norm of layer i followed by mhc_dyn + mhc_mix_norm of layer i + 1 in one kernel per row: the new streams
+// stay in registers between the two halves, the mHC norm of their mean goes through shared memory into the 24 dyn dot
+// products, and the next layer's input norm is written as a row and as x records. Same arithmetic, in the same order,
+// as the three separate kernels (VolundrModel._fused_layers, volundr.py:945-948, runs them back to back).
+struct BoundaryParams {
+    CombineParams c;               // layer i (w_next = mhc[i + 1].norm; hn unused)
+    const __nv_bfloat16* w_dyn;    // layer i + 1
+    const __nv_bfloat16* pre_s;
+    const __nv_bfloat16* post_s;
+    const __nv_bfloat16* res_s;
+    const __nv_bfloat16* w_in;
+    __nv_bfloat16* x_in_out;       // [B, D] may alias c.x_in
+    __nv_bfloat16* h;              // [B, D]
+    uint8_t* xrec_h;
+    float* post_out;               // [B, 4]  may alias c.post
+    float* res_out;                // [B, 16] may alias c.res
+    int iters;
+};
+
+constexpr int kBoundaryThreads = 768;
+
+__global__ void __launch_bounds__(kBoundaryThreads) mhc_boundary_kernel(const BoundaryParams q) {
+    extern __shared__ float hn_sm[];           // [D]
+    __shared__ float red[kRowMaxWarps];
+    __shared__ float dsm[24];
+    __shared__ float pre_sm[4];
+    pdl_launch_dependents();
+    pdl_wait();
+    const CombineParams& p = q.c;
+    const int b = blockIdx.x, D = p.D;
+    const size_t base = (size_t)b * D;
+    const int k = threadIdx.x * 8;
+    const bool on = k < D;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+    float gate = 0.f;
+    float hv[8] = {}, mv[8] = {}, xv[8] = {};
+    if (on) { ld8(p.h2 + base + k, hv); ld8(p.m + base + k, mv); ld8(p.x_in + base + k, xv); }
+    if (p.eng_val != nullptr) {
+        float a = 0.f;
+        if (on) {
+            float gw[8];
+            ld8(p.eng_gate_w + k, gw);
+#pragma unroll
+            for (int e = 0; e < 8; e++) a = fmaf(bfr(hv[e] + mv[e]), gw[e], a);
+        }
+        a = row_block_sum(a, red);
+        gate = bfr(1.f / (1.f + expf(-bfr(a + bf2f(p.eng_gate_b[0])))));
+    }
+    float r[16], po[4];
+#pragma unroll
+    for (int i = 0; i < 16; i++) r[i] = p.res[b * 16 + i];
+#pragma unroll
+    for (int s = 0; s < 4; s++) po[s] = p.post[b * 4 + s];
+    __nv_bfloat16* Hb = p.H + (size_t)b * 4 * D;
+    float o[4][8] = {};
+    float v[8] = {};
+    float ss = 0.f;
+    if (on) {
+        float hj[4][8], val[8];
+#pragma unroll
+        for (int j = 0; j < 4; j++) ld8(Hb + (size_t)j * D + k, hj[j]);
+        if (p.eng_val != nullptr) ld8(p.eng_val + base + k, val);
+#pragma unroll
+        for (int e = 0; e < 8; e++) {
+            float y = bfr(hv[e] + mv[e]);
+            if (p.eng_val != nullptr) y = bfr(y + bfr(gate * val[e]));
+            const float delta = bfr(y - xv[e]);
+#pragma unroll
+            for (int s = 0; s < 4; s++) {
+                float mixed = r[4 * s] * hj[0][e];
+                mixed = fmaf(r[4 * s + 1], hj[1][e], mixed);
+                mixed = fmaf(r[4 * s + 2], hj[2][e], mixed);
+                mixed = fmaf(r[4 * s + 3], hj[3][e], mixed);
+                o[s][e] = bfr(bfr(mixed) + bfr(po[s] * delta));
+            }
+            v[e] = bfr((((o[0][e] + o[1][e]) + o[2][e]) + o[3][e]) * 0.25f);
+            ss += v[e] * v[e];
+        }
+#pragma unroll
+        for (int s = 0; s < 4; s++) st8(Hb + (size_t)s * D + k, o[s]);
+    }
+    ss = row_block_sum(ss, red);
+    if (on) {
+        const float inv = rsqrtf(ss / (float)D + p.eps);
+        float w[8];
+        ld8(p.w_next + k, w);
+#pragma unroll
+        for (int e = 0; e < 8; e++) hn_sm[k + e] = bfr((v[e] * inv) * w[e]);   // the next layer's mHC norm, as bf16 values
+    }
+    __syncthreads();
+    // ---- dyn: 24 dot products, one warp each (lane-strided pieces, then an xor tree: as mhc_dyn_kernel)
+    for (int j = warp; j < 24; j += nw) {
+        const __nv_bfloat16* w = q.w_dyn + (size_t)j * D;
+        float a = 0.f;
+        for (int kk = lane * 8; kk < D; kk += 256) {
+            float wv[8];
+            ld8(w + kk, wv);
+#pragma unroll
+            for (int e = 0; e < 8; e++) a = fmaf(hn_sm[kk + e], wv[e], a);
+        }
+        a = warp_sum(a);
+        if (lane == 0) dsm[j] = bfr(a);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float m[16];
+        float mx = -INFINITY;
+        for (int i = 0; i < 16; i++) {
+            m[i] = bf2f(q.res_s[i]) + dsm[8 + i];
+            mx = fmaxf(mx, m[i]);
+        }
+        for (int i = 0; i < 16; i++) m[i] = expf(m[i] - mx);
+        for (int it = 0; it < q.iters; it++) {
+            for (int rr = 0; rr < 4; rr++) {
+                const float s = fmaxf(((m[4 * rr] + m[4 * rr + 1]) + m[4 * rr + 2]) + m[4 * rr + 3], 1e-9f);
+                for (int cc = 0; cc < 4; cc++) m[4 * rr + cc] = m[4 * rr + cc] / s;
+            }
+            for (int cc = 0; cc < 4; cc++) {
+                const float s = fmaxf(((m[cc] + m[4 + cc]) + m[8 + cc]) + m[12 + cc], 1e-9f);
+                for (int rr = 0; rr < 4; rr++) m[4 * rr + cc] = m[4 * rr + cc] / s;
+            }
+        }
+        for (int i = 0; i < 16; i++) q.res_out[b * 16 + i] = bfr(m[i]);
+        for (int s = 0; s < 4; s++) {
+            pre_sm[s] = bfr(bf2f(q.pre_s[s]) + dsm[s]);
+            q.post_out[b * 4 + s] = bfr(bf2f(q.post_s[s]) + dsm[4 + s]);
+        }
+    }
+    __syncthreads();
+    float x[8] = {};
+    float ss2 = 0.f;
+    if (on) {
+#pragma unroll
+        for (int e = 0; e < 8; e++) {
+            x[e] = bfr(((bfr(pre_sm[0] * o[0][e]) + bfr(pre_sm[1] * o[1][e])) + bfr(pre_sm[2] * o[2][e])) + bfr(pre_sm[3] * o[3][e]));
+            ss2 += x[e] * x[e];
+        }
+        st8(q.x_in_out + base + k, x);
+    }
+    ss2 = row_block_sum(ss2, red);
+    const float inv2 = rsqrtf(ss2 / (float)D + p.eps);
+    float ho[8] = {};
+    if (on) {
+        float w[8];
+        ld8(q.w_in + k, w);
+#pragma unroll
+        for (int e = 0; e < 8; e++) ho[e] = (x[e] * inv2) * (1.f + w[e]);
+        st8(q.h + base + k, ho);
+    }
+    if (q.xrec_h != nullptr) {   // whole warps take part in the group sums
+        if (on) xrec_store_row_piece(q.xrec_h, b, threadIdx.x, ho);
+        else { __shfl_xor_sync(0xffffffffu, 0.f, 1); __shfl_xor_sync(0xffffffffu, 0.f, 2); __shfl_xor_sync(0xffffffffu, 0.f, 4); }
+    }
+}
+
 // ------------------------------------------------------------------------------------------------ bf16 linear, few rows
 // y[M, N] = bf16(x[M, K] . W[N, K]^T (+ bias)), fp32 accumulation: the linears the reference keeps unquantised
 // (convert.py:16-17: lm_head, in_proj_b, mhc.dyn, BCSA indexer, Engram gate / value, f_up). One warp per output row.
@@ -628,6 +784,23 @@ int vk_mhc_combine_norm(void* H, const void* h2, const void* m, const void* x_in
                        final_norm, eps};
     if (D % 8 != 0) return VK_EINVAL;
     return (int)vk_launch(mhc_combine_norm_kernel, dim3(B), dim3(row_threads(D)), 0, stream, p);
+}
+
+// mhc_combine_norm of one layer + mhc_mix_norm of the next in one launch (see mhc_boundary_kernel). D / 8 <= 768.
+int vk_mhc_boundary(void* H, const void* h2, const void* m, void* x_in, float* post, float* res, const void* w_next,
+                    const void* eng_val, const void* eng_gate_w, const void* eng_gate_b, const void* w_dyn, const void* pre_s,
+                    const void* post_s, const void* res_s, const void* w_in, void* h, void* xrec_h, int B, int D, int iters,
+                    float eps, cudaStream_t stream) {
+    if (B <= 0 || D <= 0 || D % 64 != 0 || D / 8 > kBoundaryThreads || (xrec_h != nullptr && B > 16)) return VK_EINVAL;
+    BoundaryParams q = {};
+    q.c = {(__nv_bfloat16*)H, (const __nv_bfloat16*)h2, (const __nv_bfloat16*)m, (const __nv_bfloat16*)x_in, post, res,
+           (const __nv_bfloat16*)w_next, nullptr, (const __nv_bfloat16*)eng_val, (const __nv_bfloat16*)eng_gate_w,
+           (const __nv_bfloat16*)eng_gate_b, nullptr, D, 0, eps};
+    q.w_dyn = (const __nv_bfloat16*)w_dyn; q.pre_s = (const __nv_bfloat16*)pre_s; q.post_s = (const __nv_bfloat16*)post_s;
+    q.res_s = (const __nv_bfloat16*)res_s; q.w_in = (const __nv_bfloat16*)w_in; q.x_in_out = (__nv_bfloat16*)x_in;
+    q.h = (__nv_bfloat16*)h; q.xrec_h = (uint8_t*)xrec_h; q.post_out = post; q.res_out = res; q.iters = iters;
+    const int threads = ((D / 8 + 31) / 32) * 32;
+    return (int)vk_launch(mhc_boundary_kernel, dim3(B), dim3(threads), (size_t)D * 4, stream, q);
 }
 
 int vk_bf16_gemm(const void* x, int ldx, const void* W, const void* bias, void* y, int ldy, int M, int N, int K,

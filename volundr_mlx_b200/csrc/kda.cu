@@ -56,6 +56,12 @@ __global__ void __launch_bounds__(128) kda_step_kernel(const KdaParams p) {
     const __nv_bfloat16* conv_in = p.conv + (size_t)par * p.conv_stride;
     __nv_bfloat16* conv_out = p.conv + (size_t)(1 - par) * p.conv_stride;
 
+    // the state does not depend on this step's prologue: start fetching this warp's first rows right away
+    float* Sb = p.S + (((size_t)b * p.HV + hv) * 128) * 128;
+    float4 s_first[8];
+#pragma unroll
+    for (int i = 0; i < 8; i++) s_first[i] = *reinterpret_cast<const float4*>(Sb + (size_t)(warp * 32 + i) * 128 + 4 * lane);
+
     for (int i = c; i < p.rank; i += 128) fd[i] = bf2f(pr[p.off_fd + i]);
 
     // ---- conv + SiLU of this head's q, k, v channel c; new conv state
@@ -123,12 +129,12 @@ __global__ void __launch_bounds__(128) kda_step_kernel(const KdaParams p) {
     // ---- recurrence: warp w owns rows 32 w .. 32 w + 31 of S; lane l columns 4 l .. 4 l + 3
     const float4 k4 = *reinterpret_cast<const float4*>(ks + 4 * lane);
     const float4 q4 = *reinterpret_cast<const float4*>(qs + 4 * lane);
-    float* Sb = p.S + (((size_t)b * p.HV + hv) * 128) * 128;
 #pragma unroll 1
     for (int r0 = warp * 32; r0 < warp * 32 + 32; r0 += 8) {
         float4 s[8];
 #pragma unroll
-        for (int i = 0; i < 8; i++) s[i] = *reinterpret_cast<const float4*>(Sb + (size_t)(r0 + i) * 128 + 4 * lane);
+        for (int i = 0; i < 8; i++)
+            s[i] = r0 == warp * 32 ? s_first[i] : *reinterpret_cast<const float4*>(Sb + (size_t)(r0 + i) * 128 + 4 * lane);
         float kv[8];
 #pragma unroll
         for (int i = 0; i < 8; i++) {
