@@ -253,7 +253,7 @@ def run_ours(a):
     peak, peak_kind = measured_peaks()
     n_gemm, bytes_per_launch, sec_per_launch = gemm_roofline(model, bc, torch, ops)
     achieved = bytes_per_launch / sec_per_launch / 1e9
-    step_bytes = model.weight_bytes() + bc.state_bytes_per_step()
+    step_bytes = (model.weight_bytes() + bc.state_bytes_per_step()) * world   # every rank streams its own shard
     launches = bc.kernels_per_step  # counted by the library while the step was captured
 
     if rank != 0:

@@ -13,6 +13,7 @@ that come with the hardware:
 """
 import ctypes
 import math
+import os
 
 import numpy as np
 import torch
@@ -130,6 +131,7 @@ class BatchCache:
         self.graphs = {}
         self.kernels_per_step = None
         self.use_graph = True
+        self.tp_graph = os.environ.get("VK_TP_GRAPH", "1") == "1"   # capture the NCCL all-reduces into the step's graph
         self.steps = 0
 
     # ------------------------------------------------------------------ membership
@@ -435,7 +437,7 @@ def forward(model: Model, bc: BatchCache, toks, capture=()):
         toks = torch.tensor(list(toks), dtype=torch.int32)
     bc.tok[:B].copy_(toks.to(torch.int32), non_blocking=True)
     key = (B, tuple(capture))
-    if bc.use_graph and not capture and model.tp_size == 1:
+    if bc.use_graph and not capture and (model.tp_size == 1 or bc.tp_graph):
         g = bc.graphs.get(key)
         if g is None:
             # warm-up launch outside capture is not possible without advancing the rows, so capture directly; the

@@ -48,11 +48,11 @@ constexpr size_t kCounterBytes = 16384;                         // arrival count
 template <int FMT> struct Fmt;
 template <> struct Fmt<0> {
     static constexpr int kChunk = 1152, kStages = 8, kCtasPerSM = 2;
-    static constexpr int kWStage = kBlocksPerSB * kChunk, kStage = kWStage + kXRecBytes;
+    static constexpr int kWStage = kBlocksPerSB * kChunk, kStage = kWStage + kXRecBytes + 16;  // + 16 zero bytes
 };
 template <> struct Fmt<1> {
     static constexpr int kChunk = 4096, kStages = 6, kCtasPerSM = 1;
-    static constexpr int kWStage = kBlocksPerSB * kChunk, kStage = kWStage + kXRecBytes;
+    static constexpr int kWStage = kBlocksPerSB * kChunk, kStage = kWStage + kXRecBytes + 16;  // + 16 zero bytes
 };
 template <int FMT> constexpr int wstage_bytes() { return Fmt<FMT>::kWStage; }
 template <int FMT> constexpr size_t smem_bytes() { return (size_t)Fmt<FMT>::kStages * Fmt<FMT>::kStage + 2 * Fmt<FMT>::kStages * 8; }
@@ -66,6 +66,7 @@ struct W4Params {
     int* counters;          // [NSB] zero between launches
     long long T;            // NSB * G steps
     int M, N, NSB, G, P, ldy, maxc;
+    int S;                  // > 0: aligned mode, CTA c = (superblock c / S, K slice c % S); 0: contiguous ranges
 };
 
 __device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
@@ -116,9 +117,20 @@ __global__ void __launch_bounds__(kThreads, Fmt<FMT>::kCtasPerSM) w4_gemm_kernel
     uint64_t* empty = full + kStages;
     __shared__ int s_last;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const long long t0 = (long long)blockIdx.x * p.T / p.P, t1 = (long long)(blockIdx.x + 1) * p.T / p.P;
+    long long t0, t1;
+    if (p.S > 0) {   // one K slice of one superblock
+        const int asb = blockIdx.x / p.S, sl = blockIdx.x % p.S;
+        t0 = (long long)asb * p.G + (long long)sl * p.G / p.S;
+        t1 = (long long)asb * p.G + (long long)(sl + 1) * p.G / p.S;
+    } else {
+        t0 = (long long)blockIdx.x * p.T / p.P;
+        t1 = (long long)(blockIdx.x + 1) * p.T / p.P;
+    }
     const int n = (int)(t1 - t0);
 
+    if (threadIdx.x >= 32 && threadIdx.x < 32 + kStages * 4)   // the 16 zero bytes behind every stage's x record
+        *reinterpret_cast<uint32_t*>(smem + (size_t)((threadIdx.x - 32) >> 2) * kStageBytes + kWStageBytes + kXRecBytes +
+                                     ((threadIdx.x - 32) & 3) * 4) = 0u;
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; s++) {
             mbar_init(&full[s], 1);
@@ -180,8 +192,10 @@ __global__ void __launch_bounds__(kThreads, Fmt<FMT>::kCtasPerSM) w4_gemm_kernel
     auto flush = [&](int fsb, int kga, int kgb) {
         const bool whole = (kga == 0 && kgb == p.G);
         const long long s0 = (long long)fsb * p.G;
-        const int c_first = step_owner(s0, p.T, p.P);
-        if (!whole) {
+        const int c_first = p.S > 0 ? fsb * p.S : step_owner(s0, p.T, p.P);
+        if (!whole && p.S > 0) {
+            // ---- aligned mode: the S CTAs of this superblock started together with equal shares of K. Each stores its
+            // partial sums, waits (bounded) for the other S - 1, then adds up its own 256 / S rows in slice order.
             float* dst = p.part + (((size_t)fsb * p.maxc + (blockIdx.x - c_first)) * kSBRows) * 16;
 #pragma unroll
             for (int s = 0; s < 2; s++)
@@ -195,6 +209,70 @@ __global__ void __launch_bounds__(kThreads, Fmt<FMT>::kCtasPerSM) w4_gemm_kernel
                     }
             __threadfence();
             consumer_sync();
+            const int nc = p.S, slot = blockIdx.x - c_first;
+            int* arrive = p.counters + fsb;
+            int* depart = p.counters + 2048 + fsb;
+            if (ctid == 0) {
+                atomicAdd(arrive, 1);
+                int seen = 0;
+                for (uint32_t it = 0; it < (1u << 20); it++) {
+                    asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(seen) : "l"(arrive) : "memory");
+                    if (seen >= nc) break;
+                    __nanosleep(32);
+                }
+                s_last = seen >= nc;
+                if (!s_last) vk_set_status(VK_ST_FLAG_TIMEOUT);
+            }
+            consumer_sync();
+            if (s_last) {
+                __threadfence();
+                constexpr int V4 = MR / 4;
+                const int r0 = slot * kSBRows / nc, r1 = (slot + 1) * kSBRows / nc;
+                for (int item = ctid; item < (r1 - r0) * V4; item += 256) {
+                    const int r = r0 + item / V4, v = item % V4;
+                    const int nrow = fsb * kSBRows + r;
+                    const float4* src = reinterpret_cast<const float4*>(p.part + ((size_t)fsb * p.maxc * kSBRows + r) * 16) + v;
+                    float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+                    for (int c0 = 0; c0 < nc; c0 += 8) {
+                        float4 buf[8];
+#pragma unroll
+                        for (int u = 0; u < 8; u++)
+                            buf[u] = (c0 + u < nc) ? __ldcg(src + (size_t)(c0 + u) * kSBRows * 4) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                        for (int u = 0; u < 8; u++) {
+                            if (c0 + u < nc) { sum.x += buf[u].x; sum.y += buf[u].y; sum.z += buf[u].z; sum.w += buf[u].w; }
+                        }
+                    }
+                    if (nrow < p.N) {
+                        const float o4[4] = {sum.x, sum.y, sum.z, sum.w};
+#pragma unroll
+                        for (int e = 0; e < 4; e++)
+                            if (4 * v + e < p.M) p.y[(size_t)(4 * v + e) * p.ldy + nrow] = f2bf(o4[e]);
+                    }
+                }
+            }
+            consumer_sync();
+            if (ctid == 0) {   // the last one to leave puts both counters back to zero for the next launch
+                const int old = atomicAdd(depart, 1);
+                if (old == nc - 1) { *arrive = 0; *depart = 0; __threadfence(); }
+            }
+        } else if (!whole) {
+            float* dst = p.part + (((size_t)fsb * p.maxc + (blockIdx.x - c_first)) * kSBRows) * 16;
+#pragma unroll
+            for (int s = 0; s < 2; s++)
+#pragma unroll
+                for (int jj = 0; jj < MT; jj++)
+#pragma unroll
+                    for (int h = 0; h < 2; h++) {
+                        const int r = j * 32 + s * 16 + g + h * 8;
+                        __stcg(reinterpret_cast<float2*>(dst + (size_t)r * 16 + jj * 8 + 2 * t),
+                               make_float2(acc[s][jj][2 * h], acc[s][jj][2 * h + 1]));
+                    }
+            __threadfence();
+            consumer_sync();
+            // The CTA that arrives last at this superblock adds up the partial sums of all its ranges, in range order.
+            // (Nobody waits: a wait for the other ranges would chain every CTA to its predecessor, whose last range
+            // ends where this one's first begins.)
             if (ctid == 0) {
                 const int ncontrib = step_owner(s0 + p.G - 1, p.T, p.P) - c_first + 1;
                 const int old = atomicAdd(&p.counters[fsb], 1);
@@ -205,37 +283,28 @@ __global__ void __launch_bounds__(kThreads, Fmt<FMT>::kCtasPerSM) w4_gemm_kernel
             const int ncontrib = s_last;
             if (ncontrib) {
                 __threadfence();
-                const int nrow = fsb * kSBRows + ctid;  // one output row per consumer thread
-                if (nrow < p.N) {
-                    const float* src = p.part + ((size_t)fsb * p.maxc * kSBRows + ctid) * 16;
-                    float sum[MR];
+                constexpr int V4 = MR / 4;                                 // float4 columns of a partial row
+                for (int item = ctid; item < kSBRows * V4; item += 256) {
+                    const int r = item / V4, v = item % V4;
+                    const int nrow = fsb * kSBRows + r;
+                    const float4* src = reinterpret_cast<const float4*>(p.part + ((size_t)fsb * p.maxc * kSBRows + r) * 16) + v;
+                    float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+                    for (int c0 = 0; c0 < ncontrib; c0 += 8) {             // eight loads in flight, added in range order
+                        float4 buf[8];
 #pragma unroll
-                    for (int m = 0; m < MR; m++) sum[m] = 0.f;
-                    // contributions are fetched several at a time (all loads in flight together) and added in range order
-                    constexpr int kBatch = 16 / (MR / 4);
-                    for (int c0 = 0; c0 < ncontrib; c0 += kBatch) {
-                        float4 buf[kBatch][MR / 4];
+                        for (int u = 0; u < 8; u++)
+                            buf[u] = (c0 + u < ncontrib) ? __ldcg(src + (size_t)(c0 + u) * kSBRows * 4) : make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-                        for (int u = 0; u < kBatch; u++) {
-                            const float4* q4 = reinterpret_cast<const float4*>(src + (size_t)(c0 + u) * kSBRows * 16);
-#pragma unroll
-                            for (int v = 0; v < MR / 4; v++)
-                                buf[u][v] = (c0 + u < ncontrib) ? __ldcg(q4 + v) : make_float4(0.f, 0.f, 0.f, 0.f);
-                        }
-#pragma unroll
-                        for (int u = 0; u < kBatch; u++) {
-                            if (c0 + u < ncontrib) {
-#pragma unroll
-                                for (int v = 0; v < MR / 4; v++) {
-                                    sum[4 * v] += buf[u][v].x; sum[4 * v + 1] += buf[u][v].y;
-                                    sum[4 * v + 2] += buf[u][v].z; sum[4 * v + 3] += buf[u][v].w;
-                                }
-                            }
+                        for (int u = 0; u < 8; u++) {
+                            if (c0 + u < ncontrib) { sum.x += buf[u].x; sum.y += buf[u].y; sum.z += buf[u].z; sum.w += buf[u].w; }
                         }
                     }
+                    if (nrow < p.N) {
+                        const float o4[4] = {sum.x, sum.y, sum.z, sum.w};
 #pragma unroll
-                    for (int m = 0; m < MR; m++)
-                        if (m < p.M) p.y[(size_t)m * p.ldy + nrow] = f2bf(sum[m]);
+                        for (int e = 0; e < 4; e++)
+                            if (4 * v + e < p.M) p.y[(size_t)(4 * v + e) * p.ldy + nrow] = f2bf(o4[e]);
+                    }
                 }
             }
             consumer_sync();  // s_last is reused by the next flush
@@ -262,19 +331,27 @@ __global__ void __launch_bounds__(kThreads, Fmt<FMT>::kCtasPerSM) w4_gemm_kernel
                 for (int e = 0; e < 4; e++) acc[s][jj][e] = 0.f;
     };
 
-    for (int i = 0; i < n; i++) {
-        const int st = i % kStages;
-        if (!mbar_wait(&full[st], (i / kStages) & 1)) { ok = false; break; }
+    // per-lane offsets inside a stage that do not change from step to step: the four ldmatrix sources, and the
+    // bias-term words (threads t >= 2 hold columns the term does not use: they read the stage's zero bytes)
+    uint32_t lm_off[4];
+#pragma unroll
+    for (int q = 0; q < 4; q++) lm_off[q] = kWStageBytes + lm_row * 128 + (((2 * q + lm_half) ^ lm_r) << 4);
+    uint32_t bw_off[MT];
+#pragma unroll
+    for (int jj = 0; jj < MT; jj++) bw_off[jj] = t < 2 ? kWStageBytes + 2048 + (jj * 8 + g) * 8 + t * 4 : kWStageBytes + kXRecBytes;
+    int st = 0;
+    uint32_t phase = 0;
+    for (int i = 0; i < n; i++, st = (st + 1 == kStages ? 0 : st + 1), phase ^= (st == 0)) {
+        if (!mbar_wait(&full[st], phase)) { ok = false; break; }
         const uint8_t* stage = smem + (size_t)st * kStageBytes;
         const uint8_t* ch = stage + j * kChunkB;
-        const uint8_t* xr = stage + kWStageBytes;
-        const uint32_t xrow = smem_u32(xr) + lm_row * 128;
+        const uint32_t stage_a = smem_u32(stage);
         if constexpr (FMT == 1) {
             // plain bf16 weights: fragments as stored, accumulate straight into acc
 #pragma unroll
             for (int q = 0; q < 4; q++) {
                 uint32_t b[2 * MT];
-                const uint32_t addr = xrow + (uint32_t)(((2 * q + lm_half) ^ lm_r) << 4);
+                const uint32_t addr = stage_a + lm_off[q];
                 if constexpr (MT == 2) {
                     asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
                                  : "=r"(b[0]), "=r"(b[1]), "=r"(b[2]), "=r"(b[3])
@@ -302,7 +379,7 @@ __global__ void __launch_bounds__(kThreads, Fmt<FMT>::kCtasPerSM) w4_gemm_kernel
 #pragma unroll
         for (int q = 0; q < 4; q++) {
             uint32_t b[2 * MT];
-            const uint32_t addr = xrow + (uint32_t)(((2 * q + lm_half) ^ lm_r) << 4);
+            const uint32_t addr = stage_a + lm_off[q];
             if constexpr (MT == 2) {
                 asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
                              : "=r"(b[0]), "=r"(b[1]), "=r"(b[2]), "=r"(b[3])
@@ -329,8 +406,7 @@ __global__ void __launch_bounds__(kThreads, Fmt<FMT>::kCtasPerSM) w4_gemm_kernel
         const uint32_t sbw[4] = {sb4.x, sb4.y, sb4.z, sb4.w};
         uint32_t bw[MT];
 #pragma unroll
-        for (int jj = 0; jj < MT; jj++)
-            bw[jj] = t < 2 ? *reinterpret_cast<const uint32_t*>(xr + 2048 + (jj * 8 + g) * 8 + t * 4) : 0u;
+        for (int jj = 0; jj < MT; jj++) bw[jj] = *reinterpret_cast<const uint32_t*>(stage + bw_off[jj]);
         __syncwarp();
         if (lane == 0) mbar_arrive(&empty[st]);   // everything of this stage is in registers now
 #pragma unroll
@@ -343,7 +419,7 @@ __global__ void __launch_bounds__(kThreads, Fmt<FMT>::kCtasPerSM) w4_gemm_kernel
                 acc[s][jj][2] = fmaf(s1, d[s][jj][2], acc[s][jj][2]);
                 acc[s][jj][3] = fmaf(s1, d[s][jj][3], acc[s][jj][3]);
             }
-            const uint32_t ab[4] = {t < 2 ? sbw[2 * s] : 0u, t < 2 ? sbw[2 * s + 1] : 0u, 0u, 0u};
+            const uint32_t ab[4] = {sbw[2 * s], sbw[2 * s + 1], 0u, 0u};   // (columns 4..7 meet zeros in B)
 #pragma unroll
             for (int jj = 0; jj < MT; jj++) mma_bf16(acc[s][jj], ab, bw[jj], 0u);
         }
@@ -463,7 +539,7 @@ __global__ void bf16_repack_kernel(const __nv_bfloat16* __restrict__ W, int N, i
 int g_force_ctas = 0;
 
 struct W4Plan {
-    int P, maxc, NSB, G;
+    int P, maxc, NSB, G, S;
     long long T;
 };
 
@@ -473,6 +549,20 @@ W4Plan w4_plan(int N, int K, int ctas_per_sm = 2) {
     pl.G = K / 64;
     pl.T = (long long)pl.NSB * pl.G;
     int P = ctas_per_sm * 148;             // every CTA resident at once
+    pl.S = 0;
+    // Few superblocks (N small against the SM count): give every superblock the same number S of CTAs, each an
+    // equal slice of K, so that the S partial sums of a superblock are ready together and its CTAs share the final
+    // addition. Otherwise: equal contiguous ranges of the (superblock, group) sequence.
+    if (g_force_ctas == 0 && pl.NSB * 4 <= P && pl.NSB <= 2048) {
+        int S = P / pl.NSB;
+        if (S > pl.G) S = pl.G;
+        if (S >= 2) {
+            pl.S = S;
+            pl.P = pl.NSB * S;
+            pl.maxc = S;
+            return pl;
+        }
+    }
     if (g_force_ctas > 0) P = g_force_ctas;
     if ((long long)P > pl.T) P = (int)pl.T;
     pl.P = P;
@@ -549,7 +639,7 @@ int vk_w4_gemm_xrec(const void* packed, const void* xrec, void* y, int ldy, int 
     p.y = (__nv_bfloat16*)y;
     p.counters = (int*)ws;
     p.part = (float*)(ws + kCounterBytes + (size_t)pl.G * kXRecBytes);
-    p.T = pl.T; p.M = M; p.N = N; p.NSB = pl.NSB; p.G = pl.G; p.P = pl.P; p.ldy = ldy; p.maxc = pl.maxc;
+    p.T = pl.T; p.M = M; p.N = N; p.NSB = pl.NSB; p.G = pl.G; p.P = pl.P; p.ldy = ldy; p.maxc = pl.maxc; p.S = pl.S;
     cudaError_t e = M <= 8 ? vk_launch(w4_gemm_kernel<1, 0>, dim3(pl.P), dim3(kThreads), smem_bytes<0>(), stream, p)
                            : vk_launch(w4_gemm_kernel<2, 0>, dim3(pl.P), dim3(kThreads), smem_bytes<0>(), stream, p);
     return (int)e;
@@ -578,7 +668,7 @@ int vk_w4_gemm(const void* packed, const void* x, int ldx, void* y, int ldy, int
         p.y = (__nv_bfloat16*)y + (size_t)m0 * ldy;
         p.counters = (int*)ws;
         p.part = (float*)(ws + kCounterBytes + (size_t)pl.G * kXRecBytes);
-        p.T = pl.T; p.M = m; p.N = N; p.NSB = pl.NSB; p.G = pl.G; p.P = pl.P; p.ldy = ldy; p.maxc = pl.maxc;
+        p.T = pl.T; p.M = m; p.N = N; p.NSB = pl.NSB; p.G = pl.G; p.P = pl.P; p.ldy = ldy; p.maxc = pl.maxc; p.S = pl.S;
         VK_CUDA(vk_launch(w4_xrec_kernel, dim3(pl.G), dim3(128), 0, stream, (const __nv_bfloat16*)x + (size_t)m0 * ldx, ldx, m,
                           ws + kCounterBytes));
         cudaError_t e = m <= 8 ? vk_launch(w4_gemm_kernel<1, 0>, dim3(pl.P), dim3(kThreads), smem_bytes<0>(), stream, p)
@@ -627,7 +717,7 @@ int vk_bf16_gemm_packed(const void* packed, const void* x, int ldx, void* y, int
         p.y = (__nv_bfloat16*)y + (size_t)m0 * ldy;
         p.counters = (int*)ws;
         p.part = (float*)(ws + kCounterBytes + (size_t)pl.G * kXRecBytes);
-        p.T = pl.T; p.M = m; p.N = N; p.NSB = pl.NSB; p.G = pl.G; p.P = pl.P; p.ldy = ldy; p.maxc = pl.maxc;
+        p.T = pl.T; p.M = m; p.N = N; p.NSB = pl.NSB; p.G = pl.G; p.P = pl.P; p.ldy = ldy; p.maxc = pl.maxc; p.S = pl.S;
         VK_CUDA(vk_launch(w4_xrec_kernel, dim3(pl.G), dim3(128), 0, stream, (const __nv_bfloat16*)x + (size_t)m0 * ldx, ldx, m,
                           ws + kCounterBytes));
         cudaError_t e = m <= 8 ? vk_launch(w4_gemm_kernel<1, 1>, dim3(pl.P), dim3(kThreads), smem_bytes<1>(), stream, p)
