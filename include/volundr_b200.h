@@ -168,6 +168,8 @@ int vk_bcsa_select_static(const vk_attn_geom* g, const void* q, const void* keys
  * keys, split over `nsplit` CTAs per (row, kv head), merged, times sigmoid(gate) (volundr.py:177-179).
  * part: fp32 scratch of vk_attend_scratch_bytes. out [B, Hq*D]. */
 size_t vk_attend_scratch_bytes(const vk_attn_geom* g, int B, int nsplit);
+/* 1 (default): Q K^T and P V on the tensor cores (bf16 probabilities); 0: the scalar fp32 kernel, kept as a cross-check. */
+void vk_attend_set_tensor_cores(int on);
 int vk_attend_decode(const vk_attn_geom* g, const void* q, const void* K, const void* V, const void* PK, const void* PV,
                      const int* pos, const int* table, const int* sel, const int* nsel, const void* proj, int ldp,
                      void* part, int nsplit, void* out, void* xrec_out, int B, vk_stream_t stream);

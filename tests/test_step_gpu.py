@@ -110,3 +110,33 @@ def test_fused_layer_boundary_equals_separate_kernels(cuda):
             res.append(lg.clone())
         outs.append(torch.stack(res))
     assert torch.equal(outs[0], outs[1])
+
+
+def test_tensor_core_attention_close_to_scalar_kernel(cuda):
+    """The tensor-core attention (bf16 probabilities) against the scalar fp32 kernel on the same schedule: logits
+    within bf16 tolerance (the reference's bar for its attention kernels is 2^-7 |x| + 2e-3, test_volundr.py:266)."""
+    from volundr_mlx_b200 import _lib, batch as BT
+    from volundr_mlx_b200.volundr import Model
+
+    L = _lib.lib()
+    args = synth.small_args(bcsa_far="tokens", bcsa_score="pooled_key", bcsa_window=128, bcsa_compress=64, bcsa_topk=2)
+    params = synth.make_params(args, seed=8)
+    model = Model(args, params, cuda)
+    outs = []
+    try:
+        for tc in (1, 0):
+            L.vk_attend_set_tensor_cores(tc)
+            bc = model.make_cache(max_rows=4, n_pages=64, max_pages_per_row=8)
+            bc.use_graph = False
+            bc.apply(join=["a", "b"])
+            rng = np.random.default_rng(2)
+            res = []
+            for t in range(300):
+                lg, _ = BT.forward(model, bc, rng.integers(0, args.vocab_valid, size=2).tolist())
+                if t % 10 == 9:
+                    res.append(lg.float().clone())
+            outs.append(torch.stack(res))
+    finally:
+        L.vk_attend_set_tensor_cores(1)
+    err = (outs[0] - outs[1]).abs().max() / outs[1].abs().max()
+    assert err < 2e-2, float(err)

@@ -47,6 +47,7 @@ SIGNATURES = {
     "vk_bcsa_select_scratch_bytes": (c_size_t, [c_void_p, c_int, c_int]),
     "vk_bcsa_select": (c_int, [c_void_p] * 6 + [c_int, c_void_p, c_void_p, c_int, c_void_p]),
     "vk_bcsa_select_static": (c_int, [c_void_p] * 7 + [c_int, c_void_p]),
+    "vk_attend_set_tensor_cores": (None, [c_int]),
     "vk_attend_scratch_bytes": (c_size_t, [c_void_p, c_int, c_int]),
     "vk_attend_decode": (c_int, [c_void_p] * 11 + [c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p]),
 }

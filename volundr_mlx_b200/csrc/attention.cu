@@ -557,8 +557,200 @@ __global__ void __launch_bounds__(128) attend_merge_kernel(const float* __restri
     }
 }
 
+// ------------------------------------------------------------------------------------------------ attention, tensor cores
+// The same split-KV decode attention with both products on the tensor cores: S = Q K^T with the G query heads of the
+// kv head as the 16-row A operand (rows >= G zero) and P V with bf16 probabilities. Per unit of up to 64 keys:
+// 4 warps x (16 keys) for S, softmax pieces per head, 4 warps x (32 dims) for O. fp32 running max / sum / O.
+constexpr int kPStride = kPage + 8;   // bf16 elements per row of the probability tile
+
+__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_t(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void mma16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+template <int G>
+__global__ void __launch_bounds__(128) attend_decode_tc_kernel(const AttendParams p) {
+    __shared__ __align__(16) __nv_bfloat16 Ks[kPage * kRowStride];
+    __shared__ __align__(16) __nv_bfloat16 Vs[kPage * kRowStride];
+    __shared__ __align__(16) __nv_bfloat16 Qs[16 * kRowStride];
+    __shared__ __align__(16) __nv_bfloat16 Ps[16 * kPStride];
+    __shared__ float sc[8 * kPage];
+    __shared__ float s_aold[8], s_m[8], s_l[8];
+    __shared__ const __nv_bfloat16* rowK[kPage];
+    __shared__ const __nv_bfloat16* rowV[kPage];
+    pdl_launch_dependents();
+    pdl_wait();
+    const AttnGeom& g = p.g;
+    const int split = blockIdx.x, kv = blockIdx.y, b = blockIdx.z;
+    const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
+    const int gq = lane >> 2, tq = lane & 3;
+    const int pos = p.pos[b];
+    const int lo = g.W > 0 ? max(0, pos - g.W + 1) : 0;
+    const int wp0 = lo / kPage, nwp = pos / kPage - wp0 + 1;
+    const int ns = g.NS > 1 ? kv : 0;
+    const int nf = (p.sel != nullptr && g.NS > 0) ? p.nsel[b * g.NS + ns] : 0;
+    const int* sel = p.sel ? p.sel + ((size_t)b * g.NS + ns) * g.topk : nullptr;
+    const int spp = g.W > 0 ? kPage / g.C : 1;
+    const int nfu = g.far_tokens ? nf : (nf + kPage - 1) / kPage;
+    const int U = nwp + nfu;
+
+    // zero the tiles once (rows a unit does not fill must stay finite), stage Q (rows >= G zero)
+    for (int i = t; i < kPage * kRowStride / 8; i += 128) {
+        reinterpret_cast<uint4*>(Ks)[i] = make_uint4(0, 0, 0, 0);
+        reinterpret_cast<uint4*>(Vs)[i] = make_uint4(0, 0, 0, 0);
+    }
+    for (int i = t; i < 16 * kRowStride / 8; i += 128) reinterpret_cast<uint4*>(Qs)[i] = make_uint4(0, 0, 0, 0);
+    for (int i = t; i < 16 * kPStride / 8; i += 128) reinterpret_cast<uint4*>(Ps)[i] = make_uint4(0, 0, 0, 0);
+    if (t < 8) { s_m[t] = -INFINITY; s_l[t] = 0.f; }
+    __syncthreads();
+    for (int i = t; i < G * 16; i += 128) {
+        const int h = i >> 4, c = i & 15;
+        *reinterpret_cast<uint4*>(Qs + h * kRowStride + c * 8) =
+            *reinterpret_cast<const uint4*>(p.q + ((size_t)b * g.Hq + (size_t)kv * G + h) * kD + c * 8);
+    }
+    __syncthreads();
+    uint32_t qf[8][4];   // A fragments of Q for the 8 k-steps of the head dim
+    {
+        const int row = (lane & 7) + ((lane >> 3) & 1) * 8, col = (lane >> 4) * 8;
+#pragma unroll
+        for (int ks = 0; ks < 8; ks++) ldsm_x4(qf[ks], smem_u32(Qs + row * kRowStride + ks * 16 + col));
+    }
+    float o[4][4];       // O[head gq (and gq + 8, unused)][dims 32 warp + 8 nt + 2 tq ..]
+#pragma unroll
+    for (int nt = 0; nt < 4; nt++)
+#pragma unroll
+        for (int e = 0; e < 4; e++) o[nt][e] = 0.f;
+    if (t < 8) s_aold[t] = 0.f;
+
+    for (int u = split; u < U; u += p.nsplit) {
+        __syncthreads();
+        // ---- which rows make up this unit
+        int nrows;
+        if (u < nwp) {
+            const int page = p.table[b * g.max_pages + wp0 + u];
+            const int ra = u == 0 ? lo % kPage : 0;
+            const int rb = u == nwp - 1 ? pos % kPage : kPage - 1;
+            nrows = rb - ra + 1;
+            if (t < nrows) {
+                const size_t off = (((size_t)page * g.KVH + kv) * kPage + ra + t) * kD;
+                rowK[t] = p.K + off;
+                rowV[t] = p.V + off;
+            }
+        } else if (g.far_tokens) {
+            const int j = sel[u - nwp];
+            const int tok0 = j * g.C;
+            const int page = p.table[b * g.max_pages + tok0 / kPage];
+            nrows = g.C;
+            if (t < nrows) {
+                const size_t off = (((size_t)page * g.KVH + kv) * kPage + tok0 % kPage + t) * kD;
+                rowK[t] = p.K + off;
+                rowV[t] = p.V + off;
+            }
+        } else {
+            const int f0 = (u - nwp) * kPage;
+            nrows = min(kPage, nf - f0);
+            if (t < nrows) {
+                const int j = sel[f0 + t];
+                const int page = p.table[b * g.max_pages + (j / spp)];
+                const size_t off = (((size_t)page * g.KVH + kv) * spp + j % spp) * kD;
+                rowK[t] = p.PK + off;
+                rowV[t] = p.PV + off;
+            }
+        }
+        __syncthreads();
+        for (int i = t; i < nrows * 16; i += 128) {
+            const int r = i >> 4, cch = i & 15;
+            cp_async16(Ks + r * kRowStride + cch * 8, rowK[r] + cch * 8);
+            cp_async16(Vs + r * kRowStride + cch * 8, rowV[r] + cch * 8);
+        }
+        asm volatile("cp.async.wait_all;" ::: "memory");
+        __syncthreads();
+        // ---- S = Q K^T: warp w takes keys 16 w .. 16 w + 15
+        {
+            float sa[2][4] = {};
+            const int mat = lane >> 3, r = lane & 7;
+            const uint32_t kaddr = smem_u32(Ks + (16 * warp + (mat >> 1) * 8 + r) * kRowStride + (mat & 1) * 8);
+#pragma unroll
+            for (int ks = 0; ks < 8; ks++) {
+                uint32_t kb[4];
+                ldsm_x4(kb, kaddr + ks * 32);
+                mma16816(sa[0], qf[ks], kb[0], kb[1]);
+                mma16816(sa[1], qf[ks], kb[2], kb[3]);
+            }
+            if (gq < G) {
+#pragma unroll
+                for (int nt = 0; nt < 2; nt++) {
+                    const int key = 16 * warp + 8 * nt + 2 * tq;
+                    sc[gq * kPage + key] = key < nrows ? sa[nt][0] * p.scale : -INFINITY;
+                    sc[gq * kPage + key + 1] = key + 1 < nrows ? sa[nt][1] * p.scale : -INFINITY;
+                }
+            }
+        }
+        __syncthreads();
+        // ---- softmax pieces per head (warp w: heads w, w + 4): running max / sum, probabilities as bf16
+        for (int h = warp; h < G; h += 4) {
+            const float s0 = sc[h * kPage + lane], s1 = sc[h * kPage + 32 + lane];
+            const float mx = warp_max(fmaxf(s0, s1));   // finite: a unit has at least one row
+            const float m_old = s_m[h];
+            const float m_new = fmaxf(m_old, mx);
+            const float p0 = bfr(__expf(s0 - m_new)), p1 = bfr(__expf(s1 - m_new));
+            Ps[h * kPStride + lane] = f2bf(p0);
+            Ps[h * kPStride + 32 + lane] = f2bf(p1);
+            const float sum = warp_sum(p0 + p1);
+            if (lane == 0) {
+                const float a_old = m_old == -INFINITY ? 0.f : __expf(m_old - m_new);
+                s_l[h] = s_l[h] * a_old + sum;
+                s_m[h] = m_new;
+                s_aold[h] = a_old;
+            }
+        }
+        __syncthreads();
+        // ---- O = O * a_old + P V: warp w takes dims 32 w .. 32 w + 31
+        {
+            const float a = s_aold[gq];
+#pragma unroll
+            for (int nt = 0; nt < 4; nt++) { o[nt][0] *= a; o[nt][1] *= a; }
+            const int prow = (lane & 7) + ((lane >> 3) & 1) * 8, pcol = (lane >> 4) * 8;
+            const int mat = lane >> 3, r = lane & 7;
+#pragma unroll
+            for (int ks = 0; ks < 4; ks++) {
+                uint32_t pa[4];
+                ldsm_x4(pa, smem_u32(Ps + prow * kPStride + ks * 16 + pcol));
+#pragma unroll
+                for (int half = 0; half < 2; half++) {
+                    uint32_t vb[4];
+                    ldsm_x4_t(vb, smem_u32(Vs + (ks * 16 + (mat & 1) * 8 + r) * kRowStride + 32 * warp + half * 16 + (mat >> 1) * 8));
+                    mma16816(o[2 * half], pa, vb[0], vb[1]);
+                    mma16816(o[2 * half + 1], pa, vb[2], vb[3]);
+                }
+            }
+        }
+    }
+    __syncthreads();
+    float* out = p.part + (((size_t)b * g.KVH + kv) * p.nsplit + split) * G * (kD + 2);
+    if (gq < G) {
+#pragma unroll
+        for (int nt = 0; nt < 4; nt++)
+            *reinterpret_cast<float2*>(out + gq * (kD + 2) + 32 * warp + 8 * nt + 2 * tq) = make_float2(o[nt][0], o[nt][1]);
+    }
+    if (t < G) { out[t * (kD + 2) + kD] = s_m[t]; out[t * (kD + 2) + kD + 1] = s_l[t]; }
+}
+
+bool g_attend_tc = true;
+
 template <int G>
 cudaError_t launch_attend(const AttendParams& p, int B, cudaStream_t stream) {
+    if (g_attend_tc) return vk_launch(attend_decode_tc_kernel<G>, dim3(p.nsplit, p.g.KVH, B), dim3(128), 0, stream, p);
     return vk_launch(attend_decode_kernel<G>, dim3(p.nsplit, p.g.KVH, B), dim3(128), 0, stream, p);
 }
 
@@ -655,6 +847,9 @@ int vk_bcsa_select_static(const vk_attn_geom* gm, const void* q, const void* key
     p.scale = (float)(1.0 / sqrt((double)kD)); p.g = to_geom(gm);
     return (int)vk_launch(bcsa_select_kernel, dim3(p.g.NS, B), dim3(256), 0, stream, p);
 }
+
+// 1 (default): both attention products on the tensor cores; 0: the scalar kernel (kept as a cross-check)
+void vk_attend_set_tensor_cores(int on) { g_attend_tc = on != 0; }
 
 size_t vk_attend_scratch_bytes(const vk_attn_geom* gm, int B, int nsplit) {
     return (size_t)B * gm->Hq * nsplit * (kD + 2) * 4;

@@ -82,7 +82,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t phase) {
 }
 // Wait for phase `phase` of `bar` with an iteration limit. Returns false (and records VK_ST_MBAR_TIMEOUT) when the
 // limit runs out, so a copy that never lands ends the kernel instead of hanging the GPU.
-#define VK_MBAR_SPIN_LIMIT (1u << 22)
+#define VK_MBAR_SPIN_LIMIT (1u << 20)
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t phase) {
     for (uint32_t i = 0; i < VK_MBAR_SPIN_LIMIT; i++) {
         if (mbar_try_wait(bar, phase)) return true;

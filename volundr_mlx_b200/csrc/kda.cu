@@ -40,7 +40,7 @@ struct KdaParams {
 
 __device__ __forceinline__ float softplus_f(float x) { return fmaxf(x, 0.f) + log1pf(expf(-fabsf(x))); }
 
-__global__ void __launch_bounds__(128) kda_step_kernel(const KdaParams p) {
+__global__ void __launch_bounds__(128, 5) kda_step_kernel(const KdaParams p) {
     __shared__ float red[4];
     __shared__ __align__(16) float qs[128], ks[128], gs[128], ys[128];
     __shared__ float vs[128];

@@ -147,7 +147,7 @@ __global__ void __launch_bounds__(kThreads, Fmt<FMT>::kCtasPerSM) w4_gemm_kernel
             const int pre = n < kStages ? n : kStages;
             // the weights depend on no earlier kernel: start streaming before waiting for the producer of x
             for (int i = 0; i < pre; i++) {
-                mbar_expect_tx(&full[i], kStageBytes);
+                mbar_expect_tx(&full[i], kWStageBytes + kXRecBytes);
                 tma_bulk_g2s(smem + (size_t)i * kStageBytes, wsrc + (size_t)i * kWStageBytes, kWStageBytes, &full[i]);
             }
             pdl_launch_dependents();
@@ -160,7 +160,7 @@ __global__ void __launch_bounds__(kThreads, Fmt<FMT>::kCtasPerSM) w4_gemm_kernel
                 const int st = i % kStages;
                 if (!mbar_wait(&empty[st], ((i / kStages) - 1) & 1)) break;
                 const int kg = (int)((t0 + i) % p.G);
-                mbar_expect_tx(&full[st], kStageBytes);
+                mbar_expect_tx(&full[st], kWStageBytes + kXRecBytes);
                 tma_bulk_g2s(smem + (size_t)st * kStageBytes, wsrc + (size_t)i * kWStageBytes, kWStageBytes, &full[st]);
                 tma_bulk_g2s(smem + (size_t)st * kStageBytes + kWStageBytes, p.xrec + (size_t)kg * kXRecBytes, kXRecBytes, &full[st]);
             }
