@@ -256,9 +256,21 @@ def run_ours(a):
     step_bytes = (model.weight_bytes() + bc.state_bytes_per_step()) * world   # every rank streams its own shard
     launches = bc.kernels_per_step  # counted by the library while the step was captured
 
-    if rank != 0:
+    def leave():
+        # Every rank is past its last collective here. The step's CUDA graphs hold captured NCCL kernels, so they are
+        # released before the communicator goes away.
         if world > 1:
-            dist.destroy_process_group()
+            bc.graphs.clear()
+            barrier()
+            th = threading.Thread(target=dist.destroy_process_group, daemon=True)
+            th.start()
+            th.join(20.0)
+            if th.is_alive():   # a communicator that will not shut down must not keep a finished run from exiting
+                sys.stdout.flush()
+                os._exit(0)
+
+    if rank != 0:
+        leave()
         return
     cpu = cpu_sample() if (world == 1 and not a.no_cpu) else None
     line = {
@@ -267,7 +279,8 @@ def run_ours(a):
         "data": "synthetic",
         "config": {"workload": f"volundr-32b-shaped W4 g64, {args.num_hidden_layers} layers, {B} ragged rows "
                                f"(ctx {min(ctx)}..{max(ctx)}), greedy decode step",
-                   "parallelism": f"tp{world}", "l2": "inputs larger than L2 (weights >= 18 GB per step)",
+                   "parallelism": f"tp{world}" + ("" if world == 1 else (" exchange in the consuming kernels over peer memory"
+                                                                                 if bc.ar is not None else " NCCL all-reduce")), "l2": "inputs larger than L2 (weights >= 18 GB per step)",
                    "bytes_per_step": step_bytes, "hbm_roofline_frac": step_bytes / (ms_dev * 1e-3) / 1e9 / (peak * world),
                    "hbm_roofline_frac_nominal_8TBs": step_bytes / (ms_dev * 1e-3) / 1e9 / (8000.0 * world)},
         "e2e": {"value": B * 1e3 / ms_e2e, "unit": "tok/s", "h2d_bytes_per_step": B * 4, "d2h_bytes_per_step": B * 4},
@@ -280,8 +293,7 @@ def run_ours(a):
     if cpu is not None:
         line["cpu_baseline"] = cpu
     print(json.dumps(line), flush=True)
-    if world > 1:
-        dist.destroy_process_group()
+    leave()
 
 
 def main():

@@ -116,6 +116,41 @@ int vk_argmax(const void* logits, int ld, int valid, int* out, int B, vk_stream_
 int vk_argmax_pairs(const void* logits, int ld, int valid, int index_offset, int* pairs, int B, vk_stream_t stream);
 int vk_argmax_merge(const int* pairs, int n_ranks, int* out, int B, vk_stream_t stream);
 
+/* ---- Tensor-parallel exchange inside the consuming kernel (no counterpart in the single-GPU reference). The ranks of
+ * one node hold partial products of the row-parallel linears (out_proj / o_proj, down_proj). Instead of a separate
+ * all-reduce, the kernel that consumes the sum (vk_add_rmsnorm_ar, vk_mhc_boundary_ar, vk_mhc_combine_norm_ar: one CTA
+ * per row) pushes its partial row into every peer's region with peer stores, raises a flag there, waits (bounded) for
+ * the peers' flags and adds the rows in rank order; the bf16 sum replaces the partial row in `r` / `m`, which is
+ * therefore not const. Set-up per rank: vk_ar_alloc a region of vk_ar_region_bytes, pass the 64-byte handle to the
+ * other ranks (any host channel), vk_ar_open theirs, vk_ar_fill the descriptor, synchronise the ranks once (host
+ * barrier) before the first step. Per step: `call` = 0 .. calls_per_step - 1 in the same order on every rank, then
+ * vk_ar_advance once. A wait that runs out sets status 4 (vk_status_fetch) and the step's results are invalid.
+ * A null descriptor, or world 1, means no exchange: the _ar entry points then equal the plain ones. */
+typedef struct vk_ar_desc {
+    int world, rank, rows, row_elems, calls_per_step;
+    unsigned spin_limit;   /* polls (>= 100 ns each) before a wait gives up; vk_ar_fill sets a default of seconds */
+    void* slots[8];
+    int* flags[8];
+    int* step;
+} vk_ar_desc;
+size_t vk_ar_region_bytes(int world, int rows, int D);   /* 0: unsupported (world <= 8, world * rows <= 1008) */
+int vk_ar_alloc(size_t bytes, void** ptr, void* handle64);
+int vk_ar_open(const void* handle64, void** ptr);
+int vk_ar_close(void* ptr);
+int vk_ar_free(void* ptr);
+int vk_ar_fill(vk_ar_desc* d, int world, int rank, int rows, int D, int calls_per_step, void* const* bases);
+int vk_ar_advance(const vk_ar_desc* d, vk_stream_t stream);
+int vk_add_rmsnorm_ar(const void* x, void* r, const void* w, void* h2, void* hn, void* xrec_hn, int B, int D, float eps,
+                      int offset, const vk_ar_desc* ar, int call, vk_stream_t stream);
+int vk_mhc_combine_norm_ar(void* H, const void* h2, void* m, const void* x_in, const float* post, const float* res,
+                           const void* w_next, void* hn, const void* eng_val, const void* eng_gate_w, const void* eng_gate_b,
+                           void* y_out, int B, int D, int final_norm, float eps, const vk_ar_desc* ar, int call,
+                           vk_stream_t stream);
+int vk_mhc_boundary_ar(void* H, const void* h2, void* m, void* x_in, float* post, float* res, const void* w_next,
+                       const void* eng_val, const void* eng_gate_w, const void* eng_gate_b, const void* w_dyn, const void* pre_s,
+                       const void* post_s, const void* res_s, const void* w_in, void* h, void* xrec_h, int B, int D, int iters,
+                       float eps, const vk_ar_desc* ar, int call, vk_stream_t stream);
+
 /* ---- Kimi Delta Attention decode step (KDA.__call__, volundr.py:388-410: DF.kda_conv_gates decode_fused.py:469-493,
  * kernels.gated_delta_vec kernels.py:446-458, kernels.gated_norm kernels.py:918-928, plus in_proj_b and f_up).
  * proj [B, ldp] = [q | k | v | z (at off_z) | f_down (at off_fd)]; conv [2, slots, 3, C] with *parity naming the

@@ -5,6 +5,7 @@ import os
 import socket
 
 import numpy as np
+import pytest
 import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp
@@ -115,3 +116,16 @@ def test_merge_argmax_ties():
     vals = np.array([[1.0, 3.0], [1.0, 2.0]])
     idxs = np.array([[7, 4], [3, 9]])
     assert sharding.merge_argmax(vals, idxs).tolist() == [3, 4]
+
+
+def test_peer_handle_layout():
+    from volundr_mlx_b200 import peer
+
+    hs = [bytes([r]) * 64 for r in range(4)]
+    for r in range(4):
+        lay = peer.handle_layout(4, r, hs)
+        assert lay[r] is None and [h for h in lay if h is not None] == [hs[p] for p in range(4) if p != r]
+    with pytest.raises(ValueError):
+        peer.handle_layout(4, 0, hs[:3])
+    with pytest.raises(ValueError):
+        peer.handle_layout(2, 0, [b"x" * 63, b"y" * 64])

@@ -33,6 +33,16 @@ SIGNATURES = {
     "vk_engram_gather": (c_int, [c_void_p] * 6 + [c_int, c_int, c_int, c_float, c_void_p]),
     "vk_mhc_combine_norm": (c_int, [c_void_p] * 12 + [c_int, c_int, c_int, c_float, c_void_p]),
     "vk_mhc_boundary": (c_int, [c_void_p] * 17 + [c_int, c_int, c_int, c_float, c_void_p]),
+    "vk_ar_region_bytes": (c_size_t, [c_int, c_int, c_int]),
+    "vk_ar_alloc": (c_int, [c_size_t, c_void_p, c_void_p]),
+    "vk_ar_open": (c_int, [c_void_p, c_void_p]),
+    "vk_ar_close": (c_int, [c_void_p]),
+    "vk_ar_free": (c_int, [c_void_p]),
+    "vk_ar_fill": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]),
+    "vk_ar_advance": (c_int, [c_void_p, c_void_p]),
+    "vk_add_rmsnorm_ar": (c_int, [c_void_p] * 6 + [c_int, c_int, c_float, c_int, c_void_p, c_int, c_void_p]),
+    "vk_mhc_combine_norm_ar": (c_int, [c_void_p] * 12 + [c_int, c_int, c_int, c_float, c_void_p, c_int, c_void_p]),
+    "vk_mhc_boundary_ar": (c_int, [c_void_p] * 17 + [c_int, c_int, c_int, c_float, c_void_p, c_int, c_void_p]),
     "vk_bf16_gemm": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]),
     "vk_argmax": (c_int, [c_void_p, c_int, c_int, c_void_p, c_int, c_void_p]),
     "vk_argmax_pairs": (c_int, [c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_void_p]),

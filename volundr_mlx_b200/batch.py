@@ -132,6 +132,12 @@ class BatchCache:
         self.kernels_per_step = None
         self.use_graph = True
         self.tp_graph = os.environ.get("VK_TP_GRAPH", "1") == "1"   # capture the NCCL all-reduces into the step's graph
+        # Tensor-parallel exchange: inside the consuming kernels over peer memory (default), or NCCL all-reduces between
+        # the kernels (VK_TP_FUSED=0: the baseline the fused form is measured against).
+        self.ar = None
+        if m.tp_size > 1 and os.environ.get("VK_TP_FUSED", "1") == "1":
+            from .peer import PeerExchange
+            self.ar = PeerExchange(m.group, m.tp_rank, m.tp_size, S, D, 2 * len(m.layers), d)
         self.steps = 0
 
     # ------------------------------------------------------------------ membership
@@ -320,8 +326,10 @@ def _launch_step(model: Model, bc: BatchCache, capture=()):
             ck(L.vk_w4_gemm(_p(wt.packed), _p(x), x.stride(0), _p(y), y.stride(0), B, wt.N, wt.K, _p(ws), ws.numel(), st),
                "vk_w4_gemm")
 
+    ar = bc.ar.ref() if bc.ar is not None else None   # exchange inside the consuming kernels
+
     def allreduce(t):
-        if tp:
+        if tp and ar is None:
             torch.distributed.all_reduce(t[:B], group=model.group)
 
     w0 = model.layers[0]
@@ -374,9 +382,9 @@ def _launch_step(model: Model, bc: BatchCache, capture=()):
         mixv = bc.mix[:, :nmix]
         gemm(mixv, w["out"], bc.r, bc.xr_mix)
         allreduce(bc.r)
-        ck(L.vk_add_rmsnorm(_p(bc.x_in), _p(bc.r), _p(w["ln_post"]), _p(bc.h2), _p(bc.hn2), _p(bc.xr_hn2) if fx else None, B, D,
-                            eps, 1, st),
-           "vk_add_rmsnorm")
+        ck(L.vk_add_rmsnorm_ar(_p(bc.x_in), _p(bc.r), _p(w["ln_post"]), _p(bc.h2), _p(bc.hn2), _p(bc.xr_hn2) if fx else None,
+                               B, D, eps, 1, ar, 2 * i, st),
+           "vk_add_rmsnorm_ar")
         gemm(bc.hn2, w["gate_up"], bc.gu, bc.xr_hn2)
         ck(L.vk_silu_mul(_p(bc.gu), None if fx else _p(bc.act), _p(bc.xr_act) if fx else None, B, model.I, bc.gu.stride(0), st),
            "vk_silu_mul")
@@ -397,16 +405,16 @@ def _launch_step(model: Model, bc: BatchCache, capture=()):
         w_next = model.norm_w if last else model.layers[i + 1]["mhc_norm"]
         if fuse_boundary and not last and bc.y_dbg is None:
             wn = model.layers[i + 1]
-            ck(L.vk_mhc_boundary(_p(bc.H), _p(bc.h2), _p(bc.mlp), _p(bc.x_in), _p(bc.post), _p(bc.res), _p(w_next),
-                                 _p(val) if eng else None, _p(w["eng_gate_w"]) if eng else None,
-                                 _p(w["eng_gate_b"]) if eng else None, _p(wn["dyn"]), _p(wn["pre_s"]), _p(wn["post_s"]),
-                                 _p(wn["res_s"]), _p(wn["ln_in"]), _p(bc.h), _p(bc.xr_h) if fx else None, B, D,
-                                 a.mhc_sinkhorn_iters, eps, st), "vk_mhc_boundary")
+            ck(L.vk_mhc_boundary_ar(_p(bc.H), _p(bc.h2), _p(bc.mlp), _p(bc.x_in), _p(bc.post), _p(bc.res), _p(w_next),
+                                    _p(val) if eng else None, _p(w["eng_gate_w"]) if eng else None,
+                                    _p(w["eng_gate_b"]) if eng else None, _p(wn["dyn"]), _p(wn["pre_s"]), _p(wn["post_s"]),
+                                    _p(wn["res_s"]), _p(wn["ln_in"]), _p(bc.h), _p(bc.xr_h) if fx else None, B, D,
+                                    a.mhc_sinkhorn_iters, eps, ar, 2 * i + 1, st), "vk_mhc_boundary_ar")
             continue
-        ck(L.vk_mhc_combine_norm(_p(bc.H), _p(bc.h2), _p(bc.mlp), _p(bc.x_in), _p(bc.post), _p(bc.res), _p(w_next),
-                                 _p(bc.hn), _p(val) if eng else None, _p(w["eng_gate_w"]) if eng else None,
-                                 _p(w["eng_gate_b"]) if eng else None, _p(bc.y_dbg) if bc.y_dbg is not None else None, B, D,
-                                 1 if last else 0, eps, st), "vk_mhc_combine_norm")
+        ck(L.vk_mhc_combine_norm_ar(_p(bc.H), _p(bc.h2), _p(bc.mlp), _p(bc.x_in), _p(bc.post), _p(bc.res), _p(w_next),
+                                    _p(bc.hn), _p(val) if eng else None, _p(w["eng_gate_w"]) if eng else None,
+                                    _p(w["eng_gate_b"]) if eng else None, _p(bc.y_dbg) if bc.y_dbg is not None else None, B,
+                                    D, 1 if last else 0, eps, ar, 2 * i + 1, st), "vk_mhc_combine_norm_ar")
     V = model.vocab_shard
     if isinstance(model.lm_head, ops.BF16Weight):
         ck(L.vk_bf16_gemm_packed(_p(model.lm_head.packed), _p(bc.hn), D, _p(bc.logits), bc.logits.stride(0), B, V, D, _p(ws),
@@ -423,6 +431,8 @@ def _launch_step(model: Model, bc: BatchCache, capture=()):
         torch.distributed.all_gather_into_tensor(gathered, bc.pairs[:B], group=model.group)
         ck(L.vk_argmax_merge(_p(bc.pairs_all), n, _p(bc.greedy), B, st), "vk_argmax_merge")
     ck(L.vk_batch_step_end(_p(bc.pos), _p(bc.parity), B, st), "vk_batch_step_end")
+    if ar is not None:
+        ck(L.vk_ar_advance(ar, st), "vk_ar_advance")
     return caps
 
 
@@ -449,10 +459,14 @@ def forward(model: Model, bc: BatchCache, toks, capture=()):
                 _launch_step(model, bc, capture)
             bc.kernels_per_step = _lib.lib().vk_launch_count(0) - n0
             bc.graphs[key] = g
+            if bc.ar is not None:   # capture takes host time that differs between ranks: line them up before the step
+                torch.distributed.barrier(group=model.group)
         g.replay()
         caps = []
     else:
+        n0 = _lib.lib().vk_launch_count(0)
         caps = _launch_step(model, bc, capture)
+        bc.kernels_per_step = _lib.lib().vk_launch_count(0) - n0
     bc.steps += 1
     bc._pos = [p + 1 for p in bc._pos]
     feats = torch.cat(caps, dim=-1) if caps else None
@@ -482,4 +496,10 @@ def model_warm(model: Model):
     if isinstance(model.lm_head, ops.BF16Weight):
         for M in (1, 16):
             ops.bf16_gemm(torch.zeros((M, model.lm_head.K), dtype=BF16, device=d), model.lm_head)
+    if model.tp_size > 1:   # the communicator's first collectives (connection set-up) must not fall inside a capture
+        t = torch.zeros((16, model.args.hidden_size), dtype=BF16, device=d)
+        torch.distributed.all_reduce(t, group=model.group)
+        pr = torch.zeros((16, 2), dtype=torch.int32, device=d)
+        al = torch.zeros((model.tp_size, 16, 2), dtype=torch.int32, device=d)
+        torch.distributed.all_gather_into_tensor(al, pr, group=model.group)
     torch.cuda.synchronize(d)

@@ -1,0 +1,102 @@
+// One-shot all-reduce of a few activation rows across the GPUs of one node, done INSIDE the kernel that consumes the
+// sum (the residual add + norm after out_proj / o_proj, the layer-boundary kernel after down_proj). Tensor-parallel
+// ranks hold partial products of the row-parallel linears; the reference is single-GPU and has no counterpart.
+//
+// Every rank owns one region of device memory that all ranks have mapped (CUDA IPC):
+//     flags [world][rows] int32        flags[src][b] = sequence number of the last push of rank `src` for row b
+//     slots [4][world][rows][D] bf16   slots[seq & 3][src][b] = the partial row that `src` pushed
+// The CTA that owns row b: (1) stores its partial row into every peer's slots[.][me][b] with plain peer stores over
+// NVLink, (2) system-fence, then writes the sequence number into every peer's flags[me][b], (3) waits - bounded - until
+// its own flags[p][b] carries the number for every peer p, (4) adds the `world` partial rows in rank order in fp32
+// (the same order on every rank: all ranks get the same bits) and leaves the bf16 sum in its local row.
+// The sequence number is step * calls_per_step + call + 1 with `step` a device counter that vk_ar_advance bumps once
+// per decode step, so a captured CUDA graph can be replayed. A rank pushes call k + 1 only after it has seen every
+// peer's flag for call k, and a peer sets that flag only after the kernel of call k - 1 has finished reading, so two
+// slots would do; four are kept.
+// A wait that runs out sets VK_ST_FLAG_TIMEOUT and returns (the sum is then wrong, the host sees the status); once
+// the status word is set, later waits give up at once, so a lost peer costs one time-out and not one per call.
+#pragma once
+#include "common.cuh"
+
+constexpr int kArMaxWorld = 8;
+constexpr int kArSlots = 4;
+constexpr uint32_t kArSpinDefault = 1u << 23;   // polls of >= 100 ns each: several seconds, to ride out host-side skew
+
+// The caller's descriptor (public header: vk_ar_desc). Pointers of rank p are that rank's region as mapped into this
+// process (vk_ar_open), offset by vk_ar_fill.
+typedef struct vk_ar_desc {
+    int world, rank, rows, row_elems, calls_per_step;
+    unsigned spin_limit;           // polls before a wait gives up (vk_ar_fill sets the default)
+    void* slots[8];
+    int* flags[8];
+    int* step;
+} vk_ar_desc;
+
+struct VkArDesc {              // what the kernels get
+    int world, rank, rows, calls_per_step;
+    uint32_t spin_limit;
+    uint8_t* slots[kArMaxWorld];   // slots[p]: base of rank p's slot array (slots[rank] is local)
+    int* flags[kArMaxWorld];       // flags[p]: base of rank p's flag array
+    int* step;                     // local step counter
+};
+
+struct VkArCall {              // kernel argument: descriptor + which call of the step this is (world <= 1: no exchange)
+    VkArDesc d;
+    int call;
+};
+
+__device__ __forceinline__ size_t ar_slot_off(const VkArDesc& d, int slot, int src, int b, int D) {
+    return ((((size_t)slot * d.world + src) * d.rows + b) * (size_t)D) * 2;
+}
+
+// All threads of the CTA that owns row b call this after griddepcontrol.wait. `row` = the rank's partial [D] bf16 in
+// local memory; on return it holds the sum over ranks. D % 8 == 0.
+__device__ __forceinline__ void ar_reduce_row(const VkArCall& a, __nv_bfloat16* row, int b, int D) {
+    const VkArDesc& d = a.d;
+    if (d.world <= 1) return;
+    const int seq = (int)((unsigned)*reinterpret_cast<volatile int*>(d.step) * (unsigned)d.calls_per_step + (unsigned)a.call + 1u);
+    const int slot = seq & (kArSlots - 1);
+    const int nvec = D >> 3;
+    uint4* rowv = reinterpret_cast<uint4*>(row);
+    for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
+        const uint4 val = rowv[v];
+        for (int p = 0; p < d.world; p++) {
+            if (p == d.rank) continue;
+            *reinterpret_cast<uint4*>(d.slots[p] + ar_slot_off(d, slot, d.rank, b, D) + (size_t)v * 16) = val;
+        }
+    }
+    __threadfence_system();
+    __syncthreads();
+    const int t = threadIdx.x;
+    if (t < d.world && t != d.rank) {
+        int* remote = d.flags[t] + d.rank * d.rows + b;
+        asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(remote), "r"(seq) : "memory");
+        const int* mine = d.flags[d.rank] + t * d.rows + b;
+        int seen = 0;
+        bool ok = false;
+        if (*reinterpret_cast<volatile int*>(&g_vk_status) == 0) {
+            for (uint32_t it = 0; it < d.spin_limit; it++) {
+                asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(seen) : "l"(mine) : "memory");
+                if ((int)((unsigned)seen - (unsigned)seq) >= 0) { ok = true; break; }   // wrap-safe "seen >= seq"
+                __nanosleep(100);
+            }
+        }
+        if (!ok) vk_set_status(VK_ST_FLAG_TIMEOUT);
+    }
+    __syncthreads();
+    const uint8_t* local = d.slots[d.rank];
+    for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
+        float s[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        for (int p = 0; p < d.world; p++) {
+            uint4 u;
+            if (p == d.rank) u = rowv[v];
+            else u = __ldcg(reinterpret_cast<const uint4*>(local + ar_slot_off(d, slot, p, b, D)) + v);
+            s[0] += bf_lo(u.x); s[1] += bf_hi(u.x); s[2] += bf_lo(u.y); s[3] += bf_hi(u.y);
+            s[4] += bf_lo(u.z); s[5] += bf_hi(u.z); s[6] += bf_lo(u.w); s[7] += bf_hi(u.w);
+        }
+        uint4 o;
+        o.x = pack_bf2(s[0], s[1]); o.y = pack_bf2(s[2], s[3]); o.z = pack_bf2(s[4], s[5]); o.w = pack_bf2(s[6], s[7]);
+        rowv[v] = o;
+    }
+    __syncthreads();
+}

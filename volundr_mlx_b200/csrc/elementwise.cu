@@ -5,6 +5,7 @@
 // the same values).
 #include "common.cuh"
 #include "xrec.cuh"
+#include "allreduce.cuh"
 
 namespace {
 
@@ -213,16 +214,18 @@ __global__ void __launch_bounds__(1024) mhc_mix_norm_kernel(const MixParams p) {
 
 // ------------------------------------------------------------------------------------------------ add + norm
 // h2 = bf(x + r); hn = bf(h2 * rsqrt(mean h2^2 + eps) * (off + w))      (volundr.py:893-899)
+// Tensor-parallel: r holds this rank's partial product; the row's sum over ranks is formed first (allreduce.cuh).
 __global__ void __launch_bounds__(1024) add_rmsnorm_kernel(const __nv_bfloat16* __restrict__ x,
-                                                           const __nv_bfloat16* __restrict__ r,
+                                                           const __nv_bfloat16* r,
                                                            const __nv_bfloat16* __restrict__ w,
                                                            __nv_bfloat16* __restrict__ h2,
                                                            __nv_bfloat16* __restrict__ hn, uint8_t* __restrict__ xrec_hn,
-                                                           int D, float eps, float offset) {
+                                                           int D, float eps, float offset, const VkArCall ar) {
     __shared__ float red[kRowMaxWarps];
     pdl_launch_dependents();
     pdl_wait();
     const size_t base = (size_t)blockIdx.x * D;
+    if (r != nullptr) ar_reduce_row(ar, const_cast<__nv_bfloat16*>(r) + base, blockIdx.x, D);
     const int k0 = threadIdx.x * 8;
     float ss = 0.f;
     float v0[8];
@@ -345,6 +348,7 @@ struct CombineParams {
     __nv_bfloat16* y_out;          // [B, D] or null (debug / tests)
     int D, final_norm;
     float eps;
+    VkArCall ar;                   // tensor-parallel: m is this rank's partial product, summed over ranks first
 };
 
 __global__ void __launch_bounds__(1024) mhc_combine_norm_kernel(const CombineParams p) {
@@ -353,6 +357,7 @@ __global__ void __launch_bounds__(1024) mhc_combine_norm_kernel(const CombinePar
     pdl_wait();
     const int b = blockIdx.x, D = p.D;
     const size_t base = (size_t)b * D;
+    ar_reduce_row(p.ar, const_cast<__nv_bfloat16*>(p.m) + base, b, D);
     const int k0 = threadIdx.x * 8;
     const int stride = blockDim.x * 8;
     float gate = 0.f;
@@ -459,6 +464,7 @@ __global__ void __launch_bounds__(kBoundaryThreads) mhc_boundary_kernel(const Bo
     const CombineParams& p = q.c;
     const int b = blockIdx.x, D = p.D;
     const size_t base = (size_t)b * D;
+    ar_reduce_row(p.ar, const_cast<__nv_bfloat16*>(p.m) + base, b, D);
     const int k = threadIdx.x * 8;
     const bool on = k < D;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
@@ -747,12 +753,38 @@ int vk_mhc_mix_norm(const void* H, const void* hn, const void* w_dyn, const void
     return (int)vk_launch(mhc_mix_norm_kernel, dim3(B), dim3(row_threads(D)), 0, stream, p);
 }
 
-int vk_add_rmsnorm(const void* x, const void* r, const void* w, void* h2, void* hn, void* xrec_hn, int B, int D, float eps,
-                   int offset, cudaStream_t stream) {
+// descriptor + call index -> kernel argument; a null descriptor (or world 1) means no exchange
+static int ar_call(const vk_ar_desc* ar, int call, int B, int D, VkArCall* out) {
+    *out = VkArCall{};
+    if (ar == nullptr || ar->world <= 1) return VK_OK;
+    if (ar->world > kArMaxWorld || ar->rank < 0 || ar->rank >= ar->world || B > ar->rows || ar->row_elems != D ||
+        call < 0 || call >= ar->calls_per_step || ar->step == nullptr)
+        return VK_EINVAL;
+    out->d.world = ar->world; out->d.rank = ar->rank; out->d.rows = ar->rows; out->d.calls_per_step = ar->calls_per_step;
+    out->d.spin_limit = ar->spin_limit;
+    for (int p = 0; p < ar->world; p++) {
+        if (ar->slots[p] == nullptr || ar->flags[p] == nullptr) return VK_EINVAL;
+        out->d.slots[p] = (uint8_t*)ar->slots[p];
+        out->d.flags[p] = ar->flags[p];
+    }
+    out->d.step = ar->step;
+    out->call = call;
+    return VK_OK;
+}
+
+int vk_add_rmsnorm_ar(const void* x, void* r, const void* w, void* h2, void* hn, void* xrec_hn, int B, int D, float eps,
+                      int offset, const vk_ar_desc* ar, int call, cudaStream_t stream) {
     if (B <= 0 || D <= 0 || D % 8 != 0 || (xrec_hn != nullptr && (D % 64 != 0 || B > 16))) return VK_EINVAL;
+    VkArCall a;
+    if (ar_call(r != nullptr ? ar : nullptr, call, B, D, &a) != VK_OK) return VK_EINVAL;
     return (int)vk_launch(add_rmsnorm_kernel, dim3(B), dim3(row_threads(D)), 0, stream, (const __nv_bfloat16*)x,
                           (const __nv_bfloat16*)r, (const __nv_bfloat16*)w, (__nv_bfloat16*)h2, (__nv_bfloat16*)hn,
-                          (uint8_t*)xrec_hn, D, eps, offset ? 1.f : 0.f);
+                          (uint8_t*)xrec_hn, D, eps, offset ? 1.f : 0.f, a);
+}
+
+int vk_add_rmsnorm(const void* x, const void* r, const void* w, void* h2, void* hn, void* xrec_hn, int B, int D, float eps,
+                   int offset, cudaStream_t stream) {
+    return vk_add_rmsnorm_ar(x, const_cast<void*>(r), w, h2, hn, xrec_hn, B, D, eps, offset, nullptr, 0, stream);
 }
 
 int vk_silu_mul(const void* gu, void* act, void* xrec_act, int B, int I, int ld_gu, cudaStream_t stream) {
@@ -774,33 +806,50 @@ int vk_engram_gather(const void* const* tables, const int* ld_table, const int* 
     return (int)vk_launch(engram_gather_kernel, dim3(B), dim3(kEwThreads), 0, stream, p);
 }
 
-int vk_mhc_combine_norm(void* H, const void* h2, const void* m, const void* x_in, const float* post, const float* res,
-                        const void* w_next, void* hn, const void* eng_val, const void* eng_gate_w, const void* eng_gate_b,
-                        void* y_out, int B, int D, int final_norm, float eps, cudaStream_t stream) {
-    if (B <= 0 || D <= 0) return VK_EINVAL;
+int vk_mhc_combine_norm_ar(void* H, const void* h2, void* m, const void* x_in, const float* post, const float* res,
+                           const void* w_next, void* hn, const void* eng_val, const void* eng_gate_w, const void* eng_gate_b,
+                           void* y_out, int B, int D, int final_norm, float eps, const vk_ar_desc* ar, int call,
+                           cudaStream_t stream) {
+    if (B <= 0 || D <= 0 || D % 8 != 0) return VK_EINVAL;
     CombineParams p = {(__nv_bfloat16*)H, (const __nv_bfloat16*)h2, (const __nv_bfloat16*)m, (const __nv_bfloat16*)x_in,
                        post, res, (const __nv_bfloat16*)w_next, (__nv_bfloat16*)hn, (const __nv_bfloat16*)eng_val,
                        (const __nv_bfloat16*)eng_gate_w, (const __nv_bfloat16*)eng_gate_b, (__nv_bfloat16*)y_out, D,
-                       final_norm, eps};
-    if (D % 8 != 0) return VK_EINVAL;
+                       final_norm, eps, VkArCall{}};
+    if (ar_call(ar, call, B, D, &p.ar) != VK_OK) return VK_EINVAL;
     return (int)vk_launch(mhc_combine_norm_kernel, dim3(B), dim3(row_threads(D)), 0, stream, p);
 }
 
+int vk_mhc_combine_norm(void* H, const void* h2, const void* m, const void* x_in, const float* post, const float* res,
+                        const void* w_next, void* hn, const void* eng_val, const void* eng_gate_w, const void* eng_gate_b,
+                        void* y_out, int B, int D, int final_norm, float eps, cudaStream_t stream) {
+    return vk_mhc_combine_norm_ar(H, h2, const_cast<void*>(m), x_in, post, res, w_next, hn, eng_val, eng_gate_w, eng_gate_b,
+                                  y_out, B, D, final_norm, eps, nullptr, 0, stream);
+}
+
 // mhc_combine_norm of one layer + mhc_mix_norm of the next in one launch (see mhc_boundary_kernel). D / 8 <= 768.
-int vk_mhc_boundary(void* H, const void* h2, const void* m, void* x_in, float* post, float* res, const void* w_next,
-                    const void* eng_val, const void* eng_gate_w, const void* eng_gate_b, const void* w_dyn, const void* pre_s,
-                    const void* post_s, const void* res_s, const void* w_in, void* h, void* xrec_h, int B, int D, int iters,
-                    float eps, cudaStream_t stream) {
+int vk_mhc_boundary_ar(void* H, const void* h2, void* m, void* x_in, float* post, float* res, const void* w_next,
+                       const void* eng_val, const void* eng_gate_w, const void* eng_gate_b, const void* w_dyn, const void* pre_s,
+                       const void* post_s, const void* res_s, const void* w_in, void* h, void* xrec_h, int B, int D, int iters,
+                       float eps, const vk_ar_desc* ar, int call, cudaStream_t stream) {
     if (B <= 0 || D <= 0 || D % 64 != 0 || D / 8 > kBoundaryThreads || (xrec_h != nullptr && B > 16)) return VK_EINVAL;
     BoundaryParams q = {};
     q.c = {(__nv_bfloat16*)H, (const __nv_bfloat16*)h2, (const __nv_bfloat16*)m, (const __nv_bfloat16*)x_in, post, res,
            (const __nv_bfloat16*)w_next, nullptr, (const __nv_bfloat16*)eng_val, (const __nv_bfloat16*)eng_gate_w,
-           (const __nv_bfloat16*)eng_gate_b, nullptr, D, 0, eps};
+           (const __nv_bfloat16*)eng_gate_b, nullptr, D, 0, eps, VkArCall{}};
+    if (ar_call(ar, call, B, D, &q.c.ar) != VK_OK) return VK_EINVAL;
     q.w_dyn = (const __nv_bfloat16*)w_dyn; q.pre_s = (const __nv_bfloat16*)pre_s; q.post_s = (const __nv_bfloat16*)post_s;
     q.res_s = (const __nv_bfloat16*)res_s; q.w_in = (const __nv_bfloat16*)w_in; q.x_in_out = (__nv_bfloat16*)x_in;
     q.h = (__nv_bfloat16*)h; q.xrec_h = (uint8_t*)xrec_h; q.post_out = post; q.res_out = res; q.iters = iters;
     const int threads = ((D / 8 + 31) / 32) * 32;
     return (int)vk_launch(mhc_boundary_kernel, dim3(B), dim3(threads), (size_t)D * 4, stream, q);
+}
+
+int vk_mhc_boundary(void* H, const void* h2, const void* m, void* x_in, float* post, float* res, const void* w_next,
+                    const void* eng_val, const void* eng_gate_w, const void* eng_gate_b, const void* w_dyn, const void* pre_s,
+                    const void* post_s, const void* res_s, const void* w_in, void* h, void* xrec_h, int B, int D, int iters,
+                    float eps, cudaStream_t stream) {
+    return vk_mhc_boundary_ar(H, h2, const_cast<void*>(m), x_in, post, res, w_next, eng_val, eng_gate_w, eng_gate_b, w_dyn,
+                              pre_s, post_s, res_s, w_in, h, xrec_h, B, D, iters, eps, nullptr, 0, stream);
 }
 
 int vk_bf16_gemm(const void* x, int ldx, const void* W, const void* bias, void* y, int ldy, int M, int N, int K,

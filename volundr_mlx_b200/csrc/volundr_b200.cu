@@ -2,5 +2,6 @@
 #include "runtime.cu"
 #include "w4_gemm.cu"
 #include "elementwise.cu"
+#include "allreduce.cu"
 #include "kda.cu"
 #include "attention.cu"
