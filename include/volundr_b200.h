@@ -65,8 +65,10 @@ int vk_bf16_repack(const void* W, int N, int K, void* packed, vk_stream_t stream
 size_t vk_bf16_workspace_bytes(int M, int N, int K);
 int vk_bf16_gemm_packed(const void* packed, const void* x, int ldx, void* y, int ldy, int M, int N, int K, void* workspace,
                         size_t workspace_bytes, vk_stream_t stream);
-/* Testing aid: force the number of persistent CTAs the work is dealt to (0 = two per SM); second argument unused. */
-void vk_w4_force_plan(int ctas, int unused);
+/* Tuning / testing aid: force the number of persistent CTAs the work is dealt to (0 = two per SM), and the budget in
+ * MB of the L2 prefetch a GEMM issues for its own weights before it waits for the kernel that produces x
+ * (0 = default 72, negative = none). Results do not depend on either. */
+void vk_w4_force_plan(int ctas, int prefetch_mb);
 
 /* ---- row-wise fused kernels (one CTA per token row). bf16 activations [B, D] unless noted. An `xrec_*` argument may
  * be NULL; otherwise it receives the same output as x records for a following vk_w4_gemm_xrec (B <= 16). */

@@ -87,7 +87,7 @@ def test_gemm_small(cuda, M):
     _check_gemm(cuda, rng, M, 160, 512, 64)
 
 
-@pytest.mark.parametrize("force", [(1, 0), (2, 0), (5, 0), (37, 0), (148, 0), (1000, 0)])
+@pytest.mark.parametrize("force", [(1, 0), (2, 0), (5, -1), (37, 1), (148, 0), (1000, 0), (0, -1), (0, 1)])
 @pytest.mark.parametrize("group", [64, 128])
 def test_gemm_plans(cuda, force, group):
     rng = np.random.default_rng(7)

@@ -67,6 +67,7 @@ struct W4Params {
     long long T;            // NSB * G steps
     int M, N, NSB, G, P, ldy, maxc;
     int S;                  // > 0: aligned mode, CTA c = (superblock c / S, K slice c % S); 0: contiguous ranges
+    int pf;                 // steps per CTA (beyond the ring) whose weights are prefetched into L2 before the wait for x
 };
 
 __device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
@@ -142,14 +143,24 @@ __global__ void __launch_bounds__(kThreads, Fmt<FMT>::kCtasPerSM) w4_gemm_kernel
 
     if (warp == 0) {
         // ---------------------------------------------------------------- producer
+        const uint8_t* wsrc = p.wp + (size_t)t0 * kWStageBytes;
+        const int pre = n < kStages ? n : kStages;
         if (lane == 0) {
-            const uint8_t* wsrc = p.wp + (size_t)t0 * kWStageBytes;
-            const int pre = n < kStages ? n : kStages;
             // the weights depend on no earlier kernel: start streaming before waiting for the producer of x
             for (int i = 0; i < pre; i++) {
                 mbar_expect_tx(&full[i], kWStageBytes + kXRecBytes);
                 tma_bulk_g2s(smem + (size_t)i * kStageBytes, wsrc + (size_t)i * kWStageBytes, kWStageBytes, &full[i]);
             }
+        }
+        __syncwarp();
+        {   // ... and pull the next steps of this CTA's range into L2 while the kernel before this one still runs: the
+            // memory system is otherwise idle then, and the ring later fills from L2 instead of HBM
+            const int pf_end = n < pre + p.pf ? n : pre + p.pf;
+            for (int i = pre + lane; i < pf_end; i += 32)
+                asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(wsrc + (size_t)i * kWStageBytes), "r"(kWStageBytes)
+                             : "memory");
+        }
+        if (lane == 0) {
             pdl_launch_dependents();
             pdl_wait();
             for (int i = 0; i < pre; i++) {
@@ -537,6 +548,13 @@ __global__ void bf16_repack_kernel(const __nv_bfloat16* __restrict__ W, int N, i
 }
 
 int g_force_ctas = 0;
+int g_prefetch_mb = 72;   // L2 prefetch budget of one GEMM launch (the L2 holds 126 MB)
+
+// steps per CTA beyond the smem ring that fit the prefetch budget
+static int w4_prefetch_steps(int ctas, size_t stage_bytes, int stages) {
+    const long long per_cta = (long long)g_prefetch_mb * 1000000ll / ((long long)ctas * (long long)stage_bytes) - stages;
+    return per_cta < 0 ? 0 : (per_cta > 4096 ? 4096 : (int)per_cta);
+}
 
 struct W4Plan {
     int P, maxc, NSB, G, S;
@@ -606,9 +624,9 @@ int vk_w4_dequant(const void* w, const void* scales, const void* biases, int N, 
     return (int)cudaGetLastError();
 }
 
-void vk_w4_force_plan(int ctas, int unused) {
-    (void)unused;
+void vk_w4_force_plan(int ctas, int prefetch_mb) {
     g_force_ctas = ctas;
+    g_prefetch_mb = prefetch_mb == 0 ? 72 : (prefetch_mb < 0 ? 0 : prefetch_mb);
 }
 
 size_t vk_w4_workspace_bytes(int M, int N, int K) {
@@ -640,6 +658,7 @@ int vk_w4_gemm_xrec(const void* packed, const void* xrec, void* y, int ldy, int 
     p.counters = (int*)ws;
     p.part = (float*)(ws + kCounterBytes + (size_t)pl.G * kXRecBytes);
     p.T = pl.T; p.M = M; p.N = N; p.NSB = pl.NSB; p.G = pl.G; p.P = pl.P; p.ldy = ldy; p.maxc = pl.maxc; p.S = pl.S;
+    p.pf = w4_prefetch_steps(pl.P, (size_t)wstage_bytes<0>(), Fmt<0>::kStages);
     cudaError_t e = M <= 8 ? vk_launch(w4_gemm_kernel<1, 0>, dim3(pl.P), dim3(kThreads), smem_bytes<0>(), stream, p)
                            : vk_launch(w4_gemm_kernel<2, 0>, dim3(pl.P), dim3(kThreads), smem_bytes<0>(), stream, p);
     return (int)e;
@@ -669,6 +688,7 @@ int vk_w4_gemm(const void* packed, const void* x, int ldx, void* y, int ldy, int
         p.counters = (int*)ws;
         p.part = (float*)(ws + kCounterBytes + (size_t)pl.G * kXRecBytes);
         p.T = pl.T; p.M = m; p.N = N; p.NSB = pl.NSB; p.G = pl.G; p.P = pl.P; p.ldy = ldy; p.maxc = pl.maxc; p.S = pl.S;
+        p.pf = w4_prefetch_steps(pl.P, (size_t)wstage_bytes<0>(), Fmt<0>::kStages);
         VK_CUDA(vk_launch(w4_xrec_kernel, dim3(pl.G), dim3(128), 0, stream, (const __nv_bfloat16*)x + (size_t)m0 * ldx, ldx, m,
                           ws + kCounterBytes));
         cudaError_t e = m <= 8 ? vk_launch(w4_gemm_kernel<1, 0>, dim3(pl.P), dim3(kThreads), smem_bytes<0>(), stream, p)
@@ -718,6 +738,7 @@ int vk_bf16_gemm_packed(const void* packed, const void* x, int ldx, void* y, int
         p.counters = (int*)ws;
         p.part = (float*)(ws + kCounterBytes + (size_t)pl.G * kXRecBytes);
         p.T = pl.T; p.M = m; p.N = N; p.NSB = pl.NSB; p.G = pl.G; p.P = pl.P; p.ldy = ldy; p.maxc = pl.maxc; p.S = pl.S;
+        p.pf = w4_prefetch_steps(pl.P, (size_t)wstage_bytes<1>(), Fmt<1>::kStages);
         VK_CUDA(vk_launch(w4_xrec_kernel, dim3(pl.G), dim3(128), 0, stream, (const __nv_bfloat16*)x + (size_t)m0 * ldx, ldx, m,
                           ws + kCounterBytes));
         cudaError_t e = m <= 8 ? vk_launch(w4_gemm_kernel<1, 1>, dim3(pl.P), dim3(kThreads), smem_bytes<1>(), stream, p)
