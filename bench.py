@@ -24,6 +24,9 @@ sys.path.insert(0, str(ROOT))
 
 METRIC = "batched decode tok/s (16 ragged reqs, 32B-shaped W4)"
 B_ROWS = 16
+# dram__bytes_read.sum + dram__bytes_write.sum of w4_gemm_kernel over its algorithmic bytes, from the ncu captures
+# summarised in profiles/w4_gemm_m16_ncu.txt, weighted by the two shapes' bytes
+NCU_TRAFFIC_RATIO = 1.02
 
 
 def measured_peaks():
@@ -180,10 +183,13 @@ def run_ours(a):
     if a.layers:
         full = synth.volundr32b_args()
         kw = dict(num_hidden_layers=a.layers, mixer_types=full.mixer_types[: a.layers],
-                  engram_layers=[i for i in full.engram_layers if i < a.layers])
+                  engram_layers=[])   # (no Engram table: the reduced model is a small case for profiler captures)
     args = synth.volundr32b_args(**kw)
     params = SynthParams(args, dev, seed=4, bias_mode="free")
     model = Model(args, params, dev, tp_rank=rank, tp_size=world, group=group)
+    if a.prefetch_mb:
+        from volundr_mlx_b200 import _lib
+        _lib.lib().vk_w4_force_plan(0, a.prefetch_mb)
     del params
     torch.cuda.empty_cache()
     ctx = context_lengths()
@@ -286,7 +292,10 @@ def run_ours(a):
         "e2e": {"value": B * 1e3 / ms_e2e, "unit": "tok/s", "h2d_bytes_per_step": B * 4, "d2h_bytes_per_step": B * 4},
         "gpu_launches": launches * a.steps,
         "roofline": {"bound": "hbm", "kernel": "w4_gemm_kernel", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                     "frac": achieved / peak, "traffic": None, "peak_kind": peak_kind, "launches_per_step": n_gemm,
+                     "frac": achieved / peak, "traffic": bytes_per_launch * NCU_TRAFFIC_RATIO,
+                     "traffic_source": "ncu dram read+write of two shapes (44032x5120: 1.03x, 5120x5120: 0.99x the "
+                                       "algorithmic bytes), scaled to the average launch",
+                     "peak_kind": peak_kind, "launches_per_step": n_gemm,
                      "bytes_per_launch": bytes_per_launch},
         "clocks": clocks,
     }
@@ -304,6 +313,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=0, help="debug: only the first L layers (the result is then not the metric)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline sample")
+    ap.add_argument("--prefetch-mb", type=int, default=0,
+                    help="tuning: L2 prefetch budget of a GEMM launch in MB (0 = off, the library default)")
     a = ap.parse_args()
     a.warmup = max(a.warmup, 3)
     if a.impl == "reference":

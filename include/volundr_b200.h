@@ -67,7 +67,7 @@ int vk_bf16_gemm_packed(const void* packed, const void* x, int ldx, void* y, int
                         size_t workspace_bytes, vk_stream_t stream);
 /* Tuning / testing aid: force the number of persistent CTAs the work is dealt to (0 = two per SM), and the budget in
  * MB of the L2 prefetch a GEMM issues for its own weights before it waits for the kernel that produces x
- * (0 = default 72, negative = none). Results do not depend on either. */
+ * (0 or negative = none, the default: on B200 the prefetch measured slower than none). Results do not depend on either. */
 void vk_w4_force_plan(int ctas, int prefetch_mb);
 
 /* ---- row-wise fused kernels (one CTA per token row). bf16 activations [B, D] unless noted. An `xrec_*` argument may
@@ -101,7 +101,7 @@ int vk_mhc_combine_norm(void* H, const void* h2, const void* m, const void* x_in
                         void* y_out, int B, int D, int final_norm, float eps, vk_stream_t stream);
 /* vk_mhc_combine_norm of layer i and vk_mhc_mix_norm of layer i + 1 in one launch (VolundrModel._fused_layers runs them
  * back to back, volundr.py:945-948): H, x_in, post, res are updated in place for the next layer; h / xrec_h receive its
- * input norm. Same values as the two separate calls. D / 8 <= 768. */
+ * input norm. Same values as the two separate calls. D / 8 <= 640. */
 int vk_mhc_boundary(void* H, const void* h2, const void* m, void* x_in, float* post, float* res, const void* w_next,
                     const void* eng_val, const void* eng_gate_w, const void* eng_gate_b, const void* w_dyn, const void* pre_s,
                     const void* post_s, const void* res_s, const void* w_in, void* h, void* xrec_h, int B, int D, int iters,
@@ -157,6 +157,7 @@ int vk_mhc_boundary_ar(void* H, const void* h2, void* m, void* x_in, float* post
  * kernels.gated_delta_vec kernels.py:446-458, kernels.gated_norm kernels.py:918-928, plus in_proj_b and f_up).
  * proj [B, ldp] = [q | k | v | z (at off_z) | f_down (at off_fd)]; conv [2, slots, 3, C] with *parity naming the
  * current buffer; S fp32 [slots, HV, 128, 128] updated in place; out [B, HV*128]. */
+int vk_kda_configure(void);   /* once per device, outside stream capture: shared-memory carve-out hint for vk_kda_step */
 int vk_kda_step(const void* proj, int ldp, int off_z, int off_fd, const void* h, const void* w_b, const void* w_fup,
                 const float* conv_w, const float* A_log, const float* dt_bias, const void* norm_w, void* conv,
                 const int* parity, size_t conv_stride, float* S, void* out, void* xrec_out, const float* g_override, int B,
@@ -186,6 +187,8 @@ int vk_attn_prep(const vk_attn_geom* g, const void* proj, int ldp, int off_k, in
                  float eps, vk_stream_t stream);
 /* _block_scores + _topk_blocks (volundr.py:601-618; kernels.bcsa_scores kernels.py:1227-1240, bcsa_topk :86-98):
  * sel [B, NS, topk] ascending block indices (-1 padded), nsel [B, NS]. scratch: max_blocks uint32 per (row, group). */
+int vk_attn_configure(void);   /* once per device, outside stream capture: shared-memory opt-in of the selection kernel
+                                * (the first vk_bcsa_select on a device does the same) */
 size_t vk_bcsa_select_scratch_bytes(const vk_attn_geom* g, int B, int max_blocks);
 int vk_bcsa_select(const vk_attn_geom* g, const void* q, const void* keys, const int* pos, const int* table, void* scratch,
                    int max_blocks, int* sel, int* nsel, int B, vk_stream_t stream);

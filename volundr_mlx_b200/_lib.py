@@ -2,6 +2,7 @@
 
 There is no CPU or PyTorch fallback behind these calls: a missing library or a non-zero return raises."""
 import ctypes
+import os
 from ctypes import c_int, c_size_t, c_void_p, c_char_p, c_float, c_double
 from pathlib import Path
 
@@ -47,6 +48,8 @@ SIGNATURES = {
     "vk_argmax": (c_int, [c_void_p, c_int, c_int, c_void_p, c_int, c_void_p]),
     "vk_argmax_pairs": (c_int, [c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_void_p]),
     "vk_argmax_merge": (c_int, [c_void_p, c_int, c_void_p, c_int, c_void_p]),
+    "vk_kda_configure": (c_int, []),
+    "vk_attn_configure": (c_int, []),
     "vk_kda_step": (c_int, [c_void_p, c_int, c_int, c_int] + [c_void_p] * 9 + [c_size_t, c_void_p, c_void_p, c_void_p, c_void_p]
                     + [c_int] * 7 + [c_float, c_void_p]),
     "vk_batch_step_begin": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
@@ -71,6 +74,9 @@ def lib():
     """The loaded library; raises if it has not been built (python -m volundr_mlx_b200.build)."""
     global _LIB
     if _LIB is None:
+        global _PATH
+        if os.environ.get("VOLUNDR_B200_LIB"):   # another build of the same library (tuning experiments)
+            _PATH = Path(os.environ["VOLUNDR_B200_LIB"])
         if not _PATH.exists():
             raise RuntimeError(f"{_PATH} is missing: build it with `python -m volundr_mlx_b200.build` "
                                "(there is no fallback path)")

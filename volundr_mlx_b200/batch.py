@@ -316,7 +316,7 @@ def _launch_step(model: Model, bc: BatchCache, capture=()):
     caps = []
 
     fx = bc.fused_xrec
-    fuse_boundary = bc.fuse_boundary and D % 64 == 0 and D // 8 <= 768 and not capture
+    fuse_boundary = bc.fuse_boundary and D % 64 == 0 and D // 8 <= 640 and not capture
 
     def gemm(x, wt, y, xr=None):
         if fx and xr is not None:
@@ -484,6 +484,9 @@ def model_warm(model: Model):
         return
     _warm.add(key)
     d = model.device
+    with torch.cuda.device(d):
+        _lib.check(_lib.lib().vk_kda_configure(), "vk_kda_configure")
+        _lib.check(_lib.lib().vk_attn_configure(), "vk_attn_configure")
     seen = set()
     for w in model.layers:
         for nm in ("proj", "out", "gate_up", "down"):

@@ -226,6 +226,10 @@ struct SelectParams {
     AttnGeom g;
 };
 
+constexpr int kFastBlocks = 512;     // blocks per (row, group) the shared-memory path of the selection holds
+constexpr int kKeyStride = 272;      // bytes between key rows in shared memory (256 + 16: conflict-free 16-byte reads)
+constexpr size_t kSelectSmem = (size_t)kFastBlocks * kKeyStride + 8 * 128 * 4 + kFastBlocks * 4;
+
 __device__ __forceinline__ uint32_t score_key(float s, int j) {
     const uint32_t u = __float_as_uint(s) >> 16;  // s is bf16-valued
     const uint32_t mono = (u & 0x8000u) ? (0xFFFFu - u) : (u | 0x8000u);
@@ -259,6 +263,94 @@ __global__ void __launch_bounds__(256) bcsa_select_kernel(const SelectParams p) 
     const int nh = per_kv ? g.Hq / g.KVH : g.IH;
     const __nv_bfloat16* qb = per_kv ? p.q + ((size_t)b * g.Hq + (size_t)ns * nh) * kD : p.q + (size_t)b * g.IH * kD;
     const int spp = kPage / g.C;  // pooled slots per page
+    if (nv <= kFastBlocks) {
+        // ---- up to 512 blocks (32K tokens at C = 64): everything in shared memory. All key rows are fetched at once
+        // (one round of memory latency instead of one per pass), every thread scores whole blocks, and the k-th
+        // largest key is found by counting. The arithmetic is that of the general path below, addition by addition:
+        // the 32 four-element partial sums of a dot product are combined in the order of the warp's xor tree.
+        extern __shared__ __align__(16) uint8_t dsm[];
+        uint8_t* krows = dsm;                                                    // [nv][272 bytes]
+        float* qsm = reinterpret_cast<float*>(dsm + (size_t)kFastBlocks * kKeyStride);   // [8][128]
+        uint32_t* skeys = reinterpret_cast<uint32_t*>(qsm + 8 * kD);             // [512]
+        for (int idx = threadIdx.x; idx < nv * 16; idx += 256) {
+            const int j = idx >> 4, piece = idx & 15;
+            const int page = p.table[b * g.max_pages + (j / spp)];
+            const __nv_bfloat16* kr = per_kv ? p.keys + (((size_t)page * g.KVH + ns) * spp + j % spp) * kD
+                                             : p.keys + ((size_t)page * spp + j % spp) * kD;
+            cp_async16(krows + (size_t)j * kKeyStride + piece * 16, reinterpret_cast<const uint8_t*>(kr) + piece * 16);
+        }
+        cp_async_commit();
+        for (int i = threadIdx.x; i < nh * kD; i += 256) qsm[i] = bf2f(qb[i]);
+        const int nv4 = (nv + 3) >> 2;
+        for (int i = nv + threadIdx.x; i < nv4 * 4; i += 256) skeys[i] = 0u;   // below every real key
+        cp_async_wait0();
+        __syncthreads();
+        const float inv_nh = 1.f / (float)nh;
+        for (int j = threadIdx.x; j < nv; j += 256) {
+            const uint8_t* kr = krows + (size_t)j * kKeyStride;
+            float sc = 0.f;
+#pragma unroll 1
+            for (int h = 0; h < nh; h++) {
+                const float4* qh = reinterpret_cast<const float4*>(qsm + h * kD);
+                float s1[16];   // s1[l] = partial of "lane" l + partial of "lane" l + 16
+#pragma unroll
+                for (int m = 0; m < 8; m++) {
+                    const uint4 ka = *reinterpret_cast<const uint4*>(kr + m * 16);         // elements 8m .. 8m+7
+                    const uint4 kb = *reinterpret_cast<const uint4*>(kr + 128 + m * 16);   // elements 64+8m .. 64+8m+7
+                    const float4 q0 = qh[2 * m], q1 = qh[2 * m + 1], q2 = qh[16 + 2 * m], q3 = qh[17 + 2 * m];
+                    float a0 = q0.x * bf_lo(ka.x); a0 = fmaf(q0.y, bf_hi(ka.x), a0); a0 = fmaf(q0.z, bf_lo(ka.y), a0); a0 = fmaf(q0.w, bf_hi(ka.y), a0);
+                    float a1 = q1.x * bf_lo(ka.z); a1 = fmaf(q1.y, bf_hi(ka.z), a1); a1 = fmaf(q1.z, bf_lo(ka.w), a1); a1 = fmaf(q1.w, bf_hi(ka.w), a1);
+                    float c0 = q2.x * bf_lo(kb.x); c0 = fmaf(q2.y, bf_hi(kb.x), c0); c0 = fmaf(q2.z, bf_lo(kb.y), c0); c0 = fmaf(q2.w, bf_hi(kb.y), c0);
+                    float c1 = q3.x * bf_lo(kb.z); c1 = fmaf(q3.y, bf_hi(kb.z), c1); c1 = fmaf(q3.z, bf_lo(kb.w), c1); c1 = fmaf(q3.w, bf_hi(kb.w), c1);
+                    s1[2 * m] = a0 + c0;
+                    s1[2 * m + 1] = a1 + c1;
+                }
+#pragma unroll
+                for (int l = 0; l < 8; l++) s1[l] += s1[l + 8];
+#pragma unroll
+                for (int l = 0; l < 4; l++) s1[l] += s1[l + 4];
+                s1[0] += s1[2]; s1[1] += s1[3];
+                sc += bfr(s1[0] + s1[1]);
+            }
+            sc = bfr(sc * inv_nh);
+            sc = bfr(sc * p.scale);
+            skeys[j] = score_key(sc, j);
+        }
+        __syncthreads();
+        if (threadIdx.x == 0) s_base = 0;
+        __syncthreads();
+        for (int j0 = 0; j0 < nv; j0 += 256) {
+            const int j = j0 + threadIdx.x;
+            bool take = false;
+            if (j < nv) {
+                const uint32_t my = skeys[j];
+                int above = 0;
+                for (int i = 0; i < nv4; i++) {
+                    const uint4 v = reinterpret_cast<const uint4*>(skeys)[i];
+                    above += (v.x > my) + (v.y > my) + (v.z > my) + (v.w > my);
+                }
+                take = above < g.topk;
+            }
+            const uint32_t bal = __ballot_sync(0xffffffffu, take);
+            if (lane == 0) wcount[warp] = __popc(bal);
+            __syncthreads();
+            int off = s_base;
+            for (int w = 0; w < warp; w++) off += wcount[w];
+            if (take) {
+                const int r = off + __popc(bal & ((1u << lane) - 1u));
+                if (r < g.topk) sel[r] = j;
+            }
+            __syncthreads();
+            if (threadIdx.x == 0) {
+                int t = 0;
+                for (int w = 0; w < 8; w++) t += wcount[w];
+                s_base += t;
+            }
+            __syncthreads();
+        }
+        if (threadIdx.x == 0) p.nsel[b * g.NS + ns] = g.topk;
+        return;
+    }
     uint32_t* keys = p.scratch + ((size_t)b * g.NS + ns) * p.cap;
     float qv[8][4];  // fully unrolled below, so the heads stay in registers
 #pragma unroll
@@ -383,10 +475,6 @@ struct AttendParams {
 };
 
 constexpr int kRowStride = kD + 8;  // bf16 elements; keeps 16-byte row reads conflict-free
-
-__device__ __forceinline__ void cp_async16(void* dst_smem, const void* src) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst_smem)), "l"(src) : "memory");
-}
 
 template <int G>
 __global__ void __launch_bounds__(128) attend_decode_kernel(const AttendParams p) {
@@ -804,6 +892,22 @@ int vk_attn_prep(const vk_attn_geom* gm, const void* proj, int ldp, int off_k, i
     return (int)vk_launch(attn_prep_kernel, dim3(B), dim3(256), 0, stream, p);
 }
 
+// The selection kernel's shared-memory path needs more than the default 48 KB of dynamic shared memory: opt in once
+// per device (the first selection call on a device must therefore come outside stream capture).
+static bool select_configured() {
+    static bool done[64] = {};
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return false;
+    if (!done[dev]) {
+        if (cudaFuncSetAttribute(bcsa_select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSelectSmem) != cudaSuccess)
+            return false;
+        done[dev] = true;
+    }
+    return true;
+}
+
+int vk_attn_configure(void) { return select_configured() ? VK_OK : VK_EINVAL; }
+
 size_t vk_bcsa_select_scratch_bytes(const vk_attn_geom* gm, int B, int max_blocks) {
     return (size_t)B * (gm->NS > 0 ? gm->NS : 1) * max_blocks * 4;
 }
@@ -815,7 +919,8 @@ int vk_bcsa_select(const vk_attn_geom* gm, const void* q, const void* keys, cons
     p.q = (const __nv_bfloat16*)q; p.keys = (const __nv_bfloat16*)keys; p.pos = pos; p.table = table;
     p.scratch = (uint32_t*)scratch; p.sel = sel; p.nsel = nsel; p.cap = max_blocks; p.n_pages = gm->n_pages;
     p.scale = (float)(1.0 / sqrt((double)kD)); p.g = to_geom(gm);
-    return (int)vk_launch(bcsa_select_kernel, dim3(p.g.NS, B), dim3(256), 0, stream, p);
+    if (!select_configured()) return VK_EINVAL;
+    return (int)vk_launch(bcsa_select_kernel, dim3(p.g.NS, B), dim3(256), kSelectSmem, stream, p);
 }
 
 // ---- far-block selection for callers that cannot allocate
@@ -845,7 +950,8 @@ int vk_bcsa_select_static(const vk_attn_geom* gm, const void* q, const void* key
     p.q = (const __nv_bfloat16*)q; p.keys = (const __nv_bfloat16*)keys; p.pos = pos; p.table = table;
     p.scratch = g_select_scratch_addr[dev]; p.sel = sel; p.nsel = nsel; p.cap = kStaticBlocks; p.n_pages = gm->n_pages;
     p.scale = (float)(1.0 / sqrt((double)kD)); p.g = to_geom(gm);
-    return (int)vk_launch(bcsa_select_kernel, dim3(p.g.NS, B), dim3(256), 0, stream, p);
+    if (!select_configured()) return VK_EINVAL;
+    return (int)vk_launch(bcsa_select_kernel, dim3(p.g.NS, B), dim3(256), kSelectSmem, stream, p);
 }
 
 // 1 (default): both attention products on the tensor cores; 0: the scalar kernel (kept as a cross-check)

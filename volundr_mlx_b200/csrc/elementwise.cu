@@ -30,10 +30,12 @@ __device__ __forceinline__ float row_block_sum(float v, float* red) {
     for (int i = 0; i < nw; i++) t += red[i];
     return t;
 }
-__device__ __forceinline__ void ld8(const __nv_bfloat16* p, float (&x)[8]) {
-    const uint4 u = *reinterpret_cast<const uint4*>(p);
+__device__ __forceinline__ void unpack8(const uint4 u, float (&x)[8]) {
     x[0] = bf_lo(u.x); x[1] = bf_hi(u.x); x[2] = bf_lo(u.y); x[3] = bf_hi(u.y);
     x[4] = bf_lo(u.z); x[5] = bf_hi(u.z); x[6] = bf_lo(u.w); x[7] = bf_hi(u.w);
+}
+__device__ __forceinline__ void ld8(const __nv_bfloat16* p, float (&x)[8]) {
+    unpack8(*reinterpret_cast<const uint4*>(p), x);
 }
 __device__ __forceinline__ void st8(__nv_bfloat16* p, const float (&x)[8]) {
     uint4 u;
@@ -97,6 +99,76 @@ __global__ void __launch_bounds__(kEwThreads) embed_kernel(const EmbedParams p) 
 }
 
 // ------------------------------------------------------------------------------------------------ mHC mix + norm
+// ------------------------------------------------------------------------------------------------ mHC helpers
+// The 24 dyn outputs of one row (bf16 linear D -> 24, volundr.py:302) by the whole CTA. Thread t holds the row's
+// values hn[8 t .. 8 t + 7] (`on` = its piece exists). Order of the sum, the same wherever this is used: the thread's
+// eight products as one fma chain, an xor tree over the warp, then the warps in order. part: [24][32] floats of shared
+// memory; dsm[24] receives the bf16-rounded results (valid after the function's last barrier).
+__device__ __forceinline__ void dyn24(const float (&hv)[8], bool on, int k, const __nv_bfloat16* __restrict__ w_dyn, int D,
+                                      float* part, float* dsm) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = (blockDim.x + 31) >> 5;
+#pragma unroll
+    for (int j0 = 0; j0 < 24; j0 += 8) {
+        float acc[8];
+        uint4 wv[8];
+#pragma unroll
+        for (int j = 0; j < 8; j++)
+            wv[j] = on ? *reinterpret_cast<const uint4*>(w_dyn + (size_t)(j0 + j) * D + k) : make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            float a = hv[0] * bf_lo(wv[j].x);
+            a = fmaf(hv[1], bf_hi(wv[j].x), a);
+            a = fmaf(hv[2], bf_lo(wv[j].y), a);
+            a = fmaf(hv[3], bf_hi(wv[j].y), a);
+            a = fmaf(hv[4], bf_lo(wv[j].z), a);
+            a = fmaf(hv[5], bf_hi(wv[j].z), a);
+            a = fmaf(hv[6], bf_lo(wv[j].w), a);
+            a = fmaf(hv[7], bf_hi(wv[j].w), a);
+            acc[j] = warp_sum(a);
+        }
+        if (lane == 0) {
+#pragma unroll
+            for (int j = 0; j < 8; j++) part[(j0 + j) * 32 + warp] = acc[j];
+        }
+    }
+    __syncthreads();
+    if (threadIdx.x < 24) {
+        float a = 0.f;
+        for (int w = 0; w < nw; w++) a += part[threadIdx.x * 32 + w];
+        dsm[threadIdx.x] = bfr(a);
+    }
+    __syncthreads();
+}
+
+// res = bf(Sinkhorn_iters(exp(l - max))) of one row's 4 x 4 logits l = res_s + d[8:24], pre = bf(pre_s + d[0:4]),
+// post = bf(post_s + d[4:8]) (volundr.py:264-271, :237-243). Called by all 32 lanes of one warp: lane i < 16 owns
+// element (i / 4, i % 4); every row / column sum is formed in the order ((a0 + a1) + a2) + a3 from shuffled copies,
+// the same additions a single thread would do.
+__device__ __forceinline__ void mhc_params_warp(const float* dsm, const __nv_bfloat16* __restrict__ pre_s,
+                                                const __nv_bfloat16* __restrict__ post_s, const __nv_bfloat16* __restrict__ res_s,
+                                                int iters, float* pre_sm, float* post_out, float* res_out) {
+    const int lane = threadIdx.x & 31;
+    const int i = lane & 15, r = i >> 2, c = i & 3;
+    const float l = bf2f(res_s[i]) + dsm[8 + i];
+    float mx = l;
+#pragma unroll
+    for (int o = 8; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    float m = expf(l - mx);
+    for (int it = 0; it < iters; it++) {
+        float a0 = __shfl_sync(0xffffffffu, m, 4 * r), a1 = __shfl_sync(0xffffffffu, m, 4 * r + 1);
+        float a2 = __shfl_sync(0xffffffffu, m, 4 * r + 2), a3 = __shfl_sync(0xffffffffu, m, 4 * r + 3);
+        m = m / fmaxf(((a0 + a1) + a2) + a3, 1e-9f);
+        a0 = __shfl_sync(0xffffffffu, m, c); a1 = __shfl_sync(0xffffffffu, m, 4 + c);
+        a2 = __shfl_sync(0xffffffffu, m, 8 + c); a3 = __shfl_sync(0xffffffffu, m, 12 + c);
+        m = m / fmaxf(((a0 + a1) + a2) + a3, 1e-9f);
+    }
+    if (lane < 16) res_out[i] = bfr(m);
+    if (lane < 4) {
+        pre_sm[lane] = bfr(bf2f(pre_s[lane]) + dsm[lane]);
+        post_out[lane] = bfr(bf2f(post_s[lane]) + dsm[4 + lane]);
+    }
+}
+
 // d = dyn(hn) (bf16 linear D -> 24); pre = bf(pre_s + d[0:4]); post = bf(post_s + d[4:8]);
 // res = bf(Sinkhorn_iters(exp(l - max))), l = res_s + d[8:24]; x_in = bf(((p0 + p1) + p2) + p3), p_s = bf(pre_s H_s);
 // h = bf(x_in * rsqrt(mean x_in^2 + eps) * (1 + w_in)).   (volundr.py:319-322 with :264-278, :237-243, :132-150)
@@ -117,26 +189,19 @@ struct MixParams {
     float eps;
 };
 
-// d[b][j] = bf16(hn[b] . w_dyn[j]), one warp per (row, output)
-__global__ void __launch_bounds__(256) mhc_dyn_kernel(const __nv_bfloat16* __restrict__ hn, const __nv_bfloat16* __restrict__ w_dyn,
-                                                      float* __restrict__ d, int B, int D) {
+// d[b][j] = bf16(hn[b] . w_dyn[j]): one CTA of D / 8 threads per row (dyn24's order of summation). D <= 8192.
+__global__ void __launch_bounds__(1024) mhc_dyn_kernel(const __nv_bfloat16* __restrict__ hn, const __nv_bfloat16* __restrict__ w_dyn,
+                                                       float* __restrict__ d, int B, int D) {
+    __shared__ float part[24 * 32];
+    __shared__ float dsm[24];
     pdl_launch_dependents();
     pdl_wait();
-    const int wid = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
-    if (wid >= B * 24) return;
-    const int b = wid / 24, j = wid - b * 24;
-    const __nv_bfloat16* x = hn + (size_t)b * D;
-    const __nv_bfloat16* w = w_dyn + (size_t)j * D;
-    float a = 0.f;
-    for (int k = lane * 8; k < D; k += 256) {
-        float xv[8], wv[8];
-        ld8(x + k, xv);
-        ld8(w + k, wv);
-#pragma unroll
-        for (int e = 0; e < 8; e++) a = fmaf(xv[e], wv[e], a);
-    }
-    a = warp_sum(a);
-    if (lane == 0) d[wid] = bfr(a);
+    const int b = blockIdx.x, k = threadIdx.x * 8;
+    const bool on = k < D;
+    float hv[8] = {};
+    if (on) ld8(hn + (size_t)b * D + k, hv);
+    dyn24(hv, on, k, w_dyn, D, part, dsm);
+    if (threadIdx.x < 24) d[b * 24 + threadIdx.x] = dsm[threadIdx.x];
 }
 
 __global__ void __launch_bounds__(1024) mhc_mix_norm_kernel(const MixParams p) {
@@ -146,32 +211,9 @@ __global__ void __launch_bounds__(1024) mhc_mix_norm_kernel(const MixParams p) {
     pdl_wait();
     const int b = blockIdx.x;
     const int D = p.D;
-    if (threadIdx.x == 0) {
-        const float* dsm = p.d + b * 24;
-        float m[16];
-        float mx = -INFINITY;
-        for (int k = 0; k < 16; k++) {
-            m[k] = bf2f(p.res_s[k]) + dsm[8 + k];
-            mx = fmaxf(mx, m[k]);
-        }
-        for (int k = 0; k < 16; k++) m[k] = expf(m[k] - mx);
-        for (int it = 0; it < p.iters; it++) {
-            for (int r = 0; r < 4; r++) {
-                const float s = fmaxf(((m[4 * r] + m[4 * r + 1]) + m[4 * r + 2]) + m[4 * r + 3], 1e-9f);
-                for (int c = 0; c < 4; c++) m[4 * r + c] = m[4 * r + c] / s;
-            }
-            for (int c = 0; c < 4; c++) {
-                const float s = fmaxf(((m[c] + m[4 + c]) + m[8 + c]) + m[12 + c], 1e-9f);
-                for (int r = 0; r < 4; r++) m[4 * r + c] = m[4 * r + c] / s;
-            }
-        }
-        for (int k = 0; k < 16; k++) p.res[b * 16 + k] = bfr(m[k]);
-        for (int s = 0; s < 4; s++) {
-            pre_sm[s] = bfr(bf2f(p.pre_s[s]) + dsm[s]);
-            p.post[b * 4 + s] = bfr(bf2f(p.post_s[s]) + dsm[4 + s]);
-        }
-    }
-    // (threads other than 0 load their pieces of H meanwhile)
+    if (threadIdx.x < 32)
+        mhc_params_warp(p.d + b * 24, p.pre_s, p.post_s, p.res_s, p.iters, pre_sm, p.post + b * 4, p.res + b * 16);
+    // (the other warps load their pieces of H meanwhile)
     const __nv_bfloat16* Hb = p.H + (size_t)b * 4 * D;
     const int k0 = threadIdx.x * 8;
     float h0[8], h1[8], h2[8], h3[8];
@@ -223,10 +265,12 @@ __global__ void __launch_bounds__(1024) add_rmsnorm_kernel(const __nv_bfloat16* 
                                                            int D, float eps, float offset, const VkArCall ar) {
     __shared__ float red[kRowMaxWarps];
     pdl_launch_dependents();
+    const int k0 = threadIdx.x * 8;
+    float w0[8] = {};
+    if (k0 < D) ld8(w + k0, w0);   // (a weight: fetched while the kernel before this one is still running)
     pdl_wait();
     const size_t base = (size_t)blockIdx.x * D;
     if (r != nullptr) ar_reduce_row(ar, const_cast<__nv_bfloat16*>(r) + base, blockIdx.x, D);
-    const int k0 = threadIdx.x * 8;
     float ss = 0.f;
     float v0[8];
     for (int k = k0; k < D; k += blockDim.x * 8) {
@@ -262,7 +306,12 @@ __global__ void __launch_bounds__(1024) add_rmsnorm_kernel(const __nv_bfloat16* 
                 for (int e = 0; e < 8; e++) v[e] = bfr(v[e] + rv[e]);
             }
         }
-        ld8(w + k, wv);
+        if (k == k0) {
+#pragma unroll
+            for (int e = 0; e < 8; e++) wv[e] = w0[e];
+        } else {
+            ld8(w + k, wv);
+        }
 #pragma unroll
         for (int e = 0; e < 8; e++) o[e] = (v[e] * inv) * (offset + wv[e]);
         st8(hn + base + k, o);
@@ -434,9 +483,9 @@ __global__ void __launch_bounds__(1024) mhc_combine_norm_kernel(const CombinePar
 
 // ------------------------------------------------------------------------------------------------ layer boundary
 // mhc_combine_norm of layer i followed by mhc_dyn + mhc_mix_norm of layer i + 1 in one kernel per row: the new streams
-// stay in registers between the two halves, the mHC norm of their mean goes through shared memory into the 24 dyn dot
-// products, and the next layer's input norm is written as a row and as x records. Same arithmetic, in the same order,
-// as the three separate kernels (VolundrModel._fused_layers, volundr.py:945-948, runs them back to back).
+// stay in registers between the two halves, the mHC norm of their mean stays in registers for the 24 dyn dot
+// products (all warps together), the 4 x 4 Sinkhorn runs on 16 lanes, and the next layer's input norm is written as a
+// row and as x records. Same arithmetic, in the same order, as the three separate kernels (VolundrModel._fused_layers, volundr.py:945-948, runs them back to back).
 struct BoundaryParams {
     CombineParams c;               // layer i (w_next = mhc[i + 1].norm; hn unused)
     const __nv_bfloat16* w_dyn;    // layer i + 1
@@ -452,21 +501,29 @@ struct BoundaryParams {
     int iters;
 };
 
-constexpr int kBoundaryThreads = 768;
+constexpr int kBoundaryThreads = 640;
 
 __global__ void __launch_bounds__(kBoundaryThreads) mhc_boundary_kernel(const BoundaryParams q) {
-    extern __shared__ float hn_sm[];           // [D]
     __shared__ float red[kRowMaxWarps];
+    __shared__ float part[24 * 32];
     __shared__ float dsm[24];
     __shared__ float pre_sm[4];
     pdl_launch_dependents();
-    pdl_wait();
     const CombineParams& p = q.c;
     const int b = blockIdx.x, D = p.D;
     const size_t base = (size_t)b * D;
-    ar_reduce_row(p.ar, const_cast<__nv_bfloat16*>(p.m) + base, b, D);
     const int k = threadIdx.x * 8;
     const bool on = k < D;
+    // weights depend on no earlier kernel: fetch this thread's pieces, and start the 24 dyn rows towards L2, while the
+    // kernel before this one is still running
+    if (threadIdx.x < 24) l2_prefetch_bulk(q.w_dyn + (size_t)threadIdx.x * D, (uint32_t)D * 2u);
+    uint4 w_next_raw = make_uint4(0u, 0u, 0u, 0u), w_in_raw = w_next_raw;
+    if (on) {
+        w_next_raw = *reinterpret_cast<const uint4*>(p.w_next + k);
+        w_in_raw = *reinterpret_cast<const uint4*>(q.w_in + k);
+    }
+    pdl_wait();
+    ar_reduce_row(p.ar, const_cast<__nv_bfloat16*>(p.m) + base, b, D);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
     float gate = 0.f;
     float hv[8] = {}, mv[8] = {}, xv[8] = {};
@@ -516,52 +573,18 @@ __global__ void __launch_bounds__(kBoundaryThreads) mhc_boundary_kernel(const Bo
         for (int s = 0; s < 4; s++) st8(Hb + (size_t)s * D + k, o[s]);
     }
     ss = row_block_sum(ss, red);
+    float hnv[8] = {};
     if (on) {
         const float inv = rsqrtf(ss / (float)D + p.eps);
-        float w[8];
-        ld8(p.w_next + k, w);
+        float w_next8[8];
+        unpack8(w_next_raw, w_next8);
 #pragma unroll
-        for (int e = 0; e < 8; e++) hn_sm[k + e] = bfr((v[e] * inv) * w[e]);   // the next layer's mHC norm, as bf16 values
+        for (int e = 0; e < 8; e++) hnv[e] = bfr((v[e] * inv) * w_next8[e]);   // the next layer's mHC norm, as bf16 values
     }
-    __syncthreads();
-    // ---- dyn: 24 dot products, one warp each (lane-strided pieces, then an xor tree: as mhc_dyn_kernel)
-    for (int j = warp; j < 24; j += nw) {
-        const __nv_bfloat16* w = q.w_dyn + (size_t)j * D;
-        float a = 0.f;
-        for (int kk = lane * 8; kk < D; kk += 256) {
-            float wv[8];
-            ld8(w + kk, wv);
-#pragma unroll
-            for (int e = 0; e < 8; e++) a = fmaf(hn_sm[kk + e], wv[e], a);
-        }
-        a = warp_sum(a);
-        if (lane == 0) dsm[j] = bfr(a);
-    }
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        float m[16];
-        float mx = -INFINITY;
-        for (int i = 0; i < 16; i++) {
-            m[i] = bf2f(q.res_s[i]) + dsm[8 + i];
-            mx = fmaxf(mx, m[i]);
-        }
-        for (int i = 0; i < 16; i++) m[i] = expf(m[i] - mx);
-        for (int it = 0; it < q.iters; it++) {
-            for (int rr = 0; rr < 4; rr++) {
-                const float s = fmaxf(((m[4 * rr] + m[4 * rr + 1]) + m[4 * rr + 2]) + m[4 * rr + 3], 1e-9f);
-                for (int cc = 0; cc < 4; cc++) m[4 * rr + cc] = m[4 * rr + cc] / s;
-            }
-            for (int cc = 0; cc < 4; cc++) {
-                const float s = fmaxf(((m[cc] + m[4 + cc]) + m[8 + cc]) + m[12 + cc], 1e-9f);
-                for (int rr = 0; rr < 4; rr++) m[4 * rr + cc] = m[4 * rr + cc] / s;
-            }
-        }
-        for (int i = 0; i < 16; i++) q.res_out[b * 16 + i] = bfr(m[i]);
-        for (int s = 0; s < 4; s++) {
-            pre_sm[s] = bfr(bf2f(q.pre_s[s]) + dsm[s]);
-            q.post_out[b * 4 + s] = bfr(bf2f(q.post_s[s]) + dsm[4 + s]);
-        }
-    }
+    // ---- dyn of the next layer from the norm just formed (registers), then its mHC parameters on warp 0
+    dyn24(hnv, on, k, q.w_dyn, D, part, dsm);
+    if (threadIdx.x < 32)
+        mhc_params_warp(dsm, q.pre_s, q.post_s, q.res_s, q.iters, pre_sm, q.post_out + b * 4, q.res_out + b * 16);
     __syncthreads();
     float x[8] = {};
     float ss2 = 0.f;
@@ -577,10 +600,10 @@ __global__ void __launch_bounds__(kBoundaryThreads) mhc_boundary_kernel(const Bo
     const float inv2 = rsqrtf(ss2 / (float)D + p.eps);
     float ho[8] = {};
     if (on) {
-        float w[8];
-        ld8(q.w_in + k, w);
+        float w_in8[8];
+        unpack8(w_in_raw, w_in8);
 #pragma unroll
-        for (int e = 0; e < 8; e++) ho[e] = (x[e] * inv2) * (1.f + w[e]);
+        for (int e = 0; e < 8; e++) ho[e] = (x[e] * inv2) * (1.f + w_in8[e]);
         st8(q.h + base + k, ho);
     }
     if (q.xrec_h != nullptr) {   // whole warps take part in the group sums
@@ -745,7 +768,8 @@ int vk_mhc_mix_norm(const void* H, const void* hn, const void* w_dyn, const void
                     const void* res_s, const void* w_in, void* x_in, void* h, void* xrec_h, float* post, float* res,
                     float* d_scratch, int B, int D, int iters, float eps, cudaStream_t stream) {
     if (B <= 0 || D <= 0 || D % 8 != 0 || d_scratch == nullptr || (xrec_h != nullptr && (D % 64 != 0 || B > 16))) return VK_EINVAL;
-    VK_CUDA(vk_launch(mhc_dyn_kernel, dim3((B * 24 + 7) / 8), dim3(256), 0, stream, (const __nv_bfloat16*)hn,
+    if (D > 8192) return VK_ETOOBIG;
+    VK_CUDA(vk_launch(mhc_dyn_kernel, dim3(B), dim3(row_threads(D)), 0, stream, (const __nv_bfloat16*)hn,
                       (const __nv_bfloat16*)w_dyn, d_scratch, B, D));
     MixParams p = {(const __nv_bfloat16*)H, (const __nv_bfloat16*)hn, d_scratch,
                    (const __nv_bfloat16*)pre_s, (const __nv_bfloat16*)post_s, (const __nv_bfloat16*)res_s,
@@ -826,7 +850,7 @@ int vk_mhc_combine_norm(void* H, const void* h2, const void* m, const void* x_in
                                   y_out, B, D, final_norm, eps, nullptr, 0, stream);
 }
 
-// mhc_combine_norm of one layer + mhc_mix_norm of the next in one launch (see mhc_boundary_kernel). D / 8 <= 768.
+// mhc_combine_norm of one layer + mhc_mix_norm of the next in one launch (see mhc_boundary_kernel). D / 8 <= 640.
 int vk_mhc_boundary_ar(void* H, const void* h2, void* m, void* x_in, float* post, float* res, const void* w_next,
                        const void* eng_val, const void* eng_gate_w, const void* eng_gate_b, const void* w_dyn, const void* pre_s,
                        const void* post_s, const void* res_s, const void* w_in, void* h, void* xrec_h, int B, int D, int iters,
@@ -841,7 +865,7 @@ int vk_mhc_boundary_ar(void* H, const void* h2, void* m, void* x_in, float* post
     q.res_s = (const __nv_bfloat16*)res_s; q.w_in = (const __nv_bfloat16*)w_in; q.x_in_out = (__nv_bfloat16*)x_in;
     q.h = (__nv_bfloat16*)h; q.xrec_h = (uint8_t*)xrec_h; q.post_out = post; q.res_out = res; q.iters = iters;
     const int threads = ((D / 8 + 31) / 32) * 32;
-    return (int)vk_launch(mhc_boundary_kernel, dim3(B), dim3(threads), (size_t)D * 4, stream, q);
+    return (int)vk_launch(mhc_boundary_kernel, dim3(B), dim3(threads), 0, stream, q);
 }
 
 int vk_mhc_boundary(void* H, const void* h2, const void* m, void* x_in, float* post, float* res, const void* w_next,

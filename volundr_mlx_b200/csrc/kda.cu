@@ -40,75 +40,65 @@ struct KdaParams {
 
 __device__ __forceinline__ float softplus_f(float x) { return fmaxf(x, 0.f) + log1pf(expf(-fabsf(x))); }
 
+// sum of three values over the 128-thread block in one pass: xor tree per warp, then warps 0..3 in order (the order
+// of block_sum<4>)
+__device__ __forceinline__ void block_sum3(float& a, float& b, float& c, float (*red3)[4]) {
+    a = warp_sum(a); b = warp_sum(b); c = warp_sum(c);
+    const int warp = threadIdx.x >> 5;
+    if ((threadIdx.x & 31) == 0) { red3[0][warp] = a; red3[1][warp] = b; red3[2][warp] = c; }
+    __syncthreads();
+    a = ((red3[0][0] + red3[0][1]) + red3[0][2]) + red3[0][3];
+    b = ((red3[1][0] + red3[1][1]) + red3[1][2]) + red3[1][3];
+    c = ((red3[2][0] + red3[2][1]) + red3[2][2]) + red3[2][3];
+}
+
 __global__ void __launch_bounds__(128, 5) kda_step_kernel(const KdaParams p) {
     __shared__ float red[4];
+    __shared__ float red3[3][4];
     __shared__ __align__(16) float qs[128], ks[128], gs[128], ys[128];
     __shared__ float vs[128];
     __shared__ float fd[256];
+    // the state streams through a ring of two 8-row batches per warp: every lane copies (cp.async) and later reads
+    // only its own 16 bytes of a row, so the ring needs no barrier
+    __shared__ __align__(16) float ring[4][2][8][128];
     pdl_launch_dependents();
-    pdl_wait();
     const int hv = blockIdx.x, b = blockIdx.y;
     const int c = threadIdx.x, lane = c & 31, warp = c >> 5;
     const int rep = p.HV / p.Hk, hk = hv / rep;
     const int KD = p.Hk * 128, C = 2 * KD + p.HV * 128;
+    const int ch[3] = {hk * 128 + c, KD + hk * 128 + c, 2 * KD + hv * 128 + c};
+    // weights depend on no earlier kernel: fetch the small ones, and start the rows of in_proj_b / f_up towards L2,
+    // while the kernel before this one is still running
+    if (c == 0) l2_prefetch_bulk(p.w_b + (size_t)hv * p.D, (uint32_t)p.D * 2u);
+    if (c == 32) l2_prefetch_bulk(p.w_fup + (size_t)hv * 128 * p.rank, 128u * (uint32_t)p.rank * 2u);
+    float4 cw[3];
+#pragma unroll
+    for (int i = 0; i < 3; i++) cw[i] = *reinterpret_cast<const float4*>(p.conv_w + (size_t)ch[i] * 4);
+    const float a_log = p.A_log[hv], dtb = p.dt_bias[hv * 128 + c], nw = bf2f(p.norm_w[c]);
+    pdl_wait();
     const __nv_bfloat16* pr = p.proj + (size_t)b * p.ldp;
     const int par = *p.parity & 1;
     const __nv_bfloat16* conv_in = p.conv + (size_t)par * p.conv_stride;
     __nv_bfloat16* conv_out = p.conv + (size_t)(1 - par) * p.conv_stride;
 
-    // the state does not depend on this step's prologue: start fetching this warp's first rows right away
+    // the state does not depend on this step's prologue: start fetching this warp's first 16 rows right away
     float* Sb = p.S + (((size_t)b * p.HV + hv) * 128) * 128;
-    float4 s_first[8];
 #pragma unroll
-    for (int i = 0; i < 8; i++) s_first[i] = *reinterpret_cast<const float4*>(Sb + (size_t)(warp * 32 + i) * 128 + 4 * lane);
+    for (int bt = 0; bt < 2; bt++) {
+#pragma unroll
+        for (int i = 0; i < 8; i++)
+            cp_async16(&ring[warp][bt][i][4 * lane], Sb + (size_t)(warp * 32 + bt * 8 + i) * 128 + 4 * lane);
+        cp_async_commit();
+    }
 
     for (int i = c; i < p.rank; i += 128) fd[i] = bf2f(pr[p.off_fd + i]);
 
-    // ---- conv + SiLU of this head's q, k, v channel c; new conv state
-    const int ch[3] = {hk * 128 + c, KD + hk * 128 + c, 2 * KD + hv * 128 + c};
-    float s3[3];
-#pragma unroll
-    for (int i = 0; i < 3; i++) {
-        const size_t cb = (size_t)b * 3 * C + ch[i];
-        const __nv_bfloat16 x0 = conv_in[cb], x1 = conv_in[cb + C], x2 = conv_in[cb + 2 * (size_t)C];
-        const __nv_bfloat16 x3 = pr[ch[i]];
-        const float* w = p.conv_w + (size_t)ch[i] * 4;
-        float acc = __fmul_rn(bf2f(x0), w[0]);
-        acc = __fadd_rn(acc, __fmul_rn(bf2f(x1), w[1]));
-        acc = __fadd_rn(acc, __fmul_rn(bf2f(x2), w[2]));
-        acc = __fadd_rn(acc, __fmul_rn(bf2f(x3), w[3]));
-        s3[i] = bfr(acc / (1.f + expf(-acc)));
-        if (i == 2 || hv % rep == 0) {
-            conv_out[cb] = x1;
-            conv_out[cb + C] = x2;
-            conv_out[cb + 2 * (size_t)C] = x3;
-        }
-    }
-    const float ssq = block_sum<4>(s3[0] * s3[0], red);
-    const float ssk = block_sum<4>(s3[1] * s3[1], red);
-    qs[c] = (s3[0] / sqrtf(ssq + 1e-6f)) * 0.08838834764831845f;  // 128^-1/2
-    ks[c] = s3[1] / sqrtf(ssk + 1e-6f);
-    vs[c] = s3[2];
-
-    // ---- decay g[c] and beta
-    __syncthreads();  // fd
-    {
-        const __nv_bfloat16* wr = p.w_fup + (size_t)(hv * 128 + c) * p.rank;
-        float a = 0.f;
-        for (int r = 0; r < p.rank; r += 8) {
-            const uint4 wv = *reinterpret_cast<const uint4*>(wr + r);
-            a = fmaf(bf_lo(wv.x), fd[r], a); a = fmaf(bf_hi(wv.x), fd[r + 1], a);
-            a = fmaf(bf_lo(wv.y), fd[r + 2], a); a = fmaf(bf_hi(wv.y), fd[r + 3], a);
-            a = fmaf(bf_lo(wv.z), fd[r + 4], a); a = fmaf(bf_hi(wv.z), fd[r + 5], a);
-            a = fmaf(bf_lo(wv.w), fd[r + 6], a); a = fmaf(bf_hi(wv.w), fd[r + 7], a);
-        }
-        a = bfr(a);
-        gs[c] = expf(-expf(p.A_log[hv]) * softplus_f(a + p.dt_bias[hv * 128 + c]));
-    }
+    // ---- beta's dot product first: its loads do not depend on anything computed here
     float bdot = 0.f;
     {
         const __nv_bfloat16* wb = p.w_b + (size_t)hv * p.D;
         const __nv_bfloat16* hb = p.h + (size_t)b * p.D;
+#pragma unroll 5
         for (int k = c * 8; k < p.D; k += 1024) {
             const uint4 wv = *reinterpret_cast<const uint4*>(wb + k);
             const uint4 xv = *reinterpret_cast<const uint4*>(hb + k);
@@ -118,8 +108,49 @@ __global__ void __launch_bounds__(128, 5) kda_step_kernel(const KdaParams p) {
             bdot = fmaf(bf_lo(wv.w), bf_lo(xv.w), bdot); bdot = fmaf(bf_hi(wv.w), bf_hi(xv.w), bdot);
         }
     }
-    bdot = bfr(block_sum<4>(bdot, red));   // (also orders the qs/ks/gs/vs writes before the reads below)
+
+    // ---- conv + SiLU of this head's q, k, v channel c; new conv state
+    float s3[3];
+#pragma unroll
+    for (int i = 0; i < 3; i++) {
+        const size_t cb = (size_t)b * 3 * C + ch[i];
+        const __nv_bfloat16 x0 = conv_in[cb], x1 = conv_in[cb + C], x2 = conv_in[cb + 2 * (size_t)C];
+        const __nv_bfloat16 x3 = pr[ch[i]];
+        float acc = __fmul_rn(bf2f(x0), cw[i].x);
+        acc = __fadd_rn(acc, __fmul_rn(bf2f(x1), cw[i].y));
+        acc = __fadd_rn(acc, __fmul_rn(bf2f(x2), cw[i].z));
+        acc = __fadd_rn(acc, __fmul_rn(bf2f(x3), cw[i].w));
+        s3[i] = bfr(acc / (1.f + expf(-acc)));
+        if (i == 2 || hv % rep == 0) {
+            conv_out[cb] = x1;
+            conv_out[cb + C] = x2;
+            conv_out[cb + 2 * (size_t)C] = x3;
+        }
+    }
+    float ssq = s3[0] * s3[0], ssk = s3[1] * s3[1];
+    block_sum3(ssq, ssk, bdot, red3);   // (its barrier also publishes fd)
+    qs[c] = (s3[0] / sqrtf(ssq + 1e-6f)) * 0.08838834764831845f;  // 128^-1/2
+    ks[c] = s3[1] / sqrtf(ssk + 1e-6f);
+    vs[c] = s3[2];
+
+    // ---- decay g[c] and beta
+    {
+        const __nv_bfloat16* wr = p.w_fup + (size_t)(hv * 128 + c) * p.rank;
+        float a = 0.f;
+#pragma unroll 4
+        for (int r = 0; r < p.rank; r += 8) {
+            const uint4 wv = *reinterpret_cast<const uint4*>(wr + r);
+            a = fmaf(bf_lo(wv.x), fd[r], a); a = fmaf(bf_hi(wv.x), fd[r + 1], a);
+            a = fmaf(bf_lo(wv.y), fd[r + 2], a); a = fmaf(bf_hi(wv.y), fd[r + 3], a);
+            a = fmaf(bf_lo(wv.z), fd[r + 4], a); a = fmaf(bf_hi(wv.z), fd[r + 5], a);
+            a = fmaf(bf_lo(wv.w), fd[r + 6], a); a = fmaf(bf_hi(wv.w), fd[r + 7], a);
+        }
+        a = bfr(a);
+        gs[c] = expf(-expf(a_log) * softplus_f(a + dtb));
+    }
+    bdot = bfr(bdot);
     float beta = 1.f / (1.f + expf(-bdot));
+    __syncthreads();   // qs / ks / gs / vs
     float4 g4 = *reinterpret_cast<const float4*>(gs + 4 * lane);
     if (p.g_override != nullptr && p.g_override[b] == 0.f) {  // replay past the accepted prefix: g = 1, beta = 0
         beta = 0.f;
@@ -130,11 +161,18 @@ __global__ void __launch_bounds__(128, 5) kda_step_kernel(const KdaParams p) {
     const float4 k4 = *reinterpret_cast<const float4*>(ks + 4 * lane);
     const float4 q4 = *reinterpret_cast<const float4*>(qs + 4 * lane);
 #pragma unroll 1
-    for (int r0 = warp * 32; r0 < warp * 32 + 32; r0 += 8) {
+    for (int bt = 0; bt < 4; bt++) {
+        const int r0 = warp * 32 + bt * 8;
+        cp_async_wait1();   // every group but the newest has landed: batch bt is in the ring
         float4 s[8];
 #pragma unroll
-        for (int i = 0; i < 8; i++)
-            s[i] = r0 == warp * 32 ? s_first[i] : *reinterpret_cast<const float4*>(Sb + (size_t)(r0 + i) * 128 + 4 * lane);
+        for (int i = 0; i < 8; i++) s[i] = *reinterpret_cast<const float4*>(&ring[warp][bt & 1][i][4 * lane]);
+        if (bt + 2 < 4) {
+#pragma unroll
+            for (int i = 0; i < 8; i++)
+                cp_async16(&ring[warp][bt & 1][i][4 * lane], Sb + (size_t)(r0 + 16 + i) * 128 + 4 * lane);
+        }
+        cp_async_commit();   // (an empty group in the last two rounds keeps the count uniform)
         float kv[8];
 #pragma unroll
         for (int i = 0; i < 8; i++) {
@@ -170,7 +208,7 @@ __global__ void __launch_bounds__(128, 5) kda_step_kernel(const KdaParams p) {
     const float ss = block_sum<4>(yb * yb, red);
     const float inv = rsqrtf(ss * (1.f / 128.f) + p.eps);
     const float z = bf2f(pr[p.off_z + hv * 128 + c]);
-    const float ov = bfr(((yb * inv) * bf2f(p.norm_w[c])) * (z / (1.f + expf(-z))));
+    const float ov = bfr(((yb * inv) * nw) * (z / (1.f + expf(-z))));
     p.out[(size_t)b * p.HV * 128 + hv * 128 + c] = f2bf(ov);
     if (p.xrec_out != nullptr) {
         // this head fills two 64-column groups: element stores, group sums = warp xor tree, then warp 2g + warp 2g+1
@@ -187,6 +225,13 @@ __global__ void __launch_bounds__(128, 5) kda_step_kernel(const KdaParams p) {
 }  // namespace
 
 extern "C" {
+
+// Five CTAs of 36 KB share an SM only with the largest shared-memory carve-out: ask for it once per device, outside
+// any stream capture (a hint: the kernel is correct without it, only slower).
+int vk_kda_configure(void) {
+    VK_CUDA(cudaFuncSetAttribute(kda_step_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
+    return VK_OK;
+}
 
 int vk_kda_step(const void* proj, int ldp, int off_z, int off_fd, const void* h, const void* w_b, const void* w_fup,
                 const float* conv_w, const float* A_log, const float* dt_bias, const void* norm_w, void* conv,

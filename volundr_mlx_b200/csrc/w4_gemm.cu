@@ -46,8 +46,14 @@ constexpr size_t kCounterBytes = 16384;                         // arrival count
 // reference keeps unquantised, convert.py:16-17; the lm_head above all), 4096-byte chunks of 32 rows x 64 columns
 // stored [stripe 2][kstep 4][lane 32][4 u32] = the mma A fragments as they are loaded.
 template <int FMT> struct Fmt;
+#ifndef VK_W4_STAGES
+#define VK_W4_STAGES 8
+#endif
+#ifndef VK_W4_CTAS_PER_SM
+#define VK_W4_CTAS_PER_SM 2
+#endif
 template <> struct Fmt<0> {
-    static constexpr int kChunk = 1152, kStages = 8, kCtasPerSM = 2;
+    static constexpr int kChunk = 1152, kStages = VK_W4_STAGES, kCtasPerSM = VK_W4_CTAS_PER_SM;
     static constexpr int kWStage = kBlocksPerSB * kChunk, kStage = kWStage + kXRecBytes + 16;  // + 16 zero bytes
 };
 template <> struct Fmt<1> {
@@ -548,7 +554,7 @@ __global__ void bf16_repack_kernel(const __nv_bfloat16* __restrict__ W, int N, i
 }
 
 int g_force_ctas = 0;
-int g_prefetch_mb = 72;   // L2 prefetch budget of one GEMM launch (the L2 holds 126 MB)
+int g_prefetch_mb = 0;    // L2 prefetch budget of one GEMM launch in MB; off by default: measured slower (it competes with demand loads)
 
 // steps per CTA beyond the smem ring that fit the prefetch budget
 static int w4_prefetch_steps(int ctas, size_t stage_bytes, int stages) {
@@ -561,7 +567,7 @@ struct W4Plan {
     long long T;
 };
 
-W4Plan w4_plan(int N, int K, int ctas_per_sm = 2) {
+W4Plan w4_plan(int N, int K, int ctas_per_sm = Fmt<0>::kCtasPerSM) {
     W4Plan pl;
     pl.NSB = (N + kSBRows - 1) / kSBRows;
     pl.G = K / 64;
@@ -626,7 +632,7 @@ int vk_w4_dequant(const void* w, const void* scales, const void* biases, int N, 
 
 void vk_w4_force_plan(int ctas, int prefetch_mb) {
     g_force_ctas = ctas;
-    g_prefetch_mb = prefetch_mb == 0 ? 72 : (prefetch_mb < 0 ? 0 : prefetch_mb);
+    g_prefetch_mb = prefetch_mb < 0 ? 0 : prefetch_mb;
 }
 
 size_t vk_w4_workspace_bytes(int M, int N, int K) {
@@ -647,7 +653,9 @@ int vk_w4_gemm_xrec(const void* packed, const void* xrec, void* y, int ldy, int 
     static bool configured = false;
     if (!configured) {
         VK_CUDA(cudaFuncSetAttribute(w4_gemm_kernel<1, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes<0>()));
+        VK_CUDA(cudaFuncSetAttribute(w4_gemm_kernel<1, 0>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
         VK_CUDA(cudaFuncSetAttribute(w4_gemm_kernel<2, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes<0>()));
+        VK_CUDA(cudaFuncSetAttribute(w4_gemm_kernel<2, 0>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
         configured = true;
     }
     uint8_t* ws = (uint8_t*)workspace;
@@ -674,7 +682,9 @@ int vk_w4_gemm(const void* packed, const void* x, int ldx, void* y, int ldy, int
     static bool configured = false;
     if (!configured) {
         VK_CUDA(cudaFuncSetAttribute(w4_gemm_kernel<1, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes<0>()));
+        VK_CUDA(cudaFuncSetAttribute(w4_gemm_kernel<1, 0>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
         VK_CUDA(cudaFuncSetAttribute(w4_gemm_kernel<2, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes<0>()));
+        VK_CUDA(cudaFuncSetAttribute(w4_gemm_kernel<2, 0>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
         configured = true;
     }
     uint8_t* ws = (uint8_t*)workspace;
@@ -725,7 +735,9 @@ int vk_bf16_gemm_packed(const void* packed, const void* x, int ldx, void* y, int
     static bool configured = false;
     if (!configured) {
         VK_CUDA(cudaFuncSetAttribute(w4_gemm_kernel<1, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes<1>()));
+        VK_CUDA(cudaFuncSetAttribute(w4_gemm_kernel<1, 1>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
         VK_CUDA(cudaFuncSetAttribute(w4_gemm_kernel<2, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes<1>()));
+        VK_CUDA(cudaFuncSetAttribute(w4_gemm_kernel<2, 1>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
         configured = true;
     }
     uint8_t* ws = (uint8_t*)workspace;
