@@ -157,6 +157,8 @@ int vk_mhc_boundary_ar(void* H, const void* h2, void* m, void* x_in, float* post
  * kernels.gated_delta_vec kernels.py:446-458, kernels.gated_norm kernels.py:918-928, plus in_proj_b and f_up).
  * proj [B, ldp] = [q | k | v | z (at off_z) | f_down (at off_fd)]; conv [2, slots, 3, C] with *parity naming the
  * current buffer; S fp32 [slots, HV, 128, 128] updated in place; out [B, HV*128]. */
+/* w_fup of vk_kda_step is f_up.weight [HV*128, rank] repacked once at load time to [HV][rank / 8][128][8]. */
+int vk_kda_pack_fup(const void* src, void* dst, int HV, int rank, vk_stream_t stream);
 int vk_kda_configure(void);   /* once per device, outside stream capture: shared-memory carve-out hint for vk_kda_step */
 int vk_kda_step(const void* proj, int ldp, int off_z, int off_fd, const void* h, const void* w_b, const void* w_fup,
                 const float* conv_w, const float* A_log, const float* dt_bias, const void* norm_w, void* conv,

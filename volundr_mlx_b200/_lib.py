@@ -48,6 +48,7 @@ SIGNATURES = {
     "vk_argmax": (c_int, [c_void_p, c_int, c_int, c_void_p, c_int, c_void_p]),
     "vk_argmax_pairs": (c_int, [c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_void_p]),
     "vk_argmax_merge": (c_int, [c_void_p, c_int, c_void_p, c_int, c_void_p]),
+    "vk_kda_pack_fup": (c_int, [c_void_p, c_void_p, c_int, c_int, c_void_p]),
     "vk_kda_configure": (c_int, []),
     "vk_attn_configure": (c_int, []),
     "vk_kda_step": (c_int, [c_void_p, c_int, c_int, c_int] + [c_void_p] * 9 + [c_size_t, c_void_p, c_void_p, c_void_p, c_void_p]

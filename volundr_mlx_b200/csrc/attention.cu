@@ -107,8 +107,9 @@ __device__ __forceinline__ void store4(__nv_bfloat16* p, int lane, const float (
     *reinterpret_cast<uint2*>(p + 4 * lane) = u;
 }
 
-// NeoX rotate-half on the first rd dims of a 128-vector spread 4 per lane, angle = pos * theta^(-2i/rd) in double.
-__device__ __forceinline__ void rope128(float (&x)[4], int lane, int pos, int rd, double log2_theta) {
+// NeoX rotate-half on the first rd dims of a 128-vector spread 4 per lane; cs / sn [rd / 2] hold cos / sin of
+// angle_i = pos * theta^(-2i/rd), computed in double (rope_table).
+__device__ __forceinline__ void rope128(float (&x)[4], int lane, int rd, const double* cs, const double* sn) {
     const int half = rd / 2;
     float other[4];
     // partner lane holds the element half a rotation away
@@ -124,16 +125,40 @@ __device__ __forceinline__ void rope128(float (&x)[4], int lane, int pos, int rd
         const int d = 4 * lane + e;
         if (d < rd) {
             const int i = d < half ? d : d - half;
-            const double ang = (double)pos * exp2(-(2.0 * i / rd) * log2_theta);
-            double sn, cs;
-            sincos(ang, &sn, &cs);
-            const double v = d < half ? (double)x[e] * cs - (double)other[e] * sn : (double)x[e] * cs + (double)other[e] * sn;
+            const double v = d < half ? (double)x[e] * cs[i] - (double)other[e] * sn[i] : (double)x[e] * cs[i] + (double)other[e] * sn[i];
             x[e] = bfr((float)v);
         }
     }
 }
 
+// Mean of the C rows of a closed block, added in order in fp32, times 1/C, rounded once (BCSACache._pool,
+// volundr.py:470-476). Each lane reads the four elements it also wrote for the newest row, so the warp that wrote that
+// row can pool right away.
+__device__ __forceinline__ void pool_rows(const __nv_bfloat16* src, int C, int lane, __nv_bfloat16* dst) {
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int i0 = 0; i0 < C; i0 += 8) {
+        float x[8][4];
+#pragma unroll
+        for (int u = 0; u < 8; u++)
+            if (i0 + u < C) load4(src + (size_t)(i0 + u) * kD, lane, x[u]);
+#pragma unroll
+        for (int u = 0; u < 8; u++) {
+            if (i0 + u < C) {
+#pragma unroll
+                for (int e = 0; e < 4; e++) acc[e] += x[u][e];
+            }
+        }
+    }
+    const float invc = 1.f / (float)C;
+#pragma unroll
+    for (int e = 0; e < 4; e++) acc[e] = bfr(acc[e] * invc);
+    store4(dst, lane, acc);
+}
+
+// One warp per head: grid (rows, ceil(heads / 8)). The warp that writes a row's K (V, indexer key) also forms the
+// pooled mean of the block when this position closes one.
 __global__ void __launch_bounds__(256) attn_prep_kernel(const PrepParams p) {
+    __shared__ double cs_sm[64], sn_sm[64];
     pdl_launch_dependents();
     pdl_wait();
     const int b = blockIdx.x;
@@ -143,72 +168,57 @@ __global__ void __launch_bounds__(256) attn_prep_kernel(const PrepParams p) {
     const int page = p.table[b * g.max_pages + pos / kPage];
     const int row = pos % kPage;
     if (page < 0 || page >= p.n_pages) {
-        if (threadIdx.x == 0) vk_set_status(VK_ST_BAD_INDEX);
+        if (threadIdx.x == 0 && blockIdx.y == 0) vk_set_status(VK_ST_BAD_INDEX);
         return;
     }
+    const int hd0 = blockIdx.y * 8;
+    if (hd0 < g.Hq + g.KVH && threadIdx.x < p.rope_dims / 2) {   // this CTA has heads that rotate
+        const int i = threadIdx.x;
+        const double ang = (double)pos * exp2(-(2.0 * i / p.rope_dims) * p.log2_theta);
+        double sn, cs;
+        sincos(ang, &sn, &cs);
+        cs_sm[i] = cs;
+        sn_sm[i] = sn;
+    }
+    __syncthreads();
     const __nv_bfloat16* pr = p.proj + (size_t)b * p.ldp;
     const int nheads = g.Hq + 2 * g.KVH + (p.idxq ? g.IH + 1 : 0);
-    for (int hd = warp; hd < nheads; hd += 8) {
-        float x[4];
-        if (hd < g.Hq) {                                   // query head: norm, rope
-            load4(pr + (size_t)hd * 2 * kD, lane, x);
-            head_norm128(x, p.q_norm, lane, p.eps);
-            rope128(x, lane, pos, p.rope_dims, p.log2_theta);
-            store4(p.q + ((size_t)b * g.Hq + hd) * kD, lane, x);
-        } else if (hd < g.Hq + g.KVH) {                    // key head: norm, rope, into the page
-            const int kv = hd - g.Hq;
-            load4(pr + p.off_k + (size_t)kv * kD, lane, x);
-            head_norm128(x, p.k_norm, lane, p.eps);
-            rope128(x, lane, pos, p.rope_dims, p.log2_theta);
-            store4(p.K + (((size_t)page * g.KVH + kv) * kPage + row) * kD, lane, x);
-        } else if (hd < g.Hq + 2 * g.KVH) {                // value head: as projected
-            const int kv = hd - g.Hq - g.KVH;
-            load4(pr + p.off_v + (size_t)kv * kD, lane, x);
-            store4(p.V + (((size_t)page * g.KVH + kv) * kPage + row) * kD, lane, x);
-        } else if (hd < g.Hq + 2 * g.KVH + g.IH) {         // indexer query heads
-            const int ih = hd - g.Hq - 2 * g.KVH;
-            load4(p.idxq + ((size_t)b * g.IH + ih) * kD, lane, x);
-            head_norm128(x, p.idx_norm, lane, p.eps);
-            store4(p.qi + ((size_t)b * g.IH + ih) * kD, lane, x);
-        } else {                                           // indexer key of this position -> open block slot
-            load4(p.idxk + (size_t)b * kD, lane, x);
-            head_norm128(x, p.idx_norm, lane, p.eps);
-            store4(p.IK + ((size_t)b * g.C + pos % g.C) * kD, lane, x);
-        }
-    }
-    if (g.W <= 0 || (pos + 1) % g.C != 0) return;
-    // ---- the step closes block pos / C: means of its C rows (added in order in fp32, times 1/C, rounded once)
-    __syncthreads();  // this CTA's K / V / IK writes above are visible to its own reads below
+    const int hd = hd0 + warp;
+    if (hd >= nheads) return;
+    const bool closes = g.W > 0 && (pos + 1) % g.C == 0;
     const int slot = (pos / g.C) % (kPage / g.C);
     const int r0 = row - (g.C - 1);
-    const float invc = 1.f / (float)g.C;
-    const int njobs = 2 * g.KVH + (p.idxq ? 1 : 0);
-    for (int j = warp; j < njobs; j += 8) {
-        float acc[4] = {0.f, 0.f, 0.f, 0.f};
-        if (j < 2 * g.KVH) {
-            const int kv = j >> 1;
-            const __nv_bfloat16* src = (j & 1 ? p.V : p.K) + (((size_t)page * g.KVH + kv) * kPage + r0) * kD;
-            for (int i = 0; i < g.C; i++) {
-                float x[4];
-                load4(src + (size_t)i * kD, lane, x);
-#pragma unroll
-                for (int e = 0; e < 4; e++) acc[e] += x[e];
-            }
-#pragma unroll
-            for (int e = 0; e < 4; e++) acc[e] = bfr(acc[e] * invc);
-            __nv_bfloat16* dst = (j & 1 ? p.PV : p.PK) + (((size_t)page * g.KVH + kv) * (kPage / g.C) + slot) * kD;
-            store4(dst, lane, acc);
-        } else {
-            for (int i = 0; i < g.C; i++) {
-                float x[4];
-                load4(p.IK + ((size_t)b * g.C + i) * kD, lane, x);
-#pragma unroll
-                for (int e = 0; e < 4; e++) acc[e] += x[e];
-            }
-#pragma unroll
-            for (int e = 0; e < 4; e++) acc[e] = bfr(acc[e] * invc);
-            store4(p.BK + ((size_t)page * (kPage / g.C) + slot) * kD, lane, acc);
-        }
+    float x[4];
+    if (hd < g.Hq) {                                   // query head: norm, rope
+        load4(pr + (size_t)hd * 2 * kD, lane, x);
+        head_norm128(x, p.q_norm, lane, p.eps);
+        rope128(x, lane, p.rope_dims, cs_sm, sn_sm);
+        store4(p.q + ((size_t)b * g.Hq + hd) * kD, lane, x);
+    } else if (hd < g.Hq + g.KVH) {                    // key head: norm, rope, into the page
+        const int kv = hd - g.Hq;
+        load4(pr + p.off_k + (size_t)kv * kD, lane, x);
+        head_norm128(x, p.k_norm, lane, p.eps);
+        rope128(x, lane, p.rope_dims, cs_sm, sn_sm);
+        __nv_bfloat16* Kp = p.K + ((size_t)page * g.KVH + kv) * kPage * kD;
+        store4(Kp + (size_t)row * kD, lane, x);
+        if (closes) pool_rows(Kp + (size_t)r0 * kD, g.C, lane, p.PK + (((size_t)page * g.KVH + kv) * (kPage / g.C) + slot) * kD);
+    } else if (hd < g.Hq + 2 * g.KVH) {                // value head: as projected
+        const int kv = hd - g.Hq - g.KVH;
+        load4(pr + p.off_v + (size_t)kv * kD, lane, x);
+        __nv_bfloat16* Vp = p.V + ((size_t)page * g.KVH + kv) * kPage * kD;
+        store4(Vp + (size_t)row * kD, lane, x);
+        if (closes) pool_rows(Vp + (size_t)r0 * kD, g.C, lane, p.PV + (((size_t)page * g.KVH + kv) * (kPage / g.C) + slot) * kD);
+    } else if (hd < g.Hq + 2 * g.KVH + g.IH) {         // indexer query heads
+        const int ih = hd - g.Hq - 2 * g.KVH;
+        load4(p.idxq + ((size_t)b * g.IH + ih) * kD, lane, x);
+        head_norm128(x, p.idx_norm, lane, p.eps);
+        store4(p.qi + ((size_t)b * g.IH + ih) * kD, lane, x);
+    } else {                                           // indexer key of this position -> open block slot
+        load4(p.idxk + (size_t)b * kD, lane, x);
+        head_norm128(x, p.idx_norm, lane, p.eps);
+        __nv_bfloat16* Ip = p.IK + (size_t)b * g.C * kD;
+        store4(Ip + (size_t)(pos % g.C) * kD, lane, x);
+        if (closes) pool_rows(Ip, g.C, lane, p.BK + ((size_t)page * (kPage / g.C) + slot) * kD);
     }
 }
 
@@ -620,16 +630,36 @@ __global__ void __launch_bounds__(128) attend_merge_kernel(const float* __restri
     const int hq = blockIdx.x, b = blockIdx.y, t = threadIdx.x;
     const int G = Hq / KVH, kv = hq / G, h = hq % G;
     const float* base = part + (((size_t)b * KVH + kv) * nsplit) * G * (kD + 2) + (size_t)h * (kD + 2);
+    // (loads in batches of eight independent ones: the splits' partial results sit in L2, and a loop of dependent
+    // loads would pay that latency once per split)
+    const size_t sstride = (size_t)G * (kD + 2);
     float m = -INFINITY;
-    for (int s = 0; s < nsplit; s++) m = fmaxf(m, base[(size_t)s * G * (kD + 2) + kD]);
+    for (int s0 = 0; s0 < nsplit; s0 += 8) {
+        float mv[8];
+#pragma unroll
+        for (int u = 0; u < 8; u++) mv[u] = s0 + u < nsplit ? base[(size_t)(s0 + u) * sstride + kD] : -INFINITY;
+#pragma unroll
+        for (int u = 0; u < 8; u++) m = fmaxf(m, mv[u]);
+    }
     float l = 0.f, o = 0.f;
-    for (int s = 0; s < nsplit; s++) {
-        const float* ps = base + (size_t)s * G * (kD + 2);
-        const float ms = ps[kD];
-        if (ms == -INFINITY) continue;
-        const float w = __expf(ms - m);
-        l = fmaf(ps[kD + 1], w, l);
-        o = fmaf(ps[t], w, o);
+    for (int s0 = 0; s0 < nsplit; s0 += 8) {
+        float mv[8], lv[8], ov8[8];
+#pragma unroll
+        for (int u = 0; u < 8; u++) {
+            const bool in = s0 + u < nsplit;
+            const float* ps = base + (size_t)(in ? s0 + u : 0) * sstride;
+            mv[u] = in ? ps[kD] : -INFINITY;
+            lv[u] = ps[kD + 1];
+            ov8[u] = ps[t];
+        }
+#pragma unroll
+        for (int u = 0; u < 8; u++) {
+            if (mv[u] != -INFINITY) {   // (an empty split holds no sums)
+                const float w = __expf(mv[u] - m);
+                l = fmaf(lv[u], w, l);
+                o = fmaf(ov8[u], w, o);
+            }
+        }
     }
     const float ob = bfr(o / l);
     const float gate = bf2f(proj[(size_t)b * ldp + (size_t)hq * 2 * kD + kD + t]);
@@ -889,7 +919,8 @@ int vk_attn_prep(const vk_attn_geom* gm, const void* proj, int ldp, int off_k, i
     p.BK = (__nv_bfloat16*)BK; p.IK = (__nv_bfloat16*)IK;
     p.ldp = ldp; p.off_k = off_k; p.off_v = off_v; p.n_pages = gm->n_pages; p.rope_dims = rope_dims;
     p.log2_theta = log2(rope_theta); p.eps = eps; p.g = to_geom(gm);
-    return (int)vk_launch(attn_prep_kernel, dim3(B), dim3(256), 0, stream, p);
+    const int nheads = p.g.Hq + 2 * p.g.KVH + (idxq ? p.g.IH + 1 : 0);
+    return (int)vk_launch(attn_prep_kernel, dim3(B, (nheads + 7) / 8), dim3(256), 0, stream, p);
 }
 
 // The selection kernel's shared-memory path needs more than the default 48 KB of dynamic shared memory: opt in once

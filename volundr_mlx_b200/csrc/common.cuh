@@ -22,6 +22,19 @@ enum : int {
 
 __device__ __forceinline__ void vk_set_status(int code) { atomicCAS(&g_vk_status, 0, code); }
 
+// Phase time stamps inside one kernel, for tuning builds only (-DVK_TRACE=<kernel id>): thread 0 of every CTA stores
+// the SM's cycle counter at the marked points; vk_trace_read copies the table out. Compiled out otherwise.
+#ifdef VK_TRACE
+__device__ long long g_vk_trace[4096 * 16];
+#define VK_TS(kernel_id, i)                                                                                      \
+    do {                                                                                                         \
+        if (VK_TRACE == (kernel_id) && threadIdx.x == 0)                                                         \
+            g_vk_trace[(((blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) & 4095) * 16 + (i)] = clock64(); \
+    } while (0)
+#else
+#define VK_TS(kernel_id, i) do { } while (0)
+#endif
+
 // ---------------------------------------------------------------- bf16 <-> fp32 on raw bits
 __device__ __forceinline__ float bf_lo(uint32_t u) { return __uint_as_float(u << 16); }
 __device__ __forceinline__ float bf_hi(uint32_t u) { return __uint_as_float(u & 0xFFFF0000u); }

@@ -524,7 +524,6 @@ __global__ void __launch_bounds__(kBoundaryThreads) mhc_boundary_kernel(const Bo
     }
     pdl_wait();
     ar_reduce_row(p.ar, const_cast<__nv_bfloat16*>(p.m) + base, b, D);
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
     float gate = 0.f;
     float hv[8] = {}, mv[8] = {}, xv[8] = {};
     if (on) { ld8(p.h2 + base + k, hv); ld8(p.m + base + k, mv); ld8(p.x_in + base + k, xv); }

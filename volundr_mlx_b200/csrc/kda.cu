@@ -20,7 +20,7 @@ struct KdaParams {
     const __nv_bfloat16* proj;     // [B, ldp]: q (Hk*128) | k (Hk*128) | v (HV*128) at 0, z at off_z, f_down at off_fd
     const __nv_bfloat16* h;        // [B, D] layer input (for in_proj_b)
     const __nv_bfloat16* w_b;      // [HV, D]
-    const __nv_bfloat16* w_fup;    // [HV*128, rank]
+    const __nv_bfloat16* w_fup;    // packed by vk_kda_pack_fup: [HV][rank / 8][128][8]
     const float* conv_w;           // [C, 4]
     const float* A_log;            // [HV]
     const float* dt_bias;          // [HV*128]
@@ -37,6 +37,8 @@ struct KdaParams {
     int ldp, off_z, off_fd, D, Hk, HV, rank;
     float eps;
 };
+
+constexpr int kBdotPieces = 5;   // 16-byte pieces of the in_proj_b row a thread keeps in registers (hidden <= 5120)
 
 __device__ __forceinline__ float softplus_f(float x) { return fmaxf(x, 0.f) + log1pf(expf(-fabsf(x))); }
 
@@ -63,25 +65,51 @@ __global__ void __launch_bounds__(128, 5) kda_step_kernel(const KdaParams p) {
     __shared__ __align__(16) float ring[4][2][8][128];
     pdl_launch_dependents();
     const int hv = blockIdx.x, b = blockIdx.y;
+    VK_TS(1, 0);
     const int c = threadIdx.x, lane = c & 31, warp = c >> 5;
     const int rep = p.HV / p.Hk, hk = hv / rep;
     const int KD = p.Hk * 128, C = 2 * KD + p.HV * 128;
     const int ch[3] = {hk * 128 + c, KD + hk * 128 + c, 2 * KD + hv * 128 + c};
-    // weights depend on no earlier kernel: fetch the small ones, and start the rows of in_proj_b / f_up towards L2,
-    // while the kernel before this one is still running
-    if (c == 0) l2_prefetch_bulk(p.w_b + (size_t)hv * p.D, (uint32_t)p.D * 2u);
+    // weights depend on no earlier kernel: fetch the small ones (conv taps, this thread's pieces of the in_proj_b
+    // row), and start the head's f_up block towards L2, while the kernel before this one is still running
+    const uint4* fup = reinterpret_cast<const uint4*>(p.w_fup) + (size_t)hv * (p.rank / 8) * 128 + c;
     if (c == 32) l2_prefetch_bulk(p.w_fup + (size_t)hv * 128 * p.rank, 128u * (uint32_t)p.rank * 2u);
     float4 cw[3];
 #pragma unroll
     for (int i = 0; i < 3; i++) cw[i] = *reinterpret_cast<const float4*>(p.conv_w + (size_t)ch[i] * 4);
     const float a_log = p.A_log[hv], dtb = p.dt_bias[hv * 128 + c], nw = bf2f(p.norm_w[c]);
+    const __nv_bfloat16* wb = p.w_b + (size_t)hv * p.D;
+    uint4 wbv[kBdotPieces];
+#pragma unroll
+    for (int i = 0; i < kBdotPieces; i++) {
+        const int k = c * 8 + i * 1024;
+        wbv[i] = k < p.D ? *reinterpret_cast<const uint4*>(wb + k) : make_uint4(0u, 0u, 0u, 0u);
+    }
     pdl_wait();
+    VK_TS(1, 1);
     const __nv_bfloat16* pr = p.proj + (size_t)b * p.ldp;
     const int par = *p.parity & 1;
     const __nv_bfloat16* conv_in = p.conv + (size_t)par * p.conv_stride;
     __nv_bfloat16* conv_out = p.conv + (size_t)(1 - par) * p.conv_stride;
 
-    // the state does not depend on this step's prologue: start fetching this warp's first 16 rows right away
+    // ---- this step's inputs first (they gate the prologue), the state after them: requests are served in order,
+    // and 16 rows of state per warp would otherwise sit in front of every small load
+    const __nv_bfloat16* hb = p.h + (size_t)b * p.D;
+    uint4 hx[kBdotPieces];
+#pragma unroll
+    for (int i = 0; i < kBdotPieces; i++) {
+        const int k = c * 8 + i * 1024;
+        hx[i] = k < p.D ? *reinterpret_cast<const uint4*>(hb + k) : make_uint4(0u, 0u, 0u, 0u);
+    }
+    __nv_bfloat16 cx[3][4];
+#pragma unroll
+    for (int i = 0; i < 3; i++) {
+        const size_t cb = (size_t)b * 3 * C + ch[i];
+        cx[i][0] = conv_in[cb]; cx[i][1] = conv_in[cb + C]; cx[i][2] = conv_in[cb + 2 * (size_t)C];
+        cx[i][3] = pr[ch[i]];
+    }
+    const float z = bf2f(pr[p.off_z + hv * 128 + c]);
+    for (int i = c; i < p.rank; i += 128) fd[i] = bf2f(pr[p.off_fd + i]);
     float* Sb = p.S + (((size_t)b * p.HV + hv) * 128) * 128;
 #pragma unroll
     for (int bt = 0; bt < 2; bt++) {
@@ -91,59 +119,68 @@ __global__ void __launch_bounds__(128, 5) kda_step_kernel(const KdaParams p) {
         cp_async_commit();
     }
 
-    for (int i = c; i < p.rank; i += 128) fd[i] = bf2f(pr[p.off_fd + i]);
-
-    // ---- beta's dot product first: its loads do not depend on anything computed here
+    // ---- beta's dot product
     float bdot = 0.f;
-    {
-        const __nv_bfloat16* wb = p.w_b + (size_t)hv * p.D;
-        const __nv_bfloat16* hb = p.h + (size_t)b * p.D;
-#pragma unroll 5
-        for (int k = c * 8; k < p.D; k += 1024) {
-            const uint4 wv = *reinterpret_cast<const uint4*>(wb + k);
-            const uint4 xv = *reinterpret_cast<const uint4*>(hb + k);
-            bdot = fmaf(bf_lo(wv.x), bf_lo(xv.x), bdot); bdot = fmaf(bf_hi(wv.x), bf_hi(xv.x), bdot);
-            bdot = fmaf(bf_lo(wv.y), bf_lo(xv.y), bdot); bdot = fmaf(bf_hi(wv.y), bf_hi(xv.y), bdot);
-            bdot = fmaf(bf_lo(wv.z), bf_lo(xv.z), bdot); bdot = fmaf(bf_hi(wv.z), bf_hi(xv.z), bdot);
-            bdot = fmaf(bf_lo(wv.w), bf_lo(xv.w), bdot); bdot = fmaf(bf_hi(wv.w), bf_hi(xv.w), bdot);
-        }
+#pragma unroll
+    for (int i = 0; i < kBdotPieces; i++) {
+        const uint4 wv = wbv[i], xv = hx[i];
+        bdot = fmaf(bf_lo(wv.x), bf_lo(xv.x), bdot); bdot = fmaf(bf_hi(wv.x), bf_hi(xv.x), bdot);
+        bdot = fmaf(bf_lo(wv.y), bf_lo(xv.y), bdot); bdot = fmaf(bf_hi(wv.y), bf_hi(xv.y), bdot);
+        bdot = fmaf(bf_lo(wv.z), bf_lo(xv.z), bdot); bdot = fmaf(bf_hi(wv.z), bf_hi(xv.z), bdot);
+        bdot = fmaf(bf_lo(wv.w), bf_lo(xv.w), bdot); bdot = fmaf(bf_hi(wv.w), bf_hi(xv.w), bdot);
     }
+    for (int k = c * 8 + kBdotPieces * 1024; k < p.D; k += 1024) {   // (hidden sizes beyond 8192)
+        const uint4 wv = *reinterpret_cast<const uint4*>(wb + k);
+        const uint4 xv = *reinterpret_cast<const uint4*>(hb + k);
+        bdot = fmaf(bf_lo(wv.x), bf_lo(xv.x), bdot); bdot = fmaf(bf_hi(wv.x), bf_hi(xv.x), bdot);
+        bdot = fmaf(bf_lo(wv.y), bf_lo(xv.y), bdot); bdot = fmaf(bf_hi(wv.y), bf_hi(xv.y), bdot);
+        bdot = fmaf(bf_lo(wv.z), bf_lo(xv.z), bdot); bdot = fmaf(bf_hi(wv.z), bf_hi(xv.z), bdot);
+        bdot = fmaf(bf_lo(wv.w), bf_lo(xv.w), bdot); bdot = fmaf(bf_hi(wv.w), bf_hi(xv.w), bdot);
+    }
+    VK_TS(1, 2);
 
     // ---- conv + SiLU of this head's q, k, v channel c; new conv state
     float s3[3];
 #pragma unroll
     for (int i = 0; i < 3; i++) {
         const size_t cb = (size_t)b * 3 * C + ch[i];
-        const __nv_bfloat16 x0 = conv_in[cb], x1 = conv_in[cb + C], x2 = conv_in[cb + 2 * (size_t)C];
-        const __nv_bfloat16 x3 = pr[ch[i]];
-        float acc = __fmul_rn(bf2f(x0), cw[i].x);
-        acc = __fadd_rn(acc, __fmul_rn(bf2f(x1), cw[i].y));
-        acc = __fadd_rn(acc, __fmul_rn(bf2f(x2), cw[i].z));
-        acc = __fadd_rn(acc, __fmul_rn(bf2f(x3), cw[i].w));
+        float acc = __fmul_rn(bf2f(cx[i][0]), cw[i].x);
+        acc = __fadd_rn(acc, __fmul_rn(bf2f(cx[i][1]), cw[i].y));
+        acc = __fadd_rn(acc, __fmul_rn(bf2f(cx[i][2]), cw[i].z));
+        acc = __fadd_rn(acc, __fmul_rn(bf2f(cx[i][3]), cw[i].w));
         s3[i] = bfr(acc / (1.f + expf(-acc)));
         if (i == 2 || hv % rep == 0) {
-            conv_out[cb] = x1;
-            conv_out[cb + C] = x2;
-            conv_out[cb + 2 * (size_t)C] = x3;
+            conv_out[cb] = cx[i][1];
+            conv_out[cb + C] = cx[i][2];
+            conv_out[cb + 2 * (size_t)C] = cx[i][3];
         }
     }
     float ssq = s3[0] * s3[0], ssk = s3[1] * s3[1];
+    VK_TS(1, 3);
     block_sum3(ssq, ssk, bdot, red3);   // (its barrier also publishes fd)
     qs[c] = (s3[0] / sqrtf(ssq + 1e-6f)) * 0.08838834764831845f;  // 128^-1/2
     ks[c] = s3[1] / sqrtf(ssk + 1e-6f);
     vs[c] = s3[2];
+    VK_TS(1, 4);
 
-    // ---- decay g[c] and beta
+    // ---- decay g[c] and beta. f_up arrives packed (vk_kda_pack_fup): [head][rank / 8][channel][8], so that the 128
+    // channels of a head read consecutive 16-byte pieces
     {
-        const __nv_bfloat16* wr = p.w_fup + (size_t)(hv * 128 + c) * p.rank;
         float a = 0.f;
-#pragma unroll 4
-        for (int r = 0; r < p.rank; r += 8) {
-            const uint4 wv = *reinterpret_cast<const uint4*>(wr + r);
-            a = fmaf(bf_lo(wv.x), fd[r], a); a = fmaf(bf_hi(wv.x), fd[r + 1], a);
-            a = fmaf(bf_lo(wv.y), fd[r + 2], a); a = fmaf(bf_hi(wv.y), fd[r + 3], a);
-            a = fmaf(bf_lo(wv.z), fd[r + 4], a); a = fmaf(bf_hi(wv.z), fd[r + 5], a);
-            a = fmaf(bf_lo(wv.w), fd[r + 6], a); a = fmaf(bf_hi(wv.w), fd[r + 7], a);
+        for (int r0 = 0; r0 < p.rank; r0 += 64) {
+            uint4 wv[8];
+#pragma unroll
+            for (int u = 0; u < 8; u++) wv[u] = r0 + 8 * u < p.rank ? fup[(size_t)(r0 / 8 + u) * 128] : make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+            for (int u = 0; u < 8; u++) {
+                if (r0 + 8 * u < p.rank) {
+                    const int r = r0 + 8 * u;
+                    a = fmaf(bf_lo(wv[u].x), fd[r], a); a = fmaf(bf_hi(wv[u].x), fd[r + 1], a);
+                    a = fmaf(bf_lo(wv[u].y), fd[r + 2], a); a = fmaf(bf_hi(wv[u].y), fd[r + 3], a);
+                    a = fmaf(bf_lo(wv[u].z), fd[r + 4], a); a = fmaf(bf_hi(wv[u].z), fd[r + 5], a);
+                    a = fmaf(bf_lo(wv[u].w), fd[r + 6], a); a = fmaf(bf_hi(wv[u].w), fd[r + 7], a);
+                }
+            }
         }
         a = bfr(a);
         gs[c] = expf(-expf(a_log) * softplus_f(a + dtb));
@@ -151,6 +188,7 @@ __global__ void __launch_bounds__(128, 5) kda_step_kernel(const KdaParams p) {
     bdot = bfr(bdot);
     float beta = 1.f / (1.f + expf(-bdot));
     __syncthreads();   // qs / ks / gs / vs
+    VK_TS(1, 5);
     float4 g4 = *reinterpret_cast<const float4*>(gs + 4 * lane);
     if (p.g_override != nullptr && p.g_override[b] == 0.f) {  // replay past the accepted prefix: g = 1, beta = 0
         beta = 0.f;
@@ -173,6 +211,7 @@ __global__ void __launch_bounds__(128, 5) kda_step_kernel(const KdaParams p) {
                 cp_async16(&ring[warp][bt & 1][i][4 * lane], Sb + (size_t)(r0 + 16 + i) * 128 + 4 * lane);
         }
         cp_async_commit();   // (an empty group in the last two rounds keeps the count uniform)
+        VK_TS(1, 6 + bt);
         float kv[8];
 #pragma unroll
         for (int i = 0; i < 8; i++) {
@@ -204,10 +243,10 @@ __global__ void __launch_bounds__(128, 5) kda_step_kernel(const KdaParams p) {
     __syncthreads();
 
     // ---- gated norm over the value head
+    VK_TS(1, 10);
     const float yb = bfr(ys[c]);
     const float ss = block_sum<4>(yb * yb, red);
     const float inv = rsqrtf(ss * (1.f / 128.f) + p.eps);
-    const float z = bf2f(pr[p.off_z + hv * 128 + c]);
     const float ov = bfr(((yb * inv) * nw) * (z / (1.f + expf(-z))));
     p.out[(size_t)b * p.HV * 128 + hv * 128 + c] = f2bf(ov);
     if (p.xrec_out != nullptr) {
@@ -220,11 +259,32 @@ __global__ void __launch_bounds__(128, 5) kda_step_kernel(const KdaParams p) {
         __syncthreads();
         if ((c & 63) == 0) xrec_store_sum(p.xrec_out, kg, b, red[warp] + red[warp + 1]);
     }
+    VK_TS(1, 11);
 }
 
 }  // namespace
 
+// f_up [HV*128, rank] row-major (the checkpoint's layout) -> [HV][rank / 8][128][8]
+__global__ void kda_pack_fup_kernel(const __nv_bfloat16* __restrict__ src, __nv_bfloat16* __restrict__ dst, int HV, int rank) {
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t total = (size_t)HV * 128 * rank;
+    if (idx >= total) return;
+    const int e = (int)(idx & 7);
+    const int ch = (int)((idx >> 3) & 127);
+    const size_t rest = idx >> 10;
+    const int r8 = (int)(rest % (rank / 8)), hv = (int)(rest / (rank / 8));
+    dst[idx] = src[((size_t)hv * 128 + ch) * rank + r8 * 8 + e];
+}
+
 extern "C" {
+
+// The layout vk_kda_step reads f_up in (coalesced 16-byte pieces per channel). Once at load time.
+int vk_kda_pack_fup(const void* src, void* dst, int HV, int rank, cudaStream_t stream) {
+    if (HV <= 0 || rank <= 0 || rank % 8 != 0 || src == dst) return VK_EINVAL;
+    const size_t total = (size_t)HV * 128 * rank;
+    kda_pack_fup_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>((const __nv_bfloat16*)src, (__nv_bfloat16*)dst, HV, rank);
+    return (int)cudaGetLastError();
+}
 
 // Five CTAs of 36 KB share an SM only with the largest shared-memory carve-out: ask for it once per device, outside
 // any stream capture (a hint: the kernel is correct without it, only slower).

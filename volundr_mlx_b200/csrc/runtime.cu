@@ -37,6 +37,14 @@ const char* vk_status_string(int code) {
 
 int vk_version() { return 1; }
 
+#ifdef VK_TRACE
+int vk_trace_read(long long* host_out) {   // tuning builds only: [4096][16] cycle stamps of the traced kernel's last launch
+    VK_CUDA(cudaDeviceSynchronize());
+    VK_CUDA(cudaMemcpyFromSymbol(host_out, g_vk_trace, sizeof(long long) * 4096 * 16));
+    return VK_OK;
+}
+#endif
+
 // Kernels launched by this library since the last call with reset != 0 (a graph capture counts its kernels once).
 long long vk_launch_count(int reset) {
     const long long n = g_vk_launches;

@@ -169,17 +169,25 @@ __global__ void __launch_bounds__(kThreads, Fmt<FMT>::kCtasPerSM) w4_gemm_kernel
         if (lane == 0) {
             pdl_launch_dependents();
             pdl_wait();
+            // (running group index, stage and parity: this one thread feeds the whole CTA, so its loop carries no
+            // division and no 64-bit arithmetic)
+            int kg = (int)(t0 % p.G);
             for (int i = 0; i < pre; i++) {
-                const int kg = (int)((t0 + i) % p.G);
                 tma_bulk_g2s(smem + (size_t)i * kStageBytes + kWStageBytes, p.xrec + (size_t)kg * kXRecBytes, kXRecBytes, &full[i]);
+                kg = kg + 1 == p.G ? 0 : kg + 1;
             }
+            int st = 0;
+            uint32_t par = 0;   // parity of the "empty" phase awaited next for stage st
+            const uint8_t* wnext = wsrc + (size_t)pre * kWStageBytes;
             for (int i = pre; i < n; i++) {
-                const int st = i % kStages;
-                if (!mbar_wait(&empty[st], ((i / kStages) - 1) & 1)) break;
-                const int kg = (int)((t0 + i) % p.G);
+                if (!mbar_wait(&empty[st], par)) break;
+                uint8_t* dst = smem + (size_t)st * kStageBytes;
                 mbar_expect_tx(&full[st], kWStageBytes + kXRecBytes);
-                tma_bulk_g2s(smem + (size_t)st * kStageBytes, wsrc + (size_t)i * kWStageBytes, kWStageBytes, &full[st]);
-                tma_bulk_g2s(smem + (size_t)st * kStageBytes + kWStageBytes, p.xrec + (size_t)kg * kXRecBytes, kXRecBytes, &full[st]);
+                tma_bulk_g2s(dst, wnext, kWStageBytes, &full[st]);
+                tma_bulk_g2s(dst + kWStageBytes, p.xrec + (size_t)kg * kXRecBytes, kXRecBytes, &full[st]);
+                wnext += kWStageBytes;
+                kg = kg + 1 == p.G ? 0 : kg + 1;
+                if (++st == kStages) { st = 0; par ^= 1u; }
             }
         }
         return;

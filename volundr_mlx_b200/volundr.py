@@ -212,7 +212,12 @@ class Model:
                 w["off_z"] = 2 * Hk * 128 + HV * 128
                 w["off_fd"] = w["off_z"] + HV * 128
                 w["in_proj_b"] = _t(params[P + "in_proj_b.weight"], d, BF16)[ix(sh["b"])].contiguous()
-                w["f_up"] = _t(params[P + "f_up.weight"], d, BF16)[ix(sh["f_up"])].contiguous()
+                fup = _t(params[P + "f_up.weight"], d, BF16)[ix(sh["f_up"])].contiguous()   # [HV*128, rank]
+                w["f_up"] = torch.empty_like(fup)                                             # packed for vk_kda_step
+                with torch.cuda.device(d):
+                    _lib.check(_lib.lib().vk_kda_pack_fup(fup.data_ptr(), w["f_up"].data_ptr(), HV, fup.shape[1],
+                                                          torch.cuda.current_stream().cuda_stream), "vk_kda_pack_fup")
+                    torch.cuda.current_stream().synchronize()
                 w["conv_w"] = _t(params[P + "conv1d.weight"], d, torch.float32)[ix(sh["qkv"])].contiguous()
                 w["A_log"] = _t(params[P + "A_log"], d, torch.float32)[ix(sh["b"])].contiguous()
                 w["dt_bias"] = _t(params[P + "dt_bias"], d, torch.float32)[ix(sh["f_up"])].contiguous()
