@@ -163,7 +163,11 @@ int vk_kda_configure(void);   /* once per device, outside stream capture: shared
 int vk_kda_step(const void* proj, int ldp, int off_z, int off_fd, const void* h, const void* w_b, const void* w_fup,
                 const float* conv_w, const float* A_log, const float* dt_bias, const void* norm_w, void* conv,
                 const int* parity, size_t conv_stride, float* S, void* out, void* xrec_out, const float* g_override, int B,
-                int D, int Hk, int HV, int Dk, int Dv, int rank, float eps, vk_stream_t stream);
+                int D, int Hk, int HV, int Dk, int Dv, int rank, float eps, int early_state, vk_stream_t stream);
+/* early_state = 1 lets the kernel request the first rows of S before it waits for the kernel in front of it (they then
+ * stream in while that kernel finishes). Only valid when every earlier writer of S is known to have completed before
+ * this launch can start: true inside a replayed CUDA graph of one step (the previous step's replay is complete), not
+ * for back-to-back eager steps under programmatic dependent launch. 0 is always safe. */
 
 /* ---- paged ragged attention (64-token pages). */
 typedef struct vk_attn_geom {

@@ -704,8 +704,8 @@ __global__ void __launch_bounds__(128) attend_decode_tc_kernel(const AttendParam
     __shared__ __align__(16) __nv_bfloat16 Ps[16 * kPStride];
     __shared__ float sc[8 * kPage];
     __shared__ float s_aold[8], s_m[8], s_l[8];
-    __shared__ const __nv_bfloat16* rowK[kPage];
-    __shared__ const __nv_bfloat16* rowV[kPage];
+    __shared__ const __nv_bfloat16* rowK[2][kPage];
+    __shared__ const __nv_bfloat16* rowV[2][kPage];
     pdl_launch_dependents();
     pdl_wait();
     const AttnGeom& g = p.g;
@@ -750,9 +750,8 @@ __global__ void __launch_bounds__(128) attend_decode_tc_kernel(const AttendParam
         for (int e = 0; e < 4; e++) o[nt][e] = 0.f;
     if (t < 8) s_aold[t] = 0.f;
 
-    for (int u = split; u < U; u += p.nsplit) {
-        __syncthreads();
-        // ---- which rows make up this unit
+    // Row pointers of a unit (window page, far block's tokens, or 64 pooled far blocks) into rk / rv; returns its rows.
+    auto setup_unit = [&](int u, const __nv_bfloat16** rk, const __nv_bfloat16** rv) -> int {
         int nrows;
         if (u < nwp) {
             const int page = p.table[b * g.max_pages + wp0 + u];
@@ -761,8 +760,8 @@ __global__ void __launch_bounds__(128) attend_decode_tc_kernel(const AttendParam
             nrows = rb - ra + 1;
             if (t < nrows) {
                 const size_t off = (((size_t)page * g.KVH + kv) * kPage + ra + t) * kD;
-                rowK[t] = p.K + off;
-                rowV[t] = p.V + off;
+                rk[t] = p.K + off;
+                rv[t] = p.V + off;
             }
         } else if (g.far_tokens) {
             const int j = sel[u - nwp];
@@ -771,8 +770,8 @@ __global__ void __launch_bounds__(128) attend_decode_tc_kernel(const AttendParam
             nrows = g.C;
             if (t < nrows) {
                 const size_t off = (((size_t)page * g.KVH + kv) * kPage + tok0 % kPage + t) * kD;
-                rowK[t] = p.K + off;
-                rowV[t] = p.V + off;
+                rk[t] = p.K + off;
+                rv[t] = p.V + off;
             }
         } else {
             const int f0 = (u - nwp) * kPage;
@@ -781,17 +780,32 @@ __global__ void __launch_bounds__(128) attend_decode_tc_kernel(const AttendParam
                 const int j = sel[f0 + t];
                 const int page = p.table[b * g.max_pages + (j / spp)];
                 const size_t off = (((size_t)page * g.KVH + kv) * spp + j % spp) * kD;
-                rowK[t] = p.PK + off;
-                rowV[t] = p.PV + off;
+                rk[t] = p.PK + off;
+                rv[t] = p.PV + off;
             }
         }
-        __syncthreads();
+        return nrows;
+    };
+    auto issue_rows = [&](__nv_bfloat16* tile, const __nv_bfloat16* const* rows, int nrows) {
         for (int i = t; i < nrows * 16; i += 128) {
             const int r = i >> 4, cch = i & 15;
-            cp_async16(Ks + r * kRowStride + cch * 8, rowK[r] + cch * 8);
-            cp_async16(Vs + r * kRowStride + cch * 8, rowV[r] + cch * 8);
+            cp_async16(tile + r * kRowStride + cch * 8, rows[r] + cch * 8);
         }
-        asm volatile("cp.async.wait_all;" ::: "memory");
+        cp_async_commit();   // (one group per tile and unit, empty when there is nothing to fetch: the counts below rely on it)
+    };
+
+    // K and V of a unit travel as separate groups: Q K^T starts when K is in, V lands during the softmax; the next
+    // unit's K is requested as soon as this unit's scores are out, its V as soon as this unit's P V is done.
+    int nrows = 0, cur = 0;
+    if (split < U) nrows = setup_unit(split, rowK[0], rowV[0]);
+    __syncthreads();
+    issue_rows(Ks, rowK[0], nrows);
+    issue_rows(Vs, rowV[0], nrows);
+    for (int u = split; u < U; u += p.nsplit, cur ^= 1) {
+        const int un = u + p.nsplit;
+        int nrows_next = 0;
+        if (un < U) nrows_next = setup_unit(un, rowK[cur ^ 1], rowV[cur ^ 1]);
+        cp_async_wait1();   // K of this unit (V may still be on its way)
         __syncthreads();
         // ---- S = Q K^T: warp w takes keys 16 w .. 16 w + 15
         {
@@ -815,6 +829,7 @@ __global__ void __launch_bounds__(128) attend_decode_tc_kernel(const AttendParam
             }
         }
         __syncthreads();
+        issue_rows(Ks, rowK[cur ^ 1], nrows_next);   // every warp is done with this unit's K
         // ---- softmax pieces per head (warp w: heads w, w + 4): running max / sum, probabilities as bf16
         for (int h = warp; h < G; h += 4) {
             const float s0 = sc[h * kPage + lane], s1 = sc[h * kPage + 32 + lane];
@@ -832,6 +847,7 @@ __global__ void __launch_bounds__(128) attend_decode_tc_kernel(const AttendParam
                 s_aold[h] = a_old;
             }
         }
+        cp_async_wait1();   // V of this unit (the next unit's K may still be on its way)
         __syncthreads();
         // ---- O = O * a_old + P V: warp w takes dims 32 w .. 32 w + 31
         {
@@ -853,7 +869,11 @@ __global__ void __launch_bounds__(128) attend_decode_tc_kernel(const AttendParam
                 }
             }
         }
+        __syncthreads();   // every warp is done with this unit's V
+        issue_rows(Vs, rowV[cur ^ 1], nrows_next);
+        nrows = nrows_next;
     }
+    cp_async_wait0();
     __syncthreads();
     float* out = p.part + (((size_t)b * g.KVH + kv) * p.nsplit + split) * G * (kD + 2);
     if (gq < G) {

@@ -509,6 +509,7 @@ __global__ void __launch_bounds__(kBoundaryThreads) mhc_boundary_kernel(const Bo
     __shared__ float dsm[24];
     __shared__ float pre_sm[4];
     pdl_launch_dependents();
+    VK_TS(3, 0);
     const CombineParams& p = q.c;
     const int b = blockIdx.x, D = p.D;
     const size_t base = (size_t)b * D;
@@ -523,7 +524,9 @@ __global__ void __launch_bounds__(kBoundaryThreads) mhc_boundary_kernel(const Bo
         w_in_raw = *reinterpret_cast<const uint4*>(q.w_in + k);
     }
     pdl_wait();
+    VK_TS(3, 1);
     ar_reduce_row(p.ar, const_cast<__nv_bfloat16*>(p.m) + base, b, D);
+    VK_TS(3, 2);
     float gate = 0.f;
     float hv[8] = {}, mv[8] = {}, xv[8] = {};
     if (on) { ld8(p.h2 + base + k, hv); ld8(p.m + base + k, mv); ld8(p.x_in + base + k, xv); }
@@ -571,7 +574,9 @@ __global__ void __launch_bounds__(kBoundaryThreads) mhc_boundary_kernel(const Bo
 #pragma unroll
         for (int s = 0; s < 4; s++) st8(Hb + (size_t)s * D + k, o[s]);
     }
+    VK_TS(3, 3);
     ss = row_block_sum(ss, red);
+    VK_TS(3, 4);
     float hnv[8] = {};
     if (on) {
         const float inv = rsqrtf(ss / (float)D + p.eps);
@@ -582,9 +587,11 @@ __global__ void __launch_bounds__(kBoundaryThreads) mhc_boundary_kernel(const Bo
     }
     // ---- dyn of the next layer from the norm just formed (registers), then its mHC parameters on warp 0
     dyn24(hnv, on, k, q.w_dyn, D, part, dsm);
+    VK_TS(3, 5);
     if (threadIdx.x < 32)
         mhc_params_warp(dsm, q.pre_s, q.post_s, q.res_s, q.iters, pre_sm, q.post_out + b * 4, q.res_out + b * 16);
     __syncthreads();
+    VK_TS(3, 6);
     float x[8] = {};
     float ss2 = 0.f;
     if (on) {
@@ -596,6 +603,7 @@ __global__ void __launch_bounds__(kBoundaryThreads) mhc_boundary_kernel(const Bo
         st8(q.x_in_out + base + k, x);
     }
     ss2 = row_block_sum(ss2, red);
+    VK_TS(3, 7);
     const float inv2 = rsqrtf(ss2 / (float)D + p.eps);
     float ho[8] = {};
     if (on) {
@@ -609,6 +617,7 @@ __global__ void __launch_bounds__(kBoundaryThreads) mhc_boundary_kernel(const Bo
         if (on) xrec_store_row_piece(q.xrec_h, b, threadIdx.x, ho);
         else { __shfl_xor_sync(0xffffffffu, 0.f, 1); __shfl_xor_sync(0xffffffffu, 0.f, 2); __shfl_xor_sync(0xffffffffu, 0.f, 4); }
     }
+    VK_TS(3, 8);
 }
 
 // ------------------------------------------------------------------------------------------------ bf16 linear, few rows

@@ -36,6 +36,7 @@ struct KdaParams {
     const float* g_override;       // null, or [B] multipliers: 1 keeps the step, 0 turns it into a no-op (verify replay)
     int ldp, off_z, off_fd, D, Hk, HV, rank;
     float eps;
+    int early_state;               // 1: request the state before the dependency wait (see vk_kda_step)
 };
 
 constexpr int kBdotPieces = 5;   // 16-byte pieces of the in_proj_b row a thread keeps in registers (hidden <= 5120)
@@ -85,12 +86,20 @@ __global__ void __launch_bounds__(128, 5) kda_step_kernel(const KdaParams p) {
         const int k = c * 8 + i * 1024;
         wbv[i] = k < p.D ? *reinterpret_cast<const uint4*>(wb + k) : make_uint4(0u, 0u, 0u, 0u);
     }
+    float* Sb = p.S + (((size_t)b * p.HV + hv) * 128) * 128;
+    if (p.early_state) {
+#pragma unroll
+        for (int bt = 0; bt < 2; bt++) {
+#pragma unroll
+            for (int i = 0; i < 8; i++)
+                cp_async16(&ring[warp][bt][i][4 * lane], Sb + (size_t)(warp * 32 + bt * 8 + i) * 128 + 4 * lane);
+            cp_async_commit();
+        }
+    }
     pdl_wait();
     VK_TS(1, 1);
     const __nv_bfloat16* pr = p.proj + (size_t)b * p.ldp;
-    const int par = *p.parity & 1;
-    const __nv_bfloat16* conv_in = p.conv + (size_t)par * p.conv_stride;
-    __nv_bfloat16* conv_out = p.conv + (size_t)(1 - par) * p.conv_stride;
+    const int par_word = *p.parity;   // (used only after the loads below have been issued: both conv buffers are read)
 
     // ---- this step's inputs first (they gate the prologue), the state after them: requests are served in order,
     // and 16 rows of state per warp would otherwise sit in front of every small load
@@ -101,22 +110,26 @@ __global__ void __launch_bounds__(128, 5) kda_step_kernel(const KdaParams p) {
         const int k = c * 8 + i * 1024;
         hx[i] = k < p.D ? *reinterpret_cast<const uint4*>(hb + k) : make_uint4(0u, 0u, 0u, 0u);
     }
-    __nv_bfloat16 cx[3][4];
+    __nv_bfloat16 cx[3][4], cy[3][3];
 #pragma unroll
     for (int i = 0; i < 3; i++) {
         const size_t cb = (size_t)b * 3 * C + ch[i];
-        cx[i][0] = conv_in[cb]; cx[i][1] = conv_in[cb + C]; cx[i][2] = conv_in[cb + 2 * (size_t)C];
+        const __nv_bfloat16* c0 = p.conv + cb;
+        const __nv_bfloat16* c1 = p.conv + p.conv_stride + cb;
+        cx[i][0] = c0[0]; cx[i][1] = c0[C]; cx[i][2] = c0[2 * (size_t)C];
+        cy[i][0] = c1[0]; cy[i][1] = c1[C]; cy[i][2] = c1[2 * (size_t)C];
         cx[i][3] = pr[ch[i]];
     }
     const float z = bf2f(pr[p.off_z + hv * 128 + c]);
     for (int i = c; i < p.rank; i += 128) fd[i] = bf2f(pr[p.off_fd + i]);
-    float* Sb = p.S + (((size_t)b * p.HV + hv) * 128) * 128;
+    if (!p.early_state) {
 #pragma unroll
-    for (int bt = 0; bt < 2; bt++) {
+        for (int bt = 0; bt < 2; bt++) {
 #pragma unroll
-        for (int i = 0; i < 8; i++)
-            cp_async16(&ring[warp][bt][i][4 * lane], Sb + (size_t)(warp * 32 + bt * 8 + i) * 128 + 4 * lane);
-        cp_async_commit();
+            for (int i = 0; i < 8; i++)
+                cp_async16(&ring[warp][bt][i][4 * lane], Sb + (size_t)(warp * 32 + bt * 8 + i) * 128 + 4 * lane);
+            cp_async_commit();
+        }
     }
 
     // ---- beta's dot product
@@ -138,8 +151,19 @@ __global__ void __launch_bounds__(128, 5) kda_step_kernel(const KdaParams p) {
         bdot = fmaf(bf_lo(wv.w), bf_lo(xv.w), bdot); bdot = fmaf(bf_hi(wv.w), bf_hi(xv.w), bdot);
     }
     VK_TS(1, 2);
+    // f_up arrives packed (vk_kda_pack_fup): [head][rank / 8][channel][8], so that the 128 channels of a head read
+    // consecutive 16-byte pieces. The first 64 ranks are requested here, to arrive during the conv and its reduction.
+    uint4 fw[8];
+#pragma unroll
+    for (int u = 0; u < 8; u++) fw[u] = 8 * u < p.rank ? fup[(size_t)u * 128] : make_uint4(0u, 0u, 0u, 0u);
 
     // ---- conv + SiLU of this head's q, k, v channel c; new conv state
+    const int par = par_word & 1;
+    __nv_bfloat16* conv_out = p.conv + (size_t)(1 - par) * p.conv_stride;
+    if (par) {
+#pragma unroll
+        for (int i = 0; i < 3; i++) { cx[i][0] = cy[i][0]; cx[i][1] = cy[i][1]; cx[i][2] = cy[i][2]; }
+    }
     float s3[3];
 #pragma unroll
     for (int i = 0; i < 3; i++) {
@@ -163,24 +187,26 @@ __global__ void __launch_bounds__(128, 5) kda_step_kernel(const KdaParams p) {
     vs[c] = s3[2];
     VK_TS(1, 4);
 
-    // ---- decay g[c] and beta. f_up arrives packed (vk_kda_pack_fup): [head][rank / 8][channel][8], so that the 128
-    // channels of a head read consecutive 16-byte pieces
+    // ---- decay g[c] and beta
     {
         float a = 0.f;
         for (int r0 = 0; r0 < p.rank; r0 += 64) {
-            uint4 wv[8];
+            uint4 nx[8];   // the next 64 ranks, requested before this batch is used
 #pragma unroll
-            for (int u = 0; u < 8; u++) wv[u] = r0 + 8 * u < p.rank ? fup[(size_t)(r0 / 8 + u) * 128] : make_uint4(0u, 0u, 0u, 0u);
+            for (int u = 0; u < 8; u++)
+                nx[u] = r0 + 64 + 8 * u < p.rank ? fup[(size_t)((r0 + 64) / 8 + u) * 128] : make_uint4(0u, 0u, 0u, 0u);
 #pragma unroll
             for (int u = 0; u < 8; u++) {
                 if (r0 + 8 * u < p.rank) {
                     const int r = r0 + 8 * u;
-                    a = fmaf(bf_lo(wv[u].x), fd[r], a); a = fmaf(bf_hi(wv[u].x), fd[r + 1], a);
-                    a = fmaf(bf_lo(wv[u].y), fd[r + 2], a); a = fmaf(bf_hi(wv[u].y), fd[r + 3], a);
-                    a = fmaf(bf_lo(wv[u].z), fd[r + 4], a); a = fmaf(bf_hi(wv[u].z), fd[r + 5], a);
-                    a = fmaf(bf_lo(wv[u].w), fd[r + 6], a); a = fmaf(bf_hi(wv[u].w), fd[r + 7], a);
+                    a = fmaf(bf_lo(fw[u].x), fd[r], a); a = fmaf(bf_hi(fw[u].x), fd[r + 1], a);
+                    a = fmaf(bf_lo(fw[u].y), fd[r + 2], a); a = fmaf(bf_hi(fw[u].y), fd[r + 3], a);
+                    a = fmaf(bf_lo(fw[u].z), fd[r + 4], a); a = fmaf(bf_hi(fw[u].z), fd[r + 5], a);
+                    a = fmaf(bf_lo(fw[u].w), fd[r + 6], a); a = fmaf(bf_hi(fw[u].w), fd[r + 7], a);
                 }
             }
+#pragma unroll
+            for (int u = 0; u < 8; u++) fw[u] = nx[u];
         }
         a = bfr(a);
         gs[c] = expf(-expf(a_log) * softplus_f(a + dtb));
@@ -296,14 +322,14 @@ int vk_kda_configure(void) {
 int vk_kda_step(const void* proj, int ldp, int off_z, int off_fd, const void* h, const void* w_b, const void* w_fup,
                 const float* conv_w, const float* A_log, const float* dt_bias, const void* norm_w, void* conv,
                 const int* parity, size_t conv_stride, float* S, void* out, void* xrec_out, const float* g_override, int B,
-                int D, int Hk, int HV, int Dk, int Dv, int rank, float eps, cudaStream_t stream) {
+                int D, int Hk, int HV, int Dk, int Dv, int rank, float eps, int early_state, cudaStream_t stream) {
     if (B <= 0 || Dk != 128 || Dv != 128 || Hk <= 0 || HV % Hk != 0 || rank <= 0 || rank > 256 || rank % 8 != 0 ||
         D % 8 != 0 || parity == nullptr || (xrec_out != nullptr && B > 16))
         return VK_EINVAL;
     KdaParams p = {(const __nv_bfloat16*)proj, (const __nv_bfloat16*)h, (const __nv_bfloat16*)w_b,
                    (const __nv_bfloat16*)w_fup, conv_w, A_log, dt_bias, (const __nv_bfloat16*)norm_w,
                    (__nv_bfloat16*)conv, parity, conv_stride, S, (__nv_bfloat16*)out, (uint8_t*)xrec_out, g_override,
-                   ldp, off_z, off_fd, D, Hk, HV, rank, eps};
+                   ldp, off_z, off_fd, D, Hk, HV, rank, eps, early_state ? 1 : 0};
     return (int)vk_launch(kda_step_kernel, dim3(HV, B), dim3(128), 0, stream, p);
 }
 

@@ -179,8 +179,17 @@ __global__ void __launch_bounds__(kThreads, Fmt<FMT>::kCtasPerSM) w4_gemm_kernel
             int st = 0;
             uint32_t par = 0;   // parity of the "empty" phase awaited next for stage st
             const uint8_t* wnext = wsrc + (size_t)pre * kWStageBytes;
+#if defined(VK_TRACE) && VK_TRACE == 2
+            long long tr_wait = 0, tr_t0 = clock64();
+#endif
             for (int i = pre; i < n; i++) {
+#if defined(VK_TRACE) && VK_TRACE == 2
+                const long long tr_a = clock64();
+#endif
                 if (!mbar_wait(&empty[st], par)) break;
+#if defined(VK_TRACE) && VK_TRACE == 2
+                tr_wait += clock64() - tr_a;
+#endif
                 uint8_t* dst = smem + (size_t)st * kStageBytes;
                 mbar_expect_tx(&full[st], kWStageBytes + kXRecBytes);
                 tma_bulk_g2s(dst, wnext, kWStageBytes, &full[st]);
@@ -189,6 +198,11 @@ __global__ void __launch_bounds__(kThreads, Fmt<FMT>::kCtasPerSM) w4_gemm_kernel
                 kg = kg + 1 == p.G ? 0 : kg + 1;
                 if (++st == kStages) { st = 0; par ^= 1u; }
             }
+#if defined(VK_TRACE) && VK_TRACE == 2
+            g_vk_trace[(blockIdx.x & 4095) * 16 + 0] = tr_wait;            // producer: cycles waiting for a free stage
+            g_vk_trace[(blockIdx.x & 4095) * 16 + 1] = clock64() - tr_t0;  // producer: cycles in the refill loop
+            g_vk_trace[(blockIdx.x & 4095) * 16 + 2] = n;
+#endif
         }
         return;
     }
@@ -232,12 +246,12 @@ __global__ void __launch_bounds__(kThreads, Fmt<FMT>::kCtasPerSM) w4_gemm_kernel
                         __stcg(reinterpret_cast<float2*>(dst + (size_t)r * 16 + jj * 8 + 2 * t),
                                make_float2(acc[s][jj][2 * h], acc[s][jj][2 * h + 1]));
                     }
-            __threadfence();
             consumer_sync();
             const int nc = p.S, slot = blockIdx.x - c_first;
             int* arrive = p.counters + fsb;
             int* depart = p.counters + 2048 + fsb;
             if (ctid == 0) {
+                __threadfence();   // after the barrier: orders every consumer's partial stores before the arrival
                 atomicAdd(arrive, 1);
                 int seen = 0;
                 for (uint32_t it = 0; it < (1u << 20); it++) {
@@ -249,8 +263,7 @@ __global__ void __launch_bounds__(kThreads, Fmt<FMT>::kCtasPerSM) w4_gemm_kernel
                 if (!s_last) vk_set_status(VK_ST_FLAG_TIMEOUT);
             }
             consumer_sync();
-            if (s_last) {
-                __threadfence();
+            if (s_last) {   // (thread 0's acquire loads and the barrier order the partial sums before the reads below)
                 constexpr int V4 = MR / 4;
                 const int r0 = slot * kSBRows / nc, r1 = (slot + 1) * kSBRows / nc;
                 for (int item = ctid; item < (r1 - r0) * V4; item += 256) {
@@ -293,12 +306,12 @@ __global__ void __launch_bounds__(kThreads, Fmt<FMT>::kCtasPerSM) w4_gemm_kernel
                         __stcg(reinterpret_cast<float2*>(dst + (size_t)r * 16 + jj * 8 + 2 * t),
                                make_float2(acc[s][jj][2 * h], acc[s][jj][2 * h + 1]));
                     }
-            __threadfence();
             consumer_sync();
             // The CTA that arrives last at this superblock adds up the partial sums of all its ranges, in range order.
             // (Nobody waits: a wait for the other ranges would chain every CTA to its predecessor, whose last range
             // ends where this one's first begins.)
             if (ctid == 0) {
+                __threadfence();   // after the barrier: orders every consumer's partial stores before the arrival
                 const int ncontrib = step_owner(s0 + p.G - 1, p.T, p.P) - c_first + 1;
                 const int old = atomicAdd(&p.counters[fsb], 1);
                 s_last = (old == ncontrib - 1) ? ncontrib : 0;
@@ -366,8 +379,18 @@ __global__ void __launch_bounds__(kThreads, Fmt<FMT>::kCtasPerSM) w4_gemm_kernel
     for (int jj = 0; jj < MT; jj++) bw_off[jj] = t < 2 ? kWStageBytes + 2048 + (jj * 8 + g) * 8 + t * 4 : kWStageBytes + kXRecBytes;
     int st = 0;
     uint32_t phase = 0;
+#if defined(VK_TRACE) && VK_TRACE == 2
+    long long tc_wait = 0, tc_t0 = clock64();
+#endif
     for (int i = 0; i < n; i++, st = (st + 1 == kStages ? 0 : st + 1), phase ^= (st == 0)) {
+#if defined(VK_TRACE) && VK_TRACE == 2
+        const long long tc_a = clock64();
+#endif
         if (!mbar_wait(&full[st], phase)) { ok = false; break; }
+#if defined(VK_TRACE) && VK_TRACE == 2
+        tc_wait += clock64() - tc_a;
+        if (i == 0 && threadIdx.x == 32) g_vk_trace[(blockIdx.x & 4095) * 16 + 5] = clock64() - tc_t0;   // first data
+#endif
         const uint8_t* stage = smem + (size_t)st * kStageBytes;
         const uint8_t* ch = stage + j * kChunkB;
         const uint32_t stage_a = smem_u32(stage);
@@ -454,7 +477,17 @@ __global__ void __launch_bounds__(kThreads, Fmt<FMT>::kCtasPerSM) w4_gemm_kernel
             kg = 0; seg_kg0 = 0; sb++;
         }
     }
+#if defined(VK_TRACE) && VK_TRACE == 2
+    const long long tc_loop = clock64() - tc_t0;
+#endif
     if (ok && kg != seg_kg0) flush(sb, seg_kg0, kg);
+#if defined(VK_TRACE) && VK_TRACE == 2
+    if (threadIdx.x == 32) {
+        g_vk_trace[(blockIdx.x & 4095) * 16 + 3] = tc_wait;                 // consumer warp 0: cycles waiting for data
+        g_vk_trace[(blockIdx.x & 4095) * 16 + 4] = tc_loop;                 // consumer warp 0: cycles in the step loop
+        g_vk_trace[(blockIdx.x & 4095) * 16 + 6] = clock64() - tc_t0;       // ... including the final flush
+    }
+#endif
     // (a timed-out wait leaves the output unwritten and the status word set; copies still in flight land in this
     // CTA's shared memory, which stays allocated until the last warp of the CTA has left, after its own bounded waits)
 }
