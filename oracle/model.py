@@ -219,12 +219,21 @@ class Oracle:
     # ------------------------------------------------------------------ KDA
     def kda(self, L, h, st):
         """KDA.__call__ ops branch (volundr.py:418-439) for one token; recurrence as tests/test_volundr.py:103-116."""
-        a, p, dt = self.a, self.p, self.dt
-        Hk, HV, K, V = a.linear_num_key_heads, a.linear_num_value_heads, a.linear_key_head_dim, a.linear_value_head_dim
+        a, dt = self.a, self.dt
+        HV, K, V = a.linear_num_value_heads, a.linear_key_head_dim, a.linear_value_head_dim
         qkv = self.lin(h, L + "in_proj_qkv")
         z = np.asarray(self.lin(h, L + "in_proj_z"), dt).reshape(HV, V)
         b = np.asarray(self.lin(h, L + "in_proj_b"), dt)
         aa = np.asarray(self.lin(self.lin(h, L + "f_down"), L + "f_up"), dt).reshape(HV, K)
+        out = self.kda_core(L, qkv, z, b, aa, st)
+        return self.lin(out.reshape(HV * V), L + "out_proj")
+
+    def kda_core(self, L, qkv, z, b, aa, st):
+        """The step from the projections on: conv + SiLU (_conv_silu, volundr.py:351-360), q/k normalisation, decay and
+        beta (volundr.py:418-433), the gated delta rule on st["S"] [HV, V, K] (tests/test_volundr.py:103-116) and the
+        gated norm (volundr.py:171-174). qkv [C], z [HV, V], b [HV], aa [HV, K] (bf16-valued); returns [HV, V]."""
+        a, p, dt = self.a, self.p, self.dt
+        Hk, HV, K, V = a.linear_num_key_heads, a.linear_num_value_heads, a.linear_key_head_dim, a.linear_value_head_dim
         conv_in = np.concatenate([st["conv"], np.asarray(qkv, dt)[None]], axis=0)  # [Kc, C]
         st["conv"] = conv_in[1:].copy()
         w = np.asarray(p[L + "conv1d.weight"], dt)  # [C, Kc]
@@ -249,8 +258,7 @@ class Oracle:
         # _gated_norm (volundr.py:171-174): rms over the value head, * w, * silu(z), one rounding
         wn = np.asarray(p[L + "norm.weight"], dt)
         inv = 1 / np.sqrt((ob * ob).mean(-1, keepdims=True) + dt(a.rms_norm_eps))
-        out = self.rnd(((ob * inv) * wn) * silu(z))
-        return self.lin(out.reshape(HV * V), L + "out_proj")
+        return self.rnd(((ob * inv) * wn) * silu(z))
 
     # ------------------------------------------------------------------ attention
     def rope(self, x, pos):

@@ -144,16 +144,27 @@ __device__ __forceinline__ void dyn24(const float (&hv)[8], bool on, int k, cons
 // post = bf(post_s + d[4:8]) (volundr.py:264-271, :237-243). Called by all 32 lanes of one warp: lane i < 16 owns
 // element (i / 4, i % 4); every row / column sum is formed in the order ((a0 + a1) + a2) + a3 from shuffled copies,
 // the same additions a single thread would do.
-__device__ __forceinline__ void mhc_params_warp(const float* dsm, const __nv_bfloat16* __restrict__ pre_s,
-                                                const __nv_bfloat16* __restrict__ post_s, const __nv_bfloat16* __restrict__ res_s,
-                                                int iters, float* pre_sm, float* post_out, float* res_out) {
+// The static parts come in registers (mhc_static_load), so that their loads can be issued early.
+struct MhcStatic { float res, pre, post; };   // lane i < 16: res_s[i]; lane < 4: pre_s[lane], post_s[lane]
+__device__ __forceinline__ MhcStatic mhc_static_load(const __nv_bfloat16* __restrict__ pre_s, const __nv_bfloat16* __restrict__ post_s,
+                                                     const __nv_bfloat16* __restrict__ res_s) {
+    const int lane = threadIdx.x & 31;
+    MhcStatic st;
+    st.res = bf2f(res_s[lane & 15]);
+    st.pre = bf2f(pre_s[lane & 3]);
+    st.post = bf2f(post_s[lane & 3]);
+    return st;
+}
+__device__ __forceinline__ void mhc_params_warp(const float* dsm, const MhcStatic st, int iters, float* pre_sm, float* post_out,
+                                                float* res_out) {
     const int lane = threadIdx.x & 31;
     const int i = lane & 15, r = i >> 2, c = i & 3;
-    const float l = bf2f(res_s[i]) + dsm[8 + i];
+    const float l = st.res + dsm[8 + i];
     float mx = l;
 #pragma unroll
     for (int o = 8; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
     float m = expf(l - mx);
+    VK_TS(3, 9);
     for (int it = 0; it < iters; it++) {
         float a0 = __shfl_sync(0xffffffffu, m, 4 * r), a1 = __shfl_sync(0xffffffffu, m, 4 * r + 1);
         float a2 = __shfl_sync(0xffffffffu, m, 4 * r + 2), a3 = __shfl_sync(0xffffffffu, m, 4 * r + 3);
@@ -162,10 +173,11 @@ __device__ __forceinline__ void mhc_params_warp(const float* dsm, const __nv_bfl
         a2 = __shfl_sync(0xffffffffu, m, 8 + c); a3 = __shfl_sync(0xffffffffu, m, 12 + c);
         m = m / fmaxf(((a0 + a1) + a2) + a3, 1e-9f);
     }
+    VK_TS(3, 10);
     if (lane < 16) res_out[i] = bfr(m);
     if (lane < 4) {
-        pre_sm[lane] = bfr(bf2f(pre_s[lane]) + dsm[lane]);
-        post_out[lane] = bfr(bf2f(post_s[lane]) + dsm[4 + lane]);
+        pre_sm[lane] = bfr(st.pre + dsm[lane]);
+        post_out[lane] = bfr(st.post + dsm[4 + lane]);
     }
 }
 
@@ -212,7 +224,7 @@ __global__ void __launch_bounds__(1024) mhc_mix_norm_kernel(const MixParams p) {
     const int b = blockIdx.x;
     const int D = p.D;
     if (threadIdx.x < 32)
-        mhc_params_warp(p.d + b * 24, p.pre_s, p.post_s, p.res_s, p.iters, pre_sm, p.post + b * 4, p.res + b * 16);
+        mhc_params_warp(p.d + b * 24, mhc_static_load(p.pre_s, p.post_s, p.res_s), p.iters, pre_sm, p.post + b * 4, p.res + b * 16);
     // (the other warps load their pieces of H meanwhile)
     const __nv_bfloat16* Hb = p.H + (size_t)b * 4 * D;
     const int k0 = threadIdx.x * 8;
@@ -518,6 +530,8 @@ __global__ void __launch_bounds__(kBoundaryThreads) mhc_boundary_kernel(const Bo
     // weights depend on no earlier kernel: fetch this thread's pieces, and start the 24 dyn rows towards L2, while the
     // kernel before this one is still running
     if (threadIdx.x < 24) l2_prefetch_bulk(q.w_dyn + (size_t)threadIdx.x * D, (uint32_t)D * 2u);
+    MhcStatic mst = {0.f, 0.f, 0.f};
+    if (threadIdx.x < 32) mst = mhc_static_load(q.pre_s, q.post_s, q.res_s);
     uint4 w_next_raw = make_uint4(0u, 0u, 0u, 0u), w_in_raw = w_next_raw;
     if (on) {
         w_next_raw = *reinterpret_cast<const uint4*>(p.w_next + k);
@@ -589,7 +603,7 @@ __global__ void __launch_bounds__(kBoundaryThreads) mhc_boundary_kernel(const Bo
     dyn24(hnv, on, k, q.w_dyn, D, part, dsm);
     VK_TS(3, 5);
     if (threadIdx.x < 32)
-        mhc_params_warp(dsm, q.pre_s, q.post_s, q.res_s, q.iters, pre_sm, q.post_out + b * 4, q.res_out + b * 16);
+        mhc_params_warp(dsm, mst, q.iters, pre_sm, q.post_out + b * 4, q.res_out + b * 16);
     __syncthreads();
     VK_TS(3, 6);
     float x[8] = {};
