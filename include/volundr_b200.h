@@ -102,6 +102,7 @@ int vk_mhc_combine_norm(void* H, const void* h2, const void* m, const void* x_in
 /* vk_mhc_combine_norm of layer i and vk_mhc_mix_norm of layer i + 1 in one launch (VolundrModel._fused_layers runs them
  * back to back, volundr.py:945-948): H, x_in, post, res are updated in place for the next layer; h / xrec_h receive its
  * input norm. Same values as the two separate calls. D / 8 <= 640. */
+void vk_mhc_boundary_set_cluster(int on);   /* 1: four CTAs (one cluster) per row when D % 1024 == 0; 0 (default): one */
 int vk_mhc_boundary(void* H, const void* h2, const void* m, void* x_in, float* post, float* res, const void* w_next,
                     const void* eng_val, const void* eng_gate_w, const void* eng_gate_b, const void* w_dyn, const void* pre_s,
                     const void* post_s, const void* res_s, const void* w_in, void* h, void* xrec_h, int B, int D, int iters,
@@ -135,7 +136,7 @@ typedef struct vk_ar_desc {
     int* flags[8];
     int* step;
 } vk_ar_desc;
-size_t vk_ar_region_bytes(int world, int rows, int D);   /* 0: unsupported (world <= 8, world * rows <= 1008) */
+size_t vk_ar_region_bytes(int world, int rows, int D);   /* 0: unsupported (world <= 8, world * rows <= 252) */
 int vk_ar_alloc(size_t bytes, void** ptr, void* handle64);
 int vk_ar_open(const void* handle64, void** ptr);
 int vk_ar_close(void* ptr);

@@ -112,6 +112,39 @@ def test_fused_layer_boundary_equals_separate_kernels(cuda):
     assert torch.equal(outs[0], outs[1])
 
 
+def test_clustered_boundary_close_to_single_cta(cuda):
+    """A cluster of four CTAs per row in the layer-boundary kernel (hidden sizes that are multiples of 1024) adds the
+    row-wide sums in another order than the one-CTA kernel: logits within the bf16 floor of each other, and each
+    variant reproducible bit for bit."""
+    from volundr_mlx_b200 import _lib, batch as BT
+    from volundr_mlx_b200.volundr import Model
+
+    L = _lib.lib()
+    args = synth.block2_args()
+    assert args.hidden_size % 1024 == 0
+    params = synth.make_params(args, seed=11)
+    model = Model(args, params, cuda)
+    outs = []
+    try:
+        for cluster in (1, 0, 1):
+            L.vk_mhc_boundary_set_cluster(cluster)
+            bc = model.make_cache(max_rows=4, n_pages=32, max_pages_per_row=4)
+            bc.apply(join=["a", "b", "c"])
+            rng = np.random.default_rng(5)
+            res = []
+            for t in range(40):
+                lg, _ = BT.forward(model, bc, rng.integers(0, args.vocab_valid, size=3).tolist())
+                res.append(lg.float().clone())
+            outs.append(torch.stack(res))
+    finally:
+        L.vk_mhc_boundary_set_cluster(0)
+    from volundr_mlx_b200 import ops
+    ops.check_status()
+    assert torch.equal(outs[0], outs[2])
+    scale = outs[1].abs().max()
+    assert float((outs[0] - outs[1]).abs().max() / scale) < 3e-2
+
+
 def test_tensor_core_attention_close_to_scalar_kernel(cuda):
     """The tensor-core attention (bf16 probabilities) against the scalar fp32 kernel on the same schedule: logits
     within bf16 tolerance (the reference's bar for its attention kernels is 2^-7 |x| + 2e-3, test_volundr.py:266)."""

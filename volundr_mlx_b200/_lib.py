@@ -33,6 +33,7 @@ SIGNATURES = {
     "vk_silu_mul": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
     "vk_engram_gather": (c_int, [c_void_p] * 6 + [c_int, c_int, c_int, c_float, c_void_p]),
     "vk_mhc_combine_norm": (c_int, [c_void_p] * 12 + [c_int, c_int, c_int, c_float, c_void_p]),
+    "vk_mhc_boundary_set_cluster": (None, [c_int]),
     "vk_mhc_boundary": (c_int, [c_void_p] * 17 + [c_int, c_int, c_int, c_float, c_void_p]),
     "vk_ar_region_bytes": (c_size_t, [c_int, c_int, c_int]),
     "vk_ar_alloc": (c_int, [c_size_t, c_void_p, c_void_p]),

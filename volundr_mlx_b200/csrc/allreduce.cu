@@ -10,7 +10,7 @@ __global__ void ar_advance_kernel(int* step) {
     if (threadIdx.x == 0) *step = *step + 1;
 }
 
-constexpr size_t kArHeader = 4096;   // flags [world][rows] int32 + the step counter live in the first 4 KB
+constexpr size_t kArHeader = 4096;   // flags [world][rows][4] int32 + the step counter live in the first 4 KB
 
 inline size_t ar_slots_bytes(int world, int rows, int D) { return (size_t)kArSlots * world * rows * D * 2; }
 
@@ -20,7 +20,7 @@ extern "C" {
 
 size_t vk_ar_region_bytes(int world, int rows, int D) {
     if (world < 1 || world > kArMaxWorld || rows < 1 || D < 8 || D % 8 != 0) return 0;
-    if ((size_t)world * rows * 4 + 64 > kArHeader) return 0;
+    if ((size_t)world * rows * kArParts * 4 + 64 > kArHeader) return 0;
     return kArHeader + ar_slots_bytes(world, rows, D);
 }
 

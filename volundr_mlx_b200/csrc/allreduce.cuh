@@ -3,7 +3,8 @@
 // ranks hold partial products of the row-parallel linears; the reference is single-GPU and has no counterpart.
 //
 // Every rank owns one region of device memory that all ranks have mapped (CUDA IPC):
-//     flags [world][rows] int32        flags[src][b] = sequence number of the last push of rank `src` for row b
+//     flags [world][rows][4] int32     flags[src][b][part] = sequence number of the last push of rank `src` for that
+//                                      part of row b (a row is exchanged whole, part 0, or in up to four parts)
 //     slots [4][world][rows][D] bf16   slots[seq & 3][src][b] = the partial row that `src` pushed
 // The CTA that owns row b: (1) stores its partial row into every peer's slots[.][me][b] with plain peer stores over
 // NVLink, (2) system-fence, then writes the sequence number into every peer's flags[me][b], (3) waits - bounded - until
@@ -20,6 +21,7 @@
 
 constexpr int kArMaxWorld = 8;
 constexpr int kArSlots = 4;
+constexpr int kArParts = 4;     // flag words per (rank, row): a row may be exchanged in up to four independent parts
 constexpr uint32_t kArSpinDefault = 1u << 23;   // polls of >= 100 ns each: several seconds, to ride out host-side skew
 
 // The caller's descriptor (public header: vk_ar_desc). Pointers of rank p are that rank's region as mapped into this
@@ -49,16 +51,22 @@ __device__ __forceinline__ size_t ar_slot_off(const VkArDesc& d, int slot, int s
     return ((((size_t)slot * d.world + src) * d.rows + b) * (size_t)D) * 2;
 }
 
-// All threads of the CTA that owns row b call this after griddepcontrol.wait. `row` = the rank's partial [D] bf16 in
-// local memory; on return it holds the sum over ranks. D % 8 == 0.
+// All threads of the CTA that owns part `part` of `nparts` (<= kArParts) equal parts of row b call this after
+// griddepcontrol.wait. `row` = the rank's partial [D] bf16 in local memory; on return the part holds the sum over ranks.
+// (D / nparts) % 8 == 0. Every part has its own flag word, so the CTAs of a row need not wait for one another.
+__device__ __forceinline__ void ar_reduce_span(const VkArCall& a, __nv_bfloat16* row, int b, int D, int part, int nparts);
 __device__ __forceinline__ void ar_reduce_row(const VkArCall& a, __nv_bfloat16* row, int b, int D) {
+    ar_reduce_span(a, row, b, D, 0, 1);
+}
+__device__ __forceinline__ void ar_reduce_span(const VkArCall& a, __nv_bfloat16* row, int b, int D, int part, int nparts) {
     const VkArDesc& d = a.d;
     if (d.world <= 1) return;
     const int seq = (int)((unsigned)*reinterpret_cast<volatile int*>(d.step) * (unsigned)d.calls_per_step + (unsigned)a.call + 1u);
     const int slot = seq & (kArSlots - 1);
-    const int nvec = D >> 3;
+    const int nvec_part = (D / nparts) >> 3;
+    const int v_begin = part * nvec_part, nvec = v_begin + nvec_part;
     uint4* rowv = reinterpret_cast<uint4*>(row);
-    for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
+    for (int v = v_begin + threadIdx.x; v < nvec; v += blockDim.x) {
         const uint4 val = rowv[v];
         for (int p = 0; p < d.world; p++) {
             if (p == d.rank) continue;
@@ -69,9 +77,9 @@ __device__ __forceinline__ void ar_reduce_row(const VkArCall& a, __nv_bfloat16* 
     __syncthreads();
     const int t = threadIdx.x;
     if (t < d.world && t != d.rank) {
-        int* remote = d.flags[t] + d.rank * d.rows + b;
+        int* remote = d.flags[t] + (d.rank * d.rows + b) * kArParts + part;
         asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(remote), "r"(seq) : "memory");
-        const int* mine = d.flags[d.rank] + t * d.rows + b;
+        const int* mine = d.flags[d.rank] + (t * d.rows + b) * kArParts + part;
         int seen = 0;
         bool ok = false;
         if (*reinterpret_cast<volatile int*>(&g_vk_status) == 0) {
@@ -85,7 +93,7 @@ __device__ __forceinline__ void ar_reduce_row(const VkArCall& a, __nv_bfloat16* 
     }
     __syncthreads();
     const uint8_t* local = d.slots[d.rank];
-    for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
+    for (int v = v_begin + threadIdx.x; v < nvec; v += blockDim.x) {
         float s[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
         for (int p = 0; p < d.world; p++) {
             uint4 u;

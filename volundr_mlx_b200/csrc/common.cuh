@@ -151,6 +151,28 @@ static inline cudaError_t vk_launch(void (*kernel)(KArgs...), dim3 grid, dim3 bl
     return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
 }
 
+// The same with thread-block clusters of `cluster_x` CTAs along x (grid.x a multiple of it).
+template <typename... KArgs, typename... Args>
+static inline cudaError_t vk_launch_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, int cluster_x, size_t smem,
+                                            cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = vk_pdl_enabled() ? 1 : 0;
+    attr[1].id = cudaLaunchAttributeClusterDimension;
+    attr[1].val.clusterDim.x = (unsigned)cluster_x;
+    attr[1].val.clusterDim.y = 1;
+    attr[1].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 2;
+    g_vk_launches++;
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
 #define VK_CUDA(call)                              \
     do {                                           \
         cudaError_t e_ = (call);                   \

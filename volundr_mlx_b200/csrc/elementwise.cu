@@ -6,6 +6,7 @@
 #include "common.cuh"
 #include "xrec.cuh"
 #include "allreduce.cuh"
+#include <cooperative_groups.h>
 
 namespace {
 
@@ -105,7 +106,7 @@ __global__ void __launch_bounds__(kEwThreads) embed_kernel(const EmbedParams p) 
 // eight products as one fma chain, an xor tree over the warp, then the warps in order. part: [24][32] floats of shared
 // memory; dsm[24] receives the bf16-rounded results (valid after the function's last barrier).
 __device__ __forceinline__ void dyn24(const float (&hv)[8], bool on, int k, const __nv_bfloat16* __restrict__ w_dyn, int D,
-                                      float* part, float* dsm) {
+                                      float* part, float* dsm, bool round_out = true) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = (blockDim.x + 31) >> 5;
 #pragma unroll
     for (int j0 = 0; j0 < 24; j0 += 8) {
@@ -135,7 +136,7 @@ __device__ __forceinline__ void dyn24(const float (&hv)[8], bool on, int k, cons
     if (threadIdx.x < 24) {
         float a = 0.f;
         for (int w = 0; w < nw; w++) a += part[threadIdx.x * 32 + w];
-        dsm[threadIdx.x] = bfr(a);
+        dsm[threadIdx.x] = round_out ? bfr(a) : a;   // (a cluster adds its CTAs' sums before rounding)
     }
     __syncthreads();
 }
@@ -174,10 +175,10 @@ __device__ __forceinline__ void mhc_params_warp(const float* dsm, const MhcStati
         m = m / fmaxf(((a0 + a1) + a2) + a3, 1e-9f);
     }
     VK_TS(3, 10);
-    if (lane < 16) res_out[i] = bfr(m);
+    if (lane < 16 && res_out != nullptr) res_out[i] = bfr(m);
     if (lane < 4) {
         pre_sm[lane] = bfr(st.pre + dsm[lane]);
-        post_out[lane] = bfr(st.post + dsm[4 + lane]);
+        if (post_out != nullptr) post_out[lane] = bfr(st.post + dsm[4 + lane]);
     }
 }
 
@@ -515,21 +516,44 @@ struct BoundaryParams {
 
 constexpr int kBoundaryThreads = 640;
 
+// CL = 1: one CTA of D / 8 threads per row. CL = 4: a cluster of four CTAs per row, each with a quarter of the row's
+// 16-byte pieces; row-wide sums (norms, the engram gate, the 24 dyn products) are formed per CTA and then added over
+// the cluster through distributed shared memory in rank order, the 4 x 4 Sinkhorn runs in every CTA (identical inputs,
+// identical results) and rank 0 stores it. The row's arithmetic is spread over four SMs instead of one.
+template <int CL>
 __global__ void __launch_bounds__(kBoundaryThreads) mhc_boundary_kernel(const BoundaryParams q) {
     __shared__ float red[kRowMaxWarps];
     __shared__ float part[24 * 32];
     __shared__ float dsm[24];
     __shared__ float pre_sm[4];
+    __shared__ float csum[4];      // this CTA's share of the row-wide sums: gate, ss, ss2 (read by the cluster)
+    __shared__ float cdyn[24];     // ... and of the dyn products
     pdl_launch_dependents();
     VK_TS(3, 0);
     const CombineParams& p = q.c;
-    const int b = blockIdx.x, D = p.D;
+    namespace cg = cooperative_groups;
+    const int crank = CL > 1 ? (int)cg::this_cluster().block_rank() : 0;
+    const int b = blockIdx.x / CL, D = p.D;
     const size_t base = (size_t)b * D;
-    const int k = threadIdx.x * 8;
+    const int piece = crank * blockDim.x + threadIdx.x;
+    const int k = piece * 8;
     const bool on = k < D;
+    // sum over the row of a value every thread holds: block sum, then (CL > 1) the CTAs' sums in rank order
+    auto row_sum = [&](float v, int slot) -> float {
+        float t = row_block_sum(v, red);
+        if constexpr (CL > 1) {
+            cg::cluster_group cluster = cg::this_cluster();
+            if (threadIdx.x == 0) csum[slot] = t;
+            cluster.sync();
+            t = 0.f;
+#pragma unroll
+            for (int r = 0; r < CL; r++) t += *cluster.map_shared_rank(&csum[slot], r);
+        }
+        return t;
+    };
     // weights depend on no earlier kernel: fetch this thread's pieces, and start the 24 dyn rows towards L2, while the
     // kernel before this one is still running
-    if (threadIdx.x < 24) l2_prefetch_bulk(q.w_dyn + (size_t)threadIdx.x * D, (uint32_t)D * 2u);
+    if (crank == 0 && threadIdx.x < 24) l2_prefetch_bulk(q.w_dyn + (size_t)threadIdx.x * D, (uint32_t)D * 2u);
     MhcStatic mst = {0.f, 0.f, 0.f};
     if (threadIdx.x < 32) mst = mhc_static_load(q.pre_s, q.post_s, q.res_s);
     uint4 w_next_raw = make_uint4(0u, 0u, 0u, 0u), w_in_raw = w_next_raw;
@@ -539,11 +563,22 @@ __global__ void __launch_bounds__(kBoundaryThreads) mhc_boundary_kernel(const Bo
     }
     pdl_wait();
     VK_TS(3, 1);
-    ar_reduce_row(p.ar, const_cast<__nv_bfloat16*>(p.m) + base, b, D);
+    ar_reduce_span(p.ar, const_cast<__nv_bfloat16*>(p.m) + base, b, D, crank, CL);
     VK_TS(3, 2);
     float gate = 0.f;
     float hv[8] = {}, mv[8] = {}, xv[8] = {};
     if (on) { ld8(p.h2 + base + k, hv); ld8(p.m + base + k, mv); ld8(p.x_in + base + k, xv); }
+    float r[16], po[4];
+#pragma unroll
+    for (int i = 0; i < 16; i++) r[i] = p.res[b * 16 + i];
+#pragma unroll
+    for (int s = 0; s < 4; s++) po[s] = p.post[b * 4 + s];
+    __nv_bfloat16* Hb = p.H + (size_t)b * 4 * D;
+    float hj[4][8] = {};
+    if (on) {
+#pragma unroll
+        for (int j = 0; j < 4; j++) ld8(Hb + (size_t)j * D + k, hj[j]);
+    }
     if (p.eng_val != nullptr) {
         float a = 0.f;
         if (on) {
@@ -552,22 +587,14 @@ __global__ void __launch_bounds__(kBoundaryThreads) mhc_boundary_kernel(const Bo
 #pragma unroll
             for (int e = 0; e < 8; e++) a = fmaf(bfr(hv[e] + mv[e]), gw[e], a);
         }
-        a = row_block_sum(a, red);
+        a = row_sum(a, 0);
         gate = bfr(1.f / (1.f + expf(-bfr(a + bf2f(p.eng_gate_b[0])))));
     }
-    float r[16], po[4];
-#pragma unroll
-    for (int i = 0; i < 16; i++) r[i] = p.res[b * 16 + i];
-#pragma unroll
-    for (int s = 0; s < 4; s++) po[s] = p.post[b * 4 + s];
-    __nv_bfloat16* Hb = p.H + (size_t)b * 4 * D;
     float o[4][8] = {};
     float v[8] = {};
     float ss = 0.f;
     if (on) {
-        float hj[4][8], val[8];
-#pragma unroll
-        for (int j = 0; j < 4; j++) ld8(Hb + (size_t)j * D + k, hj[j]);
+        float val[8];
         if (p.eng_val != nullptr) ld8(p.eng_val + base + k, val);
 #pragma unroll
         for (int e = 0; e < 8; e++) {
@@ -589,7 +616,7 @@ __global__ void __launch_bounds__(kBoundaryThreads) mhc_boundary_kernel(const Bo
         for (int s = 0; s < 4; s++) st8(Hb + (size_t)s * D + k, o[s]);
     }
     VK_TS(3, 3);
-    ss = row_block_sum(ss, red);
+    ss = row_sum(ss, 1);
     VK_TS(3, 4);
     float hnv[8] = {};
     if (on) {
@@ -600,10 +627,24 @@ __global__ void __launch_bounds__(kBoundaryThreads) mhc_boundary_kernel(const Bo
         for (int e = 0; e < 8; e++) hnv[e] = bfr((v[e] * inv) * w_next8[e]);   // the next layer's mHC norm, as bf16 values
     }
     // ---- dyn of the next layer from the norm just formed (registers), then its mHC parameters on warp 0
-    dyn24(hnv, on, k, q.w_dyn, D, part, dsm);
+    if constexpr (CL > 1) {
+        cg::cluster_group cluster = cg::this_cluster();
+        dyn24(hnv, on, k, q.w_dyn, D, part, cdyn, false);
+        cluster.sync();
+        if (threadIdx.x < 24) {
+            float a = 0.f;
+#pragma unroll
+            for (int rk = 0; rk < CL; rk++) a += *cluster.map_shared_rank(&cdyn[threadIdx.x], rk);
+            dsm[threadIdx.x] = bfr(a);
+        }
+        __syncthreads();
+    } else {
+        dyn24(hnv, on, k, q.w_dyn, D, part, dsm);
+    }
     VK_TS(3, 5);
     if (threadIdx.x < 32)
-        mhc_params_warp(dsm, mst, q.iters, pre_sm, q.post_out + b * 4, q.res_out + b * 16);
+        mhc_params_warp(dsm, mst, q.iters, pre_sm, crank == 0 ? q.post_out + b * 4 : nullptr,
+                        crank == 0 ? q.res_out + b * 16 : nullptr);
     __syncthreads();
     VK_TS(3, 6);
     float x[8] = {};
@@ -616,7 +657,7 @@ __global__ void __launch_bounds__(kBoundaryThreads) mhc_boundary_kernel(const Bo
         }
         st8(q.x_in_out + base + k, x);
     }
-    ss2 = row_block_sum(ss2, red);
+    ss2 = row_sum(ss2, 2);
     VK_TS(3, 7);
     const float inv2 = rsqrtf(ss2 / (float)D + p.eps);
     float ho[8] = {};
@@ -628,9 +669,10 @@ __global__ void __launch_bounds__(kBoundaryThreads) mhc_boundary_kernel(const Bo
         st8(q.h + base + k, ho);
     }
     if (q.xrec_h != nullptr) {   // whole warps take part in the group sums
-        if (on) xrec_store_row_piece(q.xrec_h, b, threadIdx.x, ho);
+        if (on) xrec_store_row_piece(q.xrec_h, b, piece, ho);
         else { __shfl_xor_sync(0xffffffffu, 0.f, 1); __shfl_xor_sync(0xffffffffu, 0.f, 2); __shfl_xor_sync(0xffffffffu, 0.f, 4); }
     }
+    if constexpr (CL > 1) cg::this_cluster().sync();   // nobody leaves while its shared memory may still be read
     VK_TS(3, 8);
 }
 
@@ -755,7 +797,13 @@ __global__ void argmax_merge_kernel(const int* __restrict__ pairs, int n_ranks, 
 
 }  // namespace
 
+bool g_boundary_cluster = false;   // measured: no faster than one CTA per row (the kernel is bound by the latency of one
+                                   // thread's chain of loads and roundings, not by the SM's issue rate); kept selectable
+
 extern "C" {
+
+// 1: vk_mhc_boundary spreads a row over a cluster of four CTAs when the hidden size allows; 0 (default): one CTA per row
+void vk_mhc_boundary_set_cluster(int on) { g_boundary_cluster = on != 0; }
 
 int vk_argmax_pairs(const void* logits, int ld, int valid, int index_offset, int* pairs, int B, cudaStream_t stream) {
     if (B <= 0) return VK_EINVAL;
@@ -886,8 +934,11 @@ int vk_mhc_boundary_ar(void* H, const void* h2, void* m, void* x_in, float* post
     q.w_dyn = (const __nv_bfloat16*)w_dyn; q.pre_s = (const __nv_bfloat16*)pre_s; q.post_s = (const __nv_bfloat16*)post_s;
     q.res_s = (const __nv_bfloat16*)res_s; q.w_in = (const __nv_bfloat16*)w_in; q.x_in_out = (__nv_bfloat16*)x_in;
     q.h = (__nv_bfloat16*)h; q.xrec_h = (uint8_t*)xrec_h; q.post_out = post; q.res_out = res; q.iters = iters;
+    // a cluster of four CTAs per row when the row's pieces split into four whole x-record groups per CTA
+    if (g_boundary_cluster && D % 256 == 0 && (D / 32) % 32 == 0)
+        return (int)vk_launch_cluster(mhc_boundary_kernel<4>, dim3(B * 4), dim3(D / 32), 4, 0, stream, q);
     const int threads = ((D / 8 + 31) / 32) * 32;
-    return (int)vk_launch(mhc_boundary_kernel, dim3(B), dim3(threads), 0, stream, q);
+    return (int)vk_launch(mhc_boundary_kernel<1>, dim3(B), dim3(threads), 0, stream, q);
 }
 
 int vk_mhc_boundary(void* H, const void* h2, const void* m, void* x_in, float* post, float* res, const void* w_next,
