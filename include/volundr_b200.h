@@ -165,6 +165,16 @@ int vk_kda_step(const void* proj, int ldp, int off_z, int off_fd, const void* h,
                 const float* conv_w, const float* A_log, const float* dt_bias, const void* norm_w, void* conv,
                 const int* parity, size_t conv_stride, float* S, void* out, void* xrec_out, const float* g_override, int B,
                 int D, int Hk, int HV, int Dk, int Dv, int rank, float eps, int early_state, vk_stream_t stream);
+/* The same recurrence over a chunk of T tokens per row in one launch, the state read and written once: the prefill
+ * form (kernels.gated_delta_tg, kernels.py:544-555) and the verify / commit-replay form (verify._kda,
+ * spec/verify.py:33-53; batch_spec.py:186-195). Rows of proj / h / out are b * T + t. accept (optional, [B]): row b
+ * stops after accept[b] tokens; later tokens leave state, conv window and output alone. Results equal T (or accept[b])
+ * calls of vk_kda_step bit for bit. The conv window after the chunk lands in the other buffer, as after one step: flip
+ * the parity word once per launch. */
+int vk_kda_chunk(const void* proj, int ldp, int off_z, int off_fd, const void* h, const void* w_b, const void* w_fup,
+                 const float* conv_w, const float* A_log, const float* dt_bias, const void* norm_w, void* conv,
+                 const int* parity, size_t conv_stride, float* S, void* out, const int* accept, int B, int T, int D, int Hk,
+                 int HV, int Dk, int Dv, int rank, float eps, vk_stream_t stream);
 /* early_state = 1 lets the kernel request the first rows of S before it waits for the kernel in front of it (they then
  * stream in while that kernel finishes). Only valid when every earlier writer of S is known to have completed before
  * this launch can start: true inside a replayed CUDA graph of one step (the previous step's replay is complete), not

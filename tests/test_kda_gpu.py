@@ -107,3 +107,70 @@ def test_kda_step_state_and_output(cuda, Hk):
     cur = int(t_par.item())
     got_conv = t_conv[cur].float().cpu().numpy()
     np.testing.assert_array_equal(got_conv, np.stack([r["conv"] for r in rows]))
+
+
+@pytest.mark.parametrize("Hk,T", [(40, 8), (8, 19)])
+def test_kda_chunk_equals_steps(cuda, Hk, T):
+    """vk_kda_chunk (T tokens per row in one launch: the prefill / verify form) against T calls of vk_kda_step on the
+    same inputs: state, outputs and conv window bit for bit; with `accept`, row b equals accept[b] steps and its later
+    outputs stay untouched (the commit replay of a verify step, batch_spec.py:186-195)."""
+    from volundr_mlx_b200 import _lib, ops
+
+    L = _lib.lib()
+    g = torch.Generator(device="cpu").manual_seed(100 + T)
+    B, HV, K, V, D, rank = 5, 40, 128, 128, 1024, 128
+    C = 2 * Hk * K + HV * V
+    ldp = C + HV * V + rank
+    bf = dict(dtype=torch.bfloat16, device=cuda)
+    proj = torch.randn(B, T, ldp, generator=g).to(**bf)
+    h = torch.randn(B, T, D, generator=g).to(**bf)
+    w_b = (torch.randn(HV, D, generator=g) * 0.05).to(**bf)
+    fup_rows = (torch.randn(HV * K, rank, generator=g) * 0.1).to(**bf)
+    fup = torch.empty_like(fup_rows)
+    st = torch.cuda.current_stream().cuda_stream
+    _lib.check(L.vk_kda_pack_fup(fup_rows.data_ptr(), fup.data_ptr(), HV, rank, st), "vk_kda_pack_fup")
+    conv_w = torch.randn(C, 4, generator=g).to(cuda)
+    A_log = (torch.rand(HV, generator=g) * 2 - 1).to(cuda)
+    dt_bias = torch.randn(HV * K, generator=g).to(cuda)
+    norm_w = (1 + 0.1 * torch.randn(V, generator=g)).to(**bf)
+    S0 = (torch.randn(B, HV, V, K, generator=g) * 0.1).to(cuda)
+    conv0 = torch.randn(B, 3, C, generator=g).to(**bf)
+    _lib.check(L.vk_kda_configure(), "vk_kda_configure")
+    p = lambda t: t.data_ptr()
+
+    def steps(n_per_row):
+        """n_per_row[b] sequential vk_kda_step calls for row b (one row at a time)."""
+        S, outs, convs = S0.clone(), torch.zeros(B, T, HV * V, **bf), torch.zeros(B, 3, C, **bf)
+        for b in range(B):
+            conv = torch.zeros(2, 1, 3, C, **bf)
+            conv[0, 0] = conv0[b]
+            par = torch.zeros(1, dtype=torch.int32, device=cuda)
+            Sb = S[b:b + 1].clone()
+            for t in range(n_per_row[b]):
+                o = torch.empty(1, HV * V, **bf)
+                _lib.check(L.vk_kda_step(p(proj[b, t]), ldp, C, C + HV * V, p(h[b, t]), p(w_b), p(fup), p(conv_w), p(A_log),
+                                         p(dt_bias), p(norm_w), p(conv), p(par), conv[0].numel(), p(Sb), p(o), None, None, 1,
+                                         D, Hk, HV, K, V, rank, 1e-6, 0, st), "vk_kda_step")
+                par ^= 1
+                outs[b, t] = o[0]
+            S[b] = Sb[0]
+            convs[b] = conv[int(par.item()), 0]
+        return S, outs, convs
+
+    def chunk(accept):
+        S, outs = S0.clone(), torch.zeros(B, T, HV * V, **bf)
+        conv = torch.zeros(2, B, 3, C, **bf)
+        conv[0] = conv0
+        par = torch.zeros(1, dtype=torch.int32, device=cuda)
+        acc = torch.tensor(accept, dtype=torch.int32, device=cuda) if accept is not None else None
+        _lib.check(L.vk_kda_chunk(p(proj), ldp, C, C + HV * V, p(h), p(w_b), p(fup), p(conv_w), p(A_log), p(dt_bias),
+                                  p(norm_w), p(conv), p(par), conv[0].numel(), p(S), p(outs), p(acc) if acc is not None else None,
+                                  B, T, D, Hk, HV, K, V, rank, 1e-6, st), "vk_kda_chunk")
+        return S, outs, conv[1]
+
+    for accept in (None, [0, 1, T // 2, T - 1, T]):
+        want = steps([T] * B if accept is None else accept)
+        got = chunk(accept)
+        ops.check_status()
+        for name, a, b_ in zip(("state", "out", "conv"), got, want):
+            assert torch.equal(a, b_), (name, accept, float((a.float() - b_.float()).abs().max()))

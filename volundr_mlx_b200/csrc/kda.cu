@@ -290,6 +290,214 @@ __global__ void __launch_bounds__(128, 5) kda_step_kernel(const KdaParams p) {
 
 }  // namespace
 
+// ------------------------------------------------------------------------------------------------ T tokens per row
+// The same recurrence over a chunk of T tokens per row in one launch: the prefill form (kernels.gated_delta_tg,
+// kernels.py:544-555) and the verify / commit-replay form (verify._kda, spec/verify.py:33-53; batch_spec.py:186-195).
+// One CTA of 128 threads per (value head, row). Thread c keeps row c of the state S[Dv, Dk] (128 fp32 values) in
+// registers for the whole chunk: the state is read once and written once per launch, however many tokens there are.
+// Tokens go through in groups of kChunkTok: (A) conv + SiLU, norms, decay and beta of the group's tokens, (B) the
+// recurrence, token after token, thread-local (every row dot is formed as 32 four-element fma chains combined in the
+// order of a warp's xor tree: the sums, and so every bit of the result, are those of kda_step_kernel), (C) the gated
+// norm of the group's outputs. `accept[b]` (optional) ends row b's chunk early: later tokens leave state, conv window
+// and output alone (the commit of a verify step: only the accepted prefix is replayed).
+constexpr int kChunkTok = 8;
+
+struct KdaChunkParams {
+    KdaParams k;          // proj / h / out rows are (b * T + t); g_override, xrec_out, early_state unused
+    const int* accept;    // [B] or null
+    int T;
+};
+
+// xor-tree sum of p[0..31] as the 32 lanes of a warp would form it
+__device__ __forceinline__ float tree32(float (&p)[32]) {
+#pragma unroll
+    for (int l = 0; l < 16; l++) p[l] += p[l + 16];
+#pragma unroll
+    for (int l = 0; l < 8; l++) p[l] += p[l + 8];
+#pragma unroll
+    for (int l = 0; l < 4; l++) p[l] += p[l + 4];
+    p[0] += p[2]; p[1] += p[3];
+    return p[0] + p[1];
+}
+
+__global__ void __launch_bounds__(128, 2) kda_chunk_kernel(const KdaChunkParams cp) {
+    const KdaParams& p = cp.k;
+    __shared__ __align__(16) float qs[kChunkTok][128], ks[kChunkTok][128], gs[kChunkTok][128];
+    __shared__ float vs[kChunkTok][128], ys[kChunkTok][128];
+    __shared__ float fd[kChunkTok][256];
+    __shared__ float red[4 * kChunkTok][4];
+    __shared__ float betas[kChunkTok];
+    pdl_launch_dependents();
+    const int hv = blockIdx.x, b = blockIdx.y;
+    const int c = threadIdx.x, lane = c & 31, warp = c >> 5;
+    const int rep = p.HV / p.Hk, hk = hv / rep;
+    const int KD = p.Hk * 128, C = 2 * KD + p.HV * 128;
+    const int ch[3] = {hk * 128 + c, KD + hk * 128 + c, 2 * KD + hv * 128 + c};
+    const uint4* fup = reinterpret_cast<const uint4*>(p.w_fup) + (size_t)hv * (p.rank / 8) * 128 + c;
+    float4 cw[3];
+#pragma unroll
+    for (int i = 0; i < 3; i++) cw[i] = *reinterpret_cast<const float4*>(p.conv_w + (size_t)ch[i] * 4);
+    const float a_log = p.A_log[hv], dtb = p.dt_bias[hv * 128 + c], nw = bf2f(p.norm_w[c]);
+    const __nv_bfloat16* wb = p.w_b + (size_t)hv * p.D;
+    uint4 wbv[kBdotPieces];
+#pragma unroll
+    for (int i = 0; i < kBdotPieces; i++) {
+        const int k = c * 8 + i * 1024;
+        wbv[i] = k < p.D ? *reinterpret_cast<const uint4*>(wb + k) : make_uint4(0u, 0u, 0u, 0u);
+    }
+    pdl_wait();
+    const int T = cp.T;
+    const int n_tok = cp.accept != nullptr ? min(max(cp.accept[b], 0), T) : T;
+    const int par = *p.parity & 1;
+    const __nv_bfloat16* conv_in = p.conv + (size_t)par * p.conv_stride;
+    __nv_bfloat16* conv_out = p.conv + (size_t)(1 - par) * p.conv_stride;
+    // this thread's state row, and the three inputs in front of the chunk of its q / k / v channels
+    float* Srow = p.S + ((((size_t)b * p.HV + hv) * 128) + c) * 128;
+    float st[128];
+#pragma unroll
+    for (int j = 0; j < 32; j++) {
+        const float4 v4 = *reinterpret_cast<const float4*>(Srow + 4 * j);
+        st[4 * j] = v4.x; st[4 * j + 1] = v4.y; st[4 * j + 2] = v4.z; st[4 * j + 3] = v4.w;
+    }
+    __nv_bfloat16 win[3][3];
+#pragma unroll
+    for (int i = 0; i < 3; i++) {
+        const size_t cb = (size_t)b * 3 * C + ch[i];
+        win[i][0] = conv_in[cb]; win[i][1] = conv_in[cb + C]; win[i][2] = conv_in[cb + 2 * (size_t)C];
+    }
+
+    for (int t0 = 0; t0 < n_tok; t0 += kChunkTok) {
+        const int nt = min(kChunkTok, n_tok - t0);
+        // ---- (A1) per token: f_down into shared memory, conv + SiLU, partial sums of the two norms and of beta's dot
+        // (the raw conv outputs wait in qs / ks / vs, at the thread's own slots, for the norms)
+#pragma unroll 1
+        for (int tt = 0; tt < kChunkTok; tt++) {
+            if (tt < nt) {
+                const size_t rowi = (size_t)b * T + t0 + tt;
+                const __nv_bfloat16* pr = p.proj + rowi * p.ldp;
+                for (int i = c; i < p.rank; i += 128) fd[tt][i] = bf2f(pr[p.off_fd + i]);
+                float s3[3];
+#pragma unroll
+                for (int i = 0; i < 3; i++) {
+                    const __nv_bfloat16 x3 = pr[ch[i]];
+                    float acc = __fmul_rn(bf2f(win[i][0]), cw[i].x);
+                    acc = __fadd_rn(acc, __fmul_rn(bf2f(win[i][1]), cw[i].y));
+                    acc = __fadd_rn(acc, __fmul_rn(bf2f(win[i][2]), cw[i].z));
+                    acc = __fadd_rn(acc, __fmul_rn(bf2f(x3), cw[i].w));
+                    s3[i] = bfr(acc / (1.f + expf(-acc)));
+                    win[i][0] = win[i][1]; win[i][1] = win[i][2]; win[i][2] = x3;
+                }
+                qs[tt][c] = s3[0]; ks[tt][c] = s3[1]; vs[tt][c] = s3[2];
+                const __nv_bfloat16* hb = p.h + rowi * p.D;
+                float bdot = 0.f;
+#pragma unroll
+                for (int i = 0; i < kBdotPieces; i++) {
+                    const int k = c * 8 + i * 1024;
+                    const uint4 wv = wbv[i];
+                    const uint4 xv = k < p.D ? *reinterpret_cast<const uint4*>(hb + k) : make_uint4(0u, 0u, 0u, 0u);
+                    bdot = fmaf(bf_lo(wv.x), bf_lo(xv.x), bdot); bdot = fmaf(bf_hi(wv.x), bf_hi(xv.x), bdot);
+                    bdot = fmaf(bf_lo(wv.y), bf_lo(xv.y), bdot); bdot = fmaf(bf_hi(wv.y), bf_hi(xv.y), bdot);
+                    bdot = fmaf(bf_lo(wv.z), bf_lo(xv.z), bdot); bdot = fmaf(bf_hi(wv.z), bf_hi(xv.z), bdot);
+                    bdot = fmaf(bf_lo(wv.w), bf_lo(xv.w), bdot); bdot = fmaf(bf_hi(wv.w), bf_hi(xv.w), bdot);
+                }
+                for (int k = c * 8 + kBdotPieces * 1024; k < p.D; k += 1024) {   // (hidden sizes beyond 5120)
+                    const uint4 wv = *reinterpret_cast<const uint4*>(wb + k);
+                    const uint4 xv = *reinterpret_cast<const uint4*>(hb + k);
+                    bdot = fmaf(bf_lo(wv.x), bf_lo(xv.x), bdot); bdot = fmaf(bf_hi(wv.x), bf_hi(xv.x), bdot);
+                    bdot = fmaf(bf_lo(wv.y), bf_lo(xv.y), bdot); bdot = fmaf(bf_hi(wv.y), bf_hi(xv.y), bdot);
+                    bdot = fmaf(bf_lo(wv.z), bf_lo(xv.z), bdot); bdot = fmaf(bf_hi(wv.z), bf_hi(xv.z), bdot);
+                    bdot = fmaf(bf_lo(wv.w), bf_lo(xv.w), bdot); bdot = fmaf(bf_hi(wv.w), bf_hi(xv.w), bdot);
+                }
+                const float w0 = warp_sum(s3[0] * s3[0]), w1 = warp_sum(s3[1] * s3[1]), w2 = warp_sum(bdot);
+                if (lane == 0) { red[3 * tt][warp] = w0; red[3 * tt + 1][warp] = w1; red[3 * tt + 2][warp] = w2; }
+            }
+        }
+        __syncthreads();
+        // ---- (A2) per token: q^ / k^ / v, decay, beta
+#pragma unroll 1
+        for (int tt = 0; tt < kChunkTok; tt++) {
+            if (tt < nt) {
+                const float ssq = ((red[3 * tt][0] + red[3 * tt][1]) + red[3 * tt][2]) + red[3 * tt][3];
+                const float ssk = ((red[3 * tt + 1][0] + red[3 * tt + 1][1]) + red[3 * tt + 1][2]) + red[3 * tt + 1][3];
+                const float bd = ((red[3 * tt + 2][0] + red[3 * tt + 2][1]) + red[3 * tt + 2][2]) + red[3 * tt + 2][3];
+                qs[tt][c] = (qs[tt][c] / sqrtf(ssq + 1e-6f)) * 0.08838834764831845f;  // 128^-1/2
+                ks[tt][c] = ks[tt][c] / sqrtf(ssk + 1e-6f);
+                float a = 0.f;
+                for (int r = 0; r < p.rank; r += 8) {
+                    const uint4 wv = fup[(size_t)(r / 8) * 128];
+                    a = fmaf(bf_lo(wv.x), fd[tt][r], a); a = fmaf(bf_hi(wv.x), fd[tt][r + 1], a);
+                    a = fmaf(bf_lo(wv.y), fd[tt][r + 2], a); a = fmaf(bf_hi(wv.y), fd[tt][r + 3], a);
+                    a = fmaf(bf_lo(wv.z), fd[tt][r + 4], a); a = fmaf(bf_hi(wv.z), fd[tt][r + 5], a);
+                    a = fmaf(bf_lo(wv.w), fd[tt][r + 6], a); a = fmaf(bf_hi(wv.w), fd[tt][r + 7], a);
+                }
+                a = bfr(a);
+                gs[tt][c] = expf(-expf(a_log) * softplus_f(a + dtb));
+                if (c == 0) betas[tt] = 1.f / (1.f + expf(-bfr(bd)));
+            }
+        }
+        __syncthreads();
+        // ---- (B) the recurrence, token after token; thread c owns row c of S
+        for (int tt = 0; tt < nt; tt++) {
+            const float beta = betas[tt];
+            float pp[32];
+#pragma unroll
+            for (int l = 0; l < 32; l++) {
+                const float4 g4 = *reinterpret_cast<const float4*>(&gs[tt][4 * l]);
+                const float4 k4 = *reinterpret_cast<const float4*>(&ks[tt][4 * l]);
+                st[4 * l] *= g4.x; st[4 * l + 1] *= g4.y; st[4 * l + 2] *= g4.z; st[4 * l + 3] *= g4.w;
+                pp[l] = fmaf(st[4 * l + 3], k4.w, fmaf(st[4 * l + 2], k4.z, fmaf(st[4 * l + 1], k4.y, st[4 * l] * k4.x)));
+            }
+            const float d = (vs[tt][c] - tree32(pp)) * beta;
+#pragma unroll
+            for (int l = 0; l < 32; l++) {
+                const float4 k4 = *reinterpret_cast<const float4*>(&ks[tt][4 * l]);
+                const float4 q4 = *reinterpret_cast<const float4*>(&qs[tt][4 * l]);
+                st[4 * l] = fmaf(d, k4.x, st[4 * l]); st[4 * l + 1] = fmaf(d, k4.y, st[4 * l + 1]);
+                st[4 * l + 2] = fmaf(d, k4.z, st[4 * l + 2]); st[4 * l + 3] = fmaf(d, k4.w, st[4 * l + 3]);
+                pp[l] = fmaf(st[4 * l + 3], q4.w, fmaf(st[4 * l + 2], q4.z, fmaf(st[4 * l + 1], q4.y, st[4 * l] * q4.x)));
+            }
+            ys[tt][c] = tree32(pp);
+        }
+        // ---- (C) gated norm of the group's outputs (each thread reads back only what it wrote)
+#pragma unroll 1
+        for (int tt = 0; tt < kChunkTok; tt++) {
+            if (tt < nt) {
+                const float ybv = bfr(ys[tt][c]);
+                const float w = warp_sum(ybv * ybv);
+                if (lane == 0) red[3 * kChunkTok + tt][warp] = w;
+            }
+        }
+        __syncthreads();
+#pragma unroll 1
+        for (int tt = 0; tt < kChunkTok; tt++) {
+            if (tt < nt) {
+                const float ybv = bfr(ys[tt][c]);
+                const float* rr = red[3 * kChunkTok + tt];
+                float ss = 0.f;
+                ss += rr[0]; ss += rr[1]; ss += rr[2]; ss += rr[3];
+                const float inv = rsqrtf(ss * (1.f / 128.f) + p.eps);
+                const size_t rowi = (size_t)b * T + t0 + tt;
+                const float z = bf2f(p.proj[rowi * p.ldp + p.off_z + hv * 128 + c]);
+                const float ov = bfr(((ybv * inv) * nw) * (z / (1.f + expf(-z))));
+                p.out[rowi * p.HV * 128 + hv * 128 + c] = f2bf(ov);
+            }
+        }
+        __syncthreads();   // the group's shared arrays are free again
+    }
+#pragma unroll
+    for (int j = 0; j < 32; j++)
+        *reinterpret_cast<float4*>(Srow + 4 * j) = make_float4(st[4 * j], st[4 * j + 1], st[4 * j + 2], st[4 * j + 3]);
+#pragma unroll
+    for (int i = 0; i < 3; i++) {
+        if (i == 2 || hv % rep == 0) {
+            const size_t cb = (size_t)b * 3 * C + ch[i];
+            conv_out[cb] = win[i][0];
+            conv_out[cb + C] = win[i][1];
+            conv_out[cb + 2 * (size_t)C] = win[i][2];
+        }
+    }
+}
+
 // f_up [HV*128, rank] row-major (the checkpoint's layout) -> [HV][rank / 8][128][8]
 __global__ void kda_pack_fup_kernel(const __nv_bfloat16* __restrict__ src, __nv_bfloat16* __restrict__ dst, int HV, int rank) {
     const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -317,6 +525,25 @@ int vk_kda_pack_fup(const void* src, void* dst, int HV, int rank, cudaStream_t s
 int vk_kda_configure(void) {
     VK_CUDA(cudaFuncSetAttribute(kda_step_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
     return VK_OK;
+}
+
+// T tokens per row in one launch (prefill chunks; verify and its commit replay). Rows of proj / h / out are b * T + t.
+// accept (optional, [B]): row b stops after accept[b] tokens. The conv window after the chunk lands in the other
+// buffer, as after one vk_kda_step: flip the parity word once per launch.
+int vk_kda_chunk(const void* proj, int ldp, int off_z, int off_fd, const void* h, const void* w_b, const void* w_fup,
+                 const float* conv_w, const float* A_log, const float* dt_bias, const void* norm_w, void* conv,
+                 const int* parity, size_t conv_stride, float* S, void* out, const int* accept, int B, int T, int D, int Hk,
+                 int HV, int Dk, int Dv, int rank, float eps, cudaStream_t stream) {
+    if (B <= 0 || T <= 0 || Dk != 128 || Dv != 128 || Hk <= 0 || HV % Hk != 0 || rank <= 0 || rank > 256 || rank % 8 != 0 ||
+        D % 8 != 0 || parity == nullptr)
+        return VK_EINVAL;
+    KdaChunkParams cp = {};
+    cp.k = {(const __nv_bfloat16*)proj, (const __nv_bfloat16*)h, (const __nv_bfloat16*)w_b, (const __nv_bfloat16*)w_fup,
+            conv_w, A_log, dt_bias, (const __nv_bfloat16*)norm_w, (__nv_bfloat16*)conv, parity, conv_stride, S,
+            (__nv_bfloat16*)out, nullptr, nullptr, ldp, off_z, off_fd, D, Hk, HV, rank, eps, 0};
+    cp.accept = accept;
+    cp.T = T;
+    return (int)vk_launch(kda_chunk_kernel, dim3(HV, B), dim3(128), 0, stream, cp);
 }
 
 int vk_kda_step(const void* proj, int ldp, int off_z, int off_fd, const void* h, const void* w_b, const void* w_fup,
