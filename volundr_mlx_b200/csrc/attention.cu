@@ -282,9 +282,13 @@ __global__ void __launch_bounds__(256) bcsa_select_kernel(const SelectParams p) 
         uint8_t* krows = dsm;                                                    // [nv][272 bytes]
         float* qsm = reinterpret_cast<float*>(dsm + (size_t)kFastBlocks * kKeyStride);   // [8][128]
         uint32_t* skeys = reinterpret_cast<uint32_t*>(qsm + 8 * kD);             // [512]
+        // (the pages of all blocks first, in one round of loads: a table load in front of every copy below would
+        // serialise them, the copy instructions being ordered against memory operations)
+        for (int j = threadIdx.x; j < nv; j += 256) skeys[j] = (uint32_t)p.table[b * g.max_pages + (j / spp)];
+        __syncthreads();
         for (int idx = threadIdx.x; idx < nv * 16; idx += 256) {
             const int j = idx >> 4, piece = idx & 15;
-            const int page = p.table[b * g.max_pages + (j / spp)];
+            const int page = (int)skeys[j];
             const __nv_bfloat16* kr = per_kv ? p.keys + (((size_t)page * g.KVH + ns) * spp + j % spp) * kD
                                              : p.keys + ((size_t)page * spp + j % spp) * kD;
             cp_async16(krows + (size_t)j * kKeyStride + piece * 16, reinterpret_cast<const uint8_t*>(kr) + piece * 16);
@@ -292,9 +296,9 @@ __global__ void __launch_bounds__(256) bcsa_select_kernel(const SelectParams p) 
         cp_async_commit();
         for (int i = threadIdx.x; i < nh * kD; i += 256) qsm[i] = bf2f(qb[i]);
         const int nv4 = (nv + 3) >> 2;
-        for (int i = nv + threadIdx.x; i < nv4 * 4; i += 256) skeys[i] = 0u;   // below every real key
         cp_async_wait0();
-        __syncthreads();
+        __syncthreads();   // (also: every thread is done with the page numbers held in skeys)
+        for (int i = nv + threadIdx.x; i < nv4 * 4; i += 256) skeys[i] = 0u;   // below every real key
         const float inv_nh = 1.f / (float)nh;
         for (int j = threadIdx.x; j < nv; j += 256) {
             const uint8_t* kr = krows + (size_t)j * kKeyStride;
