@@ -86,6 +86,7 @@ int vk_mhc_mix_norm(const void* H, const void* hn, const void* w_dyn, const void
                     float* d_scratch, int B, int D, int iters, float eps, vk_stream_t stream);
 /* kernels.rms_norm(x, w, eps, offset, r) (kernels.py:285-306; volundr.py:893-899): h2 = bf16(x + r) (r, h2 may be
  * NULL), hn = RMSNorm(h2) * (offset + w). */
+/* (With r given, x is read before the kernel waits for the launch in front of it: that launch may write r, not x.) */
 int vk_add_rmsnorm(const void* x, const void* r, const void* w, void* h2, void* hn, void* xrec_hn, int B, int D, float eps,
                    int offset, vk_stream_t stream);
 /* _silu_mul (volundr.py:166-168) on gu = [gate (I) | up (I)] rows of stride ld_gu. */
@@ -164,7 +165,7 @@ int vk_kda_configure(void);   /* once per device, outside stream capture: shared
 int vk_kda_step(const void* proj, int ldp, int off_z, int off_fd, const void* h, const void* w_b, const void* w_fup,
                 const float* conv_w, const float* A_log, const float* dt_bias, const void* norm_w, void* conv,
                 const int* parity, size_t conv_stride, float* S, void* out, void* xrec_out, const float* g_override, int B,
-                int D, int Hk, int HV, int Dk, int Dv, int rank, float eps, int early_state, vk_stream_t stream);
+                int D, int Hk, int HV, int Dk, int Dv, int rank, float eps, vk_stream_t stream);
 /* The same recurrence over a chunk of T tokens per row in one launch, the state read and written once: the prefill
  * form (kernels.gated_delta_tg, kernels.py:544-555) and the verify / commit-replay form (verify._kda,
  * spec/verify.py:33-53; batch_spec.py:186-195). Rows of proj / h / out are b * T + t. accept (optional, [B]): row b
@@ -175,10 +176,8 @@ int vk_kda_chunk(const void* proj, int ldp, int off_z, int off_fd, const void* h
                  const float* conv_w, const float* A_log, const float* dt_bias, const void* norm_w, void* conv,
                  const int* parity, size_t conv_stride, float* S, void* out, const int* accept, int B, int T, int D, int Hk,
                  int HV, int Dk, int Dv, int rank, float eps, vk_stream_t stream);
-/* early_state = 1 lets the kernel request the first rows of S before it waits for the kernel in front of it (they then
- * stream in while that kernel finishes). Only valid when every earlier writer of S is known to have completed before
- * this launch can start: true inside a replayed CUDA graph of one step (the previous step's replay is complete), not
- * for back-to-back eager steps under programmatic dependent launch. 0 is always safe. */
+/* h, the state S, both conv buffers and the parity word are read before the kernel waits for the launch in front of
+ * it (they stream in while that launch finishes): none of them may be written by that launch. proj may. */
 
 /* ---- paged ragged attention (64-token pages). */
 typedef struct vk_attn_geom {

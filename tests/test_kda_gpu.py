@@ -85,7 +85,7 @@ def test_kda_step_state_and_output(cuda, Hk):
         _lib.check(L.vk_kda_step(t_proj.data_ptr(), ldp, C, C + HV * V, t_h.data_ptr(), t_wb.data_ptr(), t_fup.data_ptr(),
                                  t_convw.data_ptr(), t_alog.data_ptr(), t_dtb.data_ptr(), t_nw.data_ptr(), t_conv.data_ptr(),
                                  t_par.data_ptr(), t_conv[0].numel(), t_S.data_ptr(), t_out.data_ptr(), None, None, B, D, Hk,
-                                 HV, K, V, rank, args.rms_norm_eps, 0, st), "vk_kda_step")
+                                 HV, K, V, rank, args.rms_norm_eps, st), "vk_kda_step")
         t_par ^= 1
         want_out = []
         for b in range(B):
@@ -150,7 +150,7 @@ def test_kda_chunk_equals_steps(cuda, Hk, T):
                 o = torch.empty(1, HV * V, **bf)
                 _lib.check(L.vk_kda_step(p(proj[b, t]), ldp, C, C + HV * V, p(h[b, t]), p(w_b), p(fup), p(conv_w), p(A_log),
                                          p(dt_bias), p(norm_w), p(conv), p(par), conv[0].numel(), p(Sb), p(o), None, None, 1,
-                                         D, Hk, HV, K, V, rank, 1e-6, 0, st), "vk_kda_step")
+                                         D, Hk, HV, K, V, rank, 1e-6, st), "vk_kda_step")
                 par ^= 1
                 outs[b, t] = o[0]
             S[b] = Sb[0]

@@ -55,7 +55,7 @@ SIGNATURES = {
     "vk_kda_chunk": (c_int, [c_void_p, c_int, c_int, c_int] + [c_void_p] * 9 + [c_size_t, c_void_p, c_void_p, c_void_p]
                      + [c_int] * 8 + [c_float, c_void_p]),
     "vk_kda_step": (c_int, [c_void_p, c_int, c_int, c_int] + [c_void_p] * 9 + [c_size_t, c_void_p, c_void_p, c_void_p, c_void_p]
-                    + [c_int] * 7 + [c_float, c_int, c_void_p]),
+                    + [c_int] * 7 + [c_float, c_void_p]),
     "vk_batch_step_begin": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                     c_void_p]),
     "vk_batch_step_end": (c_int, [c_void_p, c_void_p, c_int, c_void_p]),

@@ -316,9 +316,6 @@ def _launch_step(model: Model, bc: BatchCache, capture=()):
     caps = []
 
     fx = bc.fused_xrec
-    # inside a captured step every earlier writer of the KDA state (the previous replay) has completed before this
-    # replay starts, so the state may be requested before a kernel's dependency wait; eager steps keep the safe order
-    early_state = 1 if torch.cuda.is_current_stream_capturing() else 0
     fuse_boundary = bc.fuse_boundary and D % 64 == 0 and D // 8 <= 640 and not capture
 
     def gemm(x, wt, y, xr=None):
@@ -357,7 +354,7 @@ def _launch_step(model: Model, bc: BatchCache, capture=()):
                              _p(w["f_up"]), _p(w["conv_w"]), _p(w["A_log"]), _p(w["dt_bias"]), _p(w["gnorm"]),
                              _p(lst["conv"]), _p(bc.parity), lst["conv"][0].numel(), _p(lst["S"]), _p(bc.mix),
                              _p(bc.xr_mix) if fx else None, None, B, D,
-                             model.Hk, model.HV, 128, 128, a.kda_gate_rank, eps, early_state, st), "vk_kda_step")
+                             model.Hk, model.HV, 128, 128, a.kda_gate_rank, eps, st), "vk_kda_step")
         else:
             bcsa = w["mixer"] == "bcsa"
             g = bc.geom[w["mixer"]]

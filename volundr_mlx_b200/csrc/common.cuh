@@ -131,7 +131,14 @@ __device__ __forceinline__ void tma_bulk_g2s(void* dst_smem, const void* src_gme
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
-// Host: launch with the PDL attribute (the kernel must call pdl_wait before reading its inputs).
+// Who may read what in front of its griddepcontrol.wait. A kernel can start as soon as every CTA of its predecessor
+// has executed launch_dependents. The streaming GEMMs (and the two small kernels that can stand in front of a layer
+// boundary: engram_gather, bf16_gemm_rows) execute it only AFTER their own wait: when their successor starts, the
+// GEMM's predecessor, and with it every earlier launch, has completed, so the successor (KDA, add + norm, the layer
+// boundary) may read, in front of its wait, anything written two or more launches back, just not the GEMM's output.
+// All other kernels execute launch_dependents first thing: their successors are GEMMs, which read nothing but
+// weights in front of their wait and should become resident as early as possible to start streaming them.
+// Host: launch with the PDL attribute (the kernel must call pdl_wait before reading its predecessor's outputs).
 bool vk_pdl_enabled();
 extern long long g_vk_launches;  // kernels launched through vk_launch since the last reset (host counter)
 template <typename... KArgs, typename... Args>

@@ -277,18 +277,28 @@ __global__ void __launch_bounds__(1024) add_rmsnorm_kernel(const __nv_bfloat16* 
                                                            __nv_bfloat16* __restrict__ hn, uint8_t* __restrict__ xrec_hn,
                                                            int D, float eps, float offset, const VkArCall ar) {
     __shared__ float red[kRowMaxWarps];
-    pdl_launch_dependents();
+    pdl_launch_dependents();   // (the dependent, a GEMM, reads only weights in front of its own wait)
     const int k0 = threadIdx.x * 8;
-    float w0[8] = {};
-    if (k0 < D) ld8(w + k0, w0);   // (a weight: fetched while the kernel before this one is still running)
-    pdl_wait();
     const size_t base = (size_t)blockIdx.x * D;
+    // in front of the wait: the weight, and x when r is given (x then comes from an earlier kernel than the one this
+    // launch waits for, which produces r)
+    float w0[8] = {}, x0[8] = {};
+    if (k0 < D) {
+        ld8(w + k0, w0);
+        if (r != nullptr) ld8(x + base + k0, x0);
+    }
+    pdl_wait();
     if (r != nullptr) ar_reduce_row(ar, const_cast<__nv_bfloat16*>(r) + base, blockIdx.x, D);
     float ss = 0.f;
     float v0[8];
     for (int k = k0; k < D; k += blockDim.x * 8) {
         float v[8];
-        ld8(x + base + k, v);
+        if (k == k0 && r != nullptr) {
+#pragma unroll
+            for (int e = 0; e < 8; e++) v[e] = x0[e];
+        } else {
+            ld8(x + base + k, v);
+        }
         if (r != nullptr) {
             float rv[8];
             ld8(r + base + k, rv);
@@ -369,8 +379,8 @@ struct EngramGatherParams {
 
 __global__ void __launch_bounds__(kEwThreads) engram_gather_kernel(const EngramGatherParams p) {
     __shared__ float red[kEwWarps];
-    pdl_launch_dependents();
     pdl_wait();
+    pdl_launch_dependents();
     const int b = blockIdx.x;
     const int cat = p.n_orders * p.dim;
     float ss = 0.f;
@@ -528,7 +538,7 @@ __global__ void __launch_bounds__(kBoundaryThreads) mhc_boundary_kernel(const Bo
     __shared__ float pre_sm[4];
     __shared__ float csum[4];      // this CTA's share of the row-wide sums: gate, ss, ss2 (read by the cluster)
     __shared__ float cdyn[24];     // ... and of the dyn products
-    pdl_launch_dependents();
+    pdl_launch_dependents();   // (the dependent, a GEMM, reads only weights in front of its own wait)
     VK_TS(3, 0);
     const CombineParams& p = q.c;
     namespace cg = cooperative_groups;
@@ -561,23 +571,32 @@ __global__ void __launch_bounds__(kBoundaryThreads) mhc_boundary_kernel(const Bo
         w_next_raw = *reinterpret_cast<const uint4*>(p.w_next + k);
         w_in_raw = *reinterpret_cast<const uint4*>(q.w_in + k);
     }
-    pdl_wait();
-    VK_TS(3, 1);
-    ar_reduce_span(p.ar, const_cast<__nv_bfloat16*>(p.m) + base, b, D, crank, CL);
-    VK_TS(3, 2);
-    float gate = 0.f;
+    // ... and so is everything this layer's earlier kernels and the previous boundary wrote (only m, and the Engram
+    // value, come from the kernels right in front): the residual streams, x_in, h2, res / post
     float hv[8] = {}, mv[8] = {}, xv[8] = {};
-    if (on) { ld8(p.h2 + base + k, hv); ld8(p.m + base + k, mv); ld8(p.x_in + base + k, xv); }
     float r[16], po[4];
 #pragma unroll
     for (int i = 0; i < 16; i++) r[i] = p.res[b * 16 + i];
 #pragma unroll
     for (int s = 0; s < 4; s++) po[s] = p.post[b * 4 + s];
     __nv_bfloat16* Hb = p.H + (size_t)b * 4 * D;
+    uint4 hraw[4] = {};
+    if (on) {
+        ld8(p.h2 + base + k, hv);
+        ld8(p.x_in + base + k, xv);
+#pragma unroll
+        for (int j = 0; j < 4; j++) hraw[j] = *reinterpret_cast<const uint4*>(Hb + (size_t)j * D + k);
+    }
+    pdl_wait();
+    VK_TS(3, 1);
+    ar_reduce_span(p.ar, const_cast<__nv_bfloat16*>(p.m) + base, b, D, crank, CL);
+    VK_TS(3, 2);
+    float gate = 0.f;
+    if (on) ld8(p.m + base + k, mv);
     float hj[4][8] = {};
     if (on) {
 #pragma unroll
-        for (int j = 0; j < 4; j++) ld8(Hb + (size_t)j * D + k, hj[j]);
+        for (int j = 0; j < 4; j++) unpack8(hraw[j], hj[j]);
     }
     if (p.eng_val != nullptr) {
         float a = 0.f;
@@ -684,8 +703,8 @@ __global__ void __launch_bounds__(256) bf16_gemm_rows_kernel(const __nv_bfloat16
                                                             const __nv_bfloat16* __restrict__ W,
                                                             const __nv_bfloat16* __restrict__ bias,
                                                             __nv_bfloat16* __restrict__ y, int ldy, int M, int N, int K) {
-    pdl_launch_dependents();
     pdl_wait();
+    pdl_launch_dependents();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n = blockIdx.x * 8 + warp;
     if (n >= N) return;

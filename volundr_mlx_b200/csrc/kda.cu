@@ -36,7 +36,6 @@ struct KdaParams {
     const float* g_override;       // null, or [B] multipliers: 1 keeps the step, 0 turns it into a no-op (verify replay)
     int ldp, off_z, off_fd, D, Hk, HV, rank;
     float eps;
-    int early_state;               // 1: request the state before the dependency wait (see vk_kda_step)
 };
 
 constexpr int kBdotPieces = 5;   // 16-byte pieces of the in_proj_b row a thread keeps in registers (hidden <= 5120)
@@ -64,7 +63,7 @@ __global__ void __launch_bounds__(128, 5) kda_step_kernel(const KdaParams p) {
     // the state streams through a ring of two 8-row batches per warp: every lane copies (cp.async) and later reads
     // only its own 16 bytes of a row, so the ring needs no barrier
     __shared__ __align__(16) float ring[4][2][8][128];
-    pdl_launch_dependents();
+    pdl_launch_dependents();   // (the dependent, a GEMM, reads only weights in front of its own wait)
     const int hv = blockIdx.x, b = blockIdx.y;
     VK_TS(1, 0);
     const int c = threadIdx.x, lane = c & 31, warp = c >> 5;
@@ -86,23 +85,10 @@ __global__ void __launch_bounds__(128, 5) kda_step_kernel(const KdaParams p) {
         const int k = c * 8 + i * 1024;
         wbv[i] = k < p.D ? *reinterpret_cast<const uint4*>(wb + k) : make_uint4(0u, 0u, 0u, 0u);
     }
+    // Also in front of the wait: everything that kernels before the one in front of this launch wrote (the in_proj
+    // GEMM, whose output alone this step waits for): the state, both conv buffers, the parity word, the layer input h.
     float* Sb = p.S + (((size_t)b * p.HV + hv) * 128) * 128;
-    if (p.early_state) {
-#pragma unroll
-        for (int bt = 0; bt < 2; bt++) {
-#pragma unroll
-            for (int i = 0; i < 8; i++)
-                cp_async16(&ring[warp][bt][i][4 * lane], Sb + (size_t)(warp * 32 + bt * 8 + i) * 128 + 4 * lane);
-            cp_async_commit();
-        }
-    }
-    pdl_wait();
-    VK_TS(1, 1);
-    const __nv_bfloat16* pr = p.proj + (size_t)b * p.ldp;
-    const int par_word = *p.parity;   // (used only after the loads below have been issued: both conv buffers are read)
-
-    // ---- this step's inputs first (they gate the prologue), the state after them: requests are served in order,
-    // and 16 rows of state per warp would otherwise sit in front of every small load
+    const int par_word = *p.parity;
     const __nv_bfloat16* hb = p.h + (size_t)b * p.D;
     uint4 hx[kBdotPieces];
 #pragma unroll
@@ -118,19 +104,21 @@ __global__ void __launch_bounds__(128, 5) kda_step_kernel(const KdaParams p) {
         const __nv_bfloat16* c1 = p.conv + p.conv_stride + cb;
         cx[i][0] = c0[0]; cx[i][1] = c0[C]; cx[i][2] = c0[2 * (size_t)C];
         cy[i][0] = c1[0]; cy[i][1] = c1[C]; cy[i][2] = c1[2 * (size_t)C];
-        cx[i][3] = pr[ch[i]];
     }
+#pragma unroll
+    for (int bt = 0; bt < 2; bt++) {
+#pragma unroll
+        for (int i = 0; i < 8; i++)
+            cp_async16(&ring[warp][bt][i][4 * lane], Sb + (size_t)(warp * 32 + bt * 8 + i) * 128 + 4 * lane);
+        cp_async_commit();
+    }
+    pdl_wait();
+    VK_TS(1, 1);
+    const __nv_bfloat16* pr = p.proj + (size_t)b * p.ldp;
+#pragma unroll
+    for (int i = 0; i < 3; i++) cx[i][3] = pr[ch[i]];
     const float z = bf2f(pr[p.off_z + hv * 128 + c]);
     for (int i = c; i < p.rank; i += 128) fd[i] = bf2f(pr[p.off_fd + i]);
-    if (!p.early_state) {
-#pragma unroll
-        for (int bt = 0; bt < 2; bt++) {
-#pragma unroll
-            for (int i = 0; i < 8; i++)
-                cp_async16(&ring[warp][bt][i][4 * lane], Sb + (size_t)(warp * 32 + bt * 8 + i) * 128 + 4 * lane);
-            cp_async_commit();
-        }
-    }
 
     // ---- beta's dot product
     float bdot = 0.f;
@@ -303,7 +291,7 @@ __global__ void __launch_bounds__(128, 5) kda_step_kernel(const KdaParams p) {
 constexpr int kChunkTok = 8;
 
 struct KdaChunkParams {
-    KdaParams k;          // proj / h / out rows are (b * T + t); g_override, xrec_out, early_state unused
+    KdaParams k;          // proj / h / out rows are (b * T + t); g_override, xrec_out unused
     const int* accept;    // [B] or null
     int T;
 };
@@ -540,7 +528,7 @@ int vk_kda_chunk(const void* proj, int ldp, int off_z, int off_fd, const void* h
     KdaChunkParams cp = {};
     cp.k = {(const __nv_bfloat16*)proj, (const __nv_bfloat16*)h, (const __nv_bfloat16*)w_b, (const __nv_bfloat16*)w_fup,
             conv_w, A_log, dt_bias, (const __nv_bfloat16*)norm_w, (__nv_bfloat16*)conv, parity, conv_stride, S,
-            (__nv_bfloat16*)out, nullptr, nullptr, ldp, off_z, off_fd, D, Hk, HV, rank, eps, 0};
+            (__nv_bfloat16*)out, nullptr, nullptr, ldp, off_z, off_fd, D, Hk, HV, rank, eps};
     cp.accept = accept;
     cp.T = T;
     return (int)vk_launch(kda_chunk_kernel, dim3(HV, B), dim3(128), 0, stream, cp);
@@ -549,14 +537,14 @@ int vk_kda_chunk(const void* proj, int ldp, int off_z, int off_fd, const void* h
 int vk_kda_step(const void* proj, int ldp, int off_z, int off_fd, const void* h, const void* w_b, const void* w_fup,
                 const float* conv_w, const float* A_log, const float* dt_bias, const void* norm_w, void* conv,
                 const int* parity, size_t conv_stride, float* S, void* out, void* xrec_out, const float* g_override, int B,
-                int D, int Hk, int HV, int Dk, int Dv, int rank, float eps, int early_state, cudaStream_t stream) {
+                int D, int Hk, int HV, int Dk, int Dv, int rank, float eps, cudaStream_t stream) {
     if (B <= 0 || Dk != 128 || Dv != 128 || Hk <= 0 || HV % Hk != 0 || rank <= 0 || rank > 256 || rank % 8 != 0 ||
         D % 8 != 0 || parity == nullptr || (xrec_out != nullptr && B > 16))
         return VK_EINVAL;
     KdaParams p = {(const __nv_bfloat16*)proj, (const __nv_bfloat16*)h, (const __nv_bfloat16*)w_b,
                    (const __nv_bfloat16*)w_fup, conv_w, A_log, dt_bias, (const __nv_bfloat16*)norm_w,
                    (__nv_bfloat16*)conv, parity, conv_stride, S, (__nv_bfloat16*)out, (uint8_t*)xrec_out, g_override,
-                   ldp, off_z, off_fd, D, Hk, HV, rank, eps, early_state ? 1 : 0};
+                   ldp, off_z, off_fd, D, Hk, HV, rank, eps};
     return (int)vk_launch(kda_step_kernel, dim3(HV, B), dim3(128), 0, stream, p);
 }
 

@@ -167,8 +167,8 @@ __global__ void __launch_bounds__(kThreads, Fmt<FMT>::kCtasPerSM) w4_gemm_kernel
                              : "memory");
         }
         if (lane == 0) {
-            pdl_launch_dependents();
             pdl_wait();
+            pdl_launch_dependents();
             // (running group index, stage and parity: this one thread feeds the whole CTA, so its loop carries no
             // division and no 64-bit arithmetic)
             int kg = (int)(t0 % p.G);
@@ -208,6 +208,9 @@ __global__ void __launch_bounds__(kThreads, Fmt<FMT>::kCtasPerSM) w4_gemm_kernel
     }
 
     // -------------------------------------------------------------------- consumers
+    // (nothing to do before the kernel in front has finished: wait for it here rather than in the bounded polls on the
+    // first stage, which must not run out while that kernel is, say, legitimately waiting for a peer GPU)
+    pdl_wait();
     const int j = warp - 1;                    // 32-row block inside the superblock
     const int g = lane >> 2, t = lane & 3;
     const int ctid = threadIdx.x - 32;         // 0..255
