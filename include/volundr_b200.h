@@ -29,7 +29,8 @@ const char* vk_status_string(int code);
  * the captured kernels once). */
 long long vk_launch_count(int reset);
 
-/* ---- INT4 affine weight GEMM, 1..16 activation rows per pass (more rows re-stream the weights per 16).
+/* ---- INT4 affine weight GEMM. Up to 16 activation rows: one pass, two CTAs per SM (the decode step). More rows (verify
+ * windows, prefill chunks) through vk_w4_gemm: passes of 64, then 32, then up to 16 rows, each streaming the weights once.
  * Replaces nn.QuantizedLinear.__call__ -> mx.quantized_matmul(x, w, scales, biases, transpose=True, group_size, bits=4)
  * (volundr-mlx/volundr.py:185-190, 377-386, 645-648) and NaxLinear.__call__ -> qmm_nax_prepped
  * (volundr-mlx/spec/nax_hook.py:40-49, agens-mlx-bench/smallm/qmm_nax.py:128-139). */

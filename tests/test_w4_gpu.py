@@ -117,9 +117,24 @@ def test_row_result_independent_of_batch(cuda):
         assert torch.equal(ops.w4_gemm(x[:m].contiguous(), wt), y16[:m])
 
 
-def test_rows_beyond_16(cuda):
-    rng = np.random.default_rng(5)
-    _check_gemm(cuda, rng, 37, 96, 512, 64)
+@pytest.mark.parametrize("M,N,K", [(37, 96, 512), (17, 300, 1024), (32, 520, 2048), (33, 520, 2048), (64, 5120, 1024),
+                                   (128, 840, 1024), (150, 264, 512)])
+def test_rows_beyond_16(cuda, M, N, K):
+    """More than 16 rows (verify windows, prefill chunks): passes of 64 / 32 / up to 16 rows, each streaming the weights
+    once; same bars as the small-M product. Against 16-row passes only the split of K over CTAs differs (one CTA per
+    SM instead of two), i.e. the association of the fp32 partial sums: equal up to a bf16 rounding step."""
+    from volundr_mlx_b200 import ops
+
+    rng = np.random.default_rng(5 + M)
+    y = _check_gemm(cuda, rng, M, N, K, 64)
+    # the same rows, 16 at a time
+    rng = np.random.default_rng(5 + M)
+    w, s, b = make_w4(rng, N, K, 64)
+    x = bf(rng.normal(0, 1, size=(M, K)))
+    wt = ops.w4_repack(*to_dev(w, s, b, cuda), 64)
+    tx = torch.from_numpy(x).to(cuda).to(torch.bfloat16)
+    y16 = torch.cat([ops.w4_gemm(tx[m0:m0 + 16].contiguous(), wt) for m0 in range(0, M, 16)])
+    torch.testing.assert_close(y.float(), y16.float(), rtol=2 ** -7, atol=1e-3)
 
 
 def test_rejects_bad_arguments(cuda):

@@ -61,12 +61,18 @@ template <> struct Fmt<1> {
     static constexpr int kWStage = kBlocksPerSB * kChunk, kStage = kWStage + kXRecBytes + 16;  // + 16 zero bytes
 };
 template <int FMT> constexpr int wstage_bytes() { return Fmt<FMT>::kWStage; }
-template <int FMT> constexpr size_t smem_bytes() { return (size_t)Fmt<FMT>::kStages * Fmt<FMT>::kStage + 2 * Fmt<FMT>::kStages * 8; }
+// x records per group a kernel variant reads: 16 activation rows each (MT = n-tiles of 8 rows: 1, 2, 4 or 8)
+template <int MT> __host__ __device__ constexpr int n_records() { return MT <= 2 ? 1 : MT / 2; }
+template <int FMT, int MT = 2> __host__ __device__ constexpr int stage_bytes() { return Fmt<FMT>::kWStage + n_records<MT>() * kXRecBytes + 16; }
+template <int FMT, int MT = 2> constexpr size_t smem_bytes() {
+    return (size_t)Fmt<FMT>::kStages * stage_bytes<FMT, MT>() + 2 * Fmt<FMT>::kStages * 8;
+}
+template <int FMT, int MT> __host__ __device__ constexpr int ctas_per_sm() { return MT <= 2 ? Fmt<FMT>::kCtasPerSM : 1; }
 constexpr int kChunkBytes = Fmt<0>::kChunk;
 
 struct W4Params {
     const uint8_t* wp;      // packed weights
-    const uint8_t* xrec;    // [G] x records
+    const uint8_t* xrec;    // [G][records per group] x records
     __nv_bfloat16* y;       // [M, ldy]
     float* part;            // [NSB][maxc][256][16] partial sums
     int* counters;          // [NSB] zero between launches
@@ -113,11 +119,13 @@ __device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, 256;
 __device__ __forceinline__ int step_owner(long long t, long long T, int P) { return (int)(((t + 1) * P - 1) / T); }
 
 template <int MT, int FMT>
-__global__ void __launch_bounds__(kThreads, Fmt<FMT>::kCtasPerSM) w4_gemm_kernel(const W4Params p) {
+__global__ void __launch_bounds__(kThreads, ctas_per_sm<FMT, MT>()) w4_gemm_kernel(const W4Params p) {
     extern __shared__ __align__(128) uint8_t smem[];
     constexpr int MR = MT * 8;
+    constexpr int PS = MR < 16 ? 16 : MR;                  // floats per row of a partial-sum slab
+    constexpr int kXR = n_records<MT>() * kXRecBytes;      // bytes of x records per stage
     constexpr int kStages = Fmt<FMT>::kStages;
-    constexpr int kStageBytes = Fmt<FMT>::kStage;
+    constexpr int kStageBytes = stage_bytes<FMT, MT>();
     constexpr int kWStageBytes = Fmt<FMT>::kWStage;
     constexpr int kChunkB = Fmt<FMT>::kChunk;
     uint64_t* full = reinterpret_cast<uint64_t*>(smem + (size_t)kStages * kStageBytes);
@@ -136,7 +144,7 @@ __global__ void __launch_bounds__(kThreads, Fmt<FMT>::kCtasPerSM) w4_gemm_kernel
     const int n = (int)(t1 - t0);
 
     if (threadIdx.x >= 32 && threadIdx.x < 32 + kStages * 4)   // the 16 zero bytes behind every stage's x record
-        *reinterpret_cast<uint32_t*>(smem + (size_t)((threadIdx.x - 32) >> 2) * kStageBytes + kWStageBytes + kXRecBytes +
+        *reinterpret_cast<uint32_t*>(smem + (size_t)((threadIdx.x - 32) >> 2) * kStageBytes + kWStageBytes + kXR +
                                      ((threadIdx.x - 32) & 3) * 4) = 0u;
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; s++) {
@@ -154,7 +162,7 @@ __global__ void __launch_bounds__(kThreads, Fmt<FMT>::kCtasPerSM) w4_gemm_kernel
         if (lane == 0) {
             // the weights depend on no earlier kernel: start streaming before waiting for the producer of x
             for (int i = 0; i < pre; i++) {
-                mbar_expect_tx(&full[i], kWStageBytes + kXRecBytes);
+                mbar_expect_tx(&full[i], kWStageBytes + kXR);
                 tma_bulk_g2s(smem + (size_t)i * kStageBytes, wsrc + (size_t)i * kWStageBytes, kWStageBytes, &full[i]);
             }
         }
@@ -173,7 +181,7 @@ __global__ void __launch_bounds__(kThreads, Fmt<FMT>::kCtasPerSM) w4_gemm_kernel
             // division and no 64-bit arithmetic)
             int kg = (int)(t0 % p.G);
             for (int i = 0; i < pre; i++) {
-                tma_bulk_g2s(smem + (size_t)i * kStageBytes + kWStageBytes, p.xrec + (size_t)kg * kXRecBytes, kXRecBytes, &full[i]);
+                tma_bulk_g2s(smem + (size_t)i * kStageBytes + kWStageBytes, p.xrec + (size_t)kg * kXR, kXR, &full[i]);
                 kg = kg + 1 == p.G ? 0 : kg + 1;
             }
             int st = 0;
@@ -191,9 +199,9 @@ __global__ void __launch_bounds__(kThreads, Fmt<FMT>::kCtasPerSM) w4_gemm_kernel
                 tr_wait += clock64() - tr_a;
 #endif
                 uint8_t* dst = smem + (size_t)st * kStageBytes;
-                mbar_expect_tx(&full[st], kWStageBytes + kXRecBytes);
+                mbar_expect_tx(&full[st], kWStageBytes + kXR);
                 tma_bulk_g2s(dst, wnext, kWStageBytes, &full[st]);
-                tma_bulk_g2s(dst + kWStageBytes, p.xrec + (size_t)kg * kXRecBytes, kXRecBytes, &full[st]);
+                tma_bulk_g2s(dst + kWStageBytes, p.xrec + (size_t)kg * kXR, kXR, &full[st]);
                 wnext += kWStageBytes;
                 kg = kg + 1 == p.G ? 0 : kg + 1;
                 if (++st == kStages) { st = 0; par ^= 1u; }
@@ -224,7 +232,7 @@ __global__ void __launch_bounds__(kThreads, Fmt<FMT>::kCtasPerSM) w4_gemm_kernel
 
     // ldmatrix source of this lane inside an x record: row, and which 16-byte piece of each 32-byte k-step
     const int lm_mat = lane >> 3, lm_r = lane & 7;
-    const int lm_row = (MT == 2 ? (lm_mat >> 1) * 8 : 0) + lm_r;
+    const int lm_row = (MT >= 2 ? (lm_mat >> 1) * 8 : 0) + lm_r;
     const int lm_half = lm_mat & 1;
 
     int sb = (int)(t0 / p.G), kg = (int)(t0 % p.G);
@@ -238,7 +246,7 @@ __global__ void __launch_bounds__(kThreads, Fmt<FMT>::kCtasPerSM) w4_gemm_kernel
         if (!whole && p.S > 0) {
             // ---- aligned mode: the S CTAs of this superblock started together with equal shares of K. Each stores its
             // partial sums, waits (bounded) for the other S - 1, then adds up its own 256 / S rows in slice order.
-            float* dst = p.part + (((size_t)fsb * p.maxc + (blockIdx.x - c_first)) * kSBRows) * 16;
+            float* dst = p.part + (((size_t)fsb * p.maxc + (blockIdx.x - c_first)) * kSBRows) * PS;
 #pragma unroll
             for (int s = 0; s < 2; s++)
 #pragma unroll
@@ -246,7 +254,7 @@ __global__ void __launch_bounds__(kThreads, Fmt<FMT>::kCtasPerSM) w4_gemm_kernel
 #pragma unroll
                     for (int h = 0; h < 2; h++) {
                         const int r = j * 32 + s * 16 + g + h * 8;
-                        __stcg(reinterpret_cast<float2*>(dst + (size_t)r * 16 + jj * 8 + 2 * t),
+                        __stcg(reinterpret_cast<float2*>(dst + (size_t)r * PS + jj * 8 + 2 * t),
                                make_float2(acc[s][jj][2 * h], acc[s][jj][2 * h + 1]));
                     }
             consumer_sync();
@@ -272,13 +280,13 @@ __global__ void __launch_bounds__(kThreads, Fmt<FMT>::kCtasPerSM) w4_gemm_kernel
                 for (int item = ctid; item < (r1 - r0) * V4; item += 256) {
                     const int r = r0 + item / V4, v = item % V4;
                     const int nrow = fsb * kSBRows + r;
-                    const float4* src = reinterpret_cast<const float4*>(p.part + ((size_t)fsb * p.maxc * kSBRows + r) * 16) + v;
+                    const float4* src = reinterpret_cast<const float4*>(p.part + ((size_t)fsb * p.maxc * kSBRows + r) * PS) + v;
                     float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
                     for (int c0 = 0; c0 < nc; c0 += 8) {
                         float4 buf[8];
 #pragma unroll
                         for (int u = 0; u < 8; u++)
-                            buf[u] = (c0 + u < nc) ? __ldcg(src + (size_t)(c0 + u) * kSBRows * 4) : make_float4(0.f, 0.f, 0.f, 0.f);
+                            buf[u] = (c0 + u < nc) ? __ldcg(src + (size_t)(c0 + u) * kSBRows * (PS / 4)) : make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
                         for (int u = 0; u < 8; u++) {
                             if (c0 + u < nc) { sum.x += buf[u].x; sum.y += buf[u].y; sum.z += buf[u].z; sum.w += buf[u].w; }
@@ -298,7 +306,7 @@ __global__ void __launch_bounds__(kThreads, Fmt<FMT>::kCtasPerSM) w4_gemm_kernel
                 if (old == nc - 1) { *arrive = 0; *depart = 0; __threadfence(); }
             }
         } else if (!whole) {
-            float* dst = p.part + (((size_t)fsb * p.maxc + (blockIdx.x - c_first)) * kSBRows) * 16;
+            float* dst = p.part + (((size_t)fsb * p.maxc + (blockIdx.x - c_first)) * kSBRows) * PS;
 #pragma unroll
             for (int s = 0; s < 2; s++)
 #pragma unroll
@@ -306,7 +314,7 @@ __global__ void __launch_bounds__(kThreads, Fmt<FMT>::kCtasPerSM) w4_gemm_kernel
 #pragma unroll
                     for (int h = 0; h < 2; h++) {
                         const int r = j * 32 + s * 16 + g + h * 8;
-                        __stcg(reinterpret_cast<float2*>(dst + (size_t)r * 16 + jj * 8 + 2 * t),
+                        __stcg(reinterpret_cast<float2*>(dst + (size_t)r * PS + jj * 8 + 2 * t),
                                make_float2(acc[s][jj][2 * h], acc[s][jj][2 * h + 1]));
                     }
             consumer_sync();
@@ -328,13 +336,13 @@ __global__ void __launch_bounds__(kThreads, Fmt<FMT>::kCtasPerSM) w4_gemm_kernel
                 for (int item = ctid; item < kSBRows * V4; item += 256) {
                     const int r = item / V4, v = item % V4;
                     const int nrow = fsb * kSBRows + r;
-                    const float4* src = reinterpret_cast<const float4*>(p.part + ((size_t)fsb * p.maxc * kSBRows + r) * 16) + v;
+                    const float4* src = reinterpret_cast<const float4*>(p.part + ((size_t)fsb * p.maxc * kSBRows + r) * PS) + v;
                     float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
                     for (int c0 = 0; c0 < ncontrib; c0 += 8) {             // eight loads in flight, added in range order
                         float4 buf[8];
 #pragma unroll
                         for (int u = 0; u < 8; u++)
-                            buf[u] = (c0 + u < ncontrib) ? __ldcg(src + (size_t)(c0 + u) * kSBRows * 4) : make_float4(0.f, 0.f, 0.f, 0.f);
+                            buf[u] = (c0 + u < ncontrib) ? __ldcg(src + (size_t)(c0 + u) * kSBRows * (PS / 4)) : make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
                         for (int u = 0; u < 8; u++) {
                             if (c0 + u < ncontrib) { sum.x += buf[u].x; sum.y += buf[u].y; sum.z += buf[u].z; sum.w += buf[u].w; }
@@ -379,7 +387,8 @@ __global__ void __launch_bounds__(kThreads, Fmt<FMT>::kCtasPerSM) w4_gemm_kernel
     for (int q = 0; q < 4; q++) lm_off[q] = kWStageBytes + lm_row * 128 + (((2 * q + lm_half) ^ lm_r) << 4);
     uint32_t bw_off[MT];
 #pragma unroll
-    for (int jj = 0; jj < MT; jj++) bw_off[jj] = t < 2 ? kWStageBytes + 2048 + (jj * 8 + g) * 8 + t * 4 : kWStageBytes + kXRecBytes;
+    for (int jj = 0; jj < MT; jj++)
+        bw_off[jj] = t < 2 ? kWStageBytes + (jj >> 1) * kXRecBytes + 2048 + ((jj & 1) * 8 + g) * 8 + t * 4 : kWStageBytes + kXR;
     int st = 0;
     uint32_t phase = 0;
 #if defined(VK_TRACE) && VK_TRACE == 2
@@ -398,6 +407,7 @@ __global__ void __launch_bounds__(kThreads, Fmt<FMT>::kCtasPerSM) w4_gemm_kernel
         const uint8_t* ch = stage + j * kChunkB;
         const uint32_t stage_a = smem_u32(stage);
         if constexpr (FMT == 1) {
+            static_assert(FMT == 0 || MT <= 2, "the bf16 format is built for up to 16 rows per pass");
             // plain bf16 weights: fragments as stored, accumulate straight into acc
 #pragma unroll
             for (int q = 0; q < 4; q++) {
@@ -431,10 +441,12 @@ __global__ void __launch_bounds__(kThreads, Fmt<FMT>::kCtasPerSM) w4_gemm_kernel
         for (int q = 0; q < 4; q++) {
             uint32_t b[2 * MT];
             const uint32_t addr = stage_a + lm_off[q];
-            if constexpr (MT == 2) {
-                asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
-                             : "=r"(b[0]), "=r"(b[1]), "=r"(b[2]), "=r"(b[3])
-                             : "r"(addr));
+            if constexpr (MT >= 2) {
+#pragma unroll
+                for (int rec = 0; rec < n_records<MT>(); rec++)   // 16 activation rows per record
+                    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                                 : "=r"(b[4 * rec]), "=r"(b[4 * rec + 1]), "=r"(b[4 * rec + 2]), "=r"(b[4 * rec + 3])
+                                 : "r"(addr + rec * kXRecBytes));
             } else {
                 asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];" : "=r"(b[0]), "=r"(b[1]) : "r"(addr));
             }
@@ -499,14 +511,16 @@ __global__ void __launch_bounds__(kThreads, Fmt<FMT>::kCtasPerSM) w4_gemm_kernel
 // x [M, ldx] row-major bf16 -> [G] records (see the file comment). One CTA of 128 threads per group: thread (m, c)
 // moves the 16-byte piece c of row m and the eight lanes of a row add up its 64 values (each lane its 8 in order,
 // then an xor tree over the lanes).
+// (grid.y = records per group: record r of a group holds rows 16 r .. 16 r + 15, the records of a group lie together)
 __global__ void __launch_bounds__(128) w4_xrec_kernel(const __nv_bfloat16* __restrict__ x, int ldx, int M, uint8_t* __restrict__ xrec) {
     pdl_launch_dependents();
     pdl_wait();
-    const int kg = blockIdx.x, m = threadIdx.x >> 3, c = threadIdx.x & 7;
+    const int kg = blockIdx.x, rec = blockIdx.y, ml = threadIdx.x >> 3, c = threadIdx.x & 7;
+    const int m = rec * 16 + ml;
     uint4 v = make_uint4(0, 0, 0, 0);
     if (m < M) v = *reinterpret_cast<const uint4*>(x + (size_t)m * ldx + kg * 64 + c * 8);
     float f[8] = {bf_lo(v.x), bf_hi(v.x), bf_lo(v.y), bf_hi(v.y), bf_lo(v.z), bf_hi(v.z), bf_lo(v.w), bf_hi(v.w)};
-    xrec_store_row_piece(xrec, m, kg * 8 + c, f);
+    xrec_store_row_piece(xrec + ((size_t)kg * gridDim.y + rec) * kXRecBytes, ml, c, f);
 }
 
 // ------------------------------------------------------------------------------------------------ repack / dequant
@@ -645,8 +659,36 @@ W4Plan w4_plan(int N, int K, int ctas_per_sm = Fmt<0>::kCtasPerSM) {
     return pl;
 }
 
-size_t w4_ws_bytes(const W4Plan& pl) {
-    return kCounterBytes + (size_t)pl.G * kXRecBytes + (size_t)pl.NSB * pl.maxc * kSBRows * 16 * 4;
+// counters | x records [G][nrec] | partial sums [NSB][maxc][256][ps] fp32
+size_t w4_ws_bytes(const W4Plan& pl, int nrec = 1, int ps = 16) {
+    return kCounterBytes + (size_t)pl.G * nrec * kXRecBytes + (size_t)pl.NSB * pl.maxc * kSBRows * ps * 4;
+}
+
+template <int MT>
+static cudaError_t w4_launch_pass(const void* packed, const __nv_bfloat16* x, int ldx, __nv_bfloat16* y, int ldy, int m, int N,
+                                  int K, uint8_t* ws, cudaStream_t stream) {
+    constexpr int NR = n_records<MT>(), PS = MT * 8 < 16 ? 16 : MT * 8;
+    const W4Plan pl = w4_plan(N, K, ctas_per_sm<0, MT>());
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(w4_gemm_kernel<MT, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes<0, MT>());
+        if (e != cudaSuccess) return e;
+        e = cudaFuncSetAttribute(w4_gemm_kernel<MT, 0>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+        if (e != cudaSuccess) return e;
+        configured = true;
+    }
+    W4Params p;
+    p.wp = (const uint8_t*)packed;
+    p.xrec = ws + kCounterBytes;
+    p.y = y;
+    p.counters = (int*)ws;
+    p.part = (float*)(ws + kCounterBytes + (size_t)pl.G * NR * kXRecBytes);
+    p.T = pl.T; p.M = m; p.N = N; p.NSB = pl.NSB; p.G = pl.G; p.P = pl.P; p.ldy = ldy; p.maxc = pl.maxc; p.S = pl.S;
+    p.pf = w4_prefetch_steps(pl.P, (size_t)wstage_bytes<0>(), Fmt<0>::kStages);
+    (void)PS;
+    cudaError_t e = vk_launch(w4_xrec_kernel, dim3(pl.G, NR), dim3(128), 0, stream, x, ldx, m, ws + kCounterBytes);
+    if (e != cudaSuccess) return e;
+    return vk_launch(w4_gemm_kernel<MT, 0>, dim3(pl.P), dim3(kThreads), smem_bytes<0, MT>(), stream, p);
 }
 
 }  // namespace
@@ -680,9 +722,13 @@ void vk_w4_force_plan(int ctas, int prefetch_mb) {
 }
 
 size_t vk_w4_workspace_bytes(int M, int N, int K) {
-    (void)M;
     if (N <= 0 || K <= 0 || K % 64 != 0) return 0;
-    return w4_ws_bytes(w4_plan(N, K));
+    size_t need = w4_ws_bytes(w4_plan(N, K));
+    if (M > 16) {   // passes of 32 / 64 rows: one CTA per SM, wider records and partial sums
+        const size_t wide = w4_ws_bytes(w4_plan(N, K, 1), M > 32 ? 4 : 2, M > 32 ? 64 : 32);
+        need = wide > need ? wide : need;
+    }
+    return need;
 }
 
 // y = x . dequant(W)^T for activations already laid out as x records (K / 64 records of 2176 bytes, rows >= M zero):
@@ -716,38 +762,29 @@ int vk_w4_gemm_xrec(const void* packed, const void* xrec, void* y, int ldy, int 
     return (int)e;
 }
 
+// Row-major x. Up to 16 rows: one pass (two CTAs per SM). More rows (verify windows, prefill chunks): passes of 64,
+// then 32, then up to 16 rows, each streaming the weights once; the wide passes keep 8 / 4 row tiles per warp and run
+// one CTA per SM.
 int vk_w4_gemm(const void* packed, const void* x, int ldx, void* y, int ldy, int M, int N, int K, void* workspace,
                size_t workspace_bytes, cudaStream_t stream) {
     if (M <= 0 || N <= 0 || K <= 0 || K % 64 != 0 || ldx % 8 != 0 || ldx < K || ldy < N) return VK_EINVAL;
     if (((uintptr_t)x & 15) || ((uintptr_t)packed & 15) || workspace == nullptr || ((uintptr_t)workspace & 15)) return VK_EINVAL;
     const W4Plan pl = w4_plan(N, K);
     if (pl.NSB > (int)(kCounterBytes / 4)) return VK_EINVAL;
-    if (workspace_bytes < w4_ws_bytes(pl)) return VK_ENOSPC;
-    static bool configured = false;
-    if (!configured) {
-        VK_CUDA(cudaFuncSetAttribute(w4_gemm_kernel<1, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes<0>()));
-        VK_CUDA(cudaFuncSetAttribute(w4_gemm_kernel<1, 0>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
-        VK_CUDA(cudaFuncSetAttribute(w4_gemm_kernel<2, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes<0>()));
-        VK_CUDA(cudaFuncSetAttribute(w4_gemm_kernel<2, 0>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
-        configured = true;
-    }
+    if (workspace_bytes < vk_w4_workspace_bytes(M, N, K)) return VK_ENOSPC;
     uint8_t* ws = (uint8_t*)workspace;
-    // rows beyond 16 re-stream the weights once per 16 rows
-    for (int m0 = 0; m0 < M; m0 += 16) {
-        const int m = M - m0 < 16 ? M - m0 : 16;
-        W4Params p;
-        p.wp = (const uint8_t*)packed;
-        p.xrec = ws + kCounterBytes;
-        p.y = (__nv_bfloat16*)y + (size_t)m0 * ldy;
-        p.counters = (int*)ws;
-        p.part = (float*)(ws + kCounterBytes + (size_t)pl.G * kXRecBytes);
-        p.T = pl.T; p.M = m; p.N = N; p.NSB = pl.NSB; p.G = pl.G; p.P = pl.P; p.ldy = ldy; p.maxc = pl.maxc; p.S = pl.S;
-        p.pf = w4_prefetch_steps(pl.P, (size_t)wstage_bytes<0>(), Fmt<0>::kStages);
-        VK_CUDA(vk_launch(w4_xrec_kernel, dim3(pl.G), dim3(128), 0, stream, (const __nv_bfloat16*)x + (size_t)m0 * ldx, ldx, m,
-                          ws + kCounterBytes));
-        cudaError_t e = m <= 8 ? vk_launch(w4_gemm_kernel<1, 0>, dim3(pl.P), dim3(kThreads), smem_bytes<0>(), stream, p)
-                               : vk_launch(w4_gemm_kernel<2, 0>, dim3(pl.P), dim3(kThreads), smem_bytes<0>(), stream, p);
+    for (int m0 = 0; m0 < M;) {
+        const int left = M - m0;
+        const __nv_bfloat16* xp = (const __nv_bfloat16*)x + (size_t)m0 * ldx;
+        __nv_bfloat16* yp = (__nv_bfloat16*)y + (size_t)m0 * ldy;
+        cudaError_t e;
+        int m;
+        if (left > 32) { m = left < 64 ? left : 64; e = w4_launch_pass<8>(packed, xp, ldx, yp, ldy, m, N, K, ws, stream); }
+        else if (left > 16) { m = left; e = w4_launch_pass<4>(packed, xp, ldx, yp, ldy, m, N, K, ws, stream); }
+        else if (left > 8) { m = left; e = w4_launch_pass<2>(packed, xp, ldx, yp, ldy, m, N, K, ws, stream); }
+        else { m = left; e = w4_launch_pass<1>(packed, xp, ldx, yp, ldy, m, N, K, ws, stream); }
         if (e != cudaSuccess) return (int)e;
+        m0 += m;
     }
     return VK_OK;
 }

@@ -67,7 +67,7 @@ def w4_gemm(x, wt: W4Weight, out=None):
     M = x.shape[0]
     if out is None:
         out = torch.empty((M, wt.N), dtype=BF16, device=x.device)
-    need = L.vk_w4_workspace_bytes(min(M, 16), wt.N, wt.K)
+    need = L.vk_w4_workspace_bytes(M, wt.N, wt.K)
     ws = workspace(need, x.device)
     _lib.check(L.vk_w4_gemm(_p(wt.packed), _p(x), x.stride(0), _p(out), out.stride(0), M, wt.N, wt.K, _p(ws),
                             ws.numel(), _stream()), "vk_w4_gemm")
