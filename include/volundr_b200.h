@@ -66,6 +66,13 @@ int vk_bf16_repack(const void* W, int N, int K, void* packed, vk_stream_t stream
 size_t vk_bf16_workspace_bytes(int M, int N, int K);
 int vk_bf16_gemm_packed(const void* packed, const void* x, int ldx, void* y, int ldy, int M, int N, int K, void* workspace,
                         size_t workspace_bytes, vk_stream_t stream);
+/* The same product for many activation rows (verify windows of B x T rows, prefill chunks) on the tcgen05 tensor cores
+ * with the accumulator in tensor memory: tiles of 128 activation rows x one 256-row superblock of the weight. The weight
+ * tile is dequantised to bf16 once, bf16(s * u + b) with a single rounding (the value vk_w4_dequant gives), so results
+ * differ from vk_w4_gemm by that rounding of the weights (within the bf16 bar). `packed` as for vk_w4_gemm. */
+size_t vk_w4_tile_workspace_bytes(int M, int K);
+int vk_w4_gemm_tile(const void* packed, const void* x, int ldx, void* y, int ldy, int M, int N, int K, void* workspace,
+                    size_t workspace_bytes, vk_stream_t stream);
 /* Tuning / testing aid: force the number of persistent CTAs the work is dealt to (0 = two per SM), and the budget in
  * MB of the L2 prefetch a GEMM issues for its own weights before it waits for the kernel that produces x
  * (0 or negative = none, the default: on B200 the prefetch measured slower than none). Results do not depend on either. */
@@ -175,8 +182,10 @@ int vk_kda_step(const void* proj, int ldp, int off_z, int off_fd, const void* h,
  * the parity word once per launch. */
 int vk_kda_chunk(const void* proj, int ldp, int off_z, int off_fd, const void* h, const void* w_b, const void* w_fup,
                  const float* conv_w, const float* A_log, const float* dt_bias, const void* norm_w, void* conv,
-                 const int* parity, size_t conv_stride, float* S, void* out, const int* accept, int B, int T, int D, int Hk,
-                 int HV, int Dk, int Dv, int rank, float eps, vk_stream_t stream);
+                 const int* parity, size_t conv_stride, float* S, void* out, const int* accept, int write_state, int B, int T,
+                 int D, int Hk, int HV, int Dk, int Dv, int rank, float eps, vk_stream_t stream);
+/* (write_state = 0: outputs only; the state and the conv buffers are not touched and the parity word is not to be
+ * flipped: the verify pass in front of a commit.) */
 /* h, the state S, both conv buffers and the parity word are read before the kernel waits for the launch in front of
  * it (they stream in while that launch finishes): none of them may be written by that launch. proj may. */
 
@@ -202,6 +211,14 @@ int vk_attn_prep(const vk_attn_geom* g, const void* proj, int ldp, int off_k, in
                  const void* q_norm, const void* k_norm, const void* idx_norm, const int* pos, const int* table, void* q,
                  void* qi, void* K, void* V, void* PK, void* PV, void* BK, void* IK, int B, int rope_dims, double rope_theta,
                  float eps, vk_stream_t stream);
+/* vk_attn_prep for rows that are consecutive positions of one sequence (a verify window, a prefill chunk): a block may
+ * then be closed by a position whose neighbours other rows of the same launch write, so all rows are written first
+ * (mode 1) and pooled by a second launch (mode 2); mode 0 = vk_attn_prep. row_map (optional, [B]): the cache row whose
+ * open-block indexer keys (IK) a row shares. */
+int vk_attn_prep_rows(const vk_attn_geom* g, const void* proj, int ldp, int off_k, int off_v, const void* idxq, const void* idxk,
+                      const void* q_norm, const void* k_norm, const void* idx_norm, const int* pos, const int* table, void* q,
+                      void* qi, void* K, void* V, void* PK, void* PV, void* BK, void* IK, int B, int rope_dims,
+                      double rope_theta, float eps, int mode, const int* row_map, vk_stream_t stream);
 /* _block_scores + _topk_blocks (volundr.py:601-618; kernels.bcsa_scores kernels.py:1227-1240, bcsa_topk :86-98):
  * sel [B, NS, topk] ascending block indices (-1 padded), nsel [B, NS]. scratch: max_blocks uint32 per (row, group). */
 int vk_attn_configure(void);   /* once per device, outside stream capture: shared-memory opt-in of the selection kernel

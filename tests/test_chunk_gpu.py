@@ -1,0 +1,119 @@
+"""T tokens per row in one pass over the weights (volundr_mlx_b200.chunk: the verify tile and the prefill chunk) against
+token-by-token decoding of the same model: logits of every position, the state a commit leaves behind (checked through
+the logits of the steps that follow) and the page accounting. Linears run with other row counts here than in the decode
+step (other split of K over CTAs), so the comparison is at the bf16 floor, not bit for bit."""
+import numpy as np
+import pytest
+import torch
+
+from volundr_mlx_b200 import synth
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def cuda():
+    if not torch.cuda.is_available():
+        pytest.skip("needs a GPU")
+    return torch.device("cuda", 0)
+
+
+def _rel(a, b):
+    return float((a.float() - b.float()).abs().max() / b.float().abs().max())
+
+
+@pytest.mark.parametrize("mode", ["reference", "paged_tokens"])
+def test_verify_chunk_and_commit(cuda, mode):
+    from volundr_mlx_b200 import batch as BT, chunk as CH, ops
+    from volundr_mlx_b200.volundr import Model
+
+    kw = {} if mode == "reference" else dict(bcsa_far="tokens", bcsa_score="pooled_key", bcsa_window=128,
+                                             bcsa_compress=64, bcsa_topk=2)
+    args = synth.small_args(**kw)
+    params = synth.make_params(args, seed=31)
+    model = Model(args, params, cuda)
+    rng = np.random.default_rng(31)
+    B, T, warm, cont = 3, 8, 60, 5           # the window covers positions 60..67: a page opens at 64
+    warm_toks = rng.integers(0, args.vocab_valid, size=(warm, B))
+    drafts = rng.integers(0, args.vocab_valid, size=(B, T))
+    cont_toks = rng.integers(0, args.vocab_valid, size=(cont, B))
+    accepted = [2, 8, 5]
+
+    def fresh():
+        bc = model.make_cache(max_rows=4, n_pages=16, max_pages_per_row=4)
+        bc.apply(join=["a", "b", "c"])
+        for t in range(warm):
+            BT.forward(model, bc, warm_toks[t].tolist())
+        return bc
+
+    # sequential decoding of all T drafts: the logits the verify pass must reproduce
+    seq = fresh()
+    want = []
+    for t in range(T):
+        lg, _ = BT.forward(model, seq, drafts[:, t].tolist())
+        want.append(lg.clone())
+    want = torch.stack(want, dim=1)          # [B, T, V]
+
+    bc = fresh()
+    free_before = int(bc.free_top.item())
+    logits, greedy, h = CH.forward_chunk(model, bc, drafts.tolist())
+    ops.check_status()
+    assert logits.shape == want.shape
+    assert _rel(logits, want) < 3e-2
+    assert torch.equal(greedy.long(), logits.float()[:, :, : args.vocab_valid].argmax(dim=2))
+    CH.commit_chunk(model, bc, h, accepted)
+    assert bc.host_pos() == [warm + n for n in accepted]
+    assert int(bc.free_top.item()) == free_before - sum(1 for n in accepted if warm + n > 64)
+
+    # every row must now continue like a request that decoded only its accepted drafts
+    after = []
+    for t in range(cont):
+        lg, _ = BT.forward(model, bc, cont_toks[t].tolist())
+        after.append(lg.clone())
+    ops.check_status()
+    for b in range(B):
+        one = model.make_cache(max_rows=1, n_pages=8, max_pages_per_row=4)
+        one.apply(join=["x"])
+        for t in range(warm):
+            BT.forward(model, one, [int(warm_toks[t, b])])
+        for t in range(accepted[b]):
+            BT.forward(model, one, [int(drafts[b, t])])
+        for t in range(cont):
+            lg, _ = BT.forward(model, one, [int(cont_toks[t, b])])
+            assert _rel(after[t][b], lg[0]) < 3e-2, (b, t)
+    ops.check_status()
+
+
+def test_prefill_chunks_then_decode(cuda):
+    from volundr_mlx_b200 import batch as BT, chunk as CH, ops
+    from volundr_mlx_b200.volundr import Model
+
+    args = synth.small_args(bcsa_far="tokens", bcsa_score="pooled_key", bcsa_window=128, bcsa_compress=64, bcsa_topk=2)
+    params = synth.make_params(args, seed=32)
+    model = Model(args, params, cuda)
+    rng = np.random.default_rng(32)
+    prompt = rng.integers(0, args.vocab_valid, size=200).tolist()
+    tail = rng.integers(0, args.vocab_valid, size=6).tolist()
+
+    seq = model.make_cache(max_rows=1, n_pages=8, max_pages_per_row=6)
+    seq.apply(join=["x"])
+    want = []
+    for t in prompt:
+        lg, _ = BT.forward(model, seq, [t])
+        want.append(lg[0].clone())
+
+    bc = model.make_cache(max_rows=1, n_pages=8, max_pages_per_row=6)
+    bc.apply(join=["x"])
+    got = []
+    for c0 in range(0, len(prompt), 48):     # chunks of 48 tokens (the last one shorter)
+        lg, _, _ = CH.forward_chunk(model, bc, [prompt[c0:c0 + 48]], write=True)
+        got.append(lg[0].clone())
+    got = torch.cat(got)
+    ops.check_status()
+    assert bc.host_pos() == [len(prompt)]
+    assert _rel(got, torch.stack(want)) < 3e-2
+    for t in tail:
+        a, _ = BT.forward(model, bc, [t])
+        b, _ = BT.forward(model, seq, [t])
+        assert _rel(a, b) < 3e-2
+    ops.check_status()

@@ -165,7 +165,7 @@ def test_kda_chunk_equals_steps(cuda, Hk, T):
         acc = torch.tensor(accept, dtype=torch.int32, device=cuda) if accept is not None else None
         _lib.check(L.vk_kda_chunk(p(proj), ldp, C, C + HV * V, p(h), p(w_b), p(fup), p(conv_w), p(A_log), p(dt_bias),
                                   p(norm_w), p(conv), p(par), conv[0].numel(), p(S), p(outs), p(acc) if acc is not None else None,
-                                  B, T, D, Hk, HV, K, V, rank, 1e-6, st), "vk_kda_chunk")
+                                  1, B, T, D, Hk, HV, K, V, rank, 1e-6, st), "vk_kda_chunk")
         return S, outs, conv[1]
 
     for accept in (None, [0, 1, T // 2, T - 1, T]):

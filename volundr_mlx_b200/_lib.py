@@ -19,6 +19,8 @@ SIGNATURES = {
     "vk_w4_packed_bytes": (c_size_t, [c_int, c_int]),
     "vk_w4_repack": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p]),
     "vk_w4_dequant": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p]),
+    "vk_w4_tile_workspace_bytes": (c_size_t, [c_int, c_int]),
+    "vk_w4_gemm_tile": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_size_t, c_void_p]),
     "vk_w4_force_plan": (None, [c_int, c_int]),
     "vk_w4_workspace_bytes": (c_size_t, [c_int, c_int, c_int]),
     "vk_w4_gemm": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_size_t, c_void_p]),
@@ -53,7 +55,7 @@ SIGNATURES = {
     "vk_kda_configure": (c_int, []),
     "vk_attn_configure": (c_int, []),
     "vk_kda_chunk": (c_int, [c_void_p, c_int, c_int, c_int] + [c_void_p] * 9 + [c_size_t, c_void_p, c_void_p, c_void_p]
-                     + [c_int] * 8 + [c_float, c_void_p]),
+                     + [c_int] * 9 + [c_float, c_void_p]),
     "vk_kda_step": (c_int, [c_void_p, c_int, c_int, c_int] + [c_void_p] * 9 + [c_size_t, c_void_p, c_void_p, c_void_p, c_void_p]
                     + [c_int] * 7 + [c_float, c_void_p]),
     "vk_batch_step_begin": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
@@ -61,6 +63,8 @@ SIGNATURES = {
     "vk_batch_step_end": (c_int, [c_void_p, c_void_p, c_int, c_void_p]),
     "vk_attn_prep": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int] + [c_void_p] * 15 + [c_int, c_int, c_double, c_float,
                                                                                           c_void_p]),
+    "vk_attn_prep_rows": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int] + [c_void_p] * 15 + [c_int, c_int, c_double, c_float,
+                                                                                               c_int, c_void_p, c_void_p]),
     "vk_bcsa_select_scratch_bytes": (c_size_t, [c_void_p, c_int, c_int]),
     "vk_bcsa_select": (c_int, [c_void_p] * 6 + [c_int, c_void_p, c_void_p, c_int, c_void_p]),
     "vk_bcsa_select_static": (c_int, [c_void_p] * 7 + [c_int, c_void_p]),

@@ -1,0 +1,264 @@
+"""T tokens per row through every layer in one pass over the weights: the tile the reference reaches through
+batch_spec.verify_forward (batch_spec.py:107-158: B x T verify) and, with one row, through the prefill chunks of
+session.prefill_iter (session.py:351-387) / verify.forward_iter (spec/verify.py:180-226).
+
+The B x T tokens run as R = B * T "virtual rows": row b * T + t is token t of request b, at position pos[b] + t, on the
+page table of request b. Linears see all R rows at once (vk_w4_gemm: wide passes; vk_bf16_gemm_packed), the row-wise
+kernels (mHC, norms, SiLU, Engram) are the decode step's kernels on R rows, attention is the decode attention with R
+query rows (each sees the keys up to its own position: all rows' K/V are written before anything is attended, blocks
+that close inside the window are pooled in a second pass), the KDA recurrence is vk_kda_chunk. Nothing here waits for
+a per-token step of another layer.
+
+forward_chunk(..., write=False) is the verify pass: K/V of all T tokens go into the pages (positions a commit does not
+keep are simply never reached), the KDA state and the Engram window stay as they were, and what a commit needs
+(the KDA layers' inputs) is kept. commit_chunk(accepted) replays the KDA recurrence over the accepted prefix of every
+row (vk_kda_chunk with `accept`), moves the Engram window, returns pages opened for rejected positions and advances
+the positions. forward_chunk(..., write=True) commits all T tokens at once (a prefill chunk).
+Tensor-parallel sharding is not wired into this path yet.
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from . import _lib, ops
+from . import batch as BT
+
+BF16 = torch.bfloat16
+PAGE = BT.PAGE
+_p = BT._p
+
+
+class ChunkScratch:
+    """Activations of R virtual rows (one allocation per (model, R))."""
+
+    def __init__(self, model, bc, R):
+        a, d, D = model.args, model.device, model.args.hidden_size
+        bf = dict(dtype=BF16, device=d)
+        f32 = dict(dtype=torch.float32, device=d)
+        i32 = dict(dtype=torch.int32, device=d)
+        self.R = R
+        wid = max(w["proj"].N for w in model.layers)
+        self.H = torch.zeros((R, 4, D), **bf)
+        self.hn, self.x_in, self.h = (torch.zeros((R, D), **bf) for _ in range(3))
+        self.post, self.res, self.dyn = torch.zeros((R, 4), **f32), torch.zeros((R, 16), **f32), torch.zeros((R, 24), **f32)
+        self.proj = torch.zeros((R, wid), **bf)
+        self.mix = torch.zeros((R, max(model.HV * 128, model.Hq * 128)), **bf)
+        self.r, self.h2, self.hn2, self.mlp = (torch.zeros((R, D), **bf) for _ in range(4))
+        self.gu = torch.zeros((R, 2 * model.I), **bf)
+        self.act = torch.zeros((R, model.I), **bf)
+        self.logits = torch.zeros((R, model.vocab_shard), **bf)
+        self.greedy = torch.zeros(R, **i32)
+        self.tok = torch.zeros(R, **i32)
+        self.pos = torch.zeros(R, **i32)
+        self.table = torch.full((R, bc.max_pages), -1, **i32)
+        self.row_map = torch.zeros(R, **i32)
+        self.engram_prev = torch.full((R, max(bc.keep, 1)), -1, **i32)
+        self.engram_rows = torch.zeros((R, max(len(a.engram_orders), 1)), **i32)
+        self.q = torch.zeros((R, model.Hq, 128), **bf)
+        if bc.indexer:
+            self.qi = torch.zeros((R, a.bcsa_index_heads, a.bcsa_index_dim), **bf)
+            self.idxq = torch.zeros((R, a.bcsa_index_heads * a.bcsa_index_dim), **bf)
+            self.idxk = torch.zeros((R, a.bcsa_index_dim), **bf)
+        self.sel = torch.full((R, max(bc.NS, 1), max(a.bcsa_topk, 1)), -1, **i32)
+        self.nsel = torch.zeros((R, max(bc.NS, 1)), **i32)
+        self.sel_scratch = torch.zeros((R, max(bc.NS, 1), bc.max_blocks), **i32)
+        self.part = torch.zeros((R, model.Hq, max(bc.nsplit_bcsa, bc.nsplit_dense), 130), **f32)
+        if a.engram_layers:
+            self.eng_e = torch.zeros((R, a.engram_dim * len(a.engram_orders)), **bf)
+            self.eng_val = torch.zeros((R, D), **bf)
+
+
+class ChunkHandle:
+    def __init__(self, T, pos0, window, kda_inputs):
+        self.T, self.pos0, self.window, self.kda_inputs = T, pos0, window, kda_inputs
+
+
+_scratch = {}
+
+
+def _get_scratch(model, bc, R):
+    key = (id(model), id(bc), R)
+    if key not in _scratch:
+        _scratch[key] = ChunkScratch(model, bc, R)
+    return _scratch[key]
+
+
+def _open_pages(bc, T):
+    """Pages for the positions pos .. pos + T - 1 of every row (host side: at most a few per row)."""
+    need = []
+    for b, p0 in enumerate(bc._pos):
+        assert (p0 + T + PAGE - 1) // PAGE <= bc.max_pages, "row would outgrow its page table"
+        for p in range(p0, p0 + T):
+            if p % PAGE == 0:
+                need.append((b, p // PAGE))
+    if need:
+        top = int(bc.free_top.item())
+        assert top >= len(need), "page pool exhausted"
+        for n, (b, pi) in enumerate(need):
+            bc.table[b, pi] = bc.free_list[top - 1 - n]
+        bc.free_top -= len(need)
+
+
+def forward_chunk(model, bc, toks, write=False):
+    """toks [B][T] (the same T for every row of the batch). Returns (logits [B, T, V] bf16, greedy [B, T] int32,
+    handle). write=False: a verify pass, to be followed by commit_chunk(model, bc, handle, accepted); write=True: all T
+    tokens are committed (handle is None)."""
+    assert model.tp_size == 1, "the chunk path is not sharded yet"
+    L = _lib.lib()
+    a, D = model.args, model.args.hidden_size
+    dev = bc.pos.device
+    t_in = torch.as_tensor(toks, dtype=torch.int32)
+    assert t_in.dim() == 2 and t_in.shape[0] == bc.B and t_in.shape[1] >= 1
+    B, T = t_in.shape
+    R = B * T
+    t_in = t_in.to(dev)
+    s = _get_scratch(model, bc, R)
+    BT.model_warm(model)
+    _open_pages(bc, T)
+    st = torch.cuda.current_stream().cuda_stream
+    eps = a.rms_norm_eps
+    ck = _lib.check
+    # ---- virtual rows
+    rows = torch.arange(B, device=dev).repeat_interleave(T)
+    s.row_map.copy_(rows.to(torch.int32))
+    s.tok.copy_(t_in.reshape(-1))
+    s.pos.copy_((bc.pos[:B].unsqueeze(1) + torch.arange(T, device=dev, dtype=torch.int32).unsqueeze(0)).reshape(-1))
+    s.table.copy_(bc.table[:B][rows])
+    window = None
+    if a.engram_layers and bc.keep > 0:
+        window = torch.cat([bc.engram_prev[:B, : bc.keep], t_in], dim=1)          # [B, keep + T]
+        s.engram_prev.copy_(window.unfold(1, bc.keep, 1)[:, :T].reshape(R, bc.keep))
+    ws = ops.workspace(max(1 << 26, L.vk_w4_workspace_bytes(R, max(w["gate_up"].N for w in model.layers), D)), dev)
+
+    def gemm(x, wt, y):
+        ck(L.vk_w4_gemm(_p(wt.packed), _p(x), x.stride(0), _p(y), y.stride(0), R, wt.N, wt.K, _p(ws), ws.numel(), st),
+           "vk_w4_gemm")
+
+    w0 = model.layers[0]
+    ck(L.vk_embed(_p(s.tok), _p(model.embed), _p(w0["mhc_norm"]), _p(s.H), _p(s.hn),
+                  _p(s.engram_prev) if a.engram_layers else None, _p(s.engram_rows), bc.orders,
+                  len(a.engram_orders) if a.engram_layers else 0, a.engram_rows, R, D, eps, st), "vk_embed")
+    kda_inputs = []
+    acc_all = torch.full((B,), T, dtype=torch.int32, device=dev)
+    nl = len(model.layers)
+    for i, (w, lst) in enumerate(zip(model.layers, bc.layers)):
+        ck(L.vk_mhc_mix_norm(_p(s.H), _p(s.hn), _p(w["dyn"]), _p(w["pre_s"]), _p(w["post_s"]), _p(w["res_s"]), _p(w["ln_in"]),
+                             _p(s.x_in), _p(s.h), None, _p(s.post), _p(s.res), _p(s.dyn), R, D, a.mhc_sinkhorn_iters, eps, st),
+           "vk_mhc_mix_norm")
+        gemm(s.h, w["proj"], s.proj)
+        if w["mixer"] == "kda":
+            nmix = model.HV * 128
+            if not write:
+                kda_inputs.append((i, s.proj[:, : w["proj"].N].clone(), s.h.clone()))
+            ck(L.vk_kda_chunk(_p(s.proj), s.proj.stride(0), w["off_z"], w["off_fd"], _p(s.h), _p(w["in_proj_b"]), _p(w["f_up"]),
+                              _p(w["conv_w"]), _p(w["A_log"]), _p(w["dt_bias"]), _p(w["gnorm"]), _p(lst["conv"]),
+                              _p(bc.parity), lst["conv"][0].numel(), _p(lst["S"]), _p(s.mix), _p(acc_all), 1 if write else 0,
+                              B, T, D, model.Hk, model.HV, 128, 128, a.kda_gate_rank, eps, st), "vk_kda_chunk")
+        else:
+            bcsa = w["mixer"] == "bcsa"
+            g = bc.geom[w["mixer"]]
+            nmix = model.Hq * 128
+            idx = bcsa and bc.indexer
+            if idx:
+                ck(L.vk_bf16_gemm(_p(s.h), D, _p(w["idx_q"]), None, _p(s.idxq), s.idxq.stride(0), R, w["idx_q"].shape[0], D, st),
+                   "vk_bf16_gemm")
+                ck(L.vk_bf16_gemm(_p(s.h), D, _p(w["idx_k"]), None, _p(s.idxk), s.idxk.stride(0), R, w["idx_k"].shape[0], D, st),
+                   "vk_bf16_gemm")
+            for mode in (1, 2):   # write every row's K / V first, pool the blocks that close afterwards
+                ck(L.vk_attn_prep_rows(ctypes.byref(g), _p(s.proj), s.proj.stride(0), w["off_k"], w["off_v"],
+                                       _p(s.idxq) if idx else None, _p(s.idxk) if idx else None, _p(w["q_norm"]),
+                                       _p(w["k_norm"]), _p(w["idx_norm"]) if idx else None, _p(s.pos), _p(s.table), _p(s.q),
+                                       _p(s.qi) if idx else None, _p(lst["K"]), _p(lst["V"]), _p(lst.get("PK")),
+                                       _p(lst.get("PV")), _p(lst.get("BK")), _p(lst.get("IK")), R, model.rope_dims,
+                                       float(a.rope_theta), eps, mode, _p(s.row_map), st), "vk_attn_prep_rows")
+                if not bcsa:
+                    break   # (a dense layer pools nothing)
+            if bcsa:
+                ck(L.vk_bcsa_select(ctypes.byref(g), _p(s.qi) if idx else _p(s.q), _p(lst["BK"]) if idx else _p(lst["PK"]),
+                                    _p(s.pos), _p(s.table), _p(s.sel_scratch), bc.max_blocks, _p(s.sel), _p(s.nsel), R, st),
+                   "vk_bcsa_select")
+            ck(L.vk_attend_decode(ctypes.byref(g), _p(s.q), _p(lst["K"]), _p(lst["V"]), _p(lst.get("PK")), _p(lst.get("PV")),
+                                  _p(s.pos), _p(s.table), _p(s.sel), _p(s.nsel), _p(s.proj), s.proj.stride(0), _p(s.part),
+                                  bc.nsplit_bcsa if bcsa else bc.nsplit_dense, _p(s.mix), None, R, st), "vk_attend_decode")
+        gemm(s.mix[:, :nmix], w["out"], s.r)
+        ck(L.vk_add_rmsnorm(_p(s.x_in), _p(s.r), _p(w["ln_post"]), _p(s.h2), _p(s.hn2), None, R, D, eps, 1, st), "vk_add_rmsnorm")
+        gemm(s.hn2, w["gate_up"], s.gu)
+        ck(L.vk_silu_mul(_p(s.gu), _p(s.act), None, R, model.I, s.gu.stride(0), st), "vk_silu_mul")
+        gemm(s.act, w["down"], s.mlp)
+        eng = "eng_norm" in w
+        val = None
+        if eng:
+            ptrs, lds, c0 = w["eng_ptrs"]
+            ck(L.vk_engram_gather(ptrs.ctypes.data_as(ctypes.c_void_p), lds.ctypes.data_as(ctypes.c_void_p),
+                                  c0.ctypes.data_as(ctypes.c_void_p), _p(s.engram_rows), _p(w["eng_norm"]), _p(s.eng_e), R,
+                                  len(a.engram_orders), a.engram_dim, eps, st), "vk_engram_gather")
+            val = s.eng_e
+            if a.engram_value:
+                ck(L.vk_bf16_gemm(_p(s.eng_e), s.eng_e.stride(0), _p(w["eng_value"]), None, _p(s.eng_val), D, R, D,
+                                  s.eng_e.shape[1], st), "vk_bf16_gemm")
+                val = s.eng_val
+        last = i + 1 == nl
+        w_next = model.norm_w if last else model.layers[i + 1]["mhc_norm"]
+        ck(L.vk_mhc_combine_norm(_p(s.H), _p(s.h2), _p(s.mlp), _p(s.x_in), _p(s.post), _p(s.res), _p(w_next), _p(s.hn),
+                                 _p(val) if eng else None, _p(w["eng_gate_w"]) if eng else None,
+                                 _p(w["eng_gate_b"]) if eng else None, None, R, D, 1 if last else 0, eps, st),
+           "vk_mhc_combine_norm")
+    V = model.vocab_shard
+    if isinstance(model.lm_head, ops.BF16Weight):
+        ck(L.vk_bf16_gemm_packed(_p(model.lm_head.packed), _p(s.hn), D, _p(s.logits), s.logits.stride(0), R, V, D, _p(ws),
+                                 ws.numel(), st), "vk_bf16_gemm_packed")
+    else:
+        ck(L.vk_bf16_gemm(_p(s.hn), D, _p(model.lm_head), None, _p(s.logits), s.logits.stride(0), R, V, D, st), "vk_bf16_gemm")
+    ck(L.vk_argmax(_p(s.logits), s.logits.stride(0), min(a.vocab_valid, V), _p(s.greedy), R, st), "vk_argmax")
+    logits = s.logits.view(B, T, V)
+    greedy = s.greedy.view(B, T)
+    handle = ChunkHandle(T, list(bc._pos), window, kda_inputs)
+    if write:
+        _finish(model, bc, handle, [T] * B, replay=False)
+        return logits, greedy, None
+    return logits, greedy, handle
+
+
+def _finish(model, bc, h: ChunkHandle, acc, replay):
+    L = _lib.lib()
+    a, D = model.args, model.args.hidden_size
+    B, T = bc.B, h.T
+    dev = bc.pos.device
+    st = torch.cuda.current_stream().cuda_stream
+    has_kda = any("S" in lst for lst in bc.layers)
+    if replay and has_kda:
+        acc_t = torch.tensor(acc, dtype=torch.int32, device=dev)
+        scratch_out = torch.empty((B * T, model.HV * 128), dtype=BF16, device=dev)
+        for i, proj, hin in h.kda_inputs:
+            w, lst = model.layers[i], bc.layers[i]
+            _lib.check(L.vk_kda_chunk(_p(proj), proj.stride(0), w["off_z"], w["off_fd"], _p(hin), _p(w["in_proj_b"]),
+                                      _p(w["f_up"]), _p(w["conv_w"]), _p(w["A_log"]), _p(w["dt_bias"]), _p(w["gnorm"]),
+                                      _p(lst["conv"]), _p(bc.parity), lst["conv"][0].numel(), _p(lst["S"]), _p(scratch_out),
+                                      _p(acc_t), 1, B, T, D, model.Hk, model.HV, 128, 128, a.kda_gate_rank,
+                                      a.rms_norm_eps, st), "vk_kda_chunk")
+    if has_kda:          # the conv windows now sit in the other buffer, as after a decode step
+        bc.parity ^= 1
+        bc.steps += 1
+    if h.window is not None:
+        idx = torch.tensor(acc, dtype=torch.long, device=dev).unsqueeze(1) + torch.arange(bc.keep, device=dev).unsqueeze(0)
+        bc.engram_prev[:B, : bc.keep] = torch.gather(h.window, 1, idx)
+    back = [(b, p // PAGE) for b in range(B) for p in range(h.pos0[b] + acc[b], h.pos0[b] + T) if p % PAGE == 0]
+    if back:
+        torch.cuda.synchronize(dev)
+        top = int(bc.free_top.item())
+        for n, (b, pi) in enumerate(back):
+            bc.free_list[top + n] = bc.table[b, pi]
+            bc.table[b, pi] = -1
+        bc.free_top += len(back)
+    bc._pos = [h.pos0[b] + acc[b] for b in range(B)]
+    bc.pos[:B] = torch.tensor(bc._pos, dtype=torch.int32, device=dev)
+
+
+def commit_chunk(model, bc, handle: ChunkHandle, accepted):
+    """accepted[b] in 0..T: the number of tokens of the verify pass request b keeps (batch_spec.commit,
+    batch_spec.py:160-199)."""
+    acc = [int(x) for x in accepted]
+    assert len(acc) == bc.B and all(0 <= n <= handle.T for n in acc)
+    _finish(model, bc, handle, acc, replay=True)

@@ -85,6 +85,8 @@ struct PrepParams {
     double log2_theta;
     float eps;
     AttnGeom g;
+    int mode;                     // 0: write the row and pool the block it closes; 1: write only; 2: pool only
+    const int* row_map;           // null, or [B]: the cache row whose open-block indexer keys (IK) row b uses
 };
 
 // offset RMSNorm of one 128-vector held 4 elements per lane; returns bf16-rounded values
@@ -185,39 +187,49 @@ __global__ void __launch_bounds__(256) attn_prep_kernel(const PrepParams p) {
     const int nheads = g.Hq + 2 * g.KVH + (p.idxq ? g.IH + 1 : 0);
     const int hd = hd0 + warp;
     if (hd >= nheads) return;
-    const bool closes = g.W > 0 && (pos + 1) % g.C == 0;
+    const bool wr = p.mode != 2;                                          // write this position's rows
+    const bool closes = p.mode != 1 && g.W > 0 && (pos + 1) % g.C == 0;   // pool the block this position closes
     const int slot = (pos / g.C) % (kPage / g.C);
     const int r0 = row - (g.C - 1);
     float x[4];
     if (hd < g.Hq) {                                   // query head: norm, rope
+        if (!wr) return;
         load4(pr + (size_t)hd * 2 * kD, lane, x);
         head_norm128(x, p.q_norm, lane, p.eps);
         rope128(x, lane, p.rope_dims, cs_sm, sn_sm);
         store4(p.q + ((size_t)b * g.Hq + hd) * kD, lane, x);
     } else if (hd < g.Hq + g.KVH) {                    // key head: norm, rope, into the page
         const int kv = hd - g.Hq;
-        load4(pr + p.off_k + (size_t)kv * kD, lane, x);
-        head_norm128(x, p.k_norm, lane, p.eps);
-        rope128(x, lane, p.rope_dims, cs_sm, sn_sm);
         __nv_bfloat16* Kp = p.K + ((size_t)page * g.KVH + kv) * kPage * kD;
-        store4(Kp + (size_t)row * kD, lane, x);
+        if (wr) {
+            load4(pr + p.off_k + (size_t)kv * kD, lane, x);
+            head_norm128(x, p.k_norm, lane, p.eps);
+            rope128(x, lane, p.rope_dims, cs_sm, sn_sm);
+            store4(Kp + (size_t)row * kD, lane, x);
+        }
         if (closes) pool_rows(Kp + (size_t)r0 * kD, g.C, lane, p.PK + (((size_t)page * g.KVH + kv) * (kPage / g.C) + slot) * kD);
     } else if (hd < g.Hq + 2 * g.KVH) {                // value head: as projected
         const int kv = hd - g.Hq - g.KVH;
-        load4(pr + p.off_v + (size_t)kv * kD, lane, x);
         __nv_bfloat16* Vp = p.V + ((size_t)page * g.KVH + kv) * kPage * kD;
-        store4(Vp + (size_t)row * kD, lane, x);
+        if (wr) {
+            load4(pr + p.off_v + (size_t)kv * kD, lane, x);
+            store4(Vp + (size_t)row * kD, lane, x);
+        }
         if (closes) pool_rows(Vp + (size_t)r0 * kD, g.C, lane, p.PV + (((size_t)page * g.KVH + kv) * (kPage / g.C) + slot) * kD);
     } else if (hd < g.Hq + 2 * g.KVH + g.IH) {         // indexer query heads
+        if (!wr) return;
         const int ih = hd - g.Hq - 2 * g.KVH;
         load4(p.idxq + ((size_t)b * g.IH + ih) * kD, lane, x);
         head_norm128(x, p.idx_norm, lane, p.eps);
         store4(p.qi + ((size_t)b * g.IH + ih) * kD, lane, x);
     } else {                                           // indexer key of this position -> open block slot
-        load4(p.idxk + (size_t)b * kD, lane, x);
-        head_norm128(x, p.idx_norm, lane, p.eps);
-        __nv_bfloat16* Ip = p.IK + (size_t)b * g.C * kD;
-        store4(Ip + (size_t)(pos % g.C) * kD, lane, x);
+        const int ikrow = p.row_map != nullptr ? p.row_map[b] : b;
+        __nv_bfloat16* Ip = p.IK + (size_t)ikrow * g.C * kD;
+        if (wr) {
+            load4(p.idxk + (size_t)b * kD, lane, x);
+            head_norm128(x, p.idx_norm, lane, p.eps);
+            store4(Ip + (size_t)(pos % g.C) * kD, lane, x);
+        }
         if (closes) pool_rows(Ip, g.C, lane, p.BK + ((size_t)page * (kPage / g.C) + slot) * kD);
     }
 }
@@ -930,12 +942,30 @@ int vk_batch_step_end(int* pos, int* parity, int B, cudaStream_t stream) {
     return (int)vk_launch(batch_step_end_kernel, dim3((B + 63) / 64), dim3(64), 0, stream, pos, parity, B);
 }
 
+int vk_attn_prep_rows(const vk_attn_geom* gm, const void* proj, int ldp, int off_k, int off_v, const void* idxq, const void* idxk,
+                      const void* q_norm, const void* k_norm, const void* idx_norm, const int* pos, const int* table, void* q,
+                      void* qi, void* K, void* V, void* PK, void* PV, void* BK, void* IK, int B, int rope_dims,
+                      double rope_theta, float eps, int mode, const int* row_map, cudaStream_t stream);
+
 int vk_attn_prep(const vk_attn_geom* gm, const void* proj, int ldp, int off_k, int off_v, const void* idxq, const void* idxk,
                  const void* q_norm, const void* k_norm, const void* idx_norm, const int* pos, const int* table, void* q,
                  void* qi, void* K, void* V, void* PK, void* PV, void* BK, void* IK, int B, int rope_dims, double rope_theta,
                  float eps, cudaStream_t stream) {
-    if (!geom_ok(gm) || B <= 0 || rope_dims % 8 != 0 || rope_dims > kD) return VK_EINVAL;
+    return vk_attn_prep_rows(gm, proj, ldp, off_k, off_v, idxq, idxk, q_norm, k_norm, idx_norm, pos, table, q, qi, K, V, PK, PV,
+                             BK, IK, B, rope_dims, rope_theta, eps, 0, nullptr, stream);
+}
+
+// The same for rows that are several positions of one sequence (a verify window, a prefill chunk): a row's block may
+// then be closed by a position whose neighbours are written by other rows of the same launch, so the caller writes all
+// rows first (mode 1) and pools in a second launch (mode 2). row_map names the cache row whose open-block indexer keys
+// a row shares.
+int vk_attn_prep_rows(const vk_attn_geom* gm, const void* proj, int ldp, int off_k, int off_v, const void* idxq, const void* idxk,
+                      const void* q_norm, const void* k_norm, const void* idx_norm, const int* pos, const int* table, void* q,
+                      void* qi, void* K, void* V, void* PK, void* PV, void* BK, void* IK, int B, int rope_dims,
+                      double rope_theta, float eps, int mode, const int* row_map, cudaStream_t stream) {
+    if (!geom_ok(gm) || B <= 0 || rope_dims % 8 != 0 || rope_dims > kD || mode < 0 || mode > 2) return VK_EINVAL;
     PrepParams p = {};
+    p.mode = mode; p.row_map = row_map;
     p.proj = (const __nv_bfloat16*)proj; p.idxq = (const __nv_bfloat16*)idxq; p.idxk = (const __nv_bfloat16*)idxk;
     p.q_norm = (const __nv_bfloat16*)q_norm; p.k_norm = (const __nv_bfloat16*)k_norm; p.idx_norm = (const __nv_bfloat16*)idx_norm;
     p.pos = pos; p.table = table; p.q = (__nv_bfloat16*)q; p.qi = (__nv_bfloat16*)qi;

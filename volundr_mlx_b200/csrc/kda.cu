@@ -294,6 +294,7 @@ struct KdaChunkParams {
     KdaParams k;          // proj / h / out rows are (b * T + t); g_override, xrec_out unused
     const int* accept;    // [B] or null
     int T;
+    int write_state;      // 0: outputs only, the state and the conv window stay as they were (a verify pass)
 };
 
 // xor-tree sum of p[0..31] as the 32 lanes of a warp would form it
@@ -472,6 +473,7 @@ __global__ void __launch_bounds__(128, 2) kda_chunk_kernel(const KdaChunkParams 
         }
         __syncthreads();   // the group's shared arrays are free again
     }
+    if (!cp.write_state) return;
 #pragma unroll
     for (int j = 0; j < 32; j++)
         *reinterpret_cast<float4*>(Srow + 4 * j) = make_float4(st[4 * j], st[4 * j + 1], st[4 * j + 2], st[4 * j + 3]);
@@ -520,8 +522,8 @@ int vk_kda_configure(void) {
 // buffer, as after one vk_kda_step: flip the parity word once per launch.
 int vk_kda_chunk(const void* proj, int ldp, int off_z, int off_fd, const void* h, const void* w_b, const void* w_fup,
                  const float* conv_w, const float* A_log, const float* dt_bias, const void* norm_w, void* conv,
-                 const int* parity, size_t conv_stride, float* S, void* out, const int* accept, int B, int T, int D, int Hk,
-                 int HV, int Dk, int Dv, int rank, float eps, cudaStream_t stream) {
+                 const int* parity, size_t conv_stride, float* S, void* out, const int* accept, int write_state, int B, int T,
+                 int D, int Hk, int HV, int Dk, int Dv, int rank, float eps, cudaStream_t stream) {
     if (B <= 0 || T <= 0 || Dk != 128 || Dv != 128 || Hk <= 0 || HV % Hk != 0 || rank <= 0 || rank > 256 || rank % 8 != 0 ||
         D % 8 != 0 || parity == nullptr)
         return VK_EINVAL;
@@ -531,6 +533,7 @@ int vk_kda_chunk(const void* proj, int ldp, int off_z, int off_fd, const void* h
             (__nv_bfloat16*)out, nullptr, nullptr, ldp, off_z, off_fd, D, Hk, HV, rank, eps};
     cp.accept = accept;
     cp.T = T;
+    cp.write_state = write_state ? 1 : 0;
     return (int)vk_launch(kda_chunk_kernel, dim3(HV, B), dim3(128), 0, stream, cp);
 }
 

@@ -1,0 +1,272 @@
+// INT4 affine weight GEMM for many activation rows (verify windows of B x T rows, prefill chunks) on the 5th-generation
+// tensor cores: y[M, N] = x[M, K] . dequant(w)[N, K]^T with tcgen05.mma, the accumulator in tensor memory.
+//
+// Replaces mx.quantized_matmul at M = B * T or a prefill chunk (batch_spec.verify_forward, batch_spec.py:107-158;
+// session.prefill_iter, session.py:351-387): there the product is compute-bound, so unlike the small-M kernel
+// (w4_gemm.cu), which multiplies raw codes and applies scale and bias to the group's fp32 product, this one
+// dequantises a weight tile to bf16 once, bf16(s * u + b) rounded once (mx.dequantize's value, vk_w4_dequant), and feeds
+// it to the tensor cores; the activations are used as they are. It reads the same packed weights (vk_w4_repack).
+//
+// One CTA = one 256-row superblock of the weight (the D tile's N) x 128 activation rows (the D tile's M) x all of K:
+//   warp 0      one lane: 1-D TMA bulk copies per 64-column group: the packed 9216-byte weight step and the 16 KB
+//               activation tile (pre-arranged by w4_xtile_kernel) into a 3-stage ring
+//   warp 1      one lane: waits for a stage's activations and dequantised weights, issues 4 tcgen05.mma (M 128, N 256,
+//               K 16, A and B from shared memory, K-major, no swizzle), commits them to the stage's "free" barrier
+//   warps 2..9  dequantisers: unpack the codes of the stage (the mma.sync fragment order of the packed layout),
+//               bf16(s * u + b) with one fused rounding, store into the canonical K-major layout, fence to the async
+//               proxy, arrive on the stage's "weights ready" barrier
+//   warps 4..7  afterwards: tcgen05.ld of their 32 accumulator lanes (= activation rows), bf16, 16-byte stores
+// Shared-memory operand layout (both operands, "K-major interleaved", 16-byte units): [k / 8][row][8 elements]: a core
+// matrix is 8 rows x 16 bytes, contiguous; leading-dimension (K) offset = rows * 16 bytes, stride (row group) offset
+// = 128 bytes.
+// Every wait is bounded: a wait that runs out sets the status word, the kernel skips ahead, frees its tensor memory
+// and returns.
+#include "common.cuh"
+
+namespace {
+
+constexpr int kTileM = 128;                    // activation rows per CTA = accumulator lanes
+constexpr int kTileN = 256;                    // weight rows per CTA = accumulator columns (one superblock)
+constexpr int kTStages = 3;
+constexpr int kPackedStep = 9216;              // bytes of one (superblock, group) of packed weights
+constexpr int kXTileBytes = kTileM * 64 * 2;   // 16 KB: [8][128][8] bf16
+constexpr int kWdBytes = kTileN * 64 * 2;      // 32 KB: [8][256][8] bf16
+constexpr int kTStageBytes = kPackedStep + kXTileBytes + kWdBytes;
+constexpr int kTileThreads = 320;
+constexpr size_t kTileSmem = (size_t)kTStages * kTStageBytes + 128;
+
+struct TileParams {
+    const uint8_t* wp;        // packed weights [NSB][G][9216]
+    const uint8_t* xt;        // activation tiles [MT][G][16 KB]
+    __nv_bfloat16* y;         // [M, ldy]
+    int M, N, G, ldy;
+};
+
+// x [M, ldx] row-major -> tiles [M / 128][G][k / 8 (8)][row (128)][8 bf16]; rows beyond M are zero
+__global__ void __launch_bounds__(128) w4_xtile_kernel(const __nv_bfloat16* __restrict__ x, int ldx, int M, int G,
+                                                       uint8_t* __restrict__ xt) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int kg = blockIdx.x, mt = blockIdx.y, r = threadIdx.x;
+    const int m = mt * kTileM + r;
+    uint8_t* dst = xt + ((size_t)mt * G + kg) * kXTileBytes;
+#pragma unroll
+    for (int c = 0; c < 8; c++) {
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        if (m < M) v = *reinterpret_cast<const uint4*>(x + (size_t)m * ldx + kg * 64 + c * 8);
+        *reinterpret_cast<uint4*>(dst + ((size_t)c * kTileM + r) * 16) = v;
+    }
+}
+
+__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+    // start address, leading-dimension and stride byte offsets in 16-byte units; version 1 (sm_100); no swizzle
+    return (uint64_t)((smem_addr >> 4) & 0x3FFF) | ((uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16) |
+           ((uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32) | (1ull << 46);
+}
+
+__global__ void __launch_bounds__(kTileThreads, 1) w4_tile_kernel(const TileParams p) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (size_t)kTStages * kTStageBytes);
+    uint64_t* full = bars;                   // [stage] packed weights + activation tile have landed (TMA bytes)
+    uint64_t* wready = bars + kTStages;      // [stage] dequantised weights are in place (256 arrivals)
+    uint64_t* freeb = bars + 2 * kTStages;   // [stage] the stage's MMAs have finished reading it
+    uint64_t* accdone = bars + 3 * kTStages; // the whole accumulation has finished
+    __shared__ uint32_t s_tmem;
+    __shared__ int s_fail;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int sb = blockIdx.x, mt = blockIdx.y;
+    const int G = p.G;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kTStages; s++) {
+            mbar_init(&full[s], 1);
+            mbar_init(&wready[s], 256);
+            mbar_init(&freeb[s], 1);
+        }
+        mbar_init(accdone, 1);
+        mbar_fence_init();
+        s_fail = 0;
+    }
+    if (warp == 1) {   // one warp allocates the accumulator: 256 columns of tensor memory
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&s_tmem)), "r"(256u)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = s_tmem;
+
+    if (warp == 0) {
+        // ---------------------------------------------------------------- producer
+        if (lane == 0) {
+            const uint8_t* wsrc = p.wp + (size_t)sb * G * kPackedStep;
+            const uint8_t* xsrc = p.xt + (size_t)mt * G * kXTileBytes;
+            pdl_wait();
+            pdl_launch_dependents();
+            int st = 0;
+            uint32_t par = 0;
+            for (int i = 0; i < G; i++) {
+                if (i >= kTStages && !mbar_wait(&freeb[st], par)) { s_fail = 1; break; }
+                uint8_t* dst = smem + (size_t)st * kTStageBytes;
+                mbar_expect_tx(&full[st], kPackedStep + kXTileBytes);
+                tma_bulk_g2s(dst, wsrc + (size_t)i * kPackedStep, kPackedStep, &full[st]);
+                tma_bulk_g2s(dst + kPackedStep, xsrc + (size_t)i * kXTileBytes, kXTileBytes, &full[st]);
+                if (++st == kTStages) { st = 0; if (i >= kTStages) par ^= 1u; }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------------------------------------------------------- MMA issue
+        if (lane == 0) {
+            // instruction descriptor: D fp32, A and B bf16, both K-major, N = 256, M = 128
+            const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kTileN >> 3) << 17) | ((uint32_t)(kTileM >> 4) << 24);
+            int st = 0;
+            uint32_t ph = 0;
+            bool ok = true;
+            for (int i = 0; i < G && ok; i++) {
+                if (!mbar_wait(&full[st], ph) || !mbar_wait(&wready[st], ph)) { ok = false; break; }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t a0 = smem_u32(smem + (size_t)st * kTStageBytes + kPackedStep);
+                const uint32_t b0 = a0 + kXTileBytes;
+#pragma unroll
+                for (int kk = 0; kk < 4; kk++) {   // K = 16 per instruction = two 16-byte units along K
+                    const uint64_t da = umma_desc(a0 + kk * 2 * (kTileM * 16), kTileM * 16, 128);
+                    const uint64_t db = umma_desc(b0 + kk * 2 * (kTileN * 16), kTileN * 16, 128);
+                    const uint32_t accumulate = (i > 0 || kk > 0) ? 1u : 0u;
+                    const uint32_t zero = 0u;   // (no output lane disabled)
+                    asm volatile(
+                        "{\n\t"
+                        ".reg .pred p;\n\t"
+                        "setp.ne.b32 p, %4, 0;\n\t"
+                        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t"
+                        "}\n" ::"r"(tmem), "l"(da), "l"(db), "r"(idesc), "r"(accumulate), "r"(zero)
+                        : "memory");
+                }
+                // the stage may be refilled once these MMAs have read it (the commit also fences the issue order)
+                asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(&freeb[st]))
+                             : "memory");
+                if (++st == kTStages) { st = 0; ph ^= 1u; }
+            }
+            if (!ok) s_fail = 1;
+            asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(accdone))
+                         : "memory");
+        }
+    } else {
+        // ---------------------------------------------------------------- dequantisers (256 threads)
+        const int dt = threadIdx.x - 64;          // 0..255
+        const int j = dt >> 5;                    // 32-row block of the superblock
+        const int g = lane >> 2, t = lane & 3;
+        int st = 0;
+        uint32_t ph = 0;
+        bool ok = true;
+        for (int i = 0; i < G; i++) {
+            if (!mbar_wait(&full[st], ph)) { ok = false; break; }
+            const uint8_t* stage = smem + (size_t)st * kTStageBytes;
+            const uint8_t* ch = stage + j * 1152;
+            uint8_t* wd = smem + (size_t)st * kTStageBytes + kPackedStep + kXTileBytes;
+            const uint4 sb4 = *reinterpret_cast<const uint4*>(ch + 1024 + g * 16);   // (scale | bias << 16) of 4 rows
+            const uint32_t sbw[4] = {sb4.x, sb4.y, sb4.z, sb4.w};
+#pragma unroll
+            for (int s = 0; s < 2; s++) {
+                const uint4 wv = *reinterpret_cast<const uint4*>(ch + s * 512 + lane * 16);
+                const uint32_t wq[4] = {wv.x, wv.y, wv.z, wv.w};
+                // rows n0 = 32 j + 16 s + g and n0 + 8; their scale / bias as bf16 pairs
+                __nv_bfloat162 sc2[2], bi2[2];
+#pragma unroll
+                for (int h = 0; h < 2; h++) {
+                    const uint32_t wsb = sbw[2 * s + h];
+                    const uint32_t ss = (wsb & 0xFFFFu) | (wsb << 16), bb = (wsb >> 16) | (wsb & 0xFFFF0000u);
+                    sc2[h] = *reinterpret_cast<const __nv_bfloat162*>(&ss);
+                    bi2[h] = *reinterpret_cast<const __nv_bfloat162*>(&bb);
+                }
+                const uint32_t c128 = 0x43004300u;
+                const __nv_bfloat162 k128 = *reinterpret_cast<const __nv_bfloat162*>(&c128);
+#pragma unroll
+                for (int q = 0; q < 4; q++) {
+                    // register i of the word: (row n0 + 8 (i & 1), columns 16 q + 8 (i >> 1) + 2 t, + 1) as 128 + code
+#pragma unroll
+                    for (int r = 0; r < 4; r++) {
+                        const uint32_t au = ((wq[q] >> (4 * r)) & 0x000F000Fu) | 0x43004300u;
+                        const __nv_bfloat162 u2 = __hsub2(*reinterpret_cast<const __nv_bfloat162*>(&au), k128);   // exact
+                        const __nv_bfloat162 v2 = __hfma2(u2, sc2[r & 1], bi2[r & 1]);                            // one rounding
+                        const int n = 32 * j + 16 * s + g + 8 * (r & 1);
+                        const int kcol = 16 * q + 8 * (r >> 1) + 2 * t;
+                        *reinterpret_cast<__nv_bfloat162*>(wd + ((size_t)(kcol >> 3) * kTileN + n) * 16 + (kcol & 7) * 2) = v2;
+                    }
+                }
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy stores -> visible to the MMA
+            mbar_arrive(&wready[st]);
+            if (++st == kTStages) { st = 0; ph ^= 1u; }
+        }
+        if (!ok) s_fail = 1;
+        // ---------------------------------------------------------------- epilogue (warps 4..7: lanes 32 (warp % 4) ..)
+        if (warp >= 4 && warp < 8) {
+            if (ok && mbar_wait(accdone, 0)) {
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const int m = mt * kTileM + (warp & 3) * 32 + lane;
+                const uint32_t taddr = tmem + ((uint32_t)((warp & 3) * 32) << 16);
+                for (int c0 = 0; c0 < kTileN; c0 += 8) {
+                    uint32_t r[8];
+                    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+                                 : "r"(taddr + (uint32_t)c0));
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                    const int n = sb * kTileN + c0;
+                    if (m < p.M && n < p.N) {
+                        __nv_bfloat16* dst = p.y + (size_t)m * p.ldy + n;
+                        if (n + 8 <= p.N && ((((size_t)m * p.ldy + n) & 7) == 0)) {
+                            uint4 o;
+                            o.x = pack_bf2(__uint_as_float(r[0]), __uint_as_float(r[1]));
+                            o.y = pack_bf2(__uint_as_float(r[2]), __uint_as_float(r[3]));
+                            o.z = pack_bf2(__uint_as_float(r[4]), __uint_as_float(r[5]));
+                            o.w = pack_bf2(__uint_as_float(r[6]), __uint_as_float(r[7]));
+                            *reinterpret_cast<uint4*>(dst) = o;
+                        } else {
+#pragma unroll
+                            for (int e = 0; e < 8; e++)
+                                if (n + e < p.N) dst[e] = f2bf(__uint_as_float(r[e]));
+                        }
+                    }
+                }
+            } else {
+                s_fail = 1;
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(256u) : "memory");
+    }
+    if (threadIdx.x == 0 && s_fail) vk_set_status(VK_ST_MBAR_TIMEOUT);
+}
+
+}  // namespace
+
+extern "C" {
+
+// Bytes of scratch vk_w4_gemm_tile needs for the re-arranged activations.
+size_t vk_w4_tile_workspace_bytes(int M, int K) {
+    if (M <= 0 || K <= 0 || K % 64 != 0) return 0;
+    return (size_t)((M + kTileM - 1) / kTileM) * (K / 64) * kXTileBytes;
+}
+
+// y[M, N] = bf16(x[M, K] . dequant(W)^T) on tcgen05 tensor cores; `packed` as for vk_w4_gemm. Any M (tiles of 128 rows).
+int vk_w4_gemm_tile(const void* packed, const void* x, int ldx, void* y, int ldy, int M, int N, int K, void* workspace,
+                    size_t workspace_bytes, cudaStream_t stream) {
+    if (M <= 0 || N <= 0 || K <= 0 || K % 64 != 0 || ldx % 8 != 0 || ldx < K || ldy < N) return VK_EINVAL;
+    if (((uintptr_t)x & 15) || ((uintptr_t)packed & 15) || workspace == nullptr || ((uintptr_t)workspace & 15)) return VK_EINVAL;
+    if (workspace_bytes < vk_w4_tile_workspace_bytes(M, K)) return VK_ENOSPC;
+    static bool configured = false;
+    if (!configured) {
+        VK_CUDA(cudaFuncSetAttribute(w4_tile_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kTileSmem));
+        configured = true;
+    }
+    const int G = K / 64, MTn = (M + kTileM - 1) / kTileM, NSB = (N + kTileN - 1) / kTileN;
+    VK_CUDA(vk_launch(w4_xtile_kernel, dim3(G, MTn), dim3(128), 0, stream, (const __nv_bfloat16*)x, ldx, M, G, (uint8_t*)workspace));
+    TileParams p = {(const uint8_t*)packed, (const uint8_t*)workspace, (__nv_bfloat16*)y, M, N, G, ldy};
+    return (int)vk_launch(w4_tile_kernel, dim3(NSB, MTn), dim3(kTileThreads), kTileSmem, stream, p);
+}
+
+}  // extern "C"

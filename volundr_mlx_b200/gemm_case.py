@@ -24,20 +24,21 @@ def make_weight(N: int, K: int, device, seed: int):
     return ops.w4_repack(w, s, b, 64)
 
 
-def run(M: int, N: int, K: int, copies: int, launches: int, replays: int, device=None):
+def run(M: int, N: int, K: int, copies: int, launches: int, replays: int, device=None, tile: bool = False):
     device = device or torch.device("cuda", 0)
     wts = [make_weight(N, K, device, 100 + i) for i in range(copies)]
     x = torch.randn(M, K, device=device).to(torch.bfloat16)
     y = torch.empty(M, N, device=device, dtype=torch.bfloat16)
+    gemm = ops.w4_gemm_tile if tile else ops.w4_gemm   # (tile: the tcgen05 kernel for many rows)
     s = torch.cuda.Stream(device)
     with torch.cuda.stream(s):
         for i in range(min(copies, 3)):
-            ops.w4_gemm(x, wts[i], y)
+            gemm(x, wts[i], y)
         torch.cuda.synchronize(device)
         g = torch.cuda.CUDAGraph()
         with torch.cuda.graph(g, stream=s):
             for i in range(launches):
-                ops.w4_gemm(x, wts[i % copies], y)
+                gemm(x, wts[i % copies], y)
         g.replay()
         torch.cuda.synchronize(device)
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -49,7 +50,8 @@ def run(M: int, N: int, K: int, copies: int, launches: int, replays: int, device
     ops.check_status(device)
     us = e0.elapsed_time(e1) * 1e3 / (replays * launches)   # per vk_w4_gemm call: x-record kernel + GEMM kernel
     nbytes = N * K * 0.5625 + M * K * 2 + M * N * 2
-    return {"M": M, "N": N, "K": K, "us_per_gemm": us, "GBps": nbytes / us / 1e3, "bytes": nbytes, "copies": copies}
+    return {"M": M, "N": N, "K": K, "kernel": "tcgen05 tile" if tile else "streaming", "us_per_gemm": us,
+            "GBps": nbytes / us / 1e3, "TFLOPs": 2.0 * M * N * K / us / 1e6, "bytes": nbytes, "copies": copies}
 
 
 def main():
@@ -60,9 +62,10 @@ def main():
     ap.add_argument("--copies", type=int, default=0, help="weight copies (default: enough for 400 MB)")
     ap.add_argument("--launches", type=int, default=12)
     ap.add_argument("--replays", type=int, default=5)
+    ap.add_argument("--tile", action="store_true", help="use vk_w4_gemm_tile (tcgen05, for many rows)")
     a = ap.parse_args()
     copies = a.copies or max(2, int(400e6 // (a.n * a.k * 0.5625)) + 1)
-    print(json.dumps(run(a.m, a.n, a.k, copies, a.launches, a.replays)))
+    print(json.dumps(run(a.m, a.n, a.k, copies, a.launches, a.replays, tile=a.tile)))
 
 
 if __name__ == "__main__":

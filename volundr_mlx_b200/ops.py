@@ -74,6 +74,19 @@ def w4_gemm(x, wt: W4Weight, out=None):
     return out
 
 
+def w4_gemm_tile(x, wt: W4Weight, out=None):
+    """The same product on the tcgen05 tensor cores (tiles of 128 rows): meant for M >= 64."""
+    L = _lib.lib()
+    assert x.dtype == BF16 and x.dim() == 2 and x.shape[1] == wt.K and x.stride(1) == 1
+    M = x.shape[0]
+    if out is None:
+        out = torch.empty((M, wt.N), dtype=BF16, device=x.device)
+    ws = workspace(L.vk_w4_tile_workspace_bytes(M, wt.K), x.device)
+    _lib.check(L.vk_w4_gemm_tile(_p(wt.packed), _p(x), x.stride(0), _p(out), out.stride(0), M, wt.N, wt.K, _p(ws),
+                                 ws.numel(), _stream()), "vk_w4_gemm_tile")
+    return out
+
+
 class BF16Weight:
     """A bf16 weight [N, K] in the streaming kernel's fragment order (4096-byte chunks of 32 rows x 64 columns)."""
 
