@@ -132,9 +132,20 @@ def forward_chunk(model, bc, toks, write=False):
         s.engram_prev.copy_(window.unfold(1, bc.keep, 1)[:, :T].reshape(R, bc.keep))
     ws = ops.workspace(max(1 << 26, L.vk_w4_workspace_bytes(R, max(w["gate_up"].N for w in model.layers), D)), dev)
 
+    tile_ws = ops.workspace(1 << 26, dev) if R < 64 else None
+    if R >= 64:
+        kmax = max(max(w[nm].K for nm in ("proj", "out", "gate_up", "down")) for w in model.layers)
+        tile_ws = torch.empty(L.vk_w4_tile_workspace_bytes(R, kmax), dtype=torch.uint8, device=dev)
+
     def gemm(x, wt, y):
-        ck(L.vk_w4_gemm(_p(wt.packed), _p(x), x.stride(0), _p(y), y.stride(0), R, wt.N, wt.K, _p(ws), ws.numel(), st),
-           "vk_w4_gemm")
+        # 64 rows and more, and a weight with enough 256-row tiles to fill the GPU: the tcgen05 tile kernel; otherwise
+        # the streaming kernel's wide passes
+        if R >= 64 and (wt.N + 255) // 256 >= 74:
+            ck(L.vk_w4_gemm_tile(_p(wt.packed), _p(x), x.stride(0), _p(y), y.stride(0), R, wt.N, wt.K, _p(tile_ws),
+                                 tile_ws.numel(), st), "vk_w4_gemm_tile")
+        else:
+            ck(L.vk_w4_gemm(_p(wt.packed), _p(x), x.stride(0), _p(y), y.stride(0), R, wt.N, wt.K, _p(ws), ws.numel(), st),
+               "vk_w4_gemm")
 
     w0 = model.layers[0]
     ck(L.vk_embed(_p(s.tok), _p(model.embed), _p(w0["mhc_norm"]), _p(s.H), _p(s.hn),
