@@ -67,12 +67,16 @@ size_t vk_bf16_workspace_bytes(int M, int N, int K);
 int vk_bf16_gemm_packed(const void* packed, const void* x, int ldx, void* y, int ldy, int M, int N, int K, void* workspace,
                         size_t workspace_bytes, vk_stream_t stream);
 /* The same product for many activation rows (verify windows of B x T rows, prefill chunks) on the tcgen05 tensor cores
- * with the accumulator in tensor memory: tiles of 128 activation rows x one 256-row superblock of the weight. The weight
+ * with the accumulator in tensor memory: one or two tiles of 128 activation rows x 256 or 64 weight rows per CTA. The weight
  * tile is dequantised to bf16 once, bf16(s * u + b) with a single rounding (the value vk_w4_dequant gives), so results
  * differ from vk_w4_gemm by that rounding of the weights (within the bf16 bar). `packed` as for vk_w4_gemm. */
 size_t vk_w4_tile_workspace_bytes(int M, int K);
 int vk_w4_gemm_tile(const void* packed, const void* x, int ldx, void* y, int ldy, int M, int N, int K, void* workspace,
                     size_t workspace_bytes, vk_stream_t stream);
+/* Tuning / testing aid for vk_w4_gemm_tile: weight rows per CTA (256 = a whole superblock, 64 = a quarter, for weights
+ * with few rows) and tiles of 128 activation rows per CTA (1 or 2; with 2 every dequantised weight tile feeds two
+ * accumulators). 0 = chosen from the shape (the default). Results do not depend on either. */
+int vk_w4_tile_force(int weight_rows, int row_tiles);
 /* Tuning / testing aid: force the number of persistent CTAs the work is dealt to (0 = two per SM), and the budget in
  * MB of the L2 prefetch a GEMM issues for its own weights before it waits for the kernel that produces x
  * (0 or negative = none, the default: on B200 the prefetch measured slower than none). Results do not depend on either. */

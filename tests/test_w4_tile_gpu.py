@@ -26,10 +26,15 @@ def make_w4(rng, N, K, group):
     return w, s, b
 
 
-@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (128, 256, 512), (37, 520, 1024), (200, 300, 2048), (256, 5120, 1024)])
-def test_tile_gemm(cuda, M, N, K):
-    from volundr_mlx_b200 import ops
+@pytest.mark.parametrize("shape", [(0, 0), (256, 1), (256, 2), (64, 1), (64, 2)])
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (128, 256, 512), (37, 520, 1024), (200, 300, 2048), (256, 5120, 1024),
+                                   (300, 768, 640)])
+def test_tile_gemm(cuda, M, N, K, shape):
+    """Every tile shape (weight rows per CTA 256 / 64, one or two tiles of activation rows per CTA; (0, 0) = chosen
+    from the shape) gives the same result, bit for bit: the accumulation order along K does not depend on it."""
+    from volundr_mlx_b200 import _lib, ops
 
+    _lib.check(_lib.lib().vk_w4_tile_force(*shape), "vk_w4_tile_force")
     rng = np.random.default_rng(M + N + K)
     w, s, b = make_w4(rng, N, K, 64)
     x = bf(rng.normal(0, 1, size=(M, K)))
@@ -38,8 +43,11 @@ def test_tile_gemm(cuda, M, N, K):
     tx = dev(x, torch.bfloat16)
     y = ops.w4_gemm_tile(tx, wt)
     y2 = ops.w4_gemm_tile(tx, wt)
+    _lib.check(_lib.lib().vk_w4_tile_force(256, 1), "vk_w4_tile_force")
+    y3 = ops.w4_gemm_tile(tx, wt)
+    _lib.check(_lib.lib().vk_w4_tile_force(0, 0), "vk_w4_tile_force")
     ops.check_status()
-    assert torch.equal(y, y2)
+    assert torch.equal(y, y2) and torch.equal(y, y3)
     got = y.float().cpu().numpy()
     np.testing.assert_allclose(got, OW.matmul(x, w, s, b, 64), rtol=2e-2, atol=2e-2)
     Wd = OW.dequant(w, s, b, 64).astype(np.float64)          # bf16-valued

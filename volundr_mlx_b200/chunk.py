@@ -140,7 +140,7 @@ def forward_chunk(model, bc, toks, write=False):
     def gemm(x, wt, y):
         # 64 rows and more, and a weight with enough 256-row tiles to fill the GPU: the tcgen05 tile kernel; otherwise
         # the streaming kernel's wide passes
-        if R >= 64 and (wt.N + 255) // 256 >= 74:
+        if R >= 64:
             ck(L.vk_w4_gemm_tile(_p(wt.packed), _p(x), x.stride(0), _p(y), y.stride(0), R, wt.N, wt.K, _p(tile_ws),
                                  tile_ws.numel(), st), "vk_w4_gemm_tile")
         else:

@@ -26,14 +26,24 @@
 namespace {
 
 constexpr int kTileM = 128;                    // activation rows per CTA = accumulator lanes
-constexpr int kTileN = 256;                    // weight rows per CTA = accumulator columns (one superblock)
-constexpr int kTStages = 3;
 constexpr int kPackedStep = 9216;              // bytes of one (superblock, group) of packed weights
 constexpr int kXTileBytes = kTileM * 64 * 2;   // 16 KB: [8][128][8] bf16
-constexpr int kWdBytes = kTileN * 64 * 2;      // 32 KB: [8][256][8] bf16
-constexpr int kTStageBytes = kPackedStep + kXTileBytes + kWdBytes;
 constexpr int kTileThreads = 320;
-constexpr size_t kTileSmem = (size_t)kTStages * kTStageBytes + 128;
+// Weight rows per CTA = accumulator columns: TN = 256 (a whole superblock) for weights with many rows; TN = 64 (a
+// quarter: two of the superblock's eight 32-row chunks) for weights whose 256-row tiles would not fill the GPU.
+// ML = tiles of 128 activation rows per CTA (1 or 2): with two, every dequantised weight tile feeds two accumulators,
+// which halves the dequantisation work per multiply-add (the limit of this kernel).
+template <int TN, int ML> struct TileCfg {
+    static constexpr int kPacked = TN / 32 * 1152;          // bytes of the CTA's chunks inside a packed step
+    static constexpr int kWd = TN * 64 * 2;                  // dequantised tile [8][TN][8] bf16
+    static constexpr int kStage = kPacked + ML * kXTileBytes + kWd;
+    static constexpr int kStages = (220 * 1024 / kStage) < 6 ? (220 * 1024 / kStage) : 6;
+    static constexpr int kSplit = 256 / TN;                  // dequantiser threads per (chunk, lane): all 256 threads work
+    static constexpr int kBarBytes = (3 * kStages + 1) * 8;  // full / wready / freeb per stage + accdone
+    static constexpr size_t kSmem = (size_t)kStages * kStage + ((kBarBytes + 127) / 128) * 128;
+    static_assert(kSmem <= 227 * 1024, "stages do not fit the CTA's shared memory");
+    static constexpr uint32_t kCols = TN * ML;               // tensor-memory columns (a power of two >= 32)
+};
 
 struct TileParams {
     const uint8_t* wp;        // packed weights [NSB][G][9216]
@@ -58,14 +68,22 @@ __global__ void __launch_bounds__(128) w4_xtile_kernel(const __nv_bfloat16* __re
     }
 }
 
+int g_tile_force_tn = 0, g_tile_force_ml = 0;
+
 __device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
     // start address, leading-dimension and stride byte offsets in 16-byte units; version 1 (sm_100); no swizzle
     return (uint64_t)((smem_addr >> 4) & 0x3FFF) | ((uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16) |
            ((uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32) | (1ull << 46);
 }
 
+template <int TN, int ML>
 __global__ void __launch_bounds__(kTileThreads, 1) w4_tile_kernel(const TileParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
+    using Cfg = TileCfg<TN, ML>;
+    constexpr int kTileN = TN;
+    constexpr int kTStages = Cfg::kStages;
+    constexpr int kTStageBytes = Cfg::kStage;
+    constexpr int kPackedBytes = Cfg::kPacked;
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (size_t)kTStages * kTStageBytes);
     uint64_t* full = bars;                   // [stage] packed weights + activation tile have landed (TMA bytes)
     uint64_t* wready = bars + kTStages;      // [stage] dequantised weights are in place (256 arrivals)
@@ -74,8 +92,11 @@ __global__ void __launch_bounds__(kTileThreads, 1) w4_tile_kernel(const TilePara
     __shared__ uint32_t s_tmem;
     __shared__ int s_fail;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int sb = blockIdx.x, mt = blockIdx.y;
+    constexpr int kPerSB = 256 / TN;                     // CTAs per superblock
+    const int sb = blockIdx.x / kPerSB, part = blockIdx.x % kPerSB, mt = blockIdx.y * ML;
+    const int n_base = sb * 256 + part * TN;             // first weight row of this CTA
     const int G = p.G;
+    const int nm = (ML == 2 && (mt + 1) * kTileM < p.M) ? 2 : 1;   // tiles of activation rows this CTA really has
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kTStages; s++) {
@@ -88,7 +109,7 @@ __global__ void __launch_bounds__(kTileThreads, 1) w4_tile_kernel(const TilePara
         s_fail = 0;
     }
     if (warp == 1) {   // one warp allocates the accumulator: 256 columns of tensor memory
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&s_tmem)), "r"(256u)
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&s_tmem)), "r"(Cfg::kCols)
                      : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -100,7 +121,7 @@ __global__ void __launch_bounds__(kTileThreads, 1) w4_tile_kernel(const TilePara
     if (warp == 0) {
         // ---------------------------------------------------------------- producer
         if (lane == 0) {
-            const uint8_t* wsrc = p.wp + (size_t)sb * G * kPackedStep;
+            const uint8_t* wsrc = p.wp + (size_t)sb * G * kPackedStep + (size_t)part * kPackedBytes;
             const uint8_t* xsrc = p.xt + (size_t)mt * G * kXTileBytes;
             pdl_wait();
             pdl_launch_dependents();
@@ -109,16 +130,18 @@ __global__ void __launch_bounds__(kTileThreads, 1) w4_tile_kernel(const TilePara
             for (int i = 0; i < G; i++) {
                 if (i >= kTStages && !mbar_wait(&freeb[st], par)) { s_fail = 1; break; }
                 uint8_t* dst = smem + (size_t)st * kTStageBytes;
-                mbar_expect_tx(&full[st], kPackedStep + kXTileBytes);
-                tma_bulk_g2s(dst, wsrc + (size_t)i * kPackedStep, kPackedStep, &full[st]);
-                tma_bulk_g2s(dst + kPackedStep, xsrc + (size_t)i * kXTileBytes, kXTileBytes, &full[st]);
+                mbar_expect_tx(&full[st], kPackedBytes + nm * kXTileBytes);
+                tma_bulk_g2s(dst, wsrc + (size_t)i * kPackedStep, kPackedBytes, &full[st]);
+                tma_bulk_g2s(dst + kPackedBytes, xsrc + (size_t)i * kXTileBytes, kXTileBytes, &full[st]);
+                if (nm == 2)
+                    tma_bulk_g2s(dst + kPackedBytes + kXTileBytes, xsrc + ((size_t)G + i) * kXTileBytes, kXTileBytes, &full[st]);
                 if (++st == kTStages) { st = 0; if (i >= kTStages) par ^= 1u; }
             }
         }
     } else if (warp == 1) {
         // ---------------------------------------------------------------- MMA issue
         if (lane == 0) {
-            // instruction descriptor: D fp32, A and B bf16, both K-major, N = 256, M = 128
+            // instruction descriptor: D fp32, A and B bf16, both K-major, N = TN, M = 128
             const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kTileN >> 3) << 17) | ((uint32_t)(kTileM >> 4) << 24);
             int st = 0;
             uint32_t ph = 0;
@@ -126,21 +149,26 @@ __global__ void __launch_bounds__(kTileThreads, 1) w4_tile_kernel(const TilePara
             for (int i = 0; i < G && ok; i++) {
                 if (!mbar_wait(&full[st], ph) || !mbar_wait(&wready[st], ph)) { ok = false; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t a0 = smem_u32(smem + (size_t)st * kTStageBytes + kPackedStep);
-                const uint32_t b0 = a0 + kXTileBytes;
+                const uint32_t a0 = smem_u32(smem + (size_t)st * kTStageBytes + kPackedBytes);
+                const uint32_t b0 = a0 + ML * kXTileBytes;
 #pragma unroll
                 for (int kk = 0; kk < 4; kk++) {   // K = 16 per instruction = two 16-byte units along K
-                    const uint64_t da = umma_desc(a0 + kk * 2 * (kTileM * 16), kTileM * 16, 128);
                     const uint64_t db = umma_desc(b0 + kk * 2 * (kTileN * 16), kTileN * 16, 128);
                     const uint32_t accumulate = (i > 0 || kk > 0) ? 1u : 0u;
                     const uint32_t zero = 0u;   // (no output lane disabled)
-                    asm volatile(
-                        "{\n\t"
-                        ".reg .pred p;\n\t"
-                        "setp.ne.b32 p, %4, 0;\n\t"
-                        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t"
-                        "}\n" ::"r"(tmem), "l"(da), "l"(db), "r"(idesc), "r"(accumulate), "r"(zero)
-                        : "memory");
+#pragma unroll
+                    for (int mi = 0; mi < ML; mi++) {   // accumulator mi: columns mi TN .. of tensor memory
+                        if (mi < nm) {
+                            const uint64_t da = umma_desc(a0 + mi * kXTileBytes + kk * 2 * (kTileM * 16), kTileM * 16, 128);
+                            asm volatile(
+                                "{\n\t"
+                                ".reg .pred p;\n\t"
+                                "setp.ne.b32 p, %4, 0;\n\t"
+                                "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t"
+                                "}\n" ::"r"(tmem + (uint32_t)(mi * TN)), "l"(da), "l"(db), "r"(idesc), "r"(accumulate), "r"(zero)
+                                : "memory");
+                        }
+                    }
                 }
                 // the stage may be refilled once these MMAs have read it (the commit also fences the issue order)
                 asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(&freeb[st]))
@@ -152,9 +180,16 @@ __global__ void __launch_bounds__(kTileThreads, 1) w4_tile_kernel(const TilePara
                          : "memory");
         }
     } else {
-        // ---------------------------------------------------------------- dequantisers (256 threads)
-        const int dt = threadIdx.x - 64;          // 0..255
-        const int j = dt >> 5;                    // 32-row block of the superblock
+        // ---------------------------------------------------------------- dequantisers (256 threads: warps 2..9)
+        // A chunk of 32 rows x 64 columns is 2 (s: 16 rows) x 4 (q: 16 columns) words per lane; with TN = 256 a warp
+        // takes a whole chunk, with TN = 64 four warps share one: (s, two values of q) each.
+        constexpr int kSplit = Cfg::kSplit;
+        const int dw = (threadIdx.x - 64) >> 5;   // 0..7
+        const int j = dw / kSplit;                // 32-row chunk of this CTA's rows
+        const int sub = dw % kSplit;
+        const int s_lo = kSplit == 1 ? 0 : (sub >> 1), s_hi = kSplit == 1 ? 2 : s_lo + 1;
+        const int q_lo = kSplit == 1 ? 0 : 2 * (sub & 1);
+        constexpr int kQ = kSplit == 1 ? 4 : 2;
         const int g = lane >> 2, t = lane & 3;
         int st = 0;
         uint32_t ph = 0;
@@ -163,18 +198,23 @@ __global__ void __launch_bounds__(kTileThreads, 1) w4_tile_kernel(const TilePara
             if (!mbar_wait(&full[st], ph)) { ok = false; break; }
             const uint8_t* stage = smem + (size_t)st * kTStageBytes;
             const uint8_t* ch = stage + j * 1152;
-            uint8_t* wd = smem + (size_t)st * kTStageBytes + kPackedStep + kXTileBytes;
+            uint8_t* wd = smem + (size_t)st * kTStageBytes + kPackedBytes + ML * kXTileBytes;
             const uint4 sb4 = *reinterpret_cast<const uint4*>(ch + 1024 + g * 16);   // (scale | bias << 16) of 4 rows
-            const uint32_t sbw[4] = {sb4.x, sb4.y, sb4.z, sb4.w};
 #pragma unroll
-            for (int s = 0; s < 2; s++) {
-                const uint4 wv = *reinterpret_cast<const uint4*>(ch + s * 512 + lane * 16);
-                const uint32_t wq[4] = {wv.x, wv.y, wv.z, wv.w};
+            for (int s = s_lo; s < s_hi; s++) {
+                uint32_t wq[kQ];
+                if constexpr (kQ == 4) {
+                    const uint4 wv = *reinterpret_cast<const uint4*>(ch + s * 512 + lane * 16);
+                    wq[0] = wv.x, wq[1] = wv.y, wq[2] = wv.z, wq[3] = wv.w;
+                } else {
+                    const uint2 wv = *reinterpret_cast<const uint2*>(ch + s * 512 + lane * 16 + q_lo * 4);
+                    wq[0] = wv.x, wq[1] = wv.y;
+                }
                 // rows n0 = 32 j + 16 s + g and n0 + 8; their scale / bias as bf16 pairs
                 __nv_bfloat162 sc2[2], bi2[2];
 #pragma unroll
                 for (int h = 0; h < 2; h++) {
-                    const uint32_t wsb = sbw[2 * s + h];
+                    const uint32_t wsb = s ? (h ? sb4.w : sb4.z) : (h ? sb4.y : sb4.x);
                     const uint32_t ss = (wsb & 0xFFFFu) | (wsb << 16), bb = (wsb >> 16) | (wsb & 0xFFFF0000u);
                     sc2[h] = *reinterpret_cast<const __nv_bfloat162*>(&ss);
                     bi2[h] = *reinterpret_cast<const __nv_bfloat162*>(&bb);
@@ -182,11 +222,12 @@ __global__ void __launch_bounds__(kTileThreads, 1) w4_tile_kernel(const TilePara
                 const uint32_t c128 = 0x43004300u;
                 const __nv_bfloat162 k128 = *reinterpret_cast<const __nv_bfloat162*>(&c128);
 #pragma unroll
-                for (int q = 0; q < 4; q++) {
+                for (int qi = 0; qi < kQ; qi++) {
+                    const int q = q_lo + qi;
                     // register i of the word: (row n0 + 8 (i & 1), columns 16 q + 8 (i >> 1) + 2 t, + 1) as 128 + code
 #pragma unroll
                     for (int r = 0; r < 4; r++) {
-                        const uint32_t au = ((wq[q] >> (4 * r)) & 0x000F000Fu) | 0x43004300u;
+                        const uint32_t au = ((wq[qi] >> (4 * r)) & 0x000F000Fu) | 0x43004300u;
                         const __nv_bfloat162 u2 = __hsub2(*reinterpret_cast<const __nv_bfloat162*>(&au), k128);   // exact
                         const __nv_bfloat162 v2 = __hfma2(u2, sc2[r & 1], bi2[r & 1]);                            // one rounding
                         const int n = 32 * j + 16 * s + g + 8 * (r & 1);
@@ -204,15 +245,16 @@ __global__ void __launch_bounds__(kTileThreads, 1) w4_tile_kernel(const TilePara
         if (warp >= 4 && warp < 8) {
             if (ok && mbar_wait(accdone, 0)) {
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const int m = mt * kTileM + (warp & 3) * 32 + lane;
-                const uint32_t taddr = tmem + ((uint32_t)((warp & 3) * 32) << 16);
+                for (int mi = 0; mi < nm; mi++)
                 for (int c0 = 0; c0 < kTileN; c0 += 8) {
+                    const int m = (mt + mi) * kTileM + (warp & 3) * 32 + lane;
+                    const uint32_t taddr = tmem + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)(mi * TN);
                     uint32_t r[8];
                     asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
                                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
                                  : "r"(taddr + (uint32_t)c0));
                     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                    const int n = sb * kTileN + c0;
+                    const int n = n_base + c0;
                     if (m < p.M && n < p.N) {
                         __nv_bfloat16* dst = p.y + (size_t)m * p.ldy + n;
                         if (n + 8 <= p.N && ((((size_t)m * p.ldy + n) & 7) == 0)) {
@@ -237,7 +279,7 @@ __global__ void __launch_bounds__(kTileThreads, 1) w4_tile_kernel(const TilePara
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     if (warp == 1) {
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(256u) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(Cfg::kCols) : "memory");
     }
     if (threadIdx.x == 0 && s_fail) vk_set_status(VK_ST_MBAR_TIMEOUT);
 }
@@ -245,6 +287,14 @@ __global__ void __launch_bounds__(kTileThreads, 1) w4_tile_kernel(const TilePara
 }  // namespace
 
 extern "C" {
+
+// Test and tuning hook: force the tile shape (weight rows per CTA 256 / 64, activation-row tiles per CTA 1 / 2); 0 = automatic.
+int vk_w4_tile_force(int tn, int ml) {
+    if ((tn != 0 && tn != 64 && tn != 256) || ml < 0 || ml > 2) return VK_EINVAL;
+    g_tile_force_tn = tn;
+    g_tile_force_ml = ml;
+    return VK_OK;
+}
 
 // Bytes of scratch vk_w4_gemm_tile needs for the re-arranged activations.
 size_t vk_w4_tile_workspace_bytes(int M, int K) {
@@ -260,13 +310,27 @@ int vk_w4_gemm_tile(const void* packed, const void* x, int ldx, void* y, int ldy
     if (workspace_bytes < vk_w4_tile_workspace_bytes(M, K)) return VK_ENOSPC;
     static bool configured = false;
     if (!configured) {
-        VK_CUDA(cudaFuncSetAttribute(w4_tile_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kTileSmem));
+        VK_CUDA((cudaFuncSetAttribute(w4_tile_kernel<256, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TileCfg<256, 1>::kSmem)));
+        VK_CUDA((cudaFuncSetAttribute(w4_tile_kernel<256, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TileCfg<256, 2>::kSmem)));
+        VK_CUDA((cudaFuncSetAttribute(w4_tile_kernel<64, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TileCfg<64, 1>::kSmem)));
+        VK_CUDA((cudaFuncSetAttribute(w4_tile_kernel<64, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TileCfg<64, 2>::kSmem)));
         configured = true;
     }
-    const int G = K / 64, MTn = (M + kTileM - 1) / kTileM, NSB = (N + kTileN - 1) / kTileN;
+    const int G = K / 64, MTn = (M + kTileM - 1) / kTileM, NSB = (N + 255) / 256;
     VK_CUDA(vk_launch(w4_xtile_kernel, dim3(G, MTn), dim3(128), 0, stream, (const __nv_bfloat16*)x, ldx, M, G, (uint8_t*)workspace));
     TileParams p = {(const uint8_t*)packed, (const uint8_t*)workspace, (__nv_bfloat16*)y, M, N, G, ldy};
-    return (int)vk_launch(w4_tile_kernel, dim3(NSB, MTn), dim3(kTileThreads), kTileSmem, stream, p);
+    // Two tiles of activation rows per CTA when there are two; whole superblocks per CTA when that still gives at
+    // least one CTA per two SMs, quarters of a superblock otherwise.
+    const int ml = g_tile_force_ml ? g_tile_force_ml : (MTn >= 2 ? 2 : 1);
+    const int gy = (MTn + ml - 1) / ml;
+    const int tn = g_tile_force_tn ? g_tile_force_tn : (NSB * gy >= 74 ? 256 : 64);
+    if (tn == 256 && ml == 2)
+        return (int)vk_launch(w4_tile_kernel<256, 2>, dim3(NSB, gy), dim3(kTileThreads), TileCfg<256, 2>::kSmem, stream, p);
+    if (tn == 256)
+        return (int)vk_launch(w4_tile_kernel<256, 1>, dim3(NSB, gy), dim3(kTileThreads), TileCfg<256, 1>::kSmem, stream, p);
+    if (ml == 2)
+        return (int)vk_launch(w4_tile_kernel<64, 2>, dim3(NSB * 4, gy), dim3(kTileThreads), TileCfg<64, 2>::kSmem, stream, p);
+    return (int)vk_launch(w4_tile_kernel<64, 1>, dim3(NSB * 4, gy), dim3(kTileThreads), TileCfg<64, 1>::kSmem, stream, p);
 }
 
 }  // extern "C"

@@ -63,7 +63,12 @@ def main():
     ap.add_argument("--launches", type=int, default=12)
     ap.add_argument("--replays", type=int, default=5)
     ap.add_argument("--tile", action="store_true", help="use vk_w4_gemm_tile (tcgen05, for many rows)")
+    ap.add_argument("--tile-shape", default="0,0", help="force the tile kernel's weight rows per CTA and row tiles per CTA")
     a = ap.parse_args()
+    if a.tile:
+        from . import _lib
+        tn, ml = (int(v) for v in a.tile_shape.split(","))
+        _lib.check(_lib.lib().vk_w4_tile_force(tn, ml), "vk_w4_tile_force")
     copies = a.copies or max(2, int(400e6 // (a.n * a.k * 0.5625)) + 1)
     print(json.dumps(run(a.m, a.n, a.k, copies, a.launches, a.replays, tile=a.tile)))
 
