@@ -12,6 +12,10 @@ class FakeCache:
         self.greedy = torch.zeros(S, dtype=torch.int32)
 
     @property
+    def _pos(self):
+        return [len(self.hist[k]) for k in self.keys]
+
+    @property
     def B(self):
         return len(self.keys)
 
@@ -85,3 +89,50 @@ def test_engine_waits_for_pages(monkeypatch):
     assert list(eng.running) == [a] and len(eng.waiting) == 1
     out = eng.run()
     assert out[a] == solo(list(range(1, 100)), 20) and out[b] == solo([1, 2], 2)
+
+
+def fake_forward_chunk(model, bc, toks, write=False):
+    """The chunk interface on the fake cache: greedy[b][t] follows the row's history plus its first t + 1 tokens;
+    write=True keeps all of them, otherwise commit_chunk keeps each row's own count."""
+    B, T = len(toks), len(toks[0])
+    assert B == bc.B and all(len(t) == T for t in toks)
+    greedy = torch.zeros((B, T), dtype=torch.int32)
+    for b, k in enumerate(bc.keys):
+        for t in range(T):
+            greedy[b, t] = fake_next(bc.hist[k] + [int(x) for x in toks[b][: t + 1]])
+    if write:
+        for b, k in enumerate(bc.keys):
+            bc.hist[k] += [int(x) for x in toks[b]]
+        return None, greedy, None
+    return None, greedy, toks
+
+
+def fake_commit_chunk(model, bc, handle, accepted):
+    for b, k in enumerate(bc.keys):
+        assert 0 <= accepted[b] <= len(handle[b])
+        bc.hist[k] += [int(x) for x in handle[b][: accepted[b]]]
+
+
+def test_engine_ragged_prefill_chunks(monkeypatch):
+    """Prompts fed in chunks of up to 4 tokens per row while other rows decode: every request still gets its solo
+    output, prompt tokens go through chunk steps, and a chunk never outgrows a row's page table or the pool."""
+    monkeypatch.setattr(E.BT, "forward", fake_forward)
+    monkeypatch.setattr(E.CH, "forward_chunk", fake_forward_chunk)
+    monkeypatch.setattr(E.CH, "commit_chunk", fake_commit_chunk)
+    eng = E.BatchEngine(FakeModel(), max_rows=3, n_pages=6, max_pages_per_row=2, prefill_chunk=4)
+    reqs = [([5, 6, 7], 4), ([1], 9), ([9, 8, 7, 6, 5, 4, 3], 2), ([2, 2], 1), ([3, 1, 4, 1, 5], 6), (list(range(1, 70)), 3),
+            (list(range(1, 126)), 3)]
+    keys = [eng.submit(p, n) for p, n in reqs]
+    steps = 0
+    while eng.waiting or eng.running:
+        eng.step()
+        steps += 1
+        assert all(p <= 2 * E.PAGE for p in eng.bc._pos)
+        assert steps < 500
+        if all(r.done for r in eng.running.values()) and not eng.waiting:
+            break
+    out = eng.run()
+    for k, (p, n) in zip(keys, reqs):
+        assert out[k] == solo(p, n), k
+    assert eng.chunk_steps >= (69 + 125) // 4 // 3
+    assert steps < sum(len(p) + n for p, n in reqs) // 3     # far fewer steps than one token per step would take

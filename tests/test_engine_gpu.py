@@ -40,3 +40,48 @@ def test_engine_equals_solo_runs():
             want.append(int(one.greedy[0]))
         assert out[k] == want, k
     ops.check_status()
+
+
+def test_engine_prefill_chunks():
+    """The same requests with prompts fed in ragged chunks of up to 32 tokens per row (engine.BatchEngine with
+    prefill_chunk: one pass over the weights per chunk, decoding rows ride along with one token) against the solo
+    stepwise runs. The chunk path's GEMMs round differently from the decode step's, so the tokens must agree up to the
+    first near-tie: where a request's tokens first differ, the token the engine chose must lie within 0.05 of the
+    maximum of the stepwise logits at that position (the bf16 bar 2e-2 on logits of magnitude about one, twice)."""
+    if not torch.cuda.is_available():
+        pytest.skip("needs a GPU")
+    from volundr_mlx_b200 import batch as BT, ops
+    from volundr_mlx_b200.engine import BatchEngine
+    from volundr_mlx_b200.volundr import Model
+
+    cuda = torch.device("cuda", 0)
+    args = synth.small_args(bcsa_far="tokens", bcsa_score="pooled_key", bcsa_window=128, bcsa_compress=64, bcsa_topk=2)
+    params = synth.make_params(args, seed=22)
+    model = Model(args, params, cuda)
+    rng = np.random.default_rng(22)
+    reqs = [(rng.integers(0, args.vocab_valid, size=n).tolist(), m)
+            for n, m in [(70, 12), (3, 20), (130, 5), (1, 8), (33, 9), (64, 30)]]
+    eng = BatchEngine(model, max_rows=3, n_pages=24, max_pages_per_row=4, prefill_chunk=32)
+    keys = [eng.submit(p, m) for p, m in reqs]
+    out = eng.run()
+    ops.check_status()
+    assert eng.chunk_steps >= 6        # (70 + 130 + 33 + 64 prompt tokens cannot go through fewer chunks of 32)
+    same = 0
+    for k, (prompt, m) in zip(keys, reqs):
+        assert len(out[k]) == m
+        one = model.make_cache(max_rows=1, n_pages=8, max_pages_per_row=4)
+        one.apply(join=["x"])
+        for t in prompt:
+            lg, _ = BT.forward(model, one, [t])
+        for j in range(m):
+            lg = lg[0].float()
+            want = int(one.greedy[0])
+            if out[k][j] != want:
+                assert float(lg.max() - lg[out[k][j]]) < 0.05, (k, j, float(lg.max() - lg[out[k][j]]))
+                break
+            if j + 1 < m:
+                lg, _ = BT.forward(model, one, [want])
+        else:
+            same += 1
+    assert same >= len(reqs) // 2, same
+    ops.check_status()

@@ -79,8 +79,13 @@ _scratch = {}
 
 
 def _get_scratch(model, bc, R):
+    """The scratch of the last few row counts (an engine that feeds prompts meets a handful of them)."""
     key = (id(model), id(bc), R)
-    if key not in _scratch:
+    if key in _scratch:
+        _scratch[key] = _scratch.pop(key)            # most recently used last
+    else:
+        while len(_scratch) >= 4:
+            _scratch.pop(next(iter(_scratch)))
         _scratch[key] = ChunkScratch(model, bc, R)
     return _scratch[key]
 
@@ -132,14 +137,13 @@ def forward_chunk(model, bc, toks, write=False):
         s.engram_prev.copy_(window.unfold(1, bc.keep, 1)[:, :T].reshape(R, bc.keep))
     ws = ops.workspace(max(1 << 26, L.vk_w4_workspace_bytes(R, max(w["gate_up"].N for w in model.layers), D)), dev)
 
-    tile_ws = ops.workspace(1 << 26, dev) if R < 64 else None
+    tile_ws = None
     if R >= 64:
         kmax = max(max(w[nm].K for nm in ("proj", "out", "gate_up", "down")) for w in model.layers)
         tile_ws = torch.empty(L.vk_w4_tile_workspace_bytes(R, kmax), dtype=torch.uint8, device=dev)
 
     def gemm(x, wt, y):
-        # 64 rows and more, and a weight with enough 256-row tiles to fill the GPU: the tcgen05 tile kernel; otherwise
-        # the streaming kernel's wide passes
+        # 64 rows and more: the tcgen05 tile kernel; fewer: the streaming kernel's passes
         if R >= 64:
             ck(L.vk_w4_gemm_tile(_p(wt.packed), _p(x), x.stride(0), _p(y), y.stride(0), R, wt.N, wt.K, _p(tile_ws),
                                  tile_ws.numel(), st), "vk_w4_gemm_tile")

@@ -1,9 +1,15 @@
 """A small continuous-batching engine on the batched decode step: admission by free rows and pages, rows that join and
-leave between steps, prompts fed through the same step as decoding rows, greedy sampling (the part of
-scheduler.BatchEngine, scheduler.py:72-560, that drives batch.forward: admission :180-239, the step :300-420, greedy
-:391, retirement :430-470). Prompts go through the decode path one token per step and row (there is no prefill tile
-yet), so this is about behaviour, not prompt throughput: a request's tokens are exactly those it gets alone, whatever
-shares the batch with it.
+leave between steps, greedy sampling (the part of scheduler.BatchEngine, scheduler.py:72-560, that drives batch.forward:
+admission :180-239, the step :300-420, greedy :391, retirement :430-470).
+
+Prompts: with prefill_chunk <= 1 every prompt token takes one decode step of its row, and a request's tokens are
+exactly those it gets alone, whatever shares the batch with it. With prefill_chunk = T > 1 a step in which some row
+still has two or more prompt tokens to feed runs as one ragged chunk through volundr_mlx_b200.chunk: every row brings
+up to T tokens (prompt rows their next tokens, decoding rows their single next token, padded to the same length), the
+chunk runs as a verify pass and the commit keeps exactly each row's own count (the reference feeds prompts in chunks
+through session.prefill_iter, session.py:351-387, one request at a time). The weights are then read once per chunk
+instead of once per prompt token. The chunk path's GEMMs round differently from the decode step's (within the bf16
+bar), so tokens can differ from the stepwise engine at near-ties of the logits.
 """
 from __future__ import annotations
 
@@ -13,6 +19,7 @@ from dataclasses import dataclass, field
 import torch
 
 from . import batch as BT
+from . import chunk as CH
 
 PAGE = BT.PAGE
 
@@ -31,8 +38,10 @@ class Request:
 
 
 class BatchEngine:
-    def __init__(self, model, max_rows=16, n_pages=4096, max_pages_per_row=512):
+    def __init__(self, model, max_rows=16, n_pages=4096, max_pages_per_row=512, prefill_chunk=0):
         self.model = model
+        self.prefill_chunk = int(prefill_chunk) if getattr(model, "tp_size", 1) == 1 else 0   # (the chunk path is not sharded)
+        self.chunk_steps = 0
         self.bc = model.make_cache(max_rows=max_rows, n_pages=n_pages, max_pages_per_row=max_pages_per_row)
         self.n_pages, self.max_pages_per_row = n_pages, max_pages_per_row
         self.waiting: deque = deque()
@@ -78,6 +87,9 @@ class BatchEngine:
         if not self.bc.B:
             return []
         rows = [self.running[k] for k in self.bc.keys]
+        T = self._chunk_len(rows)
+        if T > 1:
+            return self._chunk_step(rows, T)
         toks = [r.prompt[r.fed] if r.fed < len(r.prompt) else r.out[-1] for r in rows]
         BT.forward(self.model, self.bc, toks)
         greedy = self.bc.greedy[: self.bc.B].tolist()   # (one small device-to-host read per step)
@@ -87,6 +99,41 @@ class BatchEngine:
             if r.fed >= len(r.prompt):   # the token after the last one fed
                 r.out.append(int(g))
                 produced.append((r.key, int(g)))
+        return produced
+
+    def _chunk_len(self, rows) -> int:
+        """Tokens per row of the next step: more than one only while a prompt has two or more tokens left, and only as
+        many as every row's page table and the page pool can take (padding positions open pages until the commit)."""
+        if self.prefill_chunk <= 1:
+            return 1
+        left = max(len(r.prompt) - r.fed for r in rows)
+        T = min(self.prefill_chunk, left)
+        pos = self.bc._pos
+        T = min([T] + [self.max_pages_per_row * PAGE - p for p in pos])
+        while T > 1 and sum((p + T + PAGE - 1) // PAGE for p in pos) > self.n_pages:
+            T //= 2
+        return max(T, 1)
+
+    def _chunk_step(self, rows, T):
+        toks, n = [], []
+        for r in rows:
+            own = r.prompt[r.fed: r.fed + T] if r.fed < len(r.prompt) else [r.out[-1]]
+            n.append(len(own))
+            toks.append(list(own) + [0] * (T - len(own)))
+        if all(k == T for k in n):
+            _, greedy, _ = CH.forward_chunk(self.model, self.bc, toks, write=True)
+        else:
+            _, greedy, h = CH.forward_chunk(self.model, self.bc, toks, write=False)
+            CH.commit_chunk(self.model, self.bc, h, n)
+        greedy = greedy.tolist()
+        self.chunk_steps += 1
+        produced = []
+        for b, r in enumerate(rows):
+            r.fed += n[b]
+            if r.fed >= len(r.prompt):
+                g = int(greedy[b][n[b] - 1])
+                r.out.append(g)
+                produced.append((r.key, g))
         return produced
 
     def run(self, max_steps=1_000_000):
