@@ -28,7 +28,8 @@ namespace {
 constexpr int kTileM = 128;                    // activation rows per CTA = accumulator lanes
 constexpr int kPackedStep = 9216;              // bytes of one (superblock, group) of packed weights
 constexpr int kXTileBytes = kTileM * 64 * 2;   // 16 KB: [8][128][8] bf16
-constexpr int kTileThreads = 320;
+constexpr int kDqWarps = 8;                    // dequantiser warps (16 measured the same: the kernel is not bound by them)
+constexpr int kTileThreads = 64 + 32 * kDqWarps;
 // Weight rows per CTA = accumulator columns: TN = 256 (a whole superblock) for weights with many rows; TN = 64 (a
 // quarter: two of the superblock's eight 32-row chunks) for weights whose 256-row tiles would not fill the GPU.
 // ML = tiles of 128 activation rows per CTA (1 or 2): with two, every dequantised weight tile feeds two accumulators,
@@ -38,7 +39,7 @@ template <int TN, int ML> struct TileCfg {
     static constexpr int kWd = TN * 64 * 2;                  // dequantised tile [8][TN][8] bf16
     static constexpr int kStage = kPacked + ML * kXTileBytes + kWd;
     static constexpr int kStages = (220 * 1024 / kStage) < 6 ? (220 * 1024 / kStage) : 6;
-    static constexpr int kSplit = 256 / TN;                  // dequantiser threads per (chunk, lane): all 256 threads work
+    static constexpr int kSplit = kDqWarps / (TN / 32);      // dequantiser warps per 32-row chunk: all of them work
     static constexpr int kBarBytes = (3 * kStages + 1) * 8;  // full / wready / freeb per stage + accdone
     static constexpr size_t kSmem = (size_t)kStages * kStage + ((kBarBytes + 127) / 128) * 128;
     static_assert(kSmem <= 227 * 1024, "stages do not fit the CTA's shared memory");
@@ -86,7 +87,7 @@ __global__ void __launch_bounds__(kTileThreads, 1) w4_tile_kernel(const TilePara
     constexpr int kPackedBytes = Cfg::kPacked;
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (size_t)kTStages * kTStageBytes);
     uint64_t* full = bars;                   // [stage] packed weights + activation tile have landed (TMA bytes)
-    uint64_t* wready = bars + kTStages;      // [stage] dequantised weights are in place (256 arrivals)
+    uint64_t* wready = bars + kTStages;      // [stage] dequantised weights are in place (every dequantiser thread arrives)
     uint64_t* freeb = bars + 2 * kTStages;   // [stage] the stage's MMAs have finished reading it
     uint64_t* accdone = bars + 3 * kTStages; // the whole accumulation has finished
     __shared__ uint32_t s_tmem;
@@ -101,7 +102,7 @@ __global__ void __launch_bounds__(kTileThreads, 1) w4_tile_kernel(const TilePara
     if (threadIdx.x == 0) {
         for (int s = 0; s < kTStages; s++) {
             mbar_init(&full[s], 1);
-            mbar_init(&wready[s], 256);
+            mbar_init(&wready[s], 32 * kDqWarps);
             mbar_init(&freeb[s], 1);
         }
         mbar_init(accdone, 1);
@@ -180,16 +181,18 @@ __global__ void __launch_bounds__(kTileThreads, 1) w4_tile_kernel(const TilePara
                          : "memory");
         }
     } else {
-        // ---------------------------------------------------------------- dequantisers (256 threads: warps 2..9)
-        // A chunk of 32 rows x 64 columns is 2 (s: 16 rows) x 4 (q: 16 columns) words per lane; with TN = 256 a warp
-        // takes a whole chunk, with TN = 64 four warps share one: (s, two values of q) each.
+        // ---------------------------------------------------------------- dequantisers (warps 2 ..)
+        // A chunk of 32 rows x 64 columns is 2 (s: 16 rows) x 4 (q: 16 columns) words per lane, shared by the kSplit
+        // warps of the chunk: one warp takes all eight words, two take one s each, four (s, two q), eight (s, q).
         constexpr int kSplit = Cfg::kSplit;
-        const int dw = (threadIdx.x - 64) >> 5;   // 0..7
+        static_assert(kSplit == 1 || kSplit == 2 || kSplit == 4 || kSplit == 8, "dequantiser warps per chunk");
+        constexpr int kQ = kSplit == 1 ? 4 : 8 / kSplit;          // words of one s per thread
+        constexpr int kPerS = kSplit == 1 ? 1 : kSplit / 2;        // warps that share one s
+        const int dw = (threadIdx.x - 64) >> 5;   // 0 .. kDqWarps - 1
         const int j = dw / kSplit;                // 32-row chunk of this CTA's rows
         const int sub = dw % kSplit;
-        const int s_lo = kSplit == 1 ? 0 : (sub >> 1), s_hi = kSplit == 1 ? 2 : s_lo + 1;
-        const int q_lo = kSplit == 1 ? 0 : 2 * (sub & 1);
-        constexpr int kQ = kSplit == 1 ? 4 : 2;
+        const int s_lo = kSplit == 1 ? 0 : sub / kPerS, s_hi = kSplit == 1 ? 2 : s_lo + 1;
+        const int q_lo = (sub % kPerS) * kQ;
         const int g = lane >> 2, t = lane & 3;
         int st = 0;
         uint32_t ph = 0;
@@ -206,9 +209,11 @@ __global__ void __launch_bounds__(kTileThreads, 1) w4_tile_kernel(const TilePara
                 if constexpr (kQ == 4) {
                     const uint4 wv = *reinterpret_cast<const uint4*>(ch + s * 512 + lane * 16);
                     wq[0] = wv.x, wq[1] = wv.y, wq[2] = wv.z, wq[3] = wv.w;
-                } else {
+                } else if constexpr (kQ == 2) {
                     const uint2 wv = *reinterpret_cast<const uint2*>(ch + s * 512 + lane * 16 + q_lo * 4);
                     wq[0] = wv.x, wq[1] = wv.y;
+                } else {
+                    wq[0] = *reinterpret_cast<const uint32_t*>(ch + s * 512 + lane * 16 + q_lo * 4);
                 }
                 // rows n0 = 32 j + 16 s + g and n0 + 8; their scale / bias as bf16 pairs
                 __nv_bfloat162 sc2[2], bi2[2];
@@ -242,6 +247,7 @@ __global__ void __launch_bounds__(kTileThreads, 1) w4_tile_kernel(const TilePara
         }
         if (!ok) s_fail = 1;
         // ---------------------------------------------------------------- epilogue (warps 4..7: lanes 32 (warp % 4) ..)
+        static_assert(kDqWarps >= 6, "warps 4..7 read the accumulator");
         if (warp >= 4 && warp < 8) {
             if (ok && mbar_wait(accdone, 0)) {
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
