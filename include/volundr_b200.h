@@ -135,8 +135,9 @@ int vk_argmax_merge(const int* pairs, int n_ranks, int* out, int B, vk_stream_t 
 /* ---- Tensor-parallel exchange inside the consuming kernel (no counterpart in the single-GPU reference). The ranks of
  * one node hold partial products of the row-parallel linears (out_proj / o_proj, down_proj). Instead of a separate
  * all-reduce, the kernel that consumes the sum (vk_add_rmsnorm_ar, vk_mhc_boundary_ar, vk_mhc_combine_norm_ar: one CTA
- * per row) pushes its partial row into every peer's region with peer stores, raises a flag there, waits (bounded) for
- * the peers' flags and adds the rows in rank order; the bf16 sum replaces the partial row in `r` / `m`, which is
+ * per row) pushes its partial row into every peer's region with peer stores (every 8-byte unit = 4 bytes of data + the
+ * call's sequence number, so neither a fence nor a flag follows), polls (bounded) its own region until the peers'
+ * units carry that number and adds the rows in rank order; the bf16 sum replaces the partial row in `r` / `m`, which is
  * therefore not const. Set-up per rank: vk_ar_alloc a region of vk_ar_region_bytes, pass the 64-byte handle to the
  * other ranks (any host channel), vk_ar_open theirs, vk_ar_fill the descriptor, synchronise the ranks once (host
  * barrier) before the first step. Per step: `call` = 0 .. calls_per_step - 1 in the same order on every rank, then
@@ -146,7 +147,7 @@ typedef struct vk_ar_desc {
     int world, rank, rows, row_elems, calls_per_step;
     unsigned spin_limit;   /* polls (>= 100 ns each) before a wait gives up; vk_ar_fill sets a default of seconds */
     void* slots[8];
-    int* flags[8];
+    int* flags[8];         /* (header of each region; the kernels do not use it) */
     int* step;
 } vk_ar_desc;
 size_t vk_ar_region_bytes(int world, int rows, int D);   /* 0: unsupported (world <= 8, world * rows <= 252) */

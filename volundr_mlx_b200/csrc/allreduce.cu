@@ -10,9 +10,9 @@ __global__ void ar_advance_kernel(int* step) {
     if (threadIdx.x == 0) *step = *step + 1;
 }
 
-constexpr size_t kArHeader = 4096;   // flags [world][rows][4] int32 + the step counter live in the first 4 KB
+constexpr size_t kArHeader = 4096;   // the step counter (and an unused flag area) live in the first 4 KB
 
-inline size_t ar_slots_bytes(int world, int rows, int D) { return (size_t)kArSlots * world * rows * D * 2; }
+inline size_t ar_slots_bytes(int world, int rows, int D) { return (size_t)kArSlots * world * rows * D * 4; }
 
 }  // namespace
 

@@ -3,17 +3,21 @@
 // ranks hold partial products of the row-parallel linears; the reference is single-GPU and has no counterpart.
 //
 // Every rank owns one region of device memory that all ranks have mapped (CUDA IPC):
-//     flags [world][rows][4] int32     flags[src][b][part] = sequence number of the last push of rank `src` for that
-//                                      part of row b (a row is exchanged whole, part 0, or in up to four parts)
-//     slots [4][world][rows][D] bf16   slots[seq & 3][src][b] = the partial row that `src` pushed
-// The CTA that owns row b: (1) stores its partial row into every peer's slots[.][me][b] with plain peer stores over
-// NVLink, (2) system-fence, then writes the sequence number into every peer's flags[me][b], (3) waits - bounded - until
-// its own flags[p][b] carries the number for every peer p, (4) adds the `world` partial rows in rank order in fp32
-// (the same order on every rank: all ranks get the same bits) and leaves the bf16 sum in its local row.
+//     header                            the local step counter (and a flag area the kernels no longer use)
+//     slots [4][world][rows][D] lines   slots[seq & 3][src][b] = the partial row that `src` pushed, as 8-byte units
+//                                       {two bf16 of data, the push's sequence number}: 16-byte lines of two units
+// The sequence number travels WITH the data, so a push needs neither a fence nor a separate flag, and the receiver
+// needs one NVLink crossing, not a store + acknowledged fence + flag: the CTA that owns (a part of) row b
+// (1) stores its partial row into every peer's slots[.][me][b], one 16-byte volatile store per line (an aligned
+//     8-byte unit is never torn, so data and number of a unit arrive together),
+// (2) polls - bounded - its own slots[.][p][b] for every peer p until both units of a line carry this call's number
+//     (a slot still holds the number of four calls ago until the new line lands),
+// (3) adds the `world` partial rows in rank order in fp32 (the same order on every rank: all ranks get the same bits)
+//     and leaves the bf16 sum in its local row.
 // The sequence number is step * calls_per_step + call + 1 with `step` a device counter that vk_ar_advance bumps once
-// per decode step, so a captured CUDA graph can be replayed. A rank pushes call k + 1 only after it has seen every
-// peer's flag for call k, and a peer sets that flag only after the kernel of call k - 1 has finished reading, so two
-// slots would do; four are kept.
+// per decode step, so a captured CUDA graph can be replayed. A rank pushes call k + 1 only after it has read every
+// peer's lines of call k, and a peer can push call k + 4 into the same slot only after it has read this rank's lines
+// of calls k + 1 .. k + 3, which this rank pushes after reading call k: a line is never overwritten before it is read.
 // A wait that runs out sets VK_ST_FLAG_TIMEOUT and returns (the sum is then wrong, the host sees the status); once
 // the status word is set, later waits give up at once, so a lost peer costs one time-out and not one per call.
 #pragma once
@@ -48,7 +52,7 @@ struct VkArCall {              // kernel argument: descriptor + which call of th
 };
 
 __device__ __forceinline__ size_t ar_slot_off(const VkArDesc& d, int slot, int src, int b, int D) {
-    return ((((size_t)slot * d.world + src) * d.rows + b) * (size_t)D) * 2;
+    return ((((size_t)slot * d.world + src) * d.rows + b) * (size_t)D) * 4;   // (lines: twice the bf16 bytes)
 }
 
 // All threads of the CTA that owns part `part` of `nparts` (<= kArParts) equal parts of row b call this after
@@ -61,44 +65,45 @@ __device__ __forceinline__ void ar_reduce_row(const VkArCall& a, __nv_bfloat16* 
 __device__ __forceinline__ void ar_reduce_span(const VkArCall& a, __nv_bfloat16* row, int b, int D, int part, int nparts) {
     const VkArDesc& d = a.d;
     if (d.world <= 1) return;
-    const int seq = (int)((unsigned)*reinterpret_cast<volatile int*>(d.step) * (unsigned)d.calls_per_step + (unsigned)a.call + 1u);
-    const int slot = seq & (kArSlots - 1);
+    const uint32_t seq = (unsigned)*reinterpret_cast<volatile int*>(d.step) * (unsigned)d.calls_per_step + (unsigned)a.call + 1u;
+    const int slot = (int)(seq & (kArSlots - 1));
     const int nvec_part = (D / nparts) >> 3;
     const int v_begin = part * nvec_part, nvec = v_begin + nvec_part;
     uint4* rowv = reinterpret_cast<uint4*>(row);
+    // (1) push: every 16 bytes of the row become two lines {w0, seq, w1, seq}, {w2, seq, w3, seq} in every peer's region
     for (int v = v_begin + threadIdx.x; v < nvec; v += blockDim.x) {
         const uint4 val = rowv[v];
         for (int p = 0; p < d.world; p++) {
             if (p == d.rank) continue;
-            *reinterpret_cast<uint4*>(d.slots[p] + ar_slot_off(d, slot, d.rank, b, D) + (size_t)v * 16) = val;
+            uint4* dst = reinterpret_cast<uint4*>(d.slots[p] + ar_slot_off(d, slot, d.rank, b, D)) + 2 * (size_t)v;
+            asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %2};" ::"l"(dst), "r"(val.x), "r"(seq), "r"(val.y) : "memory");
+            asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %2};" ::"l"(dst + 1), "r"(val.z), "r"(seq), "r"(val.w) : "memory");
         }
     }
-    __threadfence_system();
-    __syncthreads();
-    const int t = threadIdx.x;
-    if (t < d.world && t != d.rank) {
-        int* remote = d.flags[t] + (d.rank * d.rows + b) * kArParts + part;
-        asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(remote), "r"(seq) : "memory");
-        const int* mine = d.flags[d.rank] + (t * d.rows + b) * kArParts + part;
-        int seen = 0;
-        bool ok = false;
-        if (*reinterpret_cast<volatile int*>(&g_vk_status) == 0) {
-            for (uint32_t it = 0; it < d.spin_limit; it++) {
-                asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(seen) : "l"(mine) : "memory");
-                if ((int)((unsigned)seen - (unsigned)seq) >= 0) { ok = true; break; }   // wrap-safe "seen >= seq"
-                __nanosleep(100);
-            }
-        }
-        if (!ok) vk_set_status(VK_ST_FLAG_TIMEOUT);
-    }
-    __syncthreads();
+    // (2) + (3): the same thread polls the lines of its own vectors (the peers' threads of the same index push them)
+    uint32_t budget = *reinterpret_cast<volatile int*>(&g_vk_status) == 0 ? d.spin_limit : 0u;
+    bool ok = true;
     const uint8_t* local = d.slots[d.rank];
     for (int v = v_begin + threadIdx.x; v < nvec; v += blockDim.x) {
         float s[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
         for (int p = 0; p < d.world; p++) {
             uint4 u;
-            if (p == d.rank) u = rowv[v];
-            else u = __ldcg(reinterpret_cast<const uint4*>(local + ar_slot_off(d, slot, p, b, D)) + v);
+            if (p == d.rank) {
+                u = rowv[v];
+            } else {
+                const uint4* src = reinterpret_cast<const uint4*>(local + ar_slot_off(d, slot, p, b, D)) + 2 * (size_t)v;
+                uint4 l0, l1;
+                uint32_t polls = 0;
+                for (;;) {
+                    asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(l0.x), "=r"(l0.y), "=r"(l0.z), "=r"(l0.w) : "l"(src) : "memory");
+                    asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(l1.x), "=r"(l1.y), "=r"(l1.z), "=r"(l1.w) : "l"(src + 1) : "memory");
+                    if (l0.y == seq && l0.w == seq && l1.y == seq && l1.w == seq) break;
+                    if (budget == 0) { ok = false; break; }   // give up: the host will see the status
+                    budget--;
+                    if (++polls > 32) __nanosleep(100);
+                }
+                u = make_uint4(l0.x, l0.z, l1.x, l1.z);
+            }
             s[0] += bf_lo(u.x); s[1] += bf_hi(u.x); s[2] += bf_lo(u.y); s[3] += bf_hi(u.y);
             s[4] += bf_lo(u.z); s[5] += bf_hi(u.z); s[6] += bf_lo(u.w); s[7] += bf_hi(u.w);
         }
@@ -106,5 +111,6 @@ __device__ __forceinline__ void ar_reduce_span(const VkArCall& a, __nv_bfloat16*
         o.x = pack_bf2(s[0], s[1]); o.y = pack_bf2(s[2], s[3]); o.z = pack_bf2(s[4], s[5]); o.w = pack_bf2(s[6], s[7]);
         rowv[v] = o;
     }
+    if (!ok) vk_set_status(VK_ST_FLAG_TIMEOUT);
     __syncthreads();
 }
