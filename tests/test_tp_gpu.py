@@ -57,6 +57,26 @@ def _worker(rank, world, port, out, fused):
                 if float(gap[r]) > 4e-2:
                     clear += 1
                     agree += int(int(bc.greedy[r]) == int(bc1.greedy[r]))
+        # the chunk path under tensor parallelism: 3 rows x 24 tokens (72 virtual rows: the tcgen05 tile GEMM on the
+        # shards, NCCL all-reduces of [72, hidden]) against the single-GPU chunk, then decode goes on from its state
+        from volundr_mlx_b200 import chunk as CH
+
+        toks = rng.integers(0, args.vocab_valid, size=(3, 24)).tolist()
+        lg, gr, _ = CH.forward_chunk(tp, bc, toks, write=True)
+        l1, g1, _ = CH.forward_chunk(ref, bc1, toks, write=True)
+        a, b = lg.float(), l1.float()[:, :, v0:v0 + lg.shape[2]]
+        worst = max(worst, float((a - b).abs().max() / l1.float().abs().max()))
+        shards = [torch.empty_like(lg) for _ in range(world)]
+        dist.all_gather(shards, lg.contiguous())
+        full = torch.cat(shards, dim=2)[:, :, :args.vocab_valid].float()
+        chunk_ok = int(torch.equal(gr.long(), full.argmax(dim=2)))
+        for t in range(4):
+            toks = rng.integers(0, args.vocab_valid, size=3).tolist()
+            lg, _ = BT.forward(tp, bc, toks)
+            l1, _ = BT.forward(ref, bc1, toks)
+            a, b = lg.float(), l1.float()[:, v0:v0 + lg.shape[1]]
+            worst = max(worst, float((a - b).abs().max() / l1.float().abs().max()))
+        merged_ok += chunk_ok - 1          # (30 stays the expected count when the chunk's merged tokens are right)
         ops.check_status()
         out.put((rank, worst, merged_ok, agree, clear))
         out.close()

@@ -14,7 +14,10 @@ keep are simply never reached), the KDA state and the Engram window stay as they
 (the KDA layers' inputs) is kept. commit_chunk(accepted) replays the KDA recurrence over the accepted prefix of every
 row (vk_kda_chunk with `accept`), moves the Engram window, returns pages opened for rejected positions and advances
 the positions. forward_chunk(..., write=True) commits all T tokens at once (a prefill chunk).
-Tensor-parallel sharding is not wired into this path yet.
+Tensor parallel: the shards' partial products of out_proj / o_proj and down_proj ([R, hidden] bf16, megabytes at
+R in the hundreds) are summed with NCCL all-reduces between the kernels (bandwidth-bound at this size, unlike the
+decode step's 160 KB exchanges, which live inside the consuming kernels); logits come back as the rank's vocabulary
+shard, greedy tokens from per-rank (max, index) pairs, all-gathered and merged.
 """
 from __future__ import annotations
 
@@ -50,6 +53,8 @@ class ChunkScratch:
         self.act = torch.zeros((R, model.I), **bf)
         self.logits = torch.zeros((R, model.vocab_shard), **bf)
         self.greedy = torch.zeros(R, **i32)
+        self.pairs = torch.zeros((R, 2), **i32)
+        self.pairs_all = torch.zeros((model.tp_size, R, 2), **i32)
         self.tok = torch.zeros(R, **i32)
         self.pos = torch.zeros(R, **i32)
         self.table = torch.full((R, bc.max_pages), -1, **i32)
@@ -110,8 +115,8 @@ def forward_chunk(model, bc, toks, write=False):
     """toks [B][T] (the same T for every row of the batch). Returns (logits [B, T, V] bf16, greedy [B, T] int32,
     handle). write=False: a verify pass, to be followed by commit_chunk(model, bc, handle, accepted); write=True: all T
     tokens are committed (handle is None)."""
-    assert model.tp_size == 1, "the chunk path is not sharded yet"
     L = _lib.lib()
+    tp = model.tp_size > 1
     a, D = model.args, model.args.hidden_size
     dev = bc.pos.device
     t_in = torch.as_tensor(toks, dtype=torch.int32)
@@ -150,6 +155,10 @@ def forward_chunk(model, bc, toks, write=False):
         else:
             ck(L.vk_w4_gemm(_p(wt.packed), _p(x), x.stride(0), _p(y), y.stride(0), R, wt.N, wt.K, _p(ws), ws.numel(), st),
                "vk_w4_gemm")
+
+    def allreduce(t):
+        if tp:
+            torch.distributed.all_reduce(t, group=model.group)
 
     w0 = model.layers[0]
     ck(L.vk_embed(_p(s.tok), _p(model.embed), _p(w0["mhc_norm"]), _p(s.H), _p(s.hn),
@@ -198,10 +207,12 @@ def forward_chunk(model, bc, toks, write=False):
                                   _p(s.pos), _p(s.table), _p(s.sel), _p(s.nsel), _p(s.proj), s.proj.stride(0), _p(s.part),
                                   bc.nsplit_bcsa if bcsa else bc.nsplit_dense, _p(s.mix), None, R, st), "vk_attend_decode")
         gemm(s.mix[:, :nmix], w["out"], s.r)
+        allreduce(s.r)
         ck(L.vk_add_rmsnorm(_p(s.x_in), _p(s.r), _p(w["ln_post"]), _p(s.h2), _p(s.hn2), None, R, D, eps, 1, st), "vk_add_rmsnorm")
         gemm(s.hn2, w["gate_up"], s.gu)
         ck(L.vk_silu_mul(_p(s.gu), _p(s.act), None, R, model.I, s.gu.stride(0), st), "vk_silu_mul")
         gemm(s.act, w["down"], s.mlp)
+        allreduce(s.mlp)
         eng = "eng_norm" in w
         val = None
         if eng:
@@ -226,7 +237,13 @@ def forward_chunk(model, bc, toks, write=False):
                                  ws.numel(), st), "vk_bf16_gemm_packed")
     else:
         ck(L.vk_bf16_gemm(_p(s.hn), D, _p(model.lm_head), None, _p(s.logits), s.logits.stride(0), R, V, D, st), "vk_bf16_gemm")
-    ck(L.vk_argmax(_p(s.logits), s.logits.stride(0), min(a.vocab_valid, V), _p(s.greedy), R, st), "vk_argmax")
+    if not tp:
+        ck(L.vk_argmax(_p(s.logits), s.logits.stride(0), min(a.vocab_valid, V), _p(s.greedy), R, st), "vk_argmax")
+    else:
+        ck(L.vk_argmax_pairs(_p(s.logits), s.logits.stride(0), max(0, min(a.vocab_valid - model.vocab0, V)), model.vocab0,
+                             _p(s.pairs), R, st), "vk_argmax_pairs")
+        torch.distributed.all_gather_into_tensor(s.pairs_all, s.pairs, group=model.group)
+        ck(L.vk_argmax_merge(_p(s.pairs_all), model.tp_size, _p(s.greedy), R, st), "vk_argmax_merge")
     logits = s.logits.view(B, T, V)
     greedy = s.greedy.view(B, T)
     handle = ChunkHandle(T, list(bc._pos), window, kda_inputs)

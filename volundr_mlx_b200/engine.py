@@ -40,7 +40,7 @@ class Request:
 class BatchEngine:
     def __init__(self, model, max_rows=16, n_pages=4096, max_pages_per_row=512, prefill_chunk=0):
         self.model = model
-        self.prefill_chunk = int(prefill_chunk) if getattr(model, "tp_size", 1) == 1 else 0   # (the chunk path is not sharded)
+        self.prefill_chunk = int(prefill_chunk)
         self.chunk_steps = 0
         self.bc = model.make_cache(max_rows=max_rows, n_pages=n_pages, max_pages_per_row=max_pages_per_row)
         self.n_pages, self.max_pages_per_row = n_pages, max_pages_per_row
