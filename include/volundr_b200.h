@@ -147,10 +147,9 @@ typedef struct vk_ar_desc {
     int world, rank, rows, row_elems, calls_per_step;
     unsigned spin_limit;   /* polls (>= 100 ns each) before a wait gives up; vk_ar_fill sets a default of seconds */
     void* slots[8];
-    int* flags[8];         /* (header of each region; the kernels do not use it) */
     int* step;
 } vk_ar_desc;
-size_t vk_ar_region_bytes(int world, int rows, int D);   /* 0: unsupported (world <= 8, world * rows <= 252) */
+size_t vk_ar_region_bytes(int world, int rows, int D);   /* 0: unsupported (world <= 8, D a multiple of 8) */
 int vk_ar_alloc(size_t bytes, void** ptr, void* handle64);
 int vk_ar_open(const void* handle64, void** ptr);
 int vk_ar_close(void* ptr);

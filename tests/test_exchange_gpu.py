@@ -1,7 +1,7 @@
 """The in-kernel tensor-parallel exchange on ONE GPU, without kernels that wait for one another: two regions stand for
-two ranks. "Rank 1" runs first with a small wait limit: it pushes its partial rows and its flags into rank 0's region,
+two ranks. "Rank 1" runs first with a small wait limit: it pushes its partial rows (data and sequence numbers) into rank 0's region,
 then its own wait for rank 0 runs out, which must surface as status 4 (the bounded-wait path; the device stays
-usable). "Rank 0" runs afterwards, finds rank 1's flags in place and must produce exactly the plain kernel's result on
+usable). "Rank 0" runs afterwards, finds rank 1's rows in place and must produce exactly the plain kernel's result on
 the bf16 sum of the two partial rows. The real two-process exchange is covered by tests/test_tp_gpu.py."""
 import ctypes
 
@@ -59,11 +59,11 @@ def test_exchange_sum_and_bounded_wait(cuda):
         return h2, hn, rc
 
     try:
-        for call in (0, 3):   # two calls of the "step": different slots, same flags
+        for call in (0, 3):   # two calls of the "step": different slots
             run(r1, d1, call)                                   # rank 1 pushes, then gives up waiting
             with pytest.raises(RuntimeError, match="flag"):
                 ops.check_status(cuda)
-            h2, hn, summed = run(r0, d0, call)                  # rank 0 finds rank 1's rows and flags
+            h2, hn, summed = run(r0, d0, call)                  # rank 0 finds rank 1's rows
             ops.check_status(cuda)
             want_r = (r0.float() + r1.float()).to(torch.bfloat16)
             assert torch.equal(summed, want_r)

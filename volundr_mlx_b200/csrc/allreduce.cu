@@ -10,7 +10,7 @@ __global__ void ar_advance_kernel(int* step) {
     if (threadIdx.x == 0) *step = *step + 1;
 }
 
-constexpr size_t kArHeader = 4096;   // the step counter (and an unused flag area) live in the first 4 KB
+constexpr size_t kArHeader = 4096;   // the step counter lives in the region's first 4 KB (its last 64 bytes)
 
 inline size_t ar_slots_bytes(int world, int rows, int D) { return (size_t)kArSlots * world * rows * D * 4; }
 
@@ -20,7 +20,6 @@ extern "C" {
 
 size_t vk_ar_region_bytes(int world, int rows, int D) {
     if (world < 1 || world > kArMaxWorld || rows < 1 || D < 8 || D % 8 != 0) return 0;
-    if ((size_t)world * rows * kArParts * 4 + 64 > kArHeader) return 0;
     return kArHeader + ar_slots_bytes(world, rows, D);
 }
 
@@ -68,7 +67,6 @@ int vk_ar_fill(vk_ar_desc* d, int world, int rank, int rows, int D, int calls_pe
     d->spin_limit = kArSpinDefault;
     for (int p = 0; p < world; p++) {
         if (bases[p] == nullptr) return VK_EINVAL;
-        d->flags[p] = (int*)bases[p];
         d->slots[p] = (uint8_t*)bases[p] + kArHeader;
     }
     d->step = (int*)((uint8_t*)bases[rank] + kArHeader - 64);

@@ -3,7 +3,7 @@
 // ranks hold partial products of the row-parallel linears; the reference is single-GPU and has no counterpart.
 //
 // Every rank owns one region of device memory that all ranks have mapped (CUDA IPC):
-//     header                            the local step counter (and a flag area the kernels no longer use)
+//     header                            the local step counter
 //     slots [4][world][rows][D] lines   slots[seq & 3][src][b] = the partial row that `src` pushed, as 8-byte units
 //                                       {two bf16 of data, the push's sequence number}: 16-byte lines of two units
 // The sequence number travels WITH the data, so a push needs neither a fence nor a separate flag, and the receiver
@@ -25,7 +25,7 @@
 
 constexpr int kArMaxWorld = 8;
 constexpr int kArSlots = 4;
-constexpr int kArParts = 4;     // flag words per (rank, row): a row may be exchanged in up to four independent parts
+constexpr int kArParts = 4;     // a row may be exchanged in up to four independent parts (one CTA each)
 constexpr uint32_t kArSpinDefault = 1u << 23;   // polls of >= 100 ns each: several seconds, to ride out host-side skew
 
 // The caller's descriptor (public header: vk_ar_desc). Pointers of rank p are that rank's region as mapped into this
@@ -34,7 +34,6 @@ typedef struct vk_ar_desc {
     int world, rank, rows, row_elems, calls_per_step;
     unsigned spin_limit;           // polls before a wait gives up (vk_ar_fill sets the default)
     void* slots[8];
-    int* flags[8];
     int* step;
 } vk_ar_desc;
 
@@ -42,7 +41,6 @@ struct VkArDesc {              // what the kernels get
     int world, rank, rows, calls_per_step;
     uint32_t spin_limit;
     uint8_t* slots[kArMaxWorld];   // slots[p]: base of rank p's slot array (slots[rank] is local)
-    int* flags[kArMaxWorld];       // flags[p]: base of rank p's flag array
     int* step;                     // local step counter
 };
 

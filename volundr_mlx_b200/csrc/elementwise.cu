@@ -876,9 +876,8 @@ static int ar_call(const vk_ar_desc* ar, int call, int B, int D, VkArCall* out) 
     out->d.world = ar->world; out->d.rank = ar->rank; out->d.rows = ar->rows; out->d.calls_per_step = ar->calls_per_step;
     out->d.spin_limit = ar->spin_limit;
     for (int p = 0; p < ar->world; p++) {
-        if (ar->slots[p] == nullptr || ar->flags[p] == nullptr) return VK_EINVAL;
+        if (ar->slots[p] == nullptr) return VK_EINVAL;
         out->d.slots[p] = (uint8_t*)ar->slots[p];
-        out->d.flags[p] = ar->flags[p];
     }
     out->d.step = ar->step;
     out->call = call;

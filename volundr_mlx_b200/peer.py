@@ -14,7 +14,7 @@ from . import _lib
 class ArDesc(ctypes.Structure):
     """vk_ar_desc of include/volundr_b200.h."""
     _fields_ = [("world", ctypes.c_int), ("rank", ctypes.c_int), ("rows", ctypes.c_int), ("row_elems", ctypes.c_int),
-                ("calls_per_step", ctypes.c_int), ("spin_limit", ctypes.c_uint), ("slots", ctypes.c_void_p * 8), ("flags", ctypes.c_void_p * 8),
+                ("calls_per_step", ctypes.c_int), ("spin_limit", ctypes.c_uint), ("slots", ctypes.c_void_p * 8),
                 ("step", ctypes.c_void_p)]
 
 
