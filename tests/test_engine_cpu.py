@@ -91,15 +91,14 @@ def test_engine_waits_for_pages(monkeypatch):
     assert out[a] == solo(list(range(1, 100)), 20) and out[b] == solo([1, 2], 2)
 
 
-def fake_forward_chunk(model, bc, toks, write=False):
-    """The chunk interface on the fake cache: greedy[b][t] follows the row's history plus its first t + 1 tokens;
-    write=True keeps all of them, otherwise commit_chunk keeps each row's own count."""
+def fake_forward_chunk(model, bc, toks, write=False, logits_at=None):
+    """The chunk interface on the fake cache: greedy[b][0] follows the row's history plus its tokens up to index
+    logits_at[b]; write=True keeps all tokens, otherwise commit_chunk keeps each row's own count."""
     B, T = len(toks), len(toks[0])
-    assert B == bc.B and all(len(t) == T for t in toks)
-    greedy = torch.zeros((B, T), dtype=torch.int32)
+    assert B == bc.B and all(len(t) == T for t in toks) and len(logits_at) == B
+    greedy = torch.zeros((B, 1), dtype=torch.int32)
     for b, k in enumerate(bc.keys):
-        for t in range(T):
-            greedy[b, t] = fake_next(bc.hist[k] + [int(x) for x in toks[b][: t + 1]])
+        greedy[b, 0] = fake_next(bc.hist[k] + [int(x) for x in toks[b][: logits_at[b] + 1]])
     if write:
         for b, k in enumerate(bc.keys):
             bc.hist[k] += [int(x) for x in toks[b]]

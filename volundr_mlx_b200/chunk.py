@@ -111,10 +111,11 @@ def _open_pages(bc, T):
         bc.free_top -= len(need)
 
 
-def forward_chunk(model, bc, toks, write=False):
+def forward_chunk(model, bc, toks, write=False, logits_at=None):
     """toks [B][T] (the same T for every row of the batch). Returns (logits [B, T, V] bf16, greedy [B, T] int32,
     handle). write=False: a verify pass, to be followed by commit_chunk(model, bc, handle, accepted); write=True: all T
-    tokens are committed (handle is None)."""
+    tokens are committed (handle is None). logits_at [B] (token index per row): the LM head runs only on that token of
+    every row (what feeding a prompt needs: the logits after its last token), logits [B, 1, V], greedy [B, 1]."""
     L = _lib.lib()
     tp = model.tp_size > 1
     a, D = model.args, model.args.hidden_size
@@ -232,20 +233,27 @@ def forward_chunk(model, bc, toks, write=False):
                                  _p(w["eng_gate_b"]) if eng else None, None, R, D, 1 if last else 0, eps, st),
            "vk_mhc_combine_norm")
     V = model.vocab_shard
+    hn, RL, TL = s.hn, R, T            # rows that go through the LM head
+    if logits_at is not None:
+        at = torch.as_tensor(logits_at, dtype=torch.long).to(dev)
+        assert at.shape == (B,) and int(at.min()) >= 0 and int(at.max()) < T
+        hn = s.hn.index_select(0, torch.arange(B, device=dev) * T + at)
+        RL, TL = B, 1
     if isinstance(model.lm_head, ops.BF16Weight):
-        ck(L.vk_bf16_gemm_packed(_p(model.lm_head.packed), _p(s.hn), D, _p(s.logits), s.logits.stride(0), R, V, D, _p(ws),
+        ck(L.vk_bf16_gemm_packed(_p(model.lm_head.packed), _p(hn), D, _p(s.logits), s.logits.stride(0), RL, V, D, _p(ws),
                                  ws.numel(), st), "vk_bf16_gemm_packed")
     else:
-        ck(L.vk_bf16_gemm(_p(s.hn), D, _p(model.lm_head), None, _p(s.logits), s.logits.stride(0), R, V, D, st), "vk_bf16_gemm")
+        ck(L.vk_bf16_gemm(_p(hn), D, _p(model.lm_head), None, _p(s.logits), s.logits.stride(0), RL, V, D, st), "vk_bf16_gemm")
     if not tp:
-        ck(L.vk_argmax(_p(s.logits), s.logits.stride(0), min(a.vocab_valid, V), _p(s.greedy), R, st), "vk_argmax")
+        ck(L.vk_argmax(_p(s.logits), s.logits.stride(0), min(a.vocab_valid, V), _p(s.greedy), RL, st), "vk_argmax")
     else:
         ck(L.vk_argmax_pairs(_p(s.logits), s.logits.stride(0), max(0, min(a.vocab_valid - model.vocab0, V)), model.vocab0,
-                             _p(s.pairs), R, st), "vk_argmax_pairs")
-        torch.distributed.all_gather_into_tensor(s.pairs_all, s.pairs, group=model.group)
-        ck(L.vk_argmax_merge(_p(s.pairs_all), model.tp_size, _p(s.greedy), R, st), "vk_argmax_merge")
-    logits = s.logits.view(B, T, V)
-    greedy = s.greedy.view(B, T)
+                             _p(s.pairs), RL, st), "vk_argmax_pairs")
+        gathered = s.pairs_all.view(-1)[: model.tp_size * RL * 2].view(model.tp_size, RL, 2)
+        torch.distributed.all_gather_into_tensor(gathered, s.pairs[:RL], group=model.group)
+        ck(L.vk_argmax_merge(_p(s.pairs_all), model.tp_size, _p(s.greedy), RL, st), "vk_argmax_merge")
+    logits = s.logits[:RL].view(B, TL, V)
+    greedy = s.greedy[:RL].view(B, TL)
     handle = ChunkHandle(T, list(bc._pos), window, kda_inputs)
     if write:
         _finish(model, bc, handle, [T] * B, replay=False)

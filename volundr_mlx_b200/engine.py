@@ -120,10 +120,11 @@ class BatchEngine:
             own = r.prompt[r.fed: r.fed + T] if r.fed < len(r.prompt) else [r.out[-1]]
             n.append(len(own))
             toks.append(list(own) + [0] * (T - len(own)))
+        last = [k - 1 for k in n]           # the LM head runs on each row's last own token only
         if all(k == T for k in n):
-            _, greedy, _ = CH.forward_chunk(self.model, self.bc, toks, write=True)
+            _, greedy, _ = CH.forward_chunk(self.model, self.bc, toks, write=True, logits_at=last)
         else:
-            _, greedy, h = CH.forward_chunk(self.model, self.bc, toks, write=False)
+            _, greedy, h = CH.forward_chunk(self.model, self.bc, toks, write=False, logits_at=last)
             CH.commit_chunk(self.model, self.bc, h, n)
         greedy = greedy.tolist()
         self.chunk_steps += 1
@@ -131,7 +132,7 @@ class BatchEngine:
         for b, r in enumerate(rows):
             r.fed += n[b]
             if r.fed >= len(r.prompt):
-                g = int(greedy[b][n[b] - 1])
+                g = int(greedy[b][0])
                 r.out.append(g)
                 produced.append((r.key, g))
         return produced
