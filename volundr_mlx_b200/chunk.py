@@ -80,19 +80,17 @@ class ChunkHandle:
         self.T, self.pos0, self.window, self.kda_inputs = T, pos0, window, kda_inputs
 
 
-_scratch = {}
-
-
 def _get_scratch(model, bc, R):
-    """The scratch of the last few row counts (an engine that feeds prompts meets a handful of them)."""
-    key = (id(model), id(bc), R)
-    if key in _scratch:
-        _scratch[key] = _scratch.pop(key)            # most recently used last
+    """The scratch of the cache's last few row counts (an engine that feeds prompts meets a handful of them). It lives
+    on the cache object, so it can never outlive the shapes it was made for."""
+    held = bc.__dict__.setdefault("_chunk_scratch", {})
+    if R in held:
+        held[R] = held.pop(R)                        # most recently used last
     else:
-        while len(_scratch) >= 4:
-            _scratch.pop(next(iter(_scratch)))
-        _scratch[key] = ChunkScratch(model, bc, R)
-    return _scratch[key]
+        while len(held) >= 4:
+            held.pop(next(iter(held)))
+        held[R] = ChunkScratch(model, bc, R)
+    return held[R]
 
 
 def _open_pages(bc, T):
