@@ -190,6 +190,13 @@ int vk_kda_chunk(const void* proj, int ldp, int off_z, int off_fd, const void* h
                  int D, int Hk, int HV, int Dk, int Dv, int rank, float eps, vk_stream_t stream);
 /* (write_state = 0: outputs only; the state and the conv buffers are not touched and the parity word is not to be
  * flipped: the verify pass in front of a commit.) */
+/* Ragged chunks: request b has accept[b] <= T tokens of its own and its rows of proj / h / out start at
+ * row_offset[b] (the requests' rows lie one after another, nothing is padded); row_offset null = vk_kda_chunk. */
+int vk_kda_chunk_ragged(const void* proj, int ldp, int off_z, int off_fd, const void* h, const void* w_b, const void* w_fup,
+                        const float* conv_w, const float* A_log, const float* dt_bias, const void* norm_w, void* conv,
+                        const int* parity, size_t conv_stride, float* S, void* out, const int* accept,
+                        const int* row_offset, int write_state, int B, int T, int D, int Hk, int HV, int Dk, int Dv,
+                        int rank, float eps, vk_stream_t stream);
 /* h, the state S, both conv buffers and the parity word are read before the kernel waits for the launch in front of
  * it (they stream in while that launch finishes): none of them may be written by that launch. proj may. */
 

@@ -128,3 +128,68 @@ def test_prefill_chunks_then_decode(cuda):
     assert one.shape == (1, 1, full.shape[2]) and _rel(one[0, 0], full[0, 30]) < 1e-2   # (the LM head's row passes differ)
     assert int(gone[0, 0]) == int(one[0, 0, : args.vocab_valid].float().argmax())
     assert two[1].host_pos() == [48]
+
+
+def test_ragged_chunk(cuda):
+    """Rows that bring different numbers of tokens (1, 70 and 9: a decoding row beside two prompt rows, the long one
+    crossing a page boundary and closing a block): the rows' tokens lie one after another, nothing is padded. The
+    logits after each row's last token and the steps that follow must be those of token-by-token decoding; a ragged
+    verify pass + commit must leave each row where its accepted count says."""
+    from volundr_mlx_b200 import batch as BT, chunk as CH, ops
+    from volundr_mlx_b200.volundr import Model
+
+    args = synth.small_args(bcsa_far="tokens", bcsa_score="pooled_key", bcsa_window=128, bcsa_compress=64, bcsa_topk=2)
+    params = synth.make_params(args, seed=33)
+    model = Model(args, params, cuda)
+    rng = np.random.default_rng(33)
+    warm, lens, cont = 20, [1, 70, 9], 4
+    warm_toks = rng.integers(0, args.vocab_valid, size=(warm, 3))
+    toks = [rng.integers(0, args.vocab_valid, size=n).tolist() for n in lens]
+    cont_toks = rng.integers(0, args.vocab_valid, size=(cont, 3))
+
+    def fresh():
+        bc = model.make_cache(max_rows=4, n_pages=16, max_pages_per_row=4)
+        bc.apply(join=["a", "b", "c"])
+        for t in range(warm):
+            BT.forward(model, bc, warm_toks[t].tolist())
+        return bc
+
+    def solo(b, n_own):
+        """Row b alone: warm-up, its first n_own chunk tokens; returns the cache and the last logits."""
+        one = model.make_cache(max_rows=1, n_pages=8, max_pages_per_row=4)
+        one.apply(join=["x"])
+        lg = None
+        for t in range(warm):
+            lg, _ = BT.forward(model, one, [int(warm_toks[t, b])])
+        for t in range(n_own):
+            lg, _ = BT.forward(model, one, [int(toks[b][t])])
+        return one, lg[0].clone()
+
+    for accepted in (None, [1, 33, 0]):
+        bc = fresh()
+        free_before = int(bc.free_top.item())
+        if accepted is None:
+            logits, greedy, _ = CH.forward_chunk(model, bc, toks, write=True)
+            kept = lens
+        else:
+            logits, greedy, h = CH.forward_chunk(model, bc, toks, write=False)
+            CH.commit_chunk(model, bc, h, accepted)
+            kept = accepted
+        ops.check_status()
+        assert logits.shape[:2] == (3, 1)
+        assert bc.host_pos() == [warm + n for n in kept]
+        assert int(bc.free_top.item()) == free_before - sum(1 for n in kept if warm + n > 64)
+        after = []
+        for t in range(cont):
+            lg, _ = BT.forward(model, bc, cont_toks[t].tolist())
+            after.append(lg.clone())
+        ops.check_status()
+        for b in range(3):
+            one, last = solo(b, kept[b])
+            if accepted is None:      # (the verify pass's logits follow the last token of the whole chunk row)
+                assert _rel(logits[b, 0], last) < 3e-2, b
+                assert int(greedy[b, 0]) == int(logits[b, 0, : args.vocab_valid].float().argmax())
+            for t in range(cont):
+                lg, _ = BT.forward(model, one, [int(cont_toks[t, b])])
+                assert _rel(after[t][b], lg[0]) < 3e-2, (b, t, accepted)
+    ops.check_status()

@@ -92,24 +92,15 @@ def test_engine_waits_for_pages(monkeypatch):
 
 
 def fake_forward_chunk(model, bc, toks, write=False, logits_at=None):
-    """The chunk interface on the fake cache: greedy[b][0] follows the row's history plus its tokens up to index
-    logits_at[b]; write=True keeps all tokens, otherwise commit_chunk keeps each row's own count."""
-    B, T = len(toks), len(toks[0])
-    assert B == bc.B and all(len(t) == T for t in toks) and len(logits_at) == B
-    greedy = torch.zeros((B, 1), dtype=torch.int32)
+    """The chunk interface on the fake cache: one list of tokens per row (ragged); greedy[b][0] follows the row's
+    history plus its tokens up to index logits_at[b]; the engine commits every chunk as it is (write=True)."""
+    assert write and len(toks) == bc.B and len(logits_at) == bc.B and all(len(t) >= 1 for t in toks)
+    greedy = torch.zeros((bc.B, 1), dtype=torch.int32)
     for b, k in enumerate(bc.keys):
+        assert 0 <= logits_at[b] < len(toks[b])
         greedy[b, 0] = fake_next(bc.hist[k] + [int(x) for x in toks[b][: logits_at[b] + 1]])
-    if write:
-        for b, k in enumerate(bc.keys):
-            bc.hist[k] += [int(x) for x in toks[b]]
-        return None, greedy, None
-    return None, greedy, toks
-
-
-def fake_commit_chunk(model, bc, handle, accepted):
-    for b, k in enumerate(bc.keys):
-        assert 0 <= accepted[b] <= len(handle[b])
-        bc.hist[k] += [int(x) for x in handle[b][: accepted[b]]]
+        bc.hist[k] += [int(x) for x in toks[b]]
+    return None, greedy, None
 
 
 def test_engine_ragged_prefill_chunks(monkeypatch):
@@ -117,7 +108,6 @@ def test_engine_ragged_prefill_chunks(monkeypatch):
     output, prompt tokens go through chunk steps, and a chunk never outgrows a row's page table or the pool."""
     monkeypatch.setattr(E.BT, "forward", fake_forward)
     monkeypatch.setattr(E.CH, "forward_chunk", fake_forward_chunk)
-    monkeypatch.setattr(E.CH, "commit_chunk", fake_commit_chunk)
     eng = E.BatchEngine(FakeModel(), max_rows=3, n_pages=6, max_pages_per_row=2, prefill_chunk=4)
     reqs = [([5, 6, 7], 4), ([1], 9), ([9, 8, 7, 6, 5, 4, 3], 2), ([2, 2], 1), ([3, 1, 4, 1, 5], 6), (list(range(1, 70)), 3),
             (list(range(1, 126)), 3)]

@@ -57,6 +57,8 @@ SIGNATURES = {
     "vk_attn_configure": (c_int, []),
     "vk_kda_chunk": (c_int, [c_void_p, c_int, c_int, c_int] + [c_void_p] * 9 + [c_size_t, c_void_p, c_void_p, c_void_p]
                      + [c_int] * 9 + [c_float, c_void_p]),
+    "vk_kda_chunk_ragged": (c_int, [c_void_p, c_int, c_int, c_int] + [c_void_p] * 9 + [c_size_t, c_void_p, c_void_p, c_void_p,
+                                    c_void_p] + [c_int] * 9 + [c_float, c_void_p]),
     "vk_kda_step": (c_int, [c_void_p, c_int, c_int, c_int] + [c_void_p] * 9 + [c_size_t, c_void_p, c_void_p, c_void_p, c_void_p]
                     + [c_int] * 7 + [c_float, c_void_p]),
     "vk_batch_step_begin": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,

@@ -2,8 +2,9 @@
 batch_spec.verify_forward (batch_spec.py:107-158: B x T verify) and, with one row, through the prefill chunks of
 session.prefill_iter (session.py:351-387) / verify.forward_iter (spec/verify.py:180-226).
 
-The B x T tokens run as R = B * T "virtual rows": row b * T + t is token t of request b, at position pos[b] + t, on the
-page table of request b. Linears see all R rows at once (vk_w4_gemm: wide passes; vk_bf16_gemm_packed), the row-wise
+The tokens run as R "virtual rows", the requests' rows one after another: row off[b] + t is token t of request b, at
+position pos[b] + t, on the page table of request b. Requests may bring different numbers of tokens (ragged chunks:
+R = the sum of the counts, nothing is padded); with T tokens each, off[b] = b * T. Linears see all R rows at once (vk_w4_gemm: wide passes; vk_bf16_gemm_packed), the row-wise
 kernels (mHC, norms, SiLU, Engram) are the decode step's kernels on R rows, attention is the decode attention with R
 query rows (each sees the keys up to its own position: all rows' K/V are written before anything is attended, blocks
 that close inside the window are pooled in a second pass), the KDA recurrence is vk_kda_chunk. Nothing here waits for
@@ -34,7 +35,7 @@ _p = BT._p
 
 
 class ChunkScratch:
-    """Activations of R virtual rows (one allocation per (model, R))."""
+    """Activations of up to R virtual rows (capacities are powers of two, so a cache meets only a few of them)."""
 
     def __init__(self, model, bc, R):
         a, d, D = model.args, model.device, model.args.hidden_size
@@ -76,29 +77,33 @@ class ChunkScratch:
 
 
 class ChunkHandle:
-    def __init__(self, T, pos0, window, kda_inputs):
-        self.T, self.pos0, self.window, self.kda_inputs = T, pos0, window, kda_inputs
+    def __init__(self, lens, pos0, window, kda_inputs, off):
+        self.lens, self.pos0, self.window, self.kda_inputs, self.off = lens, pos0, window, kda_inputs, off
+        self.T = max(lens)
 
 
 def _get_scratch(model, bc, R):
-    """The scratch of the cache's last few row counts (an engine that feeds prompts meets a handful of them). It lives
+    """Scratch for R rows: the smallest power-of-two capacity that holds them, the last few capacities kept. It lives
     on the cache object, so it can never outlive the shapes it was made for."""
+    cap = 16
+    while cap < R:
+        cap *= 2
     held = bc.__dict__.setdefault("_chunk_scratch", {})
-    if R in held:
-        held[R] = held.pop(R)                        # most recently used last
+    if cap in held:
+        held[cap] = held.pop(cap)                    # most recently used last
     else:
         while len(held) >= 4:
             held.pop(next(iter(held)))
-        held[R] = ChunkScratch(model, bc, R)
-    return held[R]
+        held[cap] = ChunkScratch(model, bc, cap)
+    return held[cap]
 
 
-def _open_pages(bc, T):
-    """Pages for the positions pos .. pos + T - 1 of every row (host side: at most a few per row)."""
+def _open_pages(bc, lens):
+    """Pages for the positions pos .. pos + lens[b] - 1 of every row (host side: at most a few per row)."""
     need = []
     for b, p0 in enumerate(bc._pos):
-        assert (p0 + T + PAGE - 1) // PAGE <= bc.max_pages, "row would outgrow its page table"
-        for p in range(p0, p0 + T):
+        assert (p0 + lens[b] + PAGE - 1) // PAGE <= bc.max_pages, "row would outgrow its page table"
+        for p in range(p0, p0 + lens[b]):
             if p % PAGE == 0:
                 need.append((b, p // PAGE))
     if need:
@@ -110,35 +115,48 @@ def _open_pages(bc, T):
 
 
 def forward_chunk(model, bc, toks, write=False, logits_at=None):
-    """toks [B][T] (the same T for every row of the batch). Returns (logits [B, T, V] bf16, greedy [B, T] int32,
-    handle). write=False: a verify pass, to be followed by commit_chunk(model, bc, handle, accepted); write=True: all T
-    tokens are committed (handle is None). logits_at [B] (token index per row): the LM head runs only on that token of
-    every row (what feeding a prompt needs: the logits after its last token), logits [B, 1, V], greedy [B, 1]."""
+    """toks [B][T], or one list of tokens per row with different lengths (a ragged chunk). Returns (logits, greedy,
+    handle): logits [B, T, V] bf16 and greedy [B, T] int32 for T tokens per row; for a ragged chunk the LM head runs on
+    one token per row (logits_at, default each row's last), logits [B, 1, V], greedy [B, 1]. write=False: a verify
+    pass, to be followed by commit_chunk(model, bc, handle, accepted); write=True: all tokens are committed (handle is
+    None). logits_at [B] (token index per row) restricts the LM head to that token of every row (what feeding a prompt
+    needs: the logits after its last token)."""
     L = _lib.lib()
     tp = model.tp_size > 1
     a, D = model.args, model.args.hidden_size
     dev = bc.pos.device
-    t_in = torch.as_tensor(toks, dtype=torch.int32)
-    assert t_in.dim() == 2 and t_in.shape[0] == bc.B and t_in.shape[1] >= 1
-    B, T = t_in.shape
-    R = B * T
-    t_in = t_in.to(dev)
+    if torch.is_tensor(toks):
+        toks = toks.tolist()
+    toks = [[int(x) for x in row] for row in toks]
+    lens = [len(row) for row in toks]
+    B, T, R = len(toks), max(lens), sum(lens)
+    assert B == bc.B and min(lens) >= 1
+    ragged = min(lens) != T
+    if ragged and logits_at is None:
+        logits_at = [n - 1 for n in lens]
+    off = [0] * B
+    for b in range(1, B):
+        off[b] = off[b - 1] + lens[b - 1]
+    t_in = torch.tensor([row + [0] * (T - len(row)) for row in toks], dtype=torch.int32).to(dev)   # [B, T], padded
     s = _get_scratch(model, bc, R)
     BT.model_warm(model)
-    _open_pages(bc, T)
+    _open_pages(bc, lens)
     st = torch.cuda.current_stream().cuda_stream
     eps = a.rms_norm_eps
     ck = _lib.check
-    # ---- virtual rows
-    rows = torch.arange(B, device=dev).repeat_interleave(T)
-    s.row_map.copy_(rows.to(torch.int32))
-    s.tok.copy_(t_in.reshape(-1))
-    s.pos.copy_((bc.pos[:B].unsqueeze(1) + torch.arange(T, device=dev, dtype=torch.int32).unsqueeze(0)).reshape(-1))
-    s.table.copy_(bc.table[:B][rows])
+    # ---- virtual rows: request and token index of each
+    lens_t = torch.tensor(lens, device=dev)
+    off_t = torch.tensor(off, dtype=torch.int32, device=dev)
+    rows = torch.arange(B, device=dev).repeat_interleave(lens_t)
+    tpos = torch.arange(R, device=dev) - off_t.long()[rows]
+    s.row_map[:R].copy_(rows.to(torch.int32))
+    s.tok[:R].copy_(t_in[rows, tpos])
+    s.pos[:R].copy_(bc.pos[:B][rows] + tpos.to(torch.int32))
+    s.table[:R].copy_(bc.table[:B][rows])
     window = None
     if a.engram_layers and bc.keep > 0:
         window = torch.cat([bc.engram_prev[:B, : bc.keep], t_in], dim=1)          # [B, keep + T]
-        s.engram_prev.copy_(window.unfold(1, bc.keep, 1)[:, :T].reshape(R, bc.keep))
+        s.engram_prev[:R].copy_(window.unfold(1, bc.keep, 1)[rows, tpos])
     ws = ops.workspace(max(1 << 26, L.vk_w4_workspace_bytes(R, max(w["gate_up"].N for w in model.layers), D)), dev)
 
     tile_ws = None
@@ -164,7 +182,7 @@ def forward_chunk(model, bc, toks, write=False, logits_at=None):
                   _p(s.engram_prev) if a.engram_layers else None, _p(s.engram_rows), bc.orders,
                   len(a.engram_orders) if a.engram_layers else 0, a.engram_rows, R, D, eps, st), "vk_embed")
     kda_inputs = []
-    acc_all = torch.full((B,), T, dtype=torch.int32, device=dev)
+    acc_all = torch.tensor(lens, dtype=torch.int32, device=dev)
     nl = len(model.layers)
     for i, (w, lst) in enumerate(zip(model.layers, bc.layers)):
         ck(L.vk_mhc_mix_norm(_p(s.H), _p(s.hn), _p(w["dyn"]), _p(w["pre_s"]), _p(w["post_s"]), _p(w["res_s"]), _p(w["ln_in"]),
@@ -174,11 +192,12 @@ def forward_chunk(model, bc, toks, write=False, logits_at=None):
         if w["mixer"] == "kda":
             nmix = model.HV * 128
             if not write:
-                kda_inputs.append((i, s.proj[:, : w["proj"].N].clone(), s.h.clone()))
-            ck(L.vk_kda_chunk(_p(s.proj), s.proj.stride(0), w["off_z"], w["off_fd"], _p(s.h), _p(w["in_proj_b"]), _p(w["f_up"]),
-                              _p(w["conv_w"]), _p(w["A_log"]), _p(w["dt_bias"]), _p(w["gnorm"]), _p(lst["conv"]),
-                              _p(bc.parity), lst["conv"][0].numel(), _p(lst["S"]), _p(s.mix), _p(acc_all), 1 if write else 0,
-                              B, T, D, model.Hk, model.HV, 128, 128, a.kda_gate_rank, eps, st), "vk_kda_chunk")
+                kda_inputs.append((i, s.proj[:R, : w["proj"].N].clone(), s.h[:R].clone()))
+            ck(L.vk_kda_chunk_ragged(_p(s.proj), s.proj.stride(0), w["off_z"], w["off_fd"], _p(s.h), _p(w["in_proj_b"]),
+                                     _p(w["f_up"]), _p(w["conv_w"]), _p(w["A_log"]), _p(w["dt_bias"]), _p(w["gnorm"]),
+                                     _p(lst["conv"]), _p(bc.parity), lst["conv"][0].numel(), _p(lst["S"]), _p(s.mix),
+                                     _p(acc_all), _p(off_t), 1 if write else 0, B, T, D, model.Hk, model.HV, 128, 128,
+                                     a.kda_gate_rank, eps, st), "vk_kda_chunk_ragged")
         else:
             bcsa = w["mixer"] == "bcsa"
             g = bc.geom[w["mixer"]]
@@ -206,12 +225,12 @@ def forward_chunk(model, bc, toks, write=False, logits_at=None):
                                   _p(s.pos), _p(s.table), _p(s.sel), _p(s.nsel), _p(s.proj), s.proj.stride(0), _p(s.part),
                                   bc.nsplit_bcsa if bcsa else bc.nsplit_dense, _p(s.mix), None, R, st), "vk_attend_decode")
         gemm(s.mix[:, :nmix], w["out"], s.r)
-        allreduce(s.r)
+        allreduce(s.r[:R])
         ck(L.vk_add_rmsnorm(_p(s.x_in), _p(s.r), _p(w["ln_post"]), _p(s.h2), _p(s.hn2), None, R, D, eps, 1, st), "vk_add_rmsnorm")
         gemm(s.hn2, w["gate_up"], s.gu)
         ck(L.vk_silu_mul(_p(s.gu), _p(s.act), None, R, model.I, s.gu.stride(0), st), "vk_silu_mul")
         gemm(s.act, w["down"], s.mlp)
-        allreduce(s.mlp)
+        allreduce(s.mlp[:R])
         eng = "eng_norm" in w
         val = None
         if eng:
@@ -234,8 +253,9 @@ def forward_chunk(model, bc, toks, write=False, logits_at=None):
     hn, RL, TL = s.hn, R, T            # rows that go through the LM head
     if logits_at is not None:
         at = torch.as_tensor(logits_at, dtype=torch.long).to(dev)
-        assert at.shape == (B,) and int(at.min()) >= 0 and int(at.max()) < T
-        hn = s.hn.index_select(0, torch.arange(B, device=dev) * T + at)
+        assert at.shape == (B,)
+        assert all(0 <= int(x) < lens[b] for b, x in enumerate(logits_at))
+        hn = s.hn.index_select(0, off_t.long() + at)
         RL, TL = B, 1
     if isinstance(model.lm_head, ops.BF16Weight):
         ck(L.vk_bf16_gemm_packed(_p(model.lm_head.packed), _p(hn), D, _p(s.logits), s.logits.stride(0), RL, V, D, _p(ws),
@@ -252,9 +272,9 @@ def forward_chunk(model, bc, toks, write=False, logits_at=None):
         ck(L.vk_argmax_merge(_p(s.pairs_all), model.tp_size, _p(s.greedy), RL, st), "vk_argmax_merge")
     logits = s.logits[:RL].view(B, TL, V)
     greedy = s.greedy[:RL].view(B, TL)
-    handle = ChunkHandle(T, list(bc._pos), window, kda_inputs)
+    handle = ChunkHandle(lens, list(bc._pos), window, kda_inputs, off_t)
     if write:
-        _finish(model, bc, handle, [T] * B, replay=False)
+        _finish(model, bc, handle, lens, replay=False)
         return logits, greedy, None
     return logits, greedy, handle
 
@@ -263,26 +283,28 @@ def _finish(model, bc, h: ChunkHandle, acc, replay):
     L = _lib.lib()
     a, D = model.args, model.args.hidden_size
     B, T = bc.B, h.T
+    R = sum(h.lens)
     dev = bc.pos.device
     st = torch.cuda.current_stream().cuda_stream
     has_kda = any("S" in lst for lst in bc.layers)
     if replay and has_kda:
         acc_t = torch.tensor(acc, dtype=torch.int32, device=dev)
-        scratch_out = torch.empty((B * T, model.HV * 128), dtype=BF16, device=dev)
+        scratch_out = torch.empty((R, model.HV * 128), dtype=BF16, device=dev)
         for i, proj, hin in h.kda_inputs:
             w, lst = model.layers[i], bc.layers[i]
-            _lib.check(L.vk_kda_chunk(_p(proj), proj.stride(0), w["off_z"], w["off_fd"], _p(hin), _p(w["in_proj_b"]),
-                                      _p(w["f_up"]), _p(w["conv_w"]), _p(w["A_log"]), _p(w["dt_bias"]), _p(w["gnorm"]),
-                                      _p(lst["conv"]), _p(bc.parity), lst["conv"][0].numel(), _p(lst["S"]), _p(scratch_out),
-                                      _p(acc_t), 1, B, T, D, model.Hk, model.HV, 128, 128, a.kda_gate_rank,
-                                      a.rms_norm_eps, st), "vk_kda_chunk")
+            _lib.check(L.vk_kda_chunk_ragged(_p(proj), proj.stride(0), w["off_z"], w["off_fd"], _p(hin), _p(w["in_proj_b"]),
+                                             _p(w["f_up"]), _p(w["conv_w"]), _p(w["A_log"]), _p(w["dt_bias"]),
+                                             _p(w["gnorm"]), _p(lst["conv"]), _p(bc.parity), lst["conv"][0].numel(),
+                                             _p(lst["S"]), _p(scratch_out), _p(acc_t), _p(h.off), 1, B, T, D, model.Hk,
+                                             model.HV, 128, 128, a.kda_gate_rank, a.rms_norm_eps, st),
+                       "vk_kda_chunk_ragged")
     if has_kda:          # the conv windows now sit in the other buffer, as after a decode step
         bc.parity ^= 1
         bc.steps += 1
     if h.window is not None:
         idx = torch.tensor(acc, dtype=torch.long, device=dev).unsqueeze(1) + torch.arange(bc.keep, device=dev).unsqueeze(0)
         bc.engram_prev[:B, : bc.keep] = torch.gather(h.window, 1, idx)
-    back = [(b, p // PAGE) for b in range(B) for p in range(h.pos0[b] + acc[b], h.pos0[b] + T) if p % PAGE == 0]
+    back = [(b, p // PAGE) for b in range(B) for p in range(h.pos0[b] + acc[b], h.pos0[b] + h.lens[b]) if p % PAGE == 0]
     if back:
         torch.cuda.synchronize(dev)
         top = int(bc.free_top.item())
@@ -298,5 +320,5 @@ def commit_chunk(model, bc, handle: ChunkHandle, accepted):
     """accepted[b] in 0..T: the number of tokens of the verify pass request b keeps (batch_spec.commit,
     batch_spec.py:160-199)."""
     acc = [int(x) for x in accepted]
-    assert len(acc) == bc.B and all(0 <= n <= handle.T for n in acc)
+    assert len(acc) == bc.B and all(0 <= n <= handle.lens[b] for b, n in enumerate(acc))
     _finish(model, bc, handle, acc, replay=True)

@@ -293,6 +293,7 @@ constexpr int kChunkTok = 8;
 struct KdaChunkParams {
     KdaParams k;          // proj / h / out rows are (b * T + t); g_override, xrec_out unused
     const int* accept;    // [B] or null
+    const int* row_off;   // [B] or null: first row of request b in proj / h / out (null: b * T)
     int T;
     int write_state;      // 0: outputs only, the state and the conv window stay as they were (a verify pass)
 };
@@ -337,6 +338,7 @@ __global__ void __launch_bounds__(128, 2) kda_chunk_kernel(const KdaChunkParams 
     pdl_wait();
     const int T = cp.T;
     const int n_tok = cp.accept != nullptr ? min(max(cp.accept[b], 0), T) : T;
+    const size_t row0 = cp.row_off != nullptr ? (size_t)cp.row_off[b] : (size_t)b * T;
     const int par = *p.parity & 1;
     const __nv_bfloat16* conv_in = p.conv + (size_t)par * p.conv_stride;
     __nv_bfloat16* conv_out = p.conv + (size_t)(1 - par) * p.conv_stride;
@@ -362,7 +364,7 @@ __global__ void __launch_bounds__(128, 2) kda_chunk_kernel(const KdaChunkParams 
 #pragma unroll 1
         for (int tt = 0; tt < kChunkTok; tt++) {
             if (tt < nt) {
-                const size_t rowi = (size_t)b * T + t0 + tt;
+                const size_t rowi = row0 + t0 + tt;
                 const __nv_bfloat16* pr = p.proj + rowi * p.ldp;
                 for (int i = c; i < p.rank; i += 128) fd[tt][i] = bf2f(pr[p.off_fd + i]);
                 float s3[3];
@@ -465,7 +467,7 @@ __global__ void __launch_bounds__(128, 2) kda_chunk_kernel(const KdaChunkParams 
                 float ss = 0.f;
                 ss += rr[0]; ss += rr[1]; ss += rr[2]; ss += rr[3];
                 const float inv = rsqrtf(ss * (1.f / 128.f) + p.eps);
-                const size_t rowi = (size_t)b * T + t0 + tt;
+                const size_t rowi = row0 + t0 + tt;
                 const float z = bf2f(p.proj[rowi * p.ldp + p.off_z + hv * 128 + c]);
                 const float ov = bfr(((ybv * inv) * nw) * (z / (1.f + expf(-z))));
                 p.out[rowi * p.HV * 128 + hv * 128 + c] = f2bf(ov);
@@ -517,13 +519,15 @@ int vk_kda_configure(void) {
     return VK_OK;
 }
 
-// T tokens per row in one launch (prefill chunks; verify and its commit replay). Rows of proj / h / out are b * T + t.
-// accept (optional, [B]): row b stops after accept[b] tokens. The conv window after the chunk lands in the other
-// buffer, as after one vk_kda_step: flip the parity word once per launch.
-int vk_kda_chunk(const void* proj, int ldp, int off_z, int off_fd, const void* h, const void* w_b, const void* w_fup,
-                 const float* conv_w, const float* A_log, const float* dt_bias, const void* norm_w, void* conv,
-                 const int* parity, size_t conv_stride, float* S, void* out, const int* accept, int write_state, int B, int T,
-                 int D, int Hk, int HV, int Dk, int Dv, int rank, float eps, cudaStream_t stream) {
+// T tokens per row in one launch (prefill chunks; verify and its commit replay). Rows of proj / h / out are b * T + t,
+// or row_offset[b] + t when row_offset is given (ragged chunks: request b has accept[b] <= T tokens of its own, the
+// requests' rows lie one after another). accept (optional, [B]): row b stops after accept[b] tokens. The conv window
+// after the chunk lands in the other buffer, as after one vk_kda_step: flip the parity word once per launch.
+int vk_kda_chunk_ragged(const void* proj, int ldp, int off_z, int off_fd, const void* h, const void* w_b, const void* w_fup,
+                        const float* conv_w, const float* A_log, const float* dt_bias, const void* norm_w, void* conv,
+                        const int* parity, size_t conv_stride, float* S, void* out, const int* accept,
+                        const int* row_offset, int write_state, int B, int T, int D, int Hk, int HV, int Dk, int Dv,
+                        int rank, float eps, cudaStream_t stream) {
     if (B <= 0 || T <= 0 || Dk != 128 || Dv != 128 || Hk <= 0 || HV % Hk != 0 || rank <= 0 || rank > 256 || rank % 8 != 0 ||
         D % 8 != 0 || parity == nullptr)
         return VK_EINVAL;
@@ -532,9 +536,18 @@ int vk_kda_chunk(const void* proj, int ldp, int off_z, int off_fd, const void* h
             conv_w, A_log, dt_bias, (const __nv_bfloat16*)norm_w, (__nv_bfloat16*)conv, parity, conv_stride, S,
             (__nv_bfloat16*)out, nullptr, nullptr, ldp, off_z, off_fd, D, Hk, HV, rank, eps};
     cp.accept = accept;
+    cp.row_off = row_offset;
     cp.T = T;
     cp.write_state = write_state ? 1 : 0;
     return (int)vk_launch(kda_chunk_kernel, dim3(HV, B), dim3(128), 0, stream, cp);
+}
+
+int vk_kda_chunk(const void* proj, int ldp, int off_z, int off_fd, const void* h, const void* w_b, const void* w_fup,
+                 const float* conv_w, const float* A_log, const float* dt_bias, const void* norm_w, void* conv,
+                 const int* parity, size_t conv_stride, float* S, void* out, const int* accept, int write_state, int B, int T,
+                 int D, int Hk, int HV, int Dk, int Dv, int rank, float eps, cudaStream_t stream) {
+    return vk_kda_chunk_ragged(proj, ldp, off_z, off_fd, h, w_b, w_fup, conv_w, A_log, dt_bias, norm_w, conv, parity,
+                               conv_stride, S, out, accept, nullptr, write_state, B, T, D, Hk, HV, Dk, Dv, rank, eps, stream);
 }
 
 int vk_kda_step(const void* proj, int ldp, int off_z, int off_fd, const void* h, const void* w_b, const void* w_fup,

@@ -5,9 +5,9 @@ admission :180-239, the step :300-420, greedy :391, retirement :430-470).
 Prompts: with prefill_chunk <= 1 every prompt token takes one decode step of its row, and a request's tokens are
 exactly those it gets alone, whatever shares the batch with it. With prefill_chunk = T > 1 a step in which some row
 still has two or more prompt tokens to feed runs as one ragged chunk through volundr_mlx_b200.chunk: every row brings
-up to T tokens (prompt rows their next tokens, decoding rows their single next token, padded to the same length), the
-chunk runs as a verify pass and the commit keeps exactly each row's own count (the reference feeds prompts in chunks
-through session.prefill_iter, session.py:351-387, one request at a time). The weights are then read once per chunk
+up to T tokens (prompt rows their next tokens, decoding rows their single next token), the rows' tokens lie one after
+another without padding and are committed as they are (the reference feeds prompts in chunks through
+session.prefill_iter, session.py:351-387, one request at a time). The weights are then read once per chunk
 instead of once per prompt token. The chunk path's GEMMs round differently from the decode step's (within the bf16
 bar), so tokens can differ from the stepwise engine at near-ties of the logits.
 """
@@ -102,30 +102,19 @@ class BatchEngine:
         return produced
 
     def _chunk_len(self, rows) -> int:
-        """Tokens per row of the next step: more than one only while a prompt has two or more tokens left, and only as
-        many as every row's page table and the page pool can take (padding positions open pages until the commit)."""
+        """Tokens a prompt row may bring to the next step: more than one only while a prompt has two or more tokens
+        left (otherwise the step is a plain decode step)."""
         if self.prefill_chunk <= 1:
             return 1
         left = max(len(r.prompt) - r.fed for r in rows)
-        T = min(self.prefill_chunk, left)
-        pos = self.bc._pos
-        T = min([T] + [self.max_pages_per_row * PAGE - p for p in pos])
-        while T > 1 and sum((p + T + PAGE - 1) // PAGE for p in pos) > self.n_pages:
-            T //= 2
-        return max(T, 1)
+        return max(1, min(self.prefill_chunk, left))
 
     def _chunk_step(self, rows, T):
-        toks, n = [], []
-        for r in rows:
-            own = r.prompt[r.fed: r.fed + T] if r.fed < len(r.prompt) else [r.out[-1]]
-            n.append(len(own))
-            toks.append(list(own) + [0] * (T - len(own)))
-        last = [k - 1 for k in n]           # the LM head runs on each row's last own token only
-        if all(k == T for k in n):
-            _, greedy, _ = CH.forward_chunk(self.model, self.bc, toks, write=True, logits_at=last)
-        else:
-            _, greedy, h = CH.forward_chunk(self.model, self.bc, toks, write=False, logits_at=last)
-            CH.commit_chunk(self.model, self.bc, h, n)
+        """One ragged chunk: prompt rows bring up to T of their next tokens, decoding rows their one next token; the
+        rows' tokens lie one after another (nothing is padded) and are committed as they are."""
+        toks = [list(r.prompt[r.fed: r.fed + T]) if r.fed < len(r.prompt) else [r.out[-1]] for r in rows]
+        n = [len(t) for t in toks]
+        _, greedy, _ = CH.forward_chunk(self.model, self.bc, toks, write=True, logits_at=[k - 1 for k in n])
         greedy = greedy.tolist()
         self.chunk_steps += 1
         produced = []
