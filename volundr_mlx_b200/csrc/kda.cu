@@ -310,18 +310,142 @@ __device__ __forceinline__ float tree32(float (&p)[32]) {
     return p[0] + p[1];
 }
 
-__global__ void __launch_bounds__(128, 2) kda_chunk_kernel(const KdaChunkParams cp) {
+// Shared memory of kda_chunk_kernel (dynamic: more than the 48 KB a kernel gets without asking).
+struct KdaChunkSmem {
+    float qs[2][kChunkTok][128], ks[2][kChunkTok][128], gs[2][kChunkTok][128], vs[2][kChunkTok][128];   // per group, two buffers
+    float ys[2][kChunkTok][128];        // the recurrence's outputs, for the gated norm one group later
+    float betas[2][kChunkTok];
+    float fd[kChunkTok][256];
+    float red[4 * kChunkTok][4];
+};
+
+__device__ __forceinline__ void front_barrier() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+
+// 256 threads: the "back" half (threads 0..127) owns the state rows and runs the recurrence of group g while the
+// "front" half (threads 128..255) prepares group g + 1 (conv + SiLU, norms, decay, beta) and finishes group g - 1
+// (gated norm, output), so only the recurrence itself lies on the critical path of a row's tokens. Every sum is formed
+// by the same threads in the same order as in kda_step_kernel (channel c = thread index within its half).
+__global__ void __launch_bounds__(256, 1) kda_chunk_kernel(const KdaChunkParams cp) {
     const KdaParams& p = cp.k;
-    __shared__ __align__(16) float qs[kChunkTok][128], ks[kChunkTok][128], gs[kChunkTok][128];
-    __shared__ float vs[kChunkTok][128], ys[kChunkTok][128];
-    __shared__ float fd[kChunkTok][256];
-    __shared__ float red[4 * kChunkTok][4];
-    __shared__ float betas[kChunkTok];
+    extern __shared__ __align__(16) uint8_t kda_chunk_smem[];
+    KdaChunkSmem& sm = *reinterpret_cast<KdaChunkSmem*>(kda_chunk_smem);
     pdl_launch_dependents();
     const int hv = blockIdx.x, b = blockIdx.y;
-    const int c = threadIdx.x, lane = c & 31, warp = c >> 5;
+    const bool front = threadIdx.x >= 128;
+    const int c = threadIdx.x & 127, lane = c & 31, warp = c >> 5;
     const int rep = p.HV / p.Hk, hk = hv / rep;
     const int KD = p.Hk * 128, C = 2 * KD + p.HV * 128;
+    const int T = cp.T;
+
+    if (!front) {
+        // ------------------------------------------------------------------------------------------ the recurrence
+        pdl_wait();
+        const int n_tok = cp.accept != nullptr ? min(max(cp.accept[b], 0), T) : T;
+        const int n_grp = (n_tok + kChunkTok - 1) / kChunkTok;
+        // Thread (vg, j) = (c >> 2, c & 3) keeps, of the four state rows 4 vg .. 4 vg + 3, the columns of the eight
+        // four-column chains l = j + 4 i: a row's dot product is 32 such chains combined in the order of a warp's xor
+        // tree, whose first three levels (l +- 16, 8, 4) stay inside one thread and whose last two (l +- 2, 1) are
+        // two shuffles between the four threads of the row. Every thread so reads only a quarter of q / k / g per
+        // token (shared-memory traffic, not arithmetic, bounded the one-thread-per-row form).
+        const int j4 = c & 3, vg = c >> 2;
+        float* Sbase = p.S + (((size_t)b * p.HV + hv) * 128 + 4 * vg) * 128;
+        float st[4][8][4];
+#pragma unroll
+        for (int r = 0; r < 4; r++)
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                const float4 v4 = *reinterpret_cast<const float4*>(Sbase + r * 128 + 4 * (j4 + 4 * i));
+                st[r][i][0] = v4.x; st[r][i][1] = v4.y; st[r][i][2] = v4.z; st[r][i][3] = v4.w;
+            }
+        VK_TS(4, 0);
+        __syncthreads();                                   // group 0 is prepared
+        VK_TS(4, 1);
+#if defined(VK_TRACE) && VK_TRACE == 4
+        long long t_wait = 0, t_mark = clock64();
+#endif
+        for (int g = 0; g < n_grp; g++) {
+            const int buf = g & 1;
+            const int nt = min(kChunkTok, n_tok - g * kChunkTok);
+            for (int tt = 0; tt < nt; tt++) {
+                const float beta = sm.betas[buf][tt];
+                const float4 v4 = *reinterpret_cast<const float4*>(&sm.vs[buf][tt][4 * vg]);
+                const float vv[4] = {v4.x, v4.y, v4.z, v4.w};
+                float pp[4][8];
+#pragma unroll
+                for (int i = 0; i < 8; i++) {
+                    const int l = j4 + 4 * i;
+                    const float4 g4 = *reinterpret_cast<const float4*>(&sm.gs[buf][tt][4 * l]);
+                    const float4 k4 = *reinterpret_cast<const float4*>(&sm.ks[buf][tt][4 * l]);
+#pragma unroll
+                    for (int r = 0; r < 4; r++) {
+                        st[r][i][0] *= g4.x; st[r][i][1] *= g4.y; st[r][i][2] *= g4.z; st[r][i][3] *= g4.w;
+                        pp[r][i] = fmaf(st[r][i][3], k4.w, fmaf(st[r][i][2], k4.z, fmaf(st[r][i][1], k4.y, st[r][i][0] * k4.x)));
+                    }
+                }
+                float d[4];
+#pragma unroll
+                for (int r = 0; r < 4; r++) {
+#pragma unroll
+                    for (int i = 0; i < 4; i++) pp[r][i] += pp[r][i + 4];      // l + 16
+                    pp[r][0] += pp[r][2]; pp[r][1] += pp[r][3];                  // l + 8
+                    float x = pp[r][0] + pp[r][1];                               // l + 4
+                    x += __shfl_xor_sync(0xffffffffu, x, 2);                     // l + 2
+                    x += __shfl_xor_sync(0xffffffffu, x, 1);                     // l + 1
+                    d[r] = (vv[r] - x) * beta;
+                }
+#pragma unroll
+                for (int i = 0; i < 8; i++) {
+                    const int l = j4 + 4 * i;
+                    const float4 k4 = *reinterpret_cast<const float4*>(&sm.ks[buf][tt][4 * l]);
+                    const float4 q4 = *reinterpret_cast<const float4*>(&sm.qs[buf][tt][4 * l]);
+#pragma unroll
+                    for (int r = 0; r < 4; r++) {
+                        st[r][i][0] = fmaf(d[r], k4.x, st[r][i][0]); st[r][i][1] = fmaf(d[r], k4.y, st[r][i][1]);
+                        st[r][i][2] = fmaf(d[r], k4.z, st[r][i][2]); st[r][i][3] = fmaf(d[r], k4.w, st[r][i][3]);
+                        pp[r][i] = fmaf(st[r][i][3], q4.w, fmaf(st[r][i][2], q4.z, fmaf(st[r][i][1], q4.y, st[r][i][0] * q4.x)));
+                    }
+                }
+                float o[4];
+#pragma unroll
+                for (int r = 0; r < 4; r++) {
+#pragma unroll
+                    for (int i = 0; i < 4; i++) pp[r][i] += pp[r][i + 4];
+                    pp[r][0] += pp[r][2]; pp[r][1] += pp[r][3];
+                    float x = pp[r][0] + pp[r][1];
+                    x += __shfl_xor_sync(0xffffffffu, x, 2);
+                    x += __shfl_xor_sync(0xffffffffu, x, 1);
+                    o[r] = x;
+                }
+                if (j4 == 0) *reinterpret_cast<float4*>(&sm.ys[buf][tt][4 * vg]) = make_float4(o[0], o[1], o[2], o[3]);
+            }
+#if defined(VK_TRACE) && VK_TRACE == 4
+            const long long t_before = clock64();
+#endif
+            __syncthreads();                               // group g + 1 is prepared, ys of group g are in place
+#if defined(VK_TRACE) && VK_TRACE == 4
+            t_wait += clock64() - t_before;
+#endif
+        }
+#if defined(VK_TRACE) && VK_TRACE == 4
+        if (threadIdx.x == 0) {
+            const int cta = ((blockIdx.y * gridDim.x) + blockIdx.x) & 4095;
+            g_vk_trace[cta * 16 + 2] = clock64();
+            g_vk_trace[cta * 16 + 3] = t_wait;
+            g_vk_trace[cta * 16 + 4] = t_mark;
+        }
+#endif
+        if (cp.write_state) {
+#pragma unroll
+            for (int r = 0; r < 4; r++)
+#pragma unroll
+                for (int i = 0; i < 8; i++)
+                    *reinterpret_cast<float4*>(Sbase + r * 128 + 4 * (j4 + 4 * i)) =
+                        make_float4(st[r][i][0], st[r][i][1], st[r][i][2], st[r][i][3]);
+        }
+        return;
+    }
+
+    // ---------------------------------------------------------------------------------------------- the front half
     const int ch[3] = {hk * 128 + c, KD + hk * 128 + c, 2 * KD + hv * 128 + c};
     const uint4* fup = reinterpret_cast<const uint4*>(p.w_fup) + (size_t)hv * (p.rank / 8) * 128 + c;
     float4 cw[3];
@@ -336,149 +460,206 @@ __global__ void __launch_bounds__(128, 2) kda_chunk_kernel(const KdaChunkParams 
         wbv[i] = k < p.D ? *reinterpret_cast<const uint4*>(wb + k) : make_uint4(0u, 0u, 0u, 0u);
     }
     pdl_wait();
-    const int T = cp.T;
     const int n_tok = cp.accept != nullptr ? min(max(cp.accept[b], 0), T) : T;
+    const int n_grp = (n_tok + kChunkTok - 1) / kChunkTok;
     const size_t row0 = cp.row_off != nullptr ? (size_t)cp.row_off[b] : (size_t)b * T;
     const int par = *p.parity & 1;
     const __nv_bfloat16* conv_in = p.conv + (size_t)par * p.conv_stride;
     __nv_bfloat16* conv_out = p.conv + (size_t)(1 - par) * p.conv_stride;
-    // this thread's state row, and the three inputs in front of the chunk of its q / k / v channels
-    float* Srow = p.S + ((((size_t)b * p.HV + hv) * 128) + c) * 128;
-    float st[128];
-#pragma unroll
-    for (int j = 0; j < 32; j++) {
-        const float4 v4 = *reinterpret_cast<const float4*>(Srow + 4 * j);
-        st[4 * j] = v4.x; st[4 * j + 1] = v4.y; st[4 * j + 2] = v4.z; st[4 * j + 3] = v4.w;
-    }
-    __nv_bfloat16 win[3][3];
+    __nv_bfloat16 win[3][3];      // the three inputs in front of the next token of this thread's q / k / v channels
 #pragma unroll
     for (int i = 0; i < 3; i++) {
         const size_t cb = (size_t)b * 3 * C + ch[i];
         win[i][0] = conv_in[cb]; win[i][1] = conv_in[cb + C]; win[i][2] = conv_in[cb + 2 * (size_t)C];
     }
 
-    for (int t0 = 0; t0 < n_tok; t0 += kChunkTok) {
+#if defined(VK_TRACE) && VK_TRACE == 4
+#define KDA_FS(i) do { if (threadIdx.x == 128 && g == 1) g_vk_trace[((((blockIdx.y * gridDim.x) + blockIdx.x) & 4095) * 16) + (i)] = clock64(); } while (0)
+#else
+#define KDA_FS(i) do { } while (0)
+#endif
+    // (A) of one group into buffer `buf`: conv + SiLU, the two norms, decay, beta
+    auto prepare = [&](int g, int buf) {
+        KDA_FS(5);
+        const int t0 = g * kChunkTok;
         const int nt = min(kChunkTok, n_tok - t0);
-        // ---- (A1) per token: f_down into shared memory, conv + SiLU, partial sums of the two norms and of beta's dot
-        // (the raw conv outputs wait in qs / ks / vs, at the thread's own slots, for the norms)
+        constexpr int kHalf = kChunkTok / 2;
 #pragma unroll 1
-        for (int tt = 0; tt < kChunkTok; tt++) {
-            if (tt < nt) {
-                const size_t rowi = row0 + t0 + tt;
-                const __nv_bfloat16* pr = p.proj + rowi * p.ldp;
-                for (int i = c; i < p.rank; i += 128) fd[tt][i] = bf2f(pr[p.off_fd + i]);
-                float s3[3];
+        for (int h0 = 0; h0 < kChunkTok; h0 += kHalf) {     // four tokens at a time, stage by stage, so that the
+            // tokens' dependent chains (loads, exp / divide, fma chains, shuffle trees) run side by side
+            __nv_bfloat16 x3[kHalf][3];
+            uint4 hx[kHalf][kBdotPieces];
+            __nv_bfloat16 fdv[kHalf][2];                    // rank <= 256: at most two f_down values per thread
 #pragma unroll
-                for (int i = 0; i < 3; i++) {
-                    const __nv_bfloat16 x3 = pr[ch[i]];
-                    float acc = __fmul_rn(bf2f(win[i][0]), cw[i].x);
-                    acc = __fadd_rn(acc, __fmul_rn(bf2f(win[i][1]), cw[i].y));
-                    acc = __fadd_rn(acc, __fmul_rn(bf2f(win[i][2]), cw[i].z));
-                    acc = __fadd_rn(acc, __fmul_rn(bf2f(x3), cw[i].w));
-                    s3[i] = bfr(acc / (1.f + expf(-acc)));
-                    win[i][0] = win[i][1]; win[i][1] = win[i][2]; win[i][2] = x3;
-                }
-                qs[tt][c] = s3[0]; ks[tt][c] = s3[1]; vs[tt][c] = s3[2];
-                const __nv_bfloat16* hb = p.h + rowi * p.D;
-                float bdot = 0.f;
+            for (int u = 0; u < kHalf; u++) {
+                const int tt = h0 + u;
+                if (tt < nt) {
+                    const size_t rowi = row0 + t0 + tt;
+                    const __nv_bfloat16* pr = p.proj + rowi * p.ldp;
+                    const __nv_bfloat16* hb = p.h + rowi * p.D;
 #pragma unroll
-                for (int i = 0; i < kBdotPieces; i++) {
-                    const int k = c * 8 + i * 1024;
-                    const uint4 wv = wbv[i];
-                    const uint4 xv = k < p.D ? *reinterpret_cast<const uint4*>(hb + k) : make_uint4(0u, 0u, 0u, 0u);
-                    bdot = fmaf(bf_lo(wv.x), bf_lo(xv.x), bdot); bdot = fmaf(bf_hi(wv.x), bf_hi(xv.x), bdot);
-                    bdot = fmaf(bf_lo(wv.y), bf_lo(xv.y), bdot); bdot = fmaf(bf_hi(wv.y), bf_hi(xv.y), bdot);
-                    bdot = fmaf(bf_lo(wv.z), bf_lo(xv.z), bdot); bdot = fmaf(bf_hi(wv.z), bf_hi(xv.z), bdot);
-                    bdot = fmaf(bf_lo(wv.w), bf_lo(xv.w), bdot); bdot = fmaf(bf_hi(wv.w), bf_hi(xv.w), bdot);
+                    for (int i = 0; i < 3; i++) x3[u][i] = pr[ch[i]];
+#pragma unroll
+                    for (int i = 0; i < kBdotPieces; i++) {
+                        const int k = c * 8 + i * 1024;
+                        hx[u][i] = k < p.D ? *reinterpret_cast<const uint4*>(hb + k) : make_uint4(0u, 0u, 0u, 0u);
+                    }
+#pragma unroll
+                    for (int i = 0; i < 2; i++)
+                        if (c + 128 * i < p.rank) fdv[u][i] = pr[p.off_fd + c + 128 * i];
                 }
-                for (int k = c * 8 + kBdotPieces * 1024; k < p.D; k += 1024) {   // (hidden sizes beyond 5120)
-                    const uint4 wv = *reinterpret_cast<const uint4*>(wb + k);
-                    const uint4 xv = *reinterpret_cast<const uint4*>(hb + k);
-                    bdot = fmaf(bf_lo(wv.x), bf_lo(xv.x), bdot); bdot = fmaf(bf_hi(wv.x), bf_hi(xv.x), bdot);
-                    bdot = fmaf(bf_lo(wv.y), bf_lo(xv.y), bdot); bdot = fmaf(bf_hi(wv.y), bf_hi(xv.y), bdot);
-                    bdot = fmaf(bf_lo(wv.z), bf_lo(xv.z), bdot); bdot = fmaf(bf_hi(wv.z), bf_hi(xv.z), bdot);
-                    bdot = fmaf(bf_lo(wv.w), bf_lo(xv.w), bdot); bdot = fmaf(bf_hi(wv.w), bf_hi(xv.w), bdot);
+            }
+            KDA_FS(6 + (h0 ? 2 : 0));
+            float s3[kHalf][3], bdot[kHalf];
+#pragma unroll
+            for (int u = 0; u < kHalf; u++) {
+                const int tt = h0 + u;
+                bdot[u] = 0.f;
+#pragma unroll
+                for (int i = 0; i < 3; i++) s3[u][i] = 0.f;
+                if (tt < nt) {
+#pragma unroll
+                    for (int i = 0; i < 2; i++)
+                        if (c + 128 * i < p.rank) sm.fd[tt][c + 128 * i] = bf2f(fdv[u][i]);
+#pragma unroll
+                    for (int i = 0; i < 3; i++) {
+                        float acc = __fmul_rn(bf2f(win[i][0]), cw[i].x);
+                        acc = __fadd_rn(acc, __fmul_rn(bf2f(win[i][1]), cw[i].y));
+                        acc = __fadd_rn(acc, __fmul_rn(bf2f(win[i][2]), cw[i].z));
+                        acc = __fadd_rn(acc, __fmul_rn(bf2f(x3[u][i]), cw[i].w));
+                        s3[u][i] = bfr(acc / (1.f + expf(-acc)));
+                        win[i][0] = win[i][1]; win[i][1] = win[i][2]; win[i][2] = x3[u][i];
+                    }
+                    float bd = 0.f;
+#pragma unroll
+                    for (int i = 0; i < kBdotPieces; i++) {
+                        const uint4 wv = wbv[i];
+                        const uint4 xv = hx[u][i];
+                        bd = fmaf(bf_lo(wv.x), bf_lo(xv.x), bd); bd = fmaf(bf_hi(wv.x), bf_hi(xv.x), bd);
+                        bd = fmaf(bf_lo(wv.y), bf_lo(xv.y), bd); bd = fmaf(bf_hi(wv.y), bf_hi(xv.y), bd);
+                        bd = fmaf(bf_lo(wv.z), bf_lo(xv.z), bd); bd = fmaf(bf_hi(wv.z), bf_hi(xv.z), bd);
+                        bd = fmaf(bf_lo(wv.w), bf_lo(xv.w), bd); bd = fmaf(bf_hi(wv.w), bf_hi(xv.w), bd);
+                    }
+                    const __nv_bfloat16* hb = p.h + (row0 + t0 + tt) * p.D;
+                    for (int k = c * 8 + kBdotPieces * 1024; k < p.D; k += 1024) {   // (hidden sizes beyond 5120)
+                        const uint4 wv = *reinterpret_cast<const uint4*>(wb + k);
+                        const uint4 xv = *reinterpret_cast<const uint4*>(hb + k);
+                        bd = fmaf(bf_lo(wv.x), bf_lo(xv.x), bd); bd = fmaf(bf_hi(wv.x), bf_hi(xv.x), bd);
+                        bd = fmaf(bf_lo(wv.y), bf_lo(xv.y), bd); bd = fmaf(bf_hi(wv.y), bf_hi(xv.y), bd);
+                        bd = fmaf(bf_lo(wv.z), bf_lo(xv.z), bd); bd = fmaf(bf_hi(wv.z), bf_hi(xv.z), bd);
+                        bd = fmaf(bf_lo(wv.w), bf_lo(xv.w), bd); bd = fmaf(bf_hi(wv.w), bf_hi(xv.w), bd);
+                    }
+                    bdot[u] = bd;
+                    sm.qs[buf][tt][c] = s3[u][0]; sm.ks[buf][tt][c] = s3[u][1]; sm.vs[buf][tt][c] = s3[u][2];
                 }
-                const float w0 = warp_sum(s3[0] * s3[0]), w1 = warp_sum(s3[1] * s3[1]), w2 = warp_sum(bdot);
-                if (lane == 0) { red[3 * tt][warp] = w0; red[3 * tt + 1][warp] = w1; red[3 * tt + 2][warp] = w2; }
+            }
+            // the twelve warp sums of the four tokens, level by level (each sum is the xor tree of warp_sum)
+            float ws[kHalf][3];
+#pragma unroll
+            for (int u = 0; u < kHalf; u++) { ws[u][0] = s3[u][0] * s3[u][0]; ws[u][1] = s3[u][1] * s3[u][1]; ws[u][2] = bdot[u]; }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+                for (int u = 0; u < kHalf; u++)
+#pragma unroll
+                    for (int i = 0; i < 3; i++) ws[u][i] += __shfl_xor_sync(0xffffffffu, ws[u][i], o);
+#pragma unroll
+            for (int u = 0; u < kHalf; u++) {
+                const int tt = h0 + u;
+                if (tt < nt && lane == 0) {
+                    sm.red[3 * tt][warp] = ws[u][0]; sm.red[3 * tt + 1][warp] = ws[u][1]; sm.red[3 * tt + 2][warp] = ws[u][2];
+                }
+            }
+            KDA_FS(7 + (h0 ? 2 : 0));
+        }
+        front_barrier();
+        KDA_FS(10);
+        // the decay's low-rank product for all tokens of the group at once: f_up is read once per group, and the
+        // tokens' fma chains (each in the order of kda_step_kernel) run side by side
+        float av[kChunkTok];
+#pragma unroll
+        for (int tt = 0; tt < kChunkTok; tt++) av[tt] = 0.f;
+        uint4 wnext = fup[0];
+        for (int r = 0; r < p.rank; r += 8) {
+            const uint4 wv = wnext;
+            if (r + 8 < p.rank) wnext = fup[(size_t)(r / 8 + 1) * 128];      // in flight while this piece is used
+            const float w8[8] = {bf_lo(wv.x), bf_hi(wv.x), bf_lo(wv.y), bf_hi(wv.y), bf_lo(wv.z), bf_hi(wv.z), bf_lo(wv.w), bf_hi(wv.w)};
+#pragma unroll
+            for (int tt = 0; tt < kChunkTok; tt++) {
+                const float4 f0 = *reinterpret_cast<const float4*>(&sm.fd[tt][r]);
+                const float4 f1 = *reinterpret_cast<const float4*>(&sm.fd[tt][r + 4]);
+                float a = av[tt];
+                a = fmaf(w8[0], f0.x, a); a = fmaf(w8[1], f0.y, a); a = fmaf(w8[2], f0.z, a); a = fmaf(w8[3], f0.w, a);
+                a = fmaf(w8[4], f1.x, a); a = fmaf(w8[5], f1.y, a); a = fmaf(w8[6], f1.z, a); a = fmaf(w8[7], f1.w, a);
+                av[tt] = a;
             }
         }
-        __syncthreads();
-        // ---- (A2) per token: q^ / k^ / v, decay, beta
-#pragma unroll 1
-        for (int tt = 0; tt < kChunkTok; tt++) {
-            if (tt < nt) {
-                const float ssq = ((red[3 * tt][0] + red[3 * tt][1]) + red[3 * tt][2]) + red[3 * tt][3];
-                const float ssk = ((red[3 * tt + 1][0] + red[3 * tt + 1][1]) + red[3 * tt + 1][2]) + red[3 * tt + 1][3];
-                const float bd = ((red[3 * tt + 2][0] + red[3 * tt + 2][1]) + red[3 * tt + 2][2]) + red[3 * tt + 2][3];
-                qs[tt][c] = (qs[tt][c] / sqrtf(ssq + 1e-6f)) * 0.08838834764831845f;  // 128^-1/2
-                ks[tt][c] = ks[tt][c] / sqrtf(ssk + 1e-6f);
-                float a = 0.f;
-                for (int r = 0; r < p.rank; r += 8) {
-                    const uint4 wv = fup[(size_t)(r / 8) * 128];
-                    a = fmaf(bf_lo(wv.x), fd[tt][r], a); a = fmaf(bf_hi(wv.x), fd[tt][r + 1], a);
-                    a = fmaf(bf_lo(wv.y), fd[tt][r + 2], a); a = fmaf(bf_hi(wv.y), fd[tt][r + 3], a);
-                    a = fmaf(bf_lo(wv.z), fd[tt][r + 4], a); a = fmaf(bf_hi(wv.z), fd[tt][r + 5], a);
-                    a = fmaf(bf_lo(wv.w), fd[tt][r + 6], a); a = fmaf(bf_hi(wv.w), fd[tt][r + 7], a);
-                }
-                a = bfr(a);
-                gs[tt][c] = expf(-expf(a_log) * softplus_f(a + dtb));
-                if (c == 0) betas[tt] = 1.f / (1.f + expf(-bfr(bd)));
-            }
-        }
-        __syncthreads();
-        // ---- (B) the recurrence, token after token; thread c owns row c of S
-        for (int tt = 0; tt < nt; tt++) {
-            const float beta = betas[tt];
-            float pp[32];
+        KDA_FS(11);
 #pragma unroll
-            for (int l = 0; l < 32; l++) {
-                const float4 g4 = *reinterpret_cast<const float4*>(&gs[tt][4 * l]);
-                const float4 k4 = *reinterpret_cast<const float4*>(&ks[tt][4 * l]);
-                st[4 * l] *= g4.x; st[4 * l + 1] *= g4.y; st[4 * l + 2] *= g4.z; st[4 * l + 3] *= g4.w;
-                pp[l] = fmaf(st[4 * l + 3], k4.w, fmaf(st[4 * l + 2], k4.z, fmaf(st[4 * l + 1], k4.y, st[4 * l] * k4.x)));
+        for (int tt = 0; tt < kChunkTok; tt++) {
+            if (tt < nt) {
+                const float ssq = ((sm.red[3 * tt][0] + sm.red[3 * tt][1]) + sm.red[3 * tt][2]) + sm.red[3 * tt][3];
+                const float ssk = ((sm.red[3 * tt + 1][0] + sm.red[3 * tt + 1][1]) + sm.red[3 * tt + 1][2]) + sm.red[3 * tt + 1][3];
+                const float bd = ((sm.red[3 * tt + 2][0] + sm.red[3 * tt + 2][1]) + sm.red[3 * tt + 2][2]) + sm.red[3 * tt + 2][3];
+                sm.qs[buf][tt][c] = (sm.qs[buf][tt][c] / sqrtf(ssq + 1e-6f)) * 0.08838834764831845f;  // 128^-1/2
+                sm.ks[buf][tt][c] = sm.ks[buf][tt][c] / sqrtf(ssk + 1e-6f);
+                const float a = bfr(av[tt]);
+                sm.gs[buf][tt][c] = expf(-expf(a_log) * softplus_f(a + dtb));
+                if (c == 0) sm.betas[buf][tt] = 1.f / (1.f + expf(-bfr(bd)));
             }
-            const float d = (vs[tt][c] - tree32(pp)) * beta;
+        }
+        KDA_FS(12);
+        front_barrier();      // (fd and red are free for the next group)
+    };
+
+    // (C) of one group: gated norm of the outputs the recurrence left in ys[buf]
+    auto finish = [&](int g, int buf) {
+        const int t0 = g * kChunkTok;
+        const int nt = min(kChunkTok, n_tok - t0);
+        float zv[kChunkTok], yv[kChunkTok];
 #pragma unroll
-            for (int l = 0; l < 32; l++) {
-                const float4 k4 = *reinterpret_cast<const float4*>(&ks[tt][4 * l]);
-                const float4 q4 = *reinterpret_cast<const float4*>(&qs[tt][4 * l]);
-                st[4 * l] = fmaf(d, k4.x, st[4 * l]); st[4 * l + 1] = fmaf(d, k4.y, st[4 * l + 1]);
-                st[4 * l + 2] = fmaf(d, k4.z, st[4 * l + 2]); st[4 * l + 3] = fmaf(d, k4.w, st[4 * l + 3]);
-                pp[l] = fmaf(st[4 * l + 3], q4.w, fmaf(st[4 * l + 2], q4.z, fmaf(st[4 * l + 1], q4.y, st[4 * l] * q4.x)));
-            }
-            ys[tt][c] = tree32(pp);
+        for (int tt = 0; tt < kChunkTok; tt++) {          // the gate inputs of the whole group are fetched together
+            if (tt < nt) zv[tt] = bf2f(p.proj[(row0 + t0 + tt) * p.ldp + p.off_z + hv * 128 + c]);
         }
-        // ---- (C) gated norm of the group's outputs (each thread reads back only what it wrote)
-#pragma unroll 1
+        float wy[kChunkTok];
+#pragma unroll
+        for (int tt = 0; tt < kChunkTok; tt++) {
+            yv[tt] = tt < nt ? bfr(sm.ys[buf][tt][c]) : 0.f;
+            wy[tt] = yv[tt] * yv[tt];
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+            for (int tt = 0; tt < kChunkTok; tt++) wy[tt] += __shfl_xor_sync(0xffffffffu, wy[tt], o);
+#pragma unroll
+        for (int tt = 0; tt < kChunkTok; tt++)
+            if (tt < nt && lane == 0) sm.red[3 * kChunkTok + tt][warp] = wy[tt];
+        front_barrier();
+#pragma unroll
         for (int tt = 0; tt < kChunkTok; tt++) {
             if (tt < nt) {
-                const float ybv = bfr(ys[tt][c]);
-                const float w = warp_sum(ybv * ybv);
-                if (lane == 0) red[3 * kChunkTok + tt][warp] = w;
-            }
-        }
-        __syncthreads();
-#pragma unroll 1
-        for (int tt = 0; tt < kChunkTok; tt++) {
-            if (tt < nt) {
-                const float ybv = bfr(ys[tt][c]);
-                const float* rr = red[3 * kChunkTok + tt];
+                const float* rr = sm.red[3 * kChunkTok + tt];
                 float ss = 0.f;
                 ss += rr[0]; ss += rr[1]; ss += rr[2]; ss += rr[3];
                 const float inv = rsqrtf(ss * (1.f / 128.f) + p.eps);
-                const size_t rowi = row0 + t0 + tt;
-                const float z = bf2f(p.proj[rowi * p.ldp + p.off_z + hv * 128 + c]);
-                const float ov = bfr(((ybv * inv) * nw) * (z / (1.f + expf(-z))));
-                p.out[rowi * p.HV * 128 + hv * 128 + c] = f2bf(ov);
+                const float z = zv[tt];
+                const float ov = bfr(((yv[tt] * inv) * nw) * (z / (1.f + expf(-z))));
+                p.out[(row0 + t0 + tt) * p.HV * 128 + hv * 128 + c] = f2bf(ov);
             }
         }
-        __syncthreads();   // the group's shared arrays are free again
+        front_barrier();
+    };
+
+    if (n_grp > 0) prepare(0, 0);
+    __syncthreads();                                       // group 0 is prepared
+    for (int g = 0; g < n_grp; g++) {
+        const int buf = g & 1;
+        if (g + 1 < n_grp) prepare(g + 1, buf ^ 1);        // while the back half runs group g
+        if (g > 0) finish(g - 1, buf ^ 1);
+        __syncthreads();                                   // group g's outputs are in ys[buf]
     }
+    if (n_grp > 0) finish(n_grp - 1, (n_grp - 1) & 1);
     if (!cp.write_state) return;
-#pragma unroll
-    for (int j = 0; j < 32; j++)
-        *reinterpret_cast<float4*>(Srow + 4 * j) = make_float4(st[4 * j], st[4 * j + 1], st[4 * j + 2], st[4 * j + 3]);
 #pragma unroll
     for (int i = 0; i < 3; i++) {
         if (i == 2 || hv % rep == 0) {
@@ -539,7 +720,12 @@ int vk_kda_chunk_ragged(const void* proj, int ldp, int off_z, int off_fd, const 
     cp.row_off = row_offset;
     cp.T = T;
     cp.write_state = write_state ? 1 : 0;
-    return (int)vk_launch(kda_chunk_kernel, dim3(HV, B), dim3(128), 0, stream, cp);
+    static bool configured = false;
+    if (!configured) {
+        VK_CUDA(cudaFuncSetAttribute(kda_chunk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(KdaChunkSmem)));
+        configured = true;
+    }
+    return (int)vk_launch(kda_chunk_kernel, dim3(HV, B), dim3(256), sizeof(KdaChunkSmem), stream, cp);
 }
 
 int vk_kda_chunk(const void* proj, int ldp, int off_z, int off_fd, const void* h, const void* w_b, const void* w_fup,
