@@ -281,13 +281,14 @@ __global__ void __launch_bounds__(128, 5) kda_step_kernel(const KdaParams p) {
 // ------------------------------------------------------------------------------------------------ T tokens per row
 // The same recurrence over a chunk of T tokens per row in one launch: the prefill form (kernels.gated_delta_tg,
 // kernels.py:544-555) and the verify / commit-replay form (verify._kda, spec/verify.py:33-53; batch_spec.py:186-195).
-// One CTA of 128 threads per (value head, row). Thread c keeps row c of the state S[Dv, Dk] (128 fp32 values) in
-// registers for the whole chunk: the state is read once and written once per launch, however many tokens there are.
-// Tokens go through in groups of kChunkTok: (A) conv + SiLU, norms, decay and beta of the group's tokens, (B) the
-// recurrence, token after token, thread-local (every row dot is formed as 32 four-element fma chains combined in the
-// order of a warp's xor tree: the sums, and so every bit of the result, are those of kda_step_kernel), (C) the gated
-// norm of the group's outputs. `accept[b]` (optional) ends row b's chunk early: later tokens leave state, conv window
-// and output alone (the commit of a verify step: only the accepted prefix is replayed).
+// One CTA per (value head, row): half of its threads keep the state S[Dv, Dk] in registers for the whole chunk (the
+// state is read once and written once per launch, however many tokens there are) and run the recurrence, the other half
+// does the per-token work around it, one token group ahead and one behind. Tokens go through in groups of kChunkTok:
+// (A) conv + SiLU, norms, decay and beta of the group's tokens, (B) the recurrence, token after token (every row dot is
+// formed as 32 four-element fma chains combined in the order of a warp's xor tree: the sums, and so every bit of the
+// result, are those of kda_step_kernel), (C) the gated norm of the group's outputs. `accept[b]` (optional) ends row b's
+// chunk early: later tokens leave state, conv window and output alone (the commit of a verify step: only the accepted
+// prefix is replayed).
 constexpr int kChunkTok = 8;
 
 struct KdaChunkParams {
@@ -319,50 +320,48 @@ struct KdaChunkSmem {
     float red[4 * kChunkTok][4];
 };
 
-__device__ __forceinline__ void front_barrier() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+// One named barrier per front group (128 threads each): ids 1 and 2 (0 is __syncthreads).
+__device__ __forceinline__ void front_barrier(int group) {
+    if (group == 0) asm volatile("bar.sync 1, 128;" ::: "memory");
+    else asm volatile("bar.sync 2, 128;" ::: "memory");
+}
 
-// 256 threads: the "back" half (threads 0..127) owns the state rows and runs the recurrence of group g while the
-// "front" half (threads 128..255) prepares group g + 1 (conv + SiLU, norms, decay, beta) and finishes group g - 1
-// (gated norm, output), so only the recurrence itself lies on the critical path of a row's tokens. Every sum is formed
-// by the same threads in the same order as in kda_step_kernel (channel c = thread index within its half).
-__global__ void __launch_bounds__(256, 1) kda_chunk_kernel(const KdaChunkParams cp) {
+// 512 threads. The "back" half (threads 0..255) owns the state and runs the recurrence of token group g while the two
+// "front" groups (threads 256..383 and 384..511) prepare group g + 1 (conv + SiLU, norms, decay, beta) and finish
+// group g - 1 (gated norm, output), each for its own four of the group's eight tokens, so only the recurrence itself
+// lies on the critical path of a row's tokens. Every sum is formed in the order of kda_step_kernel: per-channel work by
+// channel c = thread index within its front group (warp sums over 32 channels, the four warps' sums added in order),
+// the recurrence's row dots as 32 four-column chains combined in the order of a warp's xor tree.
+__global__ void __launch_bounds__(512, 1) kda_chunk_kernel(const KdaChunkParams cp) {
     const KdaParams& p = cp.k;
     extern __shared__ __align__(16) uint8_t kda_chunk_smem[];
     KdaChunkSmem& sm = *reinterpret_cast<KdaChunkSmem*>(kda_chunk_smem);
     pdl_launch_dependents();
     const int hv = blockIdx.x, b = blockIdx.y;
-    const bool front = threadIdx.x >= 128;
-    const int c = threadIdx.x & 127, lane = c & 31, warp = c >> 5;
-    const int rep = p.HV / p.Hk, hk = hv / rep;
-    const int KD = p.Hk * 128, C = 2 * KD + p.HV * 128;
     const int T = cp.T;
 
-    if (!front) {
+    if (threadIdx.x < 256) {
         // ------------------------------------------------------------------------------------------ the recurrence
+        // Thread (vg, j) = (c >> 3, c & 7) keeps, of the four state rows 4 vg .. 4 vg + 3, the columns of the four
+        // four-column chains l = j + 8 i. The xor tree's first two levels (l +- 16, 8) stay inside the thread, the last
+        // three (l +- 4, 2, 1) are three shuffles between the eight threads of the rows. A thread so reads an eighth
+        // of q / k / g per token: shared-memory traffic, not arithmetic, bounds a one-thread-per-row form.
+        const int c = threadIdx.x, j8 = c & 7, vg = c >> 3;
         pdl_wait();
         const int n_tok = cp.accept != nullptr ? min(max(cp.accept[b], 0), T) : T;
         const int n_grp = (n_tok + kChunkTok - 1) / kChunkTok;
-        // Thread (vg, j) = (c >> 2, c & 3) keeps, of the four state rows 4 vg .. 4 vg + 3, the columns of the eight
-        // four-column chains l = j + 4 i: a row's dot product is 32 such chains combined in the order of a warp's xor
-        // tree, whose first three levels (l +- 16, 8, 4) stay inside one thread and whose last two (l +- 2, 1) are
-        // two shuffles between the four threads of the row. Every thread so reads only a quarter of q / k / g per
-        // token (shared-memory traffic, not arithmetic, bounded the one-thread-per-row form).
-        const int j4 = c & 3, vg = c >> 2;
         float* Sbase = p.S + (((size_t)b * p.HV + hv) * 128 + 4 * vg) * 128;
-        float st[4][8][4];
+        float st[4][4][4];
 #pragma unroll
         for (int r = 0; r < 4; r++)
 #pragma unroll
-            for (int i = 0; i < 8; i++) {
-                const float4 v4 = *reinterpret_cast<const float4*>(Sbase + r * 128 + 4 * (j4 + 4 * i));
+            for (int i = 0; i < 4; i++) {
+                const float4 v4 = *reinterpret_cast<const float4*>(Sbase + r * 128 + 4 * (j8 + 8 * i));
                 st[r][i][0] = v4.x; st[r][i][1] = v4.y; st[r][i][2] = v4.z; st[r][i][3] = v4.w;
             }
         VK_TS(4, 0);
         __syncthreads();                                   // group 0 is prepared
         VK_TS(4, 1);
-#if defined(VK_TRACE) && VK_TRACE == 4
-        long long t_wait = 0, t_mark = clock64();
-#endif
         for (int g = 0; g < n_grp; g++) {
             const int buf = g & 1;
             const int nt = min(kChunkTok, n_tok - g * kChunkTok);
@@ -370,10 +369,10 @@ __global__ void __launch_bounds__(256, 1) kda_chunk_kernel(const KdaChunkParams 
                 const float beta = sm.betas[buf][tt];
                 const float4 v4 = *reinterpret_cast<const float4*>(&sm.vs[buf][tt][4 * vg]);
                 const float vv[4] = {v4.x, v4.y, v4.z, v4.w};
-                float pp[4][8];
+                float pp[4][4];
 #pragma unroll
-                for (int i = 0; i < 8; i++) {
-                    const int l = j4 + 4 * i;
+                for (int i = 0; i < 4; i++) {
+                    const int l = j8 + 8 * i;
                     const float4 g4 = *reinterpret_cast<const float4*>(&sm.gs[buf][tt][4 * l]);
                     const float4 k4 = *reinterpret_cast<const float4*>(&sm.ks[buf][tt][4 * l]);
 #pragma unroll
@@ -385,17 +384,16 @@ __global__ void __launch_bounds__(256, 1) kda_chunk_kernel(const KdaChunkParams 
                 float d[4];
 #pragma unroll
                 for (int r = 0; r < 4; r++) {
-#pragma unroll
-                    for (int i = 0; i < 4; i++) pp[r][i] += pp[r][i + 4];      // l + 16
-                    pp[r][0] += pp[r][2]; pp[r][1] += pp[r][3];                  // l + 8
-                    float x = pp[r][0] + pp[r][1];                               // l + 4
+                    pp[r][0] += pp[r][2]; pp[r][1] += pp[r][3];                  // l + 16
+                    float x = pp[r][0] + pp[r][1];                               // l + 8
+                    x += __shfl_xor_sync(0xffffffffu, x, 4);                     // l + 4
                     x += __shfl_xor_sync(0xffffffffu, x, 2);                     // l + 2
                     x += __shfl_xor_sync(0xffffffffu, x, 1);                     // l + 1
                     d[r] = (vv[r] - x) * beta;
                 }
 #pragma unroll
-                for (int i = 0; i < 8; i++) {
-                    const int l = j4 + 4 * i;
+                for (int i = 0; i < 4; i++) {
+                    const int l = j8 + 8 * i;
                     const float4 k4 = *reinterpret_cast<const float4*>(&sm.ks[buf][tt][4 * l]);
                     const float4 q4 = *reinterpret_cast<const float4*>(&sm.qs[buf][tt][4 * l]);
 #pragma unroll
@@ -408,44 +406,34 @@ __global__ void __launch_bounds__(256, 1) kda_chunk_kernel(const KdaChunkParams 
                 float o[4];
 #pragma unroll
                 for (int r = 0; r < 4; r++) {
-#pragma unroll
-                    for (int i = 0; i < 4; i++) pp[r][i] += pp[r][i + 4];
                     pp[r][0] += pp[r][2]; pp[r][1] += pp[r][3];
                     float x = pp[r][0] + pp[r][1];
+                    x += __shfl_xor_sync(0xffffffffu, x, 4);
                     x += __shfl_xor_sync(0xffffffffu, x, 2);
                     x += __shfl_xor_sync(0xffffffffu, x, 1);
                     o[r] = x;
                 }
-                if (j4 == 0) *reinterpret_cast<float4*>(&sm.ys[buf][tt][4 * vg]) = make_float4(o[0], o[1], o[2], o[3]);
+                if (j8 == 0) *reinterpret_cast<float4*>(&sm.ys[buf][tt][4 * vg]) = make_float4(o[0], o[1], o[2], o[3]);
             }
-#if defined(VK_TRACE) && VK_TRACE == 4
-            const long long t_before = clock64();
-#endif
             __syncthreads();                               // group g + 1 is prepared, ys of group g are in place
-#if defined(VK_TRACE) && VK_TRACE == 4
-            t_wait += clock64() - t_before;
-#endif
         }
-#if defined(VK_TRACE) && VK_TRACE == 4
-        if (threadIdx.x == 0) {
-            const int cta = ((blockIdx.y * gridDim.x) + blockIdx.x) & 4095;
-            g_vk_trace[cta * 16 + 2] = clock64();
-            g_vk_trace[cta * 16 + 3] = t_wait;
-            g_vk_trace[cta * 16 + 4] = t_mark;
-        }
-#endif
+        VK_TS(4, 2);
         if (cp.write_state) {
 #pragma unroll
             for (int r = 0; r < 4; r++)
 #pragma unroll
-                for (int i = 0; i < 8; i++)
-                    *reinterpret_cast<float4*>(Sbase + r * 128 + 4 * (j4 + 4 * i)) =
+                for (int i = 0; i < 4; i++)
+                    *reinterpret_cast<float4*>(Sbase + r * 128 + 4 * (j8 + 8 * i)) =
                         make_float4(st[r][i][0], st[r][i][1], st[r][i][2], st[r][i][3]);
         }
         return;
     }
 
-    // ---------------------------------------------------------------------------------------------- the front half
+    // ---------------------------------------------------------------------------------------------- the front groups
+    const int fg = (threadIdx.x - 256) >> 7;             // this group's tokens of every token group: 4 fg .. 4 fg + 3
+    const int c = threadIdx.x & 127, lane = c & 31, warp = c >> 5;
+    const int rep = p.HV / p.Hk, hk = hv / rep;
+    const int KD = p.Hk * 128, C = 2 * KD + p.HV * 128;
     const int ch[3] = {hk * 128 + c, KD + hk * 128 + c, 2 * KD + hv * 128 + c};
     const uint4* fup = reinterpret_cast<const uint4*>(p.w_fup) + (size_t)hv * (p.rank / 8) * 128 + c;
     float4 cw[3];
@@ -453,12 +441,6 @@ __global__ void __launch_bounds__(256, 1) kda_chunk_kernel(const KdaChunkParams 
     for (int i = 0; i < 3; i++) cw[i] = *reinterpret_cast<const float4*>(p.conv_w + (size_t)ch[i] * 4);
     const float a_log = p.A_log[hv], dtb = p.dt_bias[hv * 128 + c], nw = bf2f(p.norm_w[c]);
     const __nv_bfloat16* wb = p.w_b + (size_t)hv * p.D;
-    uint4 wbv[kBdotPieces];
-#pragma unroll
-    for (int i = 0; i < kBdotPieces; i++) {
-        const int k = c * 8 + i * 1024;
-        wbv[i] = k < p.D ? *reinterpret_cast<const uint4*>(wb + k) : make_uint4(0u, 0u, 0u, 0u);
-    }
     pdl_wait();
     const int n_tok = cp.accept != nullptr ? min(max(cp.accept[b], 0), T) : T;
     const int n_grp = (n_tok + kChunkTok - 1) / kChunkTok;
@@ -466,188 +448,185 @@ __global__ void __launch_bounds__(256, 1) kda_chunk_kernel(const KdaChunkParams 
     const int par = *p.parity & 1;
     const __nv_bfloat16* conv_in = p.conv + (size_t)par * p.conv_stride;
     __nv_bfloat16* conv_out = p.conv + (size_t)(1 - par) * p.conv_stride;
-    __nv_bfloat16 win[3][3];      // the three inputs in front of the next token of this thread's q / k / v channels
-#pragma unroll
-    for (int i = 0; i < 3; i++) {
-        const size_t cb = (size_t)b * 3 * C + ch[i];
-        win[i][0] = conv_in[cb]; win[i][1] = conv_in[cb + C]; win[i][2] = conv_in[cb + 2 * (size_t)C];
-    }
+    // input of channel kind i at chunk position tau: a row of proj, or (tau < 0) the conv window in front of the chunk
+    auto xin = [&](int i, int tau) -> __nv_bfloat16 {
+        return tau >= 0 ? p.proj[(row0 + tau) * p.ldp + ch[i]] : conv_in[(size_t)b * 3 * C + ch[i] + (size_t)(3 + tau) * C];
+    };
+    constexpr int kFront = kChunkTok / 2;                  // tokens of a token group per front group
 
-#if defined(VK_TRACE) && VK_TRACE == 4
-#define KDA_FS(i) do { if (threadIdx.x == 128 && g == 1) g_vk_trace[((((blockIdx.y * gridDim.x) + blockIdx.x) & 4095) * 16) + (i)] = clock64(); } while (0)
-#else
-#define KDA_FS(i) do { } while (0)
-#endif
-    // (A) of one group into buffer `buf`: conv + SiLU, the two norms, decay, beta
+    // (A) of this front group's tokens of token group g, into buffer `buf`: conv + SiLU, the two norms, decay, beta
     auto prepare = [&](int g, int buf) {
-        KDA_FS(5);
-        const int t0 = g * kChunkTok;
-        const int nt = min(kChunkTok, n_tok - t0);
-        constexpr int kHalf = kChunkTok / 2;
-#pragma unroll 1
-        for (int h0 = 0; h0 < kChunkTok; h0 += kHalf) {     // four tokens at a time, stage by stage, so that the
-            // tokens' dependent chains (loads, exp / divide, fma chains, shuffle trees) run side by side
-            __nv_bfloat16 x3[kHalf][3];
-            uint4 hx[kHalf][kBdotPieces];
-            __nv_bfloat16 fdv[kHalf][2];                    // rank <= 256: at most two f_down values per thread
+        const int t0 = g * kChunkTok + kFront * fg;        // chunk position of the first of them
+        const int nt = min(kFront, n_tok - t0);            // (<= 0: nothing to do but the barriers)
+        if (nt > 0) {
+            __nv_bfloat16 xs[3][kFront + 3];               // the inputs t0 - 3 .. t0 + 3 of the thread's three channels
 #pragma unroll
-            for (int u = 0; u < kHalf; u++) {
-                const int tt = h0 + u;
-                if (tt < nt) {
-                    const size_t rowi = row0 + t0 + tt;
-                    const __nv_bfloat16* pr = p.proj + rowi * p.ldp;
-                    const __nv_bfloat16* hb = p.h + rowi * p.D;
+            for (int i = 0; i < 3; i++)
 #pragma unroll
-                    for (int i = 0; i < 3; i++) x3[u][i] = pr[ch[i]];
+                for (int m = 0; m < kFront + 3; m++)
+                    if (m < nt + 3) xs[i][m] = xin(i, t0 - 3 + m);
+            float s3[kFront][3], bdot[kFront];
 #pragma unroll
-                    for (int i = 0; i < kBdotPieces; i++) {
-                        const int k = c * 8 + i * 1024;
-                        hx[u][i] = k < p.D ? *reinterpret_cast<const uint4*>(hb + k) : make_uint4(0u, 0u, 0u, 0u);
-                    }
-#pragma unroll
-                    for (int i = 0; i < 2; i++)
-                        if (c + 128 * i < p.rank) fdv[u][i] = pr[p.off_fd + c + 128 * i];
-                }
-            }
-            KDA_FS(6 + (h0 ? 2 : 0));
-            float s3[kHalf][3], bdot[kHalf];
-#pragma unroll
-            for (int u = 0; u < kHalf; u++) {
-                const int tt = h0 + u;
+            for (int u = 0; u < kFront; u++) {
                 bdot[u] = 0.f;
 #pragma unroll
-                for (int i = 0; i < 3; i++) s3[u][i] = 0.f;
-                if (tt < nt) {
-#pragma unroll
-                    for (int i = 0; i < 2; i++)
-                        if (c + 128 * i < p.rank) sm.fd[tt][c + 128 * i] = bf2f(fdv[u][i]);
-#pragma unroll
-                    for (int i = 0; i < 3; i++) {
-                        float acc = __fmul_rn(bf2f(win[i][0]), cw[i].x);
-                        acc = __fadd_rn(acc, __fmul_rn(bf2f(win[i][1]), cw[i].y));
-                        acc = __fadd_rn(acc, __fmul_rn(bf2f(win[i][2]), cw[i].z));
-                        acc = __fadd_rn(acc, __fmul_rn(bf2f(x3[u][i]), cw[i].w));
+                for (int i = 0; i < 3; i++) {
+                    s3[u][i] = 0.f;
+                    if (u < nt) {
+                        float acc = __fmul_rn(bf2f(xs[i][u]), cw[i].x);
+                        acc = __fadd_rn(acc, __fmul_rn(bf2f(xs[i][u + 1]), cw[i].y));
+                        acc = __fadd_rn(acc, __fmul_rn(bf2f(xs[i][u + 2]), cw[i].z));
+                        acc = __fadd_rn(acc, __fmul_rn(bf2f(xs[i][u + 3]), cw[i].w));
                         s3[u][i] = bfr(acc / (1.f + expf(-acc)));
-                        win[i][0] = win[i][1]; win[i][1] = win[i][2]; win[i][2] = x3[u][i];
                     }
-                    float bd = 0.f;
+                }
+            }
 #pragma unroll
-                    for (int i = 0; i < kBdotPieces; i++) {
-                        const uint4 wv = wbv[i];
-                        const uint4 xv = hx[u][i];
-                        bd = fmaf(bf_lo(wv.x), bf_lo(xv.x), bd); bd = fmaf(bf_hi(wv.x), bf_hi(xv.x), bd);
-                        bd = fmaf(bf_lo(wv.y), bf_lo(xv.y), bd); bd = fmaf(bf_hi(wv.y), bf_hi(xv.y), bd);
-                        bd = fmaf(bf_lo(wv.z), bf_lo(xv.z), bd); bd = fmaf(bf_hi(wv.z), bf_hi(xv.z), bd);
-                        bd = fmaf(bf_lo(wv.w), bf_lo(xv.w), bd); bd = fmaf(bf_hi(wv.w), bf_hi(xv.w), bd);
+            for (int sb = 0; sb < kFront; sb += 2) {       // beta's dot and f_down, two tokens at a time
+                uint4 hx[2][kBdotPieces];
+                __nv_bfloat16 fdv[2][2];                   // rank <= 256: at most two f_down values per thread
+#pragma unroll
+                for (int v = 0; v < 2; v++) {
+                    if (sb + v < nt) {
+                        const size_t rowi = row0 + t0 + sb + v;
+                        const __nv_bfloat16* hb = p.h + rowi * p.D;
+#pragma unroll
+                        for (int i = 0; i < kBdotPieces; i++) {
+                            const int k = c * 8 + i * 1024;
+                            hx[v][i] = k < p.D ? *reinterpret_cast<const uint4*>(hb + k) : make_uint4(0u, 0u, 0u, 0u);
+                        }
+#pragma unroll
+                        for (int i = 0; i < 2; i++)
+                            if (c + 128 * i < p.rank) fdv[v][i] = p.proj[rowi * p.ldp + p.off_fd + c + 128 * i];
                     }
-                    const __nv_bfloat16* hb = p.h + (row0 + t0 + tt) * p.D;
-                    for (int k = c * 8 + kBdotPieces * 1024; k < p.D; k += 1024) {   // (hidden sizes beyond 5120)
-                        const uint4 wv = *reinterpret_cast<const uint4*>(wb + k);
-                        const uint4 xv = *reinterpret_cast<const uint4*>(hb + k);
-                        bd = fmaf(bf_lo(wv.x), bf_lo(xv.x), bd); bd = fmaf(bf_hi(wv.x), bf_hi(xv.x), bd);
-                        bd = fmaf(bf_lo(wv.y), bf_lo(xv.y), bd); bd = fmaf(bf_hi(wv.y), bf_hi(xv.y), bd);
-                        bd = fmaf(bf_lo(wv.z), bf_lo(xv.z), bd); bd = fmaf(bf_hi(wv.z), bf_hi(xv.z), bd);
-                        bd = fmaf(bf_lo(wv.w), bf_lo(xv.w), bd); bd = fmaf(bf_hi(wv.w), bf_hi(xv.w), bd);
+                }
+#pragma unroll
+                for (int v = 0; v < 2; v++) {
+                    const int u = sb + v, tt = kFront * fg + u;
+                    if (u < nt) {
+#pragma unroll
+                        for (int i = 0; i < 2; i++)
+                            if (c + 128 * i < p.rank) sm.fd[tt][c + 128 * i] = bf2f(fdv[v][i]);
+                        float bd = 0.f;
+#pragma unroll
+                        for (int i = 0; i < kBdotPieces; i++) {
+                            const int k = c * 8 + i * 1024;    // (the weight row's pieces stay in L1 from token to token)
+                            const uint4 wv = k < p.D ? *reinterpret_cast<const uint4*>(wb + k) : make_uint4(0u, 0u, 0u, 0u);
+                            const uint4 xv = hx[v][i];
+                            bd = fmaf(bf_lo(wv.x), bf_lo(xv.x), bd); bd = fmaf(bf_hi(wv.x), bf_hi(xv.x), bd);
+                            bd = fmaf(bf_lo(wv.y), bf_lo(xv.y), bd); bd = fmaf(bf_hi(wv.y), bf_hi(xv.y), bd);
+                            bd = fmaf(bf_lo(wv.z), bf_lo(xv.z), bd); bd = fmaf(bf_hi(wv.z), bf_hi(xv.z), bd);
+                            bd = fmaf(bf_lo(wv.w), bf_lo(xv.w), bd); bd = fmaf(bf_hi(wv.w), bf_hi(xv.w), bd);
+                        }
+                        const __nv_bfloat16* hb = p.h + (row0 + t0 + u) * p.D;
+                        for (int k = c * 8 + kBdotPieces * 1024; k < p.D; k += 1024) {   // (hidden sizes beyond 5120)
+                            const uint4 wv = *reinterpret_cast<const uint4*>(wb + k);
+                            const uint4 xv = *reinterpret_cast<const uint4*>(hb + k);
+                            bd = fmaf(bf_lo(wv.x), bf_lo(xv.x), bd); bd = fmaf(bf_hi(wv.x), bf_hi(xv.x), bd);
+                            bd = fmaf(bf_lo(wv.y), bf_lo(xv.y), bd); bd = fmaf(bf_hi(wv.y), bf_hi(xv.y), bd);
+                            bd = fmaf(bf_lo(wv.z), bf_lo(xv.z), bd); bd = fmaf(bf_hi(wv.z), bf_hi(xv.z), bd);
+                            bd = fmaf(bf_lo(wv.w), bf_lo(xv.w), bd); bd = fmaf(bf_hi(wv.w), bf_hi(xv.w), bd);
+                        }
+                        bdot[u] = bd;
+                        sm.qs[buf][tt][c] = s3[u][0]; sm.ks[buf][tt][c] = s3[u][1]; sm.vs[buf][tt][c] = s3[u][2];
                     }
-                    bdot[u] = bd;
-                    sm.qs[buf][tt][c] = s3[u][0]; sm.ks[buf][tt][c] = s3[u][1]; sm.vs[buf][tt][c] = s3[u][2];
                 }
             }
             // the twelve warp sums of the four tokens, level by level (each sum is the xor tree of warp_sum)
-            float ws[kHalf][3];
+            float ws[kFront][3];
 #pragma unroll
-            for (int u = 0; u < kHalf; u++) { ws[u][0] = s3[u][0] * s3[u][0]; ws[u][1] = s3[u][1] * s3[u][1]; ws[u][2] = bdot[u]; }
+            for (int u = 0; u < kFront; u++) { ws[u][0] = s3[u][0] * s3[u][0]; ws[u][1] = s3[u][1] * s3[u][1]; ws[u][2] = bdot[u]; }
 #pragma unroll
             for (int o = 16; o > 0; o >>= 1)
 #pragma unroll
-                for (int u = 0; u < kHalf; u++)
+                for (int u = 0; u < kFront; u++)
 #pragma unroll
                     for (int i = 0; i < 3; i++) ws[u][i] += __shfl_xor_sync(0xffffffffu, ws[u][i], o);
 #pragma unroll
-            for (int u = 0; u < kHalf; u++) {
-                const int tt = h0 + u;
-                if (tt < nt && lane == 0) {
+            for (int u = 0; u < kFront; u++) {
+                const int tt = kFront * fg + u;
+                if (u < nt && lane == 0) {
                     sm.red[3 * tt][warp] = ws[u][0]; sm.red[3 * tt + 1][warp] = ws[u][1]; sm.red[3 * tt + 2][warp] = ws[u][2];
                 }
             }
-            KDA_FS(7 + (h0 ? 2 : 0));
         }
-        front_barrier();
-        KDA_FS(10);
-        // the decay's low-rank product for all tokens of the group at once: f_up is read once per group, and the
-        // tokens' fma chains (each in the order of kda_step_kernel) run side by side
-        float av[kChunkTok];
+        front_barrier(fg);
+        if (nt > 0) {
+            // the decay's low-rank product for the four tokens at once: f_up is read once, and the tokens' fma chains
+            // (each in the order of kda_step_kernel) run side by side
+            float av[kFront];
 #pragma unroll
-        for (int tt = 0; tt < kChunkTok; tt++) av[tt] = 0.f;
-        uint4 wnext = fup[0];
-        for (int r = 0; r < p.rank; r += 8) {
-            const uint4 wv = wnext;
-            if (r + 8 < p.rank) wnext = fup[(size_t)(r / 8 + 1) * 128];      // in flight while this piece is used
-            const float w8[8] = {bf_lo(wv.x), bf_hi(wv.x), bf_lo(wv.y), bf_hi(wv.y), bf_lo(wv.z), bf_hi(wv.z), bf_lo(wv.w), bf_hi(wv.w)};
+            for (int u = 0; u < kFront; u++) av[u] = 0.f;
+            uint4 wnext = fup[0];
+            for (int r = 0; r < p.rank; r += 8) {
+                const uint4 wv = wnext;
+                if (r + 8 < p.rank) wnext = fup[(size_t)(r / 8 + 1) * 128];      // in flight while this piece is used
+                const float w8[8] = {bf_lo(wv.x), bf_hi(wv.x), bf_lo(wv.y), bf_hi(wv.y), bf_lo(wv.z), bf_hi(wv.z), bf_lo(wv.w), bf_hi(wv.w)};
 #pragma unroll
-            for (int tt = 0; tt < kChunkTok; tt++) {
-                const float4 f0 = *reinterpret_cast<const float4*>(&sm.fd[tt][r]);
-                const float4 f1 = *reinterpret_cast<const float4*>(&sm.fd[tt][r + 4]);
-                float a = av[tt];
-                a = fmaf(w8[0], f0.x, a); a = fmaf(w8[1], f0.y, a); a = fmaf(w8[2], f0.z, a); a = fmaf(w8[3], f0.w, a);
-                a = fmaf(w8[4], f1.x, a); a = fmaf(w8[5], f1.y, a); a = fmaf(w8[6], f1.z, a); a = fmaf(w8[7], f1.w, a);
-                av[tt] = a;
+                for (int u = 0; u < kFront; u++) {
+                    const int tt = kFront * fg + u;
+                    const float4 f0 = *reinterpret_cast<const float4*>(&sm.fd[tt][r]);
+                    const float4 f1 = *reinterpret_cast<const float4*>(&sm.fd[tt][r + 4]);
+                    float a = av[u];
+                    a = fmaf(w8[0], f0.x, a); a = fmaf(w8[1], f0.y, a); a = fmaf(w8[2], f0.z, a); a = fmaf(w8[3], f0.w, a);
+                    a = fmaf(w8[4], f1.x, a); a = fmaf(w8[5], f1.y, a); a = fmaf(w8[6], f1.z, a); a = fmaf(w8[7], f1.w, a);
+                    av[u] = a;
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < kFront; u++) {
+                const int tt = kFront * fg + u;
+                if (u < nt) {
+                    const float ssq = ((sm.red[3 * tt][0] + sm.red[3 * tt][1]) + sm.red[3 * tt][2]) + sm.red[3 * tt][3];
+                    const float ssk = ((sm.red[3 * tt + 1][0] + sm.red[3 * tt + 1][1]) + sm.red[3 * tt + 1][2]) + sm.red[3 * tt + 1][3];
+                    const float bd = ((sm.red[3 * tt + 2][0] + sm.red[3 * tt + 2][1]) + sm.red[3 * tt + 2][2]) + sm.red[3 * tt + 2][3];
+                    sm.qs[buf][tt][c] = (sm.qs[buf][tt][c] / sqrtf(ssq + 1e-6f)) * 0.08838834764831845f;  // 128^-1/2
+                    sm.ks[buf][tt][c] = sm.ks[buf][tt][c] / sqrtf(ssk + 1e-6f);
+                    const float a = bfr(av[u]);
+                    sm.gs[buf][tt][c] = expf(-expf(a_log) * softplus_f(a + dtb));
+                    if (c == 0) sm.betas[buf][tt] = 1.f / (1.f + expf(-bfr(bd)));
+                }
             }
         }
-        KDA_FS(11);
-#pragma unroll
-        for (int tt = 0; tt < kChunkTok; tt++) {
-            if (tt < nt) {
-                const float ssq = ((sm.red[3 * tt][0] + sm.red[3 * tt][1]) + sm.red[3 * tt][2]) + sm.red[3 * tt][3];
-                const float ssk = ((sm.red[3 * tt + 1][0] + sm.red[3 * tt + 1][1]) + sm.red[3 * tt + 1][2]) + sm.red[3 * tt + 1][3];
-                const float bd = ((sm.red[3 * tt + 2][0] + sm.red[3 * tt + 2][1]) + sm.red[3 * tt + 2][2]) + sm.red[3 * tt + 2][3];
-                sm.qs[buf][tt][c] = (sm.qs[buf][tt][c] / sqrtf(ssq + 1e-6f)) * 0.08838834764831845f;  // 128^-1/2
-                sm.ks[buf][tt][c] = sm.ks[buf][tt][c] / sqrtf(ssk + 1e-6f);
-                const float a = bfr(av[tt]);
-                sm.gs[buf][tt][c] = expf(-expf(a_log) * softplus_f(a + dtb));
-                if (c == 0) sm.betas[buf][tt] = 1.f / (1.f + expf(-bfr(bd)));
-            }
-        }
-        KDA_FS(12);
-        front_barrier();      // (fd and red are free for the next group)
+        front_barrier(fg);      // (fd and red of these tokens are free for the next token group)
     };
 
-    // (C) of one group: gated norm of the outputs the recurrence left in ys[buf]
+    // (C) of this front group's tokens of token group g: gated norm of the outputs the recurrence left in ys[buf]
     auto finish = [&](int g, int buf) {
-        const int t0 = g * kChunkTok;
-        const int nt = min(kChunkTok, n_tok - t0);
-        float zv[kChunkTok], yv[kChunkTok];
+        const int t0 = g * kChunkTok + kFront * fg;
+        const int nt = min(kFront, n_tok - t0);
+        float zv[kFront], yv[kFront], wy[kFront];
 #pragma unroll
-        for (int tt = 0; tt < kChunkTok; tt++) {          // the gate inputs of the whole group are fetched together
-            if (tt < nt) zv[tt] = bf2f(p.proj[(row0 + t0 + tt) * p.ldp + p.off_z + hv * 128 + c]);
+        for (int u = 0; u < kFront; u++) {                 // the gate inputs are fetched together
+            zv[u] = 0.f;
+            if (u < nt) zv[u] = bf2f(p.proj[(row0 + t0 + u) * p.ldp + p.off_z + hv * 128 + c]);
         }
-        float wy[kChunkTok];
 #pragma unroll
-        for (int tt = 0; tt < kChunkTok; tt++) {
-            yv[tt] = tt < nt ? bfr(sm.ys[buf][tt][c]) : 0.f;
-            wy[tt] = yv[tt] * yv[tt];
+        for (int u = 0; u < kFront; u++) {
+            yv[u] = u < nt ? bfr(sm.ys[buf][kFront * fg + u][c]) : 0.f;
+            wy[u] = yv[u] * yv[u];
         }
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1)
 #pragma unroll
-            for (int tt = 0; tt < kChunkTok; tt++) wy[tt] += __shfl_xor_sync(0xffffffffu, wy[tt], o);
+            for (int u = 0; u < kFront; u++) wy[u] += __shfl_xor_sync(0xffffffffu, wy[u], o);
 #pragma unroll
-        for (int tt = 0; tt < kChunkTok; tt++)
-            if (tt < nt && lane == 0) sm.red[3 * kChunkTok + tt][warp] = wy[tt];
-        front_barrier();
+        for (int u = 0; u < kFront; u++)
+            if (u < nt && lane == 0) sm.red[3 * kChunkTok + kFront * fg + u][warp] = wy[u];
+        front_barrier(fg);
 #pragma unroll
-        for (int tt = 0; tt < kChunkTok; tt++) {
-            if (tt < nt) {
-                const float* rr = sm.red[3 * kChunkTok + tt];
+        for (int u = 0; u < kFront; u++) {
+            if (u < nt) {
+                const float* rr = sm.red[3 * kChunkTok + kFront * fg + u];
                 float ss = 0.f;
                 ss += rr[0]; ss += rr[1]; ss += rr[2]; ss += rr[3];
                 const float inv = rsqrtf(ss * (1.f / 128.f) + p.eps);
-                const float z = zv[tt];
-                const float ov = bfr(((yv[tt] * inv) * nw) * (z / (1.f + expf(-z))));
-                p.out[(row0 + t0 + tt) * p.HV * 128 + hv * 128 + c] = f2bf(ov);
+                const float z = zv[u];
+                const float ov = bfr(((yv[u] * inv) * nw) * (z / (1.f + expf(-z))));
+                p.out[(row0 + t0 + u) * p.HV * 128 + hv * 128 + c] = f2bf(ov);
             }
         }
-        front_barrier();
+        front_barrier(fg);
     };
 
     if (n_grp > 0) prepare(0, 0);
@@ -659,14 +638,14 @@ __global__ void __launch_bounds__(256, 1) kda_chunk_kernel(const KdaChunkParams 
         __syncthreads();                                   // group g's outputs are in ys[buf]
     }
     if (n_grp > 0) finish(n_grp - 1, (n_grp - 1) & 1);
-    if (!cp.write_state) return;
+    if (!cp.write_state || fg != 0) return;
+    // the conv window behind the chunk: the last three inputs of the thread's channels
 #pragma unroll
     for (int i = 0; i < 3; i++) {
         if (i == 2 || hv % rep == 0) {
             const size_t cb = (size_t)b * 3 * C + ch[i];
-            conv_out[cb] = win[i][0];
-            conv_out[cb + C] = win[i][1];
-            conv_out[cb + 2 * (size_t)C] = win[i][2];
+#pragma unroll
+            for (int m = 0; m < 3; m++) conv_out[cb + (size_t)m * C] = xin(i, n_tok - 3 + m);
         }
     }
 }
@@ -725,7 +704,7 @@ int vk_kda_chunk_ragged(const void* proj, int ldp, int off_z, int off_fd, const 
         VK_CUDA(cudaFuncSetAttribute(kda_chunk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(KdaChunkSmem)));
         configured = true;
     }
-    return (int)vk_launch(kda_chunk_kernel, dim3(HV, B), dim3(256), sizeof(KdaChunkSmem), stream, cp);
+    return (int)vk_launch(kda_chunk_kernel, dim3(HV, B), dim3(512), sizeof(KdaChunkSmem), stream, cp);
 }
 
 int vk_kda_chunk(const void* proj, int ldp, int off_z, int off_fd, const void* h, const void* w_b, const void* w_fup,
