@@ -481,10 +481,10 @@ __global__ void __launch_bounds__(512, 1) kda_chunk_kernel(const KdaChunkParams 
                     }
                 }
             }
-            __nv_bfloat16 fdv[kFront][2];                  // rank <= 256: at most two f_down values per thread
 #pragma unroll
-            for (int sb = 0; sb < kFront; sb += 2) {       // beta's dot and f_down, two tokens at a time (no store to
-                uint4 hx[2][kBdotPieces];                   // shared memory in between: the loads may run ahead)
+            for (int sb = 0; sb < kFront; sb += 2) {       // beta's dot and f_down, two tokens at a time
+                uint4 hx[2][kBdotPieces];
+                __nv_bfloat16 fdv[2][2];                   // rank <= 256: at most two f_down values per thread
 #pragma unroll
                 for (int v = 0; v < 2; v++) {
                     if (sb + v < nt) {
@@ -497,13 +497,16 @@ __global__ void __launch_bounds__(512, 1) kda_chunk_kernel(const KdaChunkParams 
                         }
 #pragma unroll
                         for (int i = 0; i < 2; i++)
-                            if (c + 128 * i < p.rank) fdv[sb + v][i] = p.proj[rowi * p.ldp + p.off_fd + c + 128 * i];
+                            if (c + 128 * i < p.rank) fdv[v][i] = p.proj[rowi * p.ldp + p.off_fd + c + 128 * i];
                     }
                 }
 #pragma unroll
                 for (int v = 0; v < 2; v++) {
-                    const int u = sb + v;
+                    const int u = sb + v, tt = kFront * fg + u;
                     if (u < nt) {
+#pragma unroll
+                        for (int i = 0; i < 2; i++)
+                            if (c + 128 * i < p.rank) sm.fd[tt][c + 128 * i] = bf2f(fdv[v][i]);
                         float bd = 0.f;
 #pragma unroll
                         for (int i = 0; i < kBdotPieces; i++) {
@@ -525,17 +528,8 @@ __global__ void __launch_bounds__(512, 1) kda_chunk_kernel(const KdaChunkParams 
                             bd = fmaf(bf_lo(wv.w), bf_lo(xv.w), bd); bd = fmaf(bf_hi(wv.w), bf_hi(xv.w), bd);
                         }
                         bdot[u] = bd;
+                        sm.qs[buf][tt][c] = s3[u][0]; sm.ks[buf][tt][c] = s3[u][1]; sm.vs[buf][tt][c] = s3[u][2];
                     }
-                }
-            }
-#pragma unroll
-            for (int u = 0; u < kFront; u++) {
-                const int tt = kFront * fg + u;
-                if (u < nt) {
-#pragma unroll
-                    for (int i = 0; i < 2; i++)
-                        if (c + 128 * i < p.rank) sm.fd[tt][c + 128 * i] = bf2f(fdv[u][i]);
-                    sm.qs[buf][tt][c] = s3[u][0]; sm.ks[buf][tt][c] = s3[u][1]; sm.vs[buf][tt][c] = s3[u][2];
                 }
             }
             // the twelve warp sums of the four tokens, level by level (each sum is the xor tree of warp_sum)
@@ -598,20 +592,15 @@ __global__ void __launch_bounds__(512, 1) kda_chunk_kernel(const KdaChunkParams 
     };
 
     // (C) of this front group's tokens of token group g: gated norm of the outputs the recurrence left in ys[buf]
-    // the gate inputs z of this front group's tokens of token group g (fetched early: a preparation lies in between)
-    auto gate_in = [&](int g, __nv_bfloat16 (&zb)[kFront]) {
-        const int t0 = g * kChunkTok + kFront * fg;
-        const int nt = min(kFront, n_tok - t0);
-#pragma unroll
-        for (int u = 0; u < kFront; u++)
-            if (u < nt) zb[u] = p.proj[(row0 + t0 + u) * p.ldp + p.off_z + hv * 128 + c];
-    };
-    auto finish = [&](int g, int buf, const __nv_bfloat16 (&zb)[kFront]) {
+    auto finish = [&](int g, int buf) {
         const int t0 = g * kChunkTok + kFront * fg;
         const int nt = min(kFront, n_tok - t0);
         float zv[kFront], yv[kFront], wy[kFront];
 #pragma unroll
-        for (int u = 0; u < kFront; u++) zv[u] = u < nt ? bf2f(zb[u]) : 0.f;
+        for (int u = 0; u < kFront; u++) {                 // the gate inputs are fetched together
+            zv[u] = 0.f;
+            if (u < nt) zv[u] = bf2f(p.proj[(row0 + t0 + u) * p.ldp + p.off_z + hv * 128 + c]);
+        }
 #pragma unroll
         for (int u = 0; u < kFront; u++) {
             yv[u] = u < nt ? bfr(sm.ys[buf][kFront * fg + u][c]) : 0.f;
@@ -642,18 +631,13 @@ __global__ void __launch_bounds__(512, 1) kda_chunk_kernel(const KdaChunkParams 
 
     if (n_grp > 0) prepare(0, 0);
     __syncthreads();                                       // group 0 is prepared
-    __nv_bfloat16 zb[kFront];
     for (int g = 0; g < n_grp; g++) {
         const int buf = g & 1;
-        if (g > 0) gate_in(g - 1, zb);
         if (g + 1 < n_grp) prepare(g + 1, buf ^ 1);        // while the back half runs group g
-        if (g > 0) finish(g - 1, buf ^ 1, zb);
+        if (g > 0) finish(g - 1, buf ^ 1);
         __syncthreads();                                   // group g's outputs are in ys[buf]
     }
-    if (n_grp > 0) {
-        gate_in(n_grp - 1, zb);
-        finish(n_grp - 1, (n_grp - 1) & 1, zb);
-    }
+    if (n_grp > 0) finish(n_grp - 1, (n_grp - 1) & 1);
     if (!cp.write_state || fg != 0) return;
     // the conv window behind the chunk: the last three inputs of the thread's channels
 #pragma unroll
