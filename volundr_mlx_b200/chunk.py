@@ -85,9 +85,7 @@ class ChunkHandle:
 def _get_scratch(model, bc, R):
     """Scratch for R rows: the smallest power-of-two capacity that holds them, the last few capacities kept. It lives
     on the cache object, so it can never outlive the shapes it was made for."""
-    cap = 16
-    while cap < R:
-        cap *= 2
+    cap = scratch_capacity(R)
     held = bc.__dict__.setdefault("_chunk_scratch", {})
     if cap in held:
         held[cap] = held.pop(cap)                    # most recently used last
@@ -96,6 +94,25 @@ def _get_scratch(model, bc, R):
             held.pop(next(iter(held)))
         held[cap] = ChunkScratch(model, bc, cap)
     return held[cap]
+
+
+def virtual_rows(lens, device=None):
+    """The layout of a chunk's virtual rows: request b brings lens[b] tokens and owns the rows off[b] .. off[b] +
+    lens[b] - 1. Returns (off [B] int32, rows [R] long: the request of every virtual row, tpos [R] long: its token
+    index within the request)."""
+    lens_t = torch.tensor(list(lens), dtype=torch.long, device=device)
+    off = torch.cumsum(lens_t, 0) - lens_t
+    rows = torch.arange(len(lens), device=device).repeat_interleave(lens_t)
+    tpos = torch.arange(int(lens_t.sum()), device=device) - off[rows]
+    return off.to(torch.int32), rows, tpos
+
+
+def scratch_capacity(R: int) -> int:
+    """Rows of the scratch that serves a chunk of R virtual rows: the next power of two, at least 16."""
+    cap = 16
+    while cap < R:
+        cap *= 2
+    return cap
 
 
 def _open_pages(bc, lens):
@@ -134,9 +151,6 @@ def forward_chunk(model, bc, toks, write=False, logits_at=None):
     ragged = min(lens) != T
     if ragged and logits_at is None:
         logits_at = [n - 1 for n in lens]
-    off = [0] * B
-    for b in range(1, B):
-        off[b] = off[b - 1] + lens[b - 1]
     t_in = torch.tensor([row + [0] * (T - len(row)) for row in toks], dtype=torch.int32).to(dev)   # [B, T], padded
     s = _get_scratch(model, bc, R)
     BT.model_warm(model)
@@ -145,10 +159,7 @@ def forward_chunk(model, bc, toks, write=False, logits_at=None):
     eps = a.rms_norm_eps
     ck = _lib.check
     # ---- virtual rows: request and token index of each
-    lens_t = torch.tensor(lens, device=dev)
-    off_t = torch.tensor(off, dtype=torch.int32, device=dev)
-    rows = torch.arange(B, device=dev).repeat_interleave(lens_t)
-    tpos = torch.arange(R, device=dev) - off_t.long()[rows]
+    off_t, rows, tpos = virtual_rows(lens, dev)
     s.row_map[:R].copy_(rows.to(torch.int32))
     s.tok[:R].copy_(t_in[rows, tpos])
     s.pos[:R].copy_(bc.pos[:B][rows] + tpos.to(torch.int32))
