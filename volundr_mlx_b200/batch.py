@@ -473,16 +473,12 @@ def forward(model: Model, bc: BatchCache, toks, capture=()):
     return bc.logits[:B], feats
 
 
-_warm = set()
-
-
 def model_warm(model: Model):
     """Run each GEMM shape once on scratch activations so that one-time function-attribute calls happen outside
-    graph capture."""
-    key = id(model)
-    if key in _warm:
+    graph capture (once per model object)."""
+    if getattr(model, "_vk_warm", False):
         return
-    _warm.add(key)
+    model._vk_warm = True
     d = model.device
     with torch.cuda.device(d):
         _lib.check(_lib.lib().vk_kda_configure(), "vk_kda_configure")
