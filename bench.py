@@ -80,46 +80,107 @@ class ClockSampler:
 
 
 # ------------------------------------------------------------------------------------------------ CPU baseline
-def cpu_sample(steps=2, rows=B_ROWS):
-    """The CPU oracle on a bounded sample of the workload: 2 of the 72 layers (1 KDA + 1 BCSA) at full width plus
-    1/36 of the lm_head, 16 rows at short contexts; the step time is scaled by 36 to the whole model."""
-    import torch
+SAMPLE_LAYERS = 2     # layers of the bounded CPU sample (1 KDA + 1 BCSA, full width)
+SAMPLE_SCALE = 36     # 72 layers / 2; the sample also holds 1/36 of the lm_head rows
 
+
+def host_threads():
+    """All host cores for the CPU arm, set explicitly: NumPy's BLAS does not follow torch.set_num_threads, and under
+    torchrun the environment carries OMP_NUM_THREADS=1, which the BLAS read when it was loaded."""
+    cores = os.cpu_count() or 1
+    try:
+        cores = len(os.sched_getaffinity(0))
+    except (AttributeError, OSError):
+        pass
+    try:
+        from threadpoolctl import threadpool_limits
+
+        threadpool_limits(limits=cores)
+    except Exception:      # threadpoolctl missing: the BLAS keeps the thread count it was loaded with
+        pass
+    try:
+        import torch
+
+        torch.set_num_threads(cores)
+    except Exception:
+        pass
+    return cores
+
+
+def cpu_rows(orc, a, ctx, seed=4):
+    """Oracle rows that already hold the GPU arm's contexts: K/V ~ N(0, 1) (bf16 values) by position, block means pooled
+    from them, KDA state ~ N(0, 0.1), conv window ~ N(0, 1): the distributions BatchCache.fill_synthetic draws."""
+    from oracle.numerics import bf
+
+    rng = np.random.Generator(np.random.PCG64(seed))
+    rows = []
+    KVH, D, C = a.num_key_value_heads, a.head_dim, a.bcsa_compress
+    for P in ctx:
+        r = orc.new_row()
+        r.pos = int(P)
+        for i, m in enumerate(a.mixer_types):
+            st = r.layers[i]
+            if m == "kda":
+                st["conv"] = bf(rng.normal(0, 1, size=st["conv"].shape))
+                st["S"] = rng.normal(0, 0.1, size=st["S"].shape).astype(np.float32)
+                continue
+            K = bf(rng.standard_normal(size=(P, KVH, D), dtype=np.float32))
+            V = bf(rng.standard_normal(size=(P, KVH, D), dtype=np.float32))
+            st["k"], st["v"] = list(K), list(V)
+            if m == "bcsa":
+                nb = P // C
+                st["pk"] = list(bf(K[: nb * C].reshape(nb, C, KVH, D).sum(1) * np.float32(1.0 / C)))
+                st["pv"] = list(bf(V[: nb * C].reshape(nb, C, KVH, D).sum(1) * np.float32(1.0 / C)))
+        rows.append(r)
+    return rows
+
+
+def cpu_sample(steps, warmup=1, rows=B_ROWS):
+    """The CPU oracle on a bounded sample of the workload: 2 of the 72 layers (1 KDA + 1 BCSA) at full width plus 1/36
+    of the lm_head, the 16 rows at the GPU arm's contexts. Every step is really run and timed; returns the measured
+    seconds per sample step and the tokens per second of the whole model derived from it (x 36 layers' worth)."""
     from oracle.model import Oracle
     from volundr_mlx_b200 import synth
 
-    cores = os.cpu_count() or 1
-    torch.set_num_threads(cores)
-    a = synth.volundr32b_args(num_hidden_layers=2, mixer_types=["kda", "bcsa"], engram_layers=[],
+    cores = host_threads()
+    a = synth.volundr32b_args(num_hidden_layers=SAMPLE_LAYERS, mixer_types=["kda", "bcsa"], engram_layers=[],
                               vocab_size=4224, vocab_valid=4224, engram_rows=1024)
     p = synth.make_params(a, seed=4, quant=True, bias_mode="free")
     orc = Oracle(a, p, exact=False, fast=True)
-    rws = [orc.new_row() for _ in range(rows)]
+    ctx = context_lengths()[:rows]
+    rws = cpu_rows(orc, a, ctx)
     rng = np.random.default_rng(4)
-    for r in rws:  # untimed: build the weight cache and give every row a few positions
-        orc.step(r, int(rng.integers(0, a.vocab_valid)))
+    for _ in range(max(1, warmup)):  # untimed: the first one also builds the weight cache
+        for r in rws:
+            orc.step(r, int(rng.integers(0, a.vocab_valid)))
     t0 = time.perf_counter()
     for _ in range(steps):
         for r in rws:
             orc.step(r, int(rng.integers(0, a.vocab_valid)))
     dt = (time.perf_counter() - t0) / steps
-    toks = rows / (dt * 36.0)
-    return {"value": toks, "unit": "tok/s", "cores": cores, "kind": "port",
-            "sample": f"{steps} steps x {rows} rows of 2/72 layers (1 KDA + 1 BCSA, full width) + 1/36 lm_head, x36 to the full model"}
+    toks = rows / (dt * SAMPLE_SCALE)
+    return {"value": toks, "unit": "tok/s", "cores": cores, "kind": "port", "sample_step_s": dt, "sample_steps": steps,
+            "sample": f"{steps} timed steps x {rows} rows (ctx {min(ctx)}..{max(ctx)}) of {SAMPLE_LAYERS}/72 layers (1 KDA + 1 BCSA, "
+                      f"full width) + 1/{SAMPLE_SCALE} lm_head; value = {rows} rows / ({SAMPLE_SCALE} x measured seconds per sample step)"}
 
 
 def run_reference(a):
     """--impl reference: the reference's MLX CPU path cannot run here (mlx is not installed and cannot be), so the CPU
-    restatement of that path (oracle/) is what is timed, on all host threads."""
+    restatement of that path (oracle/) is what is timed, on all host threads. A step of this arm is one step of the
+    bounded sample (2 of the 72 layers + 1/36 of the lm_head, 16 rows): `steps`, `warmup` and `ms_per_step` are what was
+    really run and measured; only `value` carries the x 36 to the whole model."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
     t0 = time.perf_counter()
-    base = cpu_sample(steps=max(1, min(a.steps, 3)))
+    base = cpu_sample(steps=a.steps, warmup=a.warmup)
     line = {"impl": "reference", "metric": METRIC, "value": base["value"], "unit": "tok/s", "n_gpus": a.gpus, "steps": a.steps,
-            "warmup": a.warmup, "ms_per_step": 1e3 * B_ROWS / base["value"], "higher_is_better": True, "scaling": "strong",
+            "warmup": a.warmup, "ms_per_step": 1e3 * base["sample_step_s"], "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": "volundr-32b-shaped W4 g64, 16 ragged rows, decode step (CPU sample scaled x36)"},
+            "config": {"workload": "volundr-32b-shaped W4 g64, 16 ragged rows, decode step; one step here = the bounded CPU "
+                                   f"sample ({SAMPLE_LAYERS} of 72 layers + 1/{SAMPLE_SCALE} lm_head), value scaled x{SAMPLE_SCALE} "
+                                   "to the whole model",
+                       "reference": "MLX CPU path unavailable on this box (mlx not installable); CPU restatement timed"},
             "cpu_baseline": base, "e2e": {"value": base["value"], "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "wall_s": time.perf_counter() - t0}
     print(json.dumps(line), flush=True)
@@ -278,7 +339,7 @@ def run_ours(a):
     if rank != 0:
         leave()
         return
-    cpu = cpu_sample() if (world == 1 and not a.no_cpu) else None
+    cpu = cpu_sample(steps=8, warmup=1) if (world == 1 and not a.no_cpu) else None
     line = {
         "metric": METRIC, "value": B * 1e3 / ms_dev, "unit": "tok/s", "n_gpus": world, "steps": a.steps, "warmup": a.warmup,
         "ms_per_step": ms_dev, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",

@@ -52,7 +52,7 @@ size_t vk_w4_workspace_bytes(int M, int N, int K);
 int vk_w4_gemm(const void* packed, const void* x, int ldx, void* y, int ldy, int M, int N, int K, void* workspace,
                size_t workspace_bytes, vk_stream_t stream);
 /* The same product for activations that already sit in the kernel's input layout ("x records": per 64 columns 2176
- * bytes = 16 rows x 64 bf16 with the 16-byte pieces xor-swizzled by row, then per row the group's sum as two bf16 pairs;
+ * bytes = 16 rows x 64 bf16 with the 16-byte pieces xor-swizzled by row, then the sixteen rows' sums over the group as fp32;
  * rows >= M zero). The row kernels below write this layout directly when given an `xrec_*` pointer (as the reference
  * fuses its input preparation into the producing op, agens-mlx-bench/smallm/prep_nax.py:24-148). M <= 16. */
 int vk_w4_gemm_xrec(const void* packed, const void* xrec, void* y, int ldy, int M, int N, int K, void* workspace,
@@ -176,7 +176,7 @@ int vk_kda_pack_fup(const void* src, void* dst, int HV, int rank, vk_stream_t st
 int vk_kda_configure(void);   /* once per device, outside stream capture: shared-memory carve-out hint for vk_kda_step */
 int vk_kda_step(const void* proj, int ldp, int off_z, int off_fd, const void* h, const void* w_b, const void* w_fup,
                 const float* conv_w, const float* A_log, const float* dt_bias, const void* norm_w, void* conv,
-                const int* parity, size_t conv_stride, float* S, void* out, void* xrec_out, const float* g_override, int B,
+                const int* parity, size_t conv_stride, float* S, void* out, void* xrec_out, int B,
                 int D, int Hk, int HV, int Dk, int Dv, int rank, float eps, vk_stream_t stream);
 /* The same recurrence over a chunk of T tokens per row in one launch, the state read and written once: the prefill
  * form (kernels.gated_delta_tg, kernels.py:544-555) and the verify / commit-replay form (verify._kda,
@@ -214,6 +214,17 @@ typedef struct vk_attn_geom {
  * keys attended, window start}. */
 int vk_batch_step_begin(const int* pos, int* table, int max_pages, int* free_list, int* free_top, int* desc, int B, int W,
                         int C, int topk, vk_stream_t stream);
+/* The same allocation for a chunk of tokens per row (the verify window of batch_spec.verify_forward, batch_spec.py:107-158;
+ * a prefill chunk of session.prefill_iter, session.py:351-387): row b is about to hold positions pos[b] ..
+ * pos[b] + lens[b] - 1 and every position that starts a page takes one, rows in order. */
+int vk_pages_open(const int* pos, const int* lens, int* table, int max_pages, const int* free_list, int* free_top, int B,
+                  vk_stream_t stream);
+/* Pages back to the pool without a host round trip: item i returns the table entries [first[i], last[i]) of row rows[i]
+ * (device arrays of n ints), ascending, or descending with `reverse`; the entries become -1. Used when a commit keeps
+ * fewer tokens than the verify pass opened pages for (batch_spec.commit, batch_spec.py:173-199) and when a row leaves
+ * the batch (BatchCache.apply, batch.py:416-431). */
+int vk_pages_release(const int* rows, const int* first, const int* last, int n, int reverse, int* table, int max_pages,
+                     int* free_list, int* free_top, int n_pages, vk_stream_t stream);
 /* BatchRows.advance (batch.py:74-77): pos += 1; flips *parity. */
 int vk_batch_step_end(int* pos, int* parity, int B, vk_stream_t stream);
 /* Attention._batched up to the cache write (volundr.py:737-747; batch.py:224-259): q/k offset norms, RoPE at pos[b],
@@ -230,6 +241,17 @@ int vk_attn_prep_rows(const vk_attn_geom* g, const void* proj, int ldp, int off_
                       const void* q_norm, const void* k_norm, const void* idx_norm, const int* pos, const int* table, void* q,
                       void* qi, void* K, void* V, void* PK, void* PV, void* BK, void* IK, int B, int rope_dims,
                       double rope_theta, float eps, int mode, const int* row_map, vk_stream_t stream);
+/* vk_attn_prep_rows for the shared-indexer form of BCSA: the C-slot ring of open-block indexer keys cannot hold a chunk
+ * that spans more than one block, so the rows' normed indexer keys go to ikc [B, Di] instead, and a block that closes
+ * inside the chunk is pooled from them (plus the ring for positions in front of first_pos[b], the first position the
+ * chunk brought for row b's sequence), as BCSACache.update pools from `ci = ik_open ++ chunk keys`
+ * (batch_spec.py:140-158, volundr.py:508-533). The ring is left untouched; the caller stores the open block's keys of
+ * the tokens it keeps. ikc null: vk_attn_prep_rows. */
+int vk_attn_prep_chunk(const vk_attn_geom* g, const void* proj, int ldp, int off_k, int off_v, const void* idxq, const void* idxk,
+                       const void* q_norm, const void* k_norm, const void* idx_norm, const int* pos, const int* table, void* q,
+                       void* qi, void* K, void* V, void* PK, void* PV, void* BK, void* IK, int B, int rope_dims,
+                       double rope_theta, float eps, int mode, const int* row_map, void* ikc, const int* first_pos,
+                       vk_stream_t stream);
 /* _block_scores + _topk_blocks (volundr.py:601-618; kernels.bcsa_scores kernels.py:1227-1240, bcsa_topk :86-98):
  * sel [B, NS, topk] ascending block indices (-1 padded), nsel [B, NS]. scratch: max_blocks uint32 per (row, group). */
 int vk_attn_configure(void);   /* once per device, outside stream capture: shared-memory opt-in of the selection kernel

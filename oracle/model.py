@@ -132,9 +132,12 @@ class Row:
 
 
 class Oracle:
-    def __init__(self, args: Args, params: dict, exact: bool = False, fast: bool = False):
-        """fast=True (CPU-baseline timing only): weights dequantised and multiplied in float32 instead of float64."""
-        self.a, self.p, self.exact, self.fast = args, params, exact, fast
+    def __init__(self, args: Args, params: dict, exact: bool = False, fast: bool = False, w32: bool = False):
+        """fast=True (CPU-baseline timing only): weights dequantised and multiplied in float32 instead of float64.
+        w32=True (full-width models): weights dequantised exactly (they are bf16 values, so float32 holds them without
+        loss) but kept and multiplied in float32 instead of float64: a quarter of the memory, the product's
+        accumulation error (about 1e-6 relative) is far below the bf16 rounding that follows it."""
+        self.a, self.p, self.exact, self.fast, self.w32 = args, params, exact, fast, w32
         self.dt = np.float64 if exact else np.float32
         self._wcache = {}
 
@@ -143,14 +146,20 @@ class Oracle:
         return np.asarray(x, dtype=np.float64) if self.exact else bf(x)
 
     def weight(self, name):
-        """Dense [N, K] matrix of linear `name` (dequantised when stored as W4)."""
+        """Dense [N, K] matrix of linear `name`. A 4-bit linear multiplies by s * u + b as it is, not by its bf16
+        rounding: mx.quantized_matmul (volundr.py:185-190) materialises no weights, see oracle.w4.affine; the bf16
+        weight bf16(s u + b) is what mx.dequantize returns and is pinned separately (oracle.w4.dequant)."""
         if name not in self._wcache:
             if name + ".scales" in self.p:
-                dq = W4.dequant_fast if self.fast else W4.dequant
-                w = dq(self.p[name + ".weight"], self.p[name + ".scales"], self.p[name + ".biases"], self.a.quant_group)
+                if self.fast:
+                    w = W4.dequant_fast(self.p[name + ".weight"], self.p[name + ".scales"], self.p[name + ".biases"],
+                                        self.a.quant_group)
+                else:
+                    w = W4.affine(self.p[name + ".weight"], self.p[name + ".scales"], self.p[name + ".biases"],
+                                  self.a.quant_group, np.float32 if self.w32 else np.float64)
             else:
                 w = self.p[name + ".weight"]
-            self._wcache[name] = np.asarray(w, dtype=np.float32 if self.fast else np.float64)
+            self._wcache[name] = np.asarray(w, dtype=np.float32 if (self.fast or self.w32) else np.float64)
         return self._wcache[name]
 
     def lin(self, x, name):

@@ -33,3 +33,36 @@ def gather_row(pool, table_row, n_tokens):
     npg = (n_tokens + PAGE - 1) // PAGE
     x = pool[table_row[:npg]]                       # [npg, KVH, PAGE, D]
     return np.transpose(x, (1, 0, 2, 3)).reshape(pool.shape[1], npg * PAGE, pool.shape[3])[:, :n_tokens]
+
+
+def pages_open(pos, lens, table, free_list, free_top):
+    """Pages for a chunk: row b is about to hold positions pos[b] .. pos[b] + lens[b] - 1; every position that starts a
+    page pops one (rows in order, positions in order), exactly what lens[b] calls of step_begin would hand out row by
+    row. `table` is updated in place; returns the new free_top."""
+    top = int(free_top)
+    for b in range(len(pos)):
+        p0, p1 = int(pos[b]), int(pos[b]) + int(lens[b])
+        pi = (p0 + PAGE - 1) // PAGE
+        while pi * PAGE < p1:
+            top -= 1
+            table[b, pi] = free_list[top]
+            pi += 1
+    return top
+
+
+def pages_release(items, reverse, table, free_list, free_top):
+    """Pages back to the pool: for every (row, first, last) the table entries [first, last) that hold a page are
+    pushed onto free_list in ascending order (descending with `reverse`) and set to -1. `table` and `free_list` are
+    updated in place; returns the new free_top. (A verify pass that rejected drafts returns the pages those drafts
+    opened, batch_spec.py:160-199 has no counterpart because the reference's rows own fixed rings; a row that leaves
+    the batch, batch.py:416-431, returns all of its pages.)"""
+    top = int(free_top)
+    for b, a, z in items:
+        idx = range(z - 1, a - 1, -1) if reverse else range(a, z)
+        for pi in idx:
+            if table[b, pi] < 0:
+                continue
+            free_list[top] = table[b, pi]
+            top += 1
+            table[b, pi] = -1
+    return top

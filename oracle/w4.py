@@ -31,9 +31,21 @@ def unpack_codes(w, K):
     return u
 
 
-def dequant(w, scales, biases, group):
-    """bf16(s * u + b), the exact sum rounded once -> float32 [N, K] (bf16-valued).
-    s * u is exact in float64 (8-bit by 4-bit significands); the float64 sum's remainder is recovered with TwoSum."""
+def dequant(w, scales, biases, group, block_rows=4096):
+    """bf16(s * u + b), the exact sum rounded once -> float32 [N, K] (bf16-valued). Large matrices go through in
+    blocks of rows (the float64 temporaries of a 44032 x 5120 weight would otherwise take several GB)."""
+    N = np.asarray(scales).shape[0]
+    if N <= block_rows:
+        return _dequant_block(w, scales, biases, group)
+    out = np.empty((N, np.asarray(scales).shape[1] * group), dtype=np.float32)
+    for r0 in range(0, N, block_rows):
+        out[r0:r0 + block_rows] = _dequant_block(w[r0:r0 + block_rows], scales[r0:r0 + block_rows],
+                                                 biases[r0:r0 + block_rows], group)
+    return out
+
+
+def _dequant_block(w, scales, biases, group):
+    """s * u is exact in float64 (8-bit by 4-bit significands); the float64 sum's remainder is recovered with TwoSum."""
     s = np.asarray(scales, dtype=np.float64)
     b = np.asarray(biases, dtype=np.float64)
     N, Gq = s.shape
@@ -45,6 +57,24 @@ def dequant(w, scales, biases, group):
     bv = r - p
     err = (p - (r - bv)) + (bb - bv)  # TwoSum remainder: p + bb == r + err exactly
     return bf_from_f64_exact(r, err)
+
+
+def affine(w, scales, biases, group, dtype=np.float64, block_rows=4096):
+    """s * u + b WITHOUT the rounding to bf16 -> [N, K] of `dtype`: the weight as a quantised matmul uses it.
+    mx.quantized_matmul never materialises bf16 weights, and the reference's own small-M kernel forms, per group,
+    s * (x_g . u_g) + b * sum(x_g) in fp32 (agens-mlx-bench/smallm/qmm_nax.py:56-67): algebraically x . (s u + b) with
+    the unrounded weight. In float64 the value is exact (s * u has 12 significant bits, the sum with b fits easily); in
+    float32 it is exact up to one rounding at 2^-24."""
+    s = np.asarray(scales)
+    N, Gq = s.shape
+    K = Gq * group
+    out = np.empty((N, K), dtype=dtype)
+    for r0 in range(0, N, block_rows):
+        u = unpack_codes(w[r0:r0 + block_rows], K).astype(np.float64)
+        ss = np.repeat(np.asarray(scales[r0:r0 + block_rows], np.float64), group, axis=1)
+        bb = np.repeat(np.asarray(biases[r0:r0 + block_rows], np.float64), group, axis=1)
+        out[r0:r0 + block_rows] = u * ss + bb
+    return out
 
 
 def dequant_fast(w, scales, biases, group):

@@ -1,0 +1,218 @@
+"""The decode step at the shapes that are benchmarked and that the baseline configurations name, against the CPU oracle.
+
+* a full-width slice of the 32B-shaped model (hidden 5120, 40 query / 8 kv heads, so five query heads per kv head, MLP
+  22016, the shared Engram table without a value projection, free biases, 64-token blocks with top-32 selection), rows
+  whose contexts lie beyond 128 + 32 * 64 tokens so that the selection is live;
+* the reduced 2-layer block exactly as the first baseline configuration states it (hidden 1024, 8 q / 2 kv heads, MLP
+  4096, block 64, top-k 8, B = 4 at contexts 37, 512, 1900 and 4096, free biases, seed 0);
+* sparse attention over ragged paged contexts up to 128 K tokens at 40 q / 8 kv heads: the attention OUTPUT, not only
+  the selected indices;
+* 64 free-running greedy steps.
+Bars: logits rtol 2e-2 / atol 2e-2 against the oracle (the bf16 bar); selected block indices bit-exact; attention output
+2^-7 |x| + 2e-3 (the reference's bar for its attention kernels, tests/test_bcsa_verify.py:83-101)."""
+import ctypes
+
+import numpy as np
+import pytest
+import torch
+
+from oracle.model import Oracle
+from oracle.numerics import bf
+from volundr_mlx_b200 import synth
+
+import seeding
+
+pytestmark = pytest.mark.gpu
+
+
+def _logits_close(got, want, what):
+    np.testing.assert_allclose(got, want, rtol=2e-2, atol=2e-2, err_msg=str(what))
+
+
+def _decode_against_oracle(model, bc, orc, rows, args, steps, rng, BT, trace_sel=False):
+    worst = 0.0
+    for t in range(steps):
+        toks = rng.integers(0, args.vocab_valid, size=bc.B).tolist()
+        logits, _ = BT.forward(model, bc, toks)
+        got = logits.float().cpu().numpy()
+        greedy = bc.greedy[: bc.B].cpu().numpy()
+        for r, k in enumerate(bc.keys):
+            trace = [] if trace_sel else None
+            want = orc.step(rows[k], toks[r], trace=trace)
+            _logits_close(got[r], want, (t, k))
+            worst = max(worst, float(np.abs(got[r] - want).max() / np.abs(want).max()))
+            assert greedy[r] == int(np.argmax(got[r][: args.vocab_valid]))
+        assert bc.host_pos() == [rows[k].pos for k in bc.keys]
+    return worst
+
+
+def test_32b_shaped_slice_matches_oracle(cuda):
+    from volundr_mlx_b200 import batch as BT, ops
+    from volundr_mlx_b200.volundr import Model
+
+    args = synth.volundr32b_args(num_hidden_layers=4, mixer_types=["kda", "bcsa", "kda", "attn"], engram_layers=[2],
+                                 engram_rows=1 << 12, vocab_size=4096, vocab_valid=4000)
+    assert args.num_attention_heads // args.num_key_value_heads == 5 and args.hidden_size == 5120
+    params = synth.make_params(args, seed=4, quant=True, bias_mode="free")
+    model = Model(args, params, cuda)
+    orc = Oracle(args, params, exact=False, w32=True)
+    far0 = args.bcsa_window + args.bcsa_topk * args.bcsa_compress          # 2176: beyond it the top-32 selection is live
+    ctx = [far0 + 300, far0 + 1500, 4999, far0 + 64 * 7 + 5, 700, 63]       # (+ one row inside the identity regime, one short)
+    keys = list("abcdef")
+    bc, rows = seeding.seeded_batch(model, orc, keys, ctx, seed=4, max_rows=8)
+    rng = np.random.default_rng(4)
+    worst = _decode_against_oracle(model, bc, orc, rows, args, 3, rng, BT)
+    ops.check_status()
+    for k in keys[:2]:
+        seeding.assert_state_close(bc, k, rows[k], args, what=k)
+    print(f"32B-shaped slice: worst relative logit error {worst:.3e}")
+
+
+def test_baseline_config1_block_matches_oracle(cuda):
+    from volundr_mlx_b200 import batch as BT, ops
+    from volundr_mlx_b200.volundr import Model
+
+    args = synth.block2_args()
+    params = synth.make_params(args, seed=0, quant=True, bias_mode="free")
+    model = Model(args, params, cuda)
+    orc = Oracle(args, params, exact=False)
+    ctx = [37, 512, 1900, 4096]
+    bc, rows = seeding.seeded_batch(model, orc, [0, 1, 2, 3], ctx, seed=0, max_rows=4)
+    rng = np.random.default_rng(0)
+    worst = _decode_against_oracle(model, bc, orc, rows, args, 6, rng, BT)
+    ops.check_status()
+    for k in range(4):
+        seeding.assert_state_close(bc, k, rows[k], args, what=k)
+    print(f"config-1 block: worst relative logit error {worst:.3e}")
+
+
+def test_sparse_attention_output_ragged_paged_contexts(cuda):
+    """16 rows, contexts log-uniform in 1 K .. 128 K tokens, 40 query / 8 kv heads of 128, 64-token pages from a
+    shuffled pool, top-32 blocks per kv head by mean-pooled-key . query plus the 128-token local window: selected
+    indices bit-exact, attention output (before the output gate is applied: gate inputs of 30 make sigmoid 1 in bf16)
+    against a float64 softmax over the same keys."""
+    from volundr_mlx_b200 import _lib, ops
+    from volundr_mlx_b200.batch import _Geom
+
+    L = _lib.lib()
+    rng = np.random.Generator(np.random.PCG64(3))
+    g = _Geom()
+    g.Hq, g.KVH, g.D = 40, 8, 128
+    g.W, g.C, g.topk = 128, 64, 32
+    g.IH, g.Di, g.NS, g.far_tokens = 4, 128, 8, 1
+    B, G = 16, 5
+    ctx = np.exp(rng.uniform(np.log(1024), np.log(131072), size=B)).astype(np.int64)
+    ctx[0] = 131072
+    pos = (ctx - 1).astype(np.int32)                      # the newest token's position
+    npg = [(int(c) + 63) // 64 for c in ctx]
+    g.max_pages = max(npg)
+    g.n_pages = sum(npg)
+    perm = rng.permutation(g.n_pages).astype(np.int32)
+    table = np.full((B, g.max_pages), -1, np.int32)
+    o = 0
+    for b in range(B):
+        table[b, : npg[b]] = perm[o:o + npg[b]]
+        o += npg[b]
+    gen = torch.Generator(device=cuda).manual_seed(3)
+    K = torch.empty((g.n_pages, g.KVH, 64, 128), dtype=torch.bfloat16, device=cuda)
+    V = torch.empty_like(K)
+    for i in range(0, g.n_pages, 512):
+        K[i:i + 512] = torch.randn((min(512, g.n_pages - i), g.KVH, 64, 128), device=cuda, generator=gen).to(torch.bfloat16)
+        V[i:i + 512] = torch.randn((min(512, g.n_pages - i), g.KVH, 64, 128), device=cuda, generator=gen).to(torch.bfloat16)
+    # pooled means with the oracle's arithmetic: rows added in order in fp32, times 1/64, one rounding
+    PK = torch.empty((g.n_pages, g.KVH, 1, 128), dtype=torch.bfloat16, device=cuda)
+    for i in range(0, g.n_pages, 512):
+        acc = torch.zeros((min(512, g.n_pages - i), g.KVH, 128), dtype=torch.float32, device=cuda)
+        for c in range(64):
+            acc = acc + K[i:i + 512, :, c].float()
+        PK[i:i + 512, :, 0] = (acc * (1.0 / 64)).to(torch.bfloat16)
+    PV = PK.clone()   # (not read in this mode: far keys are the blocks' tokens)
+    q = bf(rng.normal(size=(B, g.Hq, 128)))
+    tq = torch.from_numpy(q).to(cuda).to(torch.bfloat16)
+    proj = torch.full((B, g.Hq * 256), 30.0, dtype=torch.bfloat16, device=cuda)       # [q | gate] per head: gate = 30
+    tpos, ttab = torch.from_numpy(pos).to(cuda), torch.from_numpy(table).to(cuda)
+    nblk = g.max_pages
+    sel = torch.full((B, g.NS, g.topk), -7, dtype=torch.int32, device=cuda)
+    nsel = torch.zeros((B, g.NS), dtype=torch.int32, device=cuda)
+    scratch = torch.empty(L.vk_bcsa_select_scratch_bytes(ctypes.byref(g), B, nblk), dtype=torch.uint8, device=cuda)
+    nsplit = 16
+    part = torch.empty(L.vk_attend_scratch_bytes(ctypes.byref(g), B, nsplit), dtype=torch.uint8, device=cuda)
+    out = torch.empty((B, g.Hq * 128), dtype=torch.bfloat16, device=cuda)
+    st = torch.cuda.current_stream().cuda_stream
+    _lib.check(L.vk_attn_configure(), "vk_attn_configure")
+    _lib.check(L.vk_bcsa_select(ctypes.byref(g), tq.data_ptr(), PK.data_ptr(), tpos.data_ptr(), ttab.data_ptr(),
+                                scratch.data_ptr(), nblk, sel.data_ptr(), nsel.data_ptr(), B, st), "vk_bcsa_select")
+    _lib.check(L.vk_attend_decode(ctypes.byref(g), tq.data_ptr(), K.data_ptr(), V.data_ptr(), PK.data_ptr(), PV.data_ptr(),
+                                  tpos.data_ptr(), ttab.data_ptr(), sel.data_ptr(), nsel.data_ptr(), proj.data_ptr(),
+                                  proj.stride(0), part.data_ptr(), nsplit, out.data_ptr(), None, B, st), "vk_attend_decode")
+    ops.check_status()
+    got_sel, got_n = sel.cpu().numpy(), nsel.cpu().numpy()
+    got = out.float().cpu().numpy().reshape(B, g.Hq, 128)
+    orc = Oracle.__new__(Oracle)
+    orc.exact = False
+    pk_host = None
+    for b in range(B):
+        p = int(pos[b])
+        nv = max(0, (p - g.W + 1) // g.C)
+        pages = torch.from_numpy(table[b, : npg[b]].astype(np.int64)).to(cuda)
+        pk_host = PK[pages, :, 0].float().cpu().numpy()                    # [npg, KVH, 128]
+        lo = max(0, p - g.W + 1)
+        for kv in range(g.KVH):
+            if nv > g.topk:
+                s = orc.block_scores(q[b, kv * G:(kv + 1) * G], pk_host[:nv, kv])
+                want_sel = Oracle.topk_blocks(s, g.topk)
+            else:
+                want_sel = np.arange(nv, dtype=np.int32)
+            assert got_n[b, kv] == len(want_sel)
+            assert np.array_equal(got_sel[b, kv, : len(want_sel)], want_sel), (b, kv)
+            toks = list(range(lo, p + 1))
+            for j in want_sel:
+                toks += list(range(int(j) * 64, int(j) * 64 + 64))
+            toks = np.asarray(toks, np.int64)
+            pg = torch.from_numpy(table[b][toks // 64].astype(np.int64)).to(cuda)
+            rw = torch.from_numpy(toks % 64).to(cuda)
+            Kt = K[pg, kv, rw].double().cpu().numpy()
+            Vt = V[pg, kv, rw].double().cpu().numpy()
+            sc = (q[b, kv * G:(kv + 1) * G].astype(np.float64) @ Kt.T) * 128 ** -0.5
+            sc = np.exp(sc - sc.max(-1, keepdims=True))
+            want = (sc @ Vt) / sc.sum(-1, keepdims=True)
+            err = np.abs(got[b, kv * G:(kv + 1) * G] - want)
+            assert (err <= 2.0 ** -7 * np.abs(want) + 2e-3).all(), (b, kv, float(err.max()))
+
+
+@pytest.mark.parametrize("bias_mode", ["free", "minus8"])
+def test_greedy_64_steps_free_running(cuda, bias_mode):
+    """64 greedy steps, each row fed the device's own previous choice (nothing teacher-forced on the device side); the
+    oracle runs on the same token history. The device's token must be the oracle's at every step, except where the
+    oracle itself is at a near-tie: its best logit and its logit of the device's token lie within the logit tolerance
+    (rtol 2e-2 / atol 2e-2), the reference's rule for its own batched-vs-single gate (every accepted divergence at a
+    near-tie of the top two logits, NOTES_BATCHED.md:51-55)."""
+    from volundr_mlx_b200 import batch as BT, ops
+    from volundr_mlx_b200.volundr import Model
+
+    args = synth.small_args()
+    params = synth.make_params(args, seed=21, quant=True, bias_mode=bias_mode)
+    model = Model(args, params, cuda)
+    orc = Oracle(args, params, exact=False)
+    bc = model.make_cache(max_rows=4, n_pages=16, max_pages_per_row=3)
+    keys = ["a", "b", "c"]
+    bc.apply(join=keys)
+    rows = {k: orc.new_row() for k in keys}
+    toks = [3, 141, 59]
+    ties = 0
+    v = args.vocab_valid
+    for t in range(64):
+        logits, _ = BT.forward(model, bc, toks)
+        got = logits.float().cpu().numpy()
+        nxt = bc.greedy[: bc.B].cpu().numpy().tolist()
+        for r, k in enumerate(keys):
+            want = orc.step(rows[k], toks[r])
+            _logits_close(got[r], want, (t, k))
+            best = int(np.argmax(want[:v]))
+            if nxt[r] != best:
+                margin = float(want[best] - want[nxt[r]])
+                assert margin <= 2e-2 + 2e-2 * abs(float(want[best])), (t, k, margin)
+                ties += 1
+        toks = nxt
+    ops.check_status()
+    assert ties <= 3, ties

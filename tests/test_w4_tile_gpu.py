@@ -54,3 +54,32 @@ def test_tile_gemm(cuda, M, N, K, shape):
     exact = x.astype(np.float64) @ Wd.T
     err = np.abs(got - exact)
     assert (err <= 2.0 ** -8 * np.abs(exact) + 1e-3).all(), err.max()
+
+
+@pytest.mark.parametrize("N", [5120, 22016, 44032])
+def test_tile_gemm_sweep_shapes_against_oracle(cuda, N):
+    """The shapes of the W4A16 sweep (K = 5120, N in {5120, 22016, 44032}; codes uniform, scales |N(0, 0.02)| / 8, biases
+    N(0, 0.01), activations N(0, 1), seed 1) at the row counts of a verify window and of prefill chunks, M in {64, 128,
+    512}: rtol / atol 2e-2 against the oracle's W4 product and 2^-8 |exact| + 2e-3 against the exact product of the
+    bf16-dequantised weights (the reference's own kernel bar is max relative error 3.7e-3, smallm/NOTES.md:104-105)."""
+    from volundr_mlx_b200 import ops
+
+    K = 5120
+    rng = np.random.Generator(np.random.PCG64(1))
+    w, s, b = make_w4(rng, N, K, 64)
+    dev = lambda a, dt: torch.from_numpy(np.ascontiguousarray(a)).to(cuda).to(dt)
+    wt = ops.w4_repack(torch.from_numpy(w.view(np.int32)).to(cuda), dev(s, torch.bfloat16), dev(b, torch.bfloat16), 64)
+    Wd = OW.dequant(w, s, b, 64)                              # bf16-valued float32: exact in float32
+    for M in (64, 128, 512):
+        x = bf(rng.normal(0, 1, size=(M, K)))
+        got = ops.w4_gemm_tile(dev(x, torch.bfloat16), wt).float().cpu().numpy()
+        ops.check_status()
+        # columns sampled across the whole weight (every 256-row superblock contributes), all rows: the float64 product
+        cols = np.unique(np.concatenate([np.arange(0, N, 97), np.arange(N - 300, N)]))
+        exact = x.astype(np.float64) @ Wd[cols].astype(np.float64).T
+        err = np.abs(got[:, cols] - exact)
+        assert (err <= 2.0 ** -8 * np.abs(exact) + 2e-3).all(), (M, float(err.max()))
+        np.testing.assert_allclose(got[:, cols], bf(exact.astype(np.float32)), rtol=2e-2, atol=2e-2)
+        # ... and every column against a float32 product (exact weights, accumulation error ~1e-6)
+        full = x @ Wd.T
+        np.testing.assert_allclose(got, full, rtol=2e-2, atol=2e-2)

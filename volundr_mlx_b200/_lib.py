@@ -59,7 +59,7 @@ SIGNATURES = {
                      + [c_int] * 9 + [c_float, c_void_p]),
     "vk_kda_chunk_ragged": (c_int, [c_void_p, c_int, c_int, c_int] + [c_void_p] * 9 + [c_size_t, c_void_p, c_void_p, c_void_p,
                                     c_void_p] + [c_int] * 9 + [c_float, c_void_p]),
-    "vk_kda_step": (c_int, [c_void_p, c_int, c_int, c_int] + [c_void_p] * 9 + [c_size_t, c_void_p, c_void_p, c_void_p, c_void_p]
+    "vk_kda_step": (c_int, [c_void_p, c_int, c_int, c_int] + [c_void_p] * 9 + [c_size_t, c_void_p, c_void_p, c_void_p]
                     + [c_int] * 7 + [c_float, c_void_p]),
     "vk_batch_step_begin": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                     c_void_p]),
@@ -68,6 +68,10 @@ SIGNATURES = {
                                                                                           c_void_p]),
     "vk_attn_prep_rows": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int] + [c_void_p] * 15 + [c_int, c_int, c_double, c_float,
                                                                                                c_int, c_void_p, c_void_p]),
+    "vk_attn_prep_chunk": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int] + [c_void_p] * 15 + [c_int, c_int, c_double, c_float,
+                                                                                                c_int, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "vk_pages_open": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p]),
+    "vk_pages_release": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p]),
     "vk_bcsa_select_scratch_bytes": (c_size_t, [c_void_p, c_int, c_int]),
     "vk_bcsa_select": (c_int, [c_void_p] * 6 + [c_int, c_void_p, c_void_p, c_int, c_void_p]),
     "vk_bcsa_select_static": (c_int, [c_void_p] * 7 + [c_int, c_void_p]),

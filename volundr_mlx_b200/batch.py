@@ -19,6 +19,7 @@ import numpy as np
 import torch
 
 from . import _lib, ops
+from . import session as SS
 from .volundr import BF16, Model
 
 PAGE = 64
@@ -99,7 +100,6 @@ class BatchCache:
         self.xr_act = torch.zeros(m.I // 64 * 2176, **u8)
         self.fused_xrec = S <= 16
         self.fuse_boundary = True   # one kernel for combine(layer i) + mix(layer i + 1)
-        self.y_dbg = None
         self.q = torch.zeros((S, m.Hq, 128), **bf)
         if self.indexer:
             self.qi = torch.zeros((S, a.bcsa_index_heads, a.bcsa_index_dim), **bf)
@@ -160,9 +160,12 @@ class BatchCache:
         self.pos[: self.B] = torch.tensor(self._pos, dtype=torch.int32, device=self.pos.device) if self.B else self.pos[:0]
 
     def apply(self, leave=(), join=()):
-        """Remove the rows of the keys in `leave` (swap-remove: the last row moves into the hole, batch.py:416-431)
-        and append one fresh row (position 0, zero state) per key in `join`."""
-        torch.cuda.synchronize(self.pos.device)
+        """Remove the rows of the keys in `leave` (swap-remove: the last row moves into the hole, batch.py:416-431) and
+        append one row per item of `join`: a bare key (or (key, None)) starts a fresh sequence at position 0; (key,
+        state) continues the sequence a session.State holds (a captured or restored row, the reference's
+        join=[(key, b1_cache)], batch.py:432-453): its K/V, pooled blocks and indexer keys are scattered into pages taken
+        from the pool, its KDA, conv and Engram state copied into the row's slot. Everything here is enqueued on the
+        current stream (page give-back and allocation run as kernels): a membership change does not wait for the GPU."""
         for b in sorted((self.keys.index(k) for k in leave), reverse=True):
             last = self.B - 1
             self._release_pages(b)
@@ -172,21 +175,34 @@ class BatchCache:
             self.keys[b], self._pos[b] = self.keys[last], self._pos[last]
             self.keys.pop()
             self._pos.pop()
-        for key in join:
+        for item in join:
+            key, state = item, None
+            if isinstance(item, tuple) and len(item) == 2 and (item[1] is None or isinstance(item[1], SS.State)):
+                key, state = item
             assert self.B < self.S, "batch is full"
             b = self.B
             self._clear_row(b)
             self.keys.append(key)
             self._pos.append(0)
+            if state is not None and state.pos > 0:
+                self._put_row(b, state)
         self._sync_rows()
 
+    def release_pages(self, items, reverse):
+        """items: (row, first page index, last page index): those table entries go back to the pool on the GPU."""
+        if not items:
+            return
+        dev = self.pos.device
+        t = torch.tensor(items, dtype=torch.int32).t().contiguous().to(dev, non_blocking=True)   # [3, n]
+        _lib.check(_lib.lib().vk_pages_release(_p(t[0]), _p(t[1]), _p(t[2]), len(items), 1 if reverse else 0, _p(self.table),
+                                               self.max_pages, _p(self.free_list), _p(self.free_top), self.n_pages,
+                                               torch.cuda.current_stream().cuda_stream), "vk_pages_release")
+
     def _release_pages(self, b):
+        # a row that leaves hands its pages back last first: the next row to grow takes them in the same order
         n = (self._pos[b] + PAGE - 1) // PAGE
         if n:
-            top = int(self.free_top.item())
-            self.free_list[top: top + n] = self.table[b, :n].flip(0)
-            self.free_top += n
-            self.table[b, :n] = -1
+            self.release_pages([(b, 0, n)], reverse=True)
 
     def _par(self):
         return self.steps & 1
@@ -212,33 +228,132 @@ class BatchCache:
         self.table[b] = -1
         self.engram_prev[b] = -1
 
-    def capture_row(self, key):
-        """The row's decode state as own copies (batch.py:488-510): position, per-layer ("arrays", conv, state) /
-        ("kv", P, keys, values) / ("bcsa", ...) tuples gathered from the pages, ("engram", keep, prev)."""
-        torch.cuda.synchronize(self.pos.device)
-        b, P = self.keys.index(key), self._pos[self.keys.index(key)]
+    def _put_row(self, b, state: SS.State):
+        """Row b (cleared, no pages) takes over the sequence of `state`."""
+        L = _lib.lib()
+        a, dev = self.args, self.pos.device
+        P = int(state.pos)
+        npg = (P + PAGE - 1) // PAGE
+        assert npg <= self.max_pages, "the sequence does not fit a row's page table"
+        assert len(state.layers) == len(self.layers) + 1, "the state was captured from another model"
+        # pages for positions 0 .. P - 1 of this row only (zero tokens for every other row)
+        lens = torch.zeros(self.S, dtype=torch.int32)
+        lens[b] = P
+        lens = lens.to(dev, non_blocking=True)
+        zero = torch.zeros(self.S, dtype=torch.int32, device=dev)
+        _lib.check(L.vk_pages_open(_p(zero), _p(lens), _p(self.table), self.max_pages, _p(self.free_list), _p(self.free_top),
+                                   self.S, torch.cuda.current_stream().cuda_stream), "vk_pages_open")
+        pages = self.table[b, :npg].long()          # (a device tensor: indexing with it needs no host round trip)
+        par = self._par()
+        C = a.bcsa_compress
+        KVH = self.model.KVH
+
+        def to_pages(x, per_page):
+            """[1, heads.., n, D] rows by position -> [npg, heads.., per_page, D] (zero padded)."""
+            x = x[0]
+            n = x.shape[-2]
+            pad = npg * per_page - n
+            if pad:
+                x = torch.cat([x, x.new_zeros(x.shape[:-2] + (pad, x.shape[-1]))], dim=-2)
+            x = x.reshape(x.shape[:-2] + (npg, per_page, x.shape[-1]))
+            return x.movedim(-3, 0)
+
+        for mix, st, t in zip(a.mixer_types, self.layers, state.layers):
+            if mix == "kda":
+                assert t[0] == "arrays"
+                st["conv"][par, b] = t[1][0].to(dev)
+                st["S"][b] = t[2][0].to(dev)
+            elif mix == "attn":
+                assert t[0] == "kv" and t[1] == P and t[2].shape[1] == KVH
+                st["K"][pages] = to_pages(t[2].to(dev)[:, :, :P], PAGE)
+                st["V"][pages] = to_pages(t[3].to(dev)[:, :, :P], PAGE)
+            else:
+                kind, W, Cs, _, offset, nb, k, v, pk, pv, bk, ik = t
+                assert kind == "bcsa" and offset == P and W == a.bcsa_window and Cs == C and nb == P // C
+                st["K"][pages] = to_pages(k.to(dev)[:, :, :P], PAGE)
+                st["V"][pages] = to_pages(v.to(dev)[:, :, :P], PAGE)
+                if nb:
+                    # (pooled rows of the pages that hold closed blocks; later pages keep what they have: nothing reads
+                    # a pooled slot before the block it belongs to has closed)
+                    nbp = (nb + PAGE // C - 1) // (PAGE // C)
+                    pkp = pk.to(dev)[0][:, :nb]
+                    pvp = pv.to(dev)[0][:, :nb]
+                    pad = nbp * (PAGE // C) - nb
+                    if pad:
+                        z = pkp.new_zeros((KVH, pad, pkp.shape[-1]))
+                        pkp, pvp = torch.cat([pkp, z], 1), torch.cat([pvp, z], 1)
+                    st["PK"][pages[:nbp]] = pkp.reshape(KVH, nbp, PAGE // C, -1).movedim(1, 0)
+                    st["PV"][pages[:nbp]] = pvp.reshape(KVH, nbp, PAGE // C, -1).movedim(1, 0)
+                    if "BK" in st:
+                        bkp = bk.to(dev)[0][:nb]
+                        if pad:
+                            bkp = torch.cat([bkp, bkp.new_zeros((pad, bkp.shape[-1]))], 0)
+                        st["BK"][pages[:nbp]] = bkp.reshape(nbp, PAGE // C, -1)
+                if "IK" in st:
+                    st["IK"][b] = ik.to(dev)[0]
+        eng = state.layers[-1]
+        assert eng[0] == "engram"
+        if self.keep:
+            assert eng[1] == self.keep
+            self.engram_prev[b, : self.keep] = eng[2].to(dev)[0]
+        self._pos[b] = P
+
+    def capture_row(self, key, dcache=None, logits=None) -> SS.State:
+        """Row `key` as a session.State of own copies (batch.py:488-510; layout in volundr_mlx_b200/session.py): the
+        position, per layer the KDA conv window and state / the row's K, V (by position), pooled blocks, pooled and
+        open-block indexer keys gathered from its pages / the dense layer's K, V, and the Engram id window. `dcache`
+        (a drafter's context) and `logits` (of the last position) are carried along as given. Enqueued on the current
+        stream; nothing here waits for the GPU."""
+        b = self.keys.index(key)
+        P = self._pos[b]
         npg = (P + PAGE - 1) // PAGE
         pages = self.table[b, :npg].long()
         a = self.args
+        KVH = self.model.KVH
         out = []
+
+        def by_pos(pool, n):
+            """[n_pages, KVH, per_page, D] pool -> [1, KVH, n, D] of this row."""
+            x = pool[pages]                                   # [npg, KVH, per_page, D]
+            return x.movedim(0, 1).reshape(1, KVH, npg * pool.shape[2], x.shape[-1])[:, :, :n].contiguous()
+
         for mix, st in zip(a.mixer_types, self.layers):
             if mix == "kda":
-                out.append(("arrays", st["conv"][self._par(), b].clone(), st["S"][b].clone()))
+                out.append(("arrays", st["conv"][self._par(), b: b + 1].clone(), st["S"][b: b + 1].clone()))
+            elif mix == "attn":
+                out.append(("kv", P, by_pos(st["K"], P), by_pos(st["V"], P)))
             else:
-                k = st["K"][pages].permute(1, 0, 2, 3).reshape(self.model.KVH, npg * PAGE, 128)[:, :P].clone()
-                v = st["V"][pages].permute(1, 0, 2, 3).reshape(self.model.KVH, npg * PAGE, 128)[:, :P].clone()
-                if mix == "attn":
-                    out.append(("kv", P, k, v))
-                else:
-                    C = a.bcsa_compress
-                    nb = P // C
-                    pk = st["PK"][pages].permute(1, 0, 2, 3).reshape(self.model.KVH, -1, 128)[:, :nb].clone()
-                    pv = st["PV"][pages].permute(1, 0, 2, 3).reshape(self.model.KVH, -1, 128)[:, :nb].clone()
-                    bk = st["BK"][pages].reshape(-1, a.bcsa_index_dim)[:nb].clone() if "BK" in st else None
-                    ik = st["IK"][b].clone() if "IK" in st else None
-                    out.append(("bcsa", a.bcsa_window, C, a.bcsa_topk, P, nb, k, v, pk, pv, bk, ik))
-        out.append(("engram", self.keep, self.engram_prev[b, : self.keep].clone()))
-        return {"pos": P, "layers": out}
+                C = a.bcsa_compress
+                nb = P // C
+                bk = st["BK"][pages].reshape(1, npg * (PAGE // C), a.bcsa_index_dim)[:, :nb].contiguous() if "BK" in st else None
+                ik = st["IK"][b: b + 1].clone() if "IK" in st else None
+                out.append(("bcsa", a.bcsa_window, C, 0, P, nb, by_pos(st["K"], P), by_pos(st["V"], P), by_pos(st["PK"], nb),
+                            by_pos(st["PV"], nb), bk, ik))
+        out.append(("engram", self.keep, self.engram_prev[b: b + 1, : self.keep].clone()))
+        state = SS.State(P, out, dcache, None if logits is None else logits.clone())
+        state.count_bytes()
+        return state
+
+    def row_cache(self, key) -> SS.State:
+        """Row `key` as an independent copy that can continue on its own (batch.py:512-515): with a paged cache the
+        B = 1 "cache" of a row is its State; join it into any BatchCache of the same model."""
+        return self.capture_row(key)
+
+    @property
+    def slots_cap(self):
+        return self.S
+
+    @property
+    def state(self):
+        """Every device buffer that holds row state (batch.py:349-356)."""
+        out = [self.pos, self.table, self.free_list, self.free_top, self.engram_prev]
+        for st in self.layers:
+            out += list(st.values())
+        return out
+
+    @property
+    def nbytes(self):
+        return sum(t.numel() * t.element_size() for t in self.state)
 
     # ------------------------------------------------------------------ synthetic contexts (benchmarks, kernel tests)
     def fill_synthetic(self, keys, ctx_lens, seed=0):
@@ -353,7 +468,7 @@ def _launch_step(model: Model, bc: BatchCache, capture=()):
             ck(L.vk_kda_step(_p(bc.proj), bc.proj.stride(0), w["off_z"], w["off_fd"], _p(bc.h), _p(w["in_proj_b"]),
                              _p(w["f_up"]), _p(w["conv_w"]), _p(w["A_log"]), _p(w["dt_bias"]), _p(w["gnorm"]),
                              _p(lst["conv"]), _p(bc.parity), lst["conv"][0].numel(), _p(lst["S"]), _p(bc.mix),
-                             _p(bc.xr_mix) if fx else None, None, B, D,
+                             _p(bc.xr_mix) if fx else None, B, D,
                              model.Hk, model.HV, 128, 128, a.kda_gate_rank, eps, st), "vk_kda_step")
         else:
             bcsa = w["mixer"] == "bcsa"
@@ -403,7 +518,7 @@ def _launch_step(model: Model, bc: BatchCache, capture=()):
                 val = bc.eng_val
         last = i + 1 == nl
         w_next = model.norm_w if last else model.layers[i + 1]["mhc_norm"]
-        if fuse_boundary and not last and bc.y_dbg is None:
+        if fuse_boundary and not last:
             wn = model.layers[i + 1]
             ck(L.vk_mhc_boundary_ar(_p(bc.H), _p(bc.h2), _p(bc.mlp), _p(bc.x_in), _p(bc.post), _p(bc.res), _p(w_next),
                                     _p(val) if eng else None, _p(w["eng_gate_w"]) if eng else None,
@@ -413,7 +528,7 @@ def _launch_step(model: Model, bc: BatchCache, capture=()):
             continue
         ck(L.vk_mhc_combine_norm_ar(_p(bc.H), _p(bc.h2), _p(bc.mlp), _p(bc.x_in), _p(bc.post), _p(bc.res), _p(w_next),
                                     _p(bc.hn), _p(val) if eng else None, _p(w["eng_gate_w"]) if eng else None,
-                                    _p(w["eng_gate_b"]) if eng else None, _p(bc.y_dbg) if bc.y_dbg is not None else None, B,
+                                    _p(w["eng_gate_b"]) if eng else None, None, B,
                                     D, 1 if last else 0, eps, ar, 2 * i + 1, st), "vk_mhc_combine_norm_ar")
     V = model.vocab_shard
     if isinstance(model.lm_head, ops.BF16Weight):

@@ -67,6 +67,8 @@ class ChunkScratch:
             self.qi = torch.zeros((R, a.bcsa_index_heads, a.bcsa_index_dim), **bf)
             self.idxq = torch.zeros((R, a.bcsa_index_heads * a.bcsa_index_dim), **bf)
             self.idxk = torch.zeros((R, a.bcsa_index_dim), **bf)
+            self.ikc = torch.zeros((R, a.bcsa_index_dim), **bf)     # normed indexer key of every virtual row
+            self.first_pos = torch.zeros(R, **i32)                  # where the chunk began for the row's request
         self.sel = torch.full((R, max(bc.NS, 1), max(a.bcsa_topk, 1)), -1, **i32)
         self.nsel = torch.zeros((R, max(bc.NS, 1)), **i32)
         self.sel_scratch = torch.zeros((R, max(bc.NS, 1), bc.max_blocks), **i32)
@@ -77,9 +79,16 @@ class ChunkScratch:
 
 
 class ChunkHandle:
-    def __init__(self, lens, pos0, window, kda_inputs, off):
-        self.lens, self.pos0, self.window, self.kda_inputs, self.off = lens, pos0, window, kda_inputs, off
+    """What a verify pass leaves for its commit (the reference's `rec`, batch_spec.py:128): the rows' token counts and
+    start positions, the Engram id window, the KDA layers' inputs (the commit replays the recurrence over the accepted
+    prefix), the chunk's indexer keys per BCSA layer (the commit stores the open block's), plus the pass's outputs."""
+
+    def __init__(self, model, lens, pos0, window, kda_inputs, off, ik):
+        self.model = model
+        self.lens, self.pos0, self.window, self.kda_inputs, self.off, self.ik = lens, pos0, window, kda_inputs, off, ik
         self.T = max(lens)
+        self.greedy = None
+        self.features = None
 
 
 def _get_scratch(model, bc, R):
@@ -115,29 +124,55 @@ def scratch_capacity(R: int) -> int:
     return cap
 
 
-def _open_pages(bc, lens):
-    """Pages for the positions pos .. pos + lens[b] - 1 of every row (host side: at most a few per row)."""
-    need = []
+def _open_pages(bc, lens, lens_t):
+    """Pages for the positions pos .. pos + lens[b] - 1 of every row, handed out on the GPU (vk_pages_open); the host
+    only checks the rows' page tables for room. An exhausted pool shows in the device status word."""
     for b, p0 in enumerate(bc._pos):
         assert (p0 + lens[b] + PAGE - 1) // PAGE <= bc.max_pages, "row would outgrow its page table"
-        for p in range(p0, p0 + lens[b]):
-            if p % PAGE == 0:
-                need.append((b, p // PAGE))
-    if need:
-        top = int(bc.free_top.item())
-        assert top >= len(need), "page pool exhausted"
-        for n, (b, pi) in enumerate(need):
-            bc.table[b, pi] = bc.free_list[top - 1 - n]
-        bc.free_top -= len(need)
+    _lib.check(_lib.lib().vk_pages_open(_p(bc.pos), _p(lens_t), _p(bc.table), bc.max_pages, _p(bc.free_list), _p(bc.free_top),
+                                        bc.B, torch.cuda.current_stream().cuda_stream), "vk_pages_open")
 
 
-def forward_chunk(model, bc, toks, write=False, logits_at=None):
+def _store_open_keys(bc, lst, ikc, off, pos0, kept):
+    """The open block's indexer keys after request b kept kept[b] tokens of a chunk that began at pos0[b]: the ring
+    IK [row, C, Di] gets the keys of the positions of the last, unfinished block that the chunk brought (those in front
+    of the chunk are in the ring already; BCSACache.update, volundr.py:526-533; batch_spec.py:151-158)."""
+    C = bc.args.bcsa_compress
+    rows, slots, src = [], [], []
+    for b, (p0, n) in enumerate(zip(pos0, kept)):
+        end = p0 + n
+        for t in range(max(end - end % C, p0), end):
+            rows.append(b)
+            slots.append(t % C)
+            src.append(int(off[b]) + t - p0)
+    if rows:
+        dev = ikc.device
+        ix = lambda v: torch.tensor(v, dtype=torch.long, device=dev)
+        lst["IK"][ix(rows), ix(slots)] = ikc[ix(src)]
+
+
+def forward_chunk(model, bc, toks, write=False, logits_at=None, capture=()):
     """toks [B][T], or one list of tokens per row with different lengths (a ragged chunk). Returns (logits, greedy,
     handle): logits [B, T, V] bf16 and greedy [B, T] int32 for T tokens per row; for a ragged chunk the LM head runs on
     one token per row (logits_at, default each row's last), logits [B, 1, V], greedy [B, 1]. write=False: a verify
     pass, to be followed by commit_chunk(model, bc, handle, accepted); write=True: all tokens are committed (handle is
     None). logits_at [B] (token index per row) restricts the LM head to that token of every row (what feeding a prompt
-    needs: the logits after its last token)."""
+    needs: the logits after its last token). capture: layer indices whose entry stream-0 residual is kept
+    (batch.py:540-541; batch_spec.py:121-122): handle.features [B, T, len(capture) * hidden] ([R, ...] for a ragged
+    chunk), also returned by the generator form."""
+    gen = forward_chunk_iter(model, bc, toks, write=write, logits_at=logits_at, capture=capture)
+    try:
+        while True:
+            next(gen)
+    except StopIteration as e:
+        return e.value
+
+
+def forward_chunk_iter(model, bc, toks, write=False, logits_at=None, capture=(), yield_layers=True):
+    """forward_chunk as a generator: yields ("layer", i) after the kernels of layer i have been enqueued, so that a
+    scheduler can stop feeding a long chunk when its time slice is spent and run decode steps of other caches in between
+    (session.prefill_iter with yield_layers, session.py:351-387; verify.forward_iter, spec/verify.py:180-226). The
+    cache `bc` itself must not be stepped before the generator has finished. Returns forward_chunk's value."""
     L = _lib.lib()
     tp = model.tp_size > 1
     a, D = model.args, model.args.hidden_size
@@ -154,7 +189,8 @@ def forward_chunk(model, bc, toks, write=False, logits_at=None):
     t_in = torch.tensor([row + [0] * (T - len(row)) for row in toks], dtype=torch.int32).to(dev)   # [B, T], padded
     s = _get_scratch(model, bc, R)
     BT.model_warm(model)
-    _open_pages(bc, lens)
+    acc_all = torch.tensor(lens, dtype=torch.int32, device=dev)
+    _open_pages(bc, lens, acc_all)
     st = torch.cuda.current_stream().cuda_stream
     eps = a.rms_norm_eps
     ck = _lib.check
@@ -164,6 +200,8 @@ def forward_chunk(model, bc, toks, write=False, logits_at=None):
     s.tok[:R].copy_(t_in[rows, tpos])
     s.pos[:R].copy_(bc.pos[:B][rows] + tpos.to(torch.int32))
     s.table[:R].copy_(bc.table[:B][rows])
+    if bc.indexer:
+        s.first_pos[:R].copy_(bc.pos[:B][rows])
     window = None
     if a.engram_layers and bc.keep > 0:
         window = torch.cat([bc.engram_prev[:B, : bc.keep], t_in], dim=1)          # [B, keep + T]
@@ -192,10 +230,11 @@ def forward_chunk(model, bc, toks, write=False, logits_at=None):
     ck(L.vk_embed(_p(s.tok), _p(model.embed), _p(w0["mhc_norm"]), _p(s.H), _p(s.hn),
                   _p(s.engram_prev) if a.engram_layers else None, _p(s.engram_rows), bc.orders,
                   len(a.engram_orders) if a.engram_layers else 0, a.engram_rows, R, D, eps, st), "vk_embed")
-    kda_inputs = []
-    acc_all = torch.tensor(lens, dtype=torch.int32, device=dev)
+    kda_inputs, ik_kept, caps = [], {}, []
     nl = len(model.layers)
     for i, (w, lst) in enumerate(zip(model.layers, bc.layers)):
+        if i in capture:
+            caps.append(s.H[:R, 0].clone())
         ck(L.vk_mhc_mix_norm(_p(s.H), _p(s.hn), _p(w["dyn"]), _p(w["pre_s"]), _p(w["post_s"]), _p(w["res_s"]), _p(w["ln_in"]),
                              _p(s.x_in), _p(s.h), None, _p(s.post), _p(s.res), _p(s.dyn), R, D, a.mhc_sinkhorn_iters, eps, st),
            "vk_mhc_mix_norm")
@@ -220,14 +259,20 @@ def forward_chunk(model, bc, toks, write=False, logits_at=None):
                 ck(L.vk_bf16_gemm(_p(s.h), D, _p(w["idx_k"]), None, _p(s.idxk), s.idxk.stride(0), R, w["idx_k"].shape[0], D, st),
                    "vk_bf16_gemm")
             for mode in (1, 2):   # write every row's K / V first, pool the blocks that close afterwards
-                ck(L.vk_attn_prep_rows(ctypes.byref(g), _p(s.proj), s.proj.stride(0), w["off_k"], w["off_v"],
-                                       _p(s.idxq) if idx else None, _p(s.idxk) if idx else None, _p(w["q_norm"]),
-                                       _p(w["k_norm"]), _p(w["idx_norm"]) if idx else None, _p(s.pos), _p(s.table), _p(s.q),
-                                       _p(s.qi) if idx else None, _p(lst["K"]), _p(lst["V"]), _p(lst.get("PK")),
-                                       _p(lst.get("PV")), _p(lst.get("BK")), _p(lst.get("IK")), R, model.rope_dims,
-                                       float(a.rope_theta), eps, mode, _p(s.row_map), st), "vk_attn_prep_rows")
+                ck(L.vk_attn_prep_chunk(ctypes.byref(g), _p(s.proj), s.proj.stride(0), w["off_k"], w["off_v"],
+                                        _p(s.idxq) if idx else None, _p(s.idxk) if idx else None, _p(w["q_norm"]),
+                                        _p(w["k_norm"]), _p(w["idx_norm"]) if idx else None, _p(s.pos), _p(s.table), _p(s.q),
+                                        _p(s.qi) if idx else None, _p(lst["K"]), _p(lst["V"]), _p(lst.get("PK")),
+                                        _p(lst.get("PV")), _p(lst.get("BK")), _p(lst.get("IK")), R, model.rope_dims,
+                                        float(a.rope_theta), eps, mode, _p(s.row_map), _p(s.ikc) if idx else None,
+                                        _p(s.first_pos) if idx else None, st), "vk_attn_prep_chunk")
                 if not bcsa:
                     break   # (a dense layer pools nothing)
+            if idx:   # the open block's indexer keys: now for a chunk that is committed as it is, else at the commit
+                if write:
+                    _store_open_keys(bc, lst, s.ikc, off_t, bc._pos, lens)
+                else:
+                    ik_kept[i] = s.ikc[:R].clone()
             if bcsa:
                 ck(L.vk_bcsa_select(ctypes.byref(g), _p(s.qi) if idx else _p(s.q), _p(lst["BK"]) if idx else _p(lst["PK"]),
                                     _p(s.pos), _p(s.table), _p(s.sel_scratch), bc.max_blocks, _p(s.sel), _p(s.nsel), R, st),
@@ -260,6 +305,8 @@ def forward_chunk(model, bc, toks, write=False, logits_at=None):
                                  _p(val) if eng else None, _p(w["eng_gate_w"]) if eng else None,
                                  _p(w["eng_gate_b"]) if eng else None, None, R, D, 1 if last else 0, eps, st),
            "vk_mhc_combine_norm")
+        if yield_layers and not last:
+            yield ("layer", i)
     V = model.vocab_shard
     hn, RL, TL = s.hn, R, T            # rows that go through the LM head
     if logits_at is not None:
@@ -283,10 +330,15 @@ def forward_chunk(model, bc, toks, write=False, logits_at=None):
         ck(L.vk_argmax_merge(_p(s.pairs_all), model.tp_size, _p(s.greedy), RL, st), "vk_argmax_merge")
     logits = s.logits[:RL].view(B, TL, V)
     greedy = s.greedy[:RL].view(B, TL)
-    handle = ChunkHandle(lens, list(bc._pos), window, kda_inputs, off_t)
+    handle = ChunkHandle(model, lens, list(bc._pos), window, kda_inputs, off_t, ik_kept)
+    handle.greedy = greedy
+    if caps:
+        f = torch.cat(caps, dim=-1)
+        handle.features = f if ragged else f.view(B, T, -1)
     if write:
         _finish(model, bc, handle, lens, replay=False)
-        return logits, greedy, None
+        handle.kda_inputs, handle.ik = [], {}      # (nothing left to commit; the outputs stay readable)
+        return logits, greedy, (handle if capture else None)
     return logits, greedy, handle
 
 
@@ -309,20 +361,21 @@ def _finish(model, bc, h: ChunkHandle, acc, replay):
                                              _p(lst["S"]), _p(scratch_out), _p(acc_t), _p(h.off), 1, B, T, D, model.Hk,
                                              model.HV, 128, 128, a.kda_gate_rank, a.rms_norm_eps, st),
                        "vk_kda_chunk_ragged")
+    if replay:
+        for i, ikc in h.ik.items():
+            _store_open_keys(bc, bc.layers[i], ikc, h.off, h.pos0, acc)
     if has_kda:          # the conv windows now sit in the other buffer, as after a decode step
         bc.parity ^= 1
         bc.steps += 1
     if h.window is not None:
         idx = torch.tensor(acc, dtype=torch.long, device=dev).unsqueeze(1) + torch.arange(bc.keep, device=dev).unsqueeze(0)
         bc.engram_prev[:B, : bc.keep] = torch.gather(h.window, 1, idx)
-    back = [(b, p // PAGE) for b in range(B) for p in range(h.pos0[b] + acc[b], h.pos0[b] + h.lens[b]) if p % PAGE == 0]
+    # pages opened for positions the rows do not keep go back to the pool (on the GPU: no host round trip)
+    pages = lambda n: (n + PAGE - 1) // PAGE
+    back = [(b, pages(h.pos0[b] + acc[b]), pages(h.pos0[b] + h.lens[b])) for b in range(B)]
+    back = [x for x in back if x[2] > x[1]]
     if back:
-        torch.cuda.synchronize(dev)
-        top = int(bc.free_top.item())
-        for n, (b, pi) in enumerate(back):
-            bc.free_list[top + n] = bc.table[b, pi]
-            bc.table[b, pi] = -1
-        bc.free_top += len(back)
+        bc.release_pages(back, reverse=False)
     bc._pos = [h.pos0[b] + acc[b] for b in range(B)]
     bc.pos[:B] = torch.tensor(bc._pos, dtype=torch.int32, device=dev)
 

@@ -17,6 +17,8 @@
 // kv head comes from that head's query heads against PK. Scores follow the reference's rounding chain
 // bf16(bf16(mean_h fp32(bf16(q_h . k_j))) * scale) with the dot summed in a fixed order (4 consecutive elements per
 // lane, then an xor tree), so the selected indices are reproducible bit for bit.
+#include <atomic>
+
 #include "common.cuh"
 #include "xrec.cuh"
 
@@ -59,6 +61,50 @@ __global__ void batch_step_begin_kernel(const int* __restrict__ pos, int* __rest
     *free_top = top;
 }
 
+// Pages for a chunk of tokens per row: row b is about to hold positions pos[b] .. pos[b] + lens[b] - 1; every position
+// that starts a page takes one from the pool (rows in order, positions in order: the assignment is deterministic, and
+// equals lens[b] single steps of batch_step_begin_kernel).
+__global__ void pages_open_kernel(const int* __restrict__ pos, const int* __restrict__ lens, int* __restrict__ table,
+                                  int max_pages, const int* __restrict__ free_list, int* __restrict__ free_top, int B) {
+    pdl_launch_dependents();
+    pdl_wait();
+    if (threadIdx.x != 0) return;
+    int top = *free_top;
+    for (int b = 0; b < B; b++) {
+        const int p0 = pos[b], p1 = p0 + lens[b];
+        for (int pi = (p0 + kPage - 1) / kPage; pi * kPage < p1; pi++) {
+            if (pi >= max_pages) { vk_set_status(VK_ST_BAD_INDEX); break; }
+            if (top <= 0) { vk_set_status(VK_ST_POOL_EMPTY); break; }
+            table[b * max_pages + pi] = free_list[--top];
+        }
+    }
+    *free_top = top;
+}
+
+// Pages go back to the pool: for item i, the table entries [first[i], last[i]) of row rows[i] (entries that hold no
+// page are skipped), pushed in ascending order, or descending with `reverse` (a row that leaves hands its pages back
+// last first, so that the next row to grow takes them in the order the old row did); the entries become -1.
+__global__ void pages_release_kernel(const int* __restrict__ rows, const int* __restrict__ first, const int* __restrict__ last,
+                                     int n, int reverse, int* __restrict__ table, int max_pages, int* __restrict__ free_list,
+                                     int* __restrict__ free_top, int n_pages) {
+    pdl_launch_dependents();
+    pdl_wait();
+    if (threadIdx.x != 0) return;
+    int top = *free_top;
+    for (int i = 0; i < n; i++) {
+        const int b = rows[i];
+        const int a = max(first[i], 0), z = min(last[i], max_pages);
+        for (int k = 0; k < z - a; k++) {
+            const int pi = reverse ? z - 1 - k : a + k;
+            const int page = table[b * max_pages + pi];
+            if (page < 0) continue;
+            if (page >= n_pages || top >= n_pages) { vk_set_status(VK_ST_BAD_INDEX); continue; }
+            free_list[top++] = page;
+            table[b * max_pages + pi] = -1;
+        }
+    }
+    *free_top = top;
+}
 // every row holds one more token; the KDA conv-state buffers swap roles
 __global__ void batch_step_end_kernel(int* pos, int* parity, int B) {
     pdl_launch_dependents();
@@ -87,6 +133,12 @@ struct PrepParams {
     AttnGeom g;
     int mode;                     // 0: write the row and pool the block it closes; 1: write only; 2: pool only
     const int* row_map;           // null, or [B]: the cache row whose open-block indexer keys (IK) row b uses
+    // Rows that are consecutive positions of one sequence (modes 1 and 2): the normed indexer key of row b goes to
+    // ikc[b] (the C-slot ring of the cache row cannot hold more than one open block), and a block that closes inside
+    // the chunk is pooled from the chunk's own keys, plus the ring for the positions in front of first_pos[b], the
+    // first position the chunk brought for this row's sequence. The ring itself is left alone.
+    __nv_bfloat16* ikc;           // null, or [B, Di]
+    const int* first_pos;         // [B] (with ikc)
 };
 
 // offset RMSNorm of one 128-vector held 4 elements per lane; returns bf16-rounded values
@@ -228,9 +280,29 @@ __global__ void __launch_bounds__(256) attn_prep_kernel(const PrepParams p) {
         if (wr) {
             load4(p.idxk + (size_t)b * kD, lane, x);
             head_norm128(x, p.idx_norm, lane, p.eps);
-            store4(Ip + (size_t)(pos % g.C) * kD, lane, x);
+            store4(p.ikc != nullptr ? p.ikc + (size_t)b * kD : Ip + (size_t)(pos % g.C) * kD, lane, x);
         }
-        if (closes) pool_rows(Ip, g.C, lane, p.BK + ((size_t)page * (kPage / g.C) + slot) * kD);
+        if (closes) {
+            __nv_bfloat16* dst = p.BK + ((size_t)page * (kPage / g.C) + slot) * kD;
+            if (p.ikc == nullptr) {
+                pool_rows(Ip, g.C, lane, dst);
+            } else {   // positions pos - C + 1 .. pos in order: from the chunk's rows, or from the ring in front of it
+                const int first = p.first_pos[b];
+                float acc[4] = {0.f, 0.f, 0.f, 0.f};
+                for (int i = 0; i < g.C; i++) {
+                    const int tp = pos - (g.C - 1) + i;
+                    const __nv_bfloat16* src = tp >= first ? p.ikc + (size_t)(b - (pos - tp)) * kD : Ip + (size_t)(tp % g.C) * kD;
+                    float y[4];
+                    load4(src, lane, y);
+#pragma unroll
+                    for (int e = 0; e < 4; e++) acc[e] += y[e];
+                }
+                const float invc = 1.f / (float)g.C;
+#pragma unroll
+                for (int e = 0; e < 4; e++) acc[e] = bfr(acc[e] * invc);
+                store4(dst, lane, acc);
+            }
+        }
     }
 }
 
@@ -277,7 +349,7 @@ __global__ void __launch_bounds__(256) bcsa_select_kernel(const SelectParams p) 
         if (threadIdx.x == 0) p.nsel[b * g.NS + ns] = nv;
         return;
     }
-    if (nv > p.cap || nv > 65536) {
+    if (nv > p.cap || nv > 65536 || nv > g.max_pages * (kPage / g.C)) {
         if (threadIdx.x == 0) { vk_set_status(VK_ST_BAD_INDEX); p.nsel[b * g.NS + ns] = 0; }
         return;
     }
@@ -296,8 +368,16 @@ __global__ void __launch_bounds__(256) bcsa_select_kernel(const SelectParams p) 
         uint32_t* skeys = reinterpret_cast<uint32_t*>(qsm + 8 * kD);             // [512]
         // (the pages of all blocks first, in one round of loads: a table load in front of every copy below would
         // serialise them, the copy instructions being ordered against memory operations)
-        for (int j = threadIdx.x; j < nv; j += 256) skeys[j] = (uint32_t)p.table[b * g.max_pages + (j / spp)];
-        __syncthreads();
+        int bad = 0;
+        for (int j = threadIdx.x; j < nv; j += 256) {
+            const int page = p.table[b * g.max_pages + (j / spp)];
+            bad |= (page < 0 || page >= p.n_pages);
+            skeys[j] = (uint32_t)page;
+        }
+        if (__syncthreads_or(bad)) {   // a page number outside the pool: nothing is fetched through it
+            if (threadIdx.x == 0) { vk_set_status(VK_ST_BAD_INDEX); p.nsel[b * g.NS + ns] = 0; }
+            return;
+        }
         for (int idx = threadIdx.x; idx < nv * 16; idx += 256) {
             const int j = idx >> 4, piece = idx & 15;
             const int page = (int)skeys[j];
@@ -391,11 +471,16 @@ __global__ void __launch_bounds__(256) bcsa_select_kernel(const SelectParams p) 
 #pragma unroll
         for (int u = 0; u < 4; u++) {
             const int j = j0 + u;
+            kx[u][0] = kx[u][1] = kx[u][2] = kx[u][3] = 0.f;
             if (j < nv) {
                 const int page = p.table[b * g.max_pages + (j / spp)];
-                const __nv_bfloat16* kr = per_kv ? p.keys + (((size_t)page * g.KVH + ns) * spp + j % spp) * kD
-                                                 : p.keys + ((size_t)page * spp + j % spp) * kD;
-                load4(kr, lane, kx[u]);
+                if (page < 0 || page >= p.n_pages) {   // outside the pool: scored as zeros, reported
+                    if (lane == 0) vk_set_status(VK_ST_BAD_INDEX);
+                } else {
+                    const __nv_bfloat16* kr = per_kv ? p.keys + (((size_t)page * g.KVH + ns) * spp + j % spp) * kD
+                                                     : p.keys + ((size_t)page * spp + j % spp) * kD;
+                    load4(kr, lane, kx[u]);
+                }
             }
         }
 #pragma unroll
@@ -502,6 +587,16 @@ struct AttendParams {
 
 constexpr int kRowStride = kD + 8;  // bf16 elements; keeps 16-byte row reads conflict-free
 
+// A page number read from a row's table, checked against the pool: an entry outside it is reported through the
+// status word and replaced by page 0, so nothing is ever read or written outside the pool.
+__device__ __forceinline__ int checked_page(int page, int n_pages) {
+    if (page < 0 || page >= n_pages) {
+        vk_set_status(VK_ST_BAD_INDEX);
+        return 0;
+    }
+    return page;
+}
+
 template <int G>
 __global__ void __launch_bounds__(128) attend_decode_kernel(const AttendParams p) {
     __shared__ __align__(16) __nv_bfloat16 Ks[kPage * kRowStride];
@@ -536,7 +631,7 @@ __global__ void __launch_bounds__(128) attend_decode_kernel(const AttendParams p
         // ---- which rows make up this unit
         int nrows;
         if (u < nwp) {
-            const int page = p.table[b * g.max_pages + wp0 + u];
+            const int page = checked_page(p.table[b * g.max_pages + wp0 + u], p.n_pages);
             const int ra = u == 0 ? lo % kPage : 0;
             const int rb = u == nwp - 1 ? pos % kPage : kPage - 1;
             nrows = rb - ra + 1;
@@ -548,7 +643,7 @@ __global__ void __launch_bounds__(128) attend_decode_kernel(const AttendParams p
         } else if (g.far_tokens) {
             const int j = sel[u - nwp];
             const int tok0 = j * g.C;
-            const int page = p.table[b * g.max_pages + tok0 / kPage];
+            const int page = checked_page(p.table[b * g.max_pages + tok0 / kPage], p.n_pages);
             nrows = g.C;
             if (t < nrows) {
                 const size_t off = (((size_t)page * g.KVH + kv) * kPage + tok0 % kPage + t) * kD;
@@ -560,7 +655,7 @@ __global__ void __launch_bounds__(128) attend_decode_kernel(const AttendParams p
             nrows = min(kPage, nf - f0);
             if (t < nrows) {
                 const int j = sel[f0 + t];
-                const int page = p.table[b * g.max_pages + (j / spp)];
+                const int page = checked_page(p.table[b * g.max_pages + (j / spp)], p.n_pages);
                 const size_t off = (((size_t)page * g.KVH + kv) * spp + j % spp) * kD;
                 rowK[t] = p.PK + off;
                 rowV[t] = p.PV + off;
@@ -770,7 +865,7 @@ __global__ void __launch_bounds__(128) attend_decode_tc_kernel(const AttendParam
     auto setup_unit = [&](int u, const __nv_bfloat16** rk, const __nv_bfloat16** rv) -> int {
         int nrows;
         if (u < nwp) {
-            const int page = p.table[b * g.max_pages + wp0 + u];
+            const int page = checked_page(p.table[b * g.max_pages + wp0 + u], p.n_pages);
             const int ra = u == 0 ? lo % kPage : 0;
             const int rb = u == nwp - 1 ? pos % kPage : kPage - 1;
             nrows = rb - ra + 1;
@@ -782,7 +877,7 @@ __global__ void __launch_bounds__(128) attend_decode_tc_kernel(const AttendParam
         } else if (g.far_tokens) {
             const int j = sel[u - nwp];
             const int tok0 = j * g.C;
-            const int page = p.table[b * g.max_pages + tok0 / kPage];
+            const int page = checked_page(p.table[b * g.max_pages + tok0 / kPage], p.n_pages);
             nrows = g.C;
             if (t < nrows) {
                 const size_t off = (((size_t)page * g.KVH + kv) * kPage + tok0 % kPage + t) * kD;
@@ -794,7 +889,7 @@ __global__ void __launch_bounds__(128) attend_decode_tc_kernel(const AttendParam
             nrows = min(kPage, nf - f0);
             if (t < nrows) {
                 const int j = sel[f0 + t];
-                const int page = p.table[b * g.max_pages + (j / spp)];
+                const int page = checked_page(p.table[b * g.max_pages + (j / spp)], p.n_pages);
                 const size_t off = (((size_t)page * g.KVH + kv) * spp + j % spp) * kD;
                 rk[t] = p.PK + off;
                 rv[t] = p.PV + off;
@@ -937,35 +1032,53 @@ int vk_batch_step_begin(const int* pos, int* table, int max_pages, int* free_lis
                           desc, B, W, C, topk);
 }
 
+int vk_pages_open(const int* pos, const int* lens, int* table, int max_pages, const int* free_list, int* free_top, int B,
+                  cudaStream_t stream) {
+    if (B <= 0 || max_pages <= 0) return VK_EINVAL;
+    return (int)vk_launch(pages_open_kernel, dim3(1), dim3(32), 0, stream, pos, lens, table, max_pages, free_list, free_top, B);
+}
+
+int vk_pages_release(const int* rows, const int* first, const int* last, int n, int reverse, int* table, int max_pages,
+                     int* free_list, int* free_top, int n_pages, cudaStream_t stream) {
+    if (n <= 0 || max_pages <= 0 || n_pages <= 0) return VK_EINVAL;
+    return (int)vk_launch(pages_release_kernel, dim3(1), dim3(32), 0, stream, rows, first, last, n, reverse, table, max_pages,
+                          free_list, free_top, n_pages);
+}
+
 int vk_batch_step_end(int* pos, int* parity, int B, cudaStream_t stream) {
     if (B <= 0) return VK_EINVAL;
     return (int)vk_launch(batch_step_end_kernel, dim3((B + 63) / 64), dim3(64), 0, stream, pos, parity, B);
 }
 
-int vk_attn_prep_rows(const vk_attn_geom* gm, const void* proj, int ldp, int off_k, int off_v, const void* idxq, const void* idxk,
-                      const void* q_norm, const void* k_norm, const void* idx_norm, const int* pos, const int* table, void* q,
-                      void* qi, void* K, void* V, void* PK, void* PV, void* BK, void* IK, int B, int rope_dims,
-                      double rope_theta, float eps, int mode, const int* row_map, cudaStream_t stream);
+int vk_attn_prep_chunk(const vk_attn_geom* gm, const void* proj, int ldp, int off_k, int off_v, const void* idxq, const void* idxk,
+                       const void* q_norm, const void* k_norm, const void* idx_norm, const int* pos, const int* table, void* q,
+                       void* qi, void* K, void* V, void* PK, void* PV, void* BK, void* IK, int B, int rope_dims,
+                       double rope_theta, float eps, int mode, const int* row_map, void* ikc, const int* first_pos,
+                       cudaStream_t stream);
 
 int vk_attn_prep(const vk_attn_geom* gm, const void* proj, int ldp, int off_k, int off_v, const void* idxq, const void* idxk,
                  const void* q_norm, const void* k_norm, const void* idx_norm, const int* pos, const int* table, void* q,
                  void* qi, void* K, void* V, void* PK, void* PV, void* BK, void* IK, int B, int rope_dims, double rope_theta,
                  float eps, cudaStream_t stream) {
-    return vk_attn_prep_rows(gm, proj, ldp, off_k, off_v, idxq, idxk, q_norm, k_norm, idx_norm, pos, table, q, qi, K, V, PK, PV,
-                             BK, IK, B, rope_dims, rope_theta, eps, 0, nullptr, stream);
+    return vk_attn_prep_chunk(gm, proj, ldp, off_k, off_v, idxq, idxk, q_norm, k_norm, idx_norm, pos, table, q, qi, K, V, PK, PV,
+                              BK, IK, B, rope_dims, rope_theta, eps, 0, nullptr, nullptr, nullptr, stream);
 }
 
 // The same for rows that are several positions of one sequence (a verify window, a prefill chunk): a row's block may
 // then be closed by a position whose neighbours are written by other rows of the same launch, so the caller writes all
 // rows first (mode 1) and pools in a second launch (mode 2). row_map names the cache row whose open-block indexer keys
-// a row shares.
-int vk_attn_prep_rows(const vk_attn_geom* gm, const void* proj, int ldp, int off_k, int off_v, const void* idxq, const void* idxk,
-                      const void* q_norm, const void* k_norm, const void* idx_norm, const int* pos, const int* table, void* q,
-                      void* qi, void* K, void* V, void* PK, void* PV, void* BK, void* IK, int B, int rope_dims,
-                      double rope_theta, float eps, int mode, const int* row_map, cudaStream_t stream) {
+// a row shares. In indexer mode the rows' own indexer keys go to ikc [B, Di] and first_pos [B] tells where the chunk
+// began for the row's sequence (see PrepParams); the caller moves the open block's keys into the ring afterwards.
+int vk_attn_prep_chunk(const vk_attn_geom* gm, const void* proj, int ldp, int off_k, int off_v, const void* idxq, const void* idxk,
+                       const void* q_norm, const void* k_norm, const void* idx_norm, const int* pos, const int* table, void* q,
+                       void* qi, void* K, void* V, void* PK, void* PV, void* BK, void* IK, int B, int rope_dims,
+                       double rope_theta, float eps, int mode, const int* row_map, void* ikc, const int* first_pos,
+                       cudaStream_t stream) {
+    if (mode == 0 && ikc != nullptr) return VK_EINVAL;
+    if (ikc != nullptr && first_pos == nullptr) return VK_EINVAL;
     if (!geom_ok(gm) || B <= 0 || rope_dims % 8 != 0 || rope_dims > kD || mode < 0 || mode > 2) return VK_EINVAL;
     PrepParams p = {};
-    p.mode = mode; p.row_map = row_map;
+    p.mode = mode; p.row_map = row_map; p.ikc = (__nv_bfloat16*)ikc; p.first_pos = first_pos;
     p.proj = (const __nv_bfloat16*)proj; p.idxq = (const __nv_bfloat16*)idxq; p.idxk = (const __nv_bfloat16*)idxk;
     p.q_norm = (const __nv_bfloat16*)q_norm; p.k_norm = (const __nv_bfloat16*)k_norm; p.idx_norm = (const __nv_bfloat16*)idx_norm;
     p.pos = pos; p.table = table; p.q = (__nv_bfloat16*)q; p.qi = (__nv_bfloat16*)qi;
@@ -977,16 +1090,24 @@ int vk_attn_prep_rows(const vk_attn_geom* gm, const void* proj, int ldp, int off
     return (int)vk_launch(attn_prep_kernel, dim3(B, (nheads + 7) / 8), dim3(256), 0, stream, p);
 }
 
+int vk_attn_prep_rows(const vk_attn_geom* gm, const void* proj, int ldp, int off_k, int off_v, const void* idxq, const void* idxk,
+                      const void* q_norm, const void* k_norm, const void* idx_norm, const int* pos, const int* table, void* q,
+                      void* qi, void* K, void* V, void* PK, void* PV, void* BK, void* IK, int B, int rope_dims,
+                      double rope_theta, float eps, int mode, const int* row_map, cudaStream_t stream) {
+    return vk_attn_prep_chunk(gm, proj, ldp, off_k, off_v, idxq, idxk, q_norm, k_norm, idx_norm, pos, table, q, qi, K, V, PK, PV,
+                              BK, IK, B, rope_dims, rope_theta, eps, mode, row_map, nullptr, nullptr, stream);
+}
+
 // The selection kernel's shared-memory path needs more than the default 48 KB of dynamic shared memory: opt in once
 // per device (the first selection call on a device must therefore come outside stream capture).
 static bool select_configured() {
-    static bool done[64] = {};
+    static std::atomic<bool> done[64];
     int dev = -1;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return false;
-    if (!done[dev]) {
+    if (!done[dev].load(std::memory_order_acquire)) {
         if (cudaFuncSetAttribute(bcsa_select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSelectSmem) != cudaSuccess)
             return false;
-        done[dev] = true;
+        done[dev].store(true, std::memory_order_release);
     }
     return true;
 }
@@ -1014,26 +1135,33 @@ int vk_bcsa_select(const vk_attn_geom* gm, const void* q, const void* keys, cons
 namespace {
 constexpr int kStaticRows = 16, kStaticGroups = 8, kStaticBlocks = 2048;
 static __device__ __align__(256) uint32_t g_select_scratch[kStaticRows * kStaticGroups * kStaticBlocks];
-uint32_t* g_select_scratch_addr[64] = {};  // device address of the array, per device ordinal (host-side cache)
+std::atomic<uint32_t*> g_select_scratch_addr[64];  // device address of the array, per device ordinal (host-side cache)
 }  // namespace
 
 int vk_bcsa_select_static(const vk_attn_geom* gm, const void* q, const void* keys, const int* pos, const int* table, int* sel,
                           int* nsel, int B, cudaStream_t stream) {
     if (!geom_ok(gm) || gm->W <= 0 || B <= 0) return VK_EINVAL;
-    const int blocks = gm->max_pages * (kPage / gm->C);
+    const long long blocks = (long long)gm->max_pages * (kPage / gm->C);
+    if (gm->max_pages <= 0) return VK_EINVAL;
     if (B > kStaticRows || gm->NS > kStaticGroups || blocks > kStaticBlocks) return VK_ETOOBIG;
     int dev = -1;
     VK_CUDA(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64) return VK_EINVAL;
-    if (g_select_scratch_addr[dev] == nullptr) {
+    uint32_t* scratch = g_select_scratch_addr[dev].load(std::memory_order_acquire);
+    if (scratch == nullptr) {
         // In host code the array's name is only a handle; the kernel needs the address the current device gave it.
+        // (Two host threads that both find the slot empty look the same address up twice: harmless.)
         void* addr = nullptr;
         VK_CUDA(cudaGetSymbolAddress(&addr, g_select_scratch));
-        g_select_scratch_addr[dev] = (uint32_t*)addr;
+        scratch = (uint32_t*)addr;
+        g_select_scratch_addr[dev].store(scratch, std::memory_order_release);
     }
     SelectParams p = {};
     p.q = (const __nv_bfloat16*)q; p.keys = (const __nv_bfloat16*)keys; p.pos = pos; p.table = table;
-    p.scratch = g_select_scratch_addr[dev]; p.sel = sel; p.nsel = nsel; p.cap = kStaticBlocks; p.n_pages = gm->n_pages;
+    // (cap = this geometry's block count, as vk_bcsa_select gets it: a position beyond the row's page table is then
+    // reported instead of indexing past the table; rows are (b * NS + ns) * cap apart, inside the array for every
+    // shape that passed the check above)
+    p.scratch = scratch; p.sel = sel; p.nsel = nsel; p.cap = (int)blocks; p.n_pages = gm->n_pages;
     p.scale = (float)(1.0 / sqrt((double)kD)); p.g = to_geom(gm);
     if (!select_configured()) return VK_EINVAL;
     return (int)vk_launch(bcsa_select_kernel, dim3(p.g.NS, B), dim3(256), kSelectSmem, stream, p);

@@ -741,6 +741,50 @@ __global__ void __launch_bounds__(256) bf16_gemm_rows_kernel(const __nv_bfloat16
     }
 }
 
+// The largest value of row[0 .. valid) and the lowest index that holds it, over a block of 1024 threads. The row is
+// read in 16-byte pieces, four in flight per thread (a row of 150 thousand logits is 300 KB: one piece at a time per
+// thread would pay the memory latency 19 times over); elements in front of the first 16-byte boundary and behind the
+// last whole piece go one by one.
+__device__ __forceinline__ void argmax_take(float v, int i, float& best, int& idx) {
+    if (v > best || (v == best && i < idx)) { best = v; idx = i; }
+}
+__device__ __forceinline__ void argmax_row(const __nv_bfloat16* __restrict__ row, int valid, float& best, int& idx,
+                                           float* bv, int* bi) {
+    best = -INFINITY;
+    idx = 0x7fffffff;
+    int head = (int)(((16u - (unsigned)((uintptr_t)row & 15u)) & 15u) >> 1);
+    head = head < valid ? head : valid;
+    for (int i = threadIdx.x; i < head; i += blockDim.x) argmax_take(bf2f(row[i]), i, best, idx);
+    const int nvec = (valid - head) >> 3;
+    const uint4* v = reinterpret_cast<const uint4*>(row + head);
+    const uint4 lowest = make_uint4(0xFF80FF80u, 0xFF80FF80u, 0xFF80FF80u, 0xFF80FF80u);   // eight times -inf
+    for (int j0 = threadIdx.x; j0 < nvec; j0 += 4 * blockDim.x) {
+        uint4 x[4];
+#pragma unroll
+        for (int u = 0; u < 4; u++) x[u] = j0 + u * (int)blockDim.x < nvec ? v[j0 + u * (int)blockDim.x] : lowest;
+#pragma unroll
+        for (int u = 0; u < 4; u++) {
+            const int i0 = head + 8 * (j0 + u * (int)blockDim.x);
+            const uint32_t w[4] = {x[u].x, x[u].y, x[u].z, x[u].w};
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                argmax_take(bf_lo(w[e]), i0 + 2 * e, best, idx);
+                argmax_take(bf_hi(w[e]), i0 + 2 * e + 1, best, idx);
+            }
+        }
+    }
+    for (int i = head + 8 * nvec + threadIdx.x; i < valid; i += blockDim.x) argmax_take(bf2f(row[i]), i, best, idx);
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+        argmax_take(ov, oi, best, idx);
+    }
+    if ((threadIdx.x & 31) == 0) { bv[threadIdx.x >> 5] = best; bi[threadIdx.x >> 5] = idx; }
+    __syncthreads();
+    if (threadIdx.x == 0)
+        for (int w = 1; w < (int)(blockDim.x >> 5); w++) argmax_take(bv[w], bi[w], best, idx);
+}
+
 // first maximum over logits[:, :vocab_valid] (scheduler.py:391)
 __global__ void __launch_bounds__(1024) argmax_kernel(const __nv_bfloat16* __restrict__ logits, int ld, int valid,
                                                       int* __restrict__ out) {
@@ -749,24 +793,10 @@ __global__ void __launch_bounds__(1024) argmax_kernel(const __nv_bfloat16* __res
     pdl_launch_dependents();
     pdl_wait();
     const int b = blockIdx.x;
-    float best = -INFINITY;
-    int idx = 0x7fffffff;
-    for (int i = threadIdx.x; i < valid; i += blockDim.x) {
-        const float v = bf2f(logits[(size_t)b * ld + i]);
-        if (v > best || (v == best && i < idx)) { best = v; idx = i; }
-    }
-    for (int o = 16; o > 0; o >>= 1) {
-        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
-        const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
-        if (ov > best || (ov == best && oi < idx)) { best = ov; idx = oi; }
-    }
-    if ((threadIdx.x & 31) == 0) { bv[threadIdx.x >> 5] = best; bi[threadIdx.x >> 5] = idx; }
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        for (int w = 1; w < (int)(blockDim.x >> 5); w++)
-            if (bv[w] > best || (bv[w] == best && bi[w] < idx)) { best = bv[w]; idx = bi[w]; }
-        out[b] = idx;
-    }
+    float best;
+    int idx;
+    argmax_row(logits + (size_t)b * ld, valid, best, idx, bv, bi);
+    if (threadIdx.x == 0) out[b] = idx;
 }
 
 // Vocabulary-sharded greedy token. Each rank: (bits of its largest valid logit, global index of its first maximum).
@@ -777,22 +807,10 @@ __global__ void __launch_bounds__(1024) argmax_pairs_kernel(const __nv_bfloat16*
     pdl_launch_dependents();
     pdl_wait();
     const int b = blockIdx.x;
-    float best = -INFINITY;
-    int idx = 0x7fffffff;
-    for (int i = threadIdx.x; i < valid; i += blockDim.x) {
-        const float v = bf2f(logits[(size_t)b * ld + i]);
-        if (v > best || (v == best && i < idx)) { best = v; idx = i; }
-    }
-    for (int o = 16; o > 0; o >>= 1) {
-        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
-        const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
-        if (ov > best || (ov == best && oi < idx)) { best = ov; idx = oi; }
-    }
-    if ((threadIdx.x & 31) == 0) { bv[threadIdx.x >> 5] = best; bi[threadIdx.x >> 5] = idx; }
-    __syncthreads();
+    float best;
+    int idx;
+    argmax_row(logits + (size_t)b * ld, valid, best, idx, bv, bi);
     if (threadIdx.x == 0) {
-        for (int w = 1; w < (int)(blockDim.x >> 5); w++)
-            if (bv[w] > best || (bv[w] == best && bi[w] < idx)) { best = bv[w]; idx = bi[w]; }
         pairs[2 * b] = __float_as_int(best);
         pairs[2 * b + 1] = idx == 0x7fffffff ? idx : idx + index_offset;
     }

@@ -33,7 +33,6 @@ struct KdaParams {
     float* S;                      // [slots, HV, 128, 128]
     __nv_bfloat16* out;            // [B, HV*128]
     uint8_t* xrec_out;             // null, or HV * 2 x records receiving out
-    const float* g_override;       // null, or [B] multipliers: 1 keeps the step, 0 turns it into a no-op (verify replay)
     int ldp, off_z, off_fd, D, Hk, HV, rank;
     float eps;
 };
@@ -200,14 +199,10 @@ __global__ void __launch_bounds__(128, 5) kda_step_kernel(const KdaParams p) {
         gs[c] = expf(-expf(a_log) * softplus_f(a + dtb));
     }
     bdot = bfr(bdot);
-    float beta = 1.f / (1.f + expf(-bdot));
+    const float beta = 1.f / (1.f + expf(-bdot));
     __syncthreads();   // qs / ks / gs / vs
     VK_TS(1, 5);
-    float4 g4 = *reinterpret_cast<const float4*>(gs + 4 * lane);
-    if (p.g_override != nullptr && p.g_override[b] == 0.f) {  // replay past the accepted prefix: g = 1, beta = 0
-        beta = 0.f;
-        g4 = make_float4(1.f, 1.f, 1.f, 1.f);
-    }
+    const float4 g4 = *reinterpret_cast<const float4*>(gs + 4 * lane);
 
     // ---- recurrence: warp w owns rows 32 w .. 32 w + 31 of S; lane l columns 4 l .. 4 l + 3
     const float4 k4 = *reinterpret_cast<const float4*>(ks + 4 * lane);
@@ -292,7 +287,7 @@ __global__ void __launch_bounds__(128, 5) kda_step_kernel(const KdaParams p) {
 constexpr int kChunkTok = 8;
 
 struct KdaChunkParams {
-    KdaParams k;          // proj / h / out rows are (b * T + t); g_override, xrec_out unused
+    KdaParams k;          // proj / h / out rows are (b * T + t); xrec_out unused
     const int* accept;    // [B] or null
     const int* row_off;   // [B] or null: first row of request b in proj / h / out (null: b * T)
     int T;
@@ -694,7 +689,7 @@ int vk_kda_chunk_ragged(const void* proj, int ldp, int off_z, int off_fd, const 
     KdaChunkParams cp = {};
     cp.k = {(const __nv_bfloat16*)proj, (const __nv_bfloat16*)h, (const __nv_bfloat16*)w_b, (const __nv_bfloat16*)w_fup,
             conv_w, A_log, dt_bias, (const __nv_bfloat16*)norm_w, (__nv_bfloat16*)conv, parity, conv_stride, S,
-            (__nv_bfloat16*)out, nullptr, nullptr, ldp, off_z, off_fd, D, Hk, HV, rank, eps};
+            (__nv_bfloat16*)out, nullptr, ldp, off_z, off_fd, D, Hk, HV, rank, eps};
     cp.accept = accept;
     cp.row_off = row_offset;
     cp.T = T;
@@ -717,14 +712,14 @@ int vk_kda_chunk(const void* proj, int ldp, int off_z, int off_fd, const void* h
 
 int vk_kda_step(const void* proj, int ldp, int off_z, int off_fd, const void* h, const void* w_b, const void* w_fup,
                 const float* conv_w, const float* A_log, const float* dt_bias, const void* norm_w, void* conv,
-                const int* parity, size_t conv_stride, float* S, void* out, void* xrec_out, const float* g_override, int B,
+                const int* parity, size_t conv_stride, float* S, void* out, void* xrec_out, int B,
                 int D, int Hk, int HV, int Dk, int Dv, int rank, float eps, cudaStream_t stream) {
     if (B <= 0 || Dk != 128 || Dv != 128 || Hk <= 0 || HV % Hk != 0 || rank <= 0 || rank > 256 || rank % 8 != 0 ||
         D % 8 != 0 || parity == nullptr || (xrec_out != nullptr && B > 16))
         return VK_EINVAL;
     KdaParams p = {(const __nv_bfloat16*)proj, (const __nv_bfloat16*)h, (const __nv_bfloat16*)w_b,
                    (const __nv_bfloat16*)w_fup, conv_w, A_log, dt_bias, (const __nv_bfloat16*)norm_w,
-                   (__nv_bfloat16*)conv, parity, conv_stride, S, (__nv_bfloat16*)out, (uint8_t*)xrec_out, g_override,
+                   (__nv_bfloat16*)conv, parity, conv_stride, S, (__nv_bfloat16*)out, (uint8_t*)xrec_out,
                    ldp, off_z, off_fd, D, Hk, HV, rank, eps};
     return (int)vk_launch(kda_step_kernel, dim3(HV, B), dim3(128), 0, stream, p);
 }

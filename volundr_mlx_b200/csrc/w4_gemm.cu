@@ -19,11 +19,9 @@
 // size equals the algorithmic N*K/2 + N*(K/64)*4 bytes and no byte of it is read twice.
 //
 // Activation layout ("x records"). Per 64-column group one 2176-byte record: x[16 rows][64] bf16 with the eight
-// 16-byte pieces of a row xor-swizzled by (row & 7) (conflict-free ldmatrix), then per row two words holding the
-// group's row sum S split into two bf16 parts, S = S_hi + S_lo: word 0 = (-128 S_hi, S_hi), word 1 = (-128 S_lo, S_lo).
-// With the row's (scale, bias) word as A operand they are the B operand of one extra mma per group that adds
-// (bias - 128 scale) * S to the accumulator (every factor is an exact bf16, the products are exact in fp32).
-// vk_w4_gemm builds the records from a row-major x with a small kernel.
+// 16-byte pieces of a row xor-swizzled by (row & 7) (conflict-free ldmatrix), then the sixteen rows' sums over the
+// group's 64 columns as fp32 (64 bytes; the record's last 64 bytes are unused). The kernel adds (bias - 128 scale) * S
+// to the accumulator with them. vk_w4_gemm builds the records from a row-major x with a small kernel.
 //
 // Work split. total = superblocks * groups steps, in superblock-major order, dealt in equal contiguous ranges to
 // P persistent CTAs (two per SM). A CTA is one producer warp (TMA into an 8-stage ring: weights as soon as the CTA
@@ -143,9 +141,6 @@ __global__ void __launch_bounds__(kThreads, ctas_per_sm<FMT, MT>()) w4_gemm_kern
     }
     const int n = (int)(t1 - t0);
 
-    if (threadIdx.x >= 32 && threadIdx.x < 32 + kStages * 4)   // the 16 zero bytes behind every stage's x record
-        *reinterpret_cast<uint32_t*>(smem + (size_t)((threadIdx.x - 32) >> 2) * kStageBytes + kWStageBytes + kXR +
-                                     ((threadIdx.x - 32) & 3) * 4) = 0u;
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; s++) {
             mbar_init(&full[s], 1);
@@ -380,15 +375,14 @@ __global__ void __launch_bounds__(kThreads, ctas_per_sm<FMT, MT>()) w4_gemm_kern
                 for (int e = 0; e < 4; e++) acc[s][jj][e] = 0.f;
     };
 
-    // per-lane offsets inside a stage that do not change from step to step: the four ldmatrix sources, and the
-    // bias-term words (threads t >= 2 hold columns the term does not use: they read the stage's zero bytes)
+    // per-lane offsets inside a stage that do not change from step to step: the four ldmatrix sources and the group
+    // sums of this lane's activation rows
     uint32_t lm_off[4];
 #pragma unroll
     for (int q = 0; q < 4; q++) lm_off[q] = kWStageBytes + lm_row * 128 + (((2 * q + lm_half) ^ lm_r) << 4);
-    uint32_t bw_off[MT];
+    uint32_t sum_off[MT];   // the fp32 group sums of activation rows 8 jj + 2 t, 8 jj + 2 t + 1
 #pragma unroll
-    for (int jj = 0; jj < MT; jj++)
-        bw_off[jj] = t < 2 ? kWStageBytes + (jj >> 1) * kXRecBytes + 2048 + ((jj & 1) * 8 + g) * 8 + t * 4 : kWStageBytes + kXR;
+    for (int jj = 0; jj < MT; jj++) sum_off[jj] = kWStageBytes + (jj >> 1) * kXRecBytes + 2048 + ((jj & 1) * 8 + 2 * t) * 4;
     int st = 0;
     uint32_t phase = 0;
 #if defined(VK_TRACE) && VK_TRACE == 2
@@ -464,27 +458,33 @@ __global__ void __launch_bounds__(kThreads, ctas_per_sm<FMT, MT>()) w4_gemm_kern
                 else mma_bf16(d[1][jj], a, b[2 * jj], b[2 * jj + 1]);
             }
         }
-        // group epilogue: acc += s * (D - 128 S) + b * S = s * D + (b - 128 s) * S. The second term goes through one
-        // more mma: A = the rows' (scale, bias) words in columns 0..3, B = (-128 S_hi, S_hi, -128 S_lo, S_lo).
+        // group epilogue: acc += s * (D - 128 S) + b * S = s * D + (b - 128 s) * S, S = the group's sum of the activation
+        // row in fp32 (written into the record by whoever produced it), two fused multiply-adds per accumulator. (An
+        // earlier form sent the second term through one more mma per n-tile, with S split into two bf16 parts: at 16
+        // rows the kernel is bound by the throughput of mma.sync itself, so four mma out of twenty were a fifth of its
+        // time, and the 16-bit S cost accuracy: about 1e-4 of the result, enough to round 2 % of the outputs the other
+        // way.)
         const uint32_t sbw[4] = {sb4.x, sb4.y, sb4.z, sb4.w};
-        uint32_t bw[MT];
+        float xs[MT][2];
 #pragma unroll
-        for (int jj = 0; jj < MT; jj++) bw[jj] = *reinterpret_cast<const uint32_t*>(stage + bw_off[jj]);
+        for (int jj = 0; jj < MT; jj++) {
+            const float2 sv = *reinterpret_cast<const float2*>(stage + sum_off[jj]);
+            xs[jj][0] = sv.x;
+            xs[jj][1] = sv.y;
+        }
         __syncwarp();
         if (lane == 0) mbar_arrive(&empty[st]);   // everything of this stage is in registers now
 #pragma unroll
         for (int s = 0; s < 2; s++) {
             const float s0 = bf_lo(sbw[2 * s]), s1 = bf_lo(sbw[2 * s + 1]);
+            const float c0 = fmaf(-128.f, s0, bf_hi(sbw[2 * s])), c1 = fmaf(-128.f, s1, bf_hi(sbw[2 * s + 1]));
 #pragma unroll
             for (int jj = 0; jj < MT; jj++) {
-                acc[s][jj][0] = fmaf(s0, d[s][jj][0], acc[s][jj][0]);
-                acc[s][jj][1] = fmaf(s0, d[s][jj][1], acc[s][jj][1]);
-                acc[s][jj][2] = fmaf(s1, d[s][jj][2], acc[s][jj][2]);
-                acc[s][jj][3] = fmaf(s1, d[s][jj][3], acc[s][jj][3]);
+                acc[s][jj][0] = fmaf(c0, xs[jj][0], fmaf(s0, d[s][jj][0], acc[s][jj][0]));
+                acc[s][jj][1] = fmaf(c0, xs[jj][1], fmaf(s0, d[s][jj][1], acc[s][jj][1]));
+                acc[s][jj][2] = fmaf(c1, xs[jj][0], fmaf(s1, d[s][jj][2], acc[s][jj][2]));
+                acc[s][jj][3] = fmaf(c1, xs[jj][1], fmaf(s1, d[s][jj][3], acc[s][jj][3]));
             }
-            const uint32_t ab[4] = {sbw[2 * s], sbw[2 * s + 1], 0u, 0u};   // (columns 4..7 meet zeros in B)
-#pragma unroll
-            for (int jj = 0; jj < MT; jj++) mma_bf16(acc[s][jj], ab, bw[jj], 0u);
         }
         }
         if (++kg == p.G) {

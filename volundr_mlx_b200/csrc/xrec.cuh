@@ -1,7 +1,7 @@
 // The activation layout the streaming GEMM reads ("x records"): per 64-column group one 2176-byte record,
 //   bytes 0..2047    x[16 rows][64] bf16, the eight 16-byte pieces of a row xor-swizzled by (row & 7),
-//   bytes 2048..2175 per row two words from the group's row sum S = S_hi + S_lo (two bf16 parts):
-//                    word 0 = (-128 S_hi, S_hi), word 1 = (-128 S_lo, S_lo).
+//   bytes 2048..2111 S[16 rows] fp32: the sum of the row's 64 values of this group (the values as stored, i.e. after
+//                    their rounding to bf16), added in a fixed order; bytes 2112..2175 unused.
 // Kernels that produce a GEMM input write their rows straight into records with these helpers (the reference fuses
 // the same preparation into its producers: agens-mlx-bench/smallm/prep_nax.py:24-148). Rows a batch does not use
 // must hold zeros.
@@ -19,11 +19,7 @@ __device__ __forceinline__ __nv_bfloat16* xrec_elem(uint8_t* xrec, int kg, int m
     return reinterpret_cast<__nv_bfloat16*>(xrec_piece(xrec, kg, m, k >> 3)) + (k & 7);
 }
 __device__ __forceinline__ void xrec_store_sum(uint8_t* xrec, int kg, int m, float s) {
-    const float hi = bfr(s), lo = bfr(s - hi);
-    uint2 w;
-    w.x = pack_bf2(-128.f * hi, hi);
-    w.y = pack_bf2(-128.f * lo, lo);
-    *reinterpret_cast<uint2*>(xrec + (size_t)kg * kXRecBytes + 2048 + m * 8) = w;
+    *reinterpret_cast<float*>(xrec + (size_t)kg * kXRecBytes + 2048 + m * 4) = s;
 }
 // Eight consecutive lanes hold the eight pieces of one (row, group): each lane's 8 values are added in order, then an
 // xor tree over the lanes; the lane of piece 0 stores the sum words.
