@@ -52,11 +52,17 @@ size_t vk_w4_workspace_bytes(int M, int N, int K);
 int vk_w4_gemm(const void* packed, const void* x, int ldx, void* y, int ldy, int M, int N, int K, void* workspace,
                size_t workspace_bytes, vk_stream_t stream);
 /* The same product for activations that already sit in the kernel's input layout ("x records": per 64 columns 2176
- * bytes = 16 rows x 64 bf16 with the 16-byte pieces xor-swizzled by row, then the sixteen rows' sums over the group as fp32;
+ * bytes = 16 rows x 64 bf16 stored [16-byte piece][row][8 values], then the sixteen rows' sums over the group as fp32;
  * rows >= M zero). The row kernels below write this layout directly when given an `xrec_*` pointer (as the reference
  * fuses its input preparation into the producing op, agens-mlx-bench/smallm/prep_nax.py:24-148). M <= 16. */
 int vk_w4_gemm_xrec(const void* packed, const void* xrec, void* y, int ldy, int M, int N, int K, void* workspace,
                     size_t workspace_bytes, vk_stream_t stream);
+/* Which kernel multiplies up to 16 activation rows (vk_w4_gemm_xrec, vk_w4_gemm with M <= 16): 1 (default) the
+ * tcgen05 form (the codes expanded to bf16 in shared memory, the product on the 5th-generation tensor cores with the
+ * accumulator in tensor memory, scale and bias applied per group by the warps), 0 the mma.sync form. Same arithmetic and
+ * the same fixed sum order; the two differ in the last bits (the tensor cores' internal summation). A testing and
+ * measuring aid: set it before the first launch of a CUDA graph that records these calls. */
+void vk_w4_select(int tcgen05);
 /* The same streaming kernel over plain bf16 weights: the linears the reference keeps unquantised (convert.py:16-17),
  * above all lm_head (volundr.py:958, :968; batch.py:552). W [N, K] row-major bf16 is repacked once into the kernel's
  * fragment order (vk_bf16_repack); y = bf16(x . W^T), fp32 accumulation, 1..16 rows per pass. Workspace rules as for

@@ -59,26 +59,31 @@ def _check_gemm(cuda, rng, M, N, K, group, cols=None, force=None):
     wt = ops.w4_repack(*to_dev(w, s, b, cuda), group)
     tx = torch.from_numpy(x).to(cuda).to(torch.bfloat16)
     L = _lib.lib()
-    if force:
-        L.vk_w4_force_plan(*force)
-    try:
-        y = ops.w4_gemm(tx, wt)
-        y2 = ops.w4_gemm(tx, wt)
-        ops.check_status()
-    finally:
-        L.vk_w4_force_plan(0, 0)
-    assert torch.equal(y, y2), "the product must not depend on scheduling"
-    got = y.float().cpu().numpy()
     sel = np.arange(N) if cols is None else cols
     want = OW.matmul(x, w[sel], s[sel], b[sel], group)
-    np.testing.assert_allclose(got[:, sel], want, rtol=2e-2, atol=2e-2)
-    # and much tighter against the exact product (the kernel keeps s*u + b unrounded)
     W = OW.unpack_codes(w[sel], K).astype(np.float64) * np.repeat(s[sel].astype(np.float64), group, 1) + \
         np.repeat(b[sel].astype(np.float64), group, 1)
     exact = x.astype(np.float64) @ W.T
-    err = np.abs(got[:, sel] - exact)
-    assert (err <= 2.0 ** -8 * np.abs(exact) + 2e-3).all(), err.max()
-    return y
+    ys = []
+    for tcgen05 in (1, 0):      # up to 16 rows: the tcgen05 form (the default) and the mma.sync form of the same arithmetic
+        L.vk_w4_select(tcgen05)
+        if force:
+            L.vk_w4_force_plan(*force)
+        try:
+            y = ops.w4_gemm(tx, wt)
+            y2 = ops.w4_gemm(tx, wt)
+            ops.check_status()
+        finally:
+            L.vk_w4_force_plan(0, 0)
+            L.vk_w4_select(1)
+        assert torch.equal(y, y2), "the product must not depend on scheduling"
+        got = y.float().cpu().numpy()
+        np.testing.assert_allclose(got[:, sel], want, rtol=2e-2, atol=2e-2)
+        # and much tighter against the exact product (the kernel keeps s*u + b unrounded)
+        err = np.abs(got[:, sel] - exact)
+        assert (err <= 2.0 ** -8 * np.abs(exact) + 2e-3).all(), (tcgen05, err.max())
+        ys.append(y)
+    return ys[0]
 
 
 @pytest.mark.parametrize("M", [1, 2, 3, 4, 8, 9, 16])

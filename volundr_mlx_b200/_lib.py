@@ -23,6 +23,7 @@ SIGNATURES = {
     "vk_w4_gemm_tile": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_size_t, c_void_p]),
     "vk_w4_tile_force": (c_int, [c_int, c_int]),
     "vk_w4_force_plan": (None, [c_int, c_int]),
+    "vk_w4_select": (None, [c_int]),
     "vk_w4_workspace_bytes": (c_size_t, [c_int, c_int, c_int]),
     "vk_w4_gemm": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_size_t, c_void_p]),
     "vk_bf16_packed_bytes": (c_size_t, [c_int, c_int]),

@@ -107,10 +107,26 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t phase) {
         : "memory");
     return ok != 0;
 }
+// Non-blocking look at the barrier: true when phase `phase` has completed. (try_wait may suspend the thread for a while
+// even when the phase is already complete; a plain test returns at shared-memory latency.)
+__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t phase) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(phase)
+        : "memory");
+    return ok != 0;
+}
 // Wait for phase `phase` of `bar` with an iteration limit. Returns false (and records VK_ST_MBAR_TIMEOUT) when the
 // limit runs out, so a copy that never lands ends the kernel instead of hanging the GPU.
 #define VK_MBAR_SPIN_LIMIT (1u << 20)
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t phase) {
+#ifndef VK_NO_TEST_WAIT
+    if (mbar_test_wait(bar, phase)) return true;
+#endif
     for (uint32_t i = 0; i < VK_MBAR_SPIN_LIMIT; i++) {
         if (mbar_try_wait(bar, phase)) return true;
     }

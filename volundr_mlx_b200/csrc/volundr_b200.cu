@@ -2,6 +2,7 @@
 #include "runtime.cu"
 #include "w4_gemm.cu"
 #include "w4_tile.cu"
+#include "w4_t5.cu"
 #include "elementwise.cu"
 #include "allreduce.cu"
 #include "kda.cu"

@@ -18,8 +18,8 @@
 // One step of the kernel = one (superblock, group) = 9216 contiguous bytes, fetched by one TMA bulk copy; the packed
 // size equals the algorithmic N*K/2 + N*(K/64)*4 bytes and no byte of it is read twice.
 //
-// Activation layout ("x records"). Per 64-column group one 2176-byte record: x[16 rows][64] bf16 with the eight
-// 16-byte pieces of a row xor-swizzled by (row & 7) (conflict-free ldmatrix), then the sixteen rows' sums over the
+// Activation layout ("x records"). Per 64-column group one 2176-byte record: x[16 rows][64] bf16 stored
+// [16-byte piece 8][row 16][8 bf16] (conflict-free ldmatrix; also a tcgen05 K-major operand), then the sixteen rows' sums over the
 // group's 64 columns as fp32 (64 bytes; the record's last 64 bytes are unused). The kernel adds (bias - 128 scale) * S
 // to the accumulator with them. vk_w4_gemm builds the records from a row-major x with a small kernel.
 //
@@ -379,7 +379,7 @@ __global__ void __launch_bounds__(kThreads, ctas_per_sm<FMT, MT>()) w4_gemm_kern
     // sums of this lane's activation rows
     uint32_t lm_off[4];
 #pragma unroll
-    for (int q = 0; q < 4; q++) lm_off[q] = kWStageBytes + lm_row * 128 + (((2 * q + lm_half) ^ lm_r) << 4);
+    for (int q = 0; q < 4; q++) lm_off[q] = kWStageBytes + ((2 * q + lm_half) * 16 + lm_row) * 16;
     uint32_t sum_off[MT];   // the fp32 group sums of activation rows 8 jj + 2 t, 8 jj + 2 t + 1
 #pragma unroll
     for (int jj = 0; jj < MT; jj++) sum_off[jj] = kWStageBytes + (jj >> 1) * kXRecBytes + 2048 + ((jj & 1) * 8 + 2 * t) * 4;
@@ -611,6 +611,12 @@ __global__ void bf16_repack_kernel(const __nv_bfloat16* __restrict__ W, int N, i
     reinterpret_cast<uint32_t*>(out)[idx] = v;
 }
 
+// 0 (default): up to 16 activation rows run on w4_gemm_kernel<MT, 0> (mma.sync); 2 / 3: on w4_t5_kernel (tcgen05,
+// w4_t5.cu) with that many steps between a warp's expansion and accumulation of a step: measured at half the speed
+int g_w4_t5 = 0;
+struct W4Params;
+cudaError_t w4_t5_launch(const W4Params& p, cudaStream_t stream);
+
 int g_force_ctas = 0;
 int g_prefetch_mb = 0;    // L2 prefetch budget of one GEMM launch in MB; off by default: measured slower (it competes with demand loads)
 
@@ -668,7 +674,8 @@ template <int MT>
 static cudaError_t w4_launch_pass(const void* packed, const __nv_bfloat16* x, int ldx, __nv_bfloat16* y, int ldy, int m, int N,
                                   int K, uint8_t* ws, cudaStream_t stream) {
     constexpr int NR = n_records<MT>(), PS = MT * 8 < 16 ? 16 : MT * 8;
-    const W4Plan pl = w4_plan(N, K, ctas_per_sm<0, MT>());
+    const bool t5 = MT <= 2 && g_w4_t5 != 0;
+    const W4Plan pl = w4_plan(N, K, t5 ? 1 : ctas_per_sm<0, MT>());
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(w4_gemm_kernel<MT, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes<0, MT>());
@@ -688,6 +695,7 @@ static cudaError_t w4_launch_pass(const void* packed, const __nv_bfloat16* x, in
     (void)PS;
     cudaError_t e = vk_launch(w4_xrec_kernel, dim3(pl.G, NR), dim3(128), 0, stream, x, ldx, m, ws + kCounterBytes);
     if (e != cudaSuccess) return e;
+    if (t5) return w4_t5_launch(p, stream);
     return vk_launch(w4_gemm_kernel<MT, 0>, dim3(pl.P), dim3(kThreads), smem_bytes<0, MT>(), stream, p);
 }
 
@@ -721,9 +729,13 @@ void vk_w4_force_plan(int ctas, int prefetch_mb) {
     g_prefetch_mb = prefetch_mb < 0 ? 0 : prefetch_mb;
 }
 
+void vk_w4_select(int tcgen05) { g_w4_t5 = tcgen05 < 0 ? 0 : tcgen05; }
+
 size_t vk_w4_workspace_bytes(int M, int N, int K) {
     if (N <= 0 || K <= 0 || K % 64 != 0) return 0;
     size_t need = w4_ws_bytes(w4_plan(N, K));
+    const size_t one = w4_ws_bytes(w4_plan(N, K, 1));   // (the tcgen05 kernel runs one CTA per SM)
+    need = one > need ? one : need;
     if (M > 16) {   // passes of 32 / 64 rows: one CTA per SM, wider records and partial sums
         const size_t wide = w4_ws_bytes(w4_plan(N, K, 1), M > 32 ? 4 : 2, M > 32 ? 64 : 32);
         need = wide > need ? wide : need;
@@ -737,11 +749,12 @@ int vk_w4_gemm_xrec(const void* packed, const void* xrec, void* y, int ldy, int 
                     size_t workspace_bytes, cudaStream_t stream) {
     if (M <= 0 || M > 16 || N <= 0 || K <= 0 || K % 64 != 0 || ldy < N) return VK_EINVAL;
     if (((uintptr_t)xrec & 15) || ((uintptr_t)packed & 15) || workspace == nullptr || ((uintptr_t)workspace & 15)) return VK_EINVAL;
-    const W4Plan pl = w4_plan(N, K);
-    if (pl.NSB > (int)(kCounterBytes / 4)) return VK_EINVAL;
+    const bool t5 = g_w4_t5 != 0;
+    const W4Plan pl = w4_plan(N, K, t5 ? 1 : Fmt<0>::kCtasPerSM);
+    if (pl.NSB > (int)(kCounterBytes / 8)) return VK_EINVAL;
     if (workspace_bytes < w4_ws_bytes(pl)) return VK_ENOSPC;
     static bool configured = false;
-    if (!configured) {
+    if (!t5 && !configured) {
         VK_CUDA(cudaFuncSetAttribute(w4_gemm_kernel<1, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes<0>()));
         VK_CUDA(cudaFuncSetAttribute(w4_gemm_kernel<1, 0>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
         VK_CUDA(cudaFuncSetAttribute(w4_gemm_kernel<2, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes<0>()));
@@ -757,6 +770,7 @@ int vk_w4_gemm_xrec(const void* packed, const void* xrec, void* y, int ldy, int 
     p.part = (float*)(ws + kCounterBytes + (size_t)pl.G * kXRecBytes);
     p.T = pl.T; p.M = M; p.N = N; p.NSB = pl.NSB; p.G = pl.G; p.P = pl.P; p.ldy = ldy; p.maxc = pl.maxc; p.S = pl.S;
     p.pf = w4_prefetch_steps(pl.P, (size_t)wstage_bytes<0>(), Fmt<0>::kStages);
+    if (t5) return (int)w4_t5_launch(p, stream);
     cudaError_t e = M <= 8 ? vk_launch(w4_gemm_kernel<1, 0>, dim3(pl.P), dim3(kThreads), smem_bytes<0>(), stream, p)
                            : vk_launch(w4_gemm_kernel<2, 0>, dim3(pl.P), dim3(kThreads), smem_bytes<0>(), stream, p);
     return (int)e;

@@ -1,5 +1,9 @@
 // The activation layout the streaming GEMM reads ("x records"): per 64-column group one 2176-byte record,
-//   bytes 0..2047    x[16 rows][64] bf16, the eight 16-byte pieces of a row xor-swizzled by (row & 7),
+//   bytes 0..2047    x[16 rows][64] bf16 as [piece 8][row 16][8 bf16]: the 16-byte piece c of row m (columns 8 c ..
+//                    8 c + 7) sits at (c * 16 + m) * 16. The eight rows of a piece's 8 x 8 matrix are contiguous, which
+//                    is what ldmatrix reads without bank conflicts and what a tcgen05 shared-memory operand without
+//                    swizzle wants (core matrices of 8 rows x 16 bytes; 256 bytes between pieces along K, 128 bytes
+//                    between the two row groups),
 //   bytes 2048..2111 S[16 rows] fp32: the sum of the row's 64 values of this group (the values as stored, i.e. after
 //                    their rounding to bf16), added in a fixed order; bytes 2112..2175 unused.
 // Kernels that produce a GEMM input write their rows straight into records with these helpers (the reference fuses
@@ -12,7 +16,7 @@ constexpr int kXRecBytes = 2176;
 
 // 16-byte piece `c` (0..7) of row m in group kg
 __device__ __forceinline__ uint8_t* xrec_piece(uint8_t* xrec, int kg, int m, int c) {
-    return xrec + (size_t)kg * kXRecBytes + m * 128 + ((c ^ (m & 7)) << 4);
+    return xrec + (size_t)kg * kXRecBytes + ((c << 4) + m) * 16;
 }
 // element k (0..63) of row m in group kg
 __device__ __forceinline__ __nv_bfloat16* xrec_elem(uint8_t* xrec, int kg, int m, int k) {

@@ -69,6 +69,10 @@ def main():
         from . import _lib
         tn, ml = (int(v) for v in a.tile_shape.split(","))
         _lib.check(_lib.lib().vk_w4_tile_force(tn, ml), "vk_w4_tile_force")
+    import os
+    if os.environ.get("VK_W4_SELECT"):   # 0: mma.sync kernel, 2 / 3: the tcgen05 kernel with that expansion-to-accumulation lag
+        from . import _lib
+        _lib.lib().vk_w4_select(int(os.environ["VK_W4_SELECT"]))
     copies = a.copies or max(2, int(400e6 // (a.n * a.k * 0.5625)) + 1)
     print(json.dumps(run(a.m, a.n, a.k, copies, a.launches, a.replays, tile=a.tile)))
 
