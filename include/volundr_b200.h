@@ -287,6 +287,20 @@ int vk_attend_decode(const vk_attn_geom* g, const void* q, const void* K, const 
                      const int* pos, const int* table, const int* sel, const int* nsel, const void* proj, int ldp,
                      void* part, int nsplit, void* out, void* xrec_out, int B, vk_stream_t stream);
 
+/* The same attention for rows that are consecutive positions of one sequence (the T tokens of a verify window, a
+ * prefill chunk): bcsa_verify.attend (bcsa_verify.py:278-317), far_union + bcsa_attend (kernels.py:931-1020, :1023-1165;
+ * volundr.py:793-827) and the dense layer of batch_spec._dense (batch_spec.py:50-64). Rows are given in tiles of up to
+ * 16 consecutive rows of one sequence (tile_first / tile_count, device arrays of n_tiles ints; the rows' positions are
+ * pos[first], pos[first] + 1, ...): a tile's K / V are read once for all its rows, far blocks = the union of the rows'
+ * selections with a per-row mask. K / V of every row must already be in the pages (vk_attn_prep_chunk). nv_cap: an upper
+ * bound of the valid far blocks of any row (sizes the kernel's shared memory: vk_attend_chunk_smem_bytes; more than about
+ * 200 KB returns -3 and the caller uses vk_attend_decode). part: as for vk_attend_decode with B = R. */
+size_t vk_attend_chunk_smem_bytes(const vk_attn_geom* g, int nv_cap);
+int vk_attend_chunk(const vk_attn_geom* g, const void* q, const void* K, const void* V, const void* PK, const void* PV,
+                    const int* pos, const int* table, const int* sel, const int* nsel, const int* tile_first,
+                    const int* tile_count, int n_tiles, int nv_cap, const void* proj, int ldp, void* part, int nsplit, void* out,
+                    int R, vk_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

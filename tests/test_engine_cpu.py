@@ -125,3 +125,141 @@ def test_engine_ragged_prefill_chunks(monkeypatch):
         assert out[k] == solo(p, n), k
     assert eng.chunk_steps >= (69 + 125) // 4 // 3
     assert steps < sum(len(p) + n for p, n in reqs) // 3     # far fewer steps than one token per step would take
+
+
+# ---------------------------------------------------------------------------------- sliced prefill, sessions (fakes)
+class FakeState:
+    def __init__(self, hist, logits=None):
+        self.hist, self.logits, self.pos, self.nbytes = list(hist), logits, len(hist), 8 * len(hist) + 8
+
+
+class SlicedFakeCache(FakeCache):
+    """apply(join=[(key, state)]) / capture_row as the real cache offers them."""
+
+    def apply(self, leave=(), join=()):
+        plain = []
+        for item in join:
+            if isinstance(item, tuple):
+                k, st = item
+                assert self.B + len(plain) < self.S
+                self.keys.append(k)
+                self.hist[k] = list(st.hist) if st is not None else []
+            else:
+                plain.append(item)
+        super().apply(leave=leave, join=plain)
+
+    def capture_row(self, key, logits=None):
+        return FakeState(self.hist[key], logits)
+
+
+class SlicedFakeModel:
+    class args:
+        vocab_valid = 997
+
+    def make_cache(self, max_rows, n_pages, max_pages_per_row):
+        return SlicedFakeCache(max_rows)
+
+
+LAYERS = 5
+
+
+def fake_forward_chunk_iter(model, bc, toks, write=False, logits_at=None, capture=(), yield_layers=True):
+    """A chunk pass of LAYERS layers that hands control back after every layer but the last; the cache only changes when
+    the pass completes."""
+    assert write and len(toks) == bc.B == 1 and logits_at == [len(toks[0]) - 1]
+    for i in range(LAYERS - 1):
+        yield ("layer", i)
+    k = bc.keys[0]
+    bc.hist[k] += [int(x) for x in toks[0]]
+    g = fake_next(bc.hist[k])
+    logits = torch.zeros(1, 1, 997)
+    logits[0, 0, g] = 1.0
+    return logits, torch.tensor([[g]], dtype=torch.int32), None
+
+
+def _sliced_engine(monkeypatch, sessions=None, slice_layers=3, **kw):
+    monkeypatch.setattr(E.BT, "forward", fake_forward)
+    monkeypatch.setattr(E.CH, "forward_chunk_iter", fake_forward_chunk_iter)
+    clock = {"t": 0.0, "log": []}
+    eng = E.BatchEngine(SlicedFakeModel(), prefill_chunk=4, slice_ms=1000.0 * slice_layers, sessions=sessions,
+                        clock=lambda: clock["t"], **kw)
+
+    def sync():                     # every layer the engine waits for costs one unit of (fake) time
+        clock["t"] += 1.0
+        clock["log"].append("L")
+    eng._sync = sync
+    real_forward = E.BT.forward
+
+    def logged_forward(model, bc, toks):
+        clock["log"].append("D")
+        return real_forward(model, bc, toks)
+    monkeypatch.setattr(E.BT, "forward", logged_forward)
+    return eng, clock
+
+
+def test_sliced_prefill_interleaves_with_decode(monkeypatch):
+    """While rows decode, no more than a slice's worth of prefill layers (+ the one that overruns it) runs between two
+    decode steps, a chunk is resumed where it stopped, and every request still gets its solo output."""
+    eng, clock = _sliced_engine(monkeypatch, slice_layers=3, max_rows=3, n_pages=8, max_pages_per_row=2)
+    reqs = [([5, 6, 7], 30), (list(range(1, 60)), 4), ([9, 8, 7, 6, 5, 4, 3, 2, 1], 3), (list(range(3, 40)), 2)]
+    keys = [eng.submit(p, n) for p, n in reqs]
+    out = eng.run()
+    for k, (p, n) in zip(keys, reqs):
+        assert out[k] == solo(p, n), k
+    log = "".join(clock["log"])
+    assert "D" in log and "L" in log
+    # between two decode steps: at most slice_layers layers are waited for (the slice ends at the first layer boundary
+    # at or past the deadline)
+    runs = [len(x) for x in log.strip("L").split("D") if x]
+    assert runs and max(runs) <= 3, runs
+    assert eng.stats["slices"] > 0 and eng.stats["slice_layers_max"] <= 3
+    assert eng.reserved == 0 and eng.bc.B == 0 and eng.pc.B == 0
+
+
+def test_sessions_resume_from_longest_prefix(monkeypatch):
+    from volundr_mlx_b200.session import SessionCache
+
+    sc = SessionCache(budget_gb=1.0, interval=16, min_gap=4)
+    eng, _ = _sliced_engine(monkeypatch, sessions=sc, max_rows=2, n_pages=8, max_pages_per_row=4)
+    first = list(range(1, 50))
+    k1 = eng.submit(first, 5, session="s")
+    out = eng.run()
+    assert out[k1] == solo(first, 5)
+    kinds = sorted(s.kind for s in sc.snaps)
+    assert kinds == ["interval", "interval", "prompt", "reply"], kinds          # positions 16, 32; 49; 49 + 4
+    # a follow-up turn: the first prompt, the reply, and new tokens: only the new tokens are prefilled
+    reply = out[k1]
+    follow = first + reply + [7, 7, 7]
+    fed_before = eng.chunk_steps
+    k2 = eng.submit(follow, 3, session="s")
+    out = eng.run()
+    assert out[k2] == solo(follow, 3)
+    assert eng.finished[k2].resumed == len(first) + len(reply) - 1              # the end-of-reply snapshot
+    assert eng.chunk_steps - fed_before == 1                                    # 4 tokens left: one chunk
+    # the very same prompt again: nothing is prefilled, the first token comes from the snapshot's logits
+    fed_before = eng.chunk_steps
+    k3 = eng.submit(first, 2, session="other")
+    out = eng.run()
+    assert out[k3] == solo(first, 2) and eng.chunk_steps == fed_before
+    assert eng.stats["resumed_tokens"] >= len(first)
+
+
+def test_session_cache_budget_and_lookup():
+    import numpy as np
+    from volundr_mlx_b200.session import SessionCache
+
+    sc = SessionCache(budget_gb=1e-6, interval=8, min_gap=2)     # 1000 bytes
+    mk = lambda n: FakeState(list(range(n)))
+    a = sc.add("a", "prompt", list(range(10)), mk(10))          # 88 + 40 bytes
+    b = sc.add("b", "prompt", list(range(20)), mk(20))
+    assert a is not None and b is not None
+    assert sc.find(list(range(30)), "a") is b                    # the longest prefix wins over the own session
+    assert sc.find(list(range(10)), "a") is None                 # nothing left to feed and no logits kept
+    assert sc.find(list(range(15)), "zz") is a
+    assert sc.find([1, 2, 3], "a") is None
+    assert sc.points(0, 30) == [8, 16, 24] and sc.points(10, 30) == [16, 24] and sc.points(0, 9) == []
+    for n in range(21, 40):                                      # overflow the budget: least recently used go first
+        sc.add("c", "prompt", list(range(n)), mk(n))
+    assert sc.nbytes <= sc.budget and sc.evicted > 0
+    assert sc.find(list(range(100)), None).pos == 39
+    assert sc.add("d", "prompt", list(range(1000)), mk(1000)) is None   # larger than the whole budget

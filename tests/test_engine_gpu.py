@@ -85,3 +85,65 @@ def test_engine_prefill_chunks():
             same += 1
     assert same >= len(reqs) // 2, same
     ops.check_status()
+
+
+def _solo_check(model, BT, prompt, got, m):
+    """got == the stepwise solo tokens up to the first near-tie (see test_engine_prefill_chunks); returns True when all
+    m tokens agree."""
+    one = model.make_cache(max_rows=1, n_pages=8, max_pages_per_row=6)
+    one.apply(join=["x"])
+    for t in prompt:
+        lg, _ = BT.forward(model, one, [t])
+    for j in range(m):
+        lg = lg[0].float()
+        want = int(one.greedy[0])
+        if got[j] != want:
+            assert float(lg.max() - lg[got[j]]) < 0.05, (j, float(lg.max() - lg[got[j]]))
+            return False
+        if j + 1 < m:
+            lg, _ = BT.forward(model, one, [want])
+    return True
+
+
+def test_engine_sliced_prefill_and_sessions():
+    """Prompts prefilled on a cache of their own in chunks that stop at layer boundaries when the time slice is spent
+    (scheduler.py:241-263), then joined into the decode batch as a State; with a session cache a follow-up turn resumes
+    from the end-of-reply snapshot and prefills only its new tokens (scheduler.py:134-190, session.py:240-330)."""
+    if not torch.cuda.is_available():
+        pytest.skip("needs a GPU")
+    from volundr_mlx_b200 import batch as BT, ops
+    from volundr_mlx_b200.engine import BatchEngine
+    from volundr_mlx_b200.session import SessionCache
+    from volundr_mlx_b200.volundr import Model
+
+    cuda = torch.device("cuda", 0)
+    for mode_kw in (dict(bcsa_far="tokens", bcsa_score="pooled_key", bcsa_window=128, bcsa_compress=64, bcsa_topk=2), {}):
+        args = synth.small_args(**mode_kw)
+        params = synth.make_params(args, seed=23)
+        model = Model(args, params, cuda)
+        rng = np.random.default_rng(23)
+        reqs = [(rng.integers(0, args.vocab_valid, size=n).tolist(), m)
+                for n, m in [(70, 12), (3, 20), (200, 5), (1, 8), (33, 9), (64, 30)]]
+        sc = SessionCache(budget_gb=0.5, interval=64, min_gap=8)
+        # (a slice of 50 microseconds: every chunk is cut after its first layer or two while something decodes)
+        eng = BatchEngine(model, max_rows=3, n_pages=32, max_pages_per_row=6, prefill_chunk=48, slice_ms=0.05, sessions=sc)
+        keys = [eng.submit(p, m, session=f"s{i}") for i, (p, m) in enumerate(reqs)]
+        out = eng.run()
+        ops.check_status()
+        assert eng.stats["slices"] > 0, eng.stats
+        same = sum(_solo_check(model, BT, p, out[k], m) for k, (p, m) in zip(keys, reqs))
+        assert same >= len(reqs) // 2, same
+        assert {s.kind for s in sc.snaps} == {"prompt", "reply", "interval"}
+        # follow-up turn of request 2: prompt + reply + new tokens; only the new tokens are prefilled
+        p2, m2 = reqs[2]
+        follow = p2 + out[keys[2]] + rng.integers(0, args.vocab_valid, size=5).tolist()
+        chunks_before = eng.chunk_steps
+        k = eng.submit(follow, 10, session="s2")
+        out2 = eng.run()
+        ops.check_status()
+        assert eng.finished[k].resumed == len(p2) + m2 - 1
+        assert eng.chunk_steps - chunks_before == 1
+        _solo_check(model, BT, follow, out2[k], 10)
+        assert eng.bc.B == 0 and eng.pc.B == 0 and eng.reserved == 0
+        free = int(eng.bc.free_top.item())
+        assert free == eng.bc.n_pages, "every page went back to the pool"

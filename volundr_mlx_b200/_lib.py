@@ -78,6 +78,8 @@ SIGNATURES = {
     "vk_bcsa_select_static": (c_int, [c_void_p] * 7 + [c_int, c_void_p]),
     "vk_attend_set_tensor_cores": (None, [c_int]),
     "vk_attend_scratch_bytes": (c_size_t, [c_void_p, c_int, c_int]),
+    "vk_attend_chunk_smem_bytes": (c_size_t, [c_void_p, c_int]),
+    "vk_attend_chunk": (c_int, [c_void_p] * 12 + [c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p]),
     "vk_attend_decode": (c_int, [c_void_p] * 11 + [c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p]),
 }
 

@@ -100,6 +100,7 @@ class BatchCache:
         self.xr_act = torch.zeros(m.I // 64 * 2176, **u8)
         self.fused_xrec = S <= 16
         self.fuse_boundary = True   # one kernel for combine(layer i) + mix(layer i + 1)
+        self.tile_attention = True  # chunk path: attention over tiles of 16 query rows (else one query row at a time)
         self.q = torch.zeros((S, m.Hq, 128), **bf)
         if self.indexer:
             self.qi = torch.zeros((S, a.bcsa_index_heads, a.bcsa_index_dim), **bf)

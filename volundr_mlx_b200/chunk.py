@@ -86,6 +86,7 @@ class ChunkHandle:
     def __init__(self, model, lens, pos0, window, kda_inputs, off, ik):
         self.model = model
         self.lens, self.pos0, self.window, self.kda_inputs, self.off, self.ik = lens, pos0, window, kda_inputs, off, ik
+        self.offs = [sum(lens[:b]) for b in range(len(lens))]      # the requests' first virtual rows, on the host
         self.T = max(lens)
         self.greedy = None
         self.features = None
@@ -134,7 +135,7 @@ def _open_pages(bc, lens, lens_t):
 
 
 def _store_open_keys(bc, lst, ikc, off, pos0, kept):
-    """The open block's indexer keys after request b kept kept[b] tokens of a chunk that began at pos0[b]: the ring
+    """off: the requests' first virtual rows (host ints). The open block's indexer keys after request b kept kept[b] tokens of a chunk that began at pos0[b]: the ring
     IK [row, C, Di] gets the keys of the positions of the last, unfinished block that the chunk brought (those in front
     of the chunk are in the ring already; BCSACache.update, volundr.py:526-533; batch_spec.py:151-158)."""
     C = bc.args.bcsa_compress
@@ -144,7 +145,7 @@ def _store_open_keys(bc, lst, ikc, off, pos0, kept):
         for t in range(max(end - end % C, p0), end):
             rows.append(b)
             slots.append(t % C)
-            src.append(int(off[b]) + t - p0)
+            src.append(off[b] + t - p0)
     if rows:
         dev = ikc.device
         ix = lambda v: torch.tensor(v, dtype=torch.long, device=dev)
@@ -232,6 +233,11 @@ def forward_chunk_iter(model, bc, toks, write=False, logits_at=None, capture=(),
                   len(a.engram_orders) if a.engram_layers else 0, a.engram_rows, R, D, eps, st), "vk_embed")
     kda_inputs, ik_kept, caps = [], {}, []
     nl = len(model.layers)
+    # tiles of up to 16 consecutive rows of one request for the attention kernel that reads a tile's keys once
+    offs = [sum(lens[:b]) for b in range(B)]
+    tiles = [(offs[b] + t0, min(16, lens[b] - t0)) for b in range(B) for t0 in range(0, lens[b], 16)]
+    tile_t = torch.tensor(tiles, dtype=torch.int32).t().contiguous().to(dev)          # [2, tiles]
+    use_tiles = bc.tile_attention and T > 1
     for i, (w, lst) in enumerate(zip(model.layers, bc.layers)):
         if i in capture:
             caps.append(s.H[:R, 0].clone())
@@ -270,16 +276,28 @@ def forward_chunk_iter(model, bc, toks, write=False, logits_at=None, capture=(),
                     break   # (a dense layer pools nothing)
             if idx:   # the open block's indexer keys: now for a chunk that is committed as it is, else at the commit
                 if write:
-                    _store_open_keys(bc, lst, s.ikc, off_t, bc._pos, lens)
+                    _store_open_keys(bc, lst, s.ikc, offs, bc._pos, lens)
                 else:
                     ik_kept[i] = s.ikc[:R].clone()
             if bcsa:
                 ck(L.vk_bcsa_select(ctypes.byref(g), _p(s.qi) if idx else _p(s.q), _p(lst["BK"]) if idx else _p(lst["PK"]),
                                     _p(s.pos), _p(s.table), _p(s.sel_scratch), bc.max_blocks, _p(s.sel), _p(s.nsel), R, st),
                    "vk_bcsa_select")
-            ck(L.vk_attend_decode(ctypes.byref(g), _p(s.q), _p(lst["K"]), _p(lst["V"]), _p(lst.get("PK")), _p(lst.get("PV")),
-                                  _p(s.pos), _p(s.table), _p(s.sel), _p(s.nsel), _p(s.proj), s.proj.stride(0), _p(s.part),
-                                  bc.nsplit_bcsa if bcsa else bc.nsplit_dense, _p(s.mix), None, R, st), "vk_attend_decode")
+            done = False
+            if use_tiles:
+                W, C = (a.bcsa_window, a.bcsa_compress) if bcsa else (0, 1)
+                nv_cap = max(max(0, (p0 + n - W) // C) for p0, n in zip(bc._pos, lens)) if bcsa else 0
+                nsplit = max(1, min(16, -(-4 * 148 // (len(tiles) * model.KVH))))
+                rc = L.vk_attend_chunk(ctypes.byref(g), _p(s.q), _p(lst["K"]), _p(lst["V"]), _p(lst.get("PK")), _p(lst.get("PV")),
+                                       _p(s.pos), _p(s.table), _p(s.sel), _p(s.nsel), _p(tile_t[0]), _p(tile_t[1]), len(tiles),
+                                       nv_cap, _p(s.proj), s.proj.stride(0), _p(s.part), nsplit, _p(s.mix), R, st)
+                if rc != -3:       # (-3: the union's bookkeeping does not fit shared memory: one query row at a time)
+                    ck(rc, "vk_attend_chunk")
+                    done = True
+            if not done:
+                ck(L.vk_attend_decode(ctypes.byref(g), _p(s.q), _p(lst["K"]), _p(lst["V"]), _p(lst.get("PK")), _p(lst.get("PV")),
+                                      _p(s.pos), _p(s.table), _p(s.sel), _p(s.nsel), _p(s.proj), s.proj.stride(0), _p(s.part),
+                                      bc.nsplit_bcsa if bcsa else bc.nsplit_dense, _p(s.mix), None, R, st), "vk_attend_decode")
         gemm(s.mix[:, :nmix], w["out"], s.r)
         allreduce(s.r[:R])
         ck(L.vk_add_rmsnorm(_p(s.x_in), _p(s.r), _p(w["ln_post"]), _p(s.h2), _p(s.hn2), None, R, D, eps, 1, st), "vk_add_rmsnorm")
@@ -363,7 +381,7 @@ def _finish(model, bc, h: ChunkHandle, acc, replay):
                        "vk_kda_chunk_ragged")
     if replay:
         for i, ikc in h.ik.items():
-            _store_open_keys(bc, bc.layers[i], ikc, h.off, h.pos0, acc)
+            _store_open_keys(bc, bc.layers[i], ikc, h.offs, h.pos0, acc)
     if has_kda:          # the conv windows now sit in the other buffer, as after a decode step
         bc.parity ^= 1
         bc.steps += 1

@@ -1,4 +1,4 @@
-"""A small continuous-batching engine on the batched decode step: admission by free rows and pages, rows that join and
+"""A continuous-batching engine on the batched decode step: admission by free rows and pages, rows that join and
 leave between steps, greedy sampling (the part of scheduler.BatchEngine, scheduler.py:72-560, that drives batch.forward:
 admission :180-239, the step :300-420, greedy :391, retirement :430-470).
 
@@ -10,9 +10,23 @@ another without padding and are committed as they are (the reference feeds promp
 session.prefill_iter, session.py:351-387, one request at a time). The weights are then read once per chunk
 instead of once per prompt token. The chunk path's GEMMs round differently from the decode step's (within the bf16
 bar), so tokens can differ from the stepwise engine at near-ties of the logits.
+
+With slice_ms > 0 (and prefill_chunk = T) prompts are fed the reference's way (scheduler.py:241-263, session.prefill_iter,
+session.py:351-387): the oldest admitted request is prefilled on a one-row cache of its own, chunk after chunk of T
+tokens, and the chunk pass hands control back after every layer (chunk.forward_chunk_iter); while any request is
+decoding, a tick spends at most slice_ms on prefill layers, stops at the next layer boundary, runs ONE decode step for
+all decoding rows and picks the chunk up where it stopped in the next tick. A long prompt therefore never stalls the
+decoding streams for longer than a slice plus one layer of a chunk. A request whose prompt is through moves into the
+decode batch as a session.State (capture_row on the prefill cache, apply(join=[(key, state)]) on the batch).
+
+With a session.SessionCache (sessions=...) a request resumes from the longest snapshot whose tokens are a prefix of
+its prompt (its own session first), prefills only the rest, and leaves snapshots behind: at interval positions of a
+long prefill, at the end of its prompt (with the logits that pick the first token) and at the end of its reply
+(scheduler.py:134-190, :504-560).
 """
 from __future__ import annotations
 
+import time
 from collections import deque
 from dataclasses import dataclass, field
 
@@ -31,6 +45,9 @@ class Request:
     max_new: int
     fed: int = 0
     out: list = field(default_factory=list)
+    session: object = None
+    points: list = field(default_factory=list)      # snapshot positions still ahead inside the prompt
+    resumed: int = 0                                # prompt tokens taken from a snapshot
 
     @property
     def done(self):
@@ -38,11 +55,22 @@ class Request:
 
 
 class BatchEngine:
-    def __init__(self, model, max_rows=16, n_pages=4096, max_pages_per_row=512, prefill_chunk=0):
+    def __init__(self, model, max_rows=16, n_pages=4096, max_pages_per_row=512, prefill_chunk=0, slice_ms=0.0, sessions=None,
+                 clock=time.perf_counter):
         self.model = model
         self.prefill_chunk = int(prefill_chunk)
         self.chunk_steps = 0
+        self.slice_s = float(slice_ms) / 1e3
+        self.sliced = self.slice_s > 0 and self.prefill_chunk > 1
+        self.sessions = sessions
+        self.clock = clock
         self.bc = model.make_cache(max_rows=max_rows, n_pages=n_pages, max_pages_per_row=max_pages_per_row)
+        # sliced prefill: the request being prefilled lives on a one-row cache of its own until its prompt is through
+        self.pc = model.make_cache(max_rows=1, n_pages=max_pages_per_row, max_pages_per_row=max_pages_per_row) if self.sliced else None
+        self.prefilling: deque = deque()
+        self._gen, self._gen_n = None, 0
+        self.stats = {"slices": 0, "slice_layers_max": 0, "resumed_tokens": 0, "snapshots": 0, "stall_s_max": 0.0}
+        self._last_decode = None
         self.n_pages, self.max_pages_per_row = n_pages, max_pages_per_row
         self.waiting: deque = deque()
         self.running: dict = {}
@@ -53,9 +81,9 @@ class BatchEngine:
     def _pages(self, r: Request) -> int:
         return (len(r.prompt) + r.max_new + PAGE - 1) // PAGE
 
-    def submit(self, prompt, max_new) -> int:
+    def submit(self, prompt, max_new, session=None) -> int:
         assert len(prompt) >= 1 and max_new >= 1
-        r = Request(self._next, [int(t) for t in prompt], int(max_new))
+        r = Request(self._next, [int(t) for t in prompt], int(max_new), session=session)
         assert self._pages(r) <= self.max_pages_per_row, "request longer than a row's page table"
         self._next += 1
         self.waiting.append(r)
@@ -63,7 +91,7 @@ class BatchEngine:
 
     def _admit(self):
         join = []
-        while self.waiting and len(self.running) + len(join) < self.bc.S:
+        while self.waiting and len(self.running) + len(self.prefilling) + len(join) < self.bc.S:
             r = self.waiting[0]
             if self.reserved + self._pages(r) > self.n_pages:
                 break   # first come first served: nobody overtakes a request that waits for pages
@@ -79,6 +107,9 @@ class BatchEngine:
             r = self.running.pop(k)
             self.reserved -= self._pages(r)
             self.finished[k] = r
+            self._snapshot_reply(r)
+        if self.sliced:
+            return self._sliced_step(leave)
         join = self._admit()
         for r in join:
             self.running[r.key] = r
@@ -99,6 +130,128 @@ class BatchEngine:
             if r.fed >= len(r.prompt):   # the token after the last one fed
                 r.out.append(int(g))
                 produced.append((r.key, int(g)))
+        return produced
+
+    # ------------------------------------------------------------------ sliced prefill on a cache of its own
+    def _sync(self):
+        torch.cuda.current_stream().synchronize()
+
+    def _snapshot_reply(self, r):
+        """End of a reply: the row holds prompt + reply minus the last token (scheduler.py:504-560)."""
+        if self.sessions is None or not self.sessions.enabled or r.key not in self.bc.keys:
+            return
+        toks = (r.prompt + r.out)[:-1]
+        if not self.sessions.has(toks):
+            self.sessions.add(r.session, "reply", toks, self.bc.capture_row(r.key))
+            self.stats["snapshots"] += 1
+
+    def _start_prefill(self, r):
+        """Put request r on the prefill cache: fresh, or from the longest snapshot that is a prefix of its prompt."""
+        snap = self.sessions.find(r.prompt, r.session) if self.sessions is not None else None
+        state = None
+        if snap is not None:
+            state = snap.state
+            r.fed = r.resumed = snap.pos
+            self.stats["resumed_tokens"] += snap.pos
+        self.pc.apply(join=[(r.key, state)])
+        if self.sessions is not None:
+            r.points = self.sessions.points(r.fed, len(r.prompt))
+        return snap
+
+    def _finish_prefill(self, r, first, logits):
+        """The prompt is through: snapshot, then move the row into the decode batch."""
+        st = self.pc.capture_row(r.key, logits=logits)
+        if self.sessions is not None and self.sessions.enabled and not self.sessions.has(r.prompt):
+            self.sessions.add(r.session, "prompt", r.prompt, st)
+            self.stats["snapshots"] += 1
+        self.pc.apply(leave=[r.key])
+        self.bc.apply(join=[(r.key, st)])
+        r.out.append(first)
+        self.running[r.key] = r
+
+    def _prefill_work(self, produced):
+        """Prefill layers of the oldest admitted request: without a limit while nothing decodes (one chunk per tick),
+        else until the slice is spent, stopping at a layer boundary (scheduler.py:241-263)."""
+        decoding = bool(self.running)
+        t_end = self.clock() + self.slice_s if decoding else None
+        T = self.prefill_chunk
+        layers = 0
+        while self.prefilling:
+            r = self.prefilling[0]
+            if self._gen is None:
+                if r.key not in self.pc.keys:
+                    snap = self._start_prefill(r)
+                    if r.fed >= len(r.prompt):       # the snapshot held the whole prompt and its last logits
+                        st = self.pc.capture_row(r.key)
+                        first = int(torch.argmax(snap.state.logits[: self.model.args.vocab_valid].float()))
+                        self.pc.apply(leave=[r.key])
+                        self.bc.apply(join=[(r.key, st)])
+                        r.out.append(first)
+                        self.running[r.key] = r
+                        self.prefilling.popleft()
+                        produced.append((r.key, first))
+                        continue
+                stop = min(len(r.prompt), r.fed + T, r.points[0] if r.points else len(r.prompt))
+                chunk = r.prompt[r.fed:stop]
+                self._gen_n = len(chunk)
+                self._gen = CH.forward_chunk_iter(self.model, self.pc, [chunk], write=True, logits_at=[len(chunk) - 1])
+            try:
+                while True:
+                    next(self._gen)
+                    layers += 1
+                    if t_end is not None:
+                        self._sync()
+                        if self.clock() >= t_end:
+                            self.stats["slices"] += 1
+                            self.stats["slice_layers_max"] = max(self.stats["slice_layers_max"], layers)
+                            return
+            except StopIteration as e:
+                logits, greedy, _ = e.value
+            self._gen = None
+            r.fed += self._gen_n
+            self.chunk_steps += 1
+            if r.points and r.fed == r.points[0]:      # an interval snapshot inside a long prompt
+                r.points.pop(0)
+                if not self.sessions.has(r.prompt[: r.fed]):
+                    self.sessions.add(r.session, "interval", r.prompt[: r.fed], self.pc.capture_row(r.key))
+                    self.stats["snapshots"] += 1
+            if r.fed >= len(r.prompt):
+                first = int(greedy[0][0])
+                self._finish_prefill(r, first, logits[0, 0] if logits is not None else None)
+                self.prefilling.popleft()
+                produced.append((r.key, first))
+            if t_end is None:
+                return                                  # nothing decodes: one chunk per tick
+            self._sync()
+            if self.clock() >= t_end:
+                self.stats["slices"] += 1
+                self.stats["slice_layers_max"] = max(self.stats["slice_layers_max"], layers)
+                return
+
+    def _sliced_step(self, leave):
+        for r in self._admit():
+            self.prefilling.append(r)
+        if leave:
+            self.bc.apply(leave=leave)
+        produced = []
+        self._prefill_work(produced)
+        if self.bc.B:
+            rows = [self.running[k] for k in self.bc.keys]
+            live = [r for r in rows if not r.done]
+            if live:
+                toks = [r.out[-1] for r in rows]
+                BT.forward(self.model, self.bc, toks)
+                greedy = self.bc.greedy[: self.bc.B].tolist()
+                now = self.clock()
+                if self._last_decode is not None:
+                    self.stats["stall_s_max"] = max(self.stats["stall_s_max"], now - self._last_decode)
+                self._last_decode = now
+                for r, g in zip(rows, greedy):
+                    if not r.done:
+                        r.out.append(int(g))
+                        produced.append((r.key, int(g)))
+        else:
+            self._last_decode = None
         return produced
 
     def _chunk_len(self, rows) -> int:
@@ -129,14 +282,15 @@ class BatchEngine:
     def run(self, max_steps=1_000_000):
         """Steps until every submitted request has finished; returns {key: generated tokens}."""
         n = 0
-        while (self.waiting or self.running) and n < max_steps:
+        while (self.waiting or self.running or self.prefilling) and n < max_steps:
             self.step()
             n += 1
-            if all(r.done for r in self.running.values()) and not self.waiting:
+            if all(r.done for r in self.running.values()) and not self.waiting and not self.prefilling:
                 for k in list(self.running):
                     r = self.running.pop(k)
                     self.reserved -= self._pages(r)
                     self.finished[k] = r
+                    self._snapshot_reply(r)
                 if self.bc.B:
                     self.bc.apply(leave=list(self.bc.keys))
         return {k: r.out for k, r in self.finished.items()}

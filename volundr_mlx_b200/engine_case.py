@@ -29,6 +29,8 @@ def main():
     ap.add_argument("--hi", type=int, default=20000)
     ap.add_argument("--prefill-chunk", type=int, default=128)
     ap.add_argument("--layers", type=int, default=0, help="0 = all 72")
+    ap.add_argument("--slice-ms", type=float, default=0.0,
+                    help="> 0: prompts are prefilled on a cache of their own in time slices of this many ms between decode steps")
     a = ap.parse_args()
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(dev)
@@ -43,16 +45,16 @@ def main():
     lens = np.exp(rng.uniform(np.log(a.lo), np.log(a.hi), size=a.requests)).astype(int)
     pages_row = (int(lens.max()) + a.new) // 64 + 2
     eng = BatchEngine(model, max_rows=a.rows, n_pages=int(sum((n + a.new) // 64 + 2 for n in lens)) + 8,
-                      max_pages_per_row=pages_row, prefill_chunk=a.prefill_chunk)
+                      max_pages_per_row=pages_row, prefill_chunk=a.prefill_chunk, slice_ms=a.slice_ms)
     for n in lens:
         eng.submit(rng.integers(0, args.vocab_valid, size=int(n)).tolist(), a.new)
     torch.cuda.synchronize(dev)
     t0 = time.perf_counter()
     steps = 0
-    while eng.waiting or eng.running:
+    while eng.waiting or eng.running or eng.prefilling:
         eng.step()
         steps += 1
-        if all(r.done for r in eng.running.values()) and not eng.waiting:
+        if all(r.done for r in eng.running.values()) and not eng.waiting and not eng.prefilling:
             break
     torch.cuda.synchronize(dev)
     wall = time.perf_counter() - t0
@@ -60,7 +62,8 @@ def main():
     n_prompt, n_new = int(lens.sum()), a.requests * a.new
     print(json.dumps({"requests": a.requests, "prompt_tokens": n_prompt, "new_tokens": n_new, "wall_s": wall,
                       "tokens_per_s": (n_prompt + n_new) / wall, "steps": steps, "chunk_steps": eng.chunk_steps,
-                      "prefill_chunk": a.prefill_chunk, "layers": len(model.layers)}))
+                      "prefill_chunk": a.prefill_chunk, "layers": len(model.layers), "slice_ms": a.slice_ms,
+                      "slices": eng.stats["slices"], "longest_gap_between_decode_steps_s": eng.stats["stall_s_max"]}))
 
 
 if __name__ == "__main__":
