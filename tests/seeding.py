@@ -93,6 +93,12 @@ def seeded_batch(model, orc, keys, ctx_lens, seed, n_pages=None, max_rows=None, 
     return bc, rows
 
 
+def seeded_rows(model, orc, ctx_lens, keys, seed):
+    """The oracle rows seeded_batch(model, ., keys, ctx_lens, seed) draws, for another oracle object (same values)."""
+    rng = np.random.Generator(np.random.PCG64(seed))
+    return {k: draw_row(model.args, orc, int(P), rng, model.device)[0] for k, P in zip(keys, ctx_lens)}
+
+
 def _close(got, want, tol, what):
     """Element-wise within tol * (|want| + the tensor's scale): values that went through several layers of bf16 arithmetic
     agree to a fraction of the vector's scale, not of each (possibly tiny) element."""
@@ -101,12 +107,13 @@ def _close(got, want, tol, what):
     np.testing.assert_allclose(got, want, rtol=tol, atol=tol * max(scale, 1e-6), err_msg=str(what))
 
 
-def assert_state_close(bc, key, row, args, s_atol=2e-3, tol=2e-2, what=""):
+def assert_state_close(bc, key, row, args, s_atol=2e-3, tol=2e-2, what="", layers=None):
     """The cache row `key` (through BatchCache.capture_row) against the oracle's Row: position and Engram ids exactly;
     K / V by position, pooled block means, pooled and open-block indexer keys and the conv window within the bf16 bar
     (rtol = tol, atol = tol x the tensor's largest magnitude: the two sides hold bf16 roundings of hidden states that
-    agree to a fraction of a percent of their scale after a few layers); the fp32 KDA state within s_atol (its inputs
-    carry that bf16-level noise; the 1e-4 bar on identical inputs is tests/test_kda_gpu.py's)."""
+    agree to a fraction of a percent of their scale after a few layers); the fp32 KDA state within s_atol for all but
+    one element in 1e5, those within ten times that (its inputs carry that bf16-level noise; the 1e-4 bar on identical
+    inputs is tests/test_kda_gpu.py's)."""
     st = bc.capture_row(key)
     a = args
     assert st.pos == row.pos, (what, st.pos, row.pos)
@@ -115,9 +122,16 @@ def assert_state_close(bc, key, row, args, s_atol=2e-3, tol=2e-2, what=""):
     for i, (m, t) in enumerate(zip(a.mixer_types, st.layers)):
         o = row.layers[i]
         tag = (what, "layer", i, m)
+        if layers is not None and i not in layers:
+            continue
         if m == "kda":
             _close(f(t[1])[0], o["conv"], tol, tag + ("conv",))
-            np.testing.assert_allclose(f(t[2])[0], o["S"], rtol=1e-3, atol=s_atol, err_msg=str(tag + ("S",)))
+            got_s, want_s = f(t[2])[0], np.asarray(o["S"], np.float32)
+            out = np.abs(got_s - want_s) > s_atol + 1e-3 * np.abs(want_s)
+            # (one bf16 step in one of a step's q / k / v inputs, 2^-8 of its magnitude, moves single elements of the
+            # state by a few 1e-3: a handful of elements may sit there, none further out)
+            assert out.mean() <= 1e-5, tag + ("S", float(out.mean()))
+            np.testing.assert_allclose(got_s, want_s, rtol=1e-3, atol=10 * s_atol, err_msg=str(tag + ("S",)))
             continue
         k, v = (t[2], t[3]) if m == "attn" else (t[6], t[7])
         _close(f(k)[0], np.stack(o["k"]).transpose(1, 0, 2), tol, tag + ("K",))

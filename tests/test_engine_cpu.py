@@ -263,3 +263,89 @@ def test_session_cache_budget_and_lookup():
     assert sc.nbytes <= sc.budget and sc.evicted > 0
     assert sc.find(list(range(100)), None).pos == 39
     assert sc.add("d", "prompt", list(range(1000)), mk(1000)) is None   # larger than the whole budget
+
+
+# ---------------------------------------------------------------------------------- batched speculative steps (fakes)
+class FakeRec:
+    pass
+
+
+def fake_verify_forward(model, bc, ids, capture=()):
+    rec = FakeRec()
+    rec.ids = [list(map(int, row)) for row in ids]
+    T = len(rec.ids[0])
+    g = torch.zeros((bc.B, T), dtype=torch.int32)
+    for b, k in enumerate(bc.keys):
+        for t in range(T):
+            g[b, t] = fake_next(bc.hist[k] + rec.ids[b][: t + 1])
+    rec.greedy = g
+    return None, None, rec
+
+
+def fake_commit(bc, rec, ns):
+    for b, k in enumerate(bc.keys):
+        assert 1 <= ns[b] <= len(rec.ids[b])
+        bc.hist[k] += rec.ids[b][: ns[b]]
+
+
+class OracleDrafter:
+    """Drafts the true continuation for the first `good` places of a proposal, garbage after (good = 99: perfect)."""
+    good = 99
+
+    def reset(self, ids):
+        self.hist = list(ids)
+
+    def propose(self, k):
+        h, out = list(self.hist), []
+        for i in range(k):
+            t = fake_next(h)
+            out.append(t if i < self.good else (t + 1) % 997)
+            h.append(t)
+        return out
+
+    def record(self, emitted):
+        self.hist.extend(emitted)
+
+
+def test_speculative_steps_keep_the_greedy_sequence(monkeypatch):
+    from volundr_mlx_b200.lookup import Lookup
+
+    for good, factory in ((99, OracleDrafter), (2, OracleDrafter), (0, OracleDrafter), (None, Lookup)):
+        if good is not None:
+            OracleDrafter.good = good
+        eng, _ = _sliced_engine(monkeypatch, max_rows=3, n_pages=12, max_pages_per_row=4)
+        monkeypatch.setattr(E.SP, "verify_forward", fake_verify_forward)
+        monkeypatch.setattr(E.SP, "commit", fake_commit)
+        eng.spec, eng.spec_T, eng.bspec_max, eng.bspec_rows, eng.drafter_factory = True, 8, 4, 16, factory
+        reqs = [([5, 6, 7], 30), (list(range(1, 60)), 17), ([9, 8, 7, 6, 5, 4, 3, 2, 1], 23), ([4, 4, 4, 4, 4, 4, 4], 9)]
+        keys = [eng.submit(p, n) for p, n in reqs]
+        out = eng.run()
+        for k, (p, n) in zip(keys, reqs):
+            assert out[k] == solo(p, n), (good, k)
+        if good == 99:       # every draft accepted: far fewer steps than tokens
+            # (all but the drafts that ran past a request's last token)
+            assert eng.stats["spec_drafted"] - 7 * len(reqs) <= eng.stats["spec_accepted"] <= eng.stats["spec_drafted"] > 0
+            assert eng.stats["spec_steps"] + eng.stats["decode_steps"] < sum(n for _, n in reqs) // 2
+        elif good == 2:
+            assert 0 < eng.stats["spec_accepted"] < eng.stats["spec_drafted"]
+        elif good == 0:
+            assert eng.stats["spec_accepted"] == 0 and eng.stats["spec_steps"] > 0
+
+
+def test_lookup_proposes_what_followed_the_longest_match():
+    from volundr_mlx_b200.lookup import Lookup, bucket_of
+
+    lk = Lookup(min_gain=0.0)
+    seq = [1, 2, 3, 4, 5, 9, 9, 2, 3, 4, 7, 8, 1, 2, 3, 4]
+    lk.reset(seq)
+    cont, m = lk.find()
+    assert m == 4 and cont[:2] == [5, 9]            # "1 2 3 4" at the start beats "2 3 4" in the middle
+    assert lk.propose(3) == [5, 9, 9]
+    lk.record([5, 9, 1])                            # two of three accepted, then the model's own token
+    assert lk.hist[-3:] == [5, 9, 1] and lk.accepted == 2
+    assert [bucket_of(m) for m in (1, 2, 3, 5, 6, 9, 10, 64)] == [0, 0, 1, 2, 3, 3, 4, 5]
+    lk.reset([1, 2])
+    assert lk.propose() == []                       # too short to match anything
+    strict = Lookup(min_gain=10.0)
+    strict.reset(seq)
+    assert strict.propose() == []                   # a match, but not expected to pay

@@ -147,3 +147,66 @@ def test_engine_sliced_prefill_and_sessions():
         assert eng.bc.B == 0 and eng.pc.B == 0 and eng.reserved == 0
         free = int(eng.bc.free_top.item())
         assert free == eng.bc.n_pages, "every page went back to the pool"
+
+
+def test_engine_batched_speculative_steps():
+    """Batched speculative steps (scheduler.py:432-503 over batch_spec.verify_forward / commit): rows draft, one verify
+    pass checks all rows' drafts, each row keeps its accepted run. With a drafter that replays the request's true greedy
+    continuation every draft must be accepted (up to near-ties between the verify pass and the decode step); with
+    prompt lookup on repetitive prompts whatever is accepted, the emitted tokens stay the greedy sequence."""
+    if not torch.cuda.is_available():
+        pytest.skip("needs a GPU")
+    from volundr_mlx_b200 import batch as BT, ops
+    from volundr_mlx_b200.engine import BatchEngine
+    from volundr_mlx_b200.lookup import Lookup
+    from volundr_mlx_b200.volundr import Model
+
+    cuda = torch.device("cuda", 0)
+    args = synth.small_args()
+    params = synth.make_params(args, seed=24)
+    model = Model(args, params, cuda)
+    rng = np.random.default_rng(24)
+    pat = rng.integers(0, args.vocab_valid, size=7).tolist()
+    reqs = [(pat * 6, 24), (rng.integers(0, args.vocab_valid, size=40).tolist(), 30), (pat[::-1] * 9, 17)]
+    # the greedy continuations, from solo stepwise runs
+    truth = {}
+    for i, (prompt, m) in enumerate(reqs):
+        one = model.make_cache(max_rows=1, n_pages=8, max_pages_per_row=6)
+        one.apply(join=["x"])
+        for t in prompt:
+            BT.forward(model, one, [t])
+        seq = [int(one.greedy[0])]
+        while len(seq) < m + 8:
+            BT.forward(model, one, [seq[-1]])
+            seq.append(int(one.greedy[0]))
+        truth[tuple(prompt)] = seq
+
+    class Replay:
+        def reset(self, ids):
+            self.ids = list(ids)
+
+        def propose(self, k):
+            for prompt, seq in truth.items():
+                n = len(prompt)
+                if tuple(self.ids[:n]) == prompt:
+                    done = len(self.ids) - n
+                    return seq[done: done + k] if self.ids[n:] == seq[:done] else []
+            return []
+
+        def record(self, emitted):
+            self.ids.extend(emitted)
+
+    for factory in (Replay, Lookup):
+        eng = BatchEngine(model, max_rows=3, n_pages=32, max_pages_per_row=6, prefill_chunk=48, slice_ms=50.0, spec=True,
+                          spec_T=8, bspec_max=4, bspec_rows=16, drafter_factory=factory)
+        keys = [eng.submit(p, m) for p, m in reqs]
+        out = eng.run()
+        ops.check_status()
+        same = sum(_solo_check(model, BT, p, out[k], m) for k, (p, m) in zip(keys, reqs))
+        assert same >= 2, same
+        assert all(len(out[k]) == m for k, (p, m) in zip(keys, reqs))
+        if factory is Replay:
+            assert eng.stats["spec_steps"] > 0
+            assert eng.stats["spec_accepted"] >= 0.6 * eng.stats["spec_drafted"], eng.stats
+            assert eng.stats["spec_steps"] + eng.stats["decode_steps"] < sum(m for _, m in reqs) // 2
+        assert eng.bc.B == 0 and int(eng.bc.free_top.item()) == eng.bc.n_pages

@@ -133,6 +133,13 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t phase) {
     vk_set_status(VK_ST_MBAR_TIMEOUT);
     return false;
 }
+// Orders what this thread has observed of shared memory in the generic proxy (other warps' ld.shared / ldmatrix reads,
+// known to be over through an mbarrier) before the async-proxy operations it issues next. A producer thread executes
+// it between its wait for a free stage and the bulk copy that refills the stage: the mbarrier alone orders the
+// consumers' reads and the producer's wait, both in the generic proxy, but not the copy's writes, which happen in
+// the async proxy (measured on B200: without the fence a refill now and then overtook a warp's last reads of the
+// stage, as soon as another kernel's loads kept the memory system busy beside the GEMM).
+__device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 // global -> shared bulk copy through the TMA engine; both addresses 16-byte aligned, bytes a multiple of 16.
 __device__ __forceinline__ void tma_bulk_g2s(void* dst_smem, const void* src_gmem, uint32_t bytes, uint64_t* bar) {
     asm volatile(

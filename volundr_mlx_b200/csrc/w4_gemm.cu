@@ -193,6 +193,8 @@ __global__ void __launch_bounds__(kThreads, ctas_per_sm<FMT, MT>()) w4_gemm_kern
 #if defined(VK_TRACE) && VK_TRACE == 2
                 tr_wait += clock64() - tr_a;
 #endif
+                // (the consumers read the stage with ld.shared / ldmatrix, the refill writes it through the async proxy)
+                fence_proxy_async_smem();
                 uint8_t* dst = smem + (size_t)st * kStageBytes;
                 mbar_expect_tx(&full[st], kWStageBytes + kXR);
                 tma_bulk_g2s(dst, wnext, kWStageBytes, &full[st]);

@@ -134,6 +134,7 @@ __global__ void __launch_bounds__(kT5Threads, 1) w4_t5_kernel(const W4Params p) 
             const uint8_t* wnext = wsrc + (size_t)pre * kT5WBytes;
             for (int i = pre; i < n; i++) {   // the weights of step i go into the stage that step i - pre's codes have left
                 if (!mbar_wait(&wempty[ws], wpar)) { s_fail = 1; break; }
+                fence_proxy_async_smem();   // (the expansion warps read the codes with ld.shared)
                 mbar_expect_tx(&wfull[ws], kT5WBytes);
                 tma_bulk_g2s(smem + (size_t)ws * kT5WBytes, wnext, kT5WBytes, &wfull[ws]);
                 wnext += kT5WBytes;
@@ -146,6 +147,7 @@ __global__ void __launch_bounds__(kT5Threads, 1) w4_t5_kernel(const W4Params p) 
             uint32_t xpar = 0;
             for (int i = 0; i < n; i++) {
                 if (i >= kT5XSlots && !mbar_wait(&xempty[xs], xpar)) { s_fail = 1; break; }
+                fence_proxy_async_smem();   // (the warps read the group sums of a record with ld.shared)
                 mbar_expect_tx(&xfull[xs], kXRecBytes);
                 tma_bulk_g2s(xring + (size_t)xs * kXRecBytes, p.xrec + (size_t)kg * kXRecBytes, kXRecBytes, &xfull[xs]);
                 kg = kg + 1 == p.G ? 0 : kg + 1;

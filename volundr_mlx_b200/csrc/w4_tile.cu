@@ -130,6 +130,7 @@ __global__ void __launch_bounds__(kTileThreads, 1) w4_tile_kernel(const TilePara
             uint32_t par = 0;
             for (int i = 0; i < G; i++) {
                 if (i >= kTStages && !mbar_wait(&freeb[st], par)) { s_fail = 1; break; }
+                fence_proxy_async_smem();   // (the expansion warps read the packed codes with ld.shared)
                 uint8_t* dst = smem + (size_t)st * kTStageBytes;
                 mbar_expect_tx(&full[st], kPackedBytes + nm * kXTileBytes);
                 tma_bulk_g2s(dst, wsrc + (size_t)i * kPackedStep, kPackedBytes, &full[st]);

@@ -23,6 +23,13 @@ With a session.SessionCache (sessions=...) a request resumes from the longest sn
 its prompt (its own session first), prefills only the rest, and leaves snapshots behind: at interval positions of a
 long prefill, at the end of its prompt (with the logits that pick the first token) and at the end of its reply
 (scheduler.py:134-190, :504-560).
+
+With spec=True (sliced mode) a step of 1..bspec_max decoding rows is a batched speculative step (scheduler.py:432-503):
+each row drafts up to T - 1 tokens by copying from its own context (volundr_mlx_b200.lookup, or any object with
+propose / record / reset given as drafter_factory), all rows' [bonus, drafts] go through ONE verify pass
+(batch_spec.verify_forward), each row keeps its longest accepted run plus the model's own next token
+(batch_spec.commit with its count). Rows that have nothing to propose ride along; a step in which no row proposes
+anything is a plain decode step.
 """
 from __future__ import annotations
 
@@ -33,7 +40,9 @@ from dataclasses import dataclass, field
 import torch
 
 from . import batch as BT
+from . import batch_spec as SP
 from . import chunk as CH
+from .lookup import Lookup
 
 PAGE = BT.PAGE
 
@@ -48,6 +57,8 @@ class Request:
     session: object = None
     points: list = field(default_factory=list)      # snapshot positions still ahead inside the prompt
     resumed: int = 0                                # prompt tokens taken from a snapshot
+    drafter: object = None                          # the row's drafter (speculative steps)
+    drafter_len: int = -1                           # len(out) the drafter's history corresponds to
 
     @property
     def done(self):
@@ -56,7 +67,7 @@ class Request:
 
 class BatchEngine:
     def __init__(self, model, max_rows=16, n_pages=4096, max_pages_per_row=512, prefill_chunk=0, slice_ms=0.0, sessions=None,
-                 clock=time.perf_counter):
+                 clock=time.perf_counter, spec=False, spec_T=8, bspec_max=4, bspec_rows=16, drafter_factory=Lookup):
         self.model = model
         self.prefill_chunk = int(prefill_chunk)
         self.chunk_steps = 0
@@ -69,7 +80,10 @@ class BatchEngine:
         self.pc = model.make_cache(max_rows=1, n_pages=max_pages_per_row, max_pages_per_row=max_pages_per_row) if self.sliced else None
         self.prefilling: deque = deque()
         self._gen, self._gen_n = None, 0
-        self.stats = {"slices": 0, "slice_layers_max": 0, "resumed_tokens": 0, "snapshots": 0, "stall_s_max": 0.0}
+        self.spec, self.spec_T, self.bspec_max, self.bspec_rows = bool(spec), int(spec_T), int(bspec_max), int(bspec_rows)
+        self.drafter_factory = drafter_factory
+        self.stats = {"slices": 0, "slice_layers_max": 0, "resumed_tokens": 0, "snapshots": 0, "stall_s_max": 0.0,
+                      "spec_steps": 0, "spec_rows": 0, "spec_drafted": 0, "spec_accepted": 0, "decode_steps": 0}
         self._last_decode = None
         self.n_pages, self.max_pages_per_row = n_pages, max_pages_per_row
         self.waiting: deque = deque()
@@ -238,8 +252,11 @@ class BatchEngine:
         if self.bc.B:
             rows = [self.running[k] for k in self.bc.keys]
             live = [r for r in rows if not r.done]
-            if live:
+            if live and self.spec and len(rows) <= self.bspec_max and self._spec_step(rows, produced):
+                pass
+            elif live:
                 toks = [r.out[-1] for r in rows]
+                self.stats["decode_steps"] += 1
                 BT.forward(self.model, self.bc, toks)
                 greedy = self.bc.greedy[: self.bc.B].tolist()
                 now = self.clock()
@@ -253,6 +270,54 @@ class BatchEngine:
         else:
             self._last_decode = None
         return produced
+
+    def _spec_step(self, rows, produced) -> bool:
+        """One batched speculative step of the decoding rows (scheduler.py:432-503). Returns False (nothing done) when
+        no row has anything to propose."""
+        T = max(2, min(self.spec_T, self.bspec_rows // len(rows)))
+        drafts, any_draft = [], False
+        for r in rows:
+            if r.drafter is None or r.drafter_len != len(r.out):      # (re)entering: a fresh history
+                r.drafter = self.drafter_factory()
+                r.drafter.reset(r.prompt + r.out)
+                r.drafter_len = len(r.out)
+            d = [] if r.done else [int(t) for t in r.drafter.propose(T - 1)][: T - 1]
+            any_draft = any_draft or bool(d)
+            drafts.append(d)
+        if not any_draft:
+            for r in rows:
+                r.drafter_len = -1        # (the plain step below appends a token the drafter has not seen)
+            return False
+        # a row with fewer drafts repeats its bonus token in the unused places: they are verified and (almost surely) rejected
+        ids = [[r.out[-1]] + d + [r.out[-1]] * (T - 1 - len(d)) for r, d in zip(rows, drafts)]
+        _, _, rec = SP.verify_forward(self.model, self.bc, ids)
+        tok = rec.greedy.tolist()
+        ns = []
+        emitted = []
+        for b, r in enumerate(rows):
+            n = 1
+            while n < T and n - 1 < len(drafts[b]) and ids[b][n] == tok[b][n - 1]:
+                n += 1
+            em = ids[b][1:n] + [tok[b][n - 1]]          # accepted drafts + the model's own next token
+            em = em[: max(0, r.max_new - len(r.out))]
+            emitted.append(em)
+            ns.append(max(1, len(em)))
+        SP.commit(self.bc, rec, ns)
+        self.stats["spec_steps"] += 1
+        self.stats["spec_rows"] += len(rows)
+        for b, r in enumerate(rows):
+            self.stats["spec_drafted"] += len(drafts[b])
+            self.stats["spec_accepted"] += max(0, len(emitted[b]) - 1)
+            r.drafter.record(emitted[b])
+            for t in emitted[b]:
+                r.out.append(int(t))
+                produced.append((r.key, int(t)))
+            r.drafter_len = len(r.out)
+        now = self.clock()
+        if self._last_decode is not None:
+            self.stats["stall_s_max"] = max(self.stats["stall_s_max"], now - self._last_decode)
+        self._last_decode = now
+        return True
 
     def _chunk_len(self, rows) -> int:
         """Tokens a prompt row may bring to the next step: more than one only while a prompt has two or more tokens
