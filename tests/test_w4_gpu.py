@@ -64,9 +64,12 @@ def _check_gemm(cuda, rng, M, N, K, group, cols=None, force=None):
     W = OW.unpack_codes(w[sel], K).astype(np.float64) * np.repeat(s[sel].astype(np.float64), group, 1) + \
         np.repeat(b[sel].astype(np.float64), group, 1)
     exact = x.astype(np.float64) @ W.T
+    exact_r = x.astype(np.float64) @ bf(W).astype(np.float64).T      # with the weights as mx.dequantize returns them
     ys = []
-    for tcgen05 in (1, 0):      # up to 16 rows: the tcgen05 form (the default) and the mma.sync form of the same arithmetic
-        L.vk_w4_select(tcgen05)
+    # up to 16 rows: the two tcgen05 forms (1: per-group products, scale applied after; 4: weights dequantised to bf16
+    # first, accumulated in tensor memory) and the mma.sync form (0, the default; same arithmetic as 1)
+    for form in (1, 4, 0):
+        L.vk_w4_select(form)
         if force:
             L.vk_w4_force_plan(*force)
         try:
@@ -75,15 +78,15 @@ def _check_gemm(cuda, rng, M, N, K, group, cols=None, force=None):
             ops.check_status()
         finally:
             L.vk_w4_force_plan(0, 0)
-            L.vk_w4_select(1)
+            L.vk_w4_select(0)
         assert torch.equal(y, y2), "the product must not depend on scheduling"
         got = y.float().cpu().numpy()
         np.testing.assert_allclose(got[:, sel], want, rtol=2e-2, atol=2e-2)
-        # and much tighter against the exact product (the kernel keeps s*u + b unrounded)
-        err = np.abs(got[:, sel] - exact)
-        assert (err <= 2.0 ** -8 * np.abs(exact) + 2e-3).all(), (tcgen05, err.max())
+        # and much tighter against the exact product (forms 0 and 1 keep s*u + b unrounded, form 4 rounds it to bf16)
+        err = np.abs(got[:, sel] - (exact_r if form == 4 else exact))
+        assert (err <= 2.0 ** -8 * np.abs(exact) + 2e-3).all(), (form, err.max())
         ys.append(y)
-    return ys[0]
+    return ys[-1]
 
 
 @pytest.mark.parametrize("M", [1, 2, 3, 4, 8, 9, 16])

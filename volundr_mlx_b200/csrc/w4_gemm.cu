@@ -618,6 +618,7 @@ __global__ void bf16_repack_kernel(const __nv_bfloat16* __restrict__ W, int N, i
 int g_w4_t5 = 0;
 struct W4Params;
 cudaError_t w4_t5_launch(const W4Params& p, cudaStream_t stream);
+cudaError_t w4_tacc_launch(const W4Params& p, cudaStream_t stream);
 
 int g_force_ctas = 0;
 int g_prefetch_mb = 0;    // L2 prefetch budget of one GEMM launch in MB; off by default: measured slower (it competes with demand loads)
@@ -697,7 +698,7 @@ static cudaError_t w4_launch_pass(const void* packed, const __nv_bfloat16* x, in
     (void)PS;
     cudaError_t e = vk_launch(w4_xrec_kernel, dim3(pl.G, NR), dim3(128), 0, stream, x, ldx, m, ws + kCounterBytes);
     if (e != cudaSuccess) return e;
-    if (t5) return w4_t5_launch(p, stream);
+    if (t5) return g_w4_t5 == 4 ? w4_tacc_launch(p, stream) : w4_t5_launch(p, stream);
     return vk_launch(w4_gemm_kernel<MT, 0>, dim3(pl.P), dim3(kThreads), smem_bytes<0, MT>(), stream, p);
 }
 
@@ -772,7 +773,7 @@ int vk_w4_gemm_xrec(const void* packed, const void* xrec, void* y, int ldy, int 
     p.part = (float*)(ws + kCounterBytes + (size_t)pl.G * kXRecBytes);
     p.T = pl.T; p.M = M; p.N = N; p.NSB = pl.NSB; p.G = pl.G; p.P = pl.P; p.ldy = ldy; p.maxc = pl.maxc; p.S = pl.S;
     p.pf = w4_prefetch_steps(pl.P, (size_t)wstage_bytes<0>(), Fmt<0>::kStages);
-    if (t5) return (int)w4_t5_launch(p, stream);
+    if (t5) return (int)(g_w4_t5 == 4 ? w4_tacc_launch(p, stream) : w4_t5_launch(p, stream));
     cudaError_t e = M <= 8 ? vk_launch(w4_gemm_kernel<1, 0>, dim3(pl.P), dim3(kThreads), smem_bytes<0>(), stream, p)
                            : vk_launch(w4_gemm_kernel<2, 0>, dim3(pl.P), dim3(kThreads), smem_bytes<0>(), stream, p);
     return (int)e;
