@@ -83,7 +83,10 @@ def _check_gemm(cuda, rng, M, N, K, group, cols=None, force=None):
         got = y.float().cpu().numpy()
         np.testing.assert_allclose(got[:, sel], want, rtol=2e-2, atol=2e-2)
         # and much tighter against the exact product (forms 0 and 1 keep s*u + b unrounded, form 4 rounds it to bf16)
-        err = np.abs(got[:, sel] - (exact_r if form == 4 else exact))
+        # (beyond 16 rows only the last pass of up to 16 rows runs in the selected form: either product may be the nearer)
+        err = np.abs(got[:, sel] - exact)
+        if form == 4:
+            err = np.minimum(err, np.abs(got[:, sel] - exact_r))
         assert (err <= 2.0 ** -8 * np.abs(exact) + 2e-3).all(), (form, err.max())
         ys.append(y)
     return ys[-1]

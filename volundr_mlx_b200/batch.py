@@ -112,6 +112,8 @@ class BatchCache:
         self.max_blocks = self.max_pages * (PAGE // C) if self.has_bcsa else 1
         self.sel_scratch = torch.zeros((S, max(self.NS, 1), self.max_blocks), **i32)
         self.nsplit_bcsa, self.nsplit_dense = 16, 64
+        if os.environ.get("VK_NSPLIT"):   # tuning: "bcsa,dense"
+            self.nsplit_bcsa, self.nsplit_dense = (int(v) for v in os.environ["VK_NSPLIT"].split(","))
         self.part = torch.zeros((S, m.Hq, max(self.nsplit_bcsa, self.nsplit_dense), 130), **f32)
         if a.engram_layers:
             cat = a.engram_dim * len(a.engram_orders)
