@@ -819,6 +819,15 @@ __global__ void __launch_bounds__(128) attend_decode_tc_kernel(const AttendParam
     __shared__ const __nv_bfloat16* rowV[2][kPage];
     pdl_launch_dependents();
     pdl_wait();
+#if defined(VK_TRACE) && VK_TRACE == 7
+    long long tr[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    const long long tr_start = clock64();
+#define AT_T(var) const long long var = clock64()
+#define AT_ACC(slot, a, b) tr[slot] += (b) - (a)
+#else
+#define AT_T(var) do { } while (0)
+#define AT_ACC(slot, a, b) do { } while (0)
+#endif
     const AttnGeom& g = p.g;
     const int split = blockIdx.x, kv = blockIdx.y, b = blockIdx.z;
     const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
@@ -908,16 +917,26 @@ __global__ void __launch_bounds__(128) attend_decode_tc_kernel(const AttendParam
     // K and V of a unit travel as separate groups: Q K^T starts when K is in, V lands during the softmax; the next
     // unit's K is requested as soon as this unit's scores are out, its V as soon as this unit's P V is done.
     int nrows = 0, cur = 0;
+    AT_T(p0);
     if (split < U) nrows = setup_unit(split, rowK[0], rowV[0]);
     __syncthreads();
+    AT_T(p1);
+    AT_ACC(0, tr_start, p0); AT_ACC(1, p0, p1);
     issue_rows(Ks, rowK[0], nrows);
     issue_rows(Vs, rowV[0], nrows);
+#if defined(VK_TRACE) && VK_TRACE == 7
+    int tr_units = 0;
+#endif
     for (int u = split; u < U; u += p.nsplit, cur ^= 1) {
         const int un = u + p.nsplit;
         int nrows_next = 0;
+        AT_T(u0);
         if (un < U) nrows_next = setup_unit(un, rowK[cur ^ 1], rowV[cur ^ 1]);
+        AT_T(u1);
         cp_async_wait1();   // K of this unit (V may still be on its way)
         __syncthreads();
+        AT_T(u2);
+        AT_ACC(2, u0, u1); AT_ACC(3, u1, u2);
         // ---- S = Q K^T: warp w takes keys 16 w .. 16 w + 15
         {
             float sa[2][4] = {};
@@ -958,8 +977,11 @@ __global__ void __launch_bounds__(128) attend_decode_tc_kernel(const AttendParam
                 s_aold[h] = a_old;
             }
         }
+        AT_T(u3);
         cp_async_wait1();   // V of this unit (the next unit's K may still be on its way)
         __syncthreads();
+        AT_T(u4);
+        AT_ACC(4, u2, u3); AT_ACC(5, u3, u4);
         // ---- O = O * a_old + P V: warp w takes dims 32 w .. 32 w + 31
         {
             const float a = s_aold[gq];
@@ -983,9 +1005,19 @@ __global__ void __launch_bounds__(128) attend_decode_tc_kernel(const AttendParam
         __syncthreads();   // every warp is done with this unit's V
         issue_rows(Vs, rowV[cur ^ 1], nrows_next);
         nrows = nrows_next;
+#if defined(VK_TRACE) && VK_TRACE == 7
+        { const long long u5 = clock64(); tr[6] += u5 - u4; tr_units++; }
+#endif
     }
     cp_async_wait0();
     __syncthreads();
+#if defined(VK_TRACE) && VK_TRACE == 7
+    if (t == 0) {
+        long long* o = g_vk_trace + (((blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) & 4095) * 16;
+        for (int q = 0; q < 7; q++) o[q] = tr[q];
+        o[7] = clock64() - tr_start; o[8] = tr_units; o[9] = U;
+    }
+#endif
     float* out = p.part + (((size_t)b * g.KVH + kv) * p.nsplit + split) * G * (kD + 2);
     if (gq < G) {
 #pragma unroll
