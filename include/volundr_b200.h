@@ -57,12 +57,15 @@ int vk_w4_gemm(const void* packed, const void* x, int ldx, void* y, int ldy, int
  * fuses its input preparation into the producing op, agens-mlx-bench/smallm/prep_nax.py:24-148). M <= 16. */
 int vk_w4_gemm_xrec(const void* packed, const void* xrec, void* y, int ldy, int M, int N, int K, void* workspace,
                     size_t workspace_bytes, vk_stream_t stream);
-/* Which kernel multiplies up to 16 activation rows (vk_w4_gemm_xrec, vk_w4_gemm with M <= 16): 1 (default) the
- * tcgen05 form (the codes expanded to bf16 in shared memory, the product on the 5th-generation tensor cores with the
- * accumulator in tensor memory, scale and bias applied per group by the warps), 0 the mma.sync form. Same arithmetic and
- * the same fixed sum order; the two differ in the last bits (the tensor cores' internal summation). A testing and
- * measuring aid: set it before the first launch of a CUDA graph that records these calls. */
-void vk_w4_select(int tcgen05);
+/* Which kernel multiplies up to 16 activation rows (vk_w4_gemm_xrec, vk_w4_gemm with M <= 16):
+ *   0 (default)  mma.sync on the raw codes, scale and bias term applied per 64-column group in fp32;
+ *   2, 3         the same arithmetic with the per-group products on tcgen05 (weights as the M side; the number is the
+ *                steps between a warp's expansion and its accumulation of a step); differs from 0 in the last bits;
+ *   4            weights dequantised to bf16 in shared memory (bit-equal to vk_w4_dequant), activations x weights on
+ *                tcgen05 with the accumulator in tensor memory over all of K: the arithmetic of "dequantise, then matmul".
+ * 2 .. 4 are measured slower than 0 on B200 and are kept as tested alternatives. A testing and measuring aid, global to
+ * the process: set it before the first launch of a CUDA graph that records these calls. */
+void vk_w4_select(int form);
 /* The same streaming kernel over plain bf16 weights: the linears the reference keeps unquantised (convert.py:16-17),
  * above all lm_head (volundr.py:958, :968; batch.py:552). W [N, K] row-major bf16 is repacked once into the kernel's
  * fragment order (vk_bf16_repack); y = bf16(x . W^T), fp32 accumulation, 1..16 rows per pass. Workspace rules as for

@@ -613,8 +613,9 @@ __global__ void bf16_repack_kernel(const __nv_bfloat16* __restrict__ W, int N, i
     reinterpret_cast<uint32_t*>(out)[idx] = v;
 }
 
-// 0 (default): up to 16 activation rows run on w4_gemm_kernel<MT, 0> (mma.sync); 2 / 3: on w4_t5_kernel (tcgen05,
-// w4_t5.cu) with that many steps between a warp's expansion and accumulation of a step: measured at half the speed
+// 0 (default): up to 16 activation rows run on w4_gemm_kernel<MT, 0> (mma.sync); 2 / 3: on w4_t5_kernel (tcgen05 per
+// group, w4_t5.cu) with that many steps between a warp's expansion and accumulation of a step; 4: on w4_tacc_kernel
+// (dequantised weights, accumulation in tensor memory, w4_tacc.cu). Both tcgen05 forms are measured slower.
 int g_w4_t5 = 0;
 struct W4Params;
 cudaError_t w4_t5_launch(const W4Params& p, cudaStream_t stream);
@@ -732,7 +733,7 @@ void vk_w4_force_plan(int ctas, int prefetch_mb) {
     g_prefetch_mb = prefetch_mb < 0 ? 0 : prefetch_mb;
 }
 
-void vk_w4_select(int tcgen05) { g_w4_t5 = tcgen05 < 0 ? 0 : tcgen05; }
+void vk_w4_select(int form) { g_w4_t5 = form < 0 ? 0 : form; }
 
 size_t vk_w4_workspace_bytes(int M, int N, int K) {
     if (N <= 0 || K <= 0 || K % 64 != 0) return 0;
