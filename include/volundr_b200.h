@@ -80,6 +80,12 @@ int vk_bf16_gemm_packed(const void* packed, const void* x, int ldx, void* y, int
  * tile is dequantised to bf16 once, bf16(s * u + b) with a single rounding (the value vk_w4_dequant gives), so results
  * differ from vk_w4_gemm by that rounding of the weights (within the bf16 bar). `packed` as for vk_w4_gemm. */
 size_t vk_w4_tile_workspace_bytes(int M, int K);
+/* Up to 128 rows: with a workspace of this many bytes, zeroed once by the caller (its first 16 KB hold arrival counters the
+ * kernels leave at zero), the product runs split-K: every SM takes an equal range of the weight's 9216-byte steps and
+ * accumulates in tensor memory, ranges that share a 256-row block add their fp32 partial sums in a fixed order; with less,
+ * whole 256-row blocks per CTA, in waves. Same arithmetic either way; vk_w4_tile_split(0) forces the second form. */
+size_t vk_w4_tile_workspace_bytes_n(int M, int N, int K);
+void vk_w4_tile_split(int on);
 int vk_w4_gemm_tile(const void* packed, const void* x, int ldx, void* y, int ldy, int M, int N, int K, void* workspace,
                     size_t workspace_bytes, vk_stream_t stream);
 /* Tuning / testing aid for vk_w4_gemm_tile: weight rows per CTA (256 = a whole superblock, 64 = a quarter, for weights

@@ -30,8 +30,10 @@ def make_w4(rng, N, K, group):
 @pytest.mark.parametrize("M,N,K", [(128, 256, 64), (128, 256, 512), (37, 520, 1024), (200, 300, 2048), (256, 5120, 1024),
                                    (300, 768, 640)])
 def test_tile_gemm(cuda, M, N, K, shape):
-    """Every tile shape (weight rows per CTA 256 / 64, one or two tiles of activation rows per CTA; (0, 0) = chosen
-    from the shape) gives the same result, bit for bit: the accumulation order along K does not depend on it."""
+    """Every tile shape (weight rows per CTA 256 / 64, one or two tiles of activation rows per CTA) gives the same result,
+    bit for bit: the accumulation order along K does not depend on it. (0, 0) = chosen from the shape: up to 128 rows that
+    is the split-K kernel, whose fp32 partial sums over K ranges are added in a fixed order: the same result on every
+    call, and within one bf16 step of the whole-K accumulation."""
     from volundr_mlx_b200 import _lib, ops
 
     _lib.check(_lib.lib().vk_w4_tile_force(*shape), "vk_w4_tile_force")
@@ -47,7 +49,12 @@ def test_tile_gemm(cuda, M, N, K, shape):
     y3 = ops.w4_gemm_tile(tx, wt)
     _lib.check(_lib.lib().vk_w4_tile_force(0, 0), "vk_w4_tile_force")
     ops.check_status()
-    assert torch.equal(y, y2) and torch.equal(y, y3)
+    assert torch.equal(y, y2)
+    if shape != (0, 0) or M > 128:
+        assert torch.equal(y, y3)
+    else:
+        d = (y.float() - y3.float()).abs()
+        assert bool((d <= 2.0 ** -7 * y3.float().abs() + 1e-3).all()), float(d.max())
     got = y.float().cpu().numpy()
     np.testing.assert_allclose(got, OW.matmul(x, w, s, b, 64), rtol=2e-2, atol=2e-2)
     Wd = OW.dequant(w, s, b, 64).astype(np.float64)          # bf16-valued

@@ -20,6 +20,8 @@ SIGNATURES = {
     "vk_w4_repack": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p]),
     "vk_w4_dequant": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p]),
     "vk_w4_tile_workspace_bytes": (c_size_t, [c_int, c_int]),
+    "vk_w4_tile_workspace_bytes_n": (c_size_t, [c_int, c_int, c_int]),
+    "vk_w4_tile_split": (None, [c_int]),
     "vk_w4_gemm_tile": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_size_t, c_void_p]),
     "vk_w4_tile_force": (c_int, [c_int, c_int]),
     "vk_w4_force_plan": (None, [c_int, c_int]),

@@ -212,7 +212,10 @@ def forward_chunk_iter(model, bc, toks, write=False, logits_at=None, capture=(),
     tile_ws = None
     if R >= 64:
         kmax = max(max(w[nm].K for nm in ("proj", "out", "gate_up", "down")) for w in model.layers)
-        tile_ws = torch.empty(L.vk_w4_tile_workspace_bytes(R, kmax), dtype=torch.uint8, device=dev)
+        nmax = max(max(w[nm].N for nm in ("proj", "out", "gate_up", "down")) for w in model.layers)
+        need = max(L.vk_w4_tile_workspace_bytes_n(R, w[nm].N, w[nm].K) for w in model.layers for nm in ("proj", "out", "gate_up", "down"))
+        tile_ws = ops.tile_workspace(max(need, L.vk_w4_tile_workspace_bytes(R, kmax)), dev)   # (zeroed once: its head holds counters)
+        del nmax
 
     def gemm(x, wt, y):
         # 64 rows and more: the tcgen05 tile kernel; fewer: the streaming kernel's passes

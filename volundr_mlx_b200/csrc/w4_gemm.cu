@@ -620,6 +620,7 @@ int g_w4_t5 = 0;
 struct W4Params;
 cudaError_t w4_t5_launch(const W4Params& p, cudaStream_t stream);
 cudaError_t w4_tacc_launch(const W4Params& p, cudaStream_t stream);
+cudaError_t w4_tacc_launch128(const W4Params& p, cudaStream_t stream);
 
 int g_force_ctas = 0;
 int g_prefetch_mb = 0;    // L2 prefetch budget of one GEMM launch in MB; off by default: measured slower (it competes with demand loads)

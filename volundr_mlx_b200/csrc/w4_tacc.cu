@@ -39,21 +39,31 @@
 
 namespace {
 
-constexpr int kTaThreads = 640;
 constexpr int kTaExpWarps = 16;
 constexpr int kTaWBytes = kBlocksPerSB * kChunkBytes;        // 9216
 constexpr int kTaBBytes = kSBRows * 64 * 2;                  // 32 KB: [8][256][8] bf16
-constexpr int kTaXBytes = 2304;                              // an x record (2176) up to the next multiple of 128
-constexpr int kTaSlotBytes = kTaXBytes + kTaBBytes;          // a slot = the step's x record, then its B operand: the A
-                                                             // descriptor's rows 16..127 fall into the B operand behind it
-constexpr int kTaSlots = 4;
-constexpr int kTaStages = 6;
-constexpr size_t kTaSlotOff = (size_t)kTaStages * kTaWBytes;
-constexpr size_t kTaBarOff = kTaSlotOff + (size_t)kTaSlots * kTaSlotBytes;
-constexpr int kTaBars = 2 * kTaStages + 3 * kTaSlots + 4;
-constexpr size_t kTaSmem = kTaBarOff + kTaBars * 8;
-static_assert(kTaSmem <= 227 * 1024, "does not fit a CTA's shared memory");
-static_assert(7 * 256 + 16 * 128 <= kTaSlotBytes, "the M = 128 operand must stay inside its slot");
+// MR = activation rows the A operand really holds:
+//   16   the x records of the decode step (2176 bytes per 64-column group, rows 16..127 of the M = 128 operand are
+//        whatever follows the record in its slot); 20 warps, drain by warps 0 and 4 (lanes 0..15 of quarter 0)
+//   128  the 16 KB activation tiles of vk_w4_gemm_tile ([8][128][8] bf16 per group, rows beyond M zero): verify windows
+//        and chunks of up to 128 rows; 22 warps, drain by warps 4..7 (one lane quarter each)
+template <int MR> struct TaCfg {
+    static constexpr int kThreads = MR == 16 ? 640 : 704;
+    static constexpr int kDrainWarps = MR == 16 ? 2 : 4;
+    static constexpr int kXLoad = MR == 16 ? kXRecBytes : MR * 64 * 2;      // bytes of A per step
+    static constexpr int kXBytes = MR == 16 ? 2304 : MR * 64 * 2;           // ... up to the next multiple of 128
+    static constexpr int kLbo = MR * 16;                                     // bytes between the operand's 16-byte units along K
+    static constexpr int kSlotBytes = kXBytes + kTaBBytes;                   // a slot = the step's A operand, then its B operand
+    static constexpr int kSlots = MR == 16 ? 4 : 3;
+    static constexpr int kStages = MR == 16 ? 6 : 5;
+    static constexpr int kPS = MR == 16 ? 16 : MR;                           // floats per row of a partial-sum slab
+    static constexpr size_t kSlotOff = (size_t)kStages * kTaWBytes;
+    static constexpr size_t kBarOff = kSlotOff + (size_t)kSlots * kSlotBytes;
+    static constexpr int kBars = 2 * kStages + 3 * kSlots + 4;
+    static constexpr size_t kSmem = kBarOff + kBars * 8;
+    static_assert(kSmem <= 227 * 1024, "does not fit a CTA's shared memory");
+    static_assert(7 * kLbo + 16 * 128 <= kSlotBytes, "the M = 128 operand must stay inside its slot");
+};
 
 #if defined(VK_TRACE) && VK_TRACE == 6
 #define TA_T(var) const long long var = clock64()
@@ -63,12 +73,16 @@ static_assert(7 * 256 + 16 * 128 <= kTaSlotBytes, "the M = 128 operand must stay
 #define TA_ACC(slot, a, b) do { } while (0)
 #endif
 
-__device__ __forceinline__ void ta_drain_sync() { asm volatile("bar.sync 2, 64;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void ta_drain_sync() { asm volatile("bar.sync 2, %0;" ::"n"(N) : "memory"); }
 
-__global__ void __launch_bounds__(kTaThreads, 1) w4_tacc_kernel(const W4Params p) {
+template <int MR>
+__global__ void __launch_bounds__(TaCfg<MR>::kThreads, 1) w4_tacc_kernel(const W4Params p) {
     extern __shared__ __align__(128) uint8_t smem[];
-    uint8_t* slots = smem + kTaSlotOff;
-    uint64_t* wfull = reinterpret_cast<uint64_t*>(smem + kTaBarOff);
+    using Cfg = TaCfg<MR>;
+    constexpr int kTaSlots = Cfg::kSlots, kTaStages = Cfg::kStages, kTaSlotBytes = Cfg::kSlotBytes, kTaXBytes = Cfg::kXBytes;
+    constexpr int kDrainThreads = 32 * Cfg::kDrainWarps, kPS = Cfg::kPS;
+    uint8_t* slots = smem + Cfg::kSlotOff;
+    uint64_t* wfull = reinterpret_cast<uint64_t*>(smem + Cfg::kBarOff);
     uint64_t* wempty = wfull + kTaStages;     // every expansion warp has the stage's codes in registers
     uint64_t* xfull = wempty + kTaStages;     // [slot] the step's x record has landed
     uint64_t* bready = xfull + kTaSlots;      // [slot] the step's dequantised weights are in place
@@ -102,7 +116,7 @@ __global__ void __launch_bounds__(kTaThreads, 1) w4_tacc_kernel(const W4Params p
         }
         for (int s = 0; s < 2; s++) {
             mbar_init(&dready[s], 1);
-            mbar_init(&dfree[s], 2);
+            mbar_init(&dfree[s], Cfg::kDrainWarps);
         }
         mbar_fence_init();
         s_fail = 0;
@@ -145,8 +159,8 @@ __global__ void __launch_bounds__(kTaThreads, 1) w4_tacc_kernel(const W4Params p
             for (int i = 0; i < n; i++) {
                 const int s = i % kTaSlots;
                 if (i >= kTaSlots && !mbar_wait(&sfree[s], (uint32_t)((i / kTaSlots - 1) & 1))) { s_fail = 1; break; }
-                mbar_expect_tx(&bready[s], kXRecBytes);   // (one of the barrier's arrivals, plus the copy's bytes)
-                tma_bulk_g2s(slots + (size_t)s * kTaSlotBytes, p.xrec + (size_t)kg * kXRecBytes, kXRecBytes, &bready[s]);
+                mbar_expect_tx(&bready[s], Cfg::kXLoad);   // (one of the barrier's arrivals, plus the copy's bytes)
+                tma_bulk_g2s(slots + (size_t)s * kTaSlotBytes, p.xrec + (size_t)kg * Cfg::kXLoad, Cfg::kXLoad, &bready[s]);
                 kg = kg + 1 == p.G ? 0 : kg + 1;
             }
         }
@@ -183,7 +197,7 @@ __global__ void __launch_bounds__(kTaThreads, 1) w4_tacc_kernel(const W4Params p
 #if VK_TA_EXP == 2
                     continue;                       // (timing experiment: no MMA)
 #endif
-                    const uint64_t da = umma_desc(a0 + kk * 2 * (16 * 16), 16 * 16, 128);
+                    const uint64_t da = umma_desc(a0 + kk * 2 * Cfg::kLbo, Cfg::kLbo, 128);
                     const uint64_t db = umma_desc(b0 + kk * 2 * (kSBRows * 16), kSBRows * 16, 128);
                     const uint32_t accumulate = (first && kk == 0) ? 0u : 1u;
                     const uint32_t zero = 0u;
@@ -218,28 +232,29 @@ __global__ void __launch_bounds__(kTaThreads, 1) w4_tacc_kernel(const W4Params p
             o[8] = tr[0]; o[9] = tr[1]; o[10] = tr[2]; o[11] = tr[3]; o[12] = clock64() - tr_start; o[13] = n;
 #endif
         }
-    } else if (warp == 0 || warp == 4) {
-        // ---------------------------------------------------------------- drain (tensor-memory lanes 0..31)
+    } else if (MR == 16 ? (warp == 0 || warp == 4) : (warp >= 4 && warp < 8)) {
+        // ---------------------------------------------------------------- drain (a warp reads the lane quarter warp % 4)
         pdl_wait();
-        const int half = warp >> 2;              // columns 128 half .. 128 half + 127
-        const int dtid = half * 32 + lane;       // 0..63
-        const int m = lane;                      // activation row held by this thread
+        const int dw = MR == 16 ? (warp >> 2) : (warp - 4);         // drain warp index
+        const int dtid = dw * 32 + lane;
+        const int m = MR == 16 ? lane : dw * 32 + lane;             // activation row held by this thread
+        const int ncols = MR == 16 ? 128 : 256, col0 = MR == 16 ? dw * 128 : 0;   // accumulator columns this warp takes
         int sb = (int)(t0 / p.G), kg0 = (int)(t0 % p.G);
         int buf = 0, nseg[2] = {0, 0};
         bool ok = true;
         // rows [r0, r1) of superblock fsb: the nc partial slabs added in slab order, rounded, stored
         auto add_partials = [&](int fsb, int nc, int r0, int r1) {
-            constexpr int V4 = 4;   // float4 columns of a 16-float partial row
-            for (int item = dtid; item < (r1 - r0) * V4; item += 64) {
+            constexpr int V4 = kPS / 4;   // float4 columns of a partial row
+            for (int item = dtid; item < (r1 - r0) * V4; item += kDrainThreads) {
                 const int r = r0 + item / V4, v = item % V4;
                 const int nrow = fsb * kSBRows + r;
-                const float4* src = reinterpret_cast<const float4*>(p.part + ((size_t)fsb * p.maxc * kSBRows + r) * 16) + v;
+                const float4* src = reinterpret_cast<const float4*>(p.part + ((size_t)fsb * p.maxc * kSBRows + r) * kPS) + v;
                 float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
                 for (int c0 = 0; c0 < nc; c0 += 8) {
                     float4 b8[8];
 #pragma unroll
                     for (int u = 0; u < 8; u++)
-                        b8[u] = (c0 + u < nc) ? __ldcg(src + (size_t)(c0 + u) * kSBRows * 4) : make_float4(0.f, 0.f, 0.f, 0.f);
+                        b8[u] = (c0 + u < nc) ? __ldcg(src + (size_t)(c0 + u) * kSBRows * V4) : make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
                     for (int u = 0; u < 8; u++) {
                         if (c0 + u < nc) { sum.x += b8[u].x; sum.y += b8[u].y; sum.z += b8[u].z; sum.w += b8[u].w; }
@@ -260,12 +275,12 @@ __global__ void __launch_bounds__(kTaThreads, 1) w4_tacc_kernel(const W4Params p
             const int c_first = p.S > 0 ? sb * p.S : step_owner(s0, p.T, p.P);
             if (!mbar_wait(&dready[buf], (uint32_t)(nseg[buf] & 1))) { ok = false; break; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            float* pdst = p.part + (((size_t)sb * p.maxc + (blockIdx.x - c_first)) * kSBRows) * 16;
+            float* pdst = p.part + (((size_t)sb * p.maxc + (blockIdx.x - c_first)) * kSBRows) * kPS;
 #pragma unroll 1
-            for (int c = 0; c < 4; c++) {
+            for (int c = 0; c < ncols / 32; c++) {
                 uint32_t d[32];
-                const int col = half * 128 + c * 32;
-                const uint32_t taddr = tmem + (uint32_t)(buf * 256 + col);
+                const int col = col0 + c * 32;
+                const uint32_t taddr = tmem + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)(buf * 256 + col);
                 asm volatile(
                     "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
                     "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
@@ -277,18 +292,31 @@ __global__ void __launch_bounds__(kTaThreads, 1) w4_tacc_kernel(const W4Params p
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
                 if (m < p.M) {
                     if (whole) {
-                        __nv_bfloat16* yrow = p.y + (size_t)m * p.ldy + (size_t)sb * kSBRows + col;
+                        const size_t yoff = (size_t)m * p.ldy + (size_t)sb * kSBRows + col;
+                        __nv_bfloat16* yrow = p.y + yoff;
                         const int lim = p.N - (sb * kSBRows + col);   // columns of this piece that exist
+                        if (lim >= 32 && (yoff & 7) == 0) {
 #pragma unroll
-                        for (int e = 0; e < 32; e++)
-                            if (e < lim) yrow[e] = f2bf(__uint_as_float(d[e]));
+                            for (int e = 0; e < 32; e += 8) {
+                                uint4 o;
+                                o.x = pack_bf2(__uint_as_float(d[e]), __uint_as_float(d[e + 1]));
+                                o.y = pack_bf2(__uint_as_float(d[e + 2]), __uint_as_float(d[e + 3]));
+                                o.z = pack_bf2(__uint_as_float(d[e + 4]), __uint_as_float(d[e + 5]));
+                                o.w = pack_bf2(__uint_as_float(d[e + 6]), __uint_as_float(d[e + 7]));
+                                *reinterpret_cast<uint4*>(yrow + e) = o;
+                            }
+                        } else {
+#pragma unroll
+                            for (int e = 0; e < 32; e++)
+                                if (e < lim) yrow[e] = f2bf(__uint_as_float(d[e]));
+                        }
                     } else {
 #pragma unroll
-                        for (int e = 0; e < 32; e++) __stcg(pdst + (size_t)(col + e) * 16 + m, __uint_as_float(d[e]));
+                        for (int e = 0; e < 32; e++) __stcg(pdst + (size_t)(col + e) * kPS + m, __uint_as_float(d[e]));
                     }
-                } else if (!whole && m < 16) {   // rows M..15 of a slab are read by the final addition: keep them defined
+                } else if (!whole && m < kPS) {   // rows M.. of a slab are read by the final addition: keep them defined
 #pragma unroll
-                    for (int e = 0; e < 32; e++) __stcg(pdst + (size_t)(col + e) * 16 + m, 0.f);
+                    for (int e = 0; e < 32; e++) __stcg(pdst + (size_t)(col + e) * kPS + m, 0.f);
                 }
             }
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -297,7 +325,7 @@ __global__ void __launch_bounds__(kTaThreads, 1) w4_tacc_kernel(const W4Params p
             nseg[buf]++;
             buf ^= 1;
             if (!whole) {
-                ta_drain_sync();
+                ta_drain_sync<kDrainThreads>();
                 if (p.S > 0) {
                     // aligned mode: the S CTAs of this superblock started together with equal shares of K. Each has stored
                     // its partial sums, waits (bounded) for the others, then adds up its own share of the rows in slice order.
@@ -316,9 +344,9 @@ __global__ void __launch_bounds__(kTaThreads, 1) w4_tacc_kernel(const W4Params p
                         s_last = seen >= nc;
                         if (!s_last) vk_set_status(VK_ST_FLAG_TIMEOUT);
                     }
-                    ta_drain_sync();
+                    ta_drain_sync<kDrainThreads>();
                     if (s_last) add_partials(sb, nc, slot * kSBRows / nc, (slot + 1) * kSBRows / nc);
-                    ta_drain_sync();
+                    ta_drain_sync<kDrainThreads>();
                     if (dtid == 0) {
                         const int old = atomicAdd(depart, 1);
                         if (old == nc - 1) { *arrive = 0; *depart = 0; __threadfence(); }
@@ -331,13 +359,13 @@ __global__ void __launch_bounds__(kTaThreads, 1) w4_tacc_kernel(const W4Params p
                         s_last = (old == ncontrib - 1) ? ncontrib : 0;
                         if (s_last) p.counters[sb] = 0;
                     }
-                    ta_drain_sync();
+                    ta_drain_sync<kDrainThreads>();
                     const int ncontrib = s_last;
                     if (ncontrib) {
                         __threadfence();
                         add_partials(sb, ncontrib, 0, kSBRows);
                     }
-                    ta_drain_sync();   // s_last is reused by the next segment
+                    ta_drain_sync<kDrainThreads>();   // s_last is reused by the next segment
                 }
             }
             done += kgb - kga;
@@ -347,7 +375,7 @@ __global__ void __launch_bounds__(kTaThreads, 1) w4_tacc_kernel(const W4Params p
         if (!ok) s_fail = 1;
     } else {
         // ---------------------------------------------------------------- expansion (warps 3, 5..19): weights only
-        const int cw = warp == 3 ? 0 : warp - 4;     // 0..15
+        const int cw = MR == 16 ? (warp == 3 ? 0 : warp - 4) : (warp == 0 ? 0 : warp == 3 ? 1 : warp - 6);   // 0..15
         const int g = lane >> 2, t = lane & 3;
         // Two groups of eight warps take alternate steps (a warp expands a whole 32-row chunk of its steps): the waits of
         // one group (weights landed, slot free, stores visible) hide behind the other group's arithmetic.
@@ -415,7 +443,7 @@ __global__ void __launch_bounds__(kTaThreads, 1) w4_tacc_kernel(const W4Params p
             TA_ACC(0, c0, c1); TA_ACC(1, c2, c3); TA_ACC(2, c3, c4); TA_ACC(3, c4, c5);
         }
 #if defined(VK_TRACE) && VK_TRACE == 6
-        if (warp == 3 && lane == 0) {
+        if (cw == 0 && lane == 0) {
             long long* o = g_vk_trace + (blockIdx.x & 4095) * 16;
             for (int u = 0; u < 4; u++) o[u] = tr[u];
             o[4] = clock64() - tr_start;
@@ -430,19 +458,23 @@ __global__ void __launch_bounds__(kTaThreads, 1) w4_tacc_kernel(const W4Params p
     if (threadIdx.x == 0 && s_fail) vk_set_status(VK_ST_MBAR_TIMEOUT);
 }
 
-// p: filled for w4_plan(N, K, 1) (one CTA per SM)
-cudaError_t w4_tacc_launch(const W4Params& p, cudaStream_t stream) {
+// p: filled for w4_plan(N, K, 1) (one CTA per SM); rows128: p.xrec holds 16 KB activation tiles (up to 128 rows) and the
+// partial-sum slabs are 128 floats wide, else x records (up to 16 rows) and 16-float slabs
+template <int MR>
+static cudaError_t w4_tacc_launch_t(const W4Params& p, cudaStream_t stream) {
     static std::atomic<bool> configured[64];
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return e;
     if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
     if (!configured[dev].load(std::memory_order_acquire)) {
-        e = cudaFuncSetAttribute(w4_tacc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kTaSmem);
+        e = cudaFuncSetAttribute(w4_tacc_kernel<MR>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TaCfg<MR>::kSmem);
         if (e != cudaSuccess) return e;
         configured[dev].store(true, std::memory_order_release);
     }
-    return vk_launch(w4_tacc_kernel, dim3(p.P), dim3(kTaThreads), kTaSmem, stream, p);
+    return vk_launch(w4_tacc_kernel<MR>, dim3(p.P), dim3(TaCfg<MR>::kThreads), TaCfg<MR>::kSmem, stream, p);
 }
+cudaError_t w4_tacc_launch(const W4Params& p, cudaStream_t stream) { return w4_tacc_launch_t<16>(p, stream); }
+cudaError_t w4_tacc_launch128(const W4Params& p, cudaStream_t stream) { return w4_tacc_launch_t<128>(p, stream); }
 
 }  // namespace

@@ -309,6 +309,19 @@ size_t vk_w4_tile_workspace_bytes(int M, int K) {
     return (size_t)((M + kTileM - 1) / kTileM) * (K / 64) * kXTileBytes;
 }
 
+// Up to 128 rows run on the split-K kernel of w4_tacc.cu (every SM takes an equal range of the weight's steps, instead
+// of whole superblocks in waves) when the workspace also holds its arrival counters and partial sums: this many bytes.
+// With less (but at least vk_w4_tile_workspace_bytes) the call falls back to whole superblocks per CTA.
+size_t vk_w4_tile_workspace_bytes_n(int M, int N, int K) {
+    const size_t tiles = vk_w4_tile_workspace_bytes(M, K);
+    if (tiles == 0 || N <= 0 || M > kTileM) return tiles;
+    const W4Plan pl = w4_plan(N, K, 1);
+    return kCounterBytes + tiles + (size_t)pl.NSB * pl.maxc * kSBRows * kTileM * sizeof(float);
+}
+
+static int g_tile_split = 1;   // 0: never the split-K kernel (test and measuring aid)
+void vk_w4_tile_split(int on) { g_tile_split = on != 0; }
+
 // y[M, N] = bf16(x[M, K] . dequant(W)^T) on tcgen05 tensor cores; `packed` as for vk_w4_gemm. Any M (tiles of 128 rows).
 int vk_w4_gemm_tile(const void* packed, const void* x, int ldx, void* y, int ldy, int M, int N, int K, void* workspace,
                     size_t workspace_bytes, cudaStream_t stream) {
@@ -324,8 +337,29 @@ int vk_w4_gemm_tile(const void* packed, const void* x, int ldx, void* y, int ldy
         configured = true;
     }
     const int G = K / 64, MTn = (M + kTileM - 1) / kTileM, NSB = (N + 255) / 256;
-    VK_CUDA(vk_launch(w4_xtile_kernel, dim3(G, MTn), dim3(128), 0, stream, (const __nv_bfloat16*)x, ldx, M, G, (uint8_t*)workspace));
-    TileParams p = {(const uint8_t*)packed, (const uint8_t*)workspace, (__nv_bfloat16*)y, M, N, G, ldy};
+    // (the split-K kernel pays for weights with few 256-row blocks, where whole blocks per CTA leave most SMs idle: its
+    // partial sums are 128 KB per block and range, which costs more than it saves once every SM has a block of its own)
+    const W4Plan pl = w4_plan(N, K, 1);
+    if (MTn == 1 && g_tile_split && pl.S > 0 && g_tile_force_tn == 0 && g_tile_force_ml == 0 && NSB <= (int)(kCounterBytes / 8) &&
+        workspace_bytes >= vk_w4_tile_workspace_bytes_n(M, N, K)) {
+        uint8_t* ws = (uint8_t*)workspace;
+        uint8_t* tiles = ws + kCounterBytes;
+        VK_CUDA(vk_launch(w4_xtile_kernel, dim3(G, 1), dim3(128), 0, stream, (const __nv_bfloat16*)x, ldx, M, G, tiles));
+        W4Params q;
+        q.wp = (const uint8_t*)packed;
+        q.xrec = tiles;
+        q.y = (__nv_bfloat16*)y;
+        q.counters = (int*)ws;     // (zero between launches: the kernels leave them so; the caller's buffer starts zeroed)
+        q.part = (float*)(tiles + (size_t)G * kXTileBytes);
+        q.T = pl.T; q.M = M; q.N = N; q.NSB = pl.NSB; q.G = pl.G; q.P = pl.P; q.ldy = ldy; q.maxc = pl.maxc; q.S = pl.S;
+        q.pf = 0;
+        return (int)w4_tacc_launch128(q, stream);
+    }
+    // (a workspace with room for it keeps its first 16 KB, the split-K form's arrival counters, untouched)
+    uint8_t* xtiles = (uint8_t*)workspace;
+    if (workspace_bytes >= kCounterBytes + vk_w4_tile_workspace_bytes(M, K)) xtiles += kCounterBytes;
+    VK_CUDA(vk_launch(w4_xtile_kernel, dim3(G, MTn), dim3(128), 0, stream, (const __nv_bfloat16*)x, ldx, M, G, xtiles));
+    TileParams p = {(const uint8_t*)packed, (const uint8_t*)xtiles, (__nv_bfloat16*)y, M, N, G, ldy};
     // Two tiles of activation rows per CTA when there are two; whole superblocks per CTA when that still gives at
     // least one CTA per two SMs, quarters of a superblock otherwise.
     const int ml = g_tile_force_ml ? g_tile_force_ml : (MTn >= 2 ? 2 : 1);

@@ -60,6 +60,20 @@ def workspace(nbytes, device):
     return buf
 
 
+_tile_ws = {}
+
+
+def tile_workspace(nbytes, device):
+    """Scratch of vk_w4_gemm_tile (arrival counters, zero between launches, activation tiles, partial sums): a buffer of
+    its own, since the tile kernel's activation tiles would otherwise land on the streaming kernel's counters."""
+    key = str(device)
+    buf = _tile_ws.get(key)
+    if buf is None or buf.numel() < nbytes:
+        buf = torch.zeros(max(nbytes, 1 << 25), dtype=torch.uint8, device=device)
+        _tile_ws[key] = buf
+    return buf
+
+
 def w4_gemm(x, wt: W4Weight, out=None):
     """y[M, N] = x[M, K] . dequant(W)^T, bf16 in / out, fp32 accumulation."""
     L = _lib.lib()
@@ -81,7 +95,7 @@ def w4_gemm_tile(x, wt: W4Weight, out=None):
     M = x.shape[0]
     if out is None:
         out = torch.empty((M, wt.N), dtype=BF16, device=x.device)
-    ws = workspace(L.vk_w4_tile_workspace_bytes(M, wt.K), x.device)
+    ws = tile_workspace(L.vk_w4_tile_workspace_bytes_n(M, wt.N, wt.K), x.device)
     _lib.check(L.vk_w4_gemm_tile(_p(wt.packed), _p(x), x.stride(0), _p(out), out.stride(0), M, wt.N, wt.K, _p(ws),
                                  ws.numel(), _stream()), "vk_w4_gemm_tile")
     return out
