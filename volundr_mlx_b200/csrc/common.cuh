@@ -1,6 +1,7 @@
 // Shared device helpers for the sm_100a kernels: bf16 bit handling, bounded mbarrier waits, 1-D TMA bulk copies,
 // programmatic dependent launch (PDL) and the launch wrapper every kernel in this library goes through.
 #pragma once
+#include <atomic>
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -162,6 +163,25 @@ __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepc
 // All other kernels execute launch_dependents first thing: their successors are GEMMs, which read nothing but
 // weights in front of their wait and should become resident as early as possible to start streaming them.
 // Host: launch with the PDL attribute (the kernel must call pdl_wait before reading its predecessor's outputs).
+// One-time, per-device setup at a call site (function attributes such as the opt-in to more than 48 KB of dynamic shared
+// memory belong to the device's context): run(f) calls f() the first time it is reached on the current device, and again
+// if f failed. Safe from several threads (f may then run more than once; it only sets attributes).
+class PerDeviceOnce {
+    std::atomic<bool> done_[64];
+
+  public:
+    template <class F> cudaError_t run(F f) {
+        int dev = -1;
+        cudaError_t e = cudaGetDevice(&dev);
+        if (e != cudaSuccess) return e;
+        if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+        if (done_[dev].load(std::memory_order_acquire)) return cudaSuccess;
+        e = f();
+        if (e == cudaSuccess) done_[dev].store(true, std::memory_order_release);
+        return e;
+    }
+};
+
 bool vk_pdl_enabled();
 extern long long g_vk_launches;  // kernels launched through vk_launch since the last reset (host counter)
 template <typename... KArgs, typename... Args>

@@ -694,11 +694,8 @@ int vk_kda_chunk_ragged(const void* proj, int ldp, int off_z, int off_fd, const 
     cp.row_off = row_offset;
     cp.T = T;
     cp.write_state = write_state ? 1 : 0;
-    static bool configured = false;
-    if (!configured) {
-        VK_CUDA(cudaFuncSetAttribute(kda_chunk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(KdaChunkSmem)));
-        configured = true;
-    }
+    static PerDeviceOnce once;
+    VK_CUDA(once.run([] { return cudaFuncSetAttribute(kda_chunk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(KdaChunkSmem)); }));
     return (int)vk_launch(kda_chunk_kernel, dim3(HV, B), dim3(512), sizeof(KdaChunkSmem), stream, cp);
 }
 

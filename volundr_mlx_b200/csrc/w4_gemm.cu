@@ -681,14 +681,13 @@ static cudaError_t w4_launch_pass(const void* packed, const __nv_bfloat16* x, in
     constexpr int NR = n_records<MT>(), PS = MT * 8 < 16 ? 16 : MT * 8;
     const bool t5 = MT <= 2 && g_w4_t5 != 0;
     const W4Plan pl = w4_plan(N, K, t5 ? 1 : ctas_per_sm<0, MT>());
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(w4_gemm_kernel<MT, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes<0, MT>());
-        if (e != cudaSuccess) return e;
-        e = cudaFuncSetAttribute(w4_gemm_kernel<MT, 0>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
-        if (e != cudaSuccess) return e;
-        configured = true;
-    }
+    static PerDeviceOnce once;
+    cudaError_t e = once.run([] {
+        cudaError_t r = cudaFuncSetAttribute(w4_gemm_kernel<MT, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes<0, MT>());
+        if (r != cudaSuccess) return r;
+        return cudaFuncSetAttribute(w4_gemm_kernel<MT, 0>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+    });
+    if (e != cudaSuccess) return e;
     W4Params p;
     p.wp = (const uint8_t*)packed;
     p.xrec = ws + kCounterBytes;
@@ -698,7 +697,7 @@ static cudaError_t w4_launch_pass(const void* packed, const __nv_bfloat16* x, in
     p.T = pl.T; p.M = m; p.N = N; p.NSB = pl.NSB; p.G = pl.G; p.P = pl.P; p.ldy = ldy; p.maxc = pl.maxc; p.S = pl.S;
     p.pf = w4_prefetch_steps(pl.P, (size_t)wstage_bytes<0>(), Fmt<0>::kStages);
     (void)PS;
-    cudaError_t e = vk_launch(w4_xrec_kernel, dim3(pl.G, NR), dim3(128), 0, stream, x, ldx, m, ws + kCounterBytes);
+    e = vk_launch(w4_xrec_kernel, dim3(pl.G, NR), dim3(128), 0, stream, x, ldx, m, ws + kCounterBytes);
     if (e != cudaSuccess) return e;
     if (t5) return g_w4_t5 == 4 ? w4_tacc_launch(p, stream) : w4_t5_launch(p, stream);
     return vk_launch(w4_gemm_kernel<MT, 0>, dim3(pl.P), dim3(kThreads), smem_bytes<0, MT>(), stream, p);
@@ -758,13 +757,15 @@ int vk_w4_gemm_xrec(const void* packed, const void* xrec, void* y, int ldy, int 
     const W4Plan pl = w4_plan(N, K, t5 ? 1 : Fmt<0>::kCtasPerSM);
     if (pl.NSB > (int)(kCounterBytes / 8)) return VK_EINVAL;
     if (workspace_bytes < w4_ws_bytes(pl)) return VK_ENOSPC;
-    static bool configured = false;
-    if (!t5 && !configured) {
-        VK_CUDA(cudaFuncSetAttribute(w4_gemm_kernel<1, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes<0>()));
-        VK_CUDA(cudaFuncSetAttribute(w4_gemm_kernel<1, 0>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
-        VK_CUDA(cudaFuncSetAttribute(w4_gemm_kernel<2, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes<0>()));
-        VK_CUDA(cudaFuncSetAttribute(w4_gemm_kernel<2, 0>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
-        configured = true;
+    static PerDeviceOnce once;
+    if (!t5) {
+        VK_CUDA(once.run([] {
+            cudaError_t r = cudaFuncSetAttribute(w4_gemm_kernel<1, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes<0>());
+            if (r == cudaSuccess) r = cudaFuncSetAttribute(w4_gemm_kernel<1, 0>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+            if (r == cudaSuccess) r = cudaFuncSetAttribute(w4_gemm_kernel<2, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes<0>());
+            if (r == cudaSuccess) r = cudaFuncSetAttribute(w4_gemm_kernel<2, 0>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+            return r;
+        }));
     }
     uint8_t* ws = (uint8_t*)workspace;
     W4Params p;
@@ -832,14 +833,14 @@ int vk_bf16_gemm_packed(const void* packed, const void* x, int ldx, void* y, int
     const W4Plan pl = w4_plan(N, K, Fmt<1>::kCtasPerSM);
     if (pl.NSB > (int)(kCounterBytes / 4)) return VK_EINVAL;
     if (workspace_bytes < w4_ws_bytes(pl)) return VK_ENOSPC;
-    static bool configured = false;
-    if (!configured) {
-        VK_CUDA(cudaFuncSetAttribute(w4_gemm_kernel<1, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes<1>()));
-        VK_CUDA(cudaFuncSetAttribute(w4_gemm_kernel<1, 1>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
-        VK_CUDA(cudaFuncSetAttribute(w4_gemm_kernel<2, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes<1>()));
-        VK_CUDA(cudaFuncSetAttribute(w4_gemm_kernel<2, 1>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
-        configured = true;
-    }
+    static PerDeviceOnce once;
+    VK_CUDA(once.run([] {
+        cudaError_t r = cudaFuncSetAttribute(w4_gemm_kernel<1, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes<1>());
+        if (r == cudaSuccess) r = cudaFuncSetAttribute(w4_gemm_kernel<1, 1>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+        if (r == cudaSuccess) r = cudaFuncSetAttribute(w4_gemm_kernel<2, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes<1>());
+        if (r == cudaSuccess) r = cudaFuncSetAttribute(w4_gemm_kernel<2, 1>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+        return r;
+    }));
     uint8_t* ws = (uint8_t*)workspace;
     for (int m0 = 0; m0 < M; m0 += 16) {
         const int m = M - m0 < 16 ? M - m0 : 16;

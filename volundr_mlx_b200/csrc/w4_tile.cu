@@ -328,14 +328,14 @@ int vk_w4_gemm_tile(const void* packed, const void* x, int ldx, void* y, int ldy
     if (M <= 0 || N <= 0 || K <= 0 || K % 64 != 0 || ldx % 8 != 0 || ldx < K || ldy < N) return VK_EINVAL;
     if (((uintptr_t)x & 15) || ((uintptr_t)packed & 15) || workspace == nullptr || ((uintptr_t)workspace & 15)) return VK_EINVAL;
     if (workspace_bytes < vk_w4_tile_workspace_bytes(M, K)) return VK_ENOSPC;
-    static bool configured = false;
-    if (!configured) {
-        VK_CUDA((cudaFuncSetAttribute(w4_tile_kernel<256, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TileCfg<256, 1>::kSmem)));
-        VK_CUDA((cudaFuncSetAttribute(w4_tile_kernel<256, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TileCfg<256, 2>::kSmem)));
-        VK_CUDA((cudaFuncSetAttribute(w4_tile_kernel<64, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TileCfg<64, 1>::kSmem)));
-        VK_CUDA((cudaFuncSetAttribute(w4_tile_kernel<64, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TileCfg<64, 2>::kSmem)));
-        configured = true;
-    }
+    static PerDeviceOnce once;
+    VK_CUDA(once.run([] {
+        cudaError_t r = cudaFuncSetAttribute(w4_tile_kernel<256, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TileCfg<256, 1>::kSmem);
+        if (r == cudaSuccess) r = cudaFuncSetAttribute(w4_tile_kernel<256, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TileCfg<256, 2>::kSmem);
+        if (r == cudaSuccess) r = cudaFuncSetAttribute(w4_tile_kernel<64, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TileCfg<64, 1>::kSmem);
+        if (r == cudaSuccess) r = cudaFuncSetAttribute(w4_tile_kernel<64, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TileCfg<64, 2>::kSmem);
+        return r;
+    }));
     const int G = K / 64, MTn = (M + kTileM - 1) / kTileM, NSB = (N + 255) / 256;
     // (the split-K kernel pays for weights with few 256-row blocks, where whole blocks per CTA leave most SMs idle: its
     // partial sums are 128 KB per block and range, which costs more than it saves once every SM has a block of its own)
