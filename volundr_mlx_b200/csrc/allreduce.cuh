@@ -56,18 +56,10 @@ __device__ __forceinline__ size_t ar_slot_off(const VkArDesc& d, int slot, int s
 // All threads of the CTA that owns part `part` of `nparts` (<= kArParts) equal parts of row b call this after
 // griddepcontrol.wait. `row` = the rank's partial [D] bf16 in local memory; on return the part holds the sum over ranks.
 // (D / nparts) % 8 == 0. Every part has its own flag word, so the CTAs of a row need not wait for one another.
-// WIDE (a separate instantiation of the calling kernel, chosen on the host for more than four ranks): the lines of all
-// peers are polled together instead of one peer after the other. A poll is a round trip to L2: one after the other they
-// cost `world - 1` round trips even when every line has long arrived (measured at 8 ranks: 13.6 us per exchange against
-// 5 at 4 ranks); together they cost one, plus one more to read the lines in rank order. It is a variant of its own
-// because the extra registers slow the kernels down where they are not needed (one rank: 10.93 -> 11.06 ms per step).
-template <bool WIDE>
 __device__ __forceinline__ void ar_reduce_span(const VkArCall& a, __nv_bfloat16* row, int b, int D, int part, int nparts);
-template <bool WIDE>
 __device__ __forceinline__ void ar_reduce_row(const VkArCall& a, __nv_bfloat16* row, int b, int D) {
-    ar_reduce_span<WIDE>(a, row, b, D, 0, 1);
+    ar_reduce_span(a, row, b, D, 0, 1);
 }
-template <bool WIDE>
 __device__ __forceinline__ void ar_reduce_span(const VkArCall& a, __nv_bfloat16* row, int b, int D, int part, int nparts) {
     const VkArDesc& d = a.d;
     if (d.world <= 1) return;
@@ -92,56 +84,6 @@ __device__ __forceinline__ void ar_reduce_span(const VkArCall& a, __nv_bfloat16*
     const uint8_t* local = d.slots[d.rank];
     for (int v = v_begin + threadIdx.x; v < nvec; v += blockDim.x) {
         float s[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-        if constexpr (WIDE) {
-            // wait until the lines of every peer carry this call's number: only a ready bit per peer is kept
-            uint32_t pend = 0;
-#pragma unroll
-            for (int p = 0; p < kArMaxWorld; p++)
-                if (p < d.world && p != d.rank) pend |= 1u << p;
-            uint32_t polls = 0;
-            while (pend) {
-#pragma unroll
-                for (int base = 0; base < kArMaxWorld; base += 4) {
-                    uint32_t n0[4], n1[4], n2[4], n3[4];   // the four sequence words of a peer's two lines
-#pragma unroll
-                    for (int q = 0; q < 4; q++) {
-                        const int p = base + q;
-                        n0[q] = n1[q] = n2[q] = n3[q] = seq;
-                        if ((pend >> p) & 1u) {
-                            const uint4* src = reinterpret_cast<const uint4*>(local + ar_slot_off(d, slot, p, b, D)) + 2 * (size_t)v;
-                            uint32_t x0, x1;
-                            asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(x0), "=r"(n0[q]), "=r"(x1), "=r"(n1[q]) : "l"(src) : "memory");
-                            asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(x0), "=r"(n2[q]), "=r"(x1), "=r"(n3[q]) : "l"(src + 1) : "memory");
-                        }
-                    }
-#pragma unroll
-                    for (int q = 0; q < 4; q++)
-                        if (n0[q] == seq && n1[q] == seq && n2[q] == seq && n3[q] == seq) pend &= ~(1u << (base + q));
-                }
-                if (pend) {
-                    if (budget == 0) { ok = false; break; }   // give up: the host will see the status
-                    budget--;
-                    if (++polls > 32) __nanosleep(100);
-                }
-            }
-            // all lines are in: read them again in rank order (the same bits on every rank); these loads overlap
-            const uint4 own = rowv[v];
-#pragma unroll
-            for (int p = 0; p < kArMaxWorld; p++) {
-                if (p < d.world) {
-                    uint4 u = own;
-                    if (p != d.rank) {
-                        const uint4* src = reinterpret_cast<const uint4*>(local + ar_slot_off(d, slot, p, b, D)) + 2 * (size_t)v;
-                        uint4 l0, l1;
-                        asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(l0.x), "=r"(l0.y), "=r"(l0.z), "=r"(l0.w) : "l"(src) : "memory");
-                        asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(l1.x), "=r"(l1.y), "=r"(l1.z), "=r"(l1.w) : "l"(src + 1) : "memory");
-                        u = make_uint4(l0.x, l0.z, l1.x, l1.z);
-                    }
-                    s[0] += bf_lo(u.x); s[1] += bf_hi(u.x); s[2] += bf_lo(u.y); s[3] += bf_hi(u.y);
-                    s[4] += bf_lo(u.z); s[5] += bf_hi(u.z); s[6] += bf_lo(u.w); s[7] += bf_hi(u.w);
-                }
-            }
-        } else {
         for (int p = 0; p < d.world; p++) {
             uint4 u;
             if (p == d.rank) {
@@ -162,7 +104,6 @@ __device__ __forceinline__ void ar_reduce_span(const VkArCall& a, __nv_bfloat16*
             }
             s[0] += bf_lo(u.x); s[1] += bf_hi(u.x); s[2] += bf_lo(u.y); s[3] += bf_hi(u.y);
             s[4] += bf_lo(u.z); s[5] += bf_hi(u.z); s[6] += bf_lo(u.w); s[7] += bf_hi(u.w);
-        }
         }
         uint4 o;
         o.x = pack_bf2(s[0], s[1]); o.y = pack_bf2(s[2], s[3]); o.z = pack_bf2(s[4], s[5]); o.w = pack_bf2(s[6], s[7]);

@@ -270,7 +270,6 @@ __global__ void __launch_bounds__(1024) mhc_mix_norm_kernel(const MixParams p) {
 // ------------------------------------------------------------------------------------------------ add + norm
 // h2 = bf(x + r); hn = bf(h2 * rsqrt(mean h2^2 + eps) * (off + w))      (volundr.py:893-899)
 // Tensor-parallel: r holds this rank's partial product; the row's sum over ranks is formed first (allreduce.cuh).
-template <bool WIDE>
 __global__ void __launch_bounds__(1024) add_rmsnorm_kernel(const __nv_bfloat16* __restrict__ x,
                                                            const __nv_bfloat16* r,
                                                            const __nv_bfloat16* __restrict__ w,
@@ -289,7 +288,7 @@ __global__ void __launch_bounds__(1024) add_rmsnorm_kernel(const __nv_bfloat16* 
         if (r != nullptr) ld8(x + base + k0, x0);
     }
     pdl_wait();
-    if (r != nullptr) ar_reduce_row<WIDE>(ar, const_cast<__nv_bfloat16*>(r) + base, blockIdx.x, D);
+    if (r != nullptr) ar_reduce_row(ar, const_cast<__nv_bfloat16*>(r) + base, blockIdx.x, D);
     float ss = 0.f;
     float v0[8];
     for (int k = k0; k < D; k += blockDim.x * 8) {
@@ -424,14 +423,13 @@ struct CombineParams {
     VkArCall ar;                   // tensor-parallel: m is this rank's partial product, summed over ranks first
 };
 
-template <bool WIDE>
 __global__ void __launch_bounds__(1024) mhc_combine_norm_kernel(const CombineParams p) {
     __shared__ float red[kRowMaxWarps];
     pdl_launch_dependents();
     pdl_wait();
     const int b = blockIdx.x, D = p.D;
     const size_t base = (size_t)b * D;
-    ar_reduce_row<WIDE>(p.ar, const_cast<__nv_bfloat16*>(p.m) + base, b, D);
+    ar_reduce_row(p.ar, const_cast<__nv_bfloat16*>(p.m) + base, b, D);
     const int k0 = threadIdx.x * 8;
     const int stride = blockDim.x * 8;
     float gate = 0.f;
@@ -532,7 +530,7 @@ constexpr int kBoundaryThreads = 640;
 // 16-byte pieces; row-wide sums (norms, the engram gate, the 24 dyn products) are formed per CTA and then added over
 // the cluster through distributed shared memory in rank order, the 4 x 4 Sinkhorn runs in every CTA (identical inputs,
 // identical results) and rank 0 stores it. The row's arithmetic is spread over four SMs instead of one.
-template <int CL, bool WIDE>
+template <int CL>
 __global__ void __launch_bounds__(kBoundaryThreads) mhc_boundary_kernel(const BoundaryParams q) {
     __shared__ float red[kRowMaxWarps];
     __shared__ float part[24 * 32];
@@ -591,7 +589,7 @@ __global__ void __launch_bounds__(kBoundaryThreads) mhc_boundary_kernel(const Bo
     }
     pdl_wait();
     VK_TS(3, 1);
-    ar_reduce_span<WIDE>(p.ar, const_cast<__nv_bfloat16*>(p.m) + base, b, D, crank, CL);
+    ar_reduce_span(p.ar, const_cast<__nv_bfloat16*>(p.m) + base, b, D, crank, CL);
     VK_TS(3, 2);
     float gate = 0.f;
     if (on) ld8(p.m + base + k, mv);
@@ -909,10 +907,9 @@ int vk_add_rmsnorm_ar(const void* x, void* r, const void* w, void* h2, void* hn,
     if (B <= 0 || D <= 0 || D % 8 != 0 || (xrec_hn != nullptr && (D % 64 != 0 || B > 16))) return VK_EINVAL;
     VkArCall a;
     if (ar_call(r != nullptr ? ar : nullptr, call, B, D, &a) != VK_OK) return VK_EINVAL;
-    // (more than four ranks: the variant that polls all peers together, see allreduce.cuh)
-    return (int)vk_launch(a.d.world > 4 ? add_rmsnorm_kernel<true> : add_rmsnorm_kernel<false>, dim3(B), dim3(row_threads(D)), 0,
-                          stream, (const __nv_bfloat16*)x, (const __nv_bfloat16*)r, (const __nv_bfloat16*)w, (__nv_bfloat16*)h2,
-                          (__nv_bfloat16*)hn, (uint8_t*)xrec_hn, D, eps, offset ? 1.f : 0.f, a);
+    return (int)vk_launch(add_rmsnorm_kernel, dim3(B), dim3(row_threads(D)), 0, stream, (const __nv_bfloat16*)x,
+                          (const __nv_bfloat16*)r, (const __nv_bfloat16*)w, (__nv_bfloat16*)h2, (__nv_bfloat16*)hn,
+                          (uint8_t*)xrec_hn, D, eps, offset ? 1.f : 0.f, a);
 }
 
 int vk_add_rmsnorm(const void* x, const void* r, const void* w, void* h2, void* hn, void* xrec_hn, int B, int D, float eps,
@@ -949,8 +946,7 @@ int vk_mhc_combine_norm_ar(void* H, const void* h2, void* m, const void* x_in, c
                        (const __nv_bfloat16*)eng_gate_w, (const __nv_bfloat16*)eng_gate_b, (__nv_bfloat16*)y_out, D,
                        final_norm, eps, VkArCall{}};
     if (ar_call(ar, call, B, D, &p.ar) != VK_OK) return VK_EINVAL;
-    return (int)vk_launch(p.ar.d.world > 4 ? mhc_combine_norm_kernel<true> : mhc_combine_norm_kernel<false>, dim3(B),
-                          dim3(row_threads(D)), 0, stream, p);
+    return (int)vk_launch(mhc_combine_norm_kernel, dim3(B), dim3(row_threads(D)), 0, stream, p);
 }
 
 int vk_mhc_combine_norm(void* H, const void* h2, const void* m, const void* x_in, const float* post, const float* res,
@@ -974,13 +970,11 @@ int vk_mhc_boundary_ar(void* H, const void* h2, void* m, void* x_in, float* post
     q.w_dyn = (const __nv_bfloat16*)w_dyn; q.pre_s = (const __nv_bfloat16*)pre_s; q.post_s = (const __nv_bfloat16*)post_s;
     q.res_s = (const __nv_bfloat16*)res_s; q.w_in = (const __nv_bfloat16*)w_in; q.x_in_out = (__nv_bfloat16*)x_in;
     q.h = (__nv_bfloat16*)h; q.xrec_h = (uint8_t*)xrec_h; q.post_out = post; q.res_out = res; q.iters = iters;
-    const bool wide = q.c.ar.d.world > 4;
     // a cluster of four CTAs per row when the row's pieces split into four whole x-record groups per CTA
     if (g_boundary_cluster && D % 256 == 0 && (D / 32) % 32 == 0)
-        return (int)vk_launch_cluster(wide ? mhc_boundary_kernel<4, true> : mhc_boundary_kernel<4, false>, dim3(B * 4), dim3(D / 32), 4,
-                                      0, stream, q);
+        return (int)vk_launch_cluster(mhc_boundary_kernel<4>, dim3(B * 4), dim3(D / 32), 4, 0, stream, q);
     const int threads = ((D / 8 + 31) / 32) * 32;
-    return (int)vk_launch(wide ? mhc_boundary_kernel<1, true> : mhc_boundary_kernel<1, false>, dim3(B), dim3(threads), 0, stream, q);
+    return (int)vk_launch(mhc_boundary_kernel<1>, dim3(B), dim3(threads), 0, stream, q);
 }
 
 int vk_mhc_boundary(void* H, const void* h2, const void* m, void* x_in, float* post, float* res, const void* w_next,
