@@ -3,8 +3,7 @@ for the ranks. Ranks world - 1 .. 1 run first, one after the other, with a small
 rows (data and sequence numbers) into every other region, then its own wait for the ranks that have not run yet runs
 out, which must surface as status 4 (the bounded-wait path; the device stays usable). "Rank 0" runs last, finds every
 other rank's rows in place and must produce exactly the plain kernel's result on the bf16 of the fp32 sum, in rank
-order, of the partial rows. Two ranks take the kernels' one-peer-after-the-other polling, six and eight the variant
-that polls all peers together. The real two-process exchange is covered by tests/test_tp_gpu.py."""
+order, of the partial rows (two, six and eight ranks). The real two-process exchange is covered by tests/test_tp_gpu.py."""
 import ctypes
 
 import pytest
