@@ -80,6 +80,23 @@ def test_engine_rows_are_independent_under_queueing(monkeypatch):
     assert eng.reserved == 0 and eng.bc.B == 0
 
 
+def test_warm_graphs_leaves_the_engine_empty(monkeypatch):
+    """Pre-capturing steps every batch size once with placeholder rows and gives everything back: requests served
+    afterwards get the same tokens as without it."""
+    monkeypatch.setattr(E.BT, "forward", fake_forward)
+    sizes = []
+    real_forward = E.BT.forward
+    monkeypatch.setattr(E.BT, "forward", lambda m, bc, toks: (sizes.append(len(toks)), real_forward(m, bc, toks))[1])
+    eng = E.BatchEngine(FakeModel(), max_rows=3, n_pages=64, max_pages_per_row=8)
+    eng.warm_graphs()
+    assert sizes == [1, 2, 3] and eng.bc.B == 0 and not eng.bc.hist
+    prompts = [[5, 6, 7], [9], [1, 2]]
+    for p_ in prompts:
+        eng.submit(p_, 4)
+    out = eng.run()
+    assert [out[i] for i in range(3)] == [solo(p_, 4) for p_ in prompts]
+
+
 def test_engine_waits_for_pages(monkeypatch):
     monkeypatch.setattr(E.BT, "forward", fake_forward)
     eng = E.BatchEngine(FakeModel(), max_rows=4, n_pages=2, max_pages_per_row=2)

@@ -92,6 +92,19 @@ class BatchEngine:
         self.reserved = 0          # pages promised to the running requests (their worst case)
         self._next = 0
 
+    def warm_graphs(self):
+        """Captures the decode step's CUDA graph for every batch size 1 .. max_rows before any request arrives (a graph
+        is captured the first time its batch size is stepped, about a third of a second for the 72-layer model, which
+        would otherwise fall between two decode steps of the running rows). Placeholder rows join one by one, take one
+        step each time, and leave; their pages go back to the pool. The reference pays this cost per step instead (it
+        rebuilds a lazy graph every step and pipelines the host work, batch.py:518-554)."""
+        assert not self.running and not self.prefilling, "only on an idle engine"
+        keys = [("warm", i) for i in range(self.bc.S)]
+        for i, k in enumerate(keys):
+            self.bc.apply(join=[k])
+            BT.forward(self.model, self.bc, [0] * (i + 1))
+        self.bc.apply(leave=keys)
+
     def _pages(self, r: Request) -> int:
         return (len(r.prompt) + r.max_new + PAGE - 1) // PAGE
 

@@ -31,6 +31,7 @@ def main():
     ap.add_argument("--layers", type=int, default=0, help="0 = all 72")
     ap.add_argument("--slice-ms", type=float, default=0.0,
                     help="> 0: prompts are prefilled on a cache of their own in time slices of this many ms between decode steps")
+    ap.add_argument("--warm-graphs", action="store_true", help="capture the step's graph for every batch size before the clock starts")
     a = ap.parse_args()
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(dev)
@@ -46,6 +47,8 @@ def main():
     pages_row = (int(lens.max()) + a.new) // 64 + 2
     eng = BatchEngine(model, max_rows=a.rows, n_pages=int(sum((n + a.new) // 64 + 2 for n in lens)) + 8,
                       max_pages_per_row=pages_row, prefill_chunk=a.prefill_chunk, slice_ms=a.slice_ms)
+    if a.warm_graphs:
+        eng.warm_graphs()
     for n in lens:
         eng.submit(rng.integers(0, args.vocab_valid, size=int(n)).tolist(), a.new)
     torch.cuda.synchronize(dev)
