@@ -46,7 +46,8 @@ int vk_w4_dequant(const void* w, const void* scales, const void* biases, int N, 
                   vk_stream_t stream);
 /* Workspace bytes vk_w4_gemm needs for this shape (arrival counters, the activation records, partial sums of ranges
  * that split a block of rows over K). The first 16 KiB of the workspace must be zero before the first call and are
- * left zero by every call. */
+ * left zero by every call (a call whose bounded wait ran out, reported through the status word, may leave a counter
+ * behind: zero them again before the buffer is used by another launch). */
 size_t vk_w4_workspace_bytes(int M, int N, int K);
 /* y[M, ldy] (bf16) = x[M, ldx] (bf16) . dequant(W)^T, fp32 accumulation. ldx a multiple of 8, x 16-byte aligned. */
 int vk_w4_gemm(const void* packed, const void* x, int ldx, void* y, int ldy, int M, int N, int K, void* workspace,

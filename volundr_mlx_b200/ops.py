@@ -148,4 +148,8 @@ def check_status(device=None):
     _lib.check(L.vk_status_fetch(_p(buf), _stream()), "vk_status_fetch")
     code = int(buf.item())
     if code:
+        # a wait that ran out may have left a split-K arrival counter behind: put the scratch buffers' heads back to zero
+        for pool in (_ws, _tile_ws):
+            if key in pool:
+                pool[key][: 1 << 14].zero_()
         raise RuntimeError("volundr_b200 device status: " + L.vk_status_string(code).decode())
