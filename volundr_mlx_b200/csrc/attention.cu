@@ -813,7 +813,7 @@ __global__ void __launch_bounds__(128) attend_decode_tc_kernel(const AttendParam
     __shared__ __align__(16) __nv_bfloat16 Vs[kPage * kRowStride];
     __shared__ __align__(16) __nv_bfloat16 Qs[16 * kRowStride];
     __shared__ __align__(16) __nv_bfloat16 Ps[16 * kPStride];
-    __shared__ float sc[8 * kPage];
+    __shared__ __align__(16) float sc[8 * kPage];
     __shared__ float s_aold[8], s_m[8], s_l[8];
     __shared__ const __nv_bfloat16* rowK[2][kPage];
     __shared__ const __nv_bfloat16* rowV[2][kPage];
@@ -857,24 +857,43 @@ __global__ void __launch_bounds__(128) attend_decode_tc_kernel(const AttendParam
             *reinterpret_cast<const uint4*>(p.q + ((size_t)b * g.Hq + (size_t)kv * G + h) * kD + c * 8);
     }
     __syncthreads();
-    uint32_t qf[8][4];   // A fragments of Q for the 8 k-steps of the head dim
+    // Both products put the long side on the M side of mma.sync and the (up to 8) query heads of the kv head on its N
+    // side: S^T = K Q^T (16 keys x 8 heads per instruction) and O^T = V^T P^T (16 dims x 8 heads), 16 instructions
+    // per warp and unit of 64 keys instead of the 32 of the heads-as-rows arrangement, which left 11 of 16 rows unused
+    // at five heads (the kernel is bound by its mma.sync and instruction stream, not by memory).
+    static_assert(G <= 8, "the heads of a kv head are the N side of the instruction");
+    uint32_t qb[4][4];   // B fragments of Q^T: [pair of k-steps][b0, b1 of the first, b0, b1 of the second]
     {
-        const int row = (lane & 7) + ((lane >> 3) & 1) * 8, col = (lane >> 4) * 8;
+        const int row = lane & 7, col = (lane >> 3) * 8;
 #pragma unroll
-        for (int ks = 0; ks < 8; ks++) ldsm_x4(qf[ks], smem_u32(Qs + row * kRowStride + ks * 16 + col));
+        for (int kp = 0; kp < 4; kp++) ldsm_x4(qb[kp], smem_u32(Qs + row * kRowStride + kp * 32 + col));
     }
-    float o[4][4];       // O[head gq (and gq + 8, unused)][dims 32 warp + 8 nt + 2 tq ..]
+    float o[2][4];       // O^T[dims 32 warp + 16 mt + gq (and + 8)][heads 2 tq, 2 tq + 1]
 #pragma unroll
-    for (int nt = 0; nt < 4; nt++)
+    for (int mt = 0; mt < 2; mt++)
 #pragma unroll
-        for (int e = 0; e < 4; e++) o[nt][e] = 0.f;
+        for (int e = 0; e < 4; e++) o[mt][e] = 0.f;
     if (t < 8) s_aold[t] = 0.f;
 
     // Row pointers of a unit (window page, far block's tokens, or 64 pooled far blocks) into rk / rv; returns its rows.
-    auto setup_unit = [&](int u, const __nv_bfloat16** rk, const __nv_bfloat16** rv) -> int {
+    // The page (and far block) of a unit, fetched one unit ahead of its use: two dependent loads (selected block -> page
+    // table) that would otherwise sit between every two units of a CTA. (Pooled far blocks: one block per thread, fetched
+    // where they are used.)
+    auto fetch_idx = [&](int u, int& page_raw, int& tok0) {
+        page_raw = 0;
+        tok0 = 0;
+        if (u >= U) return;
+        if (u < nwp) {
+            page_raw = p.table[b * g.max_pages + wp0 + u];
+        } else if (g.far_tokens) {
+            tok0 = sel[u - nwp] * g.C;
+            page_raw = p.table[b * g.max_pages + tok0 / kPage];
+        }
+    };
+    auto setup_unit = [&](int u, const __nv_bfloat16** rk, const __nv_bfloat16** rv, int page_raw, int tok0) -> int {
         int nrows;
         if (u < nwp) {
-            const int page = checked_page(p.table[b * g.max_pages + wp0 + u], p.n_pages);
+            const int page = checked_page(page_raw, p.n_pages);
             const int ra = u == 0 ? lo % kPage : 0;
             const int rb = u == nwp - 1 ? pos % kPage : kPage - 1;
             nrows = rb - ra + 1;
@@ -884,9 +903,7 @@ __global__ void __launch_bounds__(128) attend_decode_tc_kernel(const AttendParam
                 rv[t] = p.V + off;
             }
         } else if (g.far_tokens) {
-            const int j = sel[u - nwp];
-            const int tok0 = j * g.C;
-            const int page = checked_page(p.table[b * g.max_pages + tok0 / kPage], p.n_pages);
+            const int page = checked_page(page_raw, p.n_pages);
             nrows = g.C;
             if (t < nrows) {
                 const size_t off = (((size_t)page * g.KVH + kv) * kPage + tok0 % kPage + t) * kD;
@@ -918,7 +935,10 @@ __global__ void __launch_bounds__(128) attend_decode_tc_kernel(const AttendParam
     // unit's K is requested as soon as this unit's scores are out, its V as soon as this unit's P V is done.
     int nrows = 0, cur = 0;
     AT_T(p0);
-    if (split < U) nrows = setup_unit(split, rowK[0], rowV[0]);
+    int pg = 0, tk = 0;
+    fetch_idx(split, pg, tk);
+    if (split < U) nrows = setup_unit(split, rowK[0], rowV[0], pg, tk);
+    fetch_idx(split + p.nsplit, pg, tk);   // (used at the top of the first iteration)
     __syncthreads();
     AT_T(p1);
     AT_ACC(0, tr_start, p0); AT_ACC(1, p0, p1);
@@ -931,50 +951,58 @@ __global__ void __launch_bounds__(128) attend_decode_tc_kernel(const AttendParam
         const int un = u + p.nsplit;
         int nrows_next = 0;
         AT_T(u0);
-        if (un < U) nrows_next = setup_unit(un, rowK[cur ^ 1], rowV[cur ^ 1]);
+        if (un < U) nrows_next = setup_unit(un, rowK[cur ^ 1], rowV[cur ^ 1], pg, tk);
+        fetch_idx(un + p.nsplit, pg, tk);   // (on its way during this unit's arithmetic)
         AT_T(u1);
         cp_async_wait1();   // K of this unit (V may still be on its way)
         __syncthreads();
         AT_T(u2);
         AT_ACC(2, u0, u1); AT_ACC(3, u1, u2);
-        // ---- S = Q K^T: warp w takes keys 16 w .. 16 w + 15
+        // ---- S^T = K Q^T: warp w takes keys 16 w .. 16 w + 15 (the M side), all heads (the N side)
         {
-            float sa[2][4] = {};
-            const int mat = lane >> 3, r = lane & 7;
-            const uint32_t kaddr = smem_u32(Ks + (16 * warp + (mat >> 1) * 8 + r) * kRowStride + (mat & 1) * 8);
+            float sa[4] = {0.f, 0.f, 0.f, 0.f};   // keys 16 w + gq (and + 8) x heads 2 tq, 2 tq + 1
+            const uint32_t kaddr = smem_u32(Ks + (16 * warp + (lane & 7) + ((lane >> 3) & 1) * 8) * kRowStride + (lane >> 4) * 8);
 #pragma unroll
             for (int ks = 0; ks < 8; ks++) {
-                uint32_t kb[4];
-                ldsm_x4(kb, kaddr + ks * 32);
-                mma16816(sa[0], qf[ks], kb[0], kb[1]);
-                mma16816(sa[1], qf[ks], kb[2], kb[3]);
+                uint32_t ka[4];
+                ldsm_x4(ka, kaddr + ks * 32);
+                mma16816(sa, ka, qb[ks >> 1][2 * (ks & 1)], qb[ks >> 1][2 * (ks & 1) + 1]);
             }
-            if (gq < G) {
 #pragma unroll
-                for (int nt = 0; nt < 2; nt++) {
-                    const int key = 16 * warp + 8 * nt + 2 * tq;
-                    sc[gq * kPage + key] = key < nrows ? sa[nt][0] * p.scale : -INFINITY;
-                    sc[gq * kPage + key + 1] = key + 1 < nrows ? sa[nt][1] * p.scale : -INFINITY;
-                }
+            for (int e = 0; e < 4; e++) {
+                const int h = 2 * tq + (e & 1), key = 16 * warp + gq + 8 * (e >> 1);
+                if (h < G) sc[h * kPage + key] = key < nrows ? sa[e] * p.scale : -INFINITY;
             }
         }
         __syncthreads();
         issue_rows(Ks, rowK[cur ^ 1], nrows_next);   // every warp is done with this unit's K
-        // ---- softmax pieces per head (warp w: heads w, w + 4): running max / sum, probabilities as bf16
-        for (int h = warp; h < G; h += 4) {
-            const float s0 = sc[h * kPage + lane], s1 = sc[h * kPage + 32 + lane];
-            const float mx = warp_max(fmaxf(s0, s1));   // finite: a unit has at least one row
-            const float m_old = s_m[h];
-            const float m_new = fmaxf(m_old, mx);
-            const float p0 = bfr(__expf(s0 - m_new)), p1 = bfr(__expf(s1 - m_new));
-            Ps[h * kPStride + lane] = f2bf(p0);
-            Ps[h * kPStride + 32 + lane] = f2bf(p1);
-            const float sum = warp_sum(p0 + p1);
-            if (lane == 0) {
-                const float a_old = m_old == -INFINITY ? 0.f : __expf(m_old - m_new);
-                s_l[h] = s_l[h] * a_old + sum;
-                s_m[h] = m_new;
-                s_aold[h] = a_old;
+        // ---- softmax pieces: sixteen lanes per head (thread t: head t / 16, keys 4 (t % 16) ..): all heads in one pass
+        {
+            const int h = t >> 4, sub = t & 15;
+            if (h < G) {   // (uniform over the sixteen lanes of a head)
+                const float4 s4 = *reinterpret_cast<const float4*>(&sc[h * kPage + 4 * sub]);
+                float mx = fmaxf(fmaxf(s4.x, s4.y), fmaxf(s4.z, s4.w));   // finite for the half-warp: a unit has at least one row
+                const float m_old = s_m[h];
+                const uint32_t half_mask = 0xFFFFu << (lane & 16);
+#pragma unroll
+                for (int off = 8; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(half_mask, mx, off));
+                const float m_new = fmaxf(m_old, mx);
+                const float p0 = bfr(__expf(s4.x - m_new)), p1 = bfr(__expf(s4.y - m_new));
+                const float p2 = bfr(__expf(s4.z - m_new)), p3 = bfr(__expf(s4.w - m_new));
+                uint2 pk;
+                pk.x = pack_bf2(p0, p1);
+                pk.y = pack_bf2(p2, p3);
+                *reinterpret_cast<uint2*>(Ps + h * kPStride + 4 * sub) = pk;
+                float sum = (p0 + p1) + (p2 + p3);
+#pragma unroll
+                for (int off = 8; off > 0; off >>= 1) sum += __shfl_xor_sync(half_mask, sum, off);
+                __syncwarp(half_mask);   // (every lane has read s_m[h])
+                if (sub == 0) {
+                    const float a_old = m_old == -INFINITY ? 0.f : __expf(m_old - m_new);
+                    s_l[h] = s_l[h] * a_old + sum;
+                    s_m[h] = m_new;
+                    s_aold[h] = a_old;
+                }
             }
         }
         AT_T(u3);
@@ -982,23 +1010,27 @@ __global__ void __launch_bounds__(128) attend_decode_tc_kernel(const AttendParam
         __syncthreads();
         AT_T(u4);
         AT_ACC(4, u2, u3); AT_ACC(5, u3, u4);
-        // ---- O = O * a_old + P V: warp w takes dims 32 w .. 32 w + 31
+        // ---- O^T = O^T * a_old + V^T P^T: warp w takes dims 32 w .. 32 w + 31 (the M side, two tiles of 16)
         {
-            const float a = s_aold[gq];
+            const float a0 = s_aold[2 * tq], a1 = s_aold[2 * tq + 1];
 #pragma unroll
-            for (int nt = 0; nt < 4; nt++) { o[nt][0] *= a; o[nt][1] *= a; }
-            const int prow = (lane & 7) + ((lane >> 3) & 1) * 8, pcol = (lane >> 4) * 8;
-            const int mat = lane >> 3, r = lane & 7;
+            for (int mt = 0; mt < 2; mt++) { o[mt][0] *= a0; o[mt][1] *= a1; o[mt][2] *= a0; o[mt][3] *= a1; }
+            // A = V^T through transposing loads of V's [key][dim] tile; B = P^T from the probability tile's [head][key] rows
+            const uint32_t vaddr = smem_u32(Vs + ((lane & 7) + (lane >> 4) * 8) * kRowStride + 32 * warp + ((lane >> 3) & 1) * 8);
+            const uint32_t paddr = smem_u32(Ps + (lane & 7) * kPStride + (lane >> 3) * 8);
 #pragma unroll
-            for (int ks = 0; ks < 4; ks++) {
-                uint32_t pa[4];
-                ldsm_x4(pa, smem_u32(Ps + prow * kPStride + ks * 16 + pcol));
+            for (int kp = 0; kp < 2; kp++) {   // two k-steps of 16 keys per load of P^T
+                uint32_t pb[4];
+                ldsm_x4(pb, paddr + kp * 64);
 #pragma unroll
-                for (int half = 0; half < 2; half++) {
-                    uint32_t vb[4];
-                    ldsm_x4_t(vb, smem_u32(Vs + (ks * 16 + (mat & 1) * 8 + r) * kRowStride + 32 * warp + half * 16 + (mat >> 1) * 8));
-                    mma16816(o[2 * half], pa, vb[0], vb[1]);
-                    mma16816(o[2 * half + 1], pa, vb[2], vb[3]);
+                for (int kk = 0; kk < 2; kk++) {
+                    const int ks = 2 * kp + kk;
+#pragma unroll
+                    for (int mt = 0; mt < 2; mt++) {
+                        uint32_t va[4];
+                        ldsm_x4_t(va, vaddr + (uint32_t)(ks * 16 * kRowStride + mt * 16) * 2u);
+                        mma16816(o[mt], va, pb[2 * kk], pb[2 * kk + 1]);
+                    }
                 }
             }
         }
@@ -1019,11 +1051,13 @@ __global__ void __launch_bounds__(128) attend_decode_tc_kernel(const AttendParam
     }
 #endif
     float* out = p.part + (((size_t)b * g.KVH + kv) * p.nsplit + split) * G * (kD + 2);
-    if (gq < G) {
 #pragma unroll
-        for (int nt = 0; nt < 4; nt++)
-            *reinterpret_cast<float2*>(out + gq * (kD + 2) + 32 * warp + 8 * nt + 2 * tq) = make_float2(o[nt][0], o[nt][1]);
-    }
+    for (int mt = 0; mt < 2; mt++)
+#pragma unroll
+        for (int e = 0; e < 4; e++) {
+            const int h = 2 * tq + (e & 1), dim = 32 * warp + 16 * mt + gq + 8 * (e >> 1);
+            if (h < G) out[h * (kD + 2) + dim] = o[mt][e];
+        }
     if (t < G) { out[t * (kD + 2) + kD] = s_m[t]; out[t * (kD + 2) + kD + 1] = s_l[t]; }
 }
 
