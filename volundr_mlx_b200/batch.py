@@ -301,6 +301,14 @@ class BatchCache:
             self.engram_prev[b, : self.keep] = eng[2].to(dev)[0]
         self._pos[b] = P
 
+    def attend_splits(self, B, bcsa):
+        """KV splits of the decode attention for B rows: about four CTAs per SM in all for the sparse layers (a CTA's fixed
+        part, staging Q and resolving its first unit, is a quarter of its life at 16 splits and 16 rows; measured: 4 splits
+        10.76 ms per step, 8: 10.80, 16: 10.82), never more than nsplit_bcsa; the dense layer keeps its own count."""
+        if not bcsa:
+            return self.nsplit_dense
+        return max(1, min(self.nsplit_bcsa, -(-592 // (B * self.model.KVH))))
+
     def capture_row(self, key, dcache=None, logits=None) -> SS.State:
         """Row `key` as a session.State of own copies (batch.py:488-510; layout in volundr_mlx_b200/session.py): the
         position, per layer the KDA conv window and state / the row's K, V (by position), pooled blocks, pooled and
@@ -495,7 +503,7 @@ def _launch_step(model: Model, bc: BatchCache, capture=()):
                                     st), "vk_bcsa_select")
             ck(L.vk_attend_decode(ctypes.byref(g), _p(bc.q), _p(lst["K"]), _p(lst["V"]), _p(lst.get("PK")),
                                   _p(lst.get("PV")), _p(bc.pos), _p(bc.table), _p(bc.sel), _p(bc.nsel), _p(bc.proj),
-                                  bc.proj.stride(0), _p(bc.part), bc.nsplit_bcsa if bcsa else bc.nsplit_dense, _p(bc.mix),
+                                  bc.proj.stride(0), _p(bc.part), bc.attend_splits(B, bcsa), _p(bc.mix),
                                   _p(bc.xr_mix) if fx else None, B, st), "vk_attend_decode")
         mixv = bc.mix[:, :nmix]
         gemm(mixv, w["out"], bc.r, bc.xr_mix)

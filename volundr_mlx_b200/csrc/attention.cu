@@ -842,11 +842,8 @@ __global__ void __launch_bounds__(128) attend_decode_tc_kernel(const AttendParam
     const int nfu = g.far_tokens ? nf : (nf + kPage - 1) / kPage;
     const int U = nwp + nfu;
 
-    // zero the tiles once (rows a unit does not fill must stay finite), stage Q (rows >= G zero)
-    for (int i = t; i < kPage * kRowStride / 8; i += 128) {
-        reinterpret_cast<uint4*>(Ks)[i] = make_uint4(0, 0, 0, 0);
-        reinterpret_cast<uint4*>(Vs)[i] = make_uint4(0, 0, 0, 0);
-    }
+    // stage Q (rows >= G zero); the K / V rows the FIRST unit does not fill are zeroed below (rows a unit does not fill
+    // must be finite; later units find the rows of earlier ones there)
     for (int i = t; i < 16 * kRowStride / 8; i += 128) reinterpret_cast<uint4*>(Qs)[i] = make_uint4(0, 0, 0, 0);
     for (int i = t; i < 16 * kPStride / 8; i += 128) reinterpret_cast<uint4*>(Ps)[i] = make_uint4(0, 0, 0, 0);
     if (t < 8) { s_m[t] = -INFINITY; s_l[t] = 0.f; }
@@ -939,6 +936,10 @@ __global__ void __launch_bounds__(128) attend_decode_tc_kernel(const AttendParam
     fetch_idx(split, pg, tk);
     if (split < U) nrows = setup_unit(split, rowK[0], rowV[0], pg, tk);
     fetch_idx(split + p.nsplit, pg, tk);   // (used at the top of the first iteration)
+    for (int i = nrows * (kRowStride / 8) + t; i < kPage * kRowStride / 8; i += 128) {
+        reinterpret_cast<uint4*>(Ks)[i] = make_uint4(0, 0, 0, 0);
+        reinterpret_cast<uint4*>(Vs)[i] = make_uint4(0, 0, 0, 0);
+    }
     __syncthreads();
     AT_T(p1);
     AT_ACC(0, tr_start, p0); AT_ACC(1, p0, p1);
