@@ -2,10 +2,10 @@
 // arithmetic, work split and result as w4_gemm_kernel<MT, 0> (acc += s * (x_g . u_g) + b * sum(x_g) per 64-column group,
 // see w4_gemm.cu), but x_g . (128 + u_g) is formed by tcgen05.mma instead of mma.sync.
 //
-// Why: at 16 rows the mma.sync kernel is bound by the warps' own instruction stream: every m16n8k16 holds a warp's issue
-// slot for about 16 cycles on this architecture (sixteen of them per 1152-byte chunk), next to the 56 logic operations
-// that expand the codes. tcgen05.mma is issued by ONE thread for the whole CTA and runs beside the warps, which are
-// left with the expansion and two fused multiply-adds per output and group.
+// Why: at 16 rows the mma.sync kernel is bound by the warps' own instruction stream (188 instructions per 1152-byte
+// chunk, sixteen of them m16n8k16 at one per 8 cycles and scheduler on this architecture, a quarter of the tcgen05
+// rate, 56 of them the logic operations that expand the codes). tcgen05.mma is issued by ONE thread for the whole CTA
+// and runs beside the warps, which are left with the expansion and two fused multiply-adds per output and group.
 //
 // One CTA per SM, 18 warps:
 //   warp 0        one lane: the TMA producer of w4_gemm_kernel (9216-byte weight step + the group's x record per

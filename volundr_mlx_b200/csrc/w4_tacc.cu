@@ -3,8 +3,8 @@
 // i.e. the activations times the dequantised weights exactly as mx.dequantize returns them (bit for bit, see the
 // expansion below), the arithmetic of "dequantise, then matmul" (volundr.py:185-190 with the weights materialised).
 //
-// Why a second form beside w4_gemm_kernel<MT, 0>: mma.sync on this architecture holds a warp's issue slot for about 16
-// cycles and runs at an eighth of the tcgen05 rate, which caps that kernel at 2.9 TB/s of weights. Here the tensor
+// Why a second form beside w4_gemm_kernel<MT, 0>: mma.sync runs at a quarter of the tcgen05 rate on this architecture
+// (one m16n8k16 per 8 cycles and scheduler) and that kernel's instruction stream holds it at 2.9 TB/s of weights. Here the tensor
 // cores are driven by ONE thread (tcgen05.mma), with the roles swapped against the usual small-M arrangement: the 256
 // weight rows of a superblock are the N side of the instruction, the activation rows the M side (M = 128, of which
 // rows 0..15 are real: the rest of the operand is whatever follows the x record in shared memory and only reaches
